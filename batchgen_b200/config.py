@@ -1,0 +1,349 @@
+"""Model and engine configuration.
+
+One ``ModelConfig`` describes every supported family; fields that a family does not use
+keep their neutral default (``index_topk == 0`` means no DSA indexer, ``moe_latent_size == 0``
+means experts work in the hidden size, ``num_kv_heads > 0`` selects GQA instead of MLA).
+
+Reference parity: the reference spreads this over per-model ``config.py`` / planner files and
+``batchgen/config/config.py:26-293`` (engine config dataclasses + JSON parser) and identifies
+models through ``batchgen/config/model_registry.py:60-117``.  Here a single registry maps model
+names (and HF-style ids) to presets.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import math
+import re
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+
+@dataclass
+class ModelConfig:
+    name: str = "tiny-deepseek-v3"
+    family: str = "deepseek_v3"  # deepseek_v3 | glm5 | kimi_k3 | kimi_k25 | gpt_oss | minimax
+    vocab_size: int = 1024
+    hidden_size: int = 256
+    num_layers: int = 2
+    first_k_dense: int = 1
+    intermediate_size: int = 512          # dense MLP intermediate
+    moe_intermediate_size: int = 128      # routed / shared expert intermediate
+    n_routed_experts: int = 8
+    n_shared_experts: int = 1
+    num_experts_per_tok: int = 2
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    norm_topk_prob: bool = True
+    scoring_func: str = "sigmoid"          # sigmoid | softmax
+    moe_latent_size: int = 0               # Kimi-K3 LatentMoE: experts run in this width
+    activation: str = "silu"               # silu | swiglu_clamped (GPT-OSS)
+    # ---- attention: MLA
+    num_heads: int = 4
+    q_lora_rank: int = 128
+    kv_lora_rank: int = 64
+    qk_nope_head_dim: int = 32
+    qk_rope_head_dim: int = 16
+    v_head_dim: int = 32
+    # ---- attention: GQA (used when num_kv_heads > 0)
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    sliding_window: int = 0
+    attention_sinks: bool = False
+    # ---- rope
+    rope_theta: float = 10000.0
+    rope_interleaved: bool = True
+    rope_scaling_factor: float = 1.0       # YaRN factor (1 = off)
+    rope_original_max_pos: int = 4096
+    rope_beta_fast: float = 32.0
+    rope_beta_slow: float = 1.0
+    rope_mscale: float = 1.0
+    rope_mscale_all_dim: float = 0.0
+    max_position_embeddings: int = 163840
+    rms_eps: float = 1e-6
+    # ---- DSA sparse-attention indexer (GLM-5.x / Kimi-K3.1)
+    index_n_heads: int = 0
+    index_head_dim: int = 0
+    index_topk: int = 0
+    indexer_full_layers: Tuple[int, ...] = ()   # layers that own an indexer; others reuse
+    # ---- quantisation of linear / expert weights
+    quant: str = "none"                    # none | fp8_block | mxfp4
+    quant_block: int = 128
+    # ---- misc
+    eos_token_id: int = 1
+    bos_token_id: int = 0
+    tie_word_embeddings: bool = False
+
+    # derived ------------------------------------------------------------------
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim
+
+    @property
+    def kv_cache_dim(self) -> int:
+        """Width of one cached latent row (normalised c_kv followed by roped k_pe)."""
+        if self.num_kv_heads > 0:
+            return 2 * self.num_kv_heads * self.head_dim
+        return self.kv_lora_rank + self.qk_rope_head_dim
+
+    @property
+    def is_mla(self) -> bool:
+        return self.num_kv_heads == 0
+
+    @property
+    def has_dsa(self) -> bool:
+        return self.index_topk > 0
+
+    @property
+    def expert_hidden(self) -> int:
+        return self.moe_latent_size or self.hidden_size
+
+    @property
+    def softmax_scale(self) -> float:
+        d = self.qk_head_dim if self.is_mla else self.head_dim
+        scale = d ** -0.5
+        if self.rope_scaling_factor > 1.0 and self.rope_mscale_all_dim:
+            m = 0.1 * self.rope_mscale_all_dim * math.log(self.rope_scaling_factor) + 1.0
+            scale = scale * m * m
+        return scale
+
+    def is_moe_layer(self, layer: int) -> bool:
+        return self.n_routed_experts > 0 and layer >= self.first_k_dense
+
+    def layer_has_indexer(self, layer: int) -> bool:
+        if not self.has_dsa:
+            return False
+        return (not self.indexer_full_layers) or layer in self.indexer_full_layers
+
+    def kv_bytes_per_token(self, kv_dtype_bytes: int = 2) -> int:
+        b = self.num_layers * self.kv_cache_dim * kv_dtype_bytes
+        if self.has_dsa:
+            n_idx = len(self.indexer_full_layers) or self.num_layers
+            b += n_idx * (self.index_head_dim + 4)  # e4m3 keys + fp32 scale per token
+        return b
+
+    def param_count(self) -> int:
+        h = self.hidden_size
+        n = 2 * self.vocab_size * h
+        for l in range(self.num_layers):
+            if self.is_mla:
+                n += h * self.q_lora_rank + self.q_lora_rank * self.num_heads * self.qk_head_dim
+                n += h * self.kv_cache_dim
+                n += self.kv_lora_rank * self.num_heads * (self.qk_nope_head_dim + self.v_head_dim)
+                n += self.num_heads * self.v_head_dim * h
+            else:
+                n += h * (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+                n += self.num_heads * self.head_dim * h
+            if self.is_moe_layer(l):
+                eh = self.expert_hidden
+                n += 3 * eh * self.moe_intermediate_size * (self.n_routed_experts + self.n_shared_experts)
+                n += h * self.n_routed_experts
+            else:
+                n += 3 * h * self.intermediate_size
+        return n
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self), indent=1)
+
+    @classmethod
+    def from_dict(cls, d: Dict) -> "ModelConfig":
+        names = {f.name for f in dataclasses.fields(cls)}
+        kw = {k: v for k, v in d.items() if k in names}
+        if "indexer_full_layers" in kw:
+            kw["indexer_full_layers"] = tuple(kw["indexer_full_layers"])
+        return cls(**kw)
+
+
+# ------------------------------------------------------------------ presets
+def tiny_deepseek_v3() -> ModelConfig:
+    """The CPU fp32 correctness model: 2 layers (dense, MoE), hidden 256, 8 experts top-2."""
+    return ModelConfig()
+
+
+def tiny_glm5() -> ModelConfig:
+    return ModelConfig(name="tiny-glm5", family="glm5", num_layers=3, first_k_dense=1,
+                       index_n_heads=4, index_head_dim=32, index_topk=16,
+                       indexer_full_layers=(0, 2), rope_interleaved=True,
+                       routed_scaling_factor=2.5)
+
+
+def tiny_kimi_k3() -> ModelConfig:
+    return ModelConfig(name="tiny-kimi-k3", family="kimi_k3", num_layers=2, first_k_dense=0,
+                       n_routed_experts=16, num_experts_per_tok=4, moe_latent_size=128,
+                       moe_intermediate_size=64, quant="none")
+
+
+def tiny_gpt_oss() -> ModelConfig:
+    return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", num_layers=2, first_k_dense=0,
+                       num_heads=8, num_kv_heads=2, head_dim=32, sliding_window=16,
+                       attention_sinks=True, scoring_func="softmax", n_shared_experts=0,
+                       n_routed_experts=8, num_experts_per_tok=2, activation="swiglu_clamped",
+                       rope_interleaved=False)
+
+
+def deepseek_v3_671b() -> ModelConfig:
+    return ModelConfig(
+        name="deepseek-v3-671b", family="deepseek_v3", vocab_size=129280, hidden_size=7168,
+        num_layers=61, first_k_dense=3, intermediate_size=18432, moe_intermediate_size=2048,
+        n_routed_experts=256, n_shared_experts=1, num_experts_per_tok=8, n_group=8, topk_group=4,
+        routed_scaling_factor=2.5, norm_topk_prob=True, num_heads=128, q_lora_rank=1536,
+        kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+        rope_theta=10000.0, rope_scaling_factor=40.0, rope_original_max_pos=4096,
+        rope_mscale=1.0, rope_mscale_all_dim=1.0, quant="fp8_block", eos_token_id=1)
+
+
+def glm5_3() -> ModelConfig:
+    full = tuple(sorted(set(list(range(0, 78, 4)) + [77])))[:21]
+    return ModelConfig(
+        name="glm-5.3-fp8", family="glm5", vocab_size=154880, hidden_size=6144, num_layers=78,
+        first_k_dense=3, intermediate_size=12288, moe_intermediate_size=2048,
+        n_routed_experts=256, n_shared_experts=1, num_experts_per_tok=8, n_group=1, topk_group=1,
+        routed_scaling_factor=2.5, num_heads=64, q_lora_rank=2048, kv_lora_rank=512,
+        qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256, rope_theta=1000000.0,
+        rope_interleaved=True, index_n_heads=32, index_head_dim=128, index_topk=2048,
+        indexer_full_layers=full, quant="fp8_block", max_position_embeddings=1048576)
+
+
+def kimi_k3() -> ModelConfig:
+    return ModelConfig(
+        name="kimi-k3", family="kimi_k3", vocab_size=163840, hidden_size=7168, num_layers=93,
+        first_k_dense=1, intermediate_size=18432, moe_intermediate_size=3072,
+        n_routed_experts=896, n_shared_experts=1, num_experts_per_tok=16, n_group=1,
+        topk_group=1, routed_scaling_factor=2.5, moe_latent_size=3584, num_heads=64,
+        q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64,
+        v_head_dim=128, quant="mxfp4", quant_block=32)
+
+
+def kimi_k25() -> ModelConfig:
+    return ModelConfig(
+        name="kimi-k2.5", family="kimi_k25", vocab_size=163840, hidden_size=7168, num_layers=61,
+        first_k_dense=1, intermediate_size=18432, moe_intermediate_size=2048,
+        n_routed_experts=384, n_shared_experts=1, num_experts_per_tok=8, routed_scaling_factor=2.827,
+        num_heads=64, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+        qk_rope_head_dim=64, v_head_dim=128, quant="mxfp4", quant_block=32)
+
+
+def gpt_oss_120b() -> ModelConfig:
+    return ModelConfig(
+        name="gpt-oss-120b", family="gpt_oss", vocab_size=201088, hidden_size=2880, num_layers=36,
+        first_k_dense=0, moe_intermediate_size=2880, n_routed_experts=128, n_shared_experts=0,
+        num_experts_per_tok=4, scoring_func="softmax", num_heads=64, num_kv_heads=8, head_dim=64,
+        sliding_window=128, attention_sinks=True, activation="swiglu_clamped",
+        rope_theta=150000.0, rope_interleaved=False, rope_scaling_factor=32.0, quant="mxfp4",
+        quant_block=32)
+
+
+def minimax_m25() -> ModelConfig:
+    return ModelConfig(
+        name="minimax-m2.5", family="minimax", vocab_size=200064, hidden_size=3072, num_layers=62,
+        first_k_dense=0, moe_intermediate_size=1536, n_routed_experts=256, n_shared_experts=0,
+        num_experts_per_tok=8, num_heads=48, num_kv_heads=8, head_dim=128, rope_interleaved=False,
+        quant="fp8_block")
+
+
+_PRESETS = {
+    "tiny-deepseek-v3": tiny_deepseek_v3,
+    "tiny-glm5": tiny_glm5,
+    "tiny-kimi-k3": tiny_kimi_k3,
+    "tiny-gpt-oss": tiny_gpt_oss,
+    "deepseek-v3-671b": deepseek_v3_671b,
+    "deepseek-r1": deepseek_v3_671b,
+    "glm-5.3-fp8": glm5_3,
+    "kimi-k3": kimi_k3,
+    "kimi-k2.5": kimi_k25,
+    "gpt-oss-120b": gpt_oss_120b,
+    "minimax-m2.5": minimax_m25,
+}
+
+# HF-style identity patterns -> preset (the reference matches on substrings of the model id,
+# batchgen/config/model_registry.py:63-117).
+_PATTERNS = [
+    (r"deepseek[-_/]?(ai/)?.*(v3|r1)", "deepseek-v3-671b"),
+    (r"glm[-_]?5", "glm-5.3-fp8"),
+    (r"kimi[-_]?k3", "kimi-k3"),
+    (r"kimi[-_]?k2", "kimi-k2.5"),
+    (r"gpt[-_]?oss", "gpt-oss-120b"),
+    (r"minimax", "minimax-m2.5"),
+]
+
+
+def list_models() -> List[str]:
+    return sorted(_PRESETS)
+
+
+def get_model_config(name: str, **overrides) -> ModelConfig:
+    key = name.lower()
+    if key not in _PRESETS:
+        for pat, preset in _PATTERNS:
+            if re.search(pat, key):
+                key = preset
+                break
+        else:
+            raise KeyError(f"unknown model {name!r}; known: {list_models()}")
+    cfg = _PRESETS[key]()
+    for k, v in overrides.items():
+        if not hasattr(cfg, k):
+            raise AttributeError(f"ModelConfig has no field {k!r}")
+        setattr(cfg, k, v)
+    return cfg
+
+
+# ------------------------------------------------------------------ engine config
+@dataclass
+class EngineConfig:
+    """Runtime knobs.  Names follow the reference's server flags where one exists
+    (docs/server-flags.md; batchgen/server/server_args.py:168-285)."""
+    page_size: int = 64
+    kv_dtype: str = "bf16"                      # bf16 | fp8
+    gpu_memory_frac: float = 0.9
+    num_gpu_pages: int = 0                      # 0 = size from free memory
+    host_kv_cache_size_gb: float = 0.0          # CPU-DRAM KV tier
+    host_kv_chunk_size: int = 8192
+    host_kv_watermark: int = 70
+    initial_gpu_page_buffer: int = 32
+    extension_gpu_page_buffer: int = 4
+    decision_frequency_pages: int = 2
+    max_prefill_tokens: int = 131072            # packed micro-batch token cap
+    max_decode_batch: int = 512                 # rows per rank in decode
+    max_model_len: int = -1
+    enable_cuda_graph: bool = True
+    cuda_graph_max_bucket_size: int = 128
+    cuda_graph_num_buckets: int = 16
+    enable_prefix_cache: bool = False
+    adaptive_chunk: bool = False
+    # parallel layout
+    world_size: int = 1
+    attn_tp_size: int = 1                       # TP degree of attention (1 = DP attention)
+    ep_size: int = 1                            # expert parallel degree
+    moe_comm: str = "fused"                     # fused | nccl  (nccl = all_gather/reduce_scatter baseline)
+    tp_comm: str = "fused"                      # fused | nccl
+    expert_offload_ratio: float = 0.0           # fraction of local experts kept in host DRAM
+    weight_ring_slots: int = 4
+    seed: int = 0
+    device: str = "cpu"
+    dtype: str = "fp32"                         # fp32 (CPU oracle) | bf16 (GPU)
+
+    def validate(self) -> None:
+        if self.page_size <= 0 or self.page_size & (self.page_size - 1):
+            raise ValueError("page_size must be a power of two")
+        if self.world_size % max(self.attn_tp_size, 1):
+            raise ValueError("attn_tp_size must divide world_size")
+        if self.ep_size not in (1, self.world_size):
+            raise ValueError("ep_size must be 1 or world_size")
+        if not 0.0 <= self.expert_offload_ratio <= 1.0:
+            raise ValueError("expert_offload_ratio must be in [0, 1]")
+        if self.kv_dtype not in ("bf16", "fp8", "fp32"):
+            raise ValueError(f"unsupported kv dtype {self.kv_dtype}")
+
+    @classmethod
+    def from_json(cls, path: str) -> "EngineConfig":
+        with open(path) as f:
+            d = json.load(f)
+        names = {f.name for f in dataclasses.fields(cls)}
+        unknown = set(d) - names
+        if unknown:
+            raise ValueError(f"unknown engine config keys: {sorted(unknown)}")
+        cfg = cls(**d)
+        cfg.validate()
+        return cfg

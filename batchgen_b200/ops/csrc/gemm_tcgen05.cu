@@ -1,0 +1,424 @@
+// Block-scaled FP8 (e4m3) and bf16 GEMM on the 5th-generation tensor cores: dense and ragged
+// grouped (per-expert) forms in one persistent, warp-specialised kernel.
+//
+//   D[m, n] = sum_kb  sA[m, kb] * sB[n / 128, kb] * ( A[m, kb*128 : +128] . B[n, kb*128 : +128] )
+//
+// A is the activation [M, K] (1x128 scales), B the weight [N, K] (128x128 scales), both
+// K-major, so every operand tile is a TMA box of 128-byte rows in the 128B-swizzled layout that
+// tcgen05.mma reads directly.  The tensor core has no fp32 block scaling, so each 128-wide K
+// block is multiplied into its own TMEM accumulator (double buffered) and the epilogue warps
+// fold it into fp32 registers with the block's scale while the next block is being multiplied.
+//
+// Roles (320 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + tcgen05.mma issuer (one elected lane)
+//   warps 2..9  epilogue: warp w owns TMEM lanes 32*(w%4).. and columns 64*((w-2)/4)..
+//
+// Replaces (by behaviour): DeepGEMM fp8_gemm_nt / m_grouped contiguous as called from
+// batchgen/gemm/w8a8_deepgemm.py:126 and batchgen/moe/grouped_fp8_deepgemm_moe.py:45-232, the
+// CuTe sm90 blockwise grouped GEMM batchgen_kernels/src/moe/fp8_blockwise/fp8_blockwise_gemm_kernel.cuh:363
+// and its fused gate+up+SiLU stage batchgen_kernels/src/moe/fp8_blockwise/fp8_blockwise_s1_kernel.cuh:131.
+#include "common.cuh"
+
+namespace bg {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int BK_BYTES = 128;  // one swizzle atom of K per stage
+constexpr int kStages = 6;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kTmemCols = 256;  // two 128-column accumulators
+constexpr int kMaxGroups = 1024;
+
+constexpr int KIND_FP8 = 0;
+constexpr int KIND_BF16 = 1;
+constexpr int EPI_STORE = 0;
+constexpr int EPI_SILU_MUL = 1;  // B rows interleaved (32 gate, 32 up): out = silu(gate) * up
+
+struct GemmParams {
+  const float* sA;      // [KB, sa_stride] (transposed: scale of row m, block kb at sA[kb*sa_stride+m])
+  int sa_stride;
+  const float* sB;      // [groups, ceil(Nw/128), KB]
+  __nv_bfloat16* D;     // [M, ldd]
+  int ldd;
+  const int* offsets;   // [groups+1] device row offsets, every segment start 128-aligned; null = dense
+  int groups;
+  int M;                // rows of A (dense) / capacity of A (grouped)
+  int N;                // rows of B per group (GEMM N)
+  int K;                // elements
+  int* status;
+};
+
+struct SharedStorage {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int offs[kMaxGroups + 1];
+};
+
+struct Tile {
+  int g;      // group (expert)
+  int m0;     // first row in A / D
+  int m_end;  // one past the last valid row
+  int nt;     // n tile
+};
+
+// Deterministic tile walk shared by all roles.  Dense: tile -> (nt, mt) with mt fastest.
+// Grouped: groups in order, inside a group nt-major with mt fastest.
+struct TileWalker {
+  const int* offs;
+  int groups, n_tiles, M;
+  int g, before;  // grouped walk state: current group and number of tiles in earlier groups
+  __device__ TileWalker(const int* offs_, int groups_, int n_tiles_, int M_)
+      : offs(offs_), groups(groups_), n_tiles(n_tiles_), M(M_), g(0), before(0) {}
+  __device__ bool get(int tile, Tile& t) {
+    if (offs == nullptr) {
+      const int m_tiles = (M + BM - 1) / BM;
+      if (tile >= m_tiles * n_tiles) return false;
+      t.g = 0;
+      t.nt = tile / m_tiles;
+      t.m0 = (tile % m_tiles) * BM;
+      t.m_end = M;
+      return true;
+    }
+    while (g < groups) {
+      const int rows = offs[g + 1] - offs[g];
+      const int m_tiles = (rows + BM - 1) / BM;
+      const int here = m_tiles * n_tiles;
+      if (tile < before + here) {
+        const int local = tile - before;
+        t.g = g;
+        t.nt = local / m_tiles;
+        t.m0 = offs[g] + (local % m_tiles) * BM;
+        t.m_end = offs[g + 1];
+        return true;
+      }
+      before += here;
+      ++g;
+    }
+    return false;
+  }
+};
+
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // carve: operand stages first (1024-byte aligned), bookkeeping after
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA_tiles = smem;
+  uint8_t* sB_tiles = smem + kStages * BM * BK_BYTES;
+  SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + kStages * (BM + BN) * BK_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kElemBytes = (KIND == KIND_FP8) ? 1 : 2;
+  constexpr int BK = BK_BYTES / kElemBytes;  // elements of K per stage
+  const int KB = p.K / BK;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int nblk = (p.N + 127) / 128;
+  volatile int* abort_flag = &ss.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ss.full[s], 1);
+      mbar_init(&ss.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ss.tmem_full[b], 1);
+      mbar_init(&ss.tmem_empty[b], kEpiWarps);
+    }
+    ss.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (p.offsets != nullptr) {
+    for (int i = threadIdx.x; i <= p.groups; i += kThreads) ss.offs[i] = p.offsets[i];
+  }
+  if (warp == 1) {
+    tmem_alloc(&ss.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ss.tmem_base;
+  const int* offs = (p.offsets != nullptr) ? ss.offs : nullptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      TileWalker walk(offs, p.groups, n_tiles, p.M);
+      Tile t;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
+        const int brow = t.g * p.N + t.nt * BN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&ss.empty[s], ph ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
+          mbar_expect_tx(&ss.full[s], (BM + BN) * BK_BYTES);
+          tma_load_2d(sA_tiles + s * BM * BK_BYTES, &tmA, &ss.full[s], kb * BK, t.m0);
+          tma_load_2d(sB_tiles + s * BN * BK_BYTES, &tmB, &ss.full[s], kb * BK, brow);
+        }
+      }
+      // Drain: do not leave the CTA while bulk copies may still land in its shared memory.
+      // Every armed stage is consumed by the MMA role, which releases it through `empty`; wait
+      // (bounded) for the last kStages releases.
+      if (ok) {
+        const uint32_t n = it < (uint32_t)kStages ? it : (uint32_t)kStages;
+        for (uint32_t j = it - n; j < it; ++j) {
+          const int s = j % kStages;
+          const uint32_t ph = (j / kStages) & 1;
+          if (!mbar_wait(&ss.empty[s], ph, abort_flag, kTimeoutProducer)) break;
+        }
+      } else {
+        for (int s = 0; s < kStages; ++s) {  // aborted: give in-flight copies a bounded time to land
+          for (uint32_t i = 0; i < (1u << 14); ++i) {
+            if (mbar_try_wait(&ss.full[s], 0) || mbar_try_wait(&ss.full[s], 1)) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, KIND == KIND_FP8 ? 0 : 1, KIND == KIND_FP8 ? 0 : 1);
+      TileWalker walk(offs, p.groups, n_tiles, p.M);
+      Tile t;
+      uint32_t it = 0;   // smem stage counter
+      uint32_t acc = 0;  // accumulator hand-off counter
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          const bool new_acc = (KIND == KIND_FP8) || kb == 0;
+          const int buf = acc & 1;
+          if (new_acc) {
+            if (!mbar_wait(&ss.tmem_empty[buf], ((acc >> 1) & 1) ^ 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          }
+          if (!mbar_wait(&ss.full[s], ph, abort_flag, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + buf * BN;
+          const uint64_t adesc = make_smem_desc_sw128(smem_u32(sA_tiles + s * BM * BK_BYTES));
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(sB_tiles + s * BN * BK_BYTES));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per stage
+            const uint32_t accum = (k > 0 || !new_acc) ? 1u : 0u;
+            if (KIND == KIND_FP8) mma_f8f6f4(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            else mma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+          }
+          tc_commit(&ss.empty[s]);
+          const bool last_of_acc = (KIND == KIND_FP8) || kb == KB - 1;
+          if (last_of_acc) {
+            tc_commit(&ss.tmem_full[buf]);
+            ++acc;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp - 2;
+    const int quad = warp & 3;        // TMEM lane quadrant this warp may access
+    const int half = ew >> 2;         // which 64 columns of the tile
+    const int row_in_tile = quad * 32 + lane;
+    TileWalker walk(offs, p.groups, n_tiles, p.M);
+    Tile t;
+    uint32_t acc = 0;
+    bool ok = true;
+    const int groups_of_k = (KIND == KIND_FP8) ? KB : 1;
+    for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
+      float r[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) r[j] = 0.f;
+      const int row = t.m0 + row_in_tile;
+      const bool row_ok = row < t.m_end;
+      // scale pointers
+      const float* sa_ptr = (KIND == KIND_FP8) ? p.sA + row : nullptr;
+      int sb_blk_lo, sb_blk_hi;  // weight scale block for columns [0,32) and [32,64) of this half
+      if (EPI == EPI_SILU_MUL) {
+        const int I = p.N / 2;
+        sb_blk_lo = (t.nt * 64) / 128;
+        sb_blk_hi = (I + t.nt * 64) / 128;
+      } else {
+        sb_blk_lo = sb_blk_hi = t.nt;
+      }
+      const float* sb_lo = (KIND == KIND_FP8) ? p.sB + (size_t)(t.g * nblk + sb_blk_lo) * KB : nullptr;
+      const float* sb_hi = (KIND == KIND_FP8) ? p.sB + (size_t)(t.g * nblk + sb_blk_hi) * KB : nullptr;
+      float sa_next = 1.f, sbl_next = 1.f, sbh_next = 1.f;
+      if (KIND == KIND_FP8) {
+        sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
+        sbl_next = __ldg(sb_lo);
+        sbh_next = __ldg(sb_hi);
+      }
+      for (int kg = 0; kg < groups_of_k; ++kg, ++acc) {
+        const float sa = sa_next, sbl = sbl_next, sbh = sbh_next;
+        if (KIND == KIND_FP8 && kg + 1 < groups_of_k) {
+          sa_next = row_ok ? __ldg(sa_ptr + (size_t)(kg + 1) * p.sa_stride) : 0.f;
+          sbl_next = __ldg(sb_lo + kg + 1);
+          sbh_next = __ldg(sb_hi + kg + 1);
+        }
+        const int buf = acc & 1;
+        if (!mbar_wait(&ss.tmem_full[buf], (acc >> 1) & 1, abort_flag, kTimeoutEpilogue)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + half * 64;
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(taddr, v0);
+        tmem_ld_32x32(taddr + 32, v1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ss.tmem_empty[buf]);
+        const float s_lo = sa * sbl, s_hi = sa * sbh;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          r[j] = fmaf(__uint_as_float(v0[j]), s_lo, r[j]);
+          r[32 + j] = fmaf(__uint_as_float(v1[j]), s_hi, r[32 + j]);
+        }
+      }
+      if (!ok) break;
+      if (row_ok) {
+        if (EPI == EPI_SILU_MUL) {
+          // columns [0,32) of this half = gate, [32,64) = up of output columns nt*64 + half*32 + j
+          const int col0 = t.nt * 64 + half * 32;
+          const int n_out = p.N / 2;
+          __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j + 8 <= n_out) {
+              __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float a = silu(r[j + 2 * q]) * r[32 + j + 2 * q];
+                const float b = silu(r[j + 2 * q + 1]) * r[32 + j + 2 * q + 1];
+                o[q] = __floats2bfloat162_rn(a, b);
+              }
+              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(o);
+            } else {
+              for (int q = 0; q < 8; ++q)
+                if (col0 + j + q < n_out) dst[j + q] = __float2bfloat16(silu(r[j + q]) * r[32 + j + q]);
+            }
+          }
+        } else {
+          const int col0 = t.nt * BN + half * 64;
+          __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+#pragma unroll
+          for (int j = 0; j < 64; j += 8) {
+            if (col0 + j + 8 <= p.N) {
+              __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(r[j + 2 * q], r[j + 2 * q + 1]);
+              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(o);
+            } else {
+              for (int q = 0; q < 8; ++q)
+                if (col0 + j + q < p.N) dst[j + q] = __float2bfloat16(r[j + q]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D row-major [rows, cols] tensor of `elem_bytes` elements, box = [box_rows, 128 bytes], 128B swizzle.
+static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, int elem_bytes,
+                       uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static size_t gemm_smem_bytes() { return kStages * (BM + BN) * BK_BYTES + sizeof(SharedStorage) + 1024; }
+
+template <int KIND, int EPI>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_rows, int b_rows, int num_sms,
+                       cudaStream_t stream) {
+  constexpr int eb = (KIND == KIND_FP8) ? 1 : 2;
+  CUtensorMap tmA, tmB;
+  if (make_map_2d(&tmA, A, a_rows, p.K, eb, BM) != 0) return -10;
+  if (make_map_2d(&tmB, B, b_rows, p.K, eb, BN) != 0) return -11;
+  static bool attr_set = false;  // one flag per template instantiation; one process drives one GPU
+  auto kern = gemm_kernel<KIND, EPI>;
+  const size_t smem = gemm_smem_bytes();
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -12;
+    attr_set = true;
+  }
+  int grid = num_sms;
+  if (p.offsets == nullptr) {
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    if (tiles < grid) grid = tiles;
+  }
+  if (grid < 1) grid = 1;
+  kern<<<grid, kThreads, smem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -13;
+}
+
+}  // namespace bg
+
+extern "C" {
+
+// Dense or grouped GEMM.  kind: 0 = e4m3 block scaled, 1 = bf16.  epi: 0 = store, 1 = silu-mul
+// (weight rows interleaved in 32-row gate/up blocks; output has N/2 columns).
+// offsets == nullptr -> dense [M, K] x [N, K]^T.  Otherwise A holds `groups` row segments
+// (128-aligned starts, offsets[groups] <= M) and B is [groups * N, K].
+// K must be a multiple of 128 elements (fp8) / 64 (bf16).  Returns 0 on a successful launch.
+int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, const void* B, const float* sB,
+            void* D, int ldd, const int* offsets, int groups, int M, int N, int K, int num_sms, int* status,
+            cudaStream_t stream) {
+  using namespace bg;
+  if (M <= 0 || N <= 0) return 0;
+  const int bk = kind == KIND_FP8 ? 128 : 64;
+  if (K % bk != 0 || groups > kMaxGroups || (epi == EPI_SILU_MUL && (N % 256) != 0)) return -1;
+  if (offsets == nullptr) groups = 1;
+  GemmParams p;
+  p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
+  const int b_rows = groups * N;
+  if (kind == KIND_FP8 && epi == EPI_STORE) return launch_gemm<KIND_FP8, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
+  if (kind == KIND_FP8 && epi == EPI_SILU_MUL) return launch_gemm<KIND_FP8, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);
+  if (kind == KIND_BF16 && epi == EPI_STORE) return launch_gemm<KIND_BF16, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
+  if (kind == KIND_BF16 && epi == EPI_SILU_MUL) return launch_gemm<KIND_BF16, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);
+  return -2;
+}
+
+}  // extern "C"

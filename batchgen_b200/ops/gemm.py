@@ -1,0 +1,112 @@
+"""GEMM entry points: block-scaled FP8 and bf16, dense and grouped.
+
+CUDA tensors go to the tcgen05 kernel (``csrc/gemm_tcgen05.cu``); CPU tensors go to the fp32
+reference.  Activation scales are consumed in *row-contiguous-per-block* layout
+(``scale[kb, m]``), which is what the fused quantisation kernels emit; a ``[T, KB]`` contiguous
+tensor is transposed on the fly.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _ext, ref
+
+KIND_FP8, KIND_BF16 = 0, 1
+EPI_STORE, EPI_SILU_MUL = 0, 1
+
+
+def interleave_gate_up_rows(n_rows: int, device=None) -> torch.Tensor:
+    """Row permutation that turns a [2I, K] gate-then-up weight into the tile-interleaved layout
+    the fused SiLU epilogue reads: every 64 consecutive rows hold 32 gate rows followed by the 32
+    up rows of the same output columns."""
+    I = n_rows // 2
+    assert I % 128 == 0, "intermediate size must be a multiple of 128"
+    j = torch.arange(I, device=device)
+    blk, within = j // 32, j % 32
+    idx = torch.empty(n_rows, dtype=torch.long, device=device)
+    idx[blk * 64 + within] = j
+    idx[blk * 64 + 32 + within] = I + j
+    return idx
+
+
+def _scales_kb_major(xs: torch.Tensor):
+    """Return (tensor, stride) with scale(m, kb) at data[kb * stride + m]."""
+    if xs.dim() != 2:
+        raise ValueError("activation scales must be 2-D [T, KB]")
+    if xs.stride(0) == 1 or xs.shape[0] == 1:
+        return xs, (xs.stride(1) if xs.shape[1] > 1 else xs.shape[0])
+    t = xs.t().contiguous()  # [KB, T]
+    return t, t.stride(0)
+
+
+def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K):
+    L = _ext.lib()
+    rc = L.bg_gemm(ctypes.c_int(kind), ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride),
+                   _ext.ptr(B), _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets),
+                   ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                   ctypes.c_int(_ext.num_sms(A.device)), _ext.ptr(_ext.status_word(A.device)), _ext.stream())
+    _ext.check(rc, "bg_gemm")
+
+
+def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
+             out: Optional[torch.Tensor] = None, silu_mul: bool = False) -> torch.Tensor:
+    """[T, K] e4m3 x [N, K] e4m3 -> [T, N] (bf16 on GPU).  With ``silu_mul`` the weight must be in
+    the interleaved gate/up layout and the result has N/2 columns."""
+    T, K = xq.shape
+    N = wq.shape[0]
+    if not xq.is_cuda:
+        y = ref.fp8_gemm(xq, xs, wq, ws)
+        if silu_mul:
+            inv = torch.argsort(interleave_gate_up_rows(N))
+            y = ref.silu_mul(y[:, inv])
+        return y
+    n_out = N // 2 if silu_mul else N
+    if out is None:
+        out = torch.empty(T, n_out, dtype=torch.bfloat16, device=xq.device)
+    if T == 0:
+        return out
+    s, stride = _scales_kb_major(xs)
+    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq, ws, out, None, 1, T, N, K)
+    return out
+
+
+def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
+                     offsets: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     silu_mul: bool = False) -> torch.Tensor:
+    """Ragged grouped GEMM.  xq: [R, K] rows grouped by expert, segment e = offsets[e]:offsets[e+1]
+    (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K]."""
+    E, N, K = wq.shape
+    R = xq.shape[0]
+    if not xq.is_cuda:
+        y = ref.grouped_fp8_gemm(xq, xs, wq, ws, offsets)
+        if silu_mul:
+            inv = torch.argsort(interleave_gate_up_rows(N))
+            y = ref.silu_mul(y[:, inv])
+        return y
+    n_out = N // 2 if silu_mul else N
+    if out is None:
+        out = torch.empty(R, n_out, dtype=torch.bfloat16, device=xq.device)
+    if R == 0:
+        return out
+    s, stride = _scales_kb_major(xs)
+    assert offsets.dtype == torch.int32 and offsets.is_cuda
+    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq.view(E * N, K), ws, out,
+            offsets, E, R, N, K)
+    return out
+
+
+def bf16_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, K] bf16 x [N, K] bf16 -> [T, N] bf16 (fp32 accumulate in TMEM)."""
+    if not x.is_cuda:
+        return (x.float() @ w.float().t()).to(x.dtype)
+    T, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    _launch(KIND_BF16, EPI_STORE, x, None, 0, w, None, out, None, 1, T, N, K)
+    return out
