@@ -1,0 +1,150 @@
+"""Naive oracle: the same architecture written the textbook way.
+
+No paging, no KV cache, no absorption, no fusion, no parallelism: every call recomputes the whole
+sequence in fp32 with *expanded* MLA keys/values (k_nope = W_UK c_kv, v = W_UV c_kv) and a per-token
+Python loop over experts.  It shares only the checkpoint-name -> tensor source with the engine, so a
+token-for-token match between the two checks the engine's paging, absorption, routing, dispatch and
+scheduling logic.  (Same role as the reference's readable torch backend,
+batchgen/attention/mla/torch_backend.py, and its HF-oracle test harness tests/kimi_k3_harness.py.)
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+import torch.nn.functional as F
+
+from ..config import ModelConfig
+from ..ops import ref
+from .weights import WeightSource
+
+
+class NaiveModel:
+    def __init__(self, cfg: ModelConfig, src: WeightSource):
+        assert cfg.is_mla, "the naive oracle covers the MLA families"
+        self.cfg, self.src = cfg, src
+
+    def _g(self, name, shape, kind="normal"):
+        return self.src.get(name, shape, kind).float()
+
+    def _rms(self, x, name, n):
+        w = self._g(name, (n,), "norm")
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.cfg.rms_eps) * w
+
+    def _rope(self, x, positions):
+        cfg = self.cfg
+        inv = ref.rope_inv_freq(cfg.qk_rope_head_dim, cfg.rope_theta, cfg.rope_scaling_factor,
+                                cfg.rope_original_max_pos, cfg.rope_beta_fast, cfg.rope_beta_slow)
+        cos, sin = ref.rope_cos_sin(positions, inv)
+        return ref.apply_rope(x, cos, sin, cfg.rope_interleaved)
+
+    def _mlp(self, x, prefix, inter, hid):
+        g = self._g(f"{prefix}.gate_proj.weight", (inter, hid))
+        u = self._g(f"{prefix}.up_proj.weight", (inter, hid))
+        d = self._g(f"{prefix}.down_proj.weight", (hid, inter))
+        return (F.silu(x @ g.t()) * (x @ u.t())) @ d.t()
+
+    @torch.no_grad()
+    def logits(self, ids: List[int]) -> torch.Tensor:
+        """Full-sequence forward -> fp32 logits [len(ids), vocab]."""
+        cfg = self.cfg
+        H, L = cfg.hidden_size, len(ids)
+        pos = torch.arange(L)
+        h = self._g("model.embed_tokens.weight", (cfg.vocab_size, H))[torch.tensor(ids)]
+        for l in range(cfg.num_layers):
+            p = f"model.layers.{l}"
+            x = self._rms(h, f"{p}.input_layernorm.weight", H)
+            # ---- MLA, expanded form
+            q_a = x @ self._g(f"{p}.self_attn.q_a_proj.weight", (cfg.q_lora_rank, H)).t()
+            q_a = self._rms(q_a, f"{p}.self_attn.q_a_layernorm.weight", cfg.q_lora_rank)
+            q = (q_a @ self._g(f"{p}.self_attn.q_b_proj.weight",
+                               (cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank)).t()).view(L, cfg.num_heads, -1)
+            q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], self._rope(q[..., cfg.qk_nope_head_dim:], pos)
+            kv_a = x @ self._g(f"{p}.self_attn.kv_a_proj_with_mqa.weight",
+                               (cfg.kv_lora_rank + cfg.qk_rope_head_dim, H)).t()
+            c_kv = self._rms(kv_a[:, : cfg.kv_lora_rank], f"{p}.self_attn.kv_a_layernorm.weight", cfg.kv_lora_rank)
+            k_pe = self._rope(kv_a[:, cfg.kv_lora_rank:], pos)
+            kvb = self._g(f"{p}.self_attn.kv_b_proj.weight",
+                          (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank))
+            kv = (c_kv @ kvb.t()).view(L, cfg.num_heads, cfg.qk_nope_head_dim + cfg.v_head_dim)
+            k_nope, v = kv[..., : cfg.qk_nope_head_dim], kv[..., cfg.qk_nope_head_dim:]
+            s = (torch.einsum("qhd,khd->hqk", q_nope, k_nope) + torch.einsum("qhd,kd->hqk", q_pe, k_pe))
+            s = s * cfg.softmax_scale
+            causal = torch.ones(L, L, dtype=torch.bool).tril()
+            if cfg.has_dsa:
+                keep = self._dsa_mask(l, p, x, q_a, pos)          # [L, L] bool
+                causal = causal & keep
+            s = s.masked_fill(~causal.unsqueeze(0), float("-inf"))
+            o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(L, -1)
+            h = h + o @ self._g(f"{p}.self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim)).t()
+            # ---- feed-forward
+            x = self._rms(h, f"{p}.post_attention_layernorm.weight", H)
+            if cfg.is_moe_layer(l):
+                h = h + self._moe(x, p)
+            else:
+                h = h + self._mlp(x, f"{p}.mlp", cfg.intermediate_size, H)
+        h = self._rms(h, "model.norm.weight", H)
+        head = "model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"
+        return h @ self._g(head, (cfg.vocab_size, H)).t()
+
+    def _moe(self, x, p):
+        cfg = self.cfg
+        E, I, eh, H = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden, cfg.hidden_size
+        logits = x @ self._g(f"{p}.mlp.gate.weight", (E, H)).t()
+        bias = self._g(f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias") if cfg.scoring_func == "sigmoid" else None
+        idx, w = ref.router_topk(logits, bias, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group,
+                                 cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.scoring_func)
+        xin = x
+        if cfg.moe_latent_size:
+            xin = x @ self._g(f"{p}.mlp.latent_down_proj.weight", (eh, H)).t()
+        out = torch.zeros(x.shape[0], eh)
+        for t in range(x.shape[0]):
+            for k in range(cfg.num_experts_per_tok):
+                e = int(idx[t, k])
+                out[t] += w[t, k] * self._mlp(xin[t: t + 1], f"{p}.mlp.experts.{e}", I, eh)[0]
+        if cfg.moe_latent_size:
+            out = self._rms(out, f"{p}.mlp.latent_norm.weight", eh)
+            out = out @ self._g(f"{p}.mlp.latent_up_proj.weight", (H, eh)).t()
+        if cfg.n_shared_experts:
+            out = out + self._mlp(x, f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+        return out
+
+    def _dsa_mask(self, l, p, x, q_a_normed, pos):
+        """Per-query key mask from the lightning indexer (index keys pass through e4m3, as cached)."""
+        cfg = self.cfg
+        L = x.shape[0]
+        if not cfg.layer_has_indexer(l):
+            src_layer = max(i for i in cfg.indexer_full_layers if i <= l)
+            return self._dsa_cache[src_layer]
+        Hi, Di, rd, H = cfg.index_n_heads, cfg.index_head_dim, cfg.qk_rope_head_dim, cfg.hidden_size
+        ip = f"{p}.self_attn.indexer"
+        k = x @ self._g(f"{ip}.wk.weight", (Di, H)).t()
+        k = F.layer_norm(k, (Di,), self._g(f"{ip}.k_norm.weight", (Di,), "norm"),
+                         self._g(f"{ip}.k_norm.bias", (Di,), "bias"), 1e-6)
+        k = torch.cat([self._rope(k[:, :rd], pos), k[:, rd:]], -1)
+        kq, ks = ref.index_k_quant(k)
+        q = (q_a_normed @ self._g(f"{ip}.wq_b.weight", (Hi * Di, cfg.q_lora_rank)).t()).view(L, Hi, Di)
+        q = torch.cat([self._rope(q[..., :rd], pos), q[..., rd:]], -1)
+        gates = (x @ self._g(f"{ip}.weights_proj.weight", (Hi, H)).t()) * (Hi ** -0.5) * (Di ** -0.5)
+        keep = torch.zeros(L, L, dtype=torch.bool)
+        for t in range(L):
+            n = t + 1
+            if n <= cfg.index_topk:
+                keep[t, :n] = True
+            else:
+                sc = ref.indexer_scores(q[t], gates[t], kq[:n], ks[:n])
+                keep[t, torch.topk(sc, cfg.index_topk)[1]] = True
+        if not hasattr(self, "_dsa_cache"):
+            self._dsa_cache = {}
+        self._dsa_cache[l] = keep
+        return keep
+
+    @torch.no_grad()
+    def generate(self, prompt: List[int], max_new_tokens: int) -> List[int]:
+        ids = list(prompt)
+        out = []
+        for _ in range(max_new_tokens):
+            nxt = int(self.logits(ids)[-1].argmax())
+            out.append(nxt)
+            ids.append(nxt)
+        return out

@@ -1,0 +1,284 @@
+"""The decoder-only transformer shared by every supported family.
+
+One class covers MLA (DeepSeek-V3/R1, GLM-5.x, Kimi) and GQA (GPT-OSS, MiniMax) attention, dense and
+MoE feed-forward (sigmoid group-limited or softmax routing, shared expert, Kimi LatentMoE) and the
+DSA sparse-attention indexer.  It is a pure function of (weights, KV cache, attention metadata):
+all state lives in the caller's ``PagedKVCache``.
+
+Tokens of a step are always flattened to ``[T]``; ``AttnMeta`` says how they map to sequences:
+
+* prefill: ``cu_seqlens`` delimits each sequence's new tokens, ``ctx_lens`` counts tokens already
+  cached before them (prefix hit / chunked prefill), ``slot_mapping`` says where each new token's KV
+  row goes, ``block_table`` row i is sequence i's pages.
+* decode: one token per sequence; ``seqlens`` includes the new token.
+
+Parallelism is injected through ``comm`` (see ``parallel.comm``): attention heads, dense MLP and the
+shared expert are tensor-parallel over ``tp`` ranks (partial sums reduced by ``comm.tp_reduce``), routed
+experts are expert-parallel (``comm.moe``).  With ``comm is None`` everything is local.
+
+Reference parity: batchgen/models/deepseek/deepseekv3/modeling_deepseek_v3.py (MLA + MoE layer
+structure, gate :746-850), batchgen/models/glm/glm5/model.py:610-700 (DSA indexer oracle) and
+:2391-2508 (decode MoE dataflow), batchgen/attention/mla/torch_backend.py (absorbed MLA math).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import attention as attn_ops
+from ..ops import fused, gemm, ref
+from ..ops import moe as moe_ops
+from .weights import LayerWeights, Linear, ModelWeights, ParallelLayout
+
+
+@dataclass
+class AttnMeta:
+    mode: str                                   # "prefill" | "decode"
+    positions: torch.Tensor                     # [T] int32
+    slot_mapping: torch.Tensor                  # [T] int64 flat KV slot of each new token (-1 = skip)
+    block_table: torch.Tensor                   # [nseq, max_pages] int32
+    seqlens: Optional[torch.Tensor] = None      # decode: [B] int32 lengths including the new token
+    cu_seqlens: Optional[List[int]] = None      # prefill: [nseq + 1]
+    ctx_lens: Optional[List[int]] = None        # prefill: tokens cached before this step
+    logit_rows: Optional[torch.Tensor] = None   # rows of T whose logits are wanted (prefill: last tokens)
+    num_valid: Optional[torch.Tensor] = None    # decode under CUDA graphs: device count of real rows
+    dsa_selection: dict = field(default_factory=dict)  # layer -> (sel_idx, sel_len) reused by shared layers
+
+
+class RopeTables:
+    def __init__(self, cfg: ModelConfig, max_pos: int, device):
+        d = cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim
+        inv = ref.rope_inv_freq(d, cfg.rope_theta, cfg.rope_scaling_factor, cfg.rope_original_max_pos,
+                                cfg.rope_beta_fast, cfg.rope_beta_slow)
+        pos = torch.arange(max_pos, dtype=torch.float32)
+        ang = pos.unsqueeze(-1) * inv
+        self.cos = ang.cos().to(device).contiguous()
+        self.sin = ang.sin().to(device).contiguous()
+        self.max_pos = max_pos
+
+
+def linear(x, lin: Linear, xq=None, xs=None, silu_mul: bool = False):
+    """y = x @ W^T.  FP8 weights consume the quantised activation (computed here unless passed in)."""
+    if lin.is_fp8:
+        if xq is None:
+            xq, xs = fused.act_quant(x)
+        if xq.is_cuda:
+            return gemm.fp8_gemm(xq, xs, lin.w, lin.s, silu_mul=silu_mul and lin.interleaved)
+        y = ref.fp8_gemm(xq, xs, lin.w, lin.s).to(x.dtype if x is not None else torch.float32)
+        return y
+    if x.is_cuda and x.dtype == torch.bfloat16 and lin.w.shape[1] % 64 == 0:
+        return gemm.bf16_gemm(x.contiguous(), lin.w)
+    return x @ lin.w.t()
+
+
+class Transformer:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: Optional[ParallelLayout] = None,
+                 comm=None, max_positions: int = 8192):
+        self.cfg = cfg
+        self.w = weights
+        self.layout = layout or ParallelLayout()
+        self.comm = comm
+        self.device = weights.embed.device
+        self.dtype = weights.embed.dtype
+        self.rope = RopeTables(cfg, max_positions, self.device)
+        self.timer = None     # optional utils.timing.TimingStats
+
+    # ------------------------------------------------------------------ helpers
+    def _mlp(self, x, xq, xs, w13: Linear, w2: Linear):
+        if w13.is_fp8 and x.is_cuda and w13.interleaved:
+            act = linear(x, w13, xq, xs, silu_mul=True)
+        else:
+            gu = linear(x, w13, xq, xs)
+            act = ref.swiglu_clamped(gu) if self.cfg.activation == "swiglu_clamped" else ref.silu_mul(gu)
+        return linear(act, w2)
+
+    def _norm(self, x, w, residual, quant):
+        return fused.rmsnorm(x, w, self.cfg.rms_eps, residual=residual, quant=quant)
+
+    # ------------------------------------------------------------------ attention
+    def _mla(self, l: int, lw: LayerWeights, x, xq, xs, meta: AttnMeta, cache) -> torch.Tensor:
+        cfg = self.cfg
+        T = x.shape[0]
+        Hh = lw.w_uk.shape[0]
+        qkv_a = linear(x, lw.wqkv_a, xq, xs)
+        q_a, kv_a = qkv_a[:, : cfg.q_lora_rank], qkv_a[:, cfg.q_lora_rank:]
+        fused.mla_kv_write(kv_a, lw.kv_norm, meta.positions, self.rope.cos, self.rope.sin, meta.slot_mapping,
+                           cache.latent(l), cfg.kv_lora_rank, cfg.rms_eps, cfg.rope_interleaved)
+        qn, qnq, qns = fused.rmsnorm(q_a, lw.q_norm, cfg.rms_eps, quant=lw.wq_b.is_fp8)
+        q = linear(qn, lw.wq_b, qnq, qns).view(T, Hh, cfg.qk_head_dim)
+        fused.rope_q_(q, meta.positions, self.rope.cos, self.rope.sin, cfg.qk_rope_head_dim, cfg.rope_interleaved)
+        q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
+        # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
+        q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_uk).transpose(0, 1)
+        sel = None
+        if cfg.has_dsa:
+            sel = self._dsa_select(l, lw, x, qn, meta, cache)
+        if meta.mode == "decode":
+            if sel is not None:
+                o_lat = attn_ops.sparse_mla_decode(q_abs, q_pe, cache.latent(l), meta.block_table, sel[0], sel[1],
+                                                   cfg.softmax_scale, cfg.kv_lora_rank)
+            else:
+                o_lat = attn_ops.mla_decode(q_abs.contiguous(), q_pe.contiguous(), cache.latent(l), meta.block_table,
+                                            meta.seqlens, cfg.softmax_scale, cfg.kv_lora_rank)
+        else:
+            if sel is not None:
+                o_lat = self._sparse_prefill(q_abs, q_pe, cache.latent(l), meta, sel)
+            else:
+                o_lat = attn_ops.mla_prefill(q_abs.contiguous(), q_pe.contiguous(), cache.latent(l), meta.block_table,
+                                             meta.cu_seqlens, meta.ctx_lens, cfg.softmax_scale, cfg.kv_lora_rank)
+        # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
+        o = torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
+        return linear(o, lw.wo)
+
+    def _dsa_select(self, l, lw, x, qn, meta: AttnMeta, cache):
+        """DSA indexer: write this step's FP8 index keys, score every cached key for each query
+        (sum_h gate_h * relu(q_h . k)), keep the top-k positions.  Layers without an indexer reuse
+        the selection of the nearest earlier layer that has one."""
+        cfg = self.cfg
+        if not cfg.layer_has_indexer(l):
+            src_layer = max(i for i in cfg.indexer_full_layers if i <= l) if cfg.indexer_full_layers else l
+            return meta.dsa_selection.get(src_layer)
+        T = x.shape[0]
+        Hi, Di = cfg.index_n_heads, cfg.index_head_dim
+        k = ref.layernorm(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b)
+        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
+        rd = cfg.qk_rope_head_dim
+        k = torch.cat([ref.apply_rope(k[:, :rd], cos, sin, cfg.rope_interleaved), k[:, rd:]], dim=-1)
+        kq, ks = ref.index_k_quant(k)
+        cache.write_index_keys(l, kq, ks, meta.slot_mapping)
+        q = linear(qn, lw.idx_wq).view(T, Hi, Di)
+        q = torch.cat([ref.apply_rope(q[..., :rd], cos, sin, cfg.rope_interleaved), q[..., rd:]], dim=-1)
+        gates = (x.float() @ lw.idx_head_w.float().t()) * (Hi ** -0.5) * (Di ** -0.5)
+        idx_keys, idx_scales = cache.index_keys(l)
+        P, S, _ = idx_keys.shape
+        sel_idx = torch.zeros(T, cfg.index_topk, dtype=torch.int32, device=x.device)
+        sel_len = torch.zeros(T, dtype=torch.int32, device=x.device)
+        if meta.mode == "decode":
+            lens = meta.seqlens.tolist()
+            rows = [(b, b, lens[b]) for b in range(T)]
+        else:
+            rows = []
+            for i in range(len(meta.cu_seqlens) - 1):
+                a, b = meta.cu_seqlens[i], meta.cu_seqlens[i + 1]
+                rows += [(t, i, meta.ctx_lens[i] + (t - a) + 1) for t in range(a, b)]
+        for t, seq, L in rows:
+            if L <= 0:
+                continue
+            if L <= cfg.index_topk:
+                sel_idx[t, :L] = torch.arange(L, dtype=torch.int32, device=x.device)
+                sel_len[t] = L
+                continue
+            npg = (L + S - 1) // S
+            pages = meta.block_table[seq, :npg].long()
+            kq_seq = idx_keys[pages].reshape(npg * S, Di)[:L]
+            ks_seq = idx_scales[pages].reshape(npg * S)[:L]
+            sc = ref.indexer_scores(q[t], gates[t], kq_seq, ks_seq)
+            idx, n = ref.topk_select(sc, L, cfg.index_topk)
+            sel_idx[t, :n] = idx
+            sel_len[t] = n
+        out = (sel_idx, sel_len)
+        meta.dsa_selection[l] = out
+        return out
+
+    def _sparse_prefill(self, q_abs, q_pe, latent, meta: AttnMeta, sel):
+        """Sparse MLA for prefill rows: every query row is a one-token 'decode' over its own selection."""
+        T = q_abs.shape[0]
+        row_seq = torch.zeros(T, dtype=torch.long, device=q_abs.device)
+        for i in range(len(meta.cu_seqlens) - 1):
+            row_seq[meta.cu_seqlens[i]: meta.cu_seqlens[i + 1]] = i
+        bt = meta.block_table[row_seq]
+        return attn_ops.sparse_mla_decode(q_abs, q_pe, latent, bt, sel[0], sel[1], self.cfg.softmax_scale,
+                                          self.cfg.kv_lora_rank)
+
+    def _gqa(self, l: int, lw: LayerWeights, x, xq, xs, meta: AttnMeta, cache) -> torch.Tensor:
+        cfg = self.cfg
+        T = x.shape[0]
+        D = cfg.head_dim
+        Hq = lw.wo.w.shape[1] // D
+        qkv = linear(x, lw.wqkv, xq, xs)
+        Hkv = (qkv.shape[1] // D - Hq) // 2
+        q = qkv[:, : Hq * D].reshape(T, Hq, D)
+        k = qkv[:, Hq * D: (Hq + Hkv) * D].reshape(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
+        q = ref.apply_rope(q, cos, sin, cfg.rope_interleaved)
+        k = ref.apply_rope(k, cos, sin, cfg.rope_interleaved)
+        kvc = cache.latent(l)                           # [P, page, 2 * Hkv_total * D]; this rank's slice is cached
+        ref.kv_cache_write(kvc, torch.cat([k.reshape(T, -1), v.reshape(T, -1)], -1), meta.slot_mapping)
+        out = torch.zeros(T, Hq, D, dtype=x.dtype, device=x.device)
+        window = cfg.sliding_window if (cfg.sliding_window and l % 2 == 0) else 0
+        if meta.mode == "decode":
+            spans = [(b, b + 1, b, int(meta.seqlens[b]) - 1) for b in range(T)]
+        else:
+            spans = [(meta.cu_seqlens[i], meta.cu_seqlens[i + 1], i, meta.ctx_lens[i])
+                     for i in range(len(meta.cu_seqlens) - 1)]
+        for a, b, seq, ctx in spans:
+            if b <= a:
+                continue
+            L = ctx + (b - a)
+            kv = ref.gather_paged(kvc, meta.block_table[seq], L)
+            ks = kv[:, : Hkv * D].reshape(L, Hkv, D)
+            vs = kv[:, Hkv * D:].reshape(L, Hkv, D)
+            out[a:b] = ref.gqa_attention(q[a:b], ks, vs, cfg.softmax_scale, q_start=ctx, window=window,
+                                         sinks=lw.sinks)
+        return linear(out.reshape(T, -1), lw.wo)
+
+    # ------------------------------------------------------------------ feed-forward
+    def _moe(self, l: int, lw: LayerWeights, x, xq, xs, meta: AttnMeta) -> torch.Tensor:
+        cfg = self.cfg
+        logits = moe_ops.router_logits(x, lw.router_w)
+        idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group,
+                                     cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.scoring_func,
+                                     num_valid=meta.num_valid)
+        shared = None
+        if lw.w13 is not None:
+            shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+            if self.comm is not None and self.layout.tp_size > 1:
+                shared = self.comm.tp_reduce(shared)
+        h = x
+        if cfg.moe_latent_size:
+            h = linear(x, lw.latent_down)
+        if self.comm is not None and self.layout.ep_size > 1:
+            routed = self.comm.moe(h, idx, w, lw.experts, cfg.n_routed_experts, num_valid=meta.num_valid)
+        else:
+            routed = moe_ops.experts_forward(h, idx, w, lw.experts, 0, cfg.n_routed_experts,
+                                             num_valid=meta.num_valid)
+        if cfg.moe_latent_size:
+            routed = linear(fused.rmsnorm(routed, lw.latent_norm, cfg.rms_eps)[0], lw.latent_up)
+        return routed if shared is None else routed + shared
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ids: torch.Tensor, meta: AttnMeta, cache) -> torch.Tensor:
+        """ids [T] -> fp32 logits [len(logit_rows) or T, vocab (this rank's shard under TP)]."""
+        cfg = self.cfg
+        h = self.w.embed[ids.long()]
+        residual = None
+        tp = self.comm is not None and self.layout.tp_size > 1
+        for l, lw in enumerate(self.w.layers):
+            fp8_in = (lw.wqkv_a or lw.wqkv).is_fp8
+            if residual is None:
+                residual = h.clone()
+                x, xq, xs = self._norm(h, lw.input_norm, None, fp8_in)
+            else:
+                x, xq, xs = self._norm(h, lw.input_norm, residual, fp8_in)
+            a = self._mla(l, lw, x, xq, xs, meta, cache) if cfg.is_mla else self._gqa(l, lw, x, xq, xs, meta, cache)
+            if tp:
+                a = self.comm.tp_reduce(a)
+            ffn_fp8 = (lw.w13 is not None and lw.w13.is_fp8)
+            x, xq, xs = self._norm(a, lw.post_norm, residual, ffn_fp8)
+            if cfg.is_moe_layer(l):
+                h = self._moe(l, lw, x, xq, xs, meta)
+            else:
+                h = self._mlp(x, xq, xs, lw.w13, lw.w2)
+                if tp:
+                    h = self.comm.tp_reduce(h)
+        x, _, _ = self._norm(h, self.w.final_norm, residual, False)
+        if meta.logit_rows is not None:
+            x = x[meta.logit_rows.long()]
+        logits = (x @ self.w.lm_head.t()).float()
+        if tp:
+            logits = self.comm.tp_gather_vocab(logits)
+        return logits

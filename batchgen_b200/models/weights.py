@@ -1,0 +1,252 @@
+"""Weight containers, random initialisation and sharding.
+
+Tensors are created per *checkpoint name* (HF DeepSeek-V3 naming, which the converter's module
+keys ``attn_L`` / ``shared_expert_L`` / ``routed_expert_L_E`` also use —
+batchgen/models/deepseek/deepseekv3/Parallel_Strategy_Manager.py:225-290) from a generator seeded
+by ``hash(seed, name)``, so every rank of a TP/EP layout derives bit-identical full tensors and
+cuts its own shard, and the naive oracle can rebuild exactly the same model.
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import ref
+from ..ops.moe import ExpertWeights
+
+FP8 = torch.float8_e4m3fn
+
+
+@dataclass
+class ParallelLayout:
+    """Which slice of the model one rank owns."""
+    tp_rank: int = 0
+    tp_size: int = 1     # attention heads / dense-MLP / shared-expert / vocab sharding
+    ep_rank: int = 0
+    ep_size: int = 1     # routed experts sharding (contiguous blocks)
+
+    def expert_range(self, n_experts: int) -> Tuple[int, int]:
+        per = n_experts // self.ep_size
+        return self.ep_rank * per, (self.ep_rank + 1) * per
+
+    def head_range(self, n_heads: int) -> Tuple[int, int]:
+        per = n_heads // self.tp_size
+        return self.tp_rank * per, (self.tp_rank + 1) * per
+
+
+@dataclass
+class Linear:
+    """A linear weight [N, K]; ``s`` holds 128x128 block scales when ``w`` is e4m3."""
+    w: torch.Tensor
+    s: Optional[torch.Tensor] = None
+    interleaved: bool = False   # gate/up rows in the tile-interleaved order of the fused SiLU epilogue
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.s is not None
+
+    def interleave_gate_up_(self) -> "Linear":
+        """GPU fp8 gate|up weights: reorder rows so the GEMM epilogue can fuse SiLU(gate)*up."""
+        if self.is_fp8 and self.w.is_cuda and not self.interleaved and (self.w.shape[0] // 2) % 128 == 0:
+            from ..ops.gemm import interleave_gate_up_rows
+            perm = interleave_gate_up_rows(self.w.shape[0], self.w.device)
+            self.w = self.w.view(torch.uint8)[perm].contiguous().view(FP8)
+            self.interleaved = True
+        return self
+
+
+def _seed_for(seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
+
+
+class WeightSource:
+    """Produces full (unsharded) tensors by name.  The default draws N(0, std); a checkpoint
+    loader can be plugged in through ``loader``."""
+
+    def __init__(self, seed: int = 0, std: float = 0.02, device="cpu",
+                 loader: Optional[Callable[[str, Tuple[int, ...]], Optional[torch.Tensor]]] = None):
+        self.seed, self.std, self.device, self.loader = seed, std, torch.device(device), loader
+
+    def get(self, name: str, shape: Tuple[int, ...], kind: str = "normal") -> torch.Tensor:
+        if self.loader is not None:
+            t = self.loader(name, shape)
+            if t is not None:
+                assert tuple(t.shape) == tuple(shape), (name, t.shape, shape)
+                return t.to(self.device, torch.float32)
+        if kind == "ones":
+            return torch.ones(shape, dtype=torch.float32, device=self.device)
+        if kind == "zeros":
+            return torch.zeros(shape, dtype=torch.float32, device=self.device)
+        g = torch.Generator(device=self.device)
+        g.manual_seed(_seed_for(self.seed, name))
+        t = torch.randn(shape, dtype=torch.float32, device=self.device, generator=g)
+        if kind == "norm":            # norm gains around 1
+            return 1.0 + 0.1 * t
+        if kind == "bias":
+            return 0.1 * t
+        return t * self.std
+
+
+def make_linear(w: torch.Tensor, quant: str, dtype: torch.dtype) -> Linear:
+    """Quantise / cast a full-precision [N, K] weight into its runtime form."""
+    if quant == "fp8_block" and w.shape[1] % 128 == 0:
+        q, s = ref.weight_quant_block(w)
+        return Linear(q.contiguous(), s.contiguous())
+    return Linear(w.to(dtype).contiguous())
+
+
+def dequant_linear(lin: Linear) -> torch.Tensor:
+    if lin.is_fp8:
+        return ref.dequant_block(lin.w, lin.s)
+    return lin.w.float()
+
+
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor = None
+    post_norm: torch.Tensor = None
+    # MLA
+    wqkv_a: Linear = None            # [q_lora + kv_lora + rope, H]
+    q_norm: torch.Tensor = None
+    kv_norm: torch.Tensor = None
+    wq_b: Linear = None              # [Hh * qk_head_dim, q_lora]
+    w_uk: torch.Tensor = None        # [Hh, nope, kv_lora]
+    w_uv: torch.Tensor = None        # [Hh, v, kv_lora]
+    wo: Linear = None                # [H, Hh * v]
+    # GQA
+    wqkv: Linear = None              # [(Hq + 2 Hkv) * D, H]
+    sinks: torch.Tensor = None
+    # DSA indexer
+    idx_wq: Linear = None            # [Hi * Di, q_lora]
+    idx_wk: Linear = None            # [Di, H]
+    idx_k_norm_w: torch.Tensor = None
+    idx_k_norm_b: torch.Tensor = None
+    idx_head_w: torch.Tensor = None  # [Hi, H] head-gate projection
+    # dense MLP (also the shared expert of a MoE layer)
+    w13: Linear = None               # [2 I, H]
+    w2: Linear = None                # [H, I]
+    # MoE
+    router_w: torch.Tensor = None    # [E, H] fp32
+    router_bias: torch.Tensor = None
+    experts: ExpertWeights = None
+    latent_down: Linear = None       # Kimi-K3 LatentMoE  [latent, H]
+    latent_up: Linear = None         # [H, latent]
+    latent_norm: torch.Tensor = None
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor = None           # [V, H]
+    final_norm: torch.Tensor = None
+    lm_head: torch.Tensor = None         # [V / tp, H]
+    layers: List[LayerWeights] = field(default_factory=list)
+
+
+def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, dtype: torch.dtype,
+                  alias_experts_every: int = 0) -> ModelWeights:
+    """Create this rank's weights.  ``alias_experts_every`` > 0 makes MoE layers share physical
+    expert storage in a cycle of that many distinct sets (benchmark-only: lets a model whose
+    expert bytes exceed HBM run with identical FLOPs and HBM traffic per layer)."""
+    H = cfg.hidden_size
+    dev = src.device
+    quant = cfg.quant if cfg.quant == "fp8_block" else "none"   # mxfp4 experts are handled by ops.mxfp4
+    mw = ModelWeights()
+    mw.embed = src.get("model.embed_tokens.weight", (cfg.vocab_size, H)).to(dtype)
+    mw.final_norm = src.get("model.norm.weight", (H,), "norm").to(dtype)
+    head = mw.embed if cfg.tie_word_embeddings else src.get("lm_head.weight", (cfg.vocab_size, H)).to(dtype)
+    v0, v1 = layout.tp_rank * cfg.vocab_size // layout.tp_size, (layout.tp_rank + 1) * cfg.vocab_size // layout.tp_size
+    mw.lm_head = head[v0:v1].contiguous()
+    expert_sets: Dict[int, ExpertWeights] = {}
+    for l in range(cfg.num_layers):
+        p = f"model.layers.{l}"
+        lw = LayerWeights()
+        lw.input_norm = src.get(f"{p}.input_layernorm.weight", (H,), "norm").to(dtype)
+        lw.post_norm = src.get(f"{p}.post_attention_layernorm.weight", (H,), "norm").to(dtype)
+        h0, h1 = layout.head_range(cfg.num_heads)
+        if cfg.is_mla:
+            qa = src.get(f"{p}.self_attn.q_a_proj.weight", (cfg.q_lora_rank, H))
+            kva = src.get(f"{p}.self_attn.kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_head_dim, H))
+            lw.wqkv_a = make_linear(torch.cat([qa, kva], 0), quant, dtype)
+            lw.q_norm = src.get(f"{p}.self_attn.q_a_layernorm.weight", (cfg.q_lora_rank,), "norm").to(dtype)
+            lw.kv_norm = src.get(f"{p}.self_attn.kv_a_layernorm.weight", (cfg.kv_lora_rank,), "norm").to(dtype)
+            qb = src.get(f"{p}.self_attn.q_b_proj.weight", (cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank))
+            qb = qb.view(cfg.num_heads, cfg.qk_head_dim, cfg.q_lora_rank)[h0:h1].reshape(-1, cfg.q_lora_rank)
+            lw.wq_b = make_linear(qb, quant, dtype)
+            kvb = src.get(f"{p}.self_attn.kv_b_proj.weight",
+                          (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank))
+            kvb = kvb.view(cfg.num_heads, cfg.qk_nope_head_dim + cfg.v_head_dim, cfg.kv_lora_rank)[h0:h1]
+            lw.w_uk = kvb[:, : cfg.qk_nope_head_dim].contiguous().to(dtype)
+            lw.w_uv = kvb[:, cfg.qk_nope_head_dim:].contiguous().to(dtype)
+            wo = src.get(f"{p}.self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
+            wo = wo.view(H, cfg.num_heads, cfg.v_head_dim)[:, h0:h1].reshape(H, -1)
+            lw.wo = make_linear(wo, quant, dtype)
+            if cfg.layer_has_indexer(l):
+                Hi, Di = cfg.index_n_heads, cfg.index_head_dim
+                lw.idx_wq = make_linear(src.get(f"{p}.self_attn.indexer.wq_b.weight", (Hi * Di, cfg.q_lora_rank)),
+                                        "none", dtype)
+                lw.idx_wk = make_linear(src.get(f"{p}.self_attn.indexer.wk.weight", (Di, H)), "none", dtype)
+                lw.idx_k_norm_w = src.get(f"{p}.self_attn.indexer.k_norm.weight", (Di,), "norm").to(dtype)
+                lw.idx_k_norm_b = src.get(f"{p}.self_attn.indexer.k_norm.bias", (Di,), "bias").to(dtype)
+                lw.idx_head_w = src.get(f"{p}.self_attn.indexer.weights_proj.weight", (Hi, H)).to(dtype)
+        else:
+            D, Hq, Hkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+            k0, k1 = layout.head_range(Hkv)
+            wq = src.get(f"{p}.self_attn.q_proj.weight", (Hq * D, H)).view(Hq, D, H)[h0:h1].reshape(-1, H)
+            wk = src.get(f"{p}.self_attn.k_proj.weight", (Hkv * D, H)).view(Hkv, D, H)[k0:k1].reshape(-1, H)
+            wv = src.get(f"{p}.self_attn.v_proj.weight", (Hkv * D, H)).view(Hkv, D, H)[k0:k1].reshape(-1, H)
+            lw.wqkv = make_linear(torch.cat([wq, wk, wv], 0), quant, dtype)
+            wo = src.get(f"{p}.self_attn.o_proj.weight", (H, Hq * D)).view(H, Hq, D)[:, h0:h1].reshape(H, -1)
+            lw.wo = make_linear(wo, quant, dtype)
+            if cfg.attention_sinks:
+                lw.sinks = src.get(f"{p}.self_attn.sinks", (Hq,), "bias")[h0:h1].contiguous()
+
+        def mlp_pair(prefix: str, inter: int, hid: int):
+            i0, i1 = layout.tp_rank * inter // layout.tp_size, (layout.tp_rank + 1) * inter // layout.tp_size
+            g = src.get(f"{prefix}.gate_proj.weight", (inter, hid))[i0:i1]
+            u = src.get(f"{prefix}.up_proj.weight", (inter, hid))[i0:i1]
+            d = src.get(f"{prefix}.down_proj.weight", (hid, inter))[:, i0:i1]
+            return (make_linear(torch.cat([g, u], 0), quant, dtype).interleave_gate_up_(),
+                    make_linear(d.contiguous(), quant, dtype))
+
+        if cfg.is_moe_layer(l):
+            E, I, eh = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden
+            lw.router_w = src.get(f"{p}.mlp.gate.weight", (E, H)).float()
+            if cfg.scoring_func == "sigmoid":
+                lw.router_bias = src.get(f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias").float()
+            if cfg.moe_latent_size:
+                lw.latent_down = make_linear(src.get(f"{p}.mlp.latent_down_proj.weight", (eh, H)), "none", dtype)
+                lw.latent_up = make_linear(src.get(f"{p}.mlp.latent_up_proj.weight", (H, eh)), "none", dtype)
+                lw.latent_norm = src.get(f"{p}.mlp.latent_norm.weight", (eh,), "norm").to(dtype)
+            key = (l - cfg.first_k_dense) % alias_experts_every if alias_experts_every else l
+            if key in expert_sets:
+                lw.experts = expert_sets[key]
+            else:
+                e0, e1 = layout.expert_range(E)
+                w13s, w2s, s13, s2 = [], [], [], []
+                equant = "fp8_block" if quant == "fp8_block" else "none"
+                for e in range(e0, e1):
+                    ep = f"{p}.mlp.experts.{e}"
+                    g = src.get(f"{ep}.gate_proj.weight", (I, eh))
+                    u = src.get(f"{ep}.up_proj.weight", (I, eh))
+                    d = src.get(f"{ep}.down_proj.weight", (eh, I))
+                    a = make_linear(torch.cat([g, u], 0), equant, dtype)
+                    b = make_linear(d, equant, dtype)
+                    w13s.append(a.w); w2s.append(b.w)
+                    if a.is_fp8:
+                        s13.append(a.s); s2.append(b.s)
+                lw.experts = ExpertWeights(
+                    w13=torch.stack(w13s), w2=torch.stack(w2s),
+                    w13_s=torch.stack(s13) if s13 else None, w2_s=torch.stack(s2) if s2 else None,
+                    quant=equant, activation=cfg.activation).to_device_layout()
+                expert_sets[key] = lw.experts
+            if cfg.n_shared_experts:
+                lw.w13, lw.w2 = mlp_pair(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+        else:
+            lw.w13, lw.w2 = mlp_pair(f"{p}.mlp", cfg.intermediate_size, H)
+        mw.layers.append(lw)
+    return mw

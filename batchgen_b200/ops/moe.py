@@ -1,0 +1,190 @@
+"""MoE building blocks: router, local dispatch (permute + gather + quant), grouped expert GEMMs,
+weighted combine.  ``experts_forward`` runs the expert stack of one rank over the tokens routed to
+its local experts; it is shared by the single-GPU model, the NCCL all-gather/reduce-scatter
+baseline and (for the post-dispatch part) the fused expert-parallel path.
+
+Reference parity: the dataflow is gate -> dispatch -> act-quant -> grouped S1 (gate+up+SiLU) ->
+quant -> grouped S3 (down) -> weighted reduce, as in batchgen/models/glm/glm5/model.py:2391-2508
+and batchgen/moe/grouped_fp8_blockwise_moe.py.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _ext, fused, gemm, ref
+
+FP8 = torch.float8_e4m3fn
+ROW_ALIGN = 128  # grouped segments start on tile boundaries of the tcgen05 GEMM
+
+
+@dataclass
+class ExpertWeights:
+    """Stacked weights of the experts one rank owns.
+
+    quant == "none":      w13 [E, 2I, Kh], w2 [E, Hout, I] in the compute dtype.
+    quant == "fp8_block": w13/w2 e4m3 with 128x128 scales w13_s [E, 2I/128, Kh/128], w2_s;
+                          on CUDA, w13 rows are stored in the gate/up tile-interleaved order.
+    """
+    w13: torch.Tensor
+    w2: torch.Tensor
+    w13_s: Optional[torch.Tensor] = None
+    w2_s: Optional[torch.Tensor] = None
+    quant: str = "none"
+    interleaved: bool = False
+    activation: str = "silu"
+
+    @property
+    def num_experts(self) -> int:
+        return self.w13.shape[0]
+
+    def to_device_layout(self) -> "ExpertWeights":
+        """Reorder w13 rows for the fused SiLU epilogue (GPU, fp8 only)."""
+        if self.quant != "fp8_block" or self.interleaved or not self.w13.is_cuda:
+            return self
+        perm = gemm.interleave_gate_up_rows(self.w13.shape[1], self.w13.device)
+        self.w13 = self.w13.view(torch.uint8)[:, perm].contiguous().view(FP8)
+        self.interleaved = True
+        return self
+
+
+def router_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """fp32 router logits [T, E] = hidden @ weight^T (weight [E, H])."""
+    if hidden.is_cuda and hidden.dtype == torch.bfloat16:
+        return torch.mm(hidden, weight.to(torch.bfloat16).t(), out_dtype=torch.float32)
+    return hidden.float() @ weight.float().t()
+
+
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int = 1,
+                topk_group: int = 1, norm_topk_prob: bool = True, scale: float = 1.0, scoring: str = "sigmoid",
+                num_valid: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (idx [T, k] int32, w [T, k] fp32).  ``num_valid`` (device int32 scalar) marks rows >= it as
+    padding: they get idx -1 / weight 0 and are ignored by dispatch."""
+    if not logits.is_cuda:
+        idx, w = ref.router_topk(logits, bias, top_k, n_group, topk_group, norm_topk_prob, scale, scoring)
+        if num_valid is not None:
+            nv = int(num_valid)
+            idx[nv:] = -1
+            w[nv:] = 0
+        return idx, w
+    T, E = logits.shape
+    logits = logits.contiguous()
+    idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    rc = _ext.lib().bg_router_topk(_ext.ptr(logits), _ext.ptr(bias), _ext.ptr(idx), _ext.ptr(w), ctypes.c_int(T),
+                                   ctypes.c_int(E), ctypes.c_int(top_k), ctypes.c_int(n_group),
+                                   ctypes.c_int(topk_group), ctypes.c_int(int(norm_topk_prob)), ctypes.c_float(scale),
+                                   ctypes.c_int(1 if scoring == "softmax" else 0), _ext.ptr(num_valid), _ext.stream())
+    _ext.check(rc, "bg_router_topk")
+    return idx, w
+
+
+def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.Tensor] = None):
+    """Group (token, k) pairs by local expert.  -> (src_row [cap] int32, pos [T, k] int32,
+    offsets [El+1] int32).  Rows past offsets[El] are unused capacity."""
+    T, K = topk_idx.shape
+    El = hi - lo
+    if not topk_idx.is_cuda:
+        idx = topk_idx
+        if num_valid is not None:
+            idx = idx.clone()
+            idx[int(num_valid):] = -1
+        src, pos, off = ref.moe_permute(idx, hi, lo, hi, align=1)
+        return src.to(torch.int32), pos.to(torch.int32), off.to(torch.int32)
+    cap = (T * K + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN + El * ROW_ALIGN
+    dev = topk_idx.device
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    cursor = torch.empty(El, dtype=torch.int32, device=dev)
+    pos = torch.empty(T, K, dtype=torch.int32, device=dev)
+    src = torch.empty(cap, dtype=torch.int32, device=dev)
+    rc = _ext.lib().bg_moe_permute(_ext.ptr(topk_idx), ctypes.c_int(T), ctypes.c_int(K), ctypes.c_int(lo),
+                                   ctypes.c_int(hi), ctypes.c_int(ROW_ALIGN), _ext.ptr(offsets), _ext.ptr(cursor),
+                                   _ext.ptr(pos), _ext.ptr(src), ctypes.c_int(cap), _ext.ptr(num_valid), _ext.stream())
+    _ext.check(rc, "bg_moe_permute")
+    return src, pos, offsets
+
+
+def gather_quant(hidden: torch.Tensor, src_row: torch.Tensor, offsets: torch.Tensor, pow2_scale: bool = False):
+    """Gather hidden rows into expert-grouped order and quantise -> (q [cap, K] e4m3, s [cap, K/128])."""
+    K = hidden.shape[1]
+    if not hidden.is_cuda:
+        rows = hidden[src_row.clamp_min(0).long()].float()
+        rows = torch.where((src_row >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))
+        return ref.act_quant(rows, 128, pow2_scale)
+    cap = src_row.shape[0]
+    q = torch.empty(cap, K, dtype=FP8, device=hidden.device)
+    s = fused._scale_buffer(cap, K // 128, hidden.device)
+    rc = _ext.lib().bg_moe_gather_quant(_ext.ptr(hidden), ctypes.c_int(hidden.stride(0)), _ext.ptr(src_row),
+                                        _ext.ptr(offsets[-1:]), _ext.ptr(q), _ext.ptr(s), ctypes.c_int(s.stride(1)),
+                                        ctypes.c_int(cap), ctypes.c_int(K), ctypes.c_int(int(pow2_scale)),
+                                        _ext.stream())
+    _ext.check(rc, "bg_moe_gather_quant")
+    return q, s
+
+
+def combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, extra: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out[t] = (extra[t]) + sum_k weights[t, k] * y[pos[t, k]] in ascending k."""
+    if not y.is_cuda:
+        out = ref.moe_combine(y, pos.long(), weights, torch.float32)
+        if extra is not None:
+            out = out + extra.float()
+        return out.to(out_dtype or y.dtype)
+    T, K = pos.shape
+    H = y.shape[1]
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty(T, H, dtype=out_dtype, device=y.device)
+    rc = _ext.lib().bg_moe_combine(_ext.ptr(y), ctypes.c_int(y.stride(0)), _ext.ptr(pos), _ext.ptr(weights),
+                                   _ext.ptr(extra), ctypes.c_int(extra.stride(0) if extra is not None else 0),
+                                   _ext.ptr(out), ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(K),
+                                   ctypes.c_int(H), ctypes.c_int(1 if out_dtype == torch.float32 else 0),
+                                   _ext.stream())
+    _ext.check(rc, "bg_moe_combine")
+    return out
+
+
+def _activation(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
+    return ref.swiglu_clamped(gate_up) if kind == "swiglu_clamped" else ref.silu_mul(gate_up)
+
+
+def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None):
+    """Run gate/up -> activation -> down for rows already grouped by expert.  fp8 path takes
+    (xq, xs); the unquantised path takes ``x_dense``.  Returns y [rows, Hout]."""
+    if ew.quant == "fp8_block":
+        if xq.is_cuda:
+            assert ew.interleaved, "call ExpertWeights.to_device_layout() after loading"
+            act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True)
+            aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:])
+            return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
+        gu = ref.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets)
+        act = _activation(gu, ew.activation)
+        aq, as_ = ref.act_quant(act)
+        return ref.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
+    # unquantised experts (CPU fp32 oracle path and bf16 debugging)
+    x = x_dense
+    out = torch.zeros(x.shape[0], ew.w2.shape[1], dtype=x.dtype, device=x.device)
+    off = offsets.tolist()
+    for e in range(ew.num_experts):
+        a, b = off[e], off[e + 1]
+        if b > a:
+            gu = x[a:b] @ ew.w13[e].t()
+            out[a:b] = _activation(gu, ew.activation) @ ew.w2[e].t()
+    return out
+
+
+def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
+                    expert_lo: int, expert_hi: int, extra: Optional[torch.Tensor] = None,
+                    num_valid: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Partial MoE output of one rank: sum over the (token, k) pairs whose expert is local."""
+    src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid)
+    if ew.quant == "fp8_block":
+        xq, xs = gather_quant(hidden, src, offsets)
+        y = grouped_experts(xq, xs, offsets, ew)
+    else:
+        rows = hidden[src.clamp_min(0).long()]
+        rows = torch.where((src >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))
+        y = grouped_experts(None, None, offsets, ew, x_dense=rows)
+    return combine(y, pos, topk_w, extra, out_dtype or hidden.dtype)

@@ -1,0 +1,425 @@
+"""The batch engine: one scheduling loop per rank that alternates prefill waves and decode
+intervals until every admitted sequence completes.
+
+Design (B200-first; differs from the reference on purpose): with 180 GB of HBM per GPU the *device*
+page pool is the primary KV store — prefill writes latent KV straight into GPU pages and decode reads
+them in place — and the pinned host tier is the overflow: rows put ON_HOLD at a page boundary are
+copied out on a side stream, loaded back when space frees up, and rows whose KV cannot be kept
+anywhere are EVICTED and recomputed.  The reference is host-KV-first (prefill offloads every layer's
+KV to CPU DRAM and decode streams it back, batchgen/batchgen_worker.py:6491-7290); the scheduling
+*policy* (admission order, marginal page charges, boundary decisions every ``decision_interval``
+decode tokens, watermark re-entry into prefill) is kept, see ``scheduler.py``.
+
+All ranks of a TP/EP job run this loop in lock step over identical inputs, so every decision is taken
+redundantly and identically on each rank; only model collectives cross ranks.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..models.transformer import AttnMeta, Transformer
+from ..ops import sampling as sampling_ops
+from . import scheduler as sched
+from .kv_cache import PagedKVCache, build_block_table, slots_for_range
+from .prefix_cache import PrefixCache
+from .sequence import (PageBufferConfig, SamplingParams, Sequence, SequenceStatus, gpu_pages_first_load,
+                       pages_for)
+
+S = SequenceStatus
+
+
+@dataclass
+class EngineStats:
+    prefill_tokens: int = 0
+    prefill_cached_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_tokens: int = 0
+    decode_seconds: float = 0.0
+    decode_steps: int = 0
+    prefill_waves: int = 0
+    holds: int = 0
+    evictions: int = 0
+    loads: int = 0
+    offloaded_pages: int = 0
+
+    def summary(self) -> Dict[str, float]:
+        return dict(
+            prefill_tok_per_s=self.prefill_tokens / self.prefill_seconds if self.prefill_seconds else 0.0,
+            decode_tok_per_s=self.decode_tokens / self.decode_seconds if self.decode_seconds else 0.0,
+            **self.__dict__)
+
+
+class Engine:
+    def __init__(self, model: Transformer, ecfg: EngineConfig, num_gpu_pages: Optional[int] = None,
+                 num_host_pages: int = 0, on_complete: Optional[Callable[[Sequence], None]] = None,
+                 graph_runner=None):
+        ecfg.validate()
+        self.model, self.cfg, self.ecfg = model, model.cfg, ecfg
+        self.device = model.device
+        self.buf = PageBufferConfig(ecfg.page_size, ecfg.initial_gpu_page_buffer, ecfg.extension_gpu_page_buffer,
+                                    ecfg.decision_frequency_pages)
+        kv_dtype = model.dtype
+        n_pages = num_gpu_pages or ecfg.num_gpu_pages
+        if not n_pages:
+            raise ValueError("num_gpu_pages must be given (see planner.size_kv_pool for automatic sizing)")
+        self.kv = PagedKVCache(self.cfg, n_pages, ecfg.page_size, self.device, kv_dtype)
+        self.host_kv = (PagedKVCache(self.cfg, num_host_pages, ecfg.page_size, "cpu", kv_dtype, pinned=True)
+                        if num_host_pages else None)
+        self.prefix = PrefixCache(self.kv.alloc, ecfg.page_size) if ecfg.enable_prefix_cache else None
+        self.kv_token_budget = (ecfg.max_model_len if ecfg.max_model_len > 0 else n_pages * ecfg.page_size)
+        self.seqs: Dict[int, Sequence] = {}
+        self._next_idx = 0
+        self.stats = EngineStats()
+        self.on_complete = on_complete
+        self.graph_runner = graph_runner
+        self.copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.guard = sched.PrefillProgressGuard()
+        self._gen = torch.Generator(device=self.device)
+        self._gen.manual_seed(ecfg.seed)
+        self.step_hook: Optional[Callable[[str], None]] = None   # watchdog feed
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None, custom_id: str = "",
+                    batch_id: str = "", prefill_order: Optional[int] = None) -> Sequence:
+        if len(prompt_ids) == 0:
+            raise ValueError("empty prompt")
+        params = params or SamplingParams()
+        if self.ecfg.max_model_len > 0 and len(prompt_ids) + params.max_new_tokens > self.ecfg.max_model_len:
+            raise ValueError(f"context {len(prompt_ids)} + {params.max_new_tokens} exceeds max_model_len "
+                             f"{self.ecfg.max_model_len}")
+        s = Sequence(global_idx=self._next_idx, prompt_ids=list(map(int, prompt_ids)), params=params,
+                     custom_id=custom_id, batch_id=batch_id, prefill_order=prefill_order)
+        self._next_idx += 1
+        self.seqs[s.global_idx] = s
+        return s
+
+    # ------------------------------------------------------------------ helpers
+    def _by_status(self, *st) -> List[Sequence]:
+        return [s for s in self.seqs.values() if s.status in st]
+
+    def _free_pages(self) -> int:
+        return self.kv.alloc.num_free
+
+    def _sync(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    def _reclaim(self, want: int) -> int:
+        if self.prefix is None or want <= 0:
+            return 0
+        return self.prefix.evict(want)
+
+    def _complete(self, s: Sequence, reason: str) -> None:
+        s.finish_reason = reason
+        if s.gpu_pages:
+            self.kv.alloc.free(s.gpu_pages)
+            s.gpu_pages = []
+        if s.host_pages and self.host_kv is not None:
+            self.host_kv.alloc.free(s.host_pages)
+            s.host_pages = []
+        s.transition(S.COMPLETED)
+        if self.on_complete is not None:
+            self.on_complete(s)
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill_wave(self) -> int:
+        """Admit and prefill one wave.  Returns the number of sequences prefilled."""
+        cands = self._by_status(S.QUEUEING, S.EVICTED)
+        if not cands:
+            return 0
+        reclaimable = self.prefix.reclaimable_pages() if self.prefix else 0
+        sel = sched.select_prefill_batch(cands, self._free_pages(), self.buf,
+                                         reserve_decode_tokens=self.buf.page_size,
+                                         reclaimable_pages=reclaimable)
+        live = len(self._by_status(S.PREFILLED, S.IN_DECODE, S.ON_HOLD))
+        self.guard.observe(len(sel.admitted), live, (len(cands), self._free_pages()))
+        if not sel.admitted:
+            return 0
+        t0 = time.perf_counter()
+        wave = [self.seqs[i] for i in sel.admitted]
+        new_lens: List[int] = []
+        for s in wave:
+            s.transition(S.IN_PREFILL)
+            ids = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
+            n_total = len(ids)
+            cached_pages: List[int] = []
+            if self.prefix is not None:
+                cached_pages, _ = self.prefix.lookup(ids)
+                self.prefix.attach(cached_pages)
+            n_cached = len(cached_pages) * self.buf.page_size
+            need = pages_for(n_total + 1, self.buf.page_size) - len(cached_pages)
+            if need > self._free_pages():
+                self._reclaim(need - self._free_pages())
+            s.gpu_pages = list(cached_pages) + self.kv.alloc.alloc(need)
+            s.cached_prefix_tokens = n_cached
+            s.num_cached_tokens = n_cached
+            new_lens.append(n_total - n_cached)
+        # pack into token-capped micro-batches and run them
+        for mb in sched.prepack_ffd(new_lens, self.ecfg.max_prefill_tokens):
+            group = [wave[i] for i in mb.seq_indices]
+            self._run_prefill_microbatch(group)
+        for s in wave:
+            if self.prefix is not None:
+                ids = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
+                self.prefix.commit(ids, s.gpu_pages)
+            s.transition(S.PREFILLED)
+            fin = s.is_finished(self.cfg.eos_token_id)
+            if fin:
+                self._complete(s, fin)
+        self._sync()
+        self.stats.prefill_seconds += time.perf_counter() - t0
+        self.stats.prefill_waves += 1
+        return len(wave)
+
+    def _run_prefill_microbatch(self, group: List[Sequence]) -> None:
+        ps = self.buf.page_size
+        ids: List[int] = []
+        pos: List[int] = []
+        slots: List[int] = []
+        cu = [0]
+        ctx_lens: List[int] = []
+        for s in group:
+            full = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
+            a, b = s.num_cached_tokens, len(full)
+            ids += full[a:b]
+            pos += list(range(a, b))
+            slots += slots_for_range(s.gpu_pages, a, b, ps)
+            cu.append(cu[-1] + (b - a))
+            ctx_lens.append(a)
+        dev = self.device
+        meta = AttnMeta(
+            mode="prefill",
+            positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+            block_table=build_block_table([s.gpu_pages for s in group], dev),
+            cu_seqlens=cu, ctx_lens=ctx_lens,
+            logit_rows=torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev))
+        logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
+        toks = self._sample(logits, group).tolist()
+        for s, t in zip(group, toks):
+            full_len = len(s.all_ids if s.reentry_decoded_baseline else s.prompt_ids)
+            self.stats.prefill_tokens += full_len - s.num_cached_tokens
+            self.stats.prefill_cached_tokens += s.cached_prefix_tokens
+            s.num_cached_tokens = full_len
+            s.output_ids.append(int(t))
+            s.reentry_decoded_baseline = 0
+
+    # ------------------------------------------------------------------ sampling
+    def _sample(self, logits: torch.Tensor, rows: List[Sequence]) -> torch.Tensor:
+        if all(s.params.temperature <= 0 for s in rows):
+            return sampling_ops.greedy(logits)
+        dev = logits.device
+        temp = torch.tensor([s.params.temperature for s in rows], dtype=torch.float32, device=dev)
+        tk = torch.tensor([s.params.top_k for s in rows], dtype=torch.int32, device=dev)
+        tp = torch.tensor([s.params.top_p for s in rows], dtype=torch.float32, device=dev)
+        return sampling_ops.sample(logits, temp, tk, tp, generator=self._gen)
+
+    # ------------------------------------------------------------------ decode
+    def _enter_decode(self, s: Sequence) -> bool:
+        """Make sure the row's KV and growth buffer are on the GPU; returns False if it does not fit."""
+        want = gpu_pages_first_load(s.context_len, self.buf, self.kv_token_budget)
+        if s.host_pages and not s.gpu_pages:          # parked in the host tier: load back
+            need = max(want, len(s.host_pages))
+            if need > self._free_pages():
+                self._reclaim(need - self._free_pages())
+            if need > self._free_pages():
+                return False
+            s.gpu_pages = self.kv.alloc.alloc(need)
+            self.kv.copy_pages_from(self.host_kv, s.host_pages, s.gpu_pages[: len(s.host_pages)], self.copy_stream)
+            if self.copy_stream is not None:
+                torch.cuda.current_stream().wait_stream(self.copy_stream)
+            self.host_kv.alloc.free(s.host_pages)
+            s.host_pages = []
+            self.stats.loads += 1
+        extra = want - len(s.gpu_pages)
+        if extra > 0:
+            if extra > self._free_pages():
+                self._reclaim(extra - self._free_pages())
+            if extra > self._free_pages():
+                return False
+            s.gpu_pages += self.kv.alloc.alloc(extra)
+        s.had_initial_gpu_reservation = True
+        s.transition(S.IN_DECODE)
+        return True
+
+    def _hold(self, s: Sequence) -> None:
+        """Take a row out of the decode batch; move its KV to the host tier when there is one."""
+        used = pages_for(s.num_cached_tokens, self.buf.page_size)
+        if self.host_kv is not None and self.host_kv.alloc.num_free >= used:
+            s.host_pages = self.host_kv.alloc.alloc(used)
+            self.host_kv.copy_pages_from(self.kv, s.gpu_pages[:used], s.host_pages, self.copy_stream)
+            if self.copy_stream is not None:
+                self.copy_stream.synchronize()
+            self.kv.alloc.free(s.gpu_pages)
+            s.gpu_pages = []
+            self.stats.offloaded_pages += used
+            s.transition(S.ON_HOLD)
+            self.stats.holds += 1
+        else:
+            self._evict(s)
+
+    def _evict(self, s: Sequence) -> None:
+        if s.gpu_pages:
+            self.kv.alloc.free(s.gpu_pages)
+        if s.host_pages and self.host_kv is not None:
+            self.host_kv.alloc.free(s.host_pages)
+        s.evict()
+        s.output_ids = list(s.output_ids)     # decoded tokens are kept and replayed through prefill
+        self.stats.evictions += 1
+
+    def _decode_step(self, rows: List[Sequence]) -> None:
+        ps = self.buf.page_size
+        dev = self.device
+        ids = [s.all_ids[s.num_cached_tokens] for s in rows]
+        pos = [s.num_cached_tokens for s in rows]
+        slots = [s.gpu_pages[p // ps] * ps + p % ps for s, p in zip(rows, pos)]
+        lens = [p + 1 for p in pos]
+        if self.graph_runner is not None:
+            logits = self.graph_runner.decode(self, rows, ids, pos, slots, lens)
+        else:
+            meta = AttnMeta(
+                mode="decode",
+                positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+                slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+                block_table=build_block_table([s.gpu_pages for s in rows], dev),
+                seqlens=torch.tensor(lens, dtype=torch.int32, device=dev))
+            logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
+        toks = self._sample(logits, rows).tolist()
+        for s, t in zip(rows, toks):
+            s.num_cached_tokens += 1
+            s.output_ids.append(int(t))
+        self.stats.decode_tokens += len(rows)
+        self.stats.decode_steps += 1
+
+    def _decode_interval(self) -> int:
+        """Admit rows, decode up to one decision interval, then apply the boundary decisions.
+        Returns the number of decode steps executed."""
+        free = {0: self._free_pages() + (self.prefix.reclaimable_pages() if self.prefix else 0)}
+        in_dec = self._by_status(S.IN_DECODE)
+        admit = sched.select_decode_batch(self.seqs.values(), free, {0: len(in_dec)}, self.ecfg.max_decode_batch,
+                                          self.buf, self.kv_token_budget, total_pages_per_bucket=self.kv.num_pages,
+                                          resident={s.global_idx for s in self.seqs.values() if s.gpu_pages})
+        for gi in admit:
+            self._enter_decode(self.seqs[gi])
+        rows = sorted(self._by_status(S.IN_DECODE), key=lambda s: s.global_idx)
+        if not rows:
+            return 0
+        t0 = time.perf_counter()
+        steps = 0
+        eos = self.cfg.eos_token_id
+        for _ in range(self.buf.decision_interval):
+            live = [s for s in rows if not s.is_finished(eos)]
+            if not live:
+                break
+            # a row about to cross into a page it does not own ends the interval early
+            if any(pages_for(s.num_cached_tokens + 1, self.buf.page_size) > len(s.gpu_pages) for s in live):
+                break
+            self._decode_step(live)
+            steps += 1
+            if self.step_hook is not None:
+                self.step_hook("decode")
+        self._sync()
+        self.stats.decode_seconds += time.perf_counter() - t0
+        self._apply_boundary()
+        return steps
+
+    def _apply_boundary(self) -> None:
+        free_host = self.host_kv.alloc.num_free if self.host_kv is not None else 0
+        d = sched.compute_boundary_decisions(
+            list(self.seqs.values()), self.cfg.eos_token_id, {0: self._free_pages()}, free_host, self.buf,
+            self.kv_token_budget, self.ecfg.max_decode_batch, self.ecfg.host_kv_chunk_size, host_tier=False,
+            reclaimable_host_pages=0)
+        if d.scheduler_error:
+            raise RuntimeError(d.scheduler_error)
+        for gi in d.completed:
+            s = self.seqs[gi]
+            self._complete(s, s.is_finished(self.cfg.eos_token_id))
+        for gi in d.on_hold:
+            self._hold(self.seqs[gi])
+        for gi, extra in d.extend.items():
+            s = self.seqs[gi]
+            if s.status != S.IN_DECODE:
+                continue
+            if extra > self._free_pages():
+                self._reclaim(extra - self._free_pages())
+            if extra > self._free_pages():
+                self._hold(s)
+                continue
+            s.gpu_pages += self.kv.alloc.alloc(extra)
+        for gi in d.load:
+            s = self.seqs[gi]
+            if s.status in (S.PREFILLED, S.ON_HOLD):
+                self._enter_decode(s)
+
+    # ------------------------------------------------------------------ main loop
+    def has_work(self) -> bool:
+        return any(s.status != S.COMPLETED for s in self.seqs.values())
+
+    def step(self) -> None:
+        """One scheduling action: a prefill wave when nothing is decodable or free pages allow more
+        admissions, otherwise one decode interval."""
+        waiting = self._by_status(S.QUEUEING, S.EVICTED)
+        decodable = self._by_status(S.PREFILLED, S.IN_DECODE, S.ON_HOLD)
+        did = 0
+        if waiting and (not decodable or self._prefill_headroom(waiting)):
+            did = self._prefill_wave()
+        if self._by_status(S.PREFILLED, S.IN_DECODE, S.ON_HOLD):
+            steps = self._decode_interval()
+            if steps == 0 and did == 0:
+                self._break_deadlock()
+        elif did == 0 and waiting:
+            self._break_deadlock()
+
+    def _prefill_headroom(self, waiting: List[Sequence]) -> bool:
+        """Is it worth leaving decode for another wave?  Yes when the decode batch has free rows and
+        the smallest waiting prompt fits the free pages (the watermark rule of the reference,
+        batchgen/worker/kv_manager.py:632-670, applied to the device pool)."""
+        if len(self._by_status(S.IN_DECODE)) >= self.ecfg.max_decode_batch:
+            return False
+        free_frac = self._free_pages() / max(1, self.kv.num_pages)
+        if not sched.watermark_trigger([free_frac], 100 - self.ecfg.host_kv_watermark, True, False):
+            return False
+        smallest = min(s.context_len for s in waiting)
+        return pages_for(smallest + self.buf.page_size, self.buf.page_size) <= self._free_pages()
+
+    def _break_deadlock(self) -> None:
+        """Nothing could run: free space by evicting the parked row with the least decoded work."""
+        parked = self._by_status(S.ON_HOLD, S.PREFILLED)
+        if parked:
+            v = min(parked, key=lambda s: (s.num_decoded, s.global_idx))
+            self._evict(v)
+            return
+        stuck = self._by_status(S.IN_DECODE)
+        if stuck:
+            # rows that can neither grow (context budget exhausted) nor be parked: finish them
+            for s in stuck:
+                if pages_for(s.num_cached_tokens + 1, self.buf.page_size) > len(s.gpu_pages):
+                    self._complete(s, "length")
+            return
+        waiting = self._by_status(S.QUEUEING, S.EVICTED)
+        if waiting:
+            s = min(waiting, key=lambda s: s.context_len)
+            if pages_for(s.context_len + 1, self.buf.page_size) > self.kv.num_pages:
+                s.status = S.COMPLETED
+                s.finish_reason = "error: prompt does not fit the KV pool"
+                if self.on_complete:
+                    self.on_complete(s)
+
+    def run_to_completion(self, max_iterations: int = 1_000_000) -> List[Sequence]:
+        it = 0
+        while self.has_work():
+            self.step()
+            it += 1
+            if it > max_iterations:
+                raise RuntimeError("engine did not converge")
+        return sorted(self.seqs.values(), key=lambda s: s.global_idx)
+
+    def generate(self, prompts: Seq[Seq[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        seqs = [self.add_request(p, params) for p in prompts]
+        self.run_to_completion()
+        return [s.output_ids for s in seqs]

@@ -1,0 +1,154 @@
+"""Paged KV storage: device pool, host (CPU-DRAM) tier, page allocators and movers.
+
+Device pool: one tensor ``[layers, pages, page_size, row]`` (row = 576 for MLA latent), plus, for
+DSA models, a second region of FP8 index keys ``[idx_layers, pages, page_size, 128]`` with fp32
+scales — the same logical page id addresses both regions (the reference's "dual" coordinators,
+batchgen/kv_cache/dual_kv_cache_coordinator.py).  Host tier: the same layout in pinned memory.
+Pages are reference counted so that sequences sharing a prefix share physical pages
+(batchgen/worker/decode.py:169-199: one physical page per distinct host page).
+
+Reference parity: batchgen/kv_cache/gpu_paged_kv_manager.py:110-761 (pool ``[layers, pages, 64,
+heads, dim]``, page-table state), core/KV_Storage/host_paged_kv_* (host pages, async load/offload).
+The native host-tier backend lives in ``core/csrc``; this module is its Python front.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence as Seq, Tuple
+
+import torch
+
+from ..config import ModelConfig
+
+FP8 = torch.float8_e4m3fn
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PageAllocator:
+    """Free-list allocator with reference counts."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free: List[int] = list(range(num_pages - 1, -1, -1))
+        self._ref = [0] * num_pages
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    @property
+    def num_used(self) -> int:
+        return self.num_pages - len(self._free)
+
+    def alloc(self, n: int) -> List[int]:
+        if n > len(self._free):
+            raise OutOfPages(f"need {n} pages, {len(self._free)} free of {self.num_pages}")
+        out = [self._free.pop() for _ in range(n)]
+        for p in out:
+            self._ref[p] = 1
+        return out
+
+    def share(self, pages: Seq[int]) -> None:
+        for p in pages:
+            assert self._ref[p] > 0, f"page {p} is not live"
+            self._ref[p] += 1
+
+    def free(self, pages: Seq[int]) -> None:
+        for p in pages:
+            assert self._ref[p] > 0, f"double free of page {p}"
+            self._ref[p] -= 1
+            if self._ref[p] == 0:
+                self._free.append(p)
+
+    def refcount(self, page: int) -> int:
+        return self._ref[page]
+
+
+class PagedKVCache:
+    """One tier (device or pinned host) of paged KV."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int, device, dtype: torch.dtype,
+                 pinned: bool = False, row_dim: Optional[int] = None):
+        self.cfg, self.num_pages, self.page_size = cfg, num_pages, page_size
+        self.device = torch.device(device)
+        self.row_dim = row_dim or cfg.kv_cache_dim
+        pin = pinned and self.device.type == "cpu" and torch.cuda.is_available()
+        self.kv = torch.zeros(cfg.num_layers, num_pages, page_size, self.row_dim, dtype=dtype, device=self.device,
+                              pin_memory=pin)
+        self.idx_layers: Dict[int, int] = {}
+        self.idx_k = self.idx_s = None
+        if cfg.has_dsa:
+            layers = list(cfg.indexer_full_layers) or list(range(cfg.num_layers))
+            self.idx_layers = {l: i for i, l in enumerate(layers)}
+            self.idx_k = torch.zeros(len(layers), num_pages, page_size, cfg.index_head_dim, dtype=FP8,
+                                     device=self.device, pin_memory=pin)
+            self.idx_s = torch.zeros(len(layers), num_pages, page_size, dtype=torch.float32, device=self.device,
+                                     pin_memory=pin)
+        self.alloc = PageAllocator(num_pages)
+
+    # ---- views used by the model
+    def latent(self, layer: int) -> torch.Tensor:
+        return self.kv[layer]
+
+    def index_keys(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        i = self.idx_layers[layer]
+        return self.idx_k[i], self.idx_s[i]
+
+    def write_index_keys(self, layer: int, kq: torch.Tensor, ks: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+        i = self.idx_layers[layer]
+        valid = slot_mapping >= 0
+        slots = slot_mapping[valid].long()
+        self.idx_k[i].view(-1, self.cfg.index_head_dim).view(torch.uint8)[slots] = kq[valid].view(torch.uint8)
+        self.idx_s[i].view(-1)[slots] = ks[valid]
+
+    def bytes_per_page(self) -> int:
+        b = self.kv[0, 0].numel() * self.kv.element_size() * self.cfg.num_layers
+        if self.idx_k is not None:
+            b += len(self.idx_layers) * (self.idx_k[0, 0].numel() + 4 * self.page_size)
+        return b
+
+    # ---- page movement between tiers
+    def copy_pages_from(self, other: "PagedKVCache", src_pages: Seq[int], dst_pages: Seq[int],
+                        stream: Optional["torch.cuda.Stream"] = None) -> None:
+        """self[:, dst] <- other[:, src] for every layer (both regions)."""
+        if not src_pages:
+            return
+        src = torch.as_tensor(list(src_pages), dtype=torch.long)
+        dst = torch.as_tensor(list(dst_pages), dtype=torch.long)
+        ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
+        with ctx:
+            if self.device.type == other.device.type == "cpu":
+                self.kv[:, dst] = other.kv[:, src]
+                if self.idx_k is not None:
+                    self.idx_k.view(torch.uint8)[:, dst] = other.idx_k.view(torch.uint8)[:, src]
+                    self.idx_s[:, dst] = other.idx_s[:, src]
+                return
+            for s, d in zip(src.tolist(), dst.tolist()):
+                self.kv[:, d].copy_(other.kv[:, s], non_blocking=True)
+                if self.idx_k is not None:
+                    self.idx_k[:, d].copy_(other.idx_k[:, s], non_blocking=True)
+                    self.idx_s[:, d].copy_(other.idx_s[:, s], non_blocking=True)
+
+
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def slots_for_range(pages: Seq[int], start: int, end: int, page_size: int) -> List[int]:
+    """Flat slot ids of token positions [start, end) of a sequence whose pages are ``pages``."""
+    return [pages[p // page_size] * page_size + p % page_size for p in range(start, end)]
+
+
+def build_block_table(page_lists: Seq[Seq[int]], device, min_width: int = 1) -> torch.Tensor:
+    width = max(min_width, max((len(p) for p in page_lists), default=1))
+    bt = torch.zeros(len(page_lists), width, dtype=torch.int32)
+    for i, p in enumerate(page_lists):
+        if p:
+            bt[i, : len(p)] = torch.as_tensor(list(p), dtype=torch.int32)
+    return bt.to(device)
