@@ -31,6 +31,7 @@ from ..config import ModelConfig
 from ..ops import attention as attn_ops
 from ..ops import fused, gemm, ref
 from ..ops import moe as moe_ops
+from ..utils.timing import null_timer
 from .weights import LayerWeights, Linear, ModelWeights, ParallelLayout
 
 
@@ -84,7 +85,7 @@ class Transformer:
         self.device = weights.embed.device
         self.dtype = weights.embed.dtype
         self.rope = RopeTables(cfg, max_positions, self.device)
-        self.timer = None     # optional utils.timing.TimingStats
+        self.timer = null_timer()     # utils.timing.TimingStats when profiling
 
     # ------------------------------------------------------------------ helpers
     def _mlp(self, x, xq, xs, w13: Linear, w2: Linear):
@@ -103,19 +104,42 @@ class Transformer:
         cfg = self.cfg
         T = x.shape[0]
         Hh = lw.w_uk.shape[0]
-        qkv_a = linear(x, lw.wqkv_a, xq, xs)
+        tm = self.timer
+        with tm.timed("attn.qkv_a_gemm", l):
+            qkv_a = linear(x, lw.wqkv_a, xq, xs)
         q_a, kv_a = qkv_a[:, : cfg.q_lora_rank], qkv_a[:, cfg.q_lora_rank:]
+        with tm.timed("attn.kv_write_qnorm_qb_rope", l):
+            self._mla_q(lw, q_a, kv_a, meta, cache, l)
+        q, qn = self._q, self._qn
+        q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
+        # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
+        with tm.timed("attn.q_absorb", l):
+            q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_uk).transpose(0, 1)
+        sel = None
+        if cfg.has_dsa:
+            with tm.timed("attn.dsa_indexer", l):
+                sel = self._dsa_select(l, lw, x, qn, meta, cache)
+        with tm.timed("attn.core_" + meta.mode, l):
+            o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
+        # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
+        with tm.timed("attn.out_absorb", l):
+            o = torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
+        with tm.timed("attn.o_proj", l):
+            return linear(o, lw.wo)
+
+    def _mla_q(self, lw, q_a, kv_a, meta, cache, l):
+        cfg = self.cfg
+        T = q_a.shape[0]
+        Hh = lw.w_uk.shape[0]
         fused.mla_kv_write(kv_a, lw.kv_norm, meta.positions, self.rope.cos, self.rope.sin, meta.slot_mapping,
                            cache.latent(l), cfg.kv_lora_rank, cfg.rms_eps, cfg.rope_interleaved)
         qn, qnq, qns = fused.rmsnorm(q_a, lw.q_norm, cfg.rms_eps, quant=lw.wq_b.is_fp8)
         q = linear(qn, lw.wq_b, qnq, qns).view(T, Hh, cfg.qk_head_dim)
         fused.rope_q_(q, meta.positions, self.rope.cos, self.rope.sin, cfg.qk_rope_head_dim, cfg.rope_interleaved)
-        q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
-        # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
-        q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_uk).transpose(0, 1)
-        sel = None
-        if cfg.has_dsa:
-            sel = self._dsa_select(l, lw, x, qn, meta, cache)
+        self._q, self._qn = q, qn
+
+    def _mla_core(self, l, lw, q_abs, q_pe, sel, meta, cache):
+        cfg = self.cfg
         if meta.mode == "decode":
             if sel is not None:
                 o_lat = attn_ops.sparse_mla_decode(q_abs, q_pe, cache.latent(l), meta.block_table, sel[0], sel[1],
@@ -129,9 +153,7 @@ class Transformer:
             else:
                 o_lat = attn_ops.mla_prefill(q_abs.contiguous(), q_pe.contiguous(), cache.latent(l), meta.block_table,
                                              meta.cu_seqlens, meta.ctx_lens, cfg.softmax_scale, cfg.kv_lora_rank)
-        # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
-        o = torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
-        return linear(o, lw.wo)
+        return o_lat
 
     def _dsa_select(self, l, lw, x, qn, meta: AttnMeta, cache):
         """DSA indexer: write this step's FP8 index keys, score every cached key for each query
@@ -229,23 +251,27 @@ class Transformer:
     # ------------------------------------------------------------------ feed-forward
     def _moe(self, l: int, lw: LayerWeights, x, xq, xs, meta: AttnMeta) -> torch.Tensor:
         cfg = self.cfg
-        logits = moe_ops.router_logits(x, lw.router_w)
-        idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group,
-                                     cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.scoring_func,
-                                     num_valid=meta.num_valid)
+        tm = self.timer
+        with tm.timed("moe.router", l):
+            logits = moe_ops.router_logits(x, lw.router_w)
+            idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group,
+                                         cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor,
+                                         cfg.scoring_func, num_valid=meta.num_valid)
         shared = None
         if lw.w13 is not None:
-            shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+            with tm.timed("moe.shared_expert", l):
+                shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
             if self.comm is not None and self.layout.tp_size > 1:
                 shared = self.comm.tp_reduce(shared)
         h = x
         if cfg.moe_latent_size:
             h = linear(x, lw.latent_down)
-        if self.comm is not None and self.layout.ep_size > 1:
-            routed = self.comm.moe(h, idx, w, lw.experts, cfg.n_routed_experts, num_valid=meta.num_valid)
-        else:
-            routed = moe_ops.experts_forward(h, idx, w, lw.experts, 0, cfg.n_routed_experts,
-                                             num_valid=meta.num_valid)
+        with tm.timed("moe.routed_experts", l):
+            if self.comm is not None and self.layout.ep_size > 1:
+                routed = self.comm.moe(h, idx, w, lw.experts, cfg.n_routed_experts, num_valid=meta.num_valid)
+            else:
+                routed = moe_ops.experts_forward(h, idx, w, lw.experts, 0, cfg.n_routed_experts,
+                                                 num_valid=meta.num_valid, timer=tm)
         if cfg.moe_latent_size:
             routed = linear(fused.rmsnorm(routed, lw.latent_norm, cfg.rms_eps)[0], lw.latent_up)
         return routed if shared is None else routed + shared
@@ -259,26 +285,33 @@ class Transformer:
         tp = self.comm is not None and self.layout.tp_size > 1
         for l, lw in enumerate(self.w.layers):
             fp8_in = (lw.wqkv_a or lw.wqkv).is_fp8
-            if residual is None:
-                residual = h.clone()
-                x, xq, xs = self._norm(h, lw.input_norm, None, fp8_in)
-            else:
-                x, xq, xs = self._norm(h, lw.input_norm, residual, fp8_in)
+            tm = self.timer
+            with tm.timed("norm", l):
+                if residual is None:
+                    residual = h.clone()
+                    x, xq, xs = self._norm(h, lw.input_norm, None, fp8_in)
+                else:
+                    x, xq, xs = self._norm(h, lw.input_norm, residual, fp8_in)
             a = self._mla(l, lw, x, xq, xs, meta, cache) if cfg.is_mla else self._gqa(l, lw, x, xq, xs, meta, cache)
             if tp:
-                a = self.comm.tp_reduce(a)
+                with tm.timed("comm.tp_reduce", l):
+                    a = self.comm.tp_reduce(a)
             ffn_fp8 = (lw.w13 is not None and lw.w13.is_fp8)
-            x, xq, xs = self._norm(a, lw.post_norm, residual, ffn_fp8)
+            with tm.timed("norm", l):
+                x, xq, xs = self._norm(a, lw.post_norm, residual, ffn_fp8)
             if cfg.is_moe_layer(l):
                 h = self._moe(l, lw, x, xq, xs, meta)
             else:
-                h = self._mlp(x, xq, xs, lw.w13, lw.w2)
+                with tm.timed("dense_mlp", l):
+                    h = self._mlp(x, xq, xs, lw.w13, lw.w2)
                 if tp:
-                    h = self.comm.tp_reduce(h)
+                    with tm.timed("comm.tp_reduce", l):
+                        h = self.comm.tp_reduce(h)
         x, _, _ = self._norm(h, self.w.final_norm, residual, False)
         if meta.logit_rows is not None:
             x = x[meta.logit_rows.long()]
-        logits = (x @ self.w.lm_head.t()).float()
+        with self.timer.timed("lm_head"):
+            logits = (x @ self.w.lm_head.t()).float()
         if tp:
             logits = self.comm.tp_gather_vocab(logits)
         return logits

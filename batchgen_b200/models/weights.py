@@ -69,8 +69,13 @@ class WeightSource:
     loader can be plugged in through ``loader``."""
 
     def __init__(self, seed: int = 0, std: float = 0.02, device="cpu",
-                 loader: Optional[Callable[[str, Tuple[int, ...]], Optional[torch.Tensor]]] = None):
+                 loader: Optional[Callable[[str, Tuple[int, ...]], Optional[torch.Tensor]]] = None,
+                 gen_device=None):
+        """``gen_device`` is where random tensors are drawn.  The default (CPU) gives the same
+        values whatever ``device`` is, so a GPU model and its CPU oracle share weights; drawing on
+        the GPU is much faster for full-size benchmark models but yields different values."""
         self.seed, self.std, self.device, self.loader = seed, std, torch.device(device), loader
+        self.gen_device = torch.device(gen_device) if gen_device is not None else torch.device("cpu")
 
     def get(self, name: str, shape: Tuple[int, ...], kind: str = "normal") -> torch.Tensor:
         if self.loader is not None:
@@ -82,9 +87,9 @@ class WeightSource:
             return torch.ones(shape, dtype=torch.float32, device=self.device)
         if kind == "zeros":
             return torch.zeros(shape, dtype=torch.float32, device=self.device)
-        g = torch.Generator(device=self.device)
+        g = torch.Generator(device=self.gen_device)
         g.manual_seed(_seed_for(self.seed, name))
-        t = torch.randn(shape, dtype=torch.float32, device=self.device, generator=g)
+        t = torch.randn(shape, dtype=torch.float32, device=self.gen_device, generator=g).to(self.device)
         if kind == "norm":            # norm gains around 1
             return 1.0 + 0.1 * t
         if kind == "bias":

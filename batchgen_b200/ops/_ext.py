@@ -69,6 +69,10 @@ def check_status(device=None) -> int:
     return s
 
 
-def check(rc: int, what: str) -> None:
+LAUNCHES = {"count": 0}   # kernels of this library launched by this process (bench.py reports it)
+
+
+def check(rc: int, what: str, kernels: int = 1) -> None:
     if rc != 0:
         raise KernelError(f"{what} failed to launch (code {rc})")
+    LAUNCHES["count"] += kernels

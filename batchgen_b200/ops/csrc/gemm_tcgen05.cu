@@ -267,7 +267,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           sbh_next = __ldg(sb_hi + kg + 1);
         }
         const int buf = acc & 1;
-        if (!mbar_wait(&ss.tmem_full[buf], (acc >> 1) & 1, abort_flag, kTimeoutEpilogue)) { ok = false; break; }
+        // warp-uniform outcome: the lanes of a warp leave the loop together
+        if (!__all_sync(0xffffffffu, mbar_wait(&ss.tmem_full[buf], (acc >> 1) & 1, abort_flag, kTimeoutEpilogue))) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + half * 64;
         uint32_t v0[32], v1[32];

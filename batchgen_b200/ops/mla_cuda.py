@@ -35,19 +35,31 @@ def mla_decode_lib(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora):
 
 
 def mla_decode(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora):
-    L = _ext.lib()
-    if hasattr(L, "bg_mla_decode") and _kernel_supports(q_abs, q_pe, cache, kv_lora):
+    if _kernel_supports(q_abs, q_pe, cache, kv_lora):
         from .mla_kernel import mla_decode_tc
         return mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora)
     return mla_decode_lib(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora)
 
 
 def _kernel_supports(q_abs, q_pe, cache, kv_lora) -> bool:
+    """The tcgen05 kernel covers the production geometry: bf16, 512 + 64 latent row, 64-token pages,
+    a multiple of 8 heads per rank.  Other (test-sized) geometries use the library path."""
+    import os
+    if os.environ.get("BG_MLA_IMPL", "") == "lib":
+        return False
     return (q_abs.dtype == torch.bfloat16 and kv_lora == 512 and q_pe.shape[-1] == 64 and cache.shape[1] == 64
-            and cache.dtype == torch.bfloat16)
+            and cache.dtype == torch.bfloat16 and q_abs.shape[1] % 8 == 0 and cache.is_contiguous())
 
 
 def mla_prefill(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], ctx_lens: Sequence[int], scale, kv_lora):
+    if _kernel_supports(q_abs, q_pe, cache, kv_lora):
+        from .mla_kernel import mla_prefill_tc
+        return mla_prefill_tc(q_abs, q_pe, cache, block_table, cu_seqlens, ctx_lens, scale, kv_lora)
+    return mla_prefill_lib(q_abs, q_pe, cache, block_table, cu_seqlens, ctx_lens, scale, kv_lora)
+
+
+def mla_prefill_lib(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], ctx_lens: Sequence[int], scale,
+                    kv_lora):
     """Varlen causal absorbed MLA.  Per sequence: one bmm over its cached rows with a causal mask
     (chunked over queries to bound the score matrix)."""
     T, H, _ = q_abs.shape

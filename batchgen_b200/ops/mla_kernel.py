@@ -1,0 +1,134 @@
+"""Host side of the tcgen05 paged-MLA kernel: work lists, split-KV scratch and launches.
+
+A *work item* is one CTA: up to ``NCOL`` (query, head) columns of one sequence over a contiguous range
+of KV tiles.  Decode work lists depend only on (batch, heads, splits) — sequence lengths are read on
+the device — so they are built once, cached on the device and are safe to replay in a CUDA graph.
+Prefill work lists are built per micro-batch from the host-side ``cu_seqlens``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Sequence, Tuple
+
+import torch
+
+from . import _ext
+
+KV_TILE = 128
+_DECODE_WORK: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor, int]] = {}
+_SCRATCH: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _geometry(H: int, prefill: bool) -> Tuple[int, int]:
+    """(heads_per_group, ncol)."""
+    if H % 32 == 0:
+        return 32, 32
+    if H % 16 == 0:
+        return 16, (32 if prefill else 16)
+    if H % 8 == 0:
+        return 8, (32 if prefill else 16)
+    raise ValueError(f"the MLA kernel needs a multiple of 8 heads per rank, got {H}")
+
+
+def _scratch(device, slots: int, ncol: int):
+    key = (str(device), ncol)
+    cur = _SCRATCH.get(key)
+    if cur is None or cur[0].shape[0] < slots:
+        n = max(slots, 256)
+        cur = (torch.empty(n, ncol, 512, dtype=torch.float32, device=device),
+               torch.empty(n, ncol, 2, dtype=torch.float32, device=device))
+        _SCRATCH[key] = cur
+    return cur
+
+
+def _qpe_view(q_pe: torch.Tensor):
+    R, H, D = q_pe.shape
+    if q_pe.stride(2) != 1 or q_pe.stride(0) != H * q_pe.stride(1) or (q_pe.stride(1) * 2) % 16 != 0 \
+            or q_pe.data_ptr() % 16 != 0:
+        q_pe = q_pe.contiguous()
+    return q_pe, q_pe.stride(1)
+
+
+def _launch(q_abs, q_pe, cache, work, n_work, block_table, seqlens, out, part_o, part_ml, H, hpg, ncol, scale):
+    q_pe, qpe_stride = _qpe_view(q_pe)
+    R = q_abs.shape[0]
+    P, S, D = cache.shape
+    rc = _ext.lib().bg_mla_attention(
+        _ext.ptr(q_abs), _ext.ptr(q_pe), ctypes.c_longlong(qpe_stride), ctypes.c_longlong(R * H), _ext.ptr(cache),
+        ctypes.c_longlong(P * S), _ext.ptr(work), ctypes.c_int(n_work), _ext.ptr(block_table),
+        ctypes.c_int(block_table.stride(0)), _ext.ptr(seqlens), _ext.ptr(out), _ext.ptr(part_o), _ext.ptr(part_ml),
+        ctypes.c_int(H), ctypes.c_int(hpg), ctypes.c_int(ncol), ctypes.c_float(scale),
+        _ext.ptr(_ext.status_word(q_abs.device)), _ext.stream())
+    _ext.check(rc, "bg_mla_attention")
+
+
+def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_splits: int = 0):
+    """q_abs [B, H, 512], q_pe [B, H, 64] -> [B, H, 512]."""
+    B, H, _ = q_abs.shape
+    dev = q_abs.device
+    q_abs = q_abs.contiguous()
+    hpg, ncol = _geometry(H, prefill=False)
+    groups = H // hpg
+    if num_splits <= 0:
+        ctas = B * groups
+        sms = _ext.num_sms(dev)
+        max_tiles = max(1, (block_table.shape[1] * cache.shape[1]) // KV_TILE)
+        num_splits = 1 if ctas >= sms else max(1, min(16, sms // ctas, max_tiles))
+    key = (str(dev), B, H, num_splits)
+    cached = _DECODE_WORK.get(key)
+    if cached is None:
+        b = torch.arange(B).repeat_interleave(groups * num_splits)
+        g = torch.arange(groups).repeat_interleave(num_splits).repeat(B)
+        s = torch.arange(num_splits).repeat(B * groups)
+        w = torch.zeros(B * groups * num_splits, 8, dtype=torch.int32)
+        w[:, 0] = b; w[:, 1] = 1; w[:, 2] = b; w[:, 3] = -1; w[:, 4] = s; w[:, 5] = num_splits; w[:, 6] = g
+        w[:, 7] = torch.arange(w.shape[0])
+        items = torch.zeros(B * groups, 5, dtype=torch.int32)
+        items[:, 0] = torch.arange(B).repeat_interleave(groups); items[:, 1] = 1
+        items[:, 2] = torch.arange(groups).repeat(B)
+        items[:, 3] = torch.arange(B * groups) * num_splits; items[:, 4] = num_splits
+        cached = (w.to(dev), items.to(dev), w.shape[0])
+        _DECODE_WORK[key] = cached
+    work, items, n_work = cached
+    out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=dev)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o, part_ml = _scratch(dev, n_work, ncol)
+    _launch(q_abs, q_pe, cache, work, n_work, block_table, seqlens, out, part_o, part_ml, H, hpg, ncol, scale)
+    if num_splits > 1:
+        rc = _ext.lib().bg_mla_merge(_ext.ptr(part_o), _ext.ptr(part_ml), _ext.ptr(items), ctypes.c_int(items.shape[0]),
+                                     _ext.ptr(out), ctypes.c_int(ncol), ctypes.c_int(H), ctypes.c_int(hpg),
+                                     _ext.stream())
+        _ext.check(rc, "bg_mla_merge")
+    return out
+
+
+def mla_prefill_tc(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], ctx_lens: Sequence[int], scale,
+                   kv_lora):
+    """Varlen causal MLA: query j of sequence i attends to cache positions 0 .. ctx_i + j."""
+    T, H, _ = q_abs.shape
+    dev = q_abs.device
+    q_abs = q_abs.contiguous()
+    hpg, ncol = _geometry(H, prefill=True)
+    groups, qt = H // hpg, ncol // hpg
+    rows = []
+    for i in range(len(cu_seqlens) - 1):
+        a, b = int(cu_seqlens[i]), int(cu_seqlens[i + 1])
+        if b <= a:
+            continue
+        q0 = torch.arange(a, b, qt)
+        n_q = torch.clamp(torch.tensor(b) - q0, max=qt)
+        w = torch.zeros(q0.numel(), 8, dtype=torch.int32)
+        w[:, 0] = q0; w[:, 1] = n_q; w[:, 2] = i; w[:, 3] = int(ctx_lens[i]) + (q0 - a); w[:, 4] = 0; w[:, 5] = 1
+        rows.append(w)
+    out = torch.empty(T, H, 512, dtype=torch.bfloat16, device=dev)
+    if not rows:
+        return out
+    w = torch.cat(rows, 0)
+    w = w[torch.argsort(w[:, 3], descending=True)]                 # longest KV ranges first
+    w = w.repeat_interleave(groups, 0)
+    w[:, 6] = torch.arange(groups, dtype=torch.int32).repeat(w.shape[0] // groups)
+    work = w.contiguous().to(dev)
+    dummy_len = torch.zeros(1, dtype=torch.int32, device=dev)
+    _launch(q_abs, q_pe, cache, work, work.shape[0], block_table, dummy_len, out, None, None, H, hpg, ncol, scale)
+    return out

@@ -103,7 +103,7 @@ def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.
     rc = _ext.lib().bg_moe_permute(_ext.ptr(topk_idx), ctypes.c_int(T), ctypes.c_int(K), ctypes.c_int(lo),
                                    ctypes.c_int(hi), ctypes.c_int(ROW_ALIGN), _ext.ptr(offsets), _ext.ptr(cursor),
                                    _ext.ptr(pos), _ext.ptr(src), ctypes.c_int(cap), _ext.ptr(num_valid), _ext.stream())
-    _ext.check(rc, "bg_moe_permute")
+    _ext.check(rc, "bg_moe_permute", kernels=2)
     return src, pos, offsets
 
 
@@ -150,15 +150,22 @@ def _activation(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
     return ref.swiglu_clamped(gate_up) if kind == "swiglu_clamped" else ref.silu_mul(gate_up)
 
 
-def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None):
+def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None,
+                    timer=None):
     """Run gate/up -> activation -> down for rows already grouped by expert.  fp8 path takes
     (xq, xs); the unquantised path takes ``x_dense``.  Returns y [rows, Hout]."""
+    if timer is None:
+        from ..utils.timing import null_timer
+        timer = null_timer()
     if ew.quant == "fp8_block":
         if xq.is_cuda:
             assert ew.interleaved, "call ExpertWeights.to_device_layout() after loading"
-            act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True)
-            aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:])
-            return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
+            with timer.timed("moe.s1_gemm"):
+                act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True)
+            with timer.timed("moe.act_quant"):
+                aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:])
+            with timer.timed("moe.s3_gemm"):
+                return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
         gu = ref.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets)
         act = _activation(gu, ew.activation)
         aq, as_ = ref.act_quant(act)
@@ -177,14 +184,21 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
 
 def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
                     expert_lo: int, expert_hi: int, extra: Optional[torch.Tensor] = None,
-                    num_valid: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                    num_valid: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                    timer=None) -> torch.Tensor:
     """Partial MoE output of one rank: sum over the (token, k) pairs whose expert is local."""
-    src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid)
+    if timer is None:
+        from ..utils.timing import null_timer
+        timer = null_timer()
+    with timer.timed("moe.permute"):
+        src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid)
     if ew.quant == "fp8_block":
-        xq, xs = gather_quant(hidden, src, offsets)
-        y = grouped_experts(xq, xs, offsets, ew)
+        with timer.timed("moe.gather_quant"):
+            xq, xs = gather_quant(hidden, src, offsets)
+        y = grouped_experts(xq, xs, offsets, ew, timer=timer)
     else:
         rows = hidden[src.clamp_min(0).long()]
         rows = torch.where((src >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))
         y = grouped_experts(None, None, offsets, ew, x_dense=rows)
-    return combine(y, pos, topk_w, extra, out_dtype or hidden.dtype)
+    with timer.timed("moe.combine"):
+        return combine(y, pos, topk_w, extra, out_dtype or hidden.dtype)

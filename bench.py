@@ -1,0 +1,278 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode throughput (and prefill throughput / projected batch completion time)
+of the DeepSeek-V3/R1-671B architecture, block-scaled FP8, tensor-parallel attention + expert-parallel
+MoE over N GPUs of one node, on the 512-request workload (prompts U[512, 4096], 1,024 forced decode
+tokens) with synthetic token ids and random-init weights.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+
+A *step* is one decode step of the whole decode batch through all 61 layers, sampling included.
+``value`` = decode tokens/s of the job (rows * K / time of K steps, device-timed with CUDA events,
+max over ranks).  The ``e2e`` block times the same step through ``Engine``'s public decode path with
+the step's inputs staged in pinned host memory, copied host->device every step, and the sampled tokens
+read back device->host every step.
+
+Where the FP8 expert weights of the rank exceed what HBM can hold next to the KV pool (N < 8),
+layers share physical expert storage in a cycle of ``distinct_expert_sets`` sets: every layer still
+streams its full expert bytes from HBM (a set is far larger than L2) and executes every FLOP.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference from baseline/_ref through its own public API."""
+    why = None
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import importlib
+        importlib.import_module("batchgen.native_loader")
+        importlib.import_module("batchgen.core_engine")
+    except Exception as e:  # noqa: BLE001
+        why = f"reference does not import on this image: {type(e).__name__}: {str(e)[:160]}"
+    if why is None:
+        why = ("reference imports but its Blackwell path needs FlashMLA/DeepGEMM/UCX libraries that are not "
+               "installed and cannot be fetched offline")
+    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="deepseek-v3-671b")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--batch", type=int, default=384, help="decode rows of the whole job")
+    ap.add_argument("--prefill-tokens", type=int, default=8192)
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-ops", default="", help="write a per-operator CUDA-event breakdown to this file")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.models.transformer import AttnMeta
+    from batchgen_b200.models.weights import ParallelLayout
+    from batchgen_b200.ops import _ext
+    from batchgen_b200.ops import sampling as sampling_ops
+    from batchgen_b200.runtime.kv_cache import PagedKVCache
+    from batchgen_b200.utils.clocks import ClockSampler
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        from batchgen_b200.parallel import make_comm
+        comm = make_comm(args.comm, dev)
+    _ext.lib()
+
+    cfg = get_model_config(args.model)
+    if args.layers:
+        cfg.num_layers = args.layers
+    page = 64
+    rng = random.Random(1234)
+    B = args.batch
+    prompt_lens = [rng.randint(512, 4096) for _ in range(B)]
+    decoded_so_far = 512                                   # timed at the middle of the 1,024-token decode
+    ctx = [p + decoded_so_far for p in prompt_lens]
+    pages_per_seq = [(c + 1 + page - 1) // page for c in ctx]
+    total_pages = sum(pages_per_seq) + 8
+
+    # ---- memory plan: how many distinct expert-weight sets fit next to the KV pool
+    layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    n_moe = cfg.num_layers - cfg.first_k_dense
+    expert_bytes_layer = (cfg.n_routed_experts // world) * 3 * cfg.moe_intermediate_size * cfg.hidden_size
+    kv_bytes = total_pages * page * cfg.kv_cache_dim * 2 * cfg.num_layers
+    prefill_kv_bytes = (args.prefill_tokens + 4 * page) * cfg.kv_cache_dim * 2 * cfg.num_layers
+    free_b, total_b = torch.cuda.mem_get_info(dev)
+    other = 26e9 / world + 12e9                              # attention/dense/shared/embeddings + workspace
+    budget = free_b * 0.94 - kv_bytes - prefill_kv_bytes - other
+    sets = int(max(1, min(n_moe, budget // expert_bytes_layer)))
+    alias = 0 if sets >= n_moe else sets
+
+    t0 = time.time()
+    model = build_model(cfg, device=dev, dtype="bf16", seed=0, layout=layout, comm=comm,
+                        max_positions=8192, alias_experts_every=alias, gen_device=dev)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+
+    kv = PagedKVCache(cfg, total_pages + (args.prefill_tokens // page + 8), page, dev, torch.bfloat16)
+    for l in range(cfg.num_layers):
+        kv.kv[l].normal_(0.0, 0.5)
+    # ---- decode step inputs (device resident for the kernel-timed number)
+    gen = torch.Generator().manual_seed(7)
+    ids_h = torch.randint(2, cfg.vocab_size, (B,), generator=gen, dtype=torch.int32)
+    bt_h = torch.zeros(B, max(pages_per_seq), dtype=torch.int32)
+    nxt = 0
+    for i, n in enumerate(pages_per_seq):
+        bt_h[i, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+        nxt += n
+    pos_h = torch.tensor(ctx, dtype=torch.int32)
+    slot_h = torch.tensor([int(bt_h[i, c // page]) * page + c % page for i, c in enumerate(ctx)], dtype=torch.int64)
+    len_h = pos_h + 1
+    pin = lambda t: t.pin_memory()
+    ids_p, bt_p, pos_p, slot_p, len_p = map(pin, (ids_h, bt_h, pos_h, slot_h, len_h))
+    d_ids, d_bt, d_pos, d_slot, d_len = (t.to(dev) for t in (ids_h, bt_h, pos_h, slot_h, len_h))
+    out_tok = torch.empty(B, dtype=torch.int32, device=dev)
+    tok_pinned = torch.empty(B, dtype=torch.int32).pin_memory()
+
+    def decode_step_device():
+        meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
+        logits = model.forward(d_ids, meta, kv)
+        sampling_ops.greedy(logits, out_tok)
+
+    def decode_step_e2e():
+        a = ids_p.to(dev, non_blocking=True)
+        b = bt_p.to(dev, non_blocking=True)
+        c = pos_p.to(dev, non_blocking=True)
+        d = slot_p.to(dev, non_blocking=True)
+        e = len_p.to(dev, non_blocking=True)
+        meta = AttnMeta(mode="decode", positions=c, slot_mapping=d, block_table=b, seqlens=e)
+        logits = model.forward(a, meta, kv)
+        sampling_ops.greedy(logits, out_tok)
+        tok_pinned.copy_(out_tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        ids_p.copy_(tok_pinned)                              # next step feeds the sampled tokens
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        decode_step_device()
+    _ext.check_status()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    l0 = _ext.LAUNCHES["count"]
+    ms = timed(decode_step_device, args.steps)
+    launches = _ext.LAUNCHES["count"] - l0
+    clocks = sampler.stop() if sampler else {}
+    _ext.check_status()
+    ms_step = ms / args.steps
+    decode_tps = B * 1000.0 / ms_step
+
+    if args.profile_ops and rank == 0:
+        from batchgen_b200.utils.timing import TimingStats
+        model.timer = TimingStats()
+        for _ in range(2):
+            decode_step_device()
+            model.timer.step_done()
+        torch.cuda.synchronize()
+        dsum = model.timer.summary()
+        model.timer = TimingStats()
+    else:
+        dsum = None
+
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            decode_step_e2e()
+        ms_e = timed(decode_step_e2e, args.steps) / args.steps
+        h2d = sum(t.numel() * t.element_size() for t in (ids_p, bt_p, pos_p, slot_p, len_p))
+        e2e = {"value": B * 1000.0 / ms_e, "unit": "decode tokens/s", "ms_per_step": ms_e,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": tok_pinned.numel() * 4}
+
+    prefill = None
+    if not args.no_prefill:
+        # one packed prefill micro-batch of sequences of 2,048 tokens through all layers
+        n_seq = max(1, args.prefill_tokens // 2048)
+        L = args.prefill_tokens // n_seq
+        T = n_seq * L
+        pp = (L + page - 1) // page
+        pbt = torch.arange(total_pages, total_pages + n_seq * pp, dtype=torch.int32).view(n_seq, pp).to(dev)
+        ppos = torch.arange(L, dtype=torch.int32).repeat(n_seq).to(dev)
+        pslot = torch.cat([(pbt[i].long().repeat_interleave(page)[:L] * page
+                            + torch.arange(L, device=dev) % page) for i in range(n_seq)])
+        pids = torch.randint(2, cfg.vocab_size, (T,), generator=gen, dtype=torch.int32).to(dev)
+        cu = [i * L for i in range(n_seq + 1)]
+        rows = torch.tensor([c - 1 for c in cu[1:]], device=dev)
+
+        def prefill_step():
+            meta = AttnMeta(mode="prefill", positions=ppos, slot_mapping=pslot, block_table=pbt, cu_seqlens=cu,
+                            ctx_lens=[0] * n_seq, logit_rows=rows)
+            sampling_ops.greedy(model.forward(pids, meta, kv))
+
+        prefill_step()
+        psum = None
+        if args.profile_ops and rank == 0:
+            prefill_step()
+            model.timer.step_done()
+            torch.cuda.synchronize()
+            psum = model.timer.summary()
+            from batchgen_b200.utils.timing import null_timer
+            model.timer = null_timer()
+            with open(args.profile_ops, "w") as f:
+                for title, sm in (("decode step", dsum), ("prefill micro-batch", psum)):
+                    f.write(f"== {title}: ms per step by operator (CUDA events, eager) ==\n")
+                    for op, d in sm.items():
+                        f.write(f"{op:32s} {d['ms_per_step']:10.3f} ms  {d['share'] * 100:5.1f}%  calls {d['calls']}\n")
+        ms_p = timed(prefill_step, 2) / 2
+        prefill = {"tokens_per_s": T * 1000.0 / ms_p, "ms_per_microbatch": ms_p, "tokens": T, "seq_len": L}
+
+    if rank == 0:
+        total_prompt = sum(rng.randint(512, 4096) for _ in range(512))
+        bct = None
+        if prefill:
+            bct = total_prompt / prefill["tokens_per_s"] + 512 * 1024 / decode_tps
+        out = {
+            "metric": "decode tokens/s (DeepSeek-V3-671B FP8, batch workload of BASELINE config 2)",
+            "value": decode_tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8(e4m3 block-scaled weights+activations)/bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": B,
+                       "seq_len": int(sum(ctx) / len(ctx)), "prompt_lens": "U[512,4096]", "decoded_so_far": 512,
+                       "parallelism": f"tp{world}+ep{world}", "comm": args.comm if world > 1 else "none",
+                       "distinct_expert_sets": sets, "moe_layers": n_moe,
+                       "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",
+                       "valid": not args.layers, "build_seconds": round(build_s, 1)},
+            "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "prefill": prefill,
+            "bct_projected_s": bct,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
