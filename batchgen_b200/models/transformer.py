@@ -107,6 +107,16 @@ class Transformer:
         tm = self.timer
         with tm.timed("attn.qkv_a_gemm", l):
             qkv_a = linear(x, lw.wqkv_a, xq, xs)
+        o = self._mla_from_qkv_a(l, lw, qkv_a, x, meta, cache)
+        with tm.timed("attn.o_proj", l):
+            return linear(o, lw.wo)
+
+    def _mla_from_qkv_a(self, l: int, lw: LayerWeights, qkv_a, x, meta: AttnMeta, cache) -> torch.Tensor:
+        """Everything between the q_a/kv_a projection and o_proj: KV write, q path, attention over the
+        paged latent cache, out-absorb.  Returns [T, local_heads * v_head_dim]."""
+        cfg = self.cfg
+        T = qkv_a.shape[0]
+        tm = self.timer
         q_a, kv_a = qkv_a[:, : cfg.q_lora_rank], qkv_a[:, cfg.q_lora_rank:]
         with tm.timed("attn.kv_write_qnorm_qb_rope", l):
             self._mla_q(lw, q_a, kv_a, meta, cache, l)
@@ -123,9 +133,7 @@ class Transformer:
             o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
         # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
         with tm.timed("attn.out_absorb", l):
-            o = torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
-        with tm.timed("attn.o_proj", l):
-            return linear(o, lw.wo)
+            return torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
 
     def _mla_q(self, lw, q_a, kv_a, meta, cache, l):
         cfg = self.cfg
@@ -315,3 +323,59 @@ class Transformer:
         if tp:
             logits = self.comm.tp_gather_vocab(logits)
         return logits
+
+    # ------------------------------------------------------------------ sequence-parallel forward
+    def forward_sp(self, ids: torch.Tensor, meta: AttnMeta, cache) -> torch.Tensor:
+        """Tensor-parallel attention + expert-parallel MoE with a row-sharded residual stream and the
+        collectives fused into the kernels (``parallel.fused.FusedComm``).  ``ids`` holds all T tokens of
+        the step (T divisible by the world size); returns fp32 logits of this rank's own rows
+        [T / world, vocab] (rows rank*Tl .. (rank+1)*Tl)."""
+        cfg, comm, tm = self.cfg, self.comm, self.timer
+        W, r = comm.world, comm.rank
+        T = ids.shape[0]
+        assert T % W == 0, "pad the step to a multiple of the world size"
+        Tl = T // W
+        eps = cfg.rms_eps
+        src = self.w.embed[ids[r * Tl:(r + 1) * Tl].long()]      # local rows of the residual stream
+        residual = torch.empty_like(src)
+        first = True
+        for l, lw in enumerate(self.w.layers):
+            # input norm of own rows (+ previous sublayer's output), quantised rows pushed to every rank
+            with tm.timed("sp.norm_push", l):
+                comm.sp_norm_push(src, residual, lw.input_norm, eps, from_rs=src is None, has_residual=not first,
+                                  push=True, want_y=False, want_q=False)
+            first = False
+            with tm.timed("attn.qkv_a_gemm", l):
+                qkv_a = comm.ag_gemm(lw.wqkv_a, T)
+            o = self._mla_from_qkv_a(l, lw, qkv_a, None, meta, cache)
+            with tm.timed("attn.o_proj_rs", l):
+                oq, os_ = fused.act_quant(o)
+                comm.gemm_rs(oq, os_, lw.wo, T)
+            if cfg.is_moe_layer(l):
+                with tm.timed("sp.norm_push", l):
+                    x, xq, xs = comm.sp_norm_push(None, residual, lw.post_norm, eps, from_rs=True, has_residual=True,
+                                                  push=False)
+                with tm.timed("moe.router", l):
+                    logits = moe_ops.router_logits(x, lw.router_w)
+                    idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group,
+                                                 cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor,
+                                                 cfg.scoring_func)
+                shared = None
+                if lw.w13 is not None:
+                    with tm.timed("moe.shared_expert", l):
+                        shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+                with tm.timed("moe.routed_experts", l):
+                    src = comm.moe_sp(x, idx, w, lw.experts, extra=shared)
+            else:
+                with tm.timed("sp.norm_push", l):
+                    comm.sp_norm_push(None, residual, lw.post_norm, eps, from_rs=True, has_residual=True, push=True,
+                                      want_y=False, want_q=False)
+                with tm.timed("dense_mlp", l):
+                    act = comm.ag_gemm(lw.w13, T, silu_mul=True)
+                    aq, as_ = fused.act_quant(act)
+                    comm.gemm_rs(aq, as_, lw.w2, T)
+                src = None                                       # next norm sums the reduce-scatter partials
+        x, _, _ = comm.sp_norm_push(src, residual, self.w.final_norm, eps, from_rs=src is None, has_residual=True,
+                                    push=False, want_q=False)
+        with tm.timed("lm_head"):
+            return (x @ self.w.lm_head.t()).float()

@@ -28,6 +28,7 @@ class ParallelLayout:
     tp_size: int = 1     # attention heads / dense-MLP / shared-expert / vocab sharding
     ep_rank: int = 0
     ep_size: int = 1     # routed experts sharding (contiguous blocks)
+    sequence_parallel: bool = False   # row-sharded residual stream: shared experts and lm_head replicated
 
     def expert_range(self, n_experts: int) -> Tuple[int, int]:
         per = n_experts // self.ep_size
@@ -164,8 +165,12 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
     mw.embed = src.get("model.embed_tokens.weight", (cfg.vocab_size, H)).to(dtype)
     mw.final_norm = src.get("model.norm.weight", (H,), "norm").to(dtype)
     head = mw.embed if cfg.tie_word_embeddings else src.get("lm_head.weight", (cfg.vocab_size, H)).to(dtype)
-    v0, v1 = layout.tp_rank * cfg.vocab_size // layout.tp_size, (layout.tp_rank + 1) * cfg.vocab_size // layout.tp_size
-    mw.lm_head = head[v0:v1].contiguous()
+    if layout.sequence_parallel:
+        mw.lm_head = head
+    else:
+        v0 = layout.tp_rank * cfg.vocab_size // layout.tp_size
+        v1 = (layout.tp_rank + 1) * cfg.vocab_size // layout.tp_size
+        mw.lm_head = head[v0:v1].contiguous()
     expert_sets: Dict[int, ExpertWeights] = {}
     for l in range(cfg.num_layers):
         p = f"model.layers.{l}"
@@ -210,8 +215,10 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
             if cfg.attention_sinks:
                 lw.sinks = src.get(f"{p}.self_attn.sinks", (Hq,), "bias")[h0:h1].contiguous()
 
-        def mlp_pair(prefix: str, inter: int, hid: int):
-            i0, i1 = layout.tp_rank * inter // layout.tp_size, (layout.tp_rank + 1) * inter // layout.tp_size
+        def mlp_pair(prefix: str, inter: int, hid: int, shard: bool = True):
+            i0, i1 = 0, inter
+            if shard:
+                i0, i1 = layout.tp_rank * inter // layout.tp_size, (layout.tp_rank + 1) * inter // layout.tp_size
             g = src.get(f"{prefix}.gate_proj.weight", (inter, hid))[i0:i1]
             u = src.get(f"{prefix}.up_proj.weight", (inter, hid))[i0:i1]
             d = src.get(f"{prefix}.down_proj.weight", (hid, inter))[:, i0:i1]
@@ -250,7 +257,8 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                     quant=equant, activation=cfg.activation).to_device_layout()
                 expert_sets[key] = lw.experts
             if cfg.n_shared_experts:
-                lw.w13, lw.w2 = mlp_pair(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+                lw.w13, lw.w2 = mlp_pair(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H,
+                                         shard=not layout.sequence_parallel)
         else:
             lw.w13, lw.w2 = mlp_pair(f"{p}.mlp", cfg.intermediate_size, H)
         mw.layers.append(lw)

@@ -180,6 +180,26 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---------------------------------------------------------------- cross-GPU flags (peer memory over NVLink)
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+constexpr uint32_t kFlagSpinLimit = 1u << 22;  // x ~100 ns sleep: about half a second, then give up
+// Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t value) {
+  for (uint32_t i = 0; i < kFlagSpinLimit; ++i) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - value) >= 0) return true;
+    __nanosleep(100);
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -48,6 +48,24 @@ struct GemmParams {
   int N;                // rows of B per group (GEMM N)
   int K;                // elements
   int* status;
+  // ---- hooks that fuse the GEMM with a collective over peer memory (all optional) -------------
+  // all-gather -> GEMM: rows [i*a_ready_rows, (i+1)*a_ready_rows) of A were pushed into this GPU's
+  // memory by rank i; they are valid once a_ready[i] >= epoch.  The TMA producer waits per tile.
+  const uint32_t* a_ready;
+  int a_ready_rows;
+  uint32_t epoch;
+  int m_rotate;         // dense: row block processed first (tiles rotate, e.g. local rows first / last)
+  // GEMM -> reduce-scatter / combine: the epilogue stores each output row into the memory of the
+  // rank that owns it.  row_map[row] = (rank, dest row) (rank < 0: drop the row); without a map row m
+  // goes to rank m / rs_rows_per_rank, dest row my_rank * rs_rows_per_rank + m % rs_rows_per_rank.
+  void* peer_out[8];
+  const int2* row_map;
+  int rs_rows_per_rank;
+  int my_rank, world;
+  // completion: when the last CTA finishes, peer_flags[r][done_flag_index + my_rank] = epoch for all r
+  uint32_t* peer_flags[8];
+  int done_flag_index;
+  unsigned int* done_counter;
 };
 
 struct SharedStorage {
@@ -71,17 +89,17 @@ struct Tile {
 // Grouped: groups in order, inside a group nt-major with mt fastest.
 struct TileWalker {
   const int* offs;
-  int groups, n_tiles, M;
+  int groups, n_tiles, M, m_rotate;
   int g, before;  // grouped walk state: current group and number of tiles in earlier groups
-  __device__ TileWalker(const int* offs_, int groups_, int n_tiles_, int M_)
-      : offs(offs_), groups(groups_), n_tiles(n_tiles_), M(M_), g(0), before(0) {}
+  __device__ TileWalker(const int* offs_, int groups_, int n_tiles_, int M_, int m_rotate_ = 0)
+      : offs(offs_), groups(groups_), n_tiles(n_tiles_), M(M_), m_rotate(m_rotate_), g(0), before(0) {}
   __device__ bool get(int tile, Tile& t) {
     if (offs == nullptr) {
       const int m_tiles = (M + BM - 1) / BM;
       if (tile >= m_tiles * n_tiles) return false;
       t.g = 0;
       t.nt = tile / m_tiles;
-      t.m0 = (tile % m_tiles) * BM;
+      t.m0 = (((tile % m_tiles) + m_rotate) % m_tiles) * BM;
       t.m_end = M;
       return true;
     }
@@ -153,12 +171,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      TileWalker walk(offs, p.groups, n_tiles, p.M);
+      TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
       Tile t;
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
         const int brow = t.g * p.N + t.nt * BN;
+        if (p.a_ready != nullptr) {
+          // rows of this tile were pushed by other ranks: wait (bounded) for their arrival flags
+          const int last = min(t.m0 + BM, t.m_end) - 1;
+          const int i_lo = p.a_ready_rows > 0 ? t.m0 / p.a_ready_rows : 0;            // rows == 0: wait for every rank
+          const int i_hi = p.a_ready_rows > 0 ? last / p.a_ready_rows : p.world - 1;
+          for (int i = i_lo; ok && i <= i_hi; ++i) {
+            if (!wait_flag_ge(p.a_ready + i, p.epoch)) {
+              if (*abort_flag == 0) *abort_flag = kTimeoutPeer;
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_global();
+        }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -190,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc(BM, BN, KIND == KIND_FP8 ? 0 : 1, KIND == KIND_FP8 ? 0 : 1);
-      TileWalker walk(offs, p.groups, n_tiles, p.M);
+      TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
       Tile t;
       uint32_t it = 0;   // smem stage counter
       uint32_t acc = 0;  // accumulator hand-off counter
@@ -230,7 +262,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int quad = warp & 3;        // TMEM lane quadrant this warp may access
     const int half = ew >> 2;         // which 64 columns of the tile
     const int row_in_tile = quad * 32 + lane;
-    TileWalker walk(offs, p.groups, n_tiles, p.M);
+    TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
     Tile t;
     uint32_t acc = 0;
     bool ok = true;
@@ -289,12 +321,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
       if (!ok) break;
-      if (row_ok) {
+      __nv_bfloat16* out_base = p.D;
+      size_t out_row = (size_t)row;
+      bool store_ok = row_ok;
+      if (p.peer_out[0] != nullptr && row_ok) {
+        int drank, drow;
+        if (p.row_map != nullptr) {
+          const int2 rm = p.row_map[row];
+          drank = rm.x;
+          drow = rm.y;
+        } else {
+          drank = row / p.rs_rows_per_rank;
+          drow = p.my_rank * p.rs_rows_per_rank + row % p.rs_rows_per_rank;
+        }
+        store_ok = drank >= 0;
+        if (store_ok) {
+          out_base = reinterpret_cast<__nv_bfloat16*>(p.peer_out[drank]);
+          out_row = (size_t)drow;
+        }
+      }
+      if (store_ok) {
         if (EPI == EPI_SILU_MUL) {
           // columns [0,32) of this half = gate, [32,64) = up of output columns nt*64 + half*32 + j
           const int col0 = t.nt * 64 + half * 32;
           const int n_out = p.N / 2;
-          __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+          __nv_bfloat16* dst = out_base + out_row * p.ldd + col0;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j + 8 <= n_out) {
@@ -313,7 +364,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         } else {
           const int col0 = t.nt * BN + half * 64;
-          __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+          __nv_bfloat16* dst = out_base + out_row * p.ldd + col0;
 #pragma unroll
           for (int j = 0; j < 64; j += 8) {
             if (col0 + j + 8 <= p.N) {
@@ -336,6 +387,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
+  if (threadIdx.x == 0 && p.done_counter != nullptr) {
+    // every store of this CTA (ordered before the barrier above) becomes visible system-wide, then
+    // the last CTA to get here tells every rank that this rank's outputs are complete
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(p.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_counter = 0u;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.done_flag_index + p.my_rank, p.epoch);
+    }
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -401,6 +463,29 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
 
 extern "C" {
 
+// Collective hooks of the next bg_gemm call on this thread (consumed by that call, then cleared).
+struct BgGemmHooks {
+  const uint32_t* a_ready; int a_ready_rows; uint32_t epoch; int m_rotate;
+  void* peer_out[8]; const int2* row_map; int rs_rows_per_rank; int my_rank; int world;
+  uint32_t* peer_flags[8]; int done_flag_index; unsigned int* done_counter;
+};
+static thread_local BgGemmHooks g_hooks;
+static thread_local bool g_hooks_set = false;
+
+void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch, int m_rotate, void* const* peer_out,
+                       const void* row_map, int rs_rows_per_rank, int my_rank, int world, uint32_t* const* peer_flags,
+                       int done_flag_index, unsigned int* done_counter) {
+  g_hooks.a_ready = a_ready; g_hooks.a_ready_rows = a_ready_rows; g_hooks.epoch = epoch; g_hooks.m_rotate = m_rotate;
+  for (int i = 0; i < 8; ++i) {
+    g_hooks.peer_out[i] = (peer_out != nullptr && i < world) ? peer_out[i] : nullptr;
+    g_hooks.peer_flags[i] = (peer_flags != nullptr && i < world) ? peer_flags[i] : nullptr;
+  }
+  g_hooks.row_map = reinterpret_cast<const int2*>(row_map); g_hooks.rs_rows_per_rank = rs_rows_per_rank;
+  g_hooks.my_rank = my_rank; g_hooks.world = world; g_hooks.done_flag_index = done_flag_index;
+  g_hooks.done_counter = done_counter;
+  g_hooks_set = true;
+}
+
 // Dense or grouped GEMM.  kind: 0 = e4m3 block scaled, 1 = bf16.  epi: 0 = store, 1 = silu-mul
 // (weight rows interleaved in 32-row gate/up blocks; output has N/2 columns).
 // offsets == nullptr -> dense [M, K] x [N, K]^T.  Otherwise A holds `groups` row segments
@@ -417,6 +502,18 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
   GemmParams p;
   p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
   p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
+  p.a_ready = nullptr; p.a_ready_rows = 1; p.epoch = 0; p.m_rotate = 0; p.row_map = nullptr; p.rs_rows_per_rank = 1;
+  p.my_rank = 0; p.world = 1; p.done_flag_index = 0; p.done_counter = nullptr;
+  for (int i = 0; i < 8; ++i) { p.peer_out[i] = nullptr; p.peer_flags[i] = nullptr; }
+  if (g_hooks_set) {
+    p.a_ready = g_hooks.a_ready; p.a_ready_rows = g_hooks.a_ready_rows;
+    p.epoch = g_hooks.epoch; p.m_rotate = g_hooks.m_rotate; p.row_map = g_hooks.row_map;
+    p.rs_rows_per_rank = g_hooks.rs_rows_per_rank > 0 ? g_hooks.rs_rows_per_rank : 1;
+    p.my_rank = g_hooks.my_rank; p.world = g_hooks.world; p.done_flag_index = g_hooks.done_flag_index;
+    p.done_counter = g_hooks.done_counter;
+    for (int i = 0; i < 8; ++i) { p.peer_out[i] = g_hooks.peer_out[i]; p.peer_flags[i] = g_hooks.peer_flags[i]; }
+    g_hooks_set = false;
+  }
   const int b_rows = groups * N;
   if (kind == KIND_FP8 && epi == EPI_STORE) return launch_gemm<KIND_FP8, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
   if (kind == KIND_FP8 && epi == EPI_SILU_MUL) return launch_gemm<KIND_FP8, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);

@@ -1,0 +1,399 @@
+// Kernels that move data between GPUs themselves (plain peer loads/stores over NVLink into a
+// symmetric heap) fused with the compute around the collective.  No NCCL call, no TMA multicast.
+//
+//   sp_norm_quant_push     owner side of GEMM->reduce-scatter: sum the partial rows every rank pushed,
+//                          add the residual, RMSNorm, quantise to e4m3 and push the quantised rows into
+//                          every rank's all-gather buffer (the all-gather of the *next* GEMM's input)
+//   ep_count_push          per-expert counts of this rank's routed tokens, pushed to every rank
+//   ep_layout              segment layout of every rank's receive buffer from the gathered counts
+//   ep_dispatch_send       quantise each local token once, store it straight into the receive buffer of
+//                          each expert-owner rank at its expert-grouped row (+ return address)
+//   wait_flags             stream-ordered bounded wait on arrival flags
+//   barrier_all            flag barrier over all ranks (setup / teardown only)
+//
+// Synchronisation is by monotonically increasing epochs in flag words of the symmetric heap:
+// a producer finishes its stores, issues a system-scope fence and release-stores the epoch into the
+// consumer's flag; consumers acquire-load until flag >= epoch, for a bounded number of polls, after
+// which they raise the status word and carry on (the host sees the error; the GPU never hangs).
+//
+// Replaces (by behaviour): NCCL all_gather / reduce_scatter / all_reduce around the MoE and
+// tensor-parallel GEMMs (batchgen/models/glm/glm5/model.py:2428-2508,
+// batchgen/models/deepseek/deepseekv3/modeling_deepseek_v3.py:3137,3173,
+// batchgen/moe/fused_moe_mxfp4_resident.py:1020-1095) and the DeepEP low-latency dispatch/combine
+// wrapper batchgen/moe/deepep_ll.py:240-400.
+#include "../../ops/csrc/common.cuh"
+
+namespace bg {
+namespace comm {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxExperts = 1024;
+
+struct Peers {
+  void* p[kMaxWorld];
+};
+
+__device__ __forceinline__ void signal_all(const Peers& flags, int index, int world, uint32_t epoch) {
+  for (int r = 0; r < world; ++r) st_release_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + index, epoch);
+}
+
+// Last-CTA-out signalling: every CTA fences its stores; the last one raises the flags.
+__device__ __forceinline__ void cta_done_signal(unsigned int* counter, const Peers& flags, int index, int world,
+                                                uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *counter = 0u;
+      __threadfence_system();
+      signal_all(flags, index, world, epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One block per owned row.  partials: [n_src, rows, H] bf16 in this rank's memory (n_src = world when
+// fed by GEMM->reduce-scatter, 1 when the input is a local tensor).  residual [rows, H] in/out.
+// Outputs: y (bf16, local, optional), local e4m3 + scales (optional), and the pushed copy into every
+// rank's gather buffer at row (my_rank * rows + r): ag_q [T, H] e4m3, ag_s [KB, ag_s_stride] fp32.
+__global__ void __launch_bounds__(256)
+sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src, const uint32_t* __restrict__ src_ready,
+                          uint32_t wait_epoch, __nv_bfloat16* __restrict__ residual,
+                          const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                          uint8_t* __restrict__ loc_q, float* __restrict__ loc_s, int loc_s_stride, Peers ag_q,
+                          Peers ag_s, int ag_s_stride, int push, int rows, int H, float eps, int my_rank, int world,
+                          Peers flags, int ready_index, uint32_t epoch, unsigned int* counter, int* status,
+                          int has_residual) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  __shared__ int wait_ok;
+  const int r = blockIdx.x;
+  if (src_ready != nullptr) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int s = 0; s < n_src; ++s)
+        if (!wait_flag_ge(src_ready + s, wait_epoch)) ok = 0;
+      if (!ok && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
+      wait_ok = ok;
+    }
+    __syncthreads();
+  }
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    for (int s = 0; s < n_src; ++s) {   // fixed source order: bit-reproducible sum
+      uint4 raw = *reinterpret_cast<const uint4*>(partials + ((size_t)s * rows + r) * H + v * 8);
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 a = __bfloat1622float2(xp[i]);
+        f[2 * i] += a.x;
+        f[2 * i + 1] += a.y;
+      }
+    }
+    if (has_residual) {
+      uint4 rraw = *reinterpret_cast<const uint4*>(residual + (size_t)r * H + v * 8);
+      const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rraw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 a = __bfloat1622float2(rp[i]);
+        f[2 * i] += a.x;
+        f[2 * i + 1] += a.y;
+      }
+    }
+    __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      float2 b = __bfloat1622float2(o[i]);
+      f[2 * i] = b.x;
+      f[2 * i + 1] = b.y;
+    }
+    *reinterpret_cast<uint4*>(residual + (size_t)r * H + v * 8) = *reinterpret_cast<const uint4*>(o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      rowbuf[v * 8 + i] = f[i];
+      ss += f[i] * f[i];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  const int grow = my_rank * rows + r;
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    uint4 wraw = *reinterpret_cast<const uint4*>(w + v * 8);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+    __align__(16) __nv_bfloat162 o[4];
+    float yv[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 ww = __bfloat1622float2(wp[i]);
+      o[i] = __floats2bfloat162_rn(rowbuf[v * 8 + 2 * i] * rstd * ww.x, rowbuf[v * 8 + 2 * i + 1] * rstd * ww.y);
+      float2 b = __bfloat1622float2(o[i]);
+      yv[2 * i] = b.x;
+      yv[2 * i + 1] = b.y;
+    }
+    if (y != nullptr) *reinterpret_cast<uint4*>(y + (size_t)r * H + v * 8) = *reinterpret_cast<const uint4*>(o);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(yv[i]));
+#pragma unroll
+    for (int o2 = 8; o2 > 0; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
+    const float sc = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+    const float inv = 1.0f / sc;
+    __align__(8) uint16_t q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = to_e4m3x2(yv[2 * i] * inv, yv[2 * i + 1] * inv);
+    const uint2 qv = *reinterpret_cast<const uint2*>(q);
+    if (loc_q != nullptr) {
+      *reinterpret_cast<uint2*>(loc_q + (size_t)r * H + v * 8) = qv;
+      if ((threadIdx.x & 15) == 0) loc_s[(size_t)(v / 16) * loc_s_stride + r] = sc;
+    }
+    if (push) {
+      for (int d = 0; d < world; ++d) {   // own copy first, then peers in ring order
+        const int dst = (my_rank + d) % world;
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(ag_q.p[dst]) + (size_t)grow * H + v * 8) = qv;
+        if ((threadIdx.x & 15) == 0)
+          reinterpret_cast<float*>(ag_s.p[dst])[(size_t)(v / 16) * ag_s_stride + grow] = sc;
+      }
+    }
+  }
+  if (push) cta_done_signal(counter, flags, ready_index + my_rank, world, epoch);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel dispatch, step 1: counts of this rank's (token, k) pairs per global expert, pushed to
+// every rank's count matrix cnt[src = my_rank][E]; also clears this rank's return-address table.
+__global__ void __launch_bounds__(1024)
+ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers cnt, int my_rank, int world, Peers flags,
+                     int ready_index, uint32_t epoch, int2* __restrict__ row_info, int row_cap) {
+  __shared__ int c[kMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) c[e] = 0;
+  for (int i = threadIdx.x; i < row_cap; i += blockDim.x) row_info[i] = make_int2(-1, -1);
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&c[e], 1);
+  }
+  __syncthreads();
+  for (int d = 0; d < world; ++d) {
+    int* dst = reinterpret_cast<int*>(cnt.p[(my_rank + d) % world]) + (size_t)my_rank * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = c[e];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    signal_all(flags, ready_index + my_rank, world, epoch);
+  }
+}
+
+// Step 2 (one block): wait for every rank's counts, then derive
+//   row_base[e]   first row, in the receive buffer of e's owner, for this rank's tokens of expert e
+//   offsets[El+1] segment offsets (128-aligned) of this rank's own receive buffer
+//   cursor[e] = 0
+__global__ void __launch_bounds__(1024)
+ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, uint32_t epoch, int E, int world,
+                 int my_rank, int align, int* __restrict__ row_base, int* __restrict__ offsets,
+                 int* __restrict__ cursor, int* __restrict__ total_rows, int* status) {
+  __shared__ int tot[kMaxExperts];
+  __shared__ int mine[kMaxExperts];
+  __shared__ int seg[kMaxExperts];
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < world; ++s)
+      if (!wait_flag_ge(cnt_ready + s, epoch)) ok = 0;
+    if (!ok && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
+    ok_s = ok;
+  }
+  __syncthreads();
+  const int El = E / world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int v = cnt[(size_t)s * E + e];
+      if (s < my_rank) before += v;
+      t += v;
+    }
+    tot[e] = t;
+    mine[e] = before;
+    cursor[e] = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {   // one thread per destination rank: serial scan over its El experts
+    const int d = threadIdx.x;
+    int run = 0;
+    for (int j = 0; j < El; ++j) {
+      const int e = d * El + j;
+      seg[e] = run;
+      if (d == my_rank) offsets[j] = run;
+      run += ((tot[e] + align - 1) / align) * align;
+    }
+    if (d == my_rank) {
+      offsets[El] = run;
+      *total_rows = run;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) row_base[e] = seg[e] + mine[e];
+}
+
+// Step 3: one block per local token.  Quantise the token once (1x128 e4m3), then store it into the
+// receive buffer of every routed expert's owner at its expert-grouped row, with its scales and the
+// return address (owner rank, token * K + k) for the combine.
+__global__ void __launch_bounds__(256)
+ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const int* __restrict__ topk_idx, int K,
+                        int E, int H, const int* __restrict__ row_base, int* __restrict__ cursor, Peers recv_q,
+                        Peers recv_s, int recv_s_stride, Peers recv_info, int recv_cap, int* __restrict__ sent_row,
+                        int my_rank, int world, Peers flags, int ready_index, uint32_t epoch, unsigned int* counter,
+                        int* status) {
+  __shared__ int dest_rank[16], dest_row[16];
+  const int t = blockIdx.x;
+  const int El = E / world;
+  if (threadIdx.x < K) {
+    const int e = topk_idx[(size_t)t * K + threadIdx.x];
+    int dr = -1, row = -1;
+    if (e >= 0 && e < E) {
+      dr = e / El;
+      row = row_base[e] + atomicAdd(&cursor[e], 1);
+      if (row >= recv_cap) {
+        if (status != nullptr) atomicMax(status, (int)kOverflow);
+        dr = -1;
+      }
+    }
+    dest_rank[threadIdx.x] = dr;
+    dest_row[threadIdx.x] = row;
+    sent_row[(size_t)t * K + threadIdx.x] = row;
+    if (dr >= 0) reinterpret_cast<int2*>(recv_info.p[dr])[row] = make_int2(my_rank, t * K + threadIdx.x);
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    uint4 raw = *reinterpret_cast<const uint4*>(hidden + (size_t)t * ldh + v * 8);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 a = __bfloat1622float2(xp[i]);
+      f[2 * i] = a.x;
+      f[2 * i + 1] = a.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = fmaxf(amax, 1e-4f) * (1.0f / 448.0f);
+    const float inv = 1.0f / sc;
+    __align__(8) uint16_t q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = to_e4m3x2(f[2 * i] * inv, f[2 * i + 1] * inv);
+    const uint2 qv = *reinterpret_cast<const uint2*>(q);
+    for (int k = 0; k < K; ++k) {
+      const int dr = dest_rank[k];
+      if (dr < 0) continue;
+      const int row = dest_row[k];
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(recv_q.p[dr]) + (size_t)row * H + v * 8) = qv;
+      if ((threadIdx.x & 15) == 0)
+        reinterpret_cast<float*>(recv_s.p[dr])[(size_t)(v / 16) * recv_s_stride + row] = sc;
+    }
+  }
+  cta_done_signal(counter, flags, ready_index + my_rank, world, epoch);
+}
+
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status) {
+  if (threadIdx.x < n) {
+    if (!wait_flag_ge(flags + threadIdx.x, epoch) && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
+  }
+}
+
+__global__ void signal_kernel(Peers flags, int index, int world, uint32_t epoch) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    signal_all(flags, index, world, epoch);
+  }
+}
+
+}  // namespace comm
+}  // namespace bg
+
+extern "C" {
+
+using bg::comm::Peers;
+
+static Peers to_peers(void* const* arr, int world) {
+  Peers p;
+  for (int i = 0; i < bg::comm::kMaxWorld; ++i) p.p[i] = (arr != nullptr && i < world) ? arr[i] : nullptr;
+  return p;
+}
+
+int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_ready, uint32_t wait_epoch,
+                          void* residual, int has_residual, const void* w, void* y, void* loc_q, float* loc_s,
+                          int loc_s_stride, void* const* ag_q, void* const* ag_s, int ag_s_stride, int push, int rows,
+                          int H, float eps, int my_rank, int world, void* const* flags, int ready_index, uint32_t epoch,
+                          unsigned int* counter, int* status, cudaStream_t stream) {
+  using namespace bg::comm;
+  if (rows <= 0) return 0;
+  if (H % 128 != 0 || world > kMaxWorld) return -1;
+  sp_norm_quant_push_kernel<<<rows, 256, (size_t)H * sizeof(float), stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(partials), n_src, src_ready, wait_epoch,
+      reinterpret_cast<__nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(w),
+      reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<uint8_t*>(loc_q), loc_s, loc_s_stride, to_peers(ag_q, world),
+      to_peers(ag_s, world), ag_s_stride, push, rows, H, eps, my_rank, world, to_peers(flags, world), ready_index, epoch,
+      counter, status, has_residual);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_ep_count_push(const int* topk_idx, int n_pairs, int E, void* const* cnt, int my_rank, int world,
+                     void* const* flags, int ready_index, uint32_t epoch, void* row_info, int row_cap,
+                     cudaStream_t stream) {
+  using namespace bg::comm;
+  if (E > kMaxExperts || world > kMaxWorld) return -1;
+  ep_count_push_kernel<<<1, 1024, 0, stream>>>(topk_idx, n_pairs, E, to_peers(cnt, world), my_rank, world,
+                                               to_peers(flags, world), ready_index, epoch,
+                                               reinterpret_cast<int2*>(row_info), row_cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_ep_layout(const int* cnt, const uint32_t* cnt_ready, uint32_t epoch, int E, int world, int my_rank, int align,
+                 int* row_base, int* offsets, int* cursor, int* total_rows, int* status, cudaStream_t stream) {
+  using namespace bg::comm;
+  if (E > kMaxExperts || E % world != 0) return -1;
+  ep_layout_kernel<<<1, 1024, 0, stream>>>(cnt, cnt_ready, epoch, E, world, my_rank, align, row_base, offsets, cursor,
+                                           total_rows, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T, int K, int E, int H,
+                        const int* row_base, int* cursor, void* const* recv_q, void* const* recv_s, int recv_s_stride,
+                        void* const* recv_info, int recv_cap, int* sent_row, int my_rank, int world, void* const* flags,
+                        int ready_index, uint32_t epoch, unsigned int* counter, int* status, cudaStream_t stream) {
+  using namespace bg::comm;
+  if (K > 16 || H % 128 != 0) return -1;
+  if (T <= 0) {  // nothing to send, but peers still wait for this rank's flag
+    signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), ready_index + my_rank, world, epoch);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
+  ep_dispatch_send_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, topk_idx, K, E, H,
+                                                 row_base, cursor, to_peers(recv_q, world), to_peers(recv_s, world),
+                                                 recv_s_stride, to_peers(recv_info, world), recv_cap, sent_row, my_rank,
+                                                 world, to_peers(flags, world), ready_index, epoch, counter, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t stream) {
+  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_signal(void* const* flags, int index, int world, uint32_t epoch, cudaStream_t stream) {
+  bg::comm::signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), index, world, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // extern "C"

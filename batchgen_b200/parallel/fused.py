@@ -1,0 +1,236 @@
+"""FusedComm: tensor-parallel attention + expert-parallel MoE with the collectives fused into kernels.
+
+The residual stream is *row-sharded* (sequence parallel): rank r owns rows [r*Tl, (r+1)*Tl) of the
+step's T tokens.  Per layer:
+
+  all-gather -> GEMM        the RMSNorm kernel of the owner quantises its rows to e4m3 and stores them
+  (qkv_a, dense gate/up)    into every rank's gather buffer over NVLink; the consumer GEMM's TMA producer
+                            waits per tile on the source rank's arrival flag, so tiles whose rows are
+                            already here run while the rest are still in flight.
+  GEMM -> reduce-scatter    the GEMM epilogue stores each partial output row (bf16) straight into the
+  (o_proj, dense down)      owner's staging slot for this source; the owner's fused
+                            sum + residual + RMSNorm + quant kernel waits for all sources.
+  EP dispatch               router on own rows -> counts pushed to all ranks -> layout -> each token is
+                            quantised once and stored at its expert-grouped row in the owner's receive
+                            buffer together with its return address.
+  grouped expert GEMMs      run on the receive buffer as soon as every source has signalled; the down
+                            projection's epilogue stores each output row into the token owner's return
+                            buffer (combine), where the weighted top-k sum (+ shared expert) is taken in
+                            fixed k order.
+
+Every wait is bounded; an expired wait raises the status word that ``ops._ext.check_status`` reads.
+``NcclComm`` is the baseline implementing the same model-facing calls with NCCL collectives.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext, fused as fused_ops, gemm as gemm_ops, moe as moe_ops
+from ..ops.moe import ExpertWeights
+from .comm import NcclComm
+from .symm import MAX_WORLD, SymmetricHeap
+
+FP8 = torch.float8_e4m3fn
+AG_READY, RS_READY, CNT_READY, DISP_READY, RET_READY = 0, 8, 16, 24, 32
+ALIGN = 128
+
+
+def _pad(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class FusedComm(NcclComm):
+    fused = True
+
+    def __init__(self, device=None, group=None):
+        super().__init__(group)
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.heap: Optional[SymmetricHeap] = None
+        self.epoch = 0
+        self.nvlink_bytes = 0
+
+    # ------------------------------------------------------------------ setup
+    def configure(self, hidden: int, expert_hidden: int, num_experts: int, top_k: int, max_tokens: int) -> None:
+        """Size and carve the symmetric heap for steps of at most ``max_tokens`` tokens (whole job)."""
+        W = self.world
+        T = _pad(max_tokens, W * 8)
+        self.T_max, self.H, self.He, self.E, self.K = T, hidden, expert_hidden, num_experts, top_k
+        Tl = T // W
+        cap = _pad(T * top_k, ALIGN) + (num_experts // W) * ALIGN
+        self.recv_cap = cap
+        sizes = {
+            "flags": 64 * 4,
+            "ag_q": T * hidden, "ag_s": (hidden // 128) * _pad(T, 4) * 4,
+            "rs_buf": T * hidden * 2,
+            "cnt": W * num_experts * 4,
+            "recv_q": cap * expert_hidden, "recv_s": (expert_hidden // 128) * _pad(cap, 4) * 4,
+            "recv_info": cap * 8,
+            "ret": Tl * top_k * expert_hidden * 2,
+        }
+        total = sum(_pad(v, 1024) for v in sizes.values()) + 64 * 1024
+        self.heap = SymmetricHeap(total, self.device, self.group)
+        for k, v in sizes.items():
+            self.heap.alloc(k, v)
+        h = self.heap
+        self.flags = h.view("flags", torch.int32, (64,))
+        self.flag_ptrs = h.peer_ptrs("flags")
+        self.ag_q = h.view("ag_q", torch.uint8, (T, hidden)).view(FP8)
+        self.ag_s_stride = _pad(T, 4)
+        self.ag_s = h.view("ag_s", torch.float32, (hidden // 128, self.ag_s_stride))
+        self.rs_buf = h.view("rs_buf", torch.bfloat16, (T, hidden))
+        self.cnt = h.view("cnt", torch.int32, (W, num_experts))
+        self.recv_q = h.view("recv_q", torch.uint8, (cap, expert_hidden)).view(FP8)
+        self.recv_s_stride = _pad(cap, 4)
+        self.recv_s = h.view("recv_s", torch.float32, (expert_hidden // 128, self.recv_s_stride))
+        self.recv_info = h.view("recv_info", torch.int32, (cap, 2))
+        self.ret = h.view("ret", torch.bfloat16, (Tl * top_k, expert_hidden))
+        dev = self.device
+        self.counters = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.row_base = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.offsets = torch.zeros(num_experts // W + 1, dtype=torch.int32, device=dev)
+        self.total_rows = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.sent_row = torch.zeros(Tl * top_k, dtype=torch.int32, device=dev)
+        self.ident_pos = torch.arange(Tl * top_k, dtype=torch.int32, device=dev)
+        self.last = {AG_READY: 0, RS_READY: 0, CNT_READY: 0, DISP_READY: 0, RET_READY: 0}
+        self.heap.barrier()
+
+    def _next(self, kind: int) -> int:
+        self.epoch += 1
+        self.last[kind] = self.epoch
+        return self.epoch
+
+    def _flag_ptr(self, kind: int):
+        return ctypes.c_void_p(self.flags.data_ptr() + 4 * kind)
+
+    def _status(self):
+        return _ext.ptr(_ext.status_word(self.device))
+
+    # ------------------------------------------------------------------ sequence-parallel primitives
+    def sp_norm_push(self, src: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                     from_rs: bool, has_residual: bool, push: bool, want_y: bool = True, want_q: bool = True):
+        """Owner-side fused (sum of reduce-scatter partials | local rows) + residual + RMSNorm + quant,
+        optionally pushing the quantised rows into every rank's gather buffer.
+        Returns (y bf16 | None, q | None, s | None) for the rank's own rows."""
+        W, Tl = self.world, residual.shape[0]
+        H = residual.shape[1]
+        dev = self.device
+        y = torch.empty(Tl, H, dtype=torch.bfloat16, device=dev) if want_y else None
+        q = s = None
+        s_stride = 0
+        if want_q:
+            q = torch.empty(Tl, H, dtype=FP8, device=dev)
+            s = fused_ops._scale_buffer(Tl, H // 128, dev)
+            s_stride = s.stride(1)
+        if from_rs:
+            partials, n_src = self.rs_buf, W
+            ready, wait_epoch = self._flag_ptr(RS_READY), self.last[RS_READY]
+        else:
+            partials, n_src = src, 1
+            ready, wait_epoch = ctypes.c_void_p(0), 0
+        epoch = self._next(AG_READY) if push else 0
+        rc = _ext.lib().bg_sp_norm_quant_push(
+            _ext.ptr(partials), ctypes.c_int(n_src), ready, ctypes.c_uint32(wait_epoch), _ext.ptr(residual),
+            ctypes.c_int(int(has_residual)), _ext.ptr(weight), _ext.ptr(y), _ext.ptr(q), _ext.ptr(s),
+            ctypes.c_int(s_stride), self.heap.peer_ptrs("ag_q"), self.heap.peer_ptrs("ag_s"),
+            ctypes.c_int(self.ag_s_stride), ctypes.c_int(int(push)), ctypes.c_int(Tl), ctypes.c_int(H),
+            ctypes.c_float(eps), ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(AG_READY),
+            ctypes.c_uint32(epoch), _ext.ptr(self.counters[0:1]), self._status(), _ext.stream())
+        _ext.check(rc, "bg_sp_norm_quant_push")
+        if push:
+            self.nvlink_bytes += (W - 1) * Tl * (H + 4 * (H // 128))
+        return y, q, s
+
+    def _set_hooks(self, a_ready=None, a_ready_rows=0, epoch=0, m_rotate=0, peer_out=None, row_map=None,
+                   rs_rows=0, done_index=0, done_counter=None, peer_flags=None):
+        _ext.lib().bg_gemm_set_hooks(
+            a_ready if a_ready is not None else ctypes.c_void_p(0), ctypes.c_int(a_ready_rows), ctypes.c_uint32(epoch),
+            ctypes.c_int(m_rotate), peer_out if peer_out is not None else ctypes.c_void_p(0),
+            _ext.ptr(row_map), ctypes.c_int(rs_rows), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+            peer_flags if peer_flags is not None else ctypes.c_void_p(0), ctypes.c_int(done_index),
+            _ext.ptr(done_counter))
+
+    def ag_gemm(self, lin, T: int, silu_mul: bool = False) -> torch.Tensor:
+        """[T, K] (gathered e4m3 rows in the symmetric buffer) x W^T; tiles start as their source
+        rank's rows arrive, this rank's own rows first."""
+        Tl = T // self.world
+        tiles_per_rank = max(1, Tl // 128)
+        self._set_hooks(a_ready=self._flag_ptr(AG_READY), a_ready_rows=Tl, epoch=self.last[AG_READY],
+                        m_rotate=(self.rank * Tl) // 128 if Tl % 128 == 0 else 0)
+        xs = self.ag_s.t()[:T]
+        return gemm_ops.fp8_gemm(self.ag_q[:T], xs, lin.w, lin.s, silu_mul=silu_mul and lin.interleaved)
+
+    def gemm_rs(self, xq, xs, lin, T: int) -> None:
+        """Partial GEMM [T, Kshard] x W^T whose epilogue stores every output row into its owner's
+        staging slot for this rank; remote rows are computed first."""
+        Tl = T // self.world
+        epoch = self._next(RS_READY)
+        rot = (((self.rank + 1) % self.world) * Tl) // 128 if Tl % 128 == 0 else 0
+        self._set_hooks(m_rotate=rot, peer_out=self.heap.peer_ptrs("rs_buf"), rs_rows=Tl, epoch=epoch,
+                        done_index=RS_READY, done_counter=self.counters[1:2], peer_flags=self.flag_ptrs)
+        N = lin.w.shape[0]
+        out = self.rs_buf.view(-1)[: T * N].view(T, N)      # only its row stride is used by the scatter epilogue
+        gemm_ops.fp8_gemm(xq, xs, lin.w, lin.s, out=out)
+        self.nvlink_bytes += (self.world - 1) * Tl * N * 2
+
+    # ------------------------------------------------------------------ expert parallel
+    def moe_sp(self, h_local: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
+               extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Routed-expert output for this rank's own rows (dispatch -> experts -> combine)."""
+        W, E, K = self.world, self.E, topk_idx.shape[1]
+        Tl, H = h_local.shape
+        L = _ext.lib()
+        st = _ext.stream()
+        e_cnt = self._next(CNT_READY)
+        rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E), self.heap.peer_ptrs("cnt"),
+                                ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(CNT_READY),
+                                ctypes.c_uint32(e_cnt), _ext.ptr(self.recv_info), ctypes.c_int(self.recv_cap), st)
+        _ext.check(rc, "bg_ep_count_push")
+        rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), ctypes.c_int(E),
+                            ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(ALIGN), _ext.ptr(self.row_base),
+                            _ext.ptr(self.offsets), _ext.ptr(self.cursor), _ext.ptr(self.total_rows), self._status(), st)
+        _ext.check(rc, "bg_ep_layout")
+        e_disp = self._next(DISP_READY)
+        rc = L.bg_ep_dispatch_send(_ext.ptr(h_local), ctypes.c_int(h_local.stride(0)), _ext.ptr(topk_idx),
+                                   ctypes.c_int(Tl), ctypes.c_int(K), ctypes.c_int(E), ctypes.c_int(H),
+                                   _ext.ptr(self.row_base), _ext.ptr(self.cursor), self.heap.peer_ptrs("recv_q"),
+                                   self.heap.peer_ptrs("recv_s"), ctypes.c_int(self.recv_s_stride),
+                                   self.heap.peer_ptrs("recv_info"), ctypes.c_int(self.recv_cap),
+                                   _ext.ptr(self.sent_row), ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs,
+                                   ctypes.c_int(DISP_READY), ctypes.c_uint32(e_disp), _ext.ptr(self.counters[2:3]),
+                                   self._status(), st)
+        _ext.check(rc, "bg_ep_dispatch_send")
+        self.nvlink_bytes += Tl * K * (H + 4 * (H // 128)) * (W - 1) // W
+        # ---- experts on the receive buffer: the gate/up GEMM waits for every source rank's rows
+        xs = self.recv_s.t()[: self.recv_cap]
+        self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
+        act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True)
+        aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
+        # ---- down projection; the epilogue returns each row to its token's owner (combine)
+        e_ret = self._next(RET_READY)
+        self._set_hooks(peer_out=self.heap.peer_ptrs("ret"), row_map=self.recv_info, epoch=e_ret,
+                        done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
+        out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
+        gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets, out=_StrideCarrier(out_stub, self.recv_cap))
+        self.nvlink_bytes += Tl * K * H * 2 * (W - 1) // W
+        rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._status(), st)
+        _ext.check(rc, "bg_wait_flags")
+        return moe_ops.combine(self.ret[: Tl * K], self.ident_pos[: Tl * K].view(Tl, K), topk_w, extra)
+
+
+class _StrideCarrier:
+    """Stands in for an output tensor when the GEMM's scatter epilogue stores rows into peer memory:
+    only ``stride(0)``, ``data_ptr`` and ``shape`` are consulted by the launcher."""
+
+    def __init__(self, row: torch.Tensor, rows: int):
+        self._row, self.shape = row, (rows, row.shape[1])
+
+    def stride(self, i: int) -> int:
+        return self._row.shape[1] if i == 0 else 1
+
+    def data_ptr(self) -> int:
+        return self._row.data_ptr()

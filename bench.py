@@ -103,7 +103,11 @@ def main() -> int:
     total_pages = sum(pages_per_seq) + 8
 
     # ---- memory plan: how many distinct expert-weight sets fit next to the KV pool
-    layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    fused = comm is not None and getattr(comm, "fused", False)
+    layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=fused)
+    if fused:
+        comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
+                       max_tokens=max(B, args.prefill_tokens))
     n_moe = cfg.num_layers - cfg.first_k_dense
     expert_bytes_layer = (cfg.n_routed_experts // world) * 3 * cfg.moe_intermediate_size * cfg.hidden_size
     kv_bytes = total_pages * page * cfg.kv_cache_dim * 2 * cfg.num_layers
@@ -140,10 +144,20 @@ def main() -> int:
     out_tok = torch.empty(B, dtype=torch.int32, device=dev)
     tok_pinned = torch.empty(B, dtype=torch.int32).pin_memory()
 
+    Bl = B // world if fused else B
+    tok_loc = torch.empty(Bl, dtype=torch.int32, device=dev)
+
+    def run_model(ids, meta):
+        """-> greedy tokens of the whole step in out_tok (fused path: own rows sampled, then gathered)."""
+        if fused:
+            sampling_ops.greedy(model.forward_sp(ids, meta, kv), tok_loc)
+            dist.all_gather_into_tensor(out_tok, tok_loc)
+        else:
+            sampling_ops.greedy(model.forward(ids, meta, kv), out_tok)
+
     def decode_step_device():
         meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
-        logits = model.forward(d_ids, meta, kv)
-        sampling_ops.greedy(logits, out_tok)
+        run_model(d_ids, meta)
 
     def decode_step_e2e():
         a = ids_p.to(dev, non_blocking=True)
@@ -152,8 +166,7 @@ def main() -> int:
         d = slot_p.to(dev, non_blocking=True)
         e = len_p.to(dev, non_blocking=True)
         meta = AttnMeta(mode="decode", positions=c, slot_mapping=d, block_table=b, seqlens=e)
-        logits = model.forward(a, meta, kv)
-        sampling_ops.greedy(logits, out_tok)
+        run_model(a, meta)
         tok_pinned.copy_(out_tok, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         ids_p.copy_(tok_pinned)                              # next step feeds the sampled tokens
@@ -229,7 +242,10 @@ def main() -> int:
         def prefill_step():
             meta = AttnMeta(mode="prefill", positions=ppos, slot_mapping=pslot, block_table=pbt, cu_seqlens=cu,
                             ctx_lens=[0] * n_seq, logit_rows=rows)
-            sampling_ops.greedy(model.forward(pids, meta, kv))
+            if fused:
+                sampling_ops.greedy(model.forward_sp(pids, meta, kv))
+            else:
+                sampling_ops.greedy(model.forward(pids, meta, kv))
 
         prefill_step()
         psum = None
@@ -261,7 +277,8 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": B,
                        "seq_len": int(sum(ctx) / len(ctx)), "prompt_lens": "U[512,4096]", "decoded_so_far": 512,
-                       "parallelism": f"tp{world}+ep{world}", "comm": args.comm if world > 1 else "none",
+                       "parallelism": f"tp{world}+ep{world}",
+                       "comm": ("fused-nvlink-kernels" if fused else "nccl") if world > 1 else "none",
                        "distinct_expert_sets": sets, "moe_layers": n_moe,
                        "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",
                        "valid": not args.layers, "build_seconds": round(build_s, 1)},

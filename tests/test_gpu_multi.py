@@ -1,0 +1,33 @@
+"""Multi-GPU: fused NVLink kernels vs the unsharded model and the NCCL baseline (needs >= 2 GPUs)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(script, nproc, timeout=600):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, script)]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-4000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert lines, r.stdout[-2000:]
+    return json.loads(lines[-1])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_sequence_parallel_forward_matches():
+    n = 2 if torch.cuda.device_count() < 4 else min(8, torch.cuda.device_count())
+    n = 1 << (n.bit_length() - 1)
+    res = _run("mp_fused_check.py", n)
+    assert res["repeatable_all"]
+    assert res["rel_nccl_vs_full_max"] < 0.08, res
+    assert res["rel_fused_vs_full_max"] < 0.08, res
+    assert res["argmax_agree_min"] > 0.8, res
