@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-// ---------------------------------------------------------------- TMA (no multicast anywhere)
+// ---------------------------------------------------------------- TMA (plain per-CTA tile loads only)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
                                             int c1) {
   asm volatile(

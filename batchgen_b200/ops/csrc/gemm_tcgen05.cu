@@ -285,16 +285,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       const float* sb_lo = (KIND == KIND_FP8) ? p.sB + (size_t)(t.g * nblk + sb_blk_lo) * KB : nullptr;
       const float* sb_hi = (KIND == KIND_FP8) ? p.sB + (size_t)(t.g * nblk + sb_blk_hi) * KB : nullptr;
+      // Activation scales pushed by other ranks (all-gather / dispatch fused into this GEMM) may only be
+      // read once the producer has seen the arrival flags, i.e. after this tile's first accumulator
+      // hand-off, and with coherent loads; local inputs are prefetched one K block ahead right away.
+      const bool remote_a = (p.a_ready != nullptr);
       float sa_next = 1.f, sbl_next = 1.f, sbh_next = 1.f;
       if (KIND == KIND_FP8) {
-        sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
+        if (!remote_a) sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
         sbl_next = __ldg(sb_lo);
         sbh_next = __ldg(sb_hi);
       }
       for (int kg = 0; kg < groups_of_k; ++kg, ++acc) {
-        const float sa = sa_next, sbl = sbl_next, sbh = sbh_next;
+        float sa = sa_next;
+        const float sbl = sbl_next, sbh = sbh_next;
         if (KIND == KIND_FP8 && kg + 1 < groups_of_k) {
-          sa_next = row_ok ? __ldg(sa_ptr + (size_t)(kg + 1) * p.sa_stride) : 0.f;
+          if (!remote_a) sa_next = row_ok ? __ldg(sa_ptr + (size_t)(kg + 1) * p.sa_stride) : 0.f;
           sbl_next = __ldg(sb_lo + kg + 1);
           sbh_next = __ldg(sb_hi + kg + 1);
         }
@@ -305,6 +310,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           break;
         }
         tc_fence_after();
+        if (KIND == KIND_FP8 && remote_a) {
+          const volatile float* sv = sa_ptr;
+          if (kg == 0) sa = row_ok ? sv[0] : 0.f;
+          if (kg + 1 < groups_of_k) sa_next = row_ok ? sv[(size_t)(kg + 1) * p.sa_stride] : 0.f;
+        }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + half * 64;
         uint32_t v0[32], v1[32];
         tmem_ld_32x32(taddr, v0);
@@ -382,6 +392,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   }
 
+  if (p.done_counter != nullptr) __threadfence_system();   // this thread's peer stores, before the CTA reports
   tc_fence_before();
   __syncthreads();
   tc_fence_after();

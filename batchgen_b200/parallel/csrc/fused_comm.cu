@@ -1,5 +1,5 @@
 // Kernels that move data between GPUs themselves (plain peer loads/stores over NVLink into a
-// symmetric heap) fused with the compute around the collective.  No NCCL call, no TMA multicast.
+// symmetric heap) fused with the compute around the collective.  No NCCL call; TMA is used on local memory only.
 //
 //   sp_norm_quant_push     owner side of GEMM->reduce-scatter: sum the partial rows every rank pushed,
 //                          add the residual, RMSNorm, quantise to e4m3 and push the quantised rows into
@@ -40,6 +40,7 @@ __device__ __forceinline__ void signal_all(const Peers& flags, int index, int wo
 // Last-CTA-out signalling: every CTA fences its stores; the last one raises the flags.
 __device__ __forceinline__ void cta_done_signal(unsigned int* counter, const Peers& flags, int index, int world,
                                                 uint32_t epoch) {
+  __threadfence_system();   // every thread: its own peer stores first
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -186,6 +187,7 @@ ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers
     int* dst = reinterpret_cast<int*>(cnt.p[(my_rank + d) % world]) + (size_t)my_rank * E;
     for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = c[e];
   }
+  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
