@@ -189,12 +189,15 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-constexpr uint32_t kFlagSpinLimit = 1u << 22;  // x ~100 ns sleep: about half a second, then give up
-// Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t value) {
+constexpr uint32_t kFlagSpinLimit = 1u << 20;  // polls of >= 200 ns each: a second or so, then give up
+// Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded; and once any
+// kernel has raised the status word (a peer is late or gone) later waits give up at once, so a
+// broken step drains in milliseconds instead of one timeout per kernel.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t value, const int* status = nullptr) {
   for (uint32_t i = 0; i < kFlagSpinLimit; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - value) >= 0) return true;
-    __nanosleep(100);
+    if (status != nullptr && (i & 63u) == 0u && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+    __nanosleep(200);
   }
   return false;
 }

@@ -183,8 +183,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int i_lo = p.a_ready_rows > 0 ? t.m0 / p.a_ready_rows : 0;            // rows == 0: wait for every rank
           const int i_hi = p.a_ready_rows > 0 ? last / p.a_ready_rows : p.world - 1;
           for (int i = i_lo; ok && i <= i_hi; ++i) {
-            if (!wait_flag_ge(p.a_ready + i, p.epoch)) {
+            if (!wait_flag_ge(p.a_ready + i, p.epoch, p.status)) {
               if (*abort_flag == 0) *abort_flag = kTimeoutPeer;
+              if (p.status != nullptr) atomicMax(p.status, (int)kTimeoutPeer);
               ok = false;
             }
           }

@@ -74,7 +74,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
     if (threadIdx.x == 0) {
       int ok = 1;
       for (int s = 0; s < n_src; ++s)
-        if (!wait_flag_ge(src_ready + s, wait_epoch)) ok = 0;
+        if (!wait_flag_ge(src_ready + s, wait_epoch, status)) ok = 0;
       if (!ok && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
       wait_ok = ok;
     }
@@ -210,7 +210,7 @@ ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_r
   if (threadIdx.x == 0) {
     int ok = 1;
     for (int s = 0; s < world; ++s)
-      if (!wait_flag_ge(cnt_ready + s, epoch)) ok = 0;
+      if (!wait_flag_ge(cnt_ready + s, epoch, status)) ok = 0;
     if (!ok && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
     ok_s = ok;
   }
@@ -310,7 +310,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
 
 __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status) {
   if (threadIdx.x < n) {
-    if (!wait_flag_ge(flags + threadIdx.x, epoch) && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
+    if (!wait_flag_ge(flags + threadIdx.x, epoch, status) && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
   }
 }
 

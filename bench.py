@@ -203,7 +203,7 @@ def main() -> int:
     ms_step = ms / args.steps
     decode_tps = B * 1000.0 / ms_step
 
-    if args.profile_ops and rank == 0:
+    if args.profile_ops:                                   # every rank runs the same steps (collectives inside)
         from batchgen_b200.utils.timing import TimingStats
         model.timer = TimingStats()
         for _ in range(2):
@@ -249,13 +249,15 @@ def main() -> int:
 
         prefill_step()
         psum = None
-        if args.profile_ops and rank == 0:
+        if args.profile_ops:
+            model.timer.reset()
             prefill_step()
             model.timer.step_done()
             torch.cuda.synchronize()
             psum = model.timer.summary()
             from batchgen_b200.utils.timing import null_timer
             model.timer = null_timer()
+        if args.profile_ops and rank == 0:
             with open(args.profile_ops, "w") as f:
                 for title, sm in (("decode step", dsum), ("prefill micro-batch", psum)):
                     f.write(f"== {title}: ms per step by operator (CUDA events, eager) ==\n")
