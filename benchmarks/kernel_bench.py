@@ -1,0 +1,131 @@
+#!/usr/bin/env python
+"""Micro-benchmarks of the individual sm_100a kernels with roofline fractions.
+
+    python benchmarks/kernel_bench.py <case> [--iters N] [size flags]
+
+Cases: gemm_fp8, gemm_bf16, grouped_fp8, mla_decode, mla_prefill, norm_quant.  Each case uses inputs
+larger than the 126 MB L2, warms up, times with CUDA events on the launching stream and prints one JSON
+line: time, achieved TFLOP/s or GB/s, and the fraction "of measured" peak (MEASURED_PEAKS.json at the
+repository root when present, else the fallback figures 6.65 TB/s / 1.59 PFLOP/s, "of fallback").
+The same command lines are the ones profiled with ncu for the summaries under profiles/.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from batchgen_b200.ops import _ext, fused, gemm, ref  # noqa: E402
+from batchgen_b200.ops.mla_kernel import mla_decode_tc, mla_prefill_tc  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+def timeit(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--rows", type=int, default=128, help="rows per expert (grouped)")
+    ap.add_argument("--batch", type=int, default=96)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=16)
+    a = ap.parse_args()
+    dev = "cuda"
+    hbm, tf, tag = peaks()
+    out = {"case": a.case}
+    if a.case in ("gemm_fp8", "gemm_bf16"):
+        M, N, K = a.m, a.n, a.k
+        if a.case == "gemm_fp8":
+            xq = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+            wq = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn)
+            xs = torch.rand(K // 128, M, device=dev).t()
+            ws = torch.rand((N + 127) // 128, K // 128, device=dev)
+            ms = timeit(lambda: gemm.fp8_gemm(xq, xs, wq, ws), a.iters)
+            byts = M * K + N * K + M * N * 2
+        else:
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+            ms = timeit(lambda: gemm.bf16_gemm(x, w), a.iters)
+            byts = 2 * (M * K + N * K + M * N)
+        fl = 2.0 * M * N * K
+        out.update(shape=[M, N, K], ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_gemm_peak=fl / ms / 1e9 / tf,
+                   gbs=byts / ms / 1e6, peak_note=tag)
+    elif a.case == "grouped_fp8":
+        E, N, K, R = a.experts, a.n, a.k, a.rows
+        pad = (R + 127) // 128 * 128
+        offs = (torch.arange(E + 1, dtype=torch.int32) * pad).to(dev)
+        xq = torch.randn(E * pad, K, device=dev).to(torch.float8_e4m3fn)
+        xs = torch.rand(K // 128, E * pad, device=dev).t()
+        wq = torch.randn(E, N, K, device=dev).to(torch.float8_e4m3fn)
+        ws = torch.rand(E, N // 128, K // 128, device=dev)
+        ms = timeit(lambda: gemm.grouped_fp8_gemm(xq, xs, wq, ws, offs), a.iters)
+        byts = E * N * K + E * pad * K + E * pad * N * 2
+        out.update(shape=[E, R, N, K], ms=ms, gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm,
+                   tflops=2.0 * E * pad * N * K / ms / 1e9, peak_note=tag)
+    elif a.case in ("mla_decode", "mla_prefill"):
+        B, H, L = a.batch, a.heads, a.ctx
+        S = 64
+        npg = (L + S - 1) // S
+        if a.case == "mla_decode":
+            cache = (torch.randn(B * npg, S, 576, device=dev) * 0.5).to(torch.bfloat16)
+            bt = torch.arange(B * npg, dtype=torch.int32, device=dev).view(B, npg)
+            q = torch.randn(B, H, 576, device=dev).to(torch.bfloat16)
+            qa, qp = q[..., :512].contiguous(), q[..., 512:].contiguous()
+            sl = torch.full((B,), L, dtype=torch.int32, device=dev)
+            ms = timeit(lambda: mla_decode_tc(qa, qp, cache, bt, sl, 0.1, 512), a.iters)
+            byts = B * L * 1152
+            fl = 2.0 * B * L * H * (576 + 512)
+        else:
+            cache = (torch.randn(B * npg, S, 576, device=dev) * 0.5).to(torch.bfloat16)
+            bt = torch.arange(B * npg, dtype=torch.int32, device=dev).view(B, npg)
+            q = torch.randn(B * L, H, 576, device=dev).to(torch.bfloat16)
+            qa, qp = q[..., :512].contiguous(), q[..., 512:].contiguous()
+            cu = [i * L for i in range(B + 1)]
+            ms = timeit(lambda: mla_prefill_tc(qa, qp, cache, bt, cu, [0] * B, 0.1, 512), a.iters)
+            byts = B * L * 1152
+            fl = 2.0 * B * (L * (L + 1) / 2) * H * (576 + 512)
+        out.update(shape=[B, H, L], ms=ms, kv_gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm,
+                   tflops=fl / ms / 1e9, frac_of_bf16_gemm_peak=fl / ms / 1e9 / tf, peak_note=tag)
+    elif a.case == "norm_quant":
+        T, H = a.m, 7168
+        x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+        r = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: fused.rmsnorm(x, w, 1e-6, residual=r, quant=True), a.iters)
+        byts = T * H * (2 + 2 + 2 + 2 + 1)
+        out.update(shape=[T, H], ms=ms, gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm, peak_note=tag)
+    else:
+        raise SystemExit(f"unknown case {a.case}")
+    _ext.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
