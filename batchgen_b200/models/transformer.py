@@ -336,9 +336,13 @@ class Transformer:
         assert T % W == 0, "pad the step to a multiple of the world size"
         Tl = T // W
         eps = cfg.rms_eps
+        comm.begin_step()
         src = self.w.embed[ids[r * Tl:(r + 1) * Tl].long()]      # local rows of the residual stream
         residual = torch.empty_like(src)
         first = True
+        nv_local = None
+        if meta.num_valid is not None:                           # padding rows of a graph bucket
+            nv_local = (meta.num_valid - r * Tl).clamp(0, Tl).to(torch.int32)
         for l, lw in enumerate(self.w.layers):
             # input norm of own rows (+ previous sublayer's output), quantised rows pushed to every rank
             with tm.timed("sp.norm_push", l):
@@ -359,7 +363,7 @@ class Transformer:
                     logits = moe_ops.router_logits(x, lw.router_w)
                     idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group,
                                                  cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor,
-                                                 cfg.scoring_func)
+                                                 cfg.scoring_func, num_valid=nv_local)
                 shared = None
                 if lw.w13 is not None:
                     with tm.timed("moe.shared_expert", l):
@@ -377,5 +381,6 @@ class Transformer:
                 src = None                                       # next norm sums the reduce-scatter partials
         x, _, _ = comm.sp_norm_push(src, residual, self.w.final_norm, eps, from_rs=src is None, has_residual=True,
                                     push=False, want_q=False)
+        comm.end_step()
         with tm.timed("lm_head"):
             return (x @ self.w.lm_head.t()).float()

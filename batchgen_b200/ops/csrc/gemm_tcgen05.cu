@@ -53,7 +53,8 @@ struct GemmParams {
   // memory by rank i; they are valid once a_ready[i] >= epoch.  The TMA producer waits per tile.
   const uint32_t* a_ready;
   int a_ready_rows;
-  uint32_t epoch;
+  uint32_t epoch;              // compared / published value = epoch + *epoch_base (base lives on the device so
+  const uint32_t* epoch_base;  // that a captured CUDA graph advances its epochs from replay to replay)
   int m_rotate;         // dense: row block processed first (tiles rotate, e.g. local rows first / last)
   // GEMM -> reduce-scatter / combine: the epilogue stores each output row into the memory of the
   // rank that owns it.  row_map[row] = (rank, dest row) (rank < 0: drop the row); without a map row m
@@ -134,6 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t epoch = p.epoch + (p.epoch_base != nullptr ? *p.epoch_base : 0u);
   constexpr int kElemBytes = (KIND == KIND_FP8) ? 1 : 2;
   constexpr int BK = BK_BYTES / kElemBytes;  // elements of K per stage
   const int KB = p.K / BK;
@@ -183,7 +185,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int i_lo = p.a_ready_rows > 0 ? t.m0 / p.a_ready_rows : 0;            // rows == 0: wait for every rank
           const int i_hi = p.a_ready_rows > 0 ? last / p.a_ready_rows : p.world - 1;
           for (int i = i_lo; ok && i <= i_hi; ++i) {
-            if (!wait_flag_ge(p.a_ready + i, p.epoch, p.status)) {
+            if (!wait_flag_ge(p.a_ready + i, epoch, p.status)) {
               if (*abort_flag == 0) *abort_flag = kTimeoutPeer;
               if (p.status != nullptr) atomicMax(p.status, (int)kTimeoutPeer);
               ok = false;
@@ -407,7 +409,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (prev == gridDim.x - 1) {
       *p.done_counter = 0u;
       __threadfence_system();
-      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.done_flag_index + p.my_rank, p.epoch);
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.done_flag_index + p.my_rank, epoch);
     }
   }
 }
@@ -477,17 +479,19 @@ extern "C" {
 
 // Collective hooks of the next bg_gemm call on this thread (consumed by that call, then cleared).
 struct BgGemmHooks {
-  const uint32_t* a_ready; int a_ready_rows; uint32_t epoch; int m_rotate;
+  const uint32_t* a_ready; int a_ready_rows; uint32_t epoch; const uint32_t* epoch_base; int m_rotate;
   void* peer_out[8]; const int2* row_map; int rs_rows_per_rank; int my_rank; int world;
   uint32_t* peer_flags[8]; int done_flag_index; unsigned int* done_counter;
 };
 static thread_local BgGemmHooks g_hooks;
 static thread_local bool g_hooks_set = false;
 
-void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch, int m_rotate, void* const* peer_out,
+void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch, const uint32_t* epoch_base, int m_rotate,
+                       void* const* peer_out,
                        const void* row_map, int rs_rows_per_rank, int my_rank, int world, uint32_t* const* peer_flags,
                        int done_flag_index, unsigned int* done_counter) {
-  g_hooks.a_ready = a_ready; g_hooks.a_ready_rows = a_ready_rows; g_hooks.epoch = epoch; g_hooks.m_rotate = m_rotate;
+  g_hooks.a_ready = a_ready; g_hooks.a_ready_rows = a_ready_rows; g_hooks.epoch = epoch;
+  g_hooks.epoch_base = epoch_base; g_hooks.m_rotate = m_rotate;
   for (int i = 0; i < 8; ++i) {
     g_hooks.peer_out[i] = (peer_out != nullptr && i < world) ? peer_out[i] : nullptr;
     g_hooks.peer_flags[i] = (peer_flags != nullptr && i < world) ? peer_flags[i] : nullptr;
@@ -514,12 +518,12 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
   GemmParams p;
   p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
   p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
-  p.a_ready = nullptr; p.a_ready_rows = 1; p.epoch = 0; p.m_rotate = 0; p.row_map = nullptr; p.rs_rows_per_rank = 1;
+  p.a_ready = nullptr; p.a_ready_rows = 1; p.epoch = 0; p.epoch_base = nullptr; p.m_rotate = 0; p.row_map = nullptr; p.rs_rows_per_rank = 1;
   p.my_rank = 0; p.world = 1; p.done_flag_index = 0; p.done_counter = nullptr;
   for (int i = 0; i < 8; ++i) { p.peer_out[i] = nullptr; p.peer_flags[i] = nullptr; }
   if (g_hooks_set) {
     p.a_ready = g_hooks.a_ready; p.a_ready_rows = g_hooks.a_ready_rows;
-    p.epoch = g_hooks.epoch; p.m_rotate = g_hooks.m_rotate; p.row_map = g_hooks.row_map;
+    p.epoch = g_hooks.epoch; p.epoch_base = g_hooks.epoch_base; p.m_rotate = g_hooks.m_rotate; p.row_map = g_hooks.row_map;
     p.rs_rows_per_rank = g_hooks.rs_rows_per_rank > 0 ? g_hooks.rs_rows_per_rank : 1;
     p.my_rank = g_hooks.my_rank; p.world = g_hooks.world; p.done_flag_index = g_hooks.done_flag_index;
     p.done_counter = g_hooks.done_counter;

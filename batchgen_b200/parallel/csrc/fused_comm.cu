@@ -33,6 +33,15 @@ struct Peers {
   void* p[kMaxWorld];
 };
 
+// Epochs are passed as (offset, base pointer): the effective value is offset + *base.  The base lives in
+// device memory and is bumped by bump_epoch_kernel at the end of every step, so a captured CUDA graph
+// publishes and expects fresh epochs on every replay without any host involvement.
+struct Epoch {
+  uint32_t off;
+  const uint32_t* base;
+  __device__ __forceinline__ uint32_t get() const { return off + (base != nullptr ? *base : 0u); }
+};
+
 __device__ __forceinline__ void signal_all(const Peers& flags, int index, int world, uint32_t epoch) {
   for (int r = 0; r < world; ++r) st_release_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + index, epoch);
 }
@@ -60,12 +69,14 @@ __device__ __forceinline__ void cta_done_signal(unsigned int* counter, const Pee
 // rank's gather buffer at row (my_rank * rows + r): ag_q [T, H] e4m3, ag_s [KB, ag_s_stride] fp32.
 __global__ void __launch_bounds__(256)
 sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src, const uint32_t* __restrict__ src_ready,
-                          uint32_t wait_epoch, __nv_bfloat16* __restrict__ residual,
+                          Epoch wait_epoch_e, __nv_bfloat16* __restrict__ residual,
                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                           uint8_t* __restrict__ loc_q, float* __restrict__ loc_s, int loc_s_stride, Peers ag_q,
                           Peers ag_s, int ag_s_stride, int push, int rows, int H, float eps, int my_rank, int world,
-                          Peers flags, int ready_index, uint32_t epoch, unsigned int* counter, int* status,
+                          Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter, int* status,
                           int has_residual) {
+  const uint32_t wait_epoch = wait_epoch_e.get();
+  const uint32_t epoch = epoch_e.get();
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   __shared__ int wait_ok;
@@ -173,7 +184,8 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
 // every rank's count matrix cnt[src = my_rank][E]; also clears this rank's return-address table.
 __global__ void __launch_bounds__(1024)
 ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers cnt, int my_rank, int world, Peers flags,
-                     int ready_index, uint32_t epoch, int2* __restrict__ row_info, int row_cap) {
+                     int ready_index, Epoch epoch_e, int2* __restrict__ row_info, int row_cap) {
+  const uint32_t epoch = epoch_e.get();
   __shared__ int c[kMaxExperts];
   for (int e = threadIdx.x; e < E; e += blockDim.x) c[e] = 0;
   for (int i = threadIdx.x; i < row_cap; i += blockDim.x) row_info[i] = make_int2(-1, -1);
@@ -200,13 +212,14 @@ ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers
 //   offsets[El+1] segment offsets (128-aligned) of this rank's own receive buffer
 //   cursor[e] = 0
 __global__ void __launch_bounds__(1024)
-ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, uint32_t epoch, int E, int world,
+ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, Epoch epoch_e, int E, int world,
                  int my_rank, int align, int* __restrict__ row_base, int* __restrict__ offsets,
                  int* __restrict__ cursor, int* __restrict__ total_rows, int* status) {
   __shared__ int tot[kMaxExperts];
   __shared__ int mine[kMaxExperts];
   __shared__ int seg[kMaxExperts];
   __shared__ int ok_s;
+  const uint32_t epoch = epoch_e.get();
   if (threadIdx.x == 0) {
     int ok = 1;
     for (int s = 0; s < world; ++s)
@@ -253,8 +266,9 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const int* __restrict__ topk_idx, int K,
                         int E, int H, const int* __restrict__ row_base, int* __restrict__ cursor, Peers recv_q,
                         Peers recv_s, int recv_s_stride, Peers recv_info, int recv_cap, int* __restrict__ sent_row,
-                        int my_rank, int world, Peers flags, int ready_index, uint32_t epoch, unsigned int* counter,
+                        int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter,
                         int* status) {
+  const uint32_t epoch = epoch_e.get();
   __shared__ int dest_rank[16], dest_row[16];
   const int t = blockIdx.x;
   const int El = E / world;
@@ -308,13 +322,19 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
   cta_done_signal(counter, flags, ready_index + my_rank, world, epoch);
 }
 
-__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status) {
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, int* status) {
+  const uint32_t epoch = epoch_e.get();
   if (threadIdx.x < n) {
     if (!wait_flag_ge(flags + threadIdx.x, epoch, status) && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
   }
 }
 
-__global__ void signal_kernel(Peers flags, int index, int world, uint32_t epoch) {
+__global__ void bump_epoch_kernel(uint32_t* base, uint32_t n) {
+  if (threadIdx.x == 0) *base += n;
+}
+
+__global__ void signal_kernel(Peers flags, int index, int world, Epoch epoch_e) {
+  const uint32_t epoch = epoch_e.get();
   if (threadIdx.x == 0) {
     __threadfence_system();
     signal_all(flags, index, world, epoch);
@@ -335,6 +355,7 @@ static Peers to_peers(void* const* arr, int world) {
 }
 
 int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_ready, uint32_t wait_epoch,
+                          const uint32_t* epoch_base,
                           void* residual, int has_residual, const void* w, void* y, void* loc_q, float* loc_s,
                           int loc_s_stride, void* const* ag_q, void* const* ag_s, int ag_s_stride, int push, int rows,
                           int H, float eps, int my_rank, int world, void* const* flags, int ready_index, uint32_t epoch,
@@ -343,30 +364,32 @@ int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_r
   if (rows <= 0) return 0;
   if (H % 128 != 0 || world > kMaxWorld) return -1;
   sp_norm_quant_push_kernel<<<rows, 256, (size_t)H * sizeof(float), stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(partials), n_src, src_ready, wait_epoch,
+      reinterpret_cast<const __nv_bfloat16*>(partials), n_src, src_ready, Epoch{wait_epoch, epoch_base},
       reinterpret_cast<__nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<uint8_t*>(loc_q), loc_s, loc_s_stride, to_peers(ag_q, world),
-      to_peers(ag_s, world), ag_s_stride, push, rows, H, eps, my_rank, world, to_peers(flags, world), ready_index, epoch,
-      counter, status, has_residual);
+      to_peers(ag_s, world), ag_s_stride, push, rows, H, eps, my_rank, world, to_peers(flags, world), ready_index,
+      Epoch{epoch, epoch_base}, counter, status, has_residual);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int bg_ep_count_push(const int* topk_idx, int n_pairs, int E, void* const* cnt, int my_rank, int world,
-                     void* const* flags, int ready_index, uint32_t epoch, void* row_info, int row_cap,
-                     cudaStream_t stream) {
+                     void* const* flags, int ready_index, uint32_t epoch, const uint32_t* epoch_base, void* row_info,
+                     int row_cap, cudaStream_t stream) {
   using namespace bg::comm;
   if (E > kMaxExperts || world > kMaxWorld) return -1;
   ep_count_push_kernel<<<1, 1024, 0, stream>>>(topk_idx, n_pairs, E, to_peers(cnt, world), my_rank, world,
-                                               to_peers(flags, world), ready_index, epoch,
+                                               to_peers(flags, world), ready_index, Epoch{epoch, epoch_base},
                                                reinterpret_cast<int2*>(row_info), row_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int bg_ep_layout(const int* cnt, const uint32_t* cnt_ready, uint32_t epoch, int E, int world, int my_rank, int align,
+int bg_ep_layout(const int* cnt, const uint32_t* cnt_ready, uint32_t epoch, const uint32_t* epoch_base, int E, int world,
+                 int my_rank, int align,
                  int* row_base, int* offsets, int* cursor, int* total_rows, int* status, cudaStream_t stream) {
   using namespace bg::comm;
   if (E > kMaxExperts || E % world != 0) return -1;
-  ep_layout_kernel<<<1, 1024, 0, stream>>>(cnt, cnt_ready, epoch, E, world, my_rank, align, row_base, offsets, cursor,
+  ep_layout_kernel<<<1, 1024, 0, stream>>>(cnt, cnt_ready, Epoch{epoch, epoch_base}, E, world, my_rank, align, row_base,
+                                           offsets, cursor,
                                            total_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -374,27 +397,35 @@ int bg_ep_layout(const int* cnt, const uint32_t* cnt_ready, uint32_t epoch, int 
 int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T, int K, int E, int H,
                         const int* row_base, int* cursor, void* const* recv_q, void* const* recv_s, int recv_s_stride,
                         void* const* recv_info, int recv_cap, int* sent_row, int my_rank, int world, void* const* flags,
-                        int ready_index, uint32_t epoch, unsigned int* counter, int* status, cudaStream_t stream) {
+                        int ready_index, uint32_t epoch, const uint32_t* epoch_base, unsigned int* counter, int* status,
+                        cudaStream_t stream) {
   using namespace bg::comm;
   if (K > 16 || H % 128 != 0) return -1;
   if (T <= 0) {  // nothing to send, but peers still wait for this rank's flag
-    signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), ready_index + my_rank, world, epoch);
+    signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), ready_index + my_rank, world, Epoch{epoch, epoch_base});
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   ep_dispatch_send_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, topk_idx, K, E, H,
                                                  row_base, cursor, to_peers(recv_q, world), to_peers(recv_s, world),
                                                  recv_s_stride, to_peers(recv_info, world), recv_cap, sent_row, my_rank,
-                                                 world, to_peers(flags, world), ready_index, epoch, counter, status);
+                                                 world, to_peers(flags, world), ready_index, Epoch{epoch, epoch_base}, counter,
+                                                 status);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t stream) {
-  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
+int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int* status,
+                  cudaStream_t stream) {
+  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int bg_signal(void* const* flags, int index, int world, uint32_t epoch, cudaStream_t stream) {
-  bg::comm::signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), index, world, epoch);
+int bg_signal(void* const* flags, int index, int world, uint32_t epoch, const uint32_t* epoch_base, cudaStream_t stream) {
+  bg::comm::signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), index, world, bg::comm::Epoch{epoch, epoch_base});
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int bg_bump_epoch(uint32_t* base, uint32_t n, cudaStream_t stream) {
+  bg::comm::bump_epoch_kernel<<<1, 32, 0, stream>>>(base, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

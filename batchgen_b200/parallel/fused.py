@@ -97,12 +97,30 @@ class FusedComm(NcclComm):
         self.sent_row = torch.zeros(Tl * top_k, dtype=torch.int32, device=dev)
         self.ident_pos = torch.arange(Tl * top_k, dtype=torch.int32, device=dev)
         self.last = {AG_READY: 0, RS_READY: 0, CNT_READY: 0, DISP_READY: 0, RET_READY: 0}
+        # Epochs are (offset within the step) + (device-resident base).  The base is bumped by a kernel at
+        # the end of every step, so a captured CUDA graph advances its epochs on every replay.
+        self.epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch = 0
         self.heap.barrier()
+
+    def begin_step(self) -> None:
+        self.epoch = 0
+        for k in self.last:
+            self.last[k] = 0
+
+    def end_step(self) -> None:
+        """Advance the device epoch base past every epoch this step used (stream-ordered)."""
+        rc = _ext.lib().bg_bump_epoch(_ext.ptr(self.epoch_base), ctypes.c_uint32(self.epoch), _ext.stream())
+        _ext.check(rc, "bg_bump_epoch")
+        self.epoch = 0
 
     def _next(self, kind: int) -> int:
         self.epoch += 1
         self.last[kind] = self.epoch
         return self.epoch
+
+    def _base(self):
+        return _ext.ptr(self.epoch_base)
 
     def _flag_ptr(self, kind: int):
         return ctypes.c_void_p(self.flags.data_ptr() + 4 * kind)
@@ -134,7 +152,8 @@ class FusedComm(NcclComm):
             ready, wait_epoch = ctypes.c_void_p(0), 0
         epoch = self._next(AG_READY) if push else 0
         rc = _ext.lib().bg_sp_norm_quant_push(
-            _ext.ptr(partials), ctypes.c_int(n_src), ready, ctypes.c_uint32(wait_epoch), _ext.ptr(residual),
+            _ext.ptr(partials), ctypes.c_int(n_src), ready, ctypes.c_uint32(wait_epoch), self._base(),
+            _ext.ptr(residual),
             ctypes.c_int(int(has_residual)), _ext.ptr(weight), _ext.ptr(y), _ext.ptr(q), _ext.ptr(s),
             ctypes.c_int(s_stride), self.heap.peer_ptrs("ag_q"), self.heap.peer_ptrs("ag_s"),
             ctypes.c_int(self.ag_s_stride), ctypes.c_int(int(push)), ctypes.c_int(Tl), ctypes.c_int(H),
@@ -149,7 +168,7 @@ class FusedComm(NcclComm):
                    rs_rows=0, done_index=0, done_counter=None, peer_flags=None):
         _ext.lib().bg_gemm_set_hooks(
             a_ready if a_ready is not None else ctypes.c_void_p(0), ctypes.c_int(a_ready_rows), ctypes.c_uint32(epoch),
-            ctypes.c_int(m_rotate), peer_out if peer_out is not None else ctypes.c_void_p(0),
+            self._base(), ctypes.c_int(m_rotate), peer_out if peer_out is not None else ctypes.c_void_p(0),
             _ext.ptr(row_map), ctypes.c_int(rs_rows), ctypes.c_int(self.rank), ctypes.c_int(self.world),
             peer_flags if peer_flags is not None else ctypes.c_void_p(0), ctypes.c_int(done_index),
             _ext.ptr(done_counter))
@@ -188,9 +207,11 @@ class FusedComm(NcclComm):
         e_cnt = self._next(CNT_READY)
         rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E), self.heap.peer_ptrs("cnt"),
                                 ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(CNT_READY),
-                                ctypes.c_uint32(e_cnt), _ext.ptr(self.recv_info), ctypes.c_int(self.recv_cap), st)
+                                ctypes.c_uint32(e_cnt), self._base(), _ext.ptr(self.recv_info),
+                                ctypes.c_int(self.recv_cap), st)
         _ext.check(rc, "bg_ep_count_push")
-        rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), ctypes.c_int(E),
+        rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
+                            ctypes.c_int(E),
                             ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(ALIGN), _ext.ptr(self.row_base),
                             _ext.ptr(self.offsets), _ext.ptr(self.cursor), _ext.ptr(self.total_rows), self._status(), st)
         _ext.check(rc, "bg_ep_layout")
@@ -201,7 +222,8 @@ class FusedComm(NcclComm):
                                    self.heap.peer_ptrs("recv_s"), ctypes.c_int(self.recv_s_stride),
                                    self.heap.peer_ptrs("recv_info"), ctypes.c_int(self.recv_cap),
                                    _ext.ptr(self.sent_row), ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs,
-                                   ctypes.c_int(DISP_READY), ctypes.c_uint32(e_disp), _ext.ptr(self.counters[2:3]),
+                                   ctypes.c_int(DISP_READY), ctypes.c_uint32(e_disp), self._base(),
+                                   _ext.ptr(self.counters[2:3]),
                                    self._status(), st)
         _ext.check(rc, "bg_ep_dispatch_send")
         self.nvlink_bytes += Tl * K * (H + 4 * (H // 128)) * (W - 1) // W
@@ -217,7 +239,8 @@ class FusedComm(NcclComm):
         out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
         gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets, out=_StrideCarrier(out_stub, self.recv_cap))
         self.nvlink_bytes += Tl * K * H * 2 * (W - 1) // W
-        rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._status(), st)
+        rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),
+                             self._status(), st)
         _ext.check(rc, "bg_wait_flags")
         return moe_ops.combine(self.ret[: Tl * K], self.ident_pos[: Tl * K].view(Tl, K), topk_w, extra)
 

@@ -1,0 +1,194 @@
+"""Whole-decode-step CUDA graphs with bucketed batch sizes.
+
+One graph per bucket captures the entire model forward of a decode step (every layer: norms, FP8
+GEMMs, MLA attention, router, dispatch, grouped expert GEMMs, combine — and, on multi-GPU jobs, the
+fused NVLink kernels or the NCCL collectives between them).  Inputs live in static device buffers that
+are refreshed from pinned host staging before each replay; rows past the real batch are padding
+(``seqlens = 0``, ``slot = -1``, router told through a device-resident ``num_valid``), so a bucket's
+graph serves every batch size up to the bucket.
+
+The fused communication kernels take their epochs as *offset + device-resident base*, and the base is
+bumped by a kernel at the end of each step, so replaying a graph publishes fresh epochs every time.
+
+Reference parity: batchgen/cuda_graph/graph_manager.py:37-547 (segments x buckets, static buffers,
+capture/replay, capture-memory ledger), buckets.py:13,99 (bucket generation), compare.py:75 (eager vs
+graph check), adapter.py (model adapter ABC; here the model's ``forward``/``forward_sp`` is the adapter).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..models.transformer import AttnMeta, Transformer
+from .kv_cache import PagedKVCache
+
+
+def generate_buckets(max_bucket: int, num_buckets: int, multiple: int = 1) -> List[int]:
+    """Roughly geometric bucket sizes ending at ``max_bucket``, each a multiple of ``multiple``."""
+    if max_bucket <= 0:
+        return []
+    out = set()
+    b = float(max(1, multiple))
+    ratio = (max_bucket / b) ** (1.0 / max(1, num_buckets - 1)) if max_bucket > b else 1.0
+    for _ in range(num_buckets):
+        v = int(-(-int(round(b)) // multiple) * multiple)
+        out.add(min(max(v, multiple), max_bucket))
+        b *= max(ratio, 1.0001)
+    out.add(-(-max_bucket // multiple) * multiple if max_bucket % multiple else max_bucket)
+    return sorted(out)
+
+
+class BatchSizeBucketing:
+    def __init__(self, buckets: Seq[int]):
+        self.buckets = sorted(set(buckets))
+
+    def bucket_for(self, n: int) -> int:
+        for b in self.buckets:
+            if b >= n:
+                return b
+        raise DecodeWidthExceedsGraphBucketError(f"decode width {n} exceeds the largest graph bucket "
+                                                 f"{self.buckets[-1] if self.buckets else 0}")
+
+
+class DecodeWidthExceedsGraphBucketError(RuntimeError):
+    pass
+
+
+@dataclass
+class CaptureLedger:
+    """Bytes of device memory each captured bucket added (the reference keeps the same ledger to size
+    the KV pool after capture)."""
+    per_bucket: Dict[int, int] = field(default_factory=dict)
+
+    @property
+    def total(self) -> int:
+        return sum(self.per_bucket.values())
+
+
+class DecodeGraphRunner:
+    def __init__(self, model: Transformer, kv: PagedKVCache, max_batch: int, max_pages_per_seq: int,
+                 num_buckets: int = 16, max_bucket: Optional[int] = None, sequence_parallel: bool = False):
+        self.model, self.kv = model, kv
+        self.dev = model.device
+        self.sp = sequence_parallel
+        self.world = model.comm.world if (model.comm is not None) else 1
+        mult = self.world if self.sp else 1
+        top = min(max_batch, max_bucket or max_batch)
+        top = -(-top // mult) * mult
+        self.bucketing = BatchSizeBucketing(generate_buckets(top, num_buckets, mult))
+        self.max_pages = max_pages_per_seq
+        B = top
+        d = self.dev
+        self.ids = torch.zeros(B, dtype=torch.int32, device=d)
+        self.pos = torch.zeros(B, dtype=torch.int32, device=d)
+        self.slots = torch.full((B,), -1, dtype=torch.int64, device=d)
+        self.lens = torch.zeros(B, dtype=torch.int32, device=d)
+        self.bt = torch.zeros(B, max_pages_per_seq, dtype=torch.int32, device=d)
+        self.num_valid = torch.zeros(1, dtype=torch.int32, device=d)
+        pin = torch.cuda.is_available()
+        self.h_ids = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_pos = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_slots = torch.full((B,), -1, dtype=torch.int64, pin_memory=pin)
+        self.h_lens = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_bt = torch.zeros(B, max_pages_per_seq, dtype=torch.int32, pin_memory=pin)
+        self.h_nv = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.outputs: Dict[int, torch.Tensor] = {}
+        self.pool = None
+        self.ledger = CaptureLedger()
+        self.replays = 0
+        self.h2d_bytes_per_step = 0
+
+    # ------------------------------------------------------------------ capture
+    def _meta(self, b: int) -> AttnMeta:
+        return AttnMeta(mode="decode", positions=self.pos[:b], slot_mapping=self.slots[:b], block_table=self.bt[:b],
+                        seqlens=self.lens[:b], num_valid=self.num_valid)
+
+    def _forward(self, b: int) -> torch.Tensor:
+        if self.sp:
+            return self.model.forward_sp(self.ids[:b], self._meta(b), self.kv)
+        return self.model.forward(self.ids[:b], self._meta(b), self.kv)
+
+    def capture(self, bucket: int) -> None:
+        if bucket in self.graphs:
+            return
+        free0 = torch.cuda.mem_get_info(self.dev)[0]
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                       # warm-up: caches, attributes, work lists
+                self._forward(bucket)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(g, pool=self.pool):
+            out = self._forward(bucket)
+        torch.cuda.synchronize(self.dev)
+        self.graphs[bucket] = g
+        self.outputs[bucket] = out
+        self.ledger.per_bucket[bucket] = max(0, free0 - torch.cuda.mem_get_info(self.dev)[0])
+
+    def capture_all(self) -> None:
+        for b in sorted(self.bucketing.buckets, reverse=True):   # largest first: smaller ones reuse its pool
+            self.capture(b)
+
+    # ------------------------------------------------------------------ replay
+    def stage(self, ids: Seq[int], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]]) -> int:
+        """Fill the pinned staging buffers and enqueue the host->device copies.  Returns the bucket."""
+        n = len(ids)
+        b = self.bucketing.bucket_for(n)
+        self.h_ids[:n] = torch.as_tensor(ids, dtype=torch.int32)
+        self.h_pos[:n] = torch.as_tensor(pos, dtype=torch.int32)
+        self.h_slots[:n] = torch.as_tensor(slots, dtype=torch.int64)
+        self.h_lens[:n] = torch.as_tensor(lens, dtype=torch.int32)
+        if b > n:
+            self.h_ids[n:b] = 0
+            self.h_pos[n:b] = 0
+            self.h_slots[n:b] = -1
+            self.h_lens[n:b] = 0
+        for i, pl in enumerate(page_lists):
+            k = len(pl)
+            self.h_bt[i, :k] = torch.as_tensor(pl, dtype=torch.int32)
+        self.h_nv[0] = n
+        nb = True
+        self.ids[:b].copy_(self.h_ids[:b], non_blocking=nb)
+        self.pos[:b].copy_(self.h_pos[:b], non_blocking=nb)
+        self.slots[:b].copy_(self.h_slots[:b], non_blocking=nb)
+        self.lens[:b].copy_(self.h_lens[:b], non_blocking=nb)
+        self.bt[:n].copy_(self.h_bt[:n], non_blocking=nb)
+        self.num_valid.copy_(self.h_nv, non_blocking=nb)
+        self.h2d_bytes_per_step = b * (4 + 4 + 8 + 4) + n * self.max_pages * 4 + 4
+        return b
+
+    def replay(self, bucket: int, n: int) -> torch.Tensor:
+        if bucket not in self.graphs:
+            self.capture(bucket)
+        self.graphs[bucket].replay()
+        self.replays += 1
+        out = self.outputs[bucket]
+        if self.sp:
+            return out                              # own rows of the bucket; caller slices by rank
+        return out[:n]
+
+    def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
+        """Engine hook (``Engine.graph_runner``): logits of the live rows."""
+        b = self.stage(ids, pos, slots, lens, [s.gpu_pages for s in rows])
+        return self.replay(b, len(rows))
+
+
+def compare_eager_vs_graph(runner: DecodeGraphRunner, ids, pos, slots, lens, page_lists, atol=0.0, rtol=0.0):
+    """Run one staged step eagerly and through the graph; returns (max_abs_diff, equal_bits).  The eager
+    run comes second so that the KV rows written by both are identical."""
+    b = runner.stage(ids, pos, slots, lens, page_lists)
+    n = len(ids)
+    g = runner.replay(b, n).clone()
+    torch.cuda.synchronize(runner.dev)
+    e = runner._forward(b)
+    e = e if runner.sp else e[:n]
+    torch.cuda.synchronize(runner.dev)
+    diff = (g.float() - e.float()).abs().max().item()
+    return diff, bool(torch.equal(g, e))
