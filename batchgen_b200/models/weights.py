@@ -263,3 +263,62 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
             lw.w13, lw.w2 = mlp_pair(f"{p}.mlp", cfg.intermediate_size, H)
         mw.layers.append(lw)
     return mw
+
+
+def checkpoint_tensor_specs(cfg: ModelConfig):
+    """(name, shape, init kind, layer) of every checkpoint tensor of an MLA model, in file order
+    (layer -1 = embeddings / final norm / lm_head)."""
+    H = cfg.hidden_size
+    out = [("model.embed_tokens.weight", (cfg.vocab_size, H), "normal", -1),
+           ("model.norm.weight", (H,), "norm", -1)]
+    if not cfg.tie_word_embeddings:
+        out.append(("lm_head.weight", (cfg.vocab_size, H), "normal", -1))
+    for l in range(cfg.num_layers):
+        p = f"model.layers.{l}"
+        a = f"{p}.self_attn"
+        out += [(f"{p}.input_layernorm.weight", (H,), "norm", l),
+                (f"{p}.post_attention_layernorm.weight", (H,), "norm", l)]
+        if cfg.is_mla:
+            out += [(f"{a}.q_a_proj.weight", (cfg.q_lora_rank, H), "normal", l),
+                    (f"{a}.kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_head_dim, H), "normal", l),
+                    (f"{a}.q_a_layernorm.weight", (cfg.q_lora_rank,), "norm", l),
+                    (f"{a}.kv_a_layernorm.weight", (cfg.kv_lora_rank,), "norm", l),
+                    (f"{a}.q_b_proj.weight", (cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank), "normal", l),
+                    (f"{a}.kv_b_proj.weight", (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank),
+                     "normal", l),
+                    (f"{a}.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim), "normal", l)]
+            if cfg.layer_has_indexer(l):
+                Hi, Di = cfg.index_n_heads, cfg.index_head_dim
+                out += [(f"{a}.indexer.wq_b.weight", (Hi * Di, cfg.q_lora_rank), "normal", l),
+                        (f"{a}.indexer.wk.weight", (Di, H), "normal", l),
+                        (f"{a}.indexer.k_norm.weight", (Di,), "norm", l),
+                        (f"{a}.indexer.k_norm.bias", (Di,), "bias", l),
+                        (f"{a}.indexer.weights_proj.weight", (Hi, H), "normal", l)]
+        else:
+            D, Hq, Hkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+            out += [(f"{a}.q_proj.weight", (Hq * D, H), "normal", l), (f"{a}.k_proj.weight", (Hkv * D, H), "normal", l),
+                    (f"{a}.v_proj.weight", (Hkv * D, H), "normal", l), (f"{a}.o_proj.weight", (H, Hq * D), "normal", l)]
+            if cfg.attention_sinks:
+                out.append((f"{a}.sinks", (Hq,), "bias", l))
+
+        def mlp(prefix, inter, hid):
+            return [(f"{prefix}.gate_proj.weight", (inter, hid), "normal", l),
+                    (f"{prefix}.up_proj.weight", (inter, hid), "normal", l),
+                    (f"{prefix}.down_proj.weight", (hid, inter), "normal", l)]
+
+        if cfg.is_moe_layer(l):
+            E, I, eh = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden
+            out.append((f"{p}.mlp.gate.weight", (E, H), "normal", l))
+            if cfg.scoring_func == "sigmoid":
+                out.append((f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias", l))
+            if cfg.moe_latent_size:
+                out += [(f"{p}.mlp.latent_down_proj.weight", (eh, H), "normal", l),
+                        (f"{p}.mlp.latent_up_proj.weight", (H, eh), "normal", l),
+                        (f"{p}.mlp.latent_norm.weight", (eh,), "norm", l)]
+            for e in range(E):
+                out += mlp(f"{p}.mlp.experts.{e}", I, eh)
+            if cfg.n_shared_experts:
+                out += mlp(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+        else:
+            out += mlp(f"{p}.mlp", cfg.intermediate_size, H)
+    return out

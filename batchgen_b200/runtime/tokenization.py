@@ -1,0 +1,141 @@
+"""Tokenisers and chat templating for the batch front end.
+
+No tokenizer files ship with this repository (and none can be downloaded), so three tokenisers are
+built in, selected by name or path:
+
+* ``ids``   — prompts are token ids (a JSON list, or a string of space separated integers); used by
+              the synthetic benchmarks.
+* ``bytes`` — UTF-8 bytes shifted past the special ids; works for any vocabulary >= 259.
+* a path    — a local Hugging Face ``tokenizer.json`` directory, loaded with ``transformers`` when present
+              (the reference bundles per-model ``tokenizer.json`` files and Jinja chat templates:
+              batchgen/tokenization.py:30-244, batchgen/config/fast_tokenizer.py:88,306-330).
+
+``apply_chat_template`` renders ``messages`` with the tokenizer's own Jinja template when it has one and
+with a plain role-tagged fallback otherwise; ``split_reasoning`` separates ``<think>...</think>`` content
+for ``--parse-thinking``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+
+class IdTokenizer:
+    name = "ids"
+
+    def __init__(self, vocab_size: int, bos: int = 0, eos: int = 1):
+        self.vocab_size, self.bos_token_id, self.eos_token_id = vocab_size, bos, eos
+
+    def encode(self, text: Union[str, Sequence[int]]) -> List[int]:
+        if isinstance(text, str):
+            ids = [int(t) for t in text.replace(",", " ").split()] if text.strip() else []
+        else:
+            ids = [int(t) for t in text]
+        for t in ids:
+            if not 0 <= t < self.vocab_size:
+                raise ValueError(f"token id {t} outside the vocabulary [0, {self.vocab_size})")
+        return ids
+
+    def decode(self, ids: Sequence[int], skip_special_tokens: bool = True) -> str:
+        return " ".join(str(int(i)) for i in ids)
+
+    def apply_chat_template(self, messages: List[Dict], **kw) -> List[int]:
+        out: List[int] = []
+        for m in messages:
+            c = m.get("content", "")
+            out += self.encode(c if isinstance(c, (str, list)) else str(c))
+        return out
+
+
+class ByteTokenizer:
+    name = "bytes"
+    OFFSET = 3
+
+    def __init__(self, vocab_size: int, bos: int = 0, eos: int = 1):
+        if vocab_size < 256 + self.OFFSET:
+            raise ValueError("the byte tokenizer needs a vocabulary of at least 259")
+        self.vocab_size, self.bos_token_id, self.eos_token_id = vocab_size, bos, eos
+
+    def encode(self, text: str) -> List[int]:
+        return [b + self.OFFSET for b in text.encode("utf-8")]
+
+    def decode(self, ids: Sequence[int], skip_special_tokens: bool = True) -> str:
+        bs = bytes(i - self.OFFSET for i in ids if self.OFFSET <= i < 256 + self.OFFSET)
+        return bs.decode("utf-8", errors="replace")
+
+    def apply_chat_template(self, messages: List[Dict], add_generation_prompt: bool = True, **kw) -> List[int]:
+        return self.encode(render_fallback_template(messages, add_generation_prompt))
+
+
+class HFTokenizer:
+    def __init__(self, path: str):
+        from transformers import AutoTokenizer
+        self.tok = AutoTokenizer.from_pretrained(path, local_files_only=True)
+        self.name = path
+        self.vocab_size = len(self.tok)
+        self.bos_token_id, self.eos_token_id = self.tok.bos_token_id, self.tok.eos_token_id
+
+    def encode(self, text: str) -> List[int]:
+        return self.tok.encode(text, add_special_tokens=False)
+
+    def decode(self, ids: Sequence[int], skip_special_tokens: bool = True) -> str:
+        return self.tok.decode(list(ids), skip_special_tokens=skip_special_tokens)
+
+    def apply_chat_template(self, messages: List[Dict], add_generation_prompt: bool = True, **kw) -> List[int]:
+        if getattr(self.tok, "chat_template", None):
+            return self.tok.apply_chat_template(messages, tokenize=True, add_generation_prompt=add_generation_prompt, **kw)
+        return self.encode(render_fallback_template(messages, add_generation_prompt))
+
+
+def render_fallback_template(messages: List[Dict], add_generation_prompt: bool = True) -> str:
+    parts = []
+    for m in messages:
+        role, content = m.get("role", "user"), m.get("content", "")
+        if isinstance(content, list):            # OpenAI content parts: keep the text ones
+            content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+        parts.append(f"<|{role}|>\n{content}\n")
+    if add_generation_prompt:
+        parts.append("<|assistant|>\n")
+    return "".join(parts)
+
+
+def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1):
+    if spec in ("ids", "", None):
+        return IdTokenizer(vocab_size, bos, eos)
+    if spec == "bytes":
+        return ByteTokenizer(vocab_size, bos, eos)
+    if os.path.isdir(spec):
+        return HFTokenizer(spec)
+    raise ValueError(f"unknown tokenizer {spec!r}: use 'ids', 'bytes' or a local tokenizer directory")
+
+
+_THINK = re.compile(r"<think>(.*?)</think>", re.S)
+
+
+def split_reasoning(text: str) -> Tuple[Optional[str], str]:
+    """-> (reasoning_content or None, content) for ``<think>...</think>`` style outputs."""
+    m = _THINK.search(text)
+    if not m:
+        if "</think>" in text:                      # template opened the block in the prompt
+            r, c = text.split("</think>", 1)
+            return r.strip(), c.strip()
+        return None, text
+    return m.group(1).strip(), (text[: m.start()] + text[m.end():]).strip()
+
+
+_TOOL = re.compile(r"<tool_call>\s*(\{.*?\})\s*</tool_call>", re.S)
+
+
+def parse_tool_calls(text: str) -> Tuple[List[Dict], str]:
+    """Extract ``<tool_call>{json}</tool_call>`` blocks -> (OpenAI tool_calls list, remaining text)."""
+    calls = []
+    for i, m in enumerate(_TOOL.finditer(text)):
+        try:
+            obj = json.loads(m.group(1))
+        except ValueError:
+            continue
+        calls.append({"id": f"call_{i}", "type": "function",
+                      "function": {"name": obj.get("name", ""), "arguments": json.dumps(obj.get("arguments", {}))}})
+    return calls, _TOOL.sub("", text).strip()

@@ -59,6 +59,7 @@ def main() -> int:
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="run the decode step eagerly instead of as a CUDA graph")
     ap.add_argument("--profile-ops", default="", help="write a per-operator CUDA-event breakdown to this file")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -155,11 +156,51 @@ def main() -> int:
         else:
             sampling_ops.greedy(model.forward(ids, meta, kv), out_tok)
 
-    def decode_step_device():
+    # ---- the decode step as one CUDA graph (whole model forward); sampling and token exchange follow it
+    runner = None
+    graph_kernels = 0
+    if not args.no_graph:
+        from batchgen_b200.runtime.graphs import DecodeGraphRunner
+        runner = DecodeGraphRunner(model, kv, max_batch=B, max_pages_per_seq=bt_h.shape[1], num_buckets=1,
+                                   max_bucket=B, sequence_parallel=fused)
+        pl = [bt_h[i, :n].tolist() for i, n in enumerate(pages_per_seq)]
+        runner.stage(ids_h.tolist(), pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl)
+        k0 = _ext.LAUNCHES["count"]
+        runner.capture(B)
+        graph_kernels = (_ext.LAUNCHES["count"] - k0) // 3      # two warm-up runs + the captured one
+
+    def sample_logits(logits):
+        if fused:
+            sampling_ops.greedy(logits, tok_loc)
+            dist.all_gather_into_tensor(out_tok, tok_loc)
+        else:
+            sampling_ops.greedy(logits, out_tok)
+
+    def decode_step_graph():
+        sample_logits(runner.replay(B, B))
+        _ext.LAUNCHES["count"] += graph_kernels
+
+    def decode_step_graph_e2e():
+        runner.stage(ids_p.tolist(), pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl)
+        sample_logits(runner.replay(B, B))
+        _ext.LAUNCHES["count"] += graph_kernels
+        tok_pinned.copy_(out_tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        ids_p.copy_(tok_pinned)
+
+    def decode_step_eager():
         meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
         run_model(d_ids, meta)
 
+    def decode_step_device():
+        if runner is not None:
+            decode_step_graph()
+        else:
+            decode_step_eager()
+
     def decode_step_e2e():
+        if runner is not None:
+            return decode_step_graph_e2e()
         a = ids_p.to(dev, non_blocking=True)
         b = bt_p.to(dev, non_blocking=True)
         c = pos_p.to(dev, non_blocking=True)
@@ -207,7 +248,7 @@ def main() -> int:
         from batchgen_b200.utils.timing import TimingStats
         model.timer = TimingStats()
         for _ in range(2):
-            decode_step_device()
+            decode_step_eager()
             model.timer.step_done()
         torch.cuda.synchronize()
         dsum = model.timer.summary()
@@ -221,6 +262,8 @@ def main() -> int:
             decode_step_e2e()
         ms_e = timed(decode_step_e2e, args.steps) / args.steps
         h2d = sum(t.numel() * t.element_size() for t in (ids_p, bt_p, pos_p, slot_p, len_p))
+        if runner is not None:
+            h2d = runner.h2d_bytes_per_step
         e2e = {"value": B * 1000.0 / ms_e, "unit": "decode tokens/s", "ms_per_step": ms_e,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": tok_pinned.numel() * 4}
 
@@ -281,7 +324,7 @@ def main() -> int:
                        "seq_len": int(sum(ctx) / len(ctx)), "prompt_lens": "U[512,4096]", "decoded_so_far": 512,
                        "parallelism": f"tp{world}+ep{world}",
                        "comm": ("fused-nvlink-kernels" if fused else "nccl") if world > 1 else "none",
-                       "distinct_expert_sets": sets, "moe_layers": n_moe,
+                       "distinct_expert_sets": sets, "moe_layers": n_moe, "cuda_graph": runner is not None,
                        "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",
                        "valid": not args.layers, "build_seconds": round(build_s, 1)},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "prefill": prefill,
