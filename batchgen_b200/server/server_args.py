@@ -1,0 +1,166 @@
+"""Server flags: one dataclass, one argparse builder, cross-field validation.
+
+Flag names follow the reference's (docs/server-flags.md; batchgen/server/server_args.py:168-322 dataclass,
+:325 parser, :791 validation) so that launch scripts carry over.  Flags that only make sense for the
+reference's multi-node / UCX / lane machinery are accepted where harmless and rejected with a clear
+message where they would silently do nothing (``--nnodes > 1``).
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import os
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+from ..config import EngineConfig, list_models
+
+
+@dataclass
+class ServerArgs:
+    # model / paths
+    model: str = "tiny-deepseek-v3"
+    cache_dir: str = ""
+    converted_ckpt_dir: str = ""
+    tokenizer: str = "ids"
+    # topology
+    world_size: int = 1
+    nnodes: int = 1
+    node_rank: int = 0
+    dist_init_addr: str = "127.0.0.1:29600"
+    attn_tp_size: int = 0                       # 0 = world_size (TP attention), 1 = data-parallel attention
+    device: str = "auto"                        # auto | cuda | cpu
+    # memory
+    host_kv_cache_size: float = 0.0             # GB of pinned host KV (overflow tier)
+    kv_dtype: str = "bf16"
+    gpu_memory_frac: float = 0.9
+    num_gpu_pages: int = 0
+    max_model_len: int = -1
+    page_size: int = 64
+    # scheduling
+    initial_gpu_page_buffer: int = 32
+    extension_gpu_page_buffer: int = 4
+    decision_frequency_pages: int = 2
+    host_kv_watermark: int = 70
+    host_kv_chunk_size: int = 8192
+    adaptive_chunk: bool = False
+    max_decode_batch: int = 512
+    max_prefill_tokens: int = 131072
+    # offload
+    enable_ep_with_offloading: bool = False
+    ep_offloading_ratio: float = 0.0
+    # graphs
+    enable_cuda_graph: bool = True
+    disable_cuda_graphs: bool = False
+    cuda_graph_max_bucket_size: int = 128
+    cuda_graph_num_buckets: int = 16
+    # prefix
+    enable_prefix_cache: bool = False
+    # comm
+    moe_comm: str = "fused"
+    # output
+    parse_thinking: bool = False
+    parse_tool_call: bool = False
+    detokenization_include_special_tokens: bool = False
+    storage_path: str = "./batchgen_storage"
+    incremental_output_dir: str = ""
+    # watchdogs
+    watchdog_timeout: float = 600.0
+    decode_step_timeout: float = 120.0
+    startup_timeout: float = 1800.0
+    watchdog_test_stuck_time: float = 0.0       # fault injection (host side): worker sleeps this long once
+    # logging
+    log_dir: str = ""
+    log_level: str = "info"
+    # http
+    host: str = "127.0.0.1"
+    port: int = 8000
+    # capacity
+    max_intake_capacity: int = 1_000_000
+    scheduling_slots: int = 4096
+    # cluster
+    cluster_fail_fast: bool = True
+    seed: int = 0
+
+    def engine_config(self) -> EngineConfig:
+        tp = self.attn_tp_size or self.world_size
+        return EngineConfig(
+            page_size=self.page_size, kv_dtype=self.kv_dtype, gpu_memory_frac=self.gpu_memory_frac,
+            num_gpu_pages=self.num_gpu_pages, host_kv_cache_size_gb=self.host_kv_cache_size,
+            host_kv_chunk_size=self.host_kv_chunk_size, host_kv_watermark=self.host_kv_watermark,
+            initial_gpu_page_buffer=self.initial_gpu_page_buffer,
+            extension_gpu_page_buffer=self.extension_gpu_page_buffer,
+            decision_frequency_pages=self.decision_frequency_pages, max_prefill_tokens=self.max_prefill_tokens,
+            max_decode_batch=self.max_decode_batch, max_model_len=self.max_model_len,
+            enable_cuda_graph=self.enable_cuda_graph and not self.disable_cuda_graphs,
+            cuda_graph_max_bucket_size=self.cuda_graph_max_bucket_size,
+            cuda_graph_num_buckets=self.cuda_graph_num_buckets, enable_prefix_cache=self.enable_prefix_cache,
+            adaptive_chunk=self.adaptive_chunk, world_size=self.world_size, attn_tp_size=tp,
+            ep_size=self.world_size, moe_comm=self.moe_comm, expert_offload_ratio=self.ep_offloading_ratio,
+            seed=self.seed)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser("batchgen_b200 server", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    for f in dataclasses.fields(ServerArgs):
+        flag = "--" + f.name.replace("_", "-")
+        if f.type in ("bool", bool):
+            p.add_argument(flag, action="store_true", default=f.default)
+            if f.default:
+                p.add_argument("--no-" + f.name.replace("_", "-"), dest=f.name, action="store_false")
+        else:
+            typ = {"int": int, "float": float, "str": str}.get(f.type if isinstance(f.type, str) else f.type.__name__, str)
+            p.add_argument(flag, type=typ, default=f.default)
+    return p
+
+
+class ServerArgsError(ValueError):
+    pass
+
+
+def validate_server_args(a: ServerArgs) -> ServerArgs:
+    if a.nnodes != 1 or a.node_rank != 0:
+        raise ServerArgsError("this engine serves one NVSwitch node: --nnodes must be 1 (the reference's multi-node "
+                              "restart coordinator and UCX weight store have no counterpart here)")
+    if a.world_size < 1 or a.world_size > 8 or a.world_size & (a.world_size - 1):
+        raise ServerArgsError("--world-size must be 1, 2, 4 or 8")
+    if a.attn_tp_size not in (0, 1, a.world_size):
+        raise ServerArgsError("--attn-tp-size must be 1 (DP attention) or the world size")
+    if not 0.1 <= a.gpu_memory_frac <= 0.98:
+        raise ServerArgsError("--gpu-memory-frac must be within [0.1, 0.98]")
+    if a.host_kv_cache_size < 0:
+        raise ServerArgsError("--host-kv-cache-size must be >= 0 GB")
+    if a.kv_dtype not in ("bf16", "fp8", "fp32"):
+        raise ServerArgsError("--kv-dtype must be bf16, fp8 or fp32")
+    if a.page_size <= 0 or a.page_size & (a.page_size - 1):
+        raise ServerArgsError("--page-size must be a power of two")
+    if a.extension_gpu_page_buffer < a.decision_frequency_pages:
+        raise ServerArgsError("--extension-gpu-page-buffer must cover a decision interval "
+                              "(>= --decision-frequency-pages)")
+    if not 0 <= a.host_kv_watermark <= 100:
+        raise ServerArgsError("--host-kv-watermark is a percentage")
+    if a.enable_ep_with_offloading and not 0 < a.ep_offloading_ratio <= 1:
+        raise ServerArgsError("--enable-ep-with-offloading needs --ep-offloading-ratio in (0, 1]")
+    if not a.enable_ep_with_offloading and a.ep_offloading_ratio:
+        raise ServerArgsError("--ep-offloading-ratio needs --enable-ep-with-offloading")
+    if a.moe_comm not in ("fused", "nccl"):
+        raise ServerArgsError("--moe-comm must be fused or nccl")
+    if a.cuda_graph_max_bucket_size <= 0 or a.cuda_graph_num_buckets <= 0:
+        raise ServerArgsError("CUDA graph bucket settings must be positive")
+    if a.log_level not in ("debug", "info", "warning", "error"):
+        raise ServerArgsError("--log-level must be debug, info, warning or error")
+    if a.max_intake_capacity <= 0 or a.scheduling_slots <= 0:
+        raise ServerArgsError("capacities must be positive")
+    if a.converted_ckpt_dir and not os.path.isdir(a.converted_ckpt_dir):
+        raise ServerArgsError(f"--converted-ckpt-dir {a.converted_ckpt_dir} is not a directory")
+    try:
+        from ..config import get_model_config
+        get_model_config(a.model)
+    except KeyError:
+        raise ServerArgsError(f"unknown --model {a.model!r}; known: {list_models()}")
+    return a
+
+
+def prepare_server_args(argv: Optional[List[str]] = None) -> ServerArgs:
+    ns = build_parser().parse_args(argv)
+    return validate_server_args(ServerArgs(**vars(ns)))

@@ -1,0 +1,204 @@
+"""Worker process: one per GPU (or one CPU process), running the engine's scheduling loop and talking to
+the server over two ``multiprocessing`` queues.
+
+Messages down (server -> rank 0):  ``{"type": "admit", "entries": [{slot, batch_id, request_id, prompt_ids,
+sampling}]}``, ``{"type": "cancel", "batch_id"}``, ``{"type": "shutdown"}``.
+Messages up (rank 0 -> server): ``{"type": "ready" | "deployment_capacity" | "completion" | "worker_fatal" |
+"heartbeat", ...}``.
+
+All ranks run in lock step: rank 0 drains its queue once per loop iteration and broadcasts the message list
+(``broadcast_object_list``; a one-element list when idle doubles as the heartbeat), every rank applies the
+same admissions and takes the same engine step.  Ordered teardown: the engine stops at a step boundary, the
+process group is destroyed, queues are flushed.
+
+Reference parity: batchgen/server_worker_main_loop.py:574-1083 (entry, NCCL env, rendezvous, warm-up,
+readiness, main loop with rank-0 poll + broadcast, fatal sideband, teardown), batchgen/server/process_utils.py:38
+(``die_with_parent``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import queue as queue_mod
+import signal
+import time
+import traceback
+from typing import Any, Dict, List, Optional
+
+
+def die_with_parent() -> None:
+    """Ask the kernel to SIGKILL this process when its parent dies (Linux PR_SET_PDEATHSIG)."""
+    try:
+        libc = ctypes.CDLL("libc.so.6", use_errno=True)
+        libc.prctl(1, signal.SIGKILL, 0, 0, 0)
+    except OSError:
+        pass
+
+
+def setup_nccl_env() -> None:
+    """NCCL settings for a single NVSwitch node.  NVLS stays at NCCL's default here (the reference turns it
+    off because multicast registration made graph capture slow, server_worker_main_loop.py:553-571)."""
+    os.environ.setdefault("TORCH_NCCL_ENABLE_MONITORING", "0")
+    os.environ.setdefault("NCCL_SOCKET_IFNAME", "lo")
+    if os.environ.get("BATCHGEN_DETERMINISTIC") == "1":
+        os.environ.setdefault("NCCL_ALGO", "allreduce:tree")
+
+
+def build_engine(args, rank: int, world: int, device: str):
+    import torch
+
+    from ..config import get_model_config
+    from ..models import build_model
+    from ..models.weights import ParallelLayout
+    from ..runtime.engine import Engine
+    from ..runtime.planner import size_kv_pool
+
+    cfg = get_model_config(args.model)
+    ecfg = args.engine_config()
+    ecfg.device = device
+    dtype = "bf16" if device.startswith("cuda") else "fp32"
+    loader = None
+    if args.converted_ckpt_dir:
+        from ..ckpt.converter import ConvertedCheckpoint
+        loader = ConvertedCheckpoint(args.converted_ckpt_dir).loader()
+    comm = None
+    layout = ParallelLayout()
+    if world > 1:
+        from ..parallel.comm import NcclComm
+        comm = NcclComm()
+        layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    model = build_model(cfg, device=device, dtype=dtype, seed=args.seed, layout=layout, comm=comm, loader=loader,
+                        max_positions=max(8192, args.max_model_len if args.max_model_len > 0 else 8192))
+    pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
+    eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages)
+    if device.startswith("cuda") and ecfg.enable_cuda_graph:
+        from ..runtime.graphs import DecodeGraphRunner
+        max_pages = -(-eng.kv_token_budget // ecfg.page_size)
+        eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=ecfg.max_decode_batch,
+                                             max_pages_per_seq=min(max_pages, pages),
+                                             num_buckets=ecfg.cuda_graph_num_buckets,
+                                             max_bucket=ecfg.cuda_graph_max_bucket_size)
+    return cfg, eng
+
+
+def worker_main(rank: int, world: int, args, request_queue, response_queue, ready_event, shutdown_flag,
+                feed_counter=None) -> None:
+    """Entry point of a worker process (also callable in-process for tests)."""
+    die_with_parent()
+    from ..utils import eventlog
+    log = eventlog.configure_process(f"worker{rank}", args.log_dir or None, args.log_level,
+                                     flight_recorder=bool(args.log_dir))
+    import torch
+    import torch.distributed as dist
+
+    def up(msg: Dict[str, Any]) -> None:
+        if rank == 0:
+            response_queue.put(msg)
+
+    try:
+        use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
+        device = f"cuda:{rank}" if use_cuda else "cpu"
+        if use_cuda:
+            torch.cuda.set_device(rank)
+        if world > 1:
+            setup_nccl_env()
+            dist.init_process_group("nccl" if use_cuda else "gloo", init_method=f"tcp://{args.dist_init_addr}",
+                                    rank=rank, world_size=world)
+            t = torch.ones(1, device=device)
+            dist.all_reduce(t)                        # warm-up: the first collective builds the communicators
+        from ..runtime.sequence import SamplingParams
+        cfg, eng = build_engine(args, rank, world, device)
+        log.info("worker.ready", rank=rank, device=device, gpu_pages=eng.kv.num_pages,
+                 host_pages=eng.host_kv.num_pages if eng.host_kv else 0)
+        up({"type": "deployment_capacity", "gpu_pages": eng.kv.num_pages, "page_size": eng.buf.page_size,
+            "kv_token_budget": eng.kv_token_budget, "max_decode_batch": eng.ecfg.max_decode_batch,
+            "model": cfg.name, "vocab_size": cfg.vocab_size})
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            ready_event.set()
+
+        by_idx: Dict[int, Dict[str, Any]] = {}
+        cancelled = set()
+
+        def on_complete(seq) -> None:
+            meta = by_idx.pop(seq.global_idx, None)
+            if meta is None:
+                return
+            reason = "cancelled" if meta["batch_id"] in cancelled else seq.finish_reason
+            up({"type": "completion", "slot": meta["slot"], "batch_id": meta["batch_id"],
+                "request_id": meta["request_id"], "output_ids": list(seq.output_ids),
+                "prompt_tokens": len(seq.prompt_ids), "cached_tokens": seq.cached_prefix_tokens,
+                "finish_reason": reason})
+
+        eng.on_complete = on_complete
+        if feed_counter is not None:
+            eng.step_hook = lambda phase: feed_counter.__setattr__("value", feed_counter.value + 1)
+        stuck = float(args.watchdog_test_stuck_time or 0.0)
+        last_beat = time.monotonic()
+        running = True
+        while running:
+            msgs: List[Dict[str, Any]] = []
+            if rank == 0:
+                try:
+                    block = not eng.has_work()
+                    m = request_queue.get(timeout=0.2) if block else request_queue.get_nowait()
+                    msgs.append(m)
+                    while len(msgs) < 64:
+                        msgs.append(request_queue.get_nowait())
+                except queue_mod.Empty:
+                    pass
+                if shutdown_flag.is_set():
+                    msgs.append({"type": "shutdown"})
+            if world > 1:
+                box = [msgs]
+                dist.broadcast_object_list(box, src=0)
+                msgs = box[0]
+            for m in msgs:
+                kind = m.get("type")
+                if kind == "shutdown":
+                    running = False
+                elif kind == "cancel":
+                    cancelled.add(m["batch_id"])
+                    for s in list(eng.seqs.values()):
+                        if s.batch_id == m["batch_id"] and s.status.name != "COMPLETED":
+                            s.params.max_new_tokens = max(1, s.num_decoded)   # finishes at the next boundary
+                elif kind == "admit":
+                    for e in m["entries"]:
+                        try:
+                            sp = SamplingParams(**e["sampling"])
+                            s = eng.add_request(e["prompt_ids"], sp, custom_id=e["request_id"], batch_id=e["batch_id"])
+                            by_idx[s.global_idx] = {"slot": e["slot"], "batch_id": e["batch_id"],
+                                                    "request_id": e["request_id"]}
+                        except Exception as ex:  # noqa: BLE001  (bad request: report, keep serving)
+                            up({"type": "completion", "slot": e["slot"], "batch_id": e["batch_id"],
+                                "request_id": e["request_id"], "output_ids": [], "prompt_tokens": 0,
+                                "cached_tokens": 0, "finish_reason": f"error: {ex}"})
+            if not running:
+                break
+            if stuck > 0 and eng.has_work():
+                time.sleep(stuck)                      # host-side fault injection for the watchdog test
+                stuck = 0.0
+            if eng.has_work():
+                eng.step()
+                if feed_counter is not None:
+                    feed_counter.value += 1
+                # completed sequences are dropped so that the table does not grow without bound
+                for gi in [g for g, s in eng.seqs.items() if s.status.name == "COMPLETED"]:
+                    del eng.seqs[gi]
+            if rank == 0 and time.monotonic() - last_beat > 5.0:
+                last_beat = time.monotonic()
+                up({"type": "heartbeat", "ts": time.time(), "live": len(eng.seqs), "free_pages": eng.kv.alloc.num_free,
+                    "stats": eng.stats.summary()})
+        log.info("worker.shutdown", rank=rank)
+    except Exception as ex:  # noqa: BLE001
+        log.error("worker.fatal", rank=rank, error=str(ex), trace=traceback.format_exc()[-1500:])
+        response_queue.put({"type": "worker_fatal", "rank": rank, "error": f"{type(ex).__name__}: {ex}"})
+        raise
+    finally:
+        try:
+            if world > 1 and dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+        log.close()

@@ -1,0 +1,202 @@
+"""WorkerManager: owns the worker cohort (one process per GPU), its queues, its liveness and its restarts.
+
+``start()`` spawns the cohort (``multiprocessing`` *spawn* context, so CUDA is initialised only in the
+children), waits for rank 0's readiness event and starts a monitor thread that notices a dead worker within
+a poll period and fails the cohort fast: a lost rank takes the whole generation down (world size is fixed,
+as in the reference's cluster fail-fast, docs/server-flags.md:126-146), in-flight batches are failed with the
+reason through the lifecycle hooks, and the server keeps its storage.  ``restart_workers()`` replaces the
+cohort with a new generation (phases: P0 quiesce intake, P1 stop old cohort, P2 start new cohort and resume),
+the equivalent of ``POST /v1/workers/restart``.
+
+Reference parity: batchgen/server/worker_manager.py:177,668 (start), :1433 (restart), :1819-1980 (spawn),
+:2062-2250 (exit monitor), batchgen/server/restart_coordinator.py (epochs and phases; single node here, so
+the TCPStore control plane reduces to in-process state), batchgen/server/watchdog.py:19-197.
+"""
+from __future__ import annotations
+
+import multiprocessing as mp
+import threading
+import time
+from typing import Callable, Dict, List, Optional
+
+from .io_struct import WorkerStatus
+from .server_args import ServerArgs
+
+
+class WorkerStartError(RuntimeError):
+    pass
+
+
+class Watchdog(threading.Thread):
+    """Feed-counter watchdog: if the counter does not move for ``timeout`` seconds while ``armed()`` is true,
+    ``on_stall(elapsed)`` runs once per stall."""
+
+    def __init__(self, read_counter: Callable[[], int], timeout: float, on_stall: Callable[[float], None],
+                 armed: Callable[[], bool] = lambda: True, period: float = 0.25):
+        super().__init__(name="watchdog", daemon=True)
+        self.read, self.timeout, self.on_stall, self.armed, self.period = read_counter, timeout, on_stall, armed, period
+        self._stop = threading.Event()
+        self.stalls = 0
+
+    def run(self) -> None:
+        last, since, fired = self.read(), time.monotonic(), False
+        while not self._stop.wait(self.period):
+            cur = self.read()
+            now = time.monotonic()
+            if cur != last or not self.armed():
+                last, since, fired = cur, now, False
+            elif not fired and now - since > self.timeout:
+                fired = True
+                self.stalls += 1
+                self.on_stall(now - since)
+
+    def stop(self) -> None:
+        self._stop.set()
+
+
+class WorkerManager:
+    def __init__(self, args: ServerArgs, worker_target=None):
+        self.args = args
+        self.ctx = mp.get_context("spawn")
+        self.request_queue = self.ctx.Queue()
+        self.response_queue = self.ctx.Queue()
+        self.procs: List[mp.Process] = []
+        self.generation = 0
+        self.state = "stopped"
+        self.last_error: Optional[str] = None
+        self.capacity: Optional[Dict] = None
+        self._ready = self.ctx.Event()
+        self._shutdown = self.ctx.Event()
+        self.feed = self.ctx.Value("q", 0)
+        self._monitor: Optional[threading.Thread] = None
+        self._monitor_stop = threading.Event()
+        self._hooks: Dict[str, Callable] = {}
+        self._target = worker_target
+        self._lock = threading.RLock()
+        self.watchdog: Optional[Watchdog] = None
+        self.phase = "idle"
+
+    # ------------------------------------------------------------------ hooks
+    def set_lifecycle_hooks(self, **hooks: Callable) -> None:
+        """quiesce(), resume(), fail_in_flight(reason): called around restarts and on cohort loss."""
+        self._hooks.update(hooks)
+
+    def _hook(self, name: str, *a) -> None:
+        h = self._hooks.get(name)
+        if h is not None:
+            h(*a)
+
+    # ------------------------------------------------------------------ start / stop
+    def start(self, timeout: Optional[float] = None) -> None:
+        with self._lock:
+            if self.state in ("starting", "ready"):
+                return
+            from .worker import worker_main
+            target = self._target or worker_main
+            self.state = "starting"
+            self.generation += 1
+            self._ready.clear()
+            self._shutdown.clear()
+            self.last_error = None
+            W = self.args.world_size
+            self.procs = []
+            for r in range(W):
+                p = self.ctx.Process(target=target, name=f"bg-worker-{r}",
+                                     args=(r, W, self.args, self.request_queue, self.response_queue, self._ready,
+                                           self._shutdown, self.feed), daemon=True)
+                p.start()
+                self.procs.append(p)
+        deadline = time.monotonic() + (timeout or self.args.startup_timeout)
+        while not self._ready.wait(0.1):
+            dead = [p for p in self.procs if not p.is_alive()]
+            if dead:
+                self.last_error = f"worker {dead[0].name} exited with code {dead[0].exitcode} during start-up"
+                self._kill_all()
+                self.state = "failed"
+                raise WorkerStartError(self.last_error)
+            if time.monotonic() > deadline:
+                self.last_error = "workers did not become ready before --startup-timeout"
+                self._kill_all()
+                self.state = "failed"
+                raise WorkerStartError(self.last_error)
+        self.state = "ready"
+        self._monitor_stop.clear()
+        self._monitor = threading.Thread(target=self._monitor_loop, name="worker-monitor", daemon=True)
+        self._monitor.start()
+        if self.args.watchdog_timeout > 0:
+            self.watchdog = Watchdog(lambda: self.feed.value, self.args.watchdog_timeout, self._on_stall,
+                                     armed=lambda: self.state == "ready" and bool(self._hooks.get("has_work", lambda: False)()))
+            self.watchdog.start()
+
+    def _on_stall(self, elapsed: float) -> None:
+        self.last_error = f"watchdog: no engine step for {elapsed:.1f} s while work was pending"
+        self._fail_cohort(self.last_error)
+
+    def _monitor_loop(self) -> None:
+        while not self._monitor_stop.wait(0.2):
+            if self.state != "ready":
+                continue
+            dead = [p for p in self.procs if not p.is_alive()]
+            if dead:
+                self._fail_cohort(f"worker {dead[0].name} exited with code {dead[0].exitcode}")
+                return
+
+    def _fail_cohort(self, reason: str) -> None:
+        with self._lock:
+            if self.state != "ready":
+                return
+            self.state = "failed"
+            self.last_error = reason
+        self._kill_all()
+        self._hook("fail_in_flight", reason)
+
+    def _kill_all(self) -> None:
+        for p in self.procs:
+            if p.is_alive():
+                p.terminate()
+        for p in self.procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.kill()
+
+    def stop(self, timeout: float = 20.0) -> None:
+        with self._lock:
+            if self.state == "stopped":
+                return
+            self._monitor_stop.set()
+            if self.watchdog is not None:
+                self.watchdog.stop()
+                self.watchdog = None
+            self._shutdown.set()
+            try:
+                self.request_queue.put({"type": "shutdown"})
+            except Exception:  # noqa: BLE001
+                pass
+        for p in self.procs:
+            p.join(timeout=timeout)
+        self._kill_all()
+        self.procs = []
+        self.state = "stopped"
+
+    def restart_workers(self, reason: str = "requested") -> int:
+        """Replace the cohort; returns the new generation."""
+        self.phase = "P0"
+        self._hook("quiesce")
+        self.phase = "P1"
+        self._hook("fail_in_flight", f"workers restarting: {reason}")
+        self.stop()
+        # messages addressed to the old cohort must not reach the new one
+        self.request_queue = self.ctx.Queue()
+        self.response_queue = self.ctx.Queue()
+        self._hook("rebind_queues", self.request_queue, self.response_queue)
+        self.phase = "P2"
+        self.start()
+        self._hook("resume")
+        self.phase = "idle"
+        return self.generation
+
+    # ------------------------------------------------------------------ status
+    def status(self) -> WorkerStatus:
+        return WorkerStatus(state=self.state, generation=self.generation, world_size=self.args.world_size,
+                            pids=[p.pid for p in self.procs if p.pid], last_error=self.last_error,
+                            capacity=self.capacity)

@@ -1,0 +1,200 @@
+"""HTTP server end to end with a CPU worker process, plus the control-plane units."""
+import json
+import os
+import signal
+import time
+
+import pytest
+from fastapi.testclient import TestClient
+
+from batchgen_b200.server.http_server import create_app
+from batchgen_b200.server.pools import HIGH, IntakeFull, IntakePool, IntakeRequest, SchedulingPool
+from batchgen_b200.server.server_args import ServerArgs, ServerArgsError, prepare_server_args, validate_server_args
+from batchgen_b200.server.storage import StorageManager, StorageOwnershipError
+from batchgen_b200.server.io_struct import BatchObject
+
+
+def _args(tmp_path, **kw):
+    base = dict(model="tiny-deepseek-v3", device="cpu", tokenizer="bytes", page_size=16, num_gpu_pages=192,
+                initial_gpu_page_buffer=2, extension_gpu_page_buffer=1, decision_frequency_pages=1,
+                storage_path=str(tmp_path / "store"), startup_timeout=120.0, watchdog_timeout=0.0,
+                enable_prefix_cache=True, max_model_len=512)
+    base.update(kw)
+    return validate_server_args(ServerArgs(**base))
+
+
+def _lines(n, max_tokens=4):
+    return [{"custom_id": f"r{i}", "method": "POST", "url": "/v1/chat/completions",
+             "body": {"model": "tiny", "messages": [{"role": "user", "content": f"question number {i}"}],
+                      "max_tokens": max_tokens, "ignore_eos": True}} for i in range(n)]
+
+
+def _upload(c, lines):
+    data = ("\n".join(json.dumps(l) for l in lines) + "\n").encode()
+    r = c.post("/v1/files", files={"file": ("in.jsonl", data, "application/jsonl")}, data={"purpose": "batch"})
+    assert r.status_code == 200, r.text
+    return r.json()
+
+
+def _wait(c, bid, timeout=120):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        b = c.get(f"/v1/batches/{bid}").json()
+        if b["status"] in ("completed", "failed", "cancelled"):
+            return b
+        time.sleep(0.1)
+    raise AssertionError(f"batch stuck: {b}")
+
+
+@pytest.fixture(scope="module")
+def server(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("srv")
+    app = create_app(_args(tmp))
+    with TestClient(app) as c:
+        assert c.get("/health").status_code == 200, c.get("/health").text
+        yield c, app
+
+
+def test_batch_round_trip_and_api_surface(server):
+    c, app = server
+    assert c.get("/v1/models").json()["data"][0]["id"] == "tiny-deepseek-v3"
+    assert c.get("/v1/models/other").status_code == 404
+    f = _upload(c, _lines(6))
+    assert c.get(f"/v1/files/{f['id']}").json()["bytes"] == f["bytes"]
+    assert _upload(c, _lines(6))["id"] == f["id"]                       # sha256 de-duplication
+    r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions",
+                                    "max_decoding_length": 9})
+    assert r.status_code == 200, r.text
+    b = _wait(c, r.json()["id"])
+    assert b["status"] == "completed" and b["request_counts"] == {"total": 6, "completed": 6, "failed": 0}
+    out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+    assert sorted(o["custom_id"] for o in out) == [f"r{i}" for i in range(6)]
+    for o in out:
+        body = o["response"]["body"]
+        assert o["response"]["status_code"] == 200 and body["usage"]["completion_tokens"] == 4
+        assert body["choices"][0]["finish_reason"] == "length"
+    assert any(x["id"] == b["id"] for x in c.get("/v1/batches").json()["data"])
+    st = c.get("/v1/pool/status").json()
+    assert st["serving"] and st["scheduling_slots_used"] == 0
+    assert c.get("/v1/workers/status").json()["state"] == "ready"
+    assert c.post("/v1/inference").status_code == 410
+    assert c.get("/v1/batches/nope").status_code == 404 and c.get("/v1/files/nope/content").status_code == 404
+    assert c.post("/v1/batches", json={"input_file_id": "file-missing"}).status_code == 404
+
+
+def test_invalid_file_and_per_request_errors(server):
+    c, _ = server
+    r = c.post("/v1/files", files={"file": ("bad.jsonl", b"{not json\n", "application/jsonl")}, data={"purpose": "batch"})
+    assert r.status_code == 400
+    lines = _lines(2)
+    lines[1]["body"]["max_tokens"] = 100000            # exceeds the context budget -> error item, batch completes
+    f = _upload(c, lines)
+    b = _wait(c, c.post("/v1/batches", json={"input_file_id": f["id"]}).json()["id"])
+    assert b["status"] == "completed" and b["request_counts"] == {"total": 2, "completed": 1, "failed": 1}
+    out = {json.loads(l)["custom_id"]: json.loads(l) for l in
+           c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()}
+    assert out["r1"]["error"] is not None and out["r0"]["error"] is None
+
+
+def test_sessions_and_turns_reuse_context(server):
+    c, _ = server
+    s = c.post("/v1/sessions", json={}).json()
+    t1 = c.post("/v1/turns", json={"session_id": s["id"], "prompt": "a" * 40, "max_tokens": 3, "ignore_eos": True}).json()
+    t2 = c.post("/v1/turns", json={"session_id": s["id"], "prompt": "b" * 10, "max_tokens": 3, "ignore_eos": True}).json()
+    assert t1["turn_index"] == 0 and t2["turn_index"] == 1
+    assert t2["usage"]["prompt_tokens"] == 40 + 3 + 10
+    assert t2["usage"]["prompt_tokens_details"]["cached_tokens"] >= 32      # prefix pages of turn 1 re-used
+    assert c.get(f"/v1/sessions/{s['id']}").json()["turns"] == 2
+    assert c.post(f"/v1/sessions/{s['id']}/close").json()["status"] == "closed"
+    assert c.post("/v1/turns", json={"session_id": s["id"], "prompt": "x"}).status_code == 410
+
+
+def test_cancel_batch(server):
+    c, _ = server
+    f = _upload(c, _lines(3, max_tokens=200))
+    bid = c.post("/v1/batches", json={"input_file_id": f["id"]}).json()["id"]
+    time.sleep(0.3)
+    assert c.post(f"/v1/batches/{bid}/cancel").json()["status"] in ("cancelling", "cancelled", "completed")
+    b = _wait(c, bid)
+    assert b["status"] in ("cancelled", "completed")
+    assert b["request_counts"]["completed"] + b["request_counts"]["failed"] == 3
+
+
+def test_worker_restart_and_worker_loss_fail_fast(server):
+    c, app = server
+    gen0 = c.get("/v1/workers/status").json()["generation"]
+    r = c.post("/v1/workers/restart")
+    assert r.status_code == 200 and r.json()["generation"] == gen0 + 1
+    f = _upload(c, _lines(2))
+    assert _wait(c, c.post("/v1/batches", json={"input_file_id": f["id"]}).json()["id"])["status"] == "completed"
+    # host-side failure: the worker process dies between steps; the monitor fails the cohort and the batch
+    f = _upload(c, _lines(2, max_tokens=400))
+    bid = c.post("/v1/batches", json={"input_file_id": f["id"]}).json()["id"]
+    time.sleep(0.5)
+    os.kill(app.state.worker.procs[0].pid, signal.SIGKILL)
+    b = _wait(c, bid)
+    assert b["status"] == "failed" and b["errors"]["data"][0]["code"] == "worker_failure"
+    assert c.get("/health").status_code == 503
+    assert c.post("/v1/batches", json={"input_file_id": f["id"]}).status_code == 503
+    assert c.post("/v1/workers/restart").status_code == 200          # recovery: a new generation serves again
+    assert c.get("/health").status_code == 200
+
+
+# ---------------------------------------------------------------------- units
+def test_intake_pool_all_or_nothing_and_priority():
+    p = IntakePool(4)
+    mk = lambda b, i, pr=0: IntakeRequest(b, f"r{i}", [1], {}, pr)
+    p.submit_batch([mk("a", 0), mk("a", 1)])
+    with pytest.raises(IntakeFull):
+        p.submit_batch([mk("b", i) for i in range(3)])
+    assert len(p) == 2
+    p.submit_batch([mk("c", 0, HIGH)])
+    assert [r.batch_id for r in p.drain(2)] == ["c", "a"]
+    p.submit_batch([mk("d", 0)])
+    assert p.cancel_batch("a") == 1 and [r.batch_id for r in p.drain(10)] == ["d"]
+
+
+def test_scheduling_pool_slots_and_dedupe():
+    sp = SchedulingPool(2)
+    ip = IntakePool(10)
+    ip.submit_batch([IntakeRequest("b", f"r{i}", [1], {}) for i in range(3)])
+    sp.register_batch("b", 3)
+    got = sp.select_from_intake(ip)
+    assert len(got) == 2 and sp.free == 0 and len(ip) == 1
+    assert sp.record_request_result("b", "r0", True) == (True, False)
+    assert sp.record_request_result("b", "r0", True) == (False, False)     # replayed result: ignored
+    assert sp.free == 1
+    assert len(sp.select_from_intake(ip)) == 1
+    sp.record_request_result("b", "r1", False)
+    assert sp.record_request_result("b", "r2", True) == (True, True)
+    t = sp.trackers["b"]
+    assert (t.completed, t.failed) == (2, 1) and sp.free == 2
+
+
+def test_storage_ownership_and_orphans(tmp_path):
+    s = StorageManager(str(tmp_path))
+    s.acquire_ownership()
+    with pytest.raises(StorageOwnershipError):
+        StorageManager(str(tmp_path)).acquire_ownership()
+    b = BatchObject(status="in_progress", input_file_id="x")
+    s.save_batch(b)
+    s.append_output(b.id, {"custom_id": "r0"})
+    s.release_ownership()
+    s2 = StorageManager(str(tmp_path))
+    s2.acquire_ownership()
+    assert s2.fail_orphaned_batches() == [b.id]
+    got = s2.get_batch(b.id)
+    assert got.status == "failed" and got.errors.data[0].code == "server_restart"
+    assert json.loads(s2.read_file(got.output_file_id).decode())["custom_id"] == "r0"
+    s2.release_ownership()
+
+
+def test_server_args_validation(tmp_path):
+    a = prepare_server_args(["--model", "deepseek-r1", "--world-size", "8", "--host-kv-cache-size", "64",
+                             "--no-enable-cuda-graph", "--enable-prefix-cache"])
+    assert a.world_size == 8 and not a.enable_cuda_graph and a.enable_prefix_cache
+    assert a.engine_config().attn_tp_size == 8
+    for bad in (dict(world_size=3), dict(nnodes=2), dict(model="nope"), dict(kv_dtype="int4"),
+                dict(ep_offloading_ratio=0.5), dict(extension_gpu_page_buffer=1, decision_frequency_pages=2)):
+        with pytest.raises(ServerArgsError):
+            validate_server_args(ServerArgs(**bad))
