@@ -1,0 +1,99 @@
+// C ABI of the native engine (loaded from Python with ctypes: batchgen_b200/core/native.py).
+// The reference exposes the same objects through pybind11 (core/batchgen_Binding.cpp:616-1262).
+#include <cstring>
+#include <vector>
+
+#include "host_kv.h"
+#include "weight_ring.h"
+
+using namespace bgcore;
+
+extern "C" {
+
+// ------------------------------------------------------------------ weight ring
+// backend: 0 = host (memcpy), 1 = CUDA on `device`.  Returns nullptr if the CUDA backend is unusable.
+void* bgc_ring_create(int num_slots, unsigned long long slot_bytes, int backend, int device) {
+  std::unique_ptr<CopyBackend> be = backend == 1 ? make_cuda_backend(device) : make_host_backend();
+  if (!be) return nullptr;
+  return new WeightRing(num_slots, slot_bytes, std::move(be));
+}
+void bgc_ring_destroy(void* r) { delete static_cast<WeightRing*>(r); }
+
+// tensors of the module: host pointers + sizes; slot offsets are returned through `offsets`.
+int bgc_ring_register_module(void* r, int module, const void* const* ptrs, const unsigned long long* sizes, int n,
+                             unsigned long long* offsets) {
+  std::vector<TensorSpan> spans(n);
+  for (int i = 0; i < n; ++i) spans[i] = TensorSpan{ptrs[i], static_cast<size_t>(sizes[i]), 0};
+  if (!static_cast<WeightRing*>(r)->register_module(module, &spans)) return -1;
+  for (int i = 0; i < n; ++i) offsets[i] = spans[i].slot_offset;
+  return 0;
+}
+void bgc_ring_install_queue(void* r, const int* modules, int n) {
+  static_cast<WeightRing*>(r)->install_queue(std::vector<int>(modules, modules + n));
+}
+unsigned long long bgc_ring_begin_pass(void* r, int carry) { return static_cast<WeightRing*>(r)->begin_pass(carry != 0); }
+int bgc_ring_end_pass(void* r) { return static_cast<WeightRing*>(r)->end_pass() ? 0 : -1; }
+void bgc_ring_skip(void* r, const int* modules, int n) {
+  static_cast<WeightRing*>(r)->skip_modules(std::vector<int>(modules, modules + n));
+}
+void bgc_ring_abort(void* r) { static_cast<WeightRing*>(r)->abort_passes(); }
+void bgc_ring_start(void* r) { static_cast<WeightRing*>(r)->start_producer(); }
+void bgc_ring_stop(void* r) { static_cast<WeightRing*>(r)->stop_producer(); }
+void* bgc_ring_get(void* r, int module, int timeout_ms, int* slot_out) {
+  return static_cast<WeightRing*>(r)->get_weights(module, timeout_ms, slot_out);
+}
+void bgc_ring_release(void* r, int slot, void* stream) { static_cast<WeightRing*>(r)->release(slot, stream); }
+int bgc_ring_count_state(void* r, int state) { return static_cast<WeightRing*>(r)->count_state(state); }
+// out: modules_copied, modules_skipped, bytes_copied, get_calls, get_wait_us, stalls, copy_us
+void bgc_ring_stats(void* r, unsigned long long* out) {
+  RingStats s = static_cast<WeightRing*>(r)->stats();
+  out[0] = s.modules_copied; out[1] = s.modules_skipped; out[2] = s.bytes_copied; out[3] = s.get_calls;
+  out[4] = s.get_wait_us; out[5] = s.stalls; out[6] = static_cast<unsigned long long>(s.copy_seconds * 1e6);
+}
+
+// ------------------------------------------------------------------ host paged KV + prefix coordinator
+void* bgc_hostkv_create(unsigned long long num_pages, unsigned long long page_bytes, unsigned long long prefix_slots,
+                        int* fd_out) {
+  auto* h = new HostPagedKV();
+  int fd = h->create(num_pages, page_bytes, prefix_slots);
+  if (fd < 0) {
+    delete h;
+    return nullptr;
+  }
+  if (fd_out) *fd_out = fd;
+  return h;
+}
+void* bgc_hostkv_attach(int fd) {
+  auto* h = new HostPagedKV();
+  if (!h->attach(fd)) {
+    delete h;
+    return nullptr;
+  }
+  return h;
+}
+void bgc_hostkv_destroy(void* h) { delete static_cast<HostPagedKV*>(h); }
+int bgc_hostkv_alloc(void* h, int n, int* out) { return static_cast<HostPagedKV*>(h)->alloc(n, out) ? 0 : -1; }
+void bgc_hostkv_share(void* h, const int* pages, int n) { static_cast<HostPagedKV*>(h)->share(pages, n); }
+void bgc_hostkv_free(void* h, const int* pages, int n) { static_cast<HostPagedKV*>(h)->free_pages(pages, n); }
+int bgc_hostkv_refcount(void* h, int page) { return static_cast<HostPagedKV*>(h)->refcount(page); }
+unsigned long long bgc_hostkv_num_free(void* h) { return static_cast<HostPagedKV*>(h)->num_free(); }
+unsigned long long bgc_hostkv_num_pages(void* h) { return static_cast<HostPagedKV*>(h)->num_pages(); }
+void* bgc_hostkv_page_ptr(void* h, int page) { return static_cast<HostPagedKV*>(h)->page_ptr(page); }
+void* bgc_hostkv_base(void* h) { return static_cast<HostPagedKV*>(h)->base(); }
+unsigned long long bgc_hostkv_bytes(void* h) { return static_cast<HostPagedKV*>(h)->mapped_bytes(); }
+int bgc_hostkv_audit(void* h) { return static_cast<HostPagedKV*>(h)->audit(); }
+int bgc_prefix_commit(void* h, const unsigned char* keys, const int* pages, int n) {
+  return static_cast<HostPagedKV*>(h)->prefix_commit(keys, pages, n);
+}
+int bgc_prefix_lookup_attach(void* h, const unsigned char* keys, int n, int* pages_out) {
+  return static_cast<HostPagedKV*>(h)->prefix_lookup_attach(keys, n, pages_out);
+}
+int bgc_prefix_evict(void* h, int want) { return static_cast<HostPagedKV*>(h)->prefix_evict(want); }
+int bgc_prefix_clear(void* h) { return static_cast<HostPagedKV*>(h)->prefix_clear(); }
+void bgc_prefix_stats(void* h, unsigned long long* out) {
+  uint64_t s[4];
+  static_cast<HostPagedKV*>(h)->prefix_stats(s);
+  for (int i = 0; i < 4; ++i) out[i] = s[i];
+}
+
+}  // extern "C"

@@ -1,0 +1,306 @@
+"""ctypes front of the native engine (``batchgen_b200/_C/libbg_core.so``): weight ring, node-shared host
+paged KV with its prefix coordinator, KV page movers and the CPU decode-attention kernel.
+
+The library is C++ (``core/csrc``), built in-tree by ``batchgen_b200.build``.  Everything except the CUDA copy
+backend and the page movers works without a GPU, which is how these classes are tested.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import struct
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_PATH = Path(__file__).resolve().parent.parent / "_C" / "libbg_core.so"
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not _PATH.exists():
+            from .. import build
+            build.build_core()
+        L = ctypes.CDLL(str(_PATH))
+        L.bgc_ring_create.restype = ctypes.c_void_p
+        L.bgc_ring_get.restype = ctypes.c_void_p
+        L.bgc_ring_begin_pass.restype = ctypes.c_ulonglong
+        L.bgc_hostkv_create.restype = ctypes.c_void_p
+        L.bgc_hostkv_attach.restype = ctypes.c_void_p
+        L.bgc_hostkv_page_ptr.restype = ctypes.c_void_p
+        L.bgc_hostkv_base.restype = ctypes.c_void_p
+        L.bgc_hostkv_num_free.restype = ctypes.c_ulonglong
+        L.bgc_hostkv_num_pages.restype = ctypes.c_ulonglong
+        L.bgc_hostkv_bytes.restype = ctypes.c_ulonglong
+        L.bgc_mover_create.restype = ctypes.c_void_p
+        L.bgc_mover_submit.restype = ctypes.c_long
+        L.bgc_mover_bytes.restype = ctypes.c_ulonglong
+        _LIB = L
+    return _LIB
+
+
+SLOT_STATES = {"FREE": 0, "FILLING": 1, "PRESENT": 2, "LEASED": 3, "PENDING_RELEASE": 4}
+
+
+class WeightRing:
+    """Ring of device weight slots fed from host memory by a native producer thread.
+
+    ``modules`` maps a module key (e.g. ``routed_expert_5_17``) to its host tensors; ``get(key)`` blocks until
+    the module is resident and returns tensors viewing the slot; ``release(key)`` hands the slot back."""
+
+    def __init__(self, num_slots: int, slot_bytes: int, device: str = "cpu"):
+        self.L = lib()
+        self.device = torch.device(device)
+        backend = 1 if self.device.type == "cuda" else 0
+        self.h = ctypes.c_void_p(self.L.bgc_ring_create(num_slots, ctypes.c_ulonglong(slot_bytes), backend,
+                                                        self.device.index or 0))
+        if not self.h:
+            raise RuntimeError("could not create the weight ring (CUDA backend unavailable?)")
+        self.slot_bytes = slot_bytes
+        self.ids: Dict[str, int] = {}
+        self.layout: Dict[int, List[Tuple[str, torch.dtype, Tuple[int, ...], int]]] = {}
+        self._host_refs: Dict[int, List[torch.Tensor]] = {}
+        self._leases: Dict[str, int] = {}
+
+    def register(self, key: str, tensors: Dict[str, torch.Tensor]) -> None:
+        mid = self.ids.setdefault(key, len(self.ids))
+        names = list(tensors)
+        ts = [tensors[n].contiguous() for n in names]
+        for t in ts:
+            assert t.device.type == "cpu", "streamed weights live in host memory"
+        n = len(ts)
+        ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+        sizes = (ctypes.c_ulonglong * n)(*[t.numel() * t.element_size() for t in ts])
+        offs = (ctypes.c_ulonglong * n)()
+        if self.L.bgc_ring_register_module(self.h, mid, ptrs, sizes, n, offs) != 0:
+            raise ValueError(f"module {key} does not fit a slot of {self.slot_bytes} bytes")
+        self.layout[mid] = [(names[i], ts[i].dtype, tuple(ts[i].shape), int(offs[i])) for i in range(n)]
+        self._host_refs[mid] = ts
+
+    def install_queue(self, keys: Sequence[str]) -> None:
+        arr = (ctypes.c_int * len(keys))(*[self.ids[k] for k in keys])
+        self.L.bgc_ring_install_queue(self.h, arr, len(keys))
+
+    def begin_pass(self, carry: bool = False) -> int:
+        return int(self.L.bgc_ring_begin_pass(self.h, int(carry)))
+
+    def end_pass(self) -> bool:
+        return self.L.bgc_ring_end_pass(self.h) == 0
+
+    def skip(self, keys: Sequence[str]) -> None:
+        arr = (ctypes.c_int * len(keys))(*[self.ids[k] for k in keys])
+        self.L.bgc_ring_skip(self.h, arr, len(keys))
+
+    def abort(self) -> None:
+        self.L.bgc_ring_abort(self.h)
+        self._leases.clear()
+
+    def start(self) -> None:
+        self.L.bgc_ring_start(self.h)
+
+    def stop(self) -> None:
+        self.L.bgc_ring_stop(self.h)
+
+    def get(self, key: str, timeout_ms: int = 300_000) -> Optional[Dict[str, torch.Tensor]]:
+        mid = self.ids[key]
+        slot = ctypes.c_int(-1)
+        p = self.L.bgc_ring_get(self.h, mid, timeout_ms, ctypes.byref(slot))
+        if not p:
+            return None
+        self._leases[key] = slot.value
+        out = {}
+        for name, dt, shape, off in self.layout[mid]:
+            numel = 1
+            for s in shape:
+                numel *= s
+            nbytes = numel * torch.empty(0, dtype=dt).element_size()
+            if self.device.type == "cuda":
+                out[name] = _cuda_view(p + off, nbytes, dt, shape, self.device)
+            else:
+                buf = (ctypes.c_char * nbytes).from_address(p + off)
+                out[name] = torch.frombuffer(buf, dtype=torch.uint8).view(dt).view(*shape)
+        return out
+
+    def release(self, key: str, stream: Optional[int] = None) -> None:
+        slot = self._leases.pop(key)
+        self.L.bgc_ring_release(self.h, slot, ctypes.c_void_p(stream or 0))
+
+    def count(self, state: str) -> int:
+        return self.L.bgc_ring_count_state(self.h, SLOT_STATES[state])
+
+    def stats(self) -> Dict[str, int]:
+        out = (ctypes.c_ulonglong * 7)()
+        self.L.bgc_ring_stats(self.h, out)
+        k = ["modules_copied", "modules_skipped", "bytes_copied", "get_calls", "get_wait_us", "stalls", "copy_us"]
+        return dict(zip(k, [int(v) for v in out]))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_ring_destroy(self.h)
+            self.h = None
+
+
+def _cuda_view(ptr: int, nbytes: int, dtype, shape, device) -> torch.Tensor:
+    """A torch tensor over raw device memory owned by the native ring (CUDA array interface)."""
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+    return torch.as_tensor(_Holder(), device=device).view(dtype).view(*shape)
+
+
+def prefix_keys(token_ids: Sequence[int], page_size: int, salt: bytes = b"") -> bytes:
+    """The 256-bit hash chain over full pages of ``token_ids`` (same chain as runtime.prefix_cache)."""
+    from ..runtime.prefix_cache import build_prefix_hash_chain
+    return b"".join(build_prefix_hash_chain(token_ids, page_size, salt))
+
+
+class HostPagedKV:
+    """Node-shared paged host KV region (memfd) with the prefix coordinator inside."""
+
+    def __init__(self, num_pages: int = 0, page_bytes: int = 0, prefix_slots: int = 0, fd: Optional[int] = None):
+        self.L = lib()
+        if fd is None:
+            out = ctypes.c_int(-1)
+            self.h = ctypes.c_void_p(self.L.bgc_hostkv_create(ctypes.c_ulonglong(num_pages), ctypes.c_ulonglong(page_bytes),
+                                                              ctypes.c_ulonglong(prefix_slots), ctypes.byref(out)))
+            self.fd = out.value
+        else:
+            self.h = ctypes.c_void_p(self.L.bgc_hostkv_attach(fd))
+            self.fd = fd
+        if not self.h:
+            raise RuntimeError("could not create / attach the host KV region")
+        self.page_bytes = page_bytes
+        self._pinned = False
+
+    @property
+    def num_pages(self) -> int:
+        return int(self.L.bgc_hostkv_num_pages(self.h))
+
+    @property
+    def num_free(self) -> int:
+        return int(self.L.bgc_hostkv_num_free(self.h))
+
+    def alloc(self, n: int) -> Optional[List[int]]:
+        out = (ctypes.c_int * n)()
+        return list(out) if self.L.bgc_hostkv_alloc(self.h, n, out) == 0 else None
+
+    def share(self, pages: Sequence[int]) -> None:
+        self.L.bgc_hostkv_share(self.h, (ctypes.c_int * len(pages))(*pages), len(pages))
+
+    def free(self, pages: Sequence[int]) -> None:
+        self.L.bgc_hostkv_free(self.h, (ctypes.c_int * len(pages))(*pages), len(pages))
+
+    def refcount(self, page: int) -> int:
+        return self.L.bgc_hostkv_refcount(self.h, page)
+
+    def page_ptr(self, page: int) -> int:
+        return int(self.L.bgc_hostkv_page_ptr(self.h, page))
+
+    def page_tensor(self, page: int, dtype=torch.uint8) -> torch.Tensor:
+        buf = (ctypes.c_char * self.page_bytes).from_address(self.page_ptr(page))
+        return torch.frombuffer(buf, dtype=torch.uint8).view(dtype)
+
+    def audit(self) -> int:
+        return self.L.bgc_hostkv_audit(self.h)
+
+    def pin(self) -> bool:
+        """Register the mapping with CUDA so that pages can be sources / targets of async copies."""
+        if not self._pinned and torch.cuda.is_available():
+            rc = self.L.bgc_pin_host(ctypes.c_void_p(self.L.bgc_hostkv_base(self.h)),
+                                     ctypes.c_size_t(self.L.bgc_hostkv_bytes(self.h)))
+            self._pinned = rc == 0
+        return self._pinned
+
+    # ---- prefix coordinator
+    def prefix_commit(self, token_ids: Sequence[int], pages: Sequence[int], page_size: int) -> int:
+        keys = prefix_keys(token_ids, page_size)
+        n = min(len(keys) // 32, len(pages))
+        return self.L.bgc_prefix_commit(self.h, keys, (ctypes.c_int * n)(*pages[:n]), n)
+
+    def prefix_lookup_attach(self, token_ids: Sequence[int], page_size: int) -> List[int]:
+        keys = prefix_keys(token_ids[: max(len(token_ids) - 1, 0)], page_size)
+        n = len(keys) // 32
+        out = (ctypes.c_int * max(n, 1))()
+        m = self.L.bgc_prefix_lookup_attach(self.h, keys, n, out)
+        return list(out)[:m]
+
+    def prefix_evict(self, want: int) -> int:
+        return self.L.bgc_prefix_evict(self.h, want)
+
+    def prefix_clear(self) -> int:
+        return self.L.bgc_prefix_clear(self.h)
+
+    def prefix_stats(self) -> Dict[str, int]:
+        out = (ctypes.c_ulonglong * 4)()
+        self.L.bgc_prefix_stats(self.h, out)
+        return dict(zip(["entries", "hits", "misses", "evicted"], [int(v) for v in out]))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_hostkv_destroy(self.h)
+            self.h = None
+
+
+class KVMover:
+    """Asynchronous page gather/scatter between pinned host memory and device memory (GPU only)."""
+
+    def __init__(self, device: int = 0, max_fragments: int = 4096, ring: int = 8):
+        self.L = lib()
+        self.h = ctypes.c_void_p(self.L.bgc_mover_create(device, max_fragments, ring))
+        if not self.h:
+            raise RuntimeError("KVMover needs a CUDA device")
+
+    def submit(self, src_ptrs: Sequence[int], dst_ptrs: Sequence[int], nbytes: int, use_kernel: bool = True,
+               after_stream: Optional[int] = None) -> int:
+        n = len(src_ptrs)
+        s = (ctypes.c_void_p * n)(*src_ptrs)
+        d = (ctypes.c_void_p * n)(*dst_ptrs)
+        t = self.L.bgc_mover_submit(self.h, s, d, n, ctypes.c_size_t(nbytes), int(use_kernel),
+                                    ctypes.c_void_p(after_stream or 0))
+        if t < 0:
+            raise RuntimeError(f"mover refused the request ({t})")
+        return int(t)
+
+    def done(self, task: int) -> bool:
+        return self.L.bgc_mover_done(self.h, ctypes.c_long(task)) == 1
+
+    def wait(self, task: int) -> None:
+        self.L.bgc_mover_wait(self.h, ctypes.c_long(task))
+
+    def stream_wait(self, task: int, stream: int) -> None:
+        self.L.bgc_mover_stream_wait(self.h, ctypes.c_long(task), ctypes.c_void_p(stream))
+
+    @property
+    def bytes_moved(self) -> int:
+        return int(self.L.bgc_mover_bytes(self.h))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_mover_destroy(self.h)
+            self.h = None
+
+
+def cpu_gqa_decode(q: torch.Tensor, k_pages: Sequence[Sequence[int]], v_pages: Sequence[Sequence[int]],
+                   lens: Sequence[int], page_size: int, num_kv_heads: int, scale: float, window: int = 0,
+                   threads: int = 8) -> torch.Tensor:
+    """q [B, Hq, D] fp32; k/v page *addresses* per sequence (bf16 pages [page, Hkv, D]) -> [B, Hq, D] fp32."""
+    B, Hq, D = q.shape
+    q = q.contiguous().float()
+    out = torch.empty_like(q)
+    mp = max(len(p) for p in k_pages)
+    kp = (ctypes.c_void_p * (B * mp))()
+    vp = (ctypes.c_void_p * (B * mp))()
+    for b in range(B):
+        for i, a in enumerate(k_pages[b]):
+            kp[b * mp + i] = a
+        for i, a in enumerate(v_pages[b]):
+            vp[b * mp + i] = a
+    ln = (ctypes.c_int * B)(*lens)
+    rc = lib().bgc_cpu_gqa_decode(ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(out.data_ptr()), kp, vp, ln, B, mp,
+                                  page_size, Hq, num_kv_heads, D, ctypes.c_float(scale), window, threads)
+    if rc != 0:
+        raise ValueError("bad GQA geometry")
+    return out

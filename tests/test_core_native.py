@@ -1,0 +1,166 @@
+"""Native engine on CPU: slot table (compiled standalone with g++), weight ring with the host copy backend,
+node-shared host KV + prefix coordinator across processes, CPU GQA decode kernel."""
+import multiprocessing as mp
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+
+from batchgen_b200.core import native
+from batchgen_b200.ops import ref
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "batchgen_b200", "core", "csrc")
+
+SLOT_TABLE_TEST = r'''
+#include "weight_slot_table.h"
+#include <cassert>
+#include <cstdio>
+using namespace bgcore;
+int main() {
+  WeightSlotTable t(2);
+  t.install_queue({10, 11, 12});
+  Production p;
+  assert(!t.next_production(&p));                 // no open pass
+  assert(t.begin_pass(true) == 1);
+  assert(t.next_production(&p) && p.module == 10 && p.slot == 0);
+  assert(t.next_production(&p) && p.module == 11 && p.slot == 1);
+  assert(!t.next_production(&p));                 // ring full
+  assert(t.acquire(10) == -1);                    // still FILLING
+  t.landed(0);
+  assert(t.acquire(11) == -2);                    // out of order
+  int s = t.acquire(10);
+  assert(s == 0 && t.slot(0).state == SlotState::LEASED);
+  t.release(0, true);
+  assert(t.slot(0).state == SlotState::PENDING_RELEASE && !t.next_production(&p));
+  t.reclaim(0);
+  assert(t.next_production(&p) && p.module == 12 && p.slot == 0);
+  // carry: the next pass may be produced as soon as this one is fully produced
+  assert(t.begin_pass(false) == 2 && t.begin_pass(false) == 0);   // at most two open
+  t.landed(1); assert(t.acquire(11) == 1); t.release(1, false);
+  assert(t.next_production(&p) && p.module == 10 && p.pass == 2);
+  t.landed(0); assert(t.acquire(12) == 0); t.release(0, false);
+  assert(t.end_pass());
+  // skips: module 11 is idle in pass 2
+  t.skip_modules({11});
+  t.landed(1); assert(t.acquire(10) == 1); t.release(1, false);
+  assert(t.next_production(&p) && p.module == 12);
+  assert(t.expected_module() == 12);
+  t.landed(p.slot); assert(t.acquire(12) == p.slot); t.release(p.slot, false);
+  assert(t.end_pass() && t.skipped_total() == 1);
+  // abort: in-flight slots return to FREE when they land
+  t.begin_pass(false);
+  assert(t.next_production(&p));
+  t.abort_all();
+  assert(t.slot(p.slot).state == SlotState::FILLING);
+  t.landed(p.slot);
+  assert(t.slot(p.slot).state == SlotState::FREE && t.count(SlotState::FREE) == 2 && t.open_passes() == 0);
+  std::puts("slot table ok");
+  return 0;
+}
+'''
+
+
+def test_weight_slot_table_standalone(tmp_path):
+    src = tmp_path / "t.cpp"
+    src.write_text(SLOT_TABLE_TEST)
+    exe = tmp_path / "t"
+    subprocess.run(["g++", "-std=c++17", "-O1", f"-I{CSRC}", str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, stdout=subprocess.PIPE, text=True).stdout
+    assert "slot table ok" in out
+
+
+def test_weight_ring_streams_modules_in_order_with_skips():
+    ring = native.WeightRing(num_slots=3, slot_bytes=1 << 16, device="cpu")
+    mods = {}
+    for i in range(8):
+        mods[f"expert_{i}"] = {"w13": torch.full((16, 32), float(i)), "w2": torch.full((8, 16), float(-i)).bfloat16()}
+        ring.register(f"expert_{i}", mods[f"expert_{i}"])
+    order = [f"expert_{i}" for i in range(8)]
+    ring.install_queue(order)
+    ring.start()
+    for p in range(3):
+        assert ring.begin_pass(carry=True) > 0
+        skipped = ["expert_3", "expert_6"] if p == 1 else []
+        ring.skip(skipped)
+        for k in order:
+            if k in skipped:
+                continue
+            w = ring.get(k, timeout_ms=5000)
+            assert w is not None, k
+            assert torch.equal(w["w13"], mods[k]["w13"]) and torch.equal(w["w2"], mods[k]["w2"])
+            ring.release(k)
+        assert ring.end_pass()
+    st = ring.stats()
+    assert st["modules_copied"] == 22 and st["modules_skipped"] == 2 and st["stalls"] == 0
+    # out-of-order request and stall bound
+    ring.begin_pass()
+    assert ring.get("expert_5", timeout_ms=50) is None
+    ring.abort()
+    ring.stop()
+    assert ring.count("LEASED") == 0
+    with pytest.raises(ValueError):
+        ring.register("huge", {"w": torch.zeros(1 << 20)})
+    ring.close()
+
+
+def _child_attach(fd, q):
+    kv = native.HostPagedKV(fd=fd, page_bytes=4096)
+    pages = kv.alloc(3)
+    kv.page_tensor(pages[0])[:4] = torch.tensor([9, 8, 7, 6], dtype=torch.uint8)
+    hit = kv.prefix_lookup_attach(list(range(64)) + [1], 16)
+    q.put((pages, hit, kv.num_free))
+
+
+def test_host_kv_is_shared_between_processes_and_prefix_coordinator_works():
+    kv = native.HostPagedKV(num_pages=32, page_bytes=4096, prefix_slots=256)
+    assert kv.num_free == 32 and kv.audit() == 0
+    mine = kv.alloc(4)
+    toks = list(range(64))
+    assert kv.prefix_commit(toks, mine, 16) == 4              # 4 full pages published
+    assert kv.prefix_commit(toks, mine, 16) == 0              # idempotent
+    assert all(kv.refcount(p) == 2 for p in mine)
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+    p = ctx.Process(target=_child_attach, args=(kv.fd, q))
+    p.start()
+    pages, hit, free_in_child = q.get(timeout=30)
+    p.join()
+    assert hit == mine and set(pages).isdisjoint(mine)
+    assert kv.page_tensor(pages[0])[:4].tolist() == [9, 8, 7, 6]       # the child's write is visible here
+    assert kv.num_free == 32 - 4 - 3 and all(kv.refcount(p) == 3 for p in mine)
+    kv.free(hit)                                                        # the child's references
+    kv.free(mine)                                                       # the owner's references: cache keeps them
+    assert kv.num_free == 32 - 4 - 3 and kv.prefix_evict(2) == 2        # LRU leaves first
+    assert kv.prefix_lookup_attach(toks + [0], 16) == mine[:2]
+    kv.free(mine[:2])
+    assert kv.prefix_clear() == 2 and kv.num_free == 32 - 3
+    kv.free(pages)
+    assert kv.num_free == 32 and kv.audit() == 0
+    assert kv.alloc(33) is None
+    st = kv.prefix_stats()
+    assert st["hits"] == 2 and st["evicted"] == 2
+    kv.close()
+
+
+def test_cpu_gqa_decode_matches_reference():
+    torch.manual_seed(0)
+    B, Hq, Hkv, D, S = 3, 8, 2, 64, 16
+    lens = [5, 40, 33]
+    q = torch.randn(B, Hq, D)
+    ks, vs, kp, vp = [], [], [], []
+    for L in lens:
+        n = (L + S - 1) // S
+        k = torch.randn(n, S, Hkv, D).bfloat16()
+        v = torch.randn(n, S, Hkv, D).bfloat16()
+        ks.append(k); vs.append(v)
+        kp.append([k[i].data_ptr() for i in range(n)]); vp.append([v[i].data_ptr() for i in range(n)])
+    for window in (0, 16):
+        out = native.cpu_gqa_decode(q, kp, vp, lens, S, Hkv, D ** -0.5, window=window, threads=4)
+        for b, L in enumerate(lens):
+            k = ks[b].reshape(-1, Hkv, D)[:L].float()
+            v = vs[b].reshape(-1, Hkv, D)[:L].float()
+            want = ref.gqa_attention(q[b:b + 1], k, v, D ** -0.5, q_start=L - 1, window=window)[0]
+            assert torch.allclose(out[b], want, atol=2e-4, rtol=1e-3), (b, window)
