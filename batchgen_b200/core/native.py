@@ -240,6 +240,9 @@ class HostPagedKV:
 
     def close(self) -> None:
         if self.h:
+            if self._pinned:                      # registrations do not go away with the mapping
+                self.L.bgc_unpin_host(ctypes.c_void_p(self.L.bgc_hostkv_base(self.h)))
+                self._pinned = False
             self.L.bgc_hostkv_destroy(self.h)
             self.h = None
 
