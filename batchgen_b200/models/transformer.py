@@ -173,15 +173,40 @@ class Transformer:
             return meta.dsa_selection.get(src_layer)
         T = x.shape[0]
         Hi, Di = cfg.index_n_heads, cfg.index_head_dim
-        k = ref.layernorm(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b)
-        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
         rd = cfg.qk_rope_head_dim
-        k = torch.cat([ref.apply_rope(k[:, :rd], cos, sin, cfg.rope_interleaved), k[:, rd:]], dim=-1)
-        kq, ks = ref.index_k_quant(k)
-        cache.write_index_keys(l, kq, ks, meta.slot_mapping)
+        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
+        gpu = x.is_cuda and x.dtype == torch.bfloat16
+        if gpu:
+            from ..ops import dsa as dsa_ops
+            gpu = dsa_ops.supported(Hi, Di, cache.page_size)
         q = linear(qn, lw.idx_wq).view(T, Hi, Di)
         q = torch.cat([ref.apply_rope(q[..., :rd], cos, sin, cfg.rope_interleaved), q[..., rd:]], dim=-1)
         gates = (x.float() @ lw.idx_head_w.float().t()) * (Hi ** -0.5) * (Di ** -0.5)
+        if gpu:
+            # fused LayerNorm + RoPE + e4m3 + paged store, FP8 scores on tcgen05, radix-select top-k
+            ck, cs = cache.index_keys(l)
+            dsa_ops.index_k_write(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b, meta.positions, self.rope.cos,
+                                  self.rope.sin, rd, cfg.rope_interleaved, meta.slot_mapping, ck, cs)
+            if meta.mode == "decode":
+                lengths, bt = meta.seqlens, meta.block_table
+                max_len = bt.shape[1] * cache.page_size
+            else:
+                row_seq = torch.zeros(T, dtype=torch.long, device=x.device)
+                lens = torch.zeros(T, dtype=torch.int32, device=x.device)
+                for i in range(len(meta.cu_seqlens) - 1):
+                    a, b = meta.cu_seqlens[i], meta.cu_seqlens[i + 1]
+                    row_seq[a:b] = i
+                    lens[a:b] = torch.arange(b - a, device=x.device, dtype=torch.int32) + meta.ctx_lens[i] + 1
+                lengths, bt = lens, meta.block_table[row_seq].contiguous()
+                max_len = max(meta.ctx_lens[i] + meta.cu_seqlens[i + 1] - meta.cu_seqlens[i]
+                              for i in range(len(meta.cu_seqlens) - 1))
+            out = dsa_ops.indexer_select(q.contiguous(), gates, ck, cs, bt, lengths, cfg.index_topk, max_len)
+            meta.dsa_selection[l] = out
+            return out
+        k = ref.layernorm(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b)
+        k = torch.cat([ref.apply_rope(k[:, :rd], cos, sin, cfg.rope_interleaved), k[:, rd:]], dim=-1)
+        kq, ks = ref.index_k_quant(k)
+        cache.write_index_keys(l, kq, ks, meta.slot_mapping)
         idx_keys, idx_scales = cache.index_keys(l)
         P, S, _ = idx_keys.shape
         sel_idx = torch.zeros(T, cfg.index_topk, dtype=torch.int32, device=x.device)

@@ -189,7 +189,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-constexpr uint32_t kFlagSpinLimit = 1u << 20;  // polls of >= 200 ns each: a second or so, then give up
+constexpr uint32_t kFlagSpinLimit = 1u << 23;  // polls of >= 200 ns each: ten seconds or so (host-side skew
+                                               // between ranks, e.g. graph capture, is seconds), then give up
 // Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded; and once any
 // kernel has raised the status word (a peer is late or gone) later waits give up at once, so a
 // broken step drains in milliseconds instead of one timeout per kernel.

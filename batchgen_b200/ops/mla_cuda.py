@@ -90,6 +90,13 @@ def mla_prefill_lib(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], 
 
 
 def sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora):
+    if _kernel_supports(q_abs, q_pe, cache, kv_lora):
+        from . import dsa
+        return dsa.sparse_mla_decode(q_abs.contiguous(), q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
+    return sparse_mla_decode_lib(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
+
+
+def sparse_mla_decode_lib(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora):
     B, H, _ = q_abs.shape
     P, S, D = cache.shape
     K = sel_idx.shape[1]

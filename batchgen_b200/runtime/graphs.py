@@ -130,6 +130,11 @@ class DecodeGraphRunner:
         torch.cuda.synchronize(self.dev)
         self.graphs[bucket] = g
         self.outputs[bucket] = out
+        if self.world > 1:
+            # ranks capture at different speeds; nobody replays (and waits on peers inside kernels) before
+            # every rank holds the graph
+            import torch.distributed as dist
+            dist.barrier()
         self.ledger.per_bucket[bucket] = max(0, free0 - torch.cuda.mem_get_info(self.dev)[0])
 
     def capture_all(self) -> None:

@@ -331,8 +331,18 @@ def main() -> int:
             "bct_projected_s": bct,
         }
         print(json.dumps(out))
+    sys.stdout.flush()
     if world > 1:
+        # graphs that captured collectives go first; a stuck teardown must not outlive the result
+        import gc
+        import threading
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        runner = None
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
     return 0
 
 

@@ -1,0 +1,150 @@
+"""DSA indexer kernels (index-key producer, tcgen05 FP8 scorer, radix-select top-k, sparse MLA) vs references."""
+import pytest
+import torch
+
+from batchgen_b200.ops import dsa, ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from batchgen_b200.ops import _ext
+    yield
+    torch.cuda.synchronize()
+    _ext.check_status()
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_index_k_write(interleaved):
+    T, P, S, D, rope = 200, 8, 64, 128, 64
+    k = torch.randn(T, D + 32, device=DEV).to(torch.bfloat16)[:, 32:]
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    pos = torch.randint(0, 4000, (T,), device=DEV, dtype=torch.int32)
+    inv = ref.rope_inv_freq(rope, 10000.0)
+    ang = torch.arange(4096, dtype=torch.float32).unsqueeze(-1) * inv
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    slots = torch.randperm(P * S, device=DEV)[:T].to(torch.int64)
+    slots[5] = -1
+    ck = torch.zeros(P, S, D, device=DEV, dtype=torch.float8_e4m3fn)
+    cs = torch.zeros(P, S, device=DEV)
+    dsa.index_k_write(k, w, b, pos, cos, sin, rope, interleaved, slots, ck, cs)
+    kn = ref.layernorm(k.float(), w.float(), b.float()).to(torch.bfloat16).float()
+    kr = torch.cat([ref.apply_rope(kn[:, :rope], cos[pos.long()], sin[pos.long()], interleaved), kn[:, rope:]], -1)
+    kr = kr.to(torch.bfloat16).float()
+    kq, ks = ref.index_k_quant(kr)
+    got = ck.view(-1, D).float() * cs.view(-1, 1)
+    valid = slots >= 0
+    want = kq.float() * ks.unsqueeze(-1)
+    err = (got[slots[valid]] - want[valid]).abs().max().item()
+    assert err <= 0.07 * want.abs().max().item(), err
+    assert torch.allclose(cs.view(-1)[slots[valid]], ks[valid], rtol=2e-2)
+    untouched = torch.ones(P * S, dtype=torch.bool, device=DEV)
+    untouched[slots[valid]] = False
+    assert (cs.view(-1)[untouched] == 0).all()
+
+
+def _keys(lens, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    S = 64
+    need = [(l + S - 1) // S for l in lens]
+    P = sum(need) + 2
+    kf = torch.randn(P, S, 128, device=DEV, generator=g)
+    kq = torch.empty(P, S, 128, device=DEV, dtype=torch.float8_e4m3fn)
+    ks = torch.empty(P, S, device=DEV)
+    q_, s_ = ref.index_k_quant(kf.view(-1, 128))
+    kq.view(-1, 128).copy_(q_)
+    ks.view(-1).copy_(s_)
+    perm = torch.randperm(P, device=DEV, generator=g).to(torch.int32)
+    bt = torch.zeros(len(lens), max(need) + 1, dtype=torch.int32, device=DEV)
+    o = 0
+    for i, n in enumerate(need):
+        bt[i, :n] = perm[o:o + n]
+        o += n
+    return kq, ks, bt
+
+
+def test_indexer_scores_and_topk_match_reference():
+    lens = [100, 2048, 2049, 5000, 64]
+    kq, ks, bt = _keys(lens)
+    B = len(lens)
+    q = torch.randn(B, 32, 128, device=DEV).to(torch.bfloat16)
+    gates = torch.rand(B, 32, device=DEV) * 0.1
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q8, g = dsa.quantize_index_q(q, gates)
+    scores = dsa.indexer_scores(q8, g, kq, ks, bt, ln, max(lens))
+    topk = 2048
+    idx, n = dsa.topk_select(scores, ln, topk)
+    for b, L in enumerate(lens):
+        npg = (L + 63) // 64
+        kb = kq[bt[b, :npg].long()].reshape(-1, 128)[:L]
+        sb = ks[bt[b, :npg].long()].reshape(-1)[:L]
+        want = ref.indexer_scores(q8[b].float() * (g[b] / gates[b].clamp_min(1e-12)).unsqueeze(-1), gates[b], kb, sb)
+        got = scores[b, :L]
+        assert (got - want).abs().max().item() <= 2e-3 * want.abs().max().item() + 1e-5
+        k_eff = min(L, topk)
+        assert int(n[b]) == k_eff
+        sel = idx[b, :k_eff].long()
+        assert sel.unique().numel() == k_eff and int(sel.max()) < L
+        # exactness against the scores the kernel itself produced
+        thr = torch.topk(got, k_eff)[0][-1]
+        assert (got[sel] >= thr).all()
+
+
+def test_topk_with_ties_and_negatives():
+    B, L, k = 3, 5000, 2048
+    s = torch.randn(B, L, device=DEV)
+    s[1] = 0.0                               # all equal
+    s[2, :3000] = -1.5
+    ln = torch.tensor([L, L, L], dtype=torch.int32, device=DEV)
+    idx, n = dsa.topk_select(s, ln, k)
+    for b in range(B):
+        sel = idx[b].long()
+        assert sel.unique().numel() == k
+        thr = torch.topk(s[b], k)[0][-1]
+        assert (s[b][sel] >= thr).all()
+
+
+def test_sparse_mla_decode_matches_reference():
+    lens = [3000, 500, 2500]
+    g = torch.Generator(device=DEV).manual_seed(1)
+    S = 64
+    need = [(l + S - 1) // S for l in lens]
+    P = sum(need) + 1
+    cache = (torch.randn(P, S, 576, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.zeros(3, max(need), dtype=torch.int32, device=DEV)
+    o = 0
+    for i, n in enumerate(need):
+        bt[i, :n] = torch.arange(o, o + n, dtype=torch.int32)
+        o += n
+    K = 2048
+    sel = torch.zeros(3, K, dtype=torch.int32, device=DEV)
+    sl = torch.zeros(3, dtype=torch.int32, device=DEV)
+    for b, L in enumerate(lens):
+        n = min(L, K)
+        sel[b, :n] = torch.randperm(L, device=DEV, generator=g)[:n].to(torch.int32)
+        sl[b] = n
+    q = torch.randn(3, 16, 576, device=DEV).to(torch.bfloat16)
+    qa, qp = q[..., :512].contiguous(), q[..., 512:].contiguous()
+    got = dsa.sparse_mla_decode(qa, qp, cache, bt, sel, sl, 0.1, 512)
+    want = ref.sparse_mla_decode(qa.float().cpu(), qp.float().cpu(), cache.float().cpu(), bt.cpu(), sel.cpu(), sl.cpu(),
+                                 0.1, 512)
+    assert (got.float().cpu() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
+def test_glm_shaped_model_gpu_runs_with_dsa_kernels():
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.runtime.engine import Engine
+    from batchgen_b200.runtime.sequence import SamplingParams
+    cfg = get_model_config("tiny-glm5", hidden_size=1024, q_lora_rank=512, kv_lora_rank=512, qk_nope_head_dim=128,
+                           qk_rope_head_dim=64, v_head_dim=128, num_heads=16, intermediate_size=2048,
+                           moe_intermediate_size=512, n_routed_experts=16, num_experts_per_tok=4, vocab_size=4096,
+                           index_n_heads=32, index_head_dim=128, index_topk=128, quant="fp8_block")
+    eng = Engine(build_model(cfg, "cuda", "bf16", seed=0), EngineConfig(page_size=64), num_gpu_pages=128)
+    gen = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=gen).tolist() for n in (300, 90, 200)]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    assert all(len(o) == 6 for o in outs)
