@@ -100,6 +100,13 @@ class DecodeGraphRunner:
         self.ledger = CaptureLedger()
         self.replays = 0
         self.h2d_bytes_per_step = 0
+        # sampled tokens of the last step (device) and the deferred host read-back ring (2 pinned slots)
+        self.tokens = torch.zeros(B, dtype=torch.int32, device=d)
+        self._tok_local = torch.zeros(max(1, B // mult), dtype=torch.int32, device=d)
+        self._ring = [torch.zeros(B, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._ring_ev = [torch.cuda.Event() if pin else None for _ in range(2)]
+        self._ring_n = [0, 0]
+        self._ring_next = 0
 
     # ------------------------------------------------------------------ capture
     def _meta(self, b: int) -> AttnMeta:
@@ -142,11 +149,12 @@ class DecodeGraphRunner:
             self.capture(b)
 
     # ------------------------------------------------------------------ replay
-    def stage(self, ids: Seq[int], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]]) -> int:
+    def stage(self, ids: Optional[Seq[int]], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]]) -> int:
         """Fill the pinned staging buffers and enqueue the host->device copies.  Returns the bucket."""
-        n = len(ids)
+        n = len(pos)
         b = self.bucketing.bucket_for(n)
-        self.h_ids[:n] = torch.as_tensor(ids, dtype=torch.int32)
+        if ids is not None:
+            self.h_ids[:n] = torch.as_tensor(ids, dtype=torch.int32)
         self.h_pos[:n] = torch.as_tensor(pos, dtype=torch.int32)
         self.h_slots[:n] = torch.as_tensor(slots, dtype=torch.int64)
         self.h_lens[:n] = torch.as_tensor(lens, dtype=torch.int32)
@@ -160,7 +168,10 @@ class DecodeGraphRunner:
             self.h_bt[i, :k] = torch.as_tensor(pl, dtype=torch.int32)
         self.h_nv[0] = n
         nb = True
-        self.ids[:b].copy_(self.h_ids[:b], non_blocking=nb)
+        if ids is not None:
+            self.ids[:b].copy_(self.h_ids[:b], non_blocking=nb)
+        else:                                        # feed the tokens sampled by the previous step (device side)
+            self.ids[:n].copy_(self.tokens[:n], non_blocking=nb)
         self.pos[:b].copy_(self.h_pos[:b], non_blocking=nb)
         self.slots[:b].copy_(self.h_slots[:b], non_blocking=nb)
         self.lens[:b].copy_(self.h_lens[:b], non_blocking=nb)
@@ -178,6 +189,37 @@ class DecodeGraphRunner:
         if self.sp:
             return out                              # own rows of the bucket; caller slices by rank
         return out[:n]
+
+    # ------------------------------------------------------------------ deferred token read-back
+    def decode_async(self, pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]],
+                     ids: Optional[Seq[int]] = None, sampler=None) -> int:
+        """One full decode step without a host synchronisation: stage inputs (host -> device), replay the
+        graph, sample on the device, start the device -> host copy of the tokens into a pinned ring slot.
+        ``ids is None`` feeds the tokens sampled by the previous step.  Returns a handle for ``read``.
+        The host sees a step's tokens one step late (the reference defers its token read-back the same
+        way: batchgen/worker/deferred_readback.py:57)."""
+        from ..ops import sampling as sampling_ops
+        n = len(pos)
+        b = self.stage(ids, pos, slots, lens, page_lists)
+        logits = self.replay(b, n)
+        if self.sp:
+            import torch.distributed as dist
+            tl = self._tok_local[: b // self.world]
+            (sampler or sampling_ops.greedy)(logits, tl)
+            dist.all_gather_into_tensor(self.tokens[:b], tl)
+        else:
+            (sampler or sampling_ops.greedy)(logits, self.tokens[:n])
+        slot = self._ring_next
+        self._ring_next ^= 1
+        self._ring[slot][:n].copy_(self.tokens[:n], non_blocking=True)
+        self._ring_ev[slot].record()
+        self._ring_n[slot] = n
+        return slot
+
+    def read(self, handle: int) -> torch.Tensor:
+        """Tokens of the step that returned ``handle`` (blocks until its copy has landed)."""
+        self._ring_ev[handle].synchronize()
+        return self._ring[handle][: self._ring_n[handle]]
 
     def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
         """Engine hook (``Engine.graph_runner``): logits of the live rows."""

@@ -180,13 +180,21 @@ def main() -> int:
         sample_logits(runner.replay(B, B))
         _ext.LAUNCHES["count"] += graph_kernels
 
+    pending = []
+
     def decode_step_graph_e2e():
-        runner.stage(ids_p.tolist(), pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl)
-        sample_logits(runner.replay(B, B))
+        # inputs from pinned host memory every step; tokens read back on the host every step, one step late
+        # (deferred read-back: the next step is fed the sampled tokens on the device, so the GPU never idles)
+        h = runner.decode_async(pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl,
+                                ids=ids_p.tolist() if not pending else None)
         _ext.LAUNCHES["count"] += graph_kernels
-        tok_pinned.copy_(out_tok, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        ids_p.copy_(tok_pinned)
+        pending.append(h)
+        if len(pending) > 1:
+            tok_pinned.copy_(runner.read(pending.pop(0)))
+
+    def e2e_drain():
+        while pending:
+            tok_pinned.copy_(runner.read(pending.pop(0)))
 
     def decode_step_eager():
         meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
@@ -260,7 +268,14 @@ def main() -> int:
     if not args.no_e2e:
         for _ in range(2):
             decode_step_e2e()
-        ms_e = timed(decode_step_e2e, args.steps) / args.steps
+        def e2e_steps_then_drain(k=[0]):
+            decode_step_e2e()
+            k[0] += 1
+            if k[0] % args.steps == 0 and runner is not None:
+                e2e_drain()                                    # the last step's tokens are read inside the timed region
+        if runner is not None:
+            e2e_drain()
+        ms_e = timed(e2e_steps_then_drain, args.steps) / args.steps
         h2d = sum(t.numel() * t.element_size() for t in (ids_p, bt_p, pos_p, slot_p, len_p))
         if runner is not None:
             h2d = runner.h2d_bytes_per_step
