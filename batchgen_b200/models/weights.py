@@ -160,7 +160,7 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
     expert bytes exceed HBM run with identical FLOPs and HBM traffic per layer)."""
     H = cfg.hidden_size
     dev = src.device
-    quant = cfg.quant if cfg.quant == "fp8_block" else "none"   # mxfp4 experts are handled by ops.mxfp4
+    quant = cfg.quant if cfg.quant == "fp8_block" else "none"   # mxfp4 applies to the routed experts only
     mw = ModelWeights()
     mw.embed = src.get("model.embed_tokens.weight", (cfg.vocab_size, H)).to(dtype)
     mw.final_norm = src.get("model.norm.weight", (H,), "norm").to(dtype)
@@ -241,7 +241,21 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                 e0, e1 = layout.expert_range(E)
                 w13s, w2s, s13, s2 = [], [], [], []
                 equant = "fp8_block" if quant == "fp8_block" else "none"
-                for e in range(e0, e1):
+                if cfg.quant == "mxfp4" and eh % 64 == 0 and I % 64 == 0:
+                    from ..ops import mxfp4
+                    for e in range(e0, e1):
+                        ep = f"{p}.mlp.experts.{e}"
+                        g = src.get(f"{ep}.gate_proj.weight", (I, eh))
+                        u = src.get(f"{ep}.up_proj.weight", (I, eh))
+                        d = src.get(f"{ep}.down_proj.weight", (eh, I))
+                        q13, sc13 = mxfp4.quantize(torch.cat([g, u], 0))
+                        q2, sc2 = mxfp4.quantize(d)
+                        w13s.append(q13); s13.append(sc13); w2s.append(q2); s2.append(sc2)
+                    lw.experts = ExpertWeights(w13=torch.stack(w13s), w2=torch.stack(w2s), w13_s=torch.stack(s13),
+                                               w2_s=torch.stack(s2), quant="mxfp4",
+                                               activation=cfg.activation).to_device_layout()
+                    expert_sets[key] = lw.experts
+                for e in (range(e0, e1) if key not in expert_sets else ()):
                     ep = f"{p}.mlp.experts.{e}"
                     g = src.get(f"{ep}.gate_proj.weight", (I, eh))
                     u = src.get(f"{ep}.up_proj.weight", (I, eh))
@@ -251,11 +265,12 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                     w13s.append(a.w); w2s.append(b.w)
                     if a.is_fp8:
                         s13.append(a.s); s2.append(b.s)
-                lw.experts = ExpertWeights(
-                    w13=torch.stack(w13s), w2=torch.stack(w2s),
-                    w13_s=torch.stack(s13) if s13 else None, w2_s=torch.stack(s2) if s2 else None,
-                    quant=equant, activation=cfg.activation).to_device_layout()
-                expert_sets[key] = lw.experts
+                if key not in expert_sets:
+                    lw.experts = ExpertWeights(
+                        w13=torch.stack(w13s), w2=torch.stack(w2s),
+                        w13_s=torch.stack(s13) if s13 else None, w2_s=torch.stack(s2) if s2 else None,
+                        quant=equant, activation=cfg.activation).to_device_layout()
+                    expert_sets[key] = lw.experts
             if cfg.n_shared_experts:
                 lw.w13, lw.w2 = mlp_pair(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H,
                                          shard=not layout.sequence_parallel)

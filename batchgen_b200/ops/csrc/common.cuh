@@ -189,6 +189,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Strong relaxed store: after one __threadfence_system() a run of these publishes to every peer without
+// paying a release fence per store.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 constexpr uint32_t kFlagSpinLimit = 1u << 23;  // polls of >= 200 ns each: ten seconds or so (host-side skew
                                                // between ranks, e.g. graph capture, is seconds), then give up
 // Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded; and once any

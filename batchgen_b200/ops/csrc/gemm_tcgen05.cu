@@ -30,6 +30,7 @@ constexpr int kThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr int kTmemCols = 256;  // two 128-column accumulators
 constexpr int kMaxGroups = 1024;
+constexpr int kEpiStageBytes = 16 * 128;   // per epilogue warp: 16 rows x 64 bf16, staging for peer-bound rows
 
 constexpr int KIND_FP8 = 0;
 constexpr int KIND_BF16 = 1;
@@ -132,6 +133,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* sA_tiles = smem;
   uint8_t* sB_tiles = smem + kStages * BM * BK_BYTES;
   SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + kStages * (BM + BN) * BK_BYTES);
+  uint8_t* epi_stage = smem + kStages * (BM + BN) * BK_BYTES + ((sizeof(SharedStorage) + 15) & ~size_t(15));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -375,7 +377,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (col0 + j + q < n_out) dst[j + q] = __float2bfloat16(silu(r[j + q]) * r[32 + j + q]);
             }
           }
-        } else {
+        } else if (p.peer_out[0] == nullptr) {
           const int col0 = t.nt * BN + half * 64;
           __nv_bfloat16* dst = out_base + out_row * p.ldd + col0;
 #pragma unroll
@@ -390,6 +392,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (col0 + j + q < p.N) dst[j + q] = __float2bfloat16(r[j + q]);
             }
           }
+        }
+      }
+      if (EPI != EPI_SILU_MUL && p.peer_out[0] != nullptr) {
+        // Rows bound for peer memory leave as whole 128-byte runs: the warp's 32 x 64 block goes through
+        // shared memory 16 rows at a time, then 8 lanes write one row's 128 bytes together (a row per
+        // thread would cross NVLink as 16-byte fragments).  Chunks are XOR-swizzled against bank conflicts.
+        const int col0 = t.nt * BN + half * 64;
+        uint8_t* stg = epi_stage + ew * kEpiStageBytes;
+        const unsigned long long my_dst =
+            store_ok ? reinterpret_cast<unsigned long long>(out_base + out_row * p.ldd + col0) : 0ull;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          if ((lane >> 4) == pass) {
+            const int lr = lane & 15;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(r[c * 8 + 2 * q], r[c * 8 + 2 * q + 1]);
+              *reinterpret_cast<uint4*>(stg + lr * 128 + ((c ^ (lr & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int lr = it * 4 + (lane >> 3);
+            const int c = lane & 7;
+            const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, pass * 16 + lr);
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + lr * 128 + ((c ^ (lr & 7)) << 4));
+            if (d != 0ull && col0 + c * 8 + 8 <= p.N) *(reinterpret_cast<uint4*>(d) + c) = v;
+          }
+          __syncwarp();
         }
       }
     }
@@ -409,7 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (prev == gridDim.x - 1) {
       *p.done_counter = 0u;
       __threadfence_system();
-      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.done_flag_index + p.my_rank, epoch);
+      for (int r = 0; r < p.world; ++r) st_relaxed_sys(p.peer_flags[r] + p.done_flag_index + p.my_rank, epoch);
     }
   }
 }
@@ -447,7 +481,9 @@ static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-static size_t gemm_smem_bytes() { return kStages * (BM + BN) * BK_BYTES + sizeof(SharedStorage) + 1024; }
+static size_t gemm_smem_bytes() {
+  return kStages * (BM + BN) * BK_BYTES + ((sizeof(SharedStorage) + 15) & ~size_t(15)) + kEpiWarps * kEpiStageBytes + 1024;
+}
 
 template <int KIND, int EPI>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_rows, int b_rows, int num_sms,
@@ -530,6 +566,8 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
     for (int i = 0; i < 8; ++i) { p.peer_out[i] = g_hooks.peer_out[i]; p.peer_flags[i] = g_hooks.peer_flags[i]; }
     g_hooks_set = false;
   }
+  // rows bound for peer memory are written in 16-byte pieces: whole pieces and aligned rows only
+  if (p.peer_out[0] != nullptr && (epi == EPI_SILU_MUL || (N % 8) != 0 || (ldd % 8) != 0)) return -1;
   const int b_rows = groups * N;
   if (kind == KIND_FP8 && epi == EPI_STORE) return launch_gemm<KIND_FP8, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
   if (kind == KIND_FP8 && epi == EPI_SILU_MUL) return launch_gemm<KIND_FP8, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);

@@ -5,7 +5,7 @@ extern "C" {
 
 // Paged absorbed MLA.  q_abs: [R*H, 512] bf16 contiguous; q_pe: [R*H, 64] bf16 with row stride
 // `qpe_stride` elements; cache: [n_pages*64, 576] bf16; work: device array of bg::mla::Work
-// (8 ints each); ncol: 16 or 32 = n_q * heads_per_group columns per CTA.  Split partials go to
+// (8 ints each); ncol: 16, 32 or 64 = n_q * heads_per_group columns per CTA.  Split partials go to
 // part_o / part_ml and are merged by bg_mla_merge.
 int bg_mla_attention(const void* q_abs, const void* q_pe, long long qpe_stride, long long q_rows, const void* cache,
                      long long cache_rows, const int* work, int n_work, const int* block_table, int bt_stride,
@@ -13,7 +13,7 @@ int bg_mla_attention(const void* q_abs, const void* q_pe, long long qpe_stride, 
                      int ncol, float scale, int* status, cudaStream_t stream) {
   using namespace bg::mla;
   if (n_work <= 0) return 0;
-  if ((ncol != 16 && ncol != 32) || heads_per_group <= 0 || ncol % heads_per_group != 0 || heads_per_group % 8 != 0 ||
+  if ((ncol != 16 && ncol != 32 && ncol != 64) || heads_per_group <= 0 || ncol % heads_per_group != 0 || heads_per_group % 8 != 0 ||
       H % heads_per_group != 0 || (qpe_stride * 2) % 16 != 0)
     return -1;
   CUtensorMap tkv, tq, tqpe;
@@ -26,7 +26,8 @@ int bg_mla_attention(const void* q_abs, const void* q_pe, long long qpe_stride, 
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml;
   p.H = H; p.heads_per_group = heads_per_group; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
   if (ncol == 16) return launch<16>(tkv, tq, tqpe, p, n_work, stream);
-  return launch<32>(tkv, tq, tqpe, p, n_work, stream);
+  if (ncol == 32) return launch<32>(tkv, tq, tqpe, p, n_work, stream);
+  return launch<64>(tkv, tq, tqpe, p, n_work, stream);
 }
 
 int bg_mla_merge(const float* part_o, const float* part_ml, const int* items, int n_items, void* out, int ncol, int H,

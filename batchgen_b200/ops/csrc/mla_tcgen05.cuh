@@ -2,21 +2,25 @@
 //
 // One kernel serves decode (one query per sequence), multi-query prefill chunks (causal) and
 // split-KV partials.  The latent cache row is 576 bf16 = 512 (normalised c_kv, also the value) +
-// 64 (roped k_pe).  Because MLA has a single KV head, the natural tensor-core shape puts the KV
-// *tokens* on the M axis and the (query, head) pairs on the N axis:
+// 64 (roped k_pe).  A CTA owns up to 64 (query, head) "columns" of one sequence and walks its KV range
+// in 64-token tiles (one page, loaded once by TMA as 9 swizzled 64-dim chunks that feed both GEMMs):
 //
-//   S^T[tok, col]  = KV[tok, 0:576] . Q[col, 0:576]          (A = KV tile, K-major;  B = Q, K-major)
-//   O^T[dim, col] += KV[tok, dim]^T . P^T[tok, col]          (A = same KV tile read MN-major;  B = P^T)
+//   S[col, tok]   = Q[col, 0:576] . KV[tok, 0:576]          (M = 64 columns, N = 64 tokens; both K-major)
+//   O[col, dim]  += P[col, tok] . KV[tok, dim]              (M = 64, N = 128 dims per MMA, B read N-major)
 //
-// so a 128-token KV tile is loaded once by TMA (9 swizzled 64-dim chunks) and feeds both GEMMs, with
-// N = 16 or 32 columns per CTA (e.g. the 16 heads of one tensor-parallel rank, or 32 of 128 heads).
-// S^T and the four 128-dim blocks of O^T live in TMEM.  The softmax runs over TMEM lanes (one
-// thread per token): column maxima are reduced with warp shuffles + shared memory, probabilities go
-// to shared memory as the B operand of the second GEMM, and O^T is rescaled in TMEM only when a
-// running maximum moves.
+// With the columns on the TMEM lanes the softmax needs no cross-thread reduction at all: one thread
+// owns one column, reads its 64 scores with tcgen05.ld, keeps the running maximum and sum in registers,
+// and writes its probabilities as one swizzled 128-byte row of the A operand of the second GEMM.  The
+// accumulator is rescaled (in TMEM, by the thread that owns the row) only when a maximum grew by more
+// than 2^8, so most tiles skip it.  An M = 64 accumulator occupies lanes 0..15 of each 32-lane TMEM
+// quadrant; O[:, 0:256] uses those and O[:, 256:512] the lanes 16..31 at the same columns.
+//
+// Pipeline: shared memory holds two to three tiles, so the MMA warp issues S of tile t+1 before the
+// second GEMM of tile t whenever that tile has landed; the tensor pipe then works on S(t+1) while the
+// softmax warps turn S(t) into P(t), and the loads of tiles t+2.. are already in flight.
 //
 // Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax /
-// correction / epilogue (thread = TMEM lane).  All waits are bounded (see common.cuh).
+// correction / epilogue.  All waits are bounded (see common.cuh).
 //
 // Replaces (by behaviour): FlashMLA flash_mla_with_kvcache as used by
 // batchgen/attention/mla/flashmla_backend.py:1202-1400, the flashinfer trtllm-gen MLA decode the
@@ -28,15 +32,24 @@
 namespace bg {
 namespace mla {
 
+// Optional per-role timestamps of CTA 0 (diagnostic builds only: -DBG_MLA_TRACE).
+#ifdef BG_MLA_TRACE
+__device__ long long g_mla_trace[3 * 32 * 8];
+#define BG_TR(role, t, ev)                                                                   \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && (t) < 32) g_mla_trace[((role) * 32 + (t)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define BG_TR(role, t, ev) do {} while (0)
+#endif
+
 constexpr int kLatent = 512;
 constexpr int kRope = 64;
 constexpr int kRow = kLatent + kRope;     // 576
 constexpr int kPage = 64;
-constexpr int kTile = 128;                // KV tokens per tile (= 2 pages)
-constexpr int kChunkBytes = kTile * 128;  // one 64-dim chunk of a tile: 128 rows x 128 B
+constexpr int kTile = 64;                 // KV tokens per tile (= 1 page)
+constexpr int kChunkBytes = kTile * 128;  // one 64-dim chunk of a tile: 64 rows x 128 B
 constexpr int kPairBytes = 2 * kChunkBytes;
-constexpr int kThreads = 192;
-constexpr int kRopeSlots = 2;
 
 struct Work {
   int q_row;      // first query row (rows are [R, H, *])
@@ -63,28 +76,35 @@ struct Params {
   int* status;
 };
 
+constexpr int kMRows = 64;                // MMA M: (query, head) columns per CTA, padded
+constexpr int kPBytes = kMRows * kTile * 2;   // P: 64 rows x 128 B, one swizzle atom
+
 template <int NCOL> struct Cfg {
-  static constexpr int kPairs = NCOL == 16 ? 5 : 4;
+  // shared memory: Q (9 chunks x NCOL rows x 128 B), a ring of 16 KB slots (two 64-dim chunks of one
+  // 64-token tile), a ring of 8 KB rope chunks, and P.  Q comes first: the M = 64 descriptor of a Q chunk
+  // with fewer than 64 rows reads on into the ring (rows that are never used), not past the allocation.
+  static constexpr int kPairs = NCOL == 64 ? 8 : 10;
+  static constexpr int kRopeSlots = NCOL == 16 ? 3 : 2;
   static constexpr int kQBytes = 9 * NCOL * 128;
-  static constexpr int kPBytes = NCOL * kTile * 2;
-  static constexpr int kTmemCols = NCOL == 16 ? 128 : 256;
-  static constexpr int kSmemTiles = kPairs * kPairBytes + kRopeSlots * kChunkBytes + kQBytes + kPBytes;
+  static constexpr int kSmemTiles = kQBytes + kPairs * kPairBytes + kRopeSlots * kChunkBytes + kPBytes;
 };
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;            // S: 2 x 64 columns; O: 256 columns x two lane halves
+constexpr int kMaxPairs = 10;
+constexpr int kMaxRopeSlots = 3;
 
 struct Shared {
   uint64_t q_full;
-  uint64_t pair_full[5];
-  uint64_t pair_empty[5];
-  uint64_t rope_full[kRopeSlots];
-  uint64_t rope_empty[kRopeSlots];
-  uint64_t s_full;
+  uint64_t pair_full[kMaxPairs];
+  uint64_t pair_empty[kMaxPairs];
+  uint64_t rope_full[kMaxRopeSlots];
+  uint64_t rope_empty[kMaxRopeSlots];
+  uint64_t s_full[2];
   uint64_t p_full;
   uint64_t o_done;
   uint32_t tmem_base;
   int abort_flag;
-  int limit[32];
-  float red[4][32];
-  float alpha_flag;
+  int limit[64];
 };
 
 // no-swizzle K-major descriptor (core matrices of 8 rows x 16 bytes)
@@ -107,9 +127,15 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t addr, uint32_t l
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major) {
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
-         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* v);
@@ -141,22 +167,38 @@ template <> __device__ __forceinline__ void tmem_st<32>(uint32_t taddr, const ui
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// Barrier over the 128 softmax threads that also ORs a flag, so that a bounded wait that expired in
-// one thread makes every thread leave the loop together (no thread is left alone at a barrier).
-__device__ __forceinline__ bool softmax_vote_any(bool v) {
+template <int N> __device__ __forceinline__ void softmax_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(N) : "memory");
+}
+// Barrier over the softmax threads that also ORs a flag, so that a bounded wait that expired in one
+// thread makes every thread leave the loop together (no thread is left alone at a barrier).
+template <int N> __device__ __forceinline__ bool softmax_vote_any(bool v) {
   uint32_t r;
   asm volatile(
       "{\n"
       ".reg .pred p, q;\n"
       "setp.ne.u32 q, %1, 0;\n"
-      "bar.red.or.pred p, 2, 128, q;\n"
+      "bar.red.or.pred p, 2, %2, q;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(r)
-      : "r"(static_cast<uint32_t>(v))
+      : "r"(static_cast<uint32_t>(v)), "n"(N)
       : "memory");
   return r != 0;
+}
+// Non-blocking probe of an mbarrier phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
 }
 
 template <int NCOL>
@@ -164,13 +206,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
            const __grid_constant__ CUtensorMap tm_qpe, Params p) {
   using C = Cfg<NCOL>;
+  constexpr int NS = 128;                                       // softmax threads
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* pair_buf = smem;                                     // kPairs x 32 KB
-  uint8_t* rope_buf = pair_buf + C::kPairs * kPairBytes;        // 2 x 16 KB
-  uint8_t* q_buf = rope_buf + kRopeSlots * kChunkBytes;         // 9 chunks x NCOL rows x 128 B
-  uint8_t* p_buf = q_buf + C::kQBytes;                          // P^T, no-swizzle K-major
-  Shared& ss = *reinterpret_cast<Shared*>(p_buf + C::kPBytes);
+  uint8_t* q_buf = smem;                                        // 9 chunks x NCOL rows x 128 B
+  uint8_t* pair_buf = q_buf + C::kQBytes;                       // kPairs x 16 KB
+  uint8_t* rope_buf = pair_buf + C::kPairs * kPairBytes;        // kRopeSlots x 8 KB
+  uint8_t* p_buf = rope_buf + C::kRopeSlots * kChunkBytes;      // P: 64 rows x 128 B, K-major swizzled
+  Shared& ss = *reinterpret_cast<Shared*>(p_buf + kPBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ss.abort_flag;
@@ -180,14 +223,15 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     mbar_init(&ss.q_full, 1);
     for (int i = 0; i < C::kPairs; ++i) { mbar_init(&ss.pair_full[i], 1); mbar_init(&ss.pair_empty[i], 1); }
-    for (int i = 0; i < kRopeSlots; ++i) { mbar_init(&ss.rope_full[i], 1); mbar_init(&ss.rope_empty[i], 1); }
-    mbar_init(&ss.s_full, 1);
-    mbar_init(&ss.p_full, 128);
+    for (int i = 0; i < C::kRopeSlots; ++i) { mbar_init(&ss.rope_full[i], 1); mbar_init(&ss.rope_empty[i], 1); }
+    mbar_init(&ss.s_full[0], 1);
+    mbar_init(&ss.s_full[1], 1);
+    mbar_init(&ss.p_full, NS);
     mbar_init(&ss.o_done, 1);
     ss.abort_flag = 0;
     mbar_fence_init();
   }
-  if (threadIdx.x < 32) {
+  if (threadIdx.x < 64) {
     int lim = 0;
     if (threadIdx.x < NCOL) {
       const int qi = threadIdx.x / hpg;
@@ -196,7 +240,7 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
     ss.limit[threadIdx.x] = lim;
   }
   if (warp == 1) {
-    tmem_alloc(&ss.tmem_base, C::kTmemCols);
+    tmem_alloc(&ss.tmem_base, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -207,7 +251,7 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
   int max_limit = 0;
 #pragma unroll 1
   for (int j = 0; j < NCOL; ++j) max_limit = max(max_limit, ss.limit[j]);
-  const int n_tiles_total = (max_limit + kTile - 1) / kTile;
+  const int n_tiles_total = (max_limit + kTile - 1) / kTile;      // = pages in use
   const int tile_begin = (int)(((long long)n_tiles_total * w.split) / w.n_splits);
   const int tile_end = (int)(((long long)n_tiles_total * (w.split + 1)) / w.n_splits);
   const int n_tiles = tile_end - tile_begin;
@@ -225,42 +269,33 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
         tma_load_2d(q_buf + 8 * NCOL * 128 + qi * hpg * 128, &tm_qpe, &ss.q_full, 0, grow);
       }
       const int* bt = p.block_table + (size_t)w.seq * p.bt_stride;
-      const int n_pages = (max_limit + kPage - 1) / kPage;
       bool ok = true;
       uint32_t pit = 0, rit = 0;
       for (int t = 0; ok && t < n_tiles; ++t) {
-        const int tile = tile_begin + t;
-        int page_id[2];
-        for (int h = 0; h < 2; ++h) {
-          const int pi = tile * 2 + h;
-          page_id[h] = bt[pi < n_pages ? pi : 0];   // past-the-end halves re-read a valid page; they are masked
-        }
+        const int row0 = bt[tile_begin + t] * kPage;          // a tile is one page
         for (int m = 0; m < 4 && ok; ++m, ++pit) {
           const int slot = pit % C::kPairs;
           if (!mbar_wait(&ss.pair_empty[slot], ((pit / C::kPairs) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
           mbar_expect_tx(&ss.pair_full[slot], kPairBytes);
           uint8_t* dst = pair_buf + slot * kPairBytes;
-          for (int cc = 0; cc < 2; ++cc)
-            for (int h = 0; h < 2; ++h)
-              tma_load_2d(dst + cc * kChunkBytes + h * (kPage * 128), &tm_kv, &ss.pair_full[slot], (2 * m + cc) * 64,
-                          page_id[h] * kPage);
+          tma_load_2d(dst, &tm_kv, &ss.pair_full[slot], (2 * m) * 64, row0);
+          tma_load_2d(dst + kChunkBytes, &tm_kv, &ss.pair_full[slot], (2 * m + 1) * 64, row0);
         }
         if (!ok) break;
-        const int rslot = rit % kRopeSlots;
-        if (!mbar_wait(&ss.rope_empty[rslot], ((rit / kRopeSlots) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
+        const int rslot = rit % C::kRopeSlots;
+        if (!mbar_wait(&ss.rope_empty[rslot], ((rit / C::kRopeSlots) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
         mbar_expect_tx(&ss.rope_full[rslot], kChunkBytes);
-        for (int h = 0; h < 2; ++h)
-          tma_load_2d(rope_buf + rslot * kChunkBytes + h * (kPage * 128), &tm_kv, &ss.rope_full[rslot], 8 * 64,
-                      page_id[h] * kPage);
+        tma_load_2d(rope_buf + rslot * kChunkBytes, &tm_kv, &ss.rope_full[rslot], 8 * 64, row0);
+        BG_TR(0, t, 0);
         ++rit;
       }
       if (ok) {  // drain: every armed slot is released by the MMA role
         const uint32_t np = pit < (uint32_t)C::kPairs ? pit : (uint32_t)C::kPairs;
         for (uint32_t j = pit - np; j < pit; ++j)
           if (!mbar_wait(&ss.pair_empty[j % C::kPairs], (j / C::kPairs) & 1, abort_flag, kTimeoutProducer)) break;
-        const uint32_t nr = rit < (uint32_t)kRopeSlots ? rit : (uint32_t)kRopeSlots;
+        const uint32_t nr = rit < (uint32_t)C::kRopeSlots ? rit : (uint32_t)C::kRopeSlots;
         for (uint32_t j = rit - nr; j < rit; ++j)
-          if (!mbar_wait(&ss.rope_empty[j % kRopeSlots], (j / kRopeSlots) & 1, abort_flag, kTimeoutProducer)) break;
+          if (!mbar_wait(&ss.rope_empty[j % C::kRopeSlots], (j / C::kRopeSlots) & 1, abort_flag, kTimeoutProducer)) break;
       } else {
         for (uint32_t i = 0; i < (1u << 16); ++i) __nanosleep(20);  // bounded grace period for copies in flight
       }
@@ -268,175 +303,194 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, NCOL, 0);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, NCOL, 1);
-      const uint32_t tm_s = tmem_base;
-      const uint32_t tm_o = tmem_base + NCOL;
+      constexpr uint32_t idesc_s = make_idesc_bf16(kMRows, kTile, 0, 0);     // Q . KV^T: both K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kMRows, 128, 0, 1);      // P . V: V read N-major (dims contiguous)
+      const uint32_t tm_o = tmem_base + 2 * kTile;
       bool ok = mbar_wait(&ss.q_full, 0, abort_flag, kTimeoutMma);
-      uint32_t pit = 0, rit = 0;
-      for (int t = 0; ok && t < n_tiles; ++t) {
-        const uint32_t pit0 = pit;
-        // ---- S^T = KV . Q^T over 9 chunks
-        for (int m = 0; m < 4 && ok; ++m, ++pit) {
+      // S(t) = Q . KV(t)^T over 9 chunks, into S buffer t & 1
+      auto issue_s = [&](int t) -> bool {
+        BG_TR(1, t, 0);
+        const uint32_t tm_s = tmem_base + (t & 1) * kTile;
+        for (int m = 0; m < 4; ++m) {
+          const uint32_t pit = (uint32_t)t * 4 + m;
           const int slot = pit % C::kPairs;
-          if (!mbar_wait(&ss.pair_full[slot], (pit / C::kPairs) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          if (!mbar_wait(&ss.pair_full[slot], (pit / C::kPairs) & 1, abort_flag, kTimeoutMma)) return false;
           tc_fence_after();
           for (int cc = 0; cc < 2; ++cc) {
-            const uint64_t adesc = make_smem_desc_sw128(smem_u32(pair_buf + slot * kPairBytes + cc * kChunkBytes));
-            const uint64_t bdesc = make_smem_desc_sw128(smem_u32(q_buf + (2 * m + cc) * NCOL * 128));
+            const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + (2 * m + cc) * NCOL * 128));
+            const uint64_t bdesc = make_smem_desc_sw128(smem_u32(pair_buf + slot * kPairBytes + cc * kChunkBytes));
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, (m | cc | k) ? 1u : 0u);
           }
         }
-        if (!ok) break;
-        {
-          const int rslot = rit % kRopeSlots;
-          if (!mbar_wait(&ss.rope_full[rslot], (rit / kRopeSlots) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t adesc = make_smem_desc_sw128(smem_u32(rope_buf + rslot * kChunkBytes));
-          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(q_buf + 8 * NCOL * 128));
-#pragma unroll
-          for (int k = 0; k < 4; ++k) mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, 1u);
-          tc_commit(&ss.rope_empty[rslot]);
-          tc_commit(&ss.s_full);
-          ++rit;
-        }
-        // ---- O^T += V^T . P^T
-        if (!mbar_wait(&ss.p_full, t & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+        const int rslot = t % C::kRopeSlots;
+        if (!mbar_wait(&ss.rope_full[rslot], (t / C::kRopeSlots) & 1, abort_flag, kTimeoutMma)) return false;
+        BG_TR(1, t, 1);
         tc_fence_after();
-        for (int m = 0; m < 4; ++m) {
-          const int slot = (pit0 + m) % C::kPairs;
-          const uint32_t a_base = smem_u32(pair_buf + slot * kPairBytes);
+        const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + 8 * NCOL * 128));
+        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(rope_buf + rslot * kChunkBytes));
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint64_t adesc = make_desc_mn_sw128(a_base + j * 2048, kChunkBytes, 1024);
-            const uint64_t bdesc = make_desc_nosw(smem_u32(p_buf + j * (NCOL / 8) * 256), 128, 256);
-            mma_f16(tm_o + m * NCOL, adesc, bdesc, idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, 1u);
+        tc_commit(&ss.rope_empty[rslot]);
+        tc_commit(&ss.s_full[t & 1]);
+        BG_TR(1, t, 2);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_s(0);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        // S of the next tile goes first when that tile has already landed (its rope chunk is the last
+        // load of a tile); otherwise the second GEMM of this tile is not held up behind the loads
+        bool next_issued = true;
+        if (t + 1 < n_tiles) {
+          next_issued = mbar_test(&ss.rope_full[(t + 1) % C::kRopeSlots], ((t + 1) / C::kRopeSlots) & 1);
+          if (next_issued && !issue_s(t + 1)) { ok = false; break; }
+        }
+        // ---- O += P . V : four 128-dim blocks; blocks 2, 3 accumulate in the upper lane halves
+        BG_TR(1, t, 3);
+        if (!mbar_wait(&ss.p_full, t & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+        BG_TR(1, t, 4);
+        tc_fence_after();
+        const uint64_t pdesc = make_smem_desc_sw128(smem_u32(p_buf));
+        for (int m = 0; m < 4; ++m) {
+          const int slot = ((uint32_t)t * 4 + m) % C::kPairs;
+          const uint32_t b_base = smem_u32(pair_buf + slot * kPairBytes);
+          const uint32_t d = tm_o + (m & 1) * 128 + ((m >> 1) ? (16u << 16) : 0u);
+#pragma unroll
+          for (int j = 0; j < kTile / 16; ++j) {
+            const uint64_t bdesc = make_desc_mn_sw128(b_base + j * 2048, kChunkBytes, 1024);
+            mma_f16(d, pdesc + 2 * j, bdesc, idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit(&ss.pair_empty[slot]);
         }
         tc_commit(&ss.o_done);
+        BG_TR(1, t, 5);
+        if (!next_issued && !issue_s(t + 1)) { ok = false; break; }
       }
     }
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
-    const int sw = warp - 2;                 // 0..3
-    const int quad = warp & 3;               // TMEM lane quadrant of this warp
-    const int row = quad * 32 + lane;        // token within the tile; later: dim within an O^T block
+    // Lanes 0..15 of warp q own columns 16q .. 16q+15: their S rows and O[:, 0:256].  Lanes 16..31 own
+    // O[:, 256:512] of the same columns (TMEM lanes 16..31 of the quadrant) and idle during the softmax.
+    const int quad = warp & 3;
+    const bool lo = lane < 16;
+    const int col = quad * 16 + (lane & 15);
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t tm_s = tmem_base + lane_addr;
-    const uint32_t tm_o = tmem_base + NCOL + lane_addr;
-    float m_run[NCOL], l_part[NCOL];
-#pragma unroll
-    for (int j = 0; j < NCOL; ++j) { m_run[j] = -INFINITY; l_part[j] = 0.f; }
+    const uint32_t tm_o = tmem_base + 2 * kTile + lane_addr;
+    const int lim = ss.limit[col];
+    const int src_lane = lane & 15;
+    float m_run = -INFINITY, l_run = 0.f;          // in scaled (log2) units; valid in lanes 0..15
+    uint8_t* prow = p_buf + (col >> 3) * 1024 + (col & 7) * 128;
     bool ok = true;
     for (int t = 0; ok && t < n_tiles; ++t) {
-      if (softmax_vote_any(!mbar_wait(&ss.s_full, t & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
+      if (threadIdx.x == 64) BG_TR(2, t, 0);
+      if (softmax_vote_any<NS>(!mbar_wait(&ss.s_full[t & 1], (t >> 1) & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[NCOL];
-      tmem_ld<NCOL>(tm_s, sv);
+      if (threadIdx.x == 64) BG_TR(2, t, 1);
+      const int tok0 = (tile_begin + t) * kTile;
+      uint32_t sv[64];
+      tmem_ld<32>(tmem_base + lane_addr + (t & 1) * kTile, sv);
+      tmem_ld<32>(tmem_base + lane_addr + (t & 1) * kTile + 32, sv + 32);
       tmem_ld_wait();
-      const int tok = (tile_begin + t) * kTile + row;
-      float s[NCOL], tmax[NCOL];
+      float mt = -INFINITY;
+      const int n_ok = lo ? min(max(lim - tok0, 0), kTile) : 0;      // tokens of this tile the column may see
 #pragma unroll
-      for (int j = 0; j < NCOL; ++j) {
-        s[j] = (tok < ss.limit[j]) ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
-        tmax[j] = warp_max(s[j]);
+      for (int j = 0; j < 64; ++j) {
+        const float v = (j < n_ok) ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
+        sv[j] = __float_as_uint(v);
+        mt = fmaxf(mt, v);
       }
-      if (lane == 0) {
-#pragma unroll
-        for (int j = 0; j < NCOL; ++j) ss.red[sw][j] = tmax[j];
-      }
-      softmax_bar();
-      bool changed = false;
-      float alpha[NCOL];
-#pragma unroll
-      for (int j = 0; j < NCOL; ++j) {
-        const float mt = fmaxf(fmaxf(ss.red[0][j], ss.red[1][j]), fmaxf(ss.red[2][j], ss.red[3][j]));
-        const float mn = fmaxf(m_run[j], mt);
-        alpha[j] = (mn == -INFINITY) ? 1.f : exp2f(m_run[j] - mn);   // m_run = -inf -> 0 (nothing accumulated yet)
-        changed |= (mn > m_run[j]);
-        m_run[j] = mn;
-      }
-      if (changed && t > 0) {
-        // running maxima moved: rescale the accumulators (O^T in TMEM, l in registers).  The previous
-        // tile's second GEMM has completed: its commit precedes this tile's s_full in issue order.
+      // keep the old maximum unless it grew by more than 2^8: probabilities stay below 256 and the
+      // accumulator is rescaled rarely
+      const bool grow = mt > m_run + 8.f;
+      const float m_new = grow ? mt : m_run;
+      const float alpha = (grow && m_run != -INFINITY) ? ex2_approx(m_run - m_new) : 1.f;
+      if (threadIdx.x == 64) BG_TR(2, t, 2);
+      // The previous tile's second GEMM reads P and accumulates into O: both are touched below.
+      if (t > 0 && softmax_vote_any<NS>(!mbar_wait(&ss.o_done, (t - 1) & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
+      tc_fence_after();
+      if (threadIdx.x == 64) BG_TR(2, t, 3);
+      const float alpha_row = __shfl_sync(0xffffffffu, alpha, src_lane);     // upper lanes: the factor of their column
+      if (t > 0 && __any_sync(0xffffffffu, alpha_row != 1.f)) {
 #pragma unroll 1
-        for (int blk = 0; blk < 4; ++blk) {
-          uint32_t ov[NCOL];
-          tmem_ld<NCOL>(tm_o + blk * NCOL, ov);
+        for (int c = 0; c < 8; ++c) {
+          uint32_t ov[32];
+          tmem_ld<32>(tm_o + c * 32, ov);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < NCOL; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha[j]);
-          tmem_st<NCOL>(tm_o + blk * NCOL, ov);
+          for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha_row);
+          tmem_st<32>(tm_o + c * 32, ov);
         }
         tmem_st_wait();
-#pragma unroll
-        for (int j = 0; j < NCOL; ++j) l_part[j] *= alpha[j];
       }
-      // probabilities -> shared memory (B operand, K-major core matrices: [k-step][col/8][k-half][col%8][tok%8])
+      if (threadIdx.x == 64) BG_TR(2, t, 4);
+      if (lo) {
+        // probabilities -> one swizzled 128-byte row of P (the K-major A operand of the second GEMM)
+        float lsum = 0.f;
+        const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
 #pragma unroll
-      for (int j = 0; j < NCOL; ++j) {
-        const float pj = (s[j] == -INFINITY) ? 0.f : exp2f(s[j] - m_run[j]);
-        const __nv_bfloat16 pb = __float2bfloat16(pj);
-        l_part[j] += __bfloat162float(pb);
-        const uint32_t off = (row >> 4) * ((NCOL / 8) * 256) + (j >> 3) * 256 + ((row >> 3) & 1) * 128 + (j & 7) * 16 +
-                             (row & 7) * 2;
-        *reinterpret_cast<__nv_bfloat16*>(p_buf + off) = pb;
+        for (int c = 0; c < 8; ++c) {
+          __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float p0 = ex2_approx(__uint_as_float(sv[c * 8 + 2 * q]) + neg_m);
+            const float p1 = ex2_approx(__uint_as_float(sv[c * 8 + 2 * q + 1]) + neg_m);
+            o[q] = __floats2bfloat162_rn(p0, p1);
+            lsum += __low2float(o[q]) + __high2float(o[q]);
+          }
+          *reinterpret_cast<uint4*>(prow + ((c ^ (col & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
+        }
+        l_run = l_run * alpha + lsum;
+        m_run = m_new;
       }
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&ss.p_full);
-      softmax_bar();   // red[] is reused by the next tile
+      if (threadIdx.x == 64) BG_TR(2, t, 5);
     }
     // ---- epilogue
     if (ok && n_tiles > 0)
-      ok = !softmax_vote_any(!mbar_wait(&ss.o_done, (n_tiles - 1) & 1, abort_flag, kTimeoutEpilogue));
+      ok = !softmax_vote_any<NS>(!mbar_wait(&ss.o_done, (n_tiles - 1) & 1, abort_flag, kTimeoutEpilogue));
     if (ok) {
       tc_fence_after();
-      // total row sums: reduce the per-thread partials over the 128 token lanes
-      float l_tot[NCOL];
-#pragma unroll
-      for (int j = 0; j < NCOL; ++j) l_tot[j] = warp_sum(l_part[j]);
-      softmax_bar();
-      if (lane == 0) {
-#pragma unroll
-        for (int j = 0; j < NCOL; ++j) ss.red[sw][j] = l_tot[j];
-      }
-      softmax_bar();
-#pragma unroll
-      for (int j = 0; j < NCOL; ++j) l_tot[j] = ss.red[0][j] + ss.red[1][j] + ss.red[2][j] + ss.red[3][j];
+      const float l_row = __shfl_sync(0xffffffffu, l_run, src_lane);
+      const float m_row = __shfl_sync(0xffffffffu, m_run, src_lane);
+      const int qi = col / hpg, hl = col % hpg;
+      const bool col_ok = col < NCOL && qi < w.n_q;
       const bool direct = (w.n_splits == 1);
+      const int dim0 = lo ? 0 : 256;
+      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+      __nv_bfloat16* orow = p.out + ((size_t)(w.q_row + qi) * p.H + w.head_group * hpg + hl) * kLatent + dim0;
+      float* prow_o = direct ? nullptr : p.part_o + ((size_t)w.out_slot * NCOL + col) * kLatent + dim0;
 #pragma unroll 1
-      for (int blk = 0; blk < 4; ++blk) {
-        uint32_t ov[NCOL];
+      for (int c = 0; c < 8; ++c) {
+        uint32_t ov[32];
         if (n_tiles > 0) {
-          tmem_ld<NCOL>(tm_o + blk * NCOL, ov);
+          tmem_ld<32>(tm_o + c * 32, ov);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int j = 0; j < NCOL; ++j) ov[j] = 0u;
+          for (int j = 0; j < 32; ++j) ov[j] = 0u;
         }
-        const int dim = blk * 128 + row;
+        if (!col_ok) continue;
+        if (direct) {
 #pragma unroll
-        for (int j = 0; j < NCOL; ++j) {
-          const int qi = j / hpg, hl = j % hpg;
-          if (qi >= w.n_q) continue;
-          const float o = __uint_as_float(ov[j]);
-          if (direct) {
-            const float inv = l_tot[j] > 0.f ? 1.0f / l_tot[j] : 0.f;
-            p.out[((size_t)(w.q_row + qi) * p.H + w.head_group * hpg + hl) * kLatent + dim] = __float2bfloat16(o * inv);
-          } else {
-            p.part_o[((size_t)w.out_slot * NCOL + j) * kLatent + dim] = o;
+          for (int j = 0; j < 32; j += 8) {
+            __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              o[q] = __floats2bfloat162_rn(__uint_as_float(ov[j + 2 * q]) * inv, __uint_as_float(ov[j + 2 * q + 1]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + j) = *reinterpret_cast<const uint4*>(o);
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<uint4*>(prow_o + c * 32 + j) = make_uint4(ov[j], ov[j + 1], ov[j + 2], ov[j + 3]);
         }
       }
-      if (!direct && threadIdx.x == 64) {
-        for (int j = 0; j < NCOL; ++j) {
-          p.part_ml[((size_t)w.out_slot * NCOL + j) * 2 + 0] = m_run[j];
-          p.part_ml[((size_t)w.out_slot * NCOL + j) * 2 + 1] = l_tot[j];
-        }
+      if (!direct && lo && col_ok) {
+        p.part_ml[((size_t)w.out_slot * NCOL + col) * 2 + 0] = m_row;
+        p.part_ml[((size_t)w.out_slot * NCOL + col) * 2 + 1] = l_row;
       }
     }
   }
@@ -444,7 +498,7 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
 }
 

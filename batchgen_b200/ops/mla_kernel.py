@@ -14,15 +14,17 @@ import torch
 
 from . import _ext
 
-KV_TILE = 128
+KV_TILE = 64
 _DECODE_WORK: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor, int]] = {}
 _SCRATCH: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def _geometry(H: int, prefill: bool) -> Tuple[int, int]:
     """(heads_per_group, ncol)."""
+    if H % 64 == 0:
+        return 64, 64
     if H % 32 == 0:
-        return 32, 32
+        return 32, (64 if prefill else 32)
     if H % 16 == 0:
         return 16, (32 if prefill else 16)
     if H % 8 == 0:
@@ -62,6 +64,42 @@ def _launch(q_abs, q_pe, cache, work, n_work, block_table, seqlens, out, part_o,
     _ext.check(rc, "bg_mla_attention")
 
 
+def _decode_work_lists(order: Sequence[int], groups: int, num_splits: int):
+    """Work items (one CTA each) and merge items for decode rows taken in ``order``."""
+    B = len(order)
+    rows = torch.as_tensor(list(order), dtype=torch.int32)
+    b = rows.repeat_interleave(groups * num_splits)
+    g = torch.arange(groups, dtype=torch.int32).repeat_interleave(num_splits).repeat(B)
+    sp = torch.arange(num_splits, dtype=torch.int32).repeat(B * groups)
+    w = torch.zeros(B * groups * num_splits, 8, dtype=torch.int32)
+    w[:, 0] = b; w[:, 1] = 1; w[:, 2] = b; w[:, 3] = -1; w[:, 4] = sp; w[:, 5] = num_splits; w[:, 6] = g
+    w[:, 7] = torch.arange(w.shape[0], dtype=torch.int32)
+    items = torch.zeros(B * groups, 5, dtype=torch.int32)
+    items[:, 0] = rows.repeat_interleave(groups); items[:, 1] = 1
+    items[:, 2] = torch.arange(groups, dtype=torch.int32).repeat(B)
+    items[:, 3] = torch.arange(B * groups, dtype=torch.int32) * num_splits; items[:, 4] = num_splits
+    return w, items
+
+
+def reorder_decode_work(device, lengths: Sequence[int]) -> int:
+    """Rewrite, in place, every cached decode work list of batch size ``len(lengths)`` on ``device`` so that
+    the longest sequences come first (longest-processing-time order for the hardware CTA scheduler).  The
+    lists are static device buffers, so CUDA graphs that captured a decode launch pick the new order up on
+    their next replay.  Any order is correct; a stale one only balances worse.  Returns lists rewritten."""
+    B = len(lengths)
+    order = sorted(range(B), key=lambda i: -int(lengths[i]))
+    n = 0
+    for (dev, b, H, splits), (w_d, items_d, _) in _DECODE_WORK.items():
+        if dev != str(device) or b != B:
+            continue
+        groups = items_d.shape[0] // B
+        w, items = _decode_work_lists(order, groups, splits)
+        w_d.copy_(w, non_blocking=False)
+        items_d.copy_(items, non_blocking=False)
+        n += 1
+    return n
+
+
 def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_splits: int = 0):
     """q_abs [B, H, 512], q_pe [B, H, 64] -> [B, H, 512]."""
     B, H, _ = q_abs.shape
@@ -70,23 +108,16 @@ def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_
     hpg, ncol = _geometry(H, prefill=False)
     groups = H // hpg
     if num_splits <= 0:
+        # enough CTAs for about four rounds over the SMs: the hardware hands out CTAs as SMs free up, so
+        # finer work items (and longest-first order, see reorder_decode_work) even out ragged lengths
         ctas = B * groups
         sms = _ext.num_sms(dev)
         max_tiles = max(1, (block_table.shape[1] * cache.shape[1]) // KV_TILE)
-        num_splits = 1 if ctas >= sms else max(1, min(16, sms // ctas, max_tiles))
+        num_splits = max(1, min(16, -(-4 * sms // ctas), max_tiles))
     key = (str(dev), B, H, num_splits)
     cached = _DECODE_WORK.get(key)
     if cached is None:
-        b = torch.arange(B).repeat_interleave(groups * num_splits)
-        g = torch.arange(groups).repeat_interleave(num_splits).repeat(B)
-        s = torch.arange(num_splits).repeat(B * groups)
-        w = torch.zeros(B * groups * num_splits, 8, dtype=torch.int32)
-        w[:, 0] = b; w[:, 1] = 1; w[:, 2] = b; w[:, 3] = -1; w[:, 4] = s; w[:, 5] = num_splits; w[:, 6] = g
-        w[:, 7] = torch.arange(w.shape[0])
-        items = torch.zeros(B * groups, 5, dtype=torch.int32)
-        items[:, 0] = torch.arange(B).repeat_interleave(groups); items[:, 1] = 1
-        items[:, 2] = torch.arange(groups).repeat(B)
-        items[:, 3] = torch.arange(B * groups) * num_splits; items[:, 4] = num_splits
+        w, items = _decode_work_lists(list(range(B)), groups, num_splits)
         cached = (w.to(dev), items.to(dev), w.shape[0])
         _DECODE_WORK[key] = cached
     work, items, n_work = cached

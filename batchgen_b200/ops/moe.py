@@ -28,6 +28,8 @@ class ExpertWeights:
     quant == "none":      w13 [E, 2I, Kh], w2 [E, Hout, I] in the compute dtype.
     quant == "fp8_block": w13/w2 e4m3 with 128x128 scales w13_s [E, 2I/128, Kh/128], w2_s;
                           on CUDA, w13 rows are stored in the gate/up tile-interleaved order.
+    quant == "mxfp4":     w13/w2 packed e2m1 (uint8, two values per byte) with e8m0 scales per 32
+                          (w13 [E, 2I, Kh/2], w13_s [E, 2I, Kh/32]); same interleave rule on CUDA.
     """
     w13: torch.Tensor
     w2: torch.Tensor
@@ -43,10 +45,16 @@ class ExpertWeights:
 
     def to_device_layout(self) -> "ExpertWeights":
         """Reorder w13 rows for the fused SiLU epilogue (GPU, fp8 only)."""
-        if self.quant != "fp8_block" or self.interleaved or not self.w13.is_cuda:
+        if self.quant not in ("fp8_block", "mxfp4") or self.interleaved or not self.w13.is_cuda:
             return self
         perm = gemm.interleave_gate_up_rows(self.w13.shape[1], self.w13.device)
-        self.w13 = self.w13.view(torch.uint8)[:, perm].contiguous().view(FP8)
+        if self.quant == "mxfp4":
+            if self.activation != "silu":
+                return self                      # other activations run unfused: natural row order
+            self.w13 = self.w13[:, perm].contiguous()
+            self.w13_s = self.w13_s[:, perm].contiguous()
+        else:
+            self.w13 = self.w13.view(torch.uint8)[:, perm].contiguous().view(FP8)
         self.interleaved = True
         return self
 
@@ -170,6 +178,18 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         act = _activation(gu, ew.activation)
         aq, as_ = ref.act_quant(act)
         return ref.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
+    if ew.quant == "mxfp4":
+        from . import mxfp4
+        x = x_dense
+        if x.is_cuda and ew.interleaved:
+            with timer.timed("moe.s1_gemm"):
+                act = mxfp4.grouped_mxfp4_gemm(x, ew.w13, ew.w13_s, offsets, silu_mul=True)
+        else:
+            with timer.timed("moe.s1_gemm"):
+                gu = mxfp4.grouped_mxfp4_gemm(x, ew.w13, ew.w13_s, offsets)
+            act = _activation(gu, ew.activation).to(x.dtype)
+        with timer.timed("moe.s3_gemm"):
+            return mxfp4.grouped_mxfp4_gemm(act, ew.w2, ew.w2_s, offsets)
     # unquantised experts (CPU fp32 oracle path and bf16 debugging)
     x = x_dense
     out = torch.zeros(x.shape[0], ew.w2.shape[1], dtype=x.dtype, device=x.device)

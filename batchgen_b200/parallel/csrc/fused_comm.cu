@@ -43,7 +43,8 @@ struct Epoch {
 };
 
 __device__ __forceinline__ void signal_all(const Peers& flags, int index, int world, uint32_t epoch) {
-  for (int r = 0; r < world; ++r) st_release_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + index, epoch);
+  // callers have fenced (system scope) after the data stores; the flag stores themselves need no fence each
+  for (int r = 0; r < world; ++r) st_relaxed_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + index, epoch);
 }
 
 // Last-CTA-out signalling: every CTA fences its stores; the last one raises the flags.

@@ -107,6 +107,7 @@ class DecodeGraphRunner:
         self._ring_ev = [torch.cuda.Event() if pin else None for _ in range(2)]
         self._ring_n = [0, 0]
         self._ring_next = 0
+        self._row_key = None
 
     # ------------------------------------------------------------------ capture
     def _meta(self, b: int) -> AttnMeta:
@@ -224,6 +225,13 @@ class DecodeGraphRunner:
     def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
         """Engine hook (``Engine.graph_runner``): logits of the live rows."""
         b = self.stage(ids, pos, slots, lens, [s.gpu_pages for s in rows])
+        key = tuple(id(s) for s in rows)
+        if key != self._row_key and self.model.cfg.is_mla and torch.device(self.dev).type == "cuda":
+            # batch membership changed: put the longest sequences first in the attention work lists
+            from ..ops import mla_kernel
+            self._row_key = key
+            padded = list(lens) + [0] * (b - len(lens))
+            mla_kernel.reorder_decode_work(self.dev, padded)
         return self.replay(b, len(rows))
 
 

@@ -243,6 +243,11 @@ def main() -> int:
     for _ in range(max(args.warmup, 3)):
         decode_step_device()
     _ext.check_status()
+    if cfg.is_mla:
+        # longest sequences first in the attention work lists (static device buffers: graphs see the new order)
+        from batchgen_b200.ops import mla_kernel
+        mla_kernel.reorder_decode_work(dev, [int(c) for c in ctx])
+        decode_step_device()
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     l0 = _ext.LAUNCHES["count"]
     ms = timed(decode_step_device, args.steps)
