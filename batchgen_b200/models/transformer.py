@@ -22,6 +22,8 @@ structure, gate :746-850), batchgen/models/glm/glm5/model.py:610-700 (DSA indexe
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -394,7 +396,7 @@ class Transformer:
                     with tm.timed("moe.shared_expert", l):
                         shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
                 with tm.timed("moe.routed_experts", l):
-                    src = comm.moe_sp(x, idx, w, lw.experts, extra=shared)
+                    src = comm.moe_sp(x, idx, w, lw.experts, extra=shared, timer=self.timer)
             else:
                 with tm.timed("sp.norm_push", l):
                     comm.sp_norm_push(None, residual, lw.post_norm, eps, from_rs=True, has_residual=True, push=True,
@@ -407,5 +409,9 @@ class Transformer:
         x, _, _ = comm.sp_norm_push(src, residual, self.w.final_norm, eps, from_rs=src is None, has_residual=True,
                                     push=False, want_q=False)
         comm.end_step()
+        if meta.logit_rows is not None:
+            # only the wanted rows that this rank owns (the caller gathers them in rank order)
+            rows = meta.logit_rows.long()
+            x = x[rows[(rows >= r * Tl) & (rows < (r + 1) * Tl)] - r * Tl]
         with tm.timed("lm_head"):
             return (x @ self.w.lm_head.t()).float()

@@ -12,7 +12,8 @@
 
 namespace bg {
 
-constexpr uint32_t kSpinLimit = 1u << 21;  // mbarrier try_wait attempts before giving up
+constexpr uint64_t kWaitBudgetNs = 30ull * 1000000000ull;   // intra-CTA pipeline waits (wall time)
+constexpr uint64_t kFlagBudgetNs = 10ull * 1000000000ull;   // waits on a flag that a peer GPU raises
 
 enum Status : int {
   kOk = 0,
@@ -67,13 +68,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises *abort_flag) when the budget runs out or another
-// role already aborted.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises *abort_flag) when the budget runs out or another role
+// already aborted.  The budget is wall time (kWaitBudgetNs), checked every 64K polls: a role inside a
+// CTA may legitimately sit here for as long as its producer waits for a peer GPU (kFlagBudgetNs, which is
+// shorter), so the limit must not depend on how fast the poll loop spins.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int why) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if ((i & 0xFFFFu) == 0xFFFFu) {
+        const uint64_t t = global_timer_ns();
+        if (t0 == 0) t0 = t;
+        else if (t - t0 > kWaitBudgetNs) break;
+      }
+    }
   }
   if (*abort_flag == 0) *abort_flag = why;
   return false;
@@ -194,18 +210,25 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-constexpr uint32_t kFlagSpinLimit = 1u << 23;  // polls of >= 200 ns each: ten seconds or so (host-side skew
-                                               // between ranks, e.g. graph capture, is seconds), then give up
-// Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded; and once any
+// Wait until *flag >= value (flags are monotonically increasing epochs).  Bounded by wall time
+// (kFlagBudgetNs: ranks can be seconds apart after loading weights or capturing graphs); and once any
 // kernel has raised the status word (a peer is late or gone) later waits give up at once, so a
 // broken step drains in milliseconds instead of one timeout per kernel.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t value, const int* status = nullptr) {
-  for (uint32_t i = 0; i < kFlagSpinLimit; ++i) {
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t value, const int* status = nullptr,
+                                             uint64_t budget_ns = kFlagBudgetNs) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - value) >= 0) return true;
-    if (status != nullptr && (i & 63u) == 0u && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+    if ((i & 63u) == 0u) {
+      if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+      if ((i & 1023u) == 0u) {
+        const uint64_t t = global_timer_ns();
+        if (t0 == 0) t0 = t;
+        else if (t - t0 > budget_ns) return false;
+      }
+    }
     __nanosleep(200);
   }
-  return false;
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 

@@ -178,6 +178,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
       Tile t;
       uint32_t it = 0;
+      uint32_t ready_mask = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
         const int brow = t.g * p.N + t.nt * BN;
@@ -187,7 +188,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int i_lo = p.a_ready_rows > 0 ? t.m0 / p.a_ready_rows : 0;            // rows == 0: wait for every rank
           const int i_hi = p.a_ready_rows > 0 ? last / p.a_ready_rows : p.world - 1;
           for (int i = i_lo; ok && i <= i_hi; ++i) {
-            if (!wait_flag_ge(p.a_ready + i, epoch, p.status)) {
+            if (ready_mask & (1u << i)) continue;   // flags only grow: a rank seen once stays arrived
+            if (wait_flag_ge(p.a_ready + i, epoch, p.status)) {
+              ready_mask |= 1u << i;
+            } else {
               if (*abort_flag == 0) *abort_flag = kTimeoutPeer;
               if (p.status != nullptr) atomicMax(p.status, (int)kTimeoutPeer);
               ok = false;

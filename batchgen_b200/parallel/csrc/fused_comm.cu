@@ -323,10 +323,11 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
   cta_done_signal(counter, flags, ready_index + my_rank, world, epoch);
 }
 
-__global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, int* status) {
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, int* status, uint64_t budget_ns) {
   const uint32_t epoch = epoch_e.get();
   if (threadIdx.x < n) {
-    if (!wait_flag_ge(flags + threadIdx.x, epoch, status) && status != nullptr) atomicMax(status, (int)kTimeoutPeer);
+    if (!wait_flag_ge(flags + threadIdx.x, epoch, status, budget_ns) && status != nullptr)
+      atomicMax(status, (int)kTimeoutPeer);
   }
 }
 
@@ -416,7 +417,18 @@ int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T,
 
 int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int* status,
                   cudaStream_t stream) {
-  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status);
+  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
+                                                    bg::kFlagBudgetNs);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Same wait with an explicit budget in milliseconds (failure-detection tests make a wait run out on a flag
+// that nothing raises and read the status word; the context stays usable).
+int bg_wait_flags_budget(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int budget_ms,
+                         int* status, cudaStream_t stream) {
+  if (n < 0 || n > 32 || budget_ms < 0) return -1;
+  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
+                                                    (uint64_t)budget_ms * 1000000ull);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -52,6 +52,7 @@ class FusedComm(NcclComm):
         self.heap: Optional[SymmetricHeap] = None
         self.epoch = 0
         self.nvlink_bytes = 0
+        self._started = False
 
     # ------------------------------------------------------------------ setup
     def configure(self, hidden: int, expert_hidden: int, num_experts: int, top_k: int, max_tokens: int) -> None:
@@ -104,6 +105,12 @@ class FusedComm(NcclComm):
         self.heap.barrier()
 
     def begin_step(self) -> None:
+        if not self._started:
+            # the first step's kernels wait on peers with a bounded budget: start it together (ranks finish
+            # loading weights at different times)
+            self._started = True
+            if not torch.cuda.is_current_stream_capturing():
+                self.heap.barrier()
         self.epoch = 0
         for k in self.last:
             self.last[k] = 0
@@ -198,51 +205,61 @@ class FusedComm(NcclComm):
 
     # ------------------------------------------------------------------ expert parallel
     def moe_sp(self, h_local: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
-               extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+               extra: Optional[torch.Tensor] = None, timer=None) -> torch.Tensor:
         """Routed-expert output for this rank's own rows (dispatch -> experts -> combine)."""
+        if timer is None:
+            from ..utils.timing import null_timer
+            timer = null_timer()
         W, E, K = self.world, self.E, topk_idx.shape[1]
         Tl, H = h_local.shape
         L = _ext.lib()
         st = _ext.stream()
-        e_cnt = self._next(CNT_READY)
-        rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E), self.heap.peer_ptrs("cnt"),
-                                ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(CNT_READY),
-                                ctypes.c_uint32(e_cnt), self._base(), _ext.ptr(self.recv_info),
-                                ctypes.c_int(self.recv_cap), st)
-        _ext.check(rc, "bg_ep_count_push")
-        rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
-                            ctypes.c_int(E),
-                            ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(ALIGN), _ext.ptr(self.row_base),
-                            _ext.ptr(self.offsets), _ext.ptr(self.cursor), _ext.ptr(self.total_rows), self._status(), st)
-        _ext.check(rc, "bg_ep_layout")
-        e_disp = self._next(DISP_READY)
-        rc = L.bg_ep_dispatch_send(_ext.ptr(h_local), ctypes.c_int(h_local.stride(0)), _ext.ptr(topk_idx),
-                                   ctypes.c_int(Tl), ctypes.c_int(K), ctypes.c_int(E), ctypes.c_int(H),
-                                   _ext.ptr(self.row_base), _ext.ptr(self.cursor), self.heap.peer_ptrs("recv_q"),
-                                   self.heap.peer_ptrs("recv_s"), ctypes.c_int(self.recv_s_stride),
-                                   self.heap.peer_ptrs("recv_info"), ctypes.c_int(self.recv_cap),
-                                   _ext.ptr(self.sent_row), ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs,
-                                   ctypes.c_int(DISP_READY), ctypes.c_uint32(e_disp), self._base(),
-                                   _ext.ptr(self.counters[2:3]),
-                                   self._status(), st)
-        _ext.check(rc, "bg_ep_dispatch_send")
+        with timer.timed("moe.ep_count_layout"):
+            e_cnt = self._next(CNT_READY)
+            rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E),
+                                    self.heap.peer_ptrs("cnt"), ctypes.c_int(self.rank), ctypes.c_int(W),
+                                    self.flag_ptrs, ctypes.c_int(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
+                                    _ext.ptr(self.recv_info), ctypes.c_int(self.recv_cap), st)
+            _ext.check(rc, "bg_ep_count_push")
+            rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
+                                ctypes.c_int(E), ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(ALIGN),
+                                _ext.ptr(self.row_base), _ext.ptr(self.offsets), _ext.ptr(self.cursor),
+                                _ext.ptr(self.total_rows), self._status(), st)
+            _ext.check(rc, "bg_ep_layout")
+        with timer.timed("moe.ep_dispatch"):
+            e_disp = self._next(DISP_READY)
+            rc = L.bg_ep_dispatch_send(_ext.ptr(h_local), ctypes.c_int(h_local.stride(0)), _ext.ptr(topk_idx),
+                                       ctypes.c_int(Tl), ctypes.c_int(K), ctypes.c_int(E), ctypes.c_int(H),
+                                       _ext.ptr(self.row_base), _ext.ptr(self.cursor), self.heap.peer_ptrs("recv_q"),
+                                       self.heap.peer_ptrs("recv_s"), ctypes.c_int(self.recv_s_stride),
+                                       self.heap.peer_ptrs("recv_info"), ctypes.c_int(self.recv_cap),
+                                       _ext.ptr(self.sent_row), ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs,
+                                       ctypes.c_int(DISP_READY), ctypes.c_uint32(e_disp), self._base(),
+                                       _ext.ptr(self.counters[2:3]),
+                                       self._status(), st)
+            _ext.check(rc, "bg_ep_dispatch_send")
         self.nvlink_bytes += Tl * K * (H + 4 * (H // 128)) * (W - 1) // W
         # ---- experts on the receive buffer: the gate/up GEMM waits for every source rank's rows
         xs = self.recv_s.t()[: self.recv_cap]
-        self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
-        act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True)
-        aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
+        with timer.timed("moe.s1_gemm"):
+            self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
+            act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True)
+        with timer.timed("moe.act_quant"):
+            aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
-        e_ret = self._next(RET_READY)
-        self._set_hooks(peer_out=self.heap.peer_ptrs("ret"), row_map=self.recv_info, epoch=e_ret,
-                        done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
-        out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
-        gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets, out=_StrideCarrier(out_stub, self.recv_cap))
+        with timer.timed("moe.s3_gemm_return"):
+            e_ret = self._next(RET_READY)
+            self._set_hooks(peer_out=self.heap.peer_ptrs("ret"), row_map=self.recv_info, epoch=e_ret,
+                            done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
+            out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
+            gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets,
+                                      out=_StrideCarrier(out_stub, self.recv_cap))
         self.nvlink_bytes += Tl * K * H * 2 * (W - 1) // W
-        rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),
-                             self._status(), st)
-        _ext.check(rc, "bg_wait_flags")
-        return moe_ops.combine(self.ret[: Tl * K], self.ident_pos[: Tl * K].view(Tl, K), topk_w, extra)
+        with timer.timed("moe.return_wait_combine"):
+            rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),
+                                 self._status(), st)
+            _ext.check(rc, "bg_wait_flags")
+            return moe_ops.combine(self.ret[: Tl * K], self.ident_pos[: Tl * K].view(Tl, K), topk_w, extra)
 
 
 class _StrideCarrier:
@@ -257,3 +274,13 @@ class _StrideCarrier:
 
     def data_ptr(self) -> int:
         return self._row.data_ptr()
+
+
+def bounded_flag_wait(flags: torch.Tensor, n: int, epoch: int, budget_ms: int) -> None:
+    """Enqueue a wait until ``flags[i] >= epoch`` for i < n (``flags``: int32 device tensor) that gives up
+    after ``budget_ms`` and raises the device status word instead of hanging; read the outcome with
+    ``ops._ext.check_status``.  Used by the failure-detection tests and by health probes of a peer."""
+    rc = _ext.lib().bg_wait_flags_budget(_ext.ptr(flags), ctypes.c_int(n), ctypes.c_uint32(epoch), ctypes.c_void_p(0),
+                                         ctypes.c_int(budget_ms), _ext.ptr(_ext.status_word(flags.device)),
+                                         _ext.stream())
+    _ext.check(rc, "bg_wait_flags_budget")

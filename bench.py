@@ -311,6 +311,8 @@ def main() -> int:
                 sampling_ops.greedy(model.forward(pids, meta, kv))
 
         prefill_step()
+        torch.cuda.synchronize()
+        _ext.check_status()
         psum = None
         if args.profile_ops:
             model.timer.reset()
@@ -327,6 +329,7 @@ def main() -> int:
                     for op, d in sm.items():
                         f.write(f"{op:32s} {d['ms_per_step']:10.3f} ms  {d['share'] * 100:5.1f}%  calls {d['calls']}\n")
         ms_p = timed(prefill_step, 2) / 2
+        _ext.check_status()
         prefill = {"tokens_per_s": T * 1000.0 / ms_p, "ms_per_microbatch": ms_p, "tokens": T, "seq_len": L}
 
     if rank == 0:

@@ -33,12 +33,14 @@ def main():
                            num_layers=3, first_k_dense=1)
     # two sequences of different lengths; T divisible by the world size
     lens = [40 * world, 24 * world]
+    if os.environ.get("BG_CHECK_LENS"):          # e.g. "384,128": rows per rank a multiple of the GEMM tile
+        lens = [int(v) for v in os.environ["BG_CHECK_LENS"].split(",")]
     T = sum(lens)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(2, cfg.vocab_size, (T,), generator=g, dtype=torch.int32).to(dev)
 
     def meta_and_cache():
-        kv = PagedKVCache(cfg, 16, 64, dev, torch.bfloat16)
+        kv = PagedKVCache(cfg, 16 + sum((n + 63) // 64 for n in lens), 64, dev, torch.bfloat16)
         pages = [kv.alloc.alloc((n + 63) // 64) for n in lens]
         pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
         slots = torch.tensor(sum((slots_for_range(p, 0, n, 64) for p, n in zip(pages, lens)), []), device=dev)
