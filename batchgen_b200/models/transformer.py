@@ -126,7 +126,7 @@ class Transformer:
         q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
         # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
         with tm.timed("attn.q_absorb", l):
-            q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_uk).transpose(0, 1)
+            q_abs = attn_ops.mla_q_absorb(q, lw.w_uk_t, cfg.qk_nope_head_dim)
         sel = None
         if cfg.has_dsa:
             with tm.timed("attn.dsa_indexer", l):
@@ -135,7 +135,7 @@ class Transformer:
             o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
         # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
         with tm.timed("attn.out_absorb", l):
-            return torch.bmm(o_lat.transpose(0, 1), lw.w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
+            return attn_ops.mla_out_absorb(o_lat, lw.w_uv)
 
     def _mla_q(self, lw, q_a, kv_a, meta, cache, l):
         cfg = self.cfg

@@ -121,7 +121,8 @@ class LayerWeights:
     q_norm: torch.Tensor = None
     kv_norm: torch.Tensor = None
     wq_b: Linear = None              # [Hh * qk_head_dim, q_lora]
-    w_uk: torch.Tensor = None        # [Hh, nope, kv_lora]
+    w_uk: torch.Tensor = None        # [Hh, nope, kv_lora] (a view of w_uk_t)
+    w_uk_t: torch.Tensor = None      # [Hh, kv_lora, nope] contiguous
     w_uv: torch.Tensor = None        # [Hh, v, kv_lora]
     wo: Linear = None                # [H, Hh * v]
     # GQA
@@ -190,7 +191,10 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
             kvb = src.get(f"{p}.self_attn.kv_b_proj.weight",
                           (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank))
             kvb = kvb.view(cfg.num_heads, cfg.qk_nope_head_dim + cfg.v_head_dim, cfg.kv_lora_rank)[h0:h1]
-            lw.w_uk = kvb[:, : cfg.qk_nope_head_dim].contiguous().to(dtype)
+            # W_UK is kept transposed ([heads, kv_lora, nope]: the K-major operand of the absorb kernel);
+            # w_uk is a view of the same storage in the [heads, nope, kv_lora] form
+            lw.w_uk_t = kvb[:, : cfg.qk_nope_head_dim].transpose(1, 2).contiguous().to(dtype)
+            lw.w_uk = lw.w_uk_t.transpose(1, 2)
             lw.w_uv = kvb[:, cfg.qk_nope_head_dim:].contiguous().to(dtype)
             wo = src.get(f"{p}.self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
             wo = wo.view(H, cfg.num_heads, cfg.v_head_dim)[:, h0:h1].reshape(H, -1)

@@ -40,3 +40,34 @@ def sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, 
         from . import mla_cuda
         return mla_cuda.sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
     return ref.sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
+
+
+def _head_gemm(a: torch.Tensor, a_head: int, K: int, w: torch.Tensor, out: torch.Tensor, d_row: int, d_head: int):
+    T, H, N = a.shape[0], w.shape[0], w.shape[1]
+    rc = _ext.lib().bg_head_gemm(_ext.ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_int(a_head),
+                                 ctypes.c_longlong(a.stride(0)), _ext.ptr(w), _ext.ptr(out), ctypes.c_longlong(d_row),
+                                 ctypes.c_longlong(d_head), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(N),
+                                 ctypes.c_int(K), _ext.ptr(_ext.status_word(a.device)), _ext.stream())
+    _ext.check(rc, "bg_head_gemm")
+
+
+def mla_q_absorb(q: torch.Tensor, w_uk_t: torch.Tensor, nope: int) -> torch.Tensor:
+    """q [T, H, nope + rope] (the q projection, in place) x W_UK^T [H, kv_lora, nope] -> q_abs [T, H, kv_lora]."""
+    T, H, D = q.shape
+    if (q.is_cuda and q.dtype == torch.bfloat16) and q.stride(2) == 1 and q.stride(1) == D and nope % 64 == 0 and D % 8 == 0:
+        out = torch.empty(T, H, w_uk_t.shape[1], dtype=q.dtype, device=q.device)
+        _head_gemm(q.view(T, H * D) if q.is_contiguous() else q.as_strided((T, H * D), (q.stride(0), 1)), D, nope,
+                   w_uk_t, out, out.stride(0), out.stride(1))
+        return out
+    return torch.bmm(q[..., :nope].transpose(0, 1), w_uk_t.transpose(1, 2)).transpose(0, 1)
+
+
+def mla_out_absorb(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:
+    """o_lat [T, H, kv_lora] x W_UV [H, v, kv_lora] -> [T, H * v]."""
+    T, H, L = o_lat.shape
+    V = w_uv.shape[1]
+    if (o_lat.is_cuda and o_lat.dtype == torch.bfloat16) and o_lat.is_contiguous() and L % 64 == 0 and V % 8 == 0:
+        out = torch.empty(T, H * V, dtype=o_lat.dtype, device=o_lat.device)
+        _head_gemm(o_lat.view(T, H * L), L, L, w_uv, out, out.stride(0), V)
+        return out
+    return torch.bmm(o_lat.transpose(0, 1), w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)

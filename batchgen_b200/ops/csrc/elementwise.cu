@@ -116,9 +116,11 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
 template <int MODE>
 __global__ void __launch_bounds__(256)
 act_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int s_stride,
-                 int T, int K, int ldx, int pow2, const int* __restrict__ valid_rows) {
+                 int T, int K, int ldx, int pow2, const int* __restrict__ valid_rows,
+                 const int* __restrict__ row_src) {
   const int t = blockIdx.x;
   if (valid_rows != nullptr && t >= *valid_rows) return;
+  if (row_src != nullptr && row_src[t] < 0) return;      // padding row of an expert segment: nothing reads it
   const __nv_bfloat16* xr = x + (size_t)t * ldx;
   for (int v = threadIdx.x; v < K / 8; v += blockDim.x) {
     uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
@@ -244,15 +246,15 @@ int bg_rmsnorm(const void* x, void* residual, const void* w, void* out, void* ou
 // mode 0: quantise x [T, K] (row stride ldx); mode 1: quantise silu(x[:, :K]) * x[:, K:2K].
 // valid_rows (device int, may be null) limits the rows that are processed.
 int bg_act_quant(int mode, const void* x, void* q, float* s, int s_stride, int T, int K, int ldx, int pow2,
-                 const int* valid_rows, cudaStream_t stream) {
+                 const int* valid_rows, const int* row_src, cudaStream_t stream) {
   using namespace bg;
   if (T <= 0) return 0;
   if (K % 128 != 0) return -1;
   const int threads = K / 8 >= 256 ? 256 : ((K / 8 + 31) / 32) * 32;
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
   auto Q = reinterpret_cast<uint8_t*>(q);
-  if (mode == 0) act_quant_kernel<0><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows);
-  else act_quant_kernel<1><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows);
+  if (mode == 0) act_quant_kernel<0><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
+  else act_quant_kernel<1><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

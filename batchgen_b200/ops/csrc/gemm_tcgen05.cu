@@ -44,6 +44,8 @@ struct GemmParams {
   __nv_bfloat16* D;     // [M, ldd]
   int ldd;
   const int* offsets;   // [groups+1] device row offsets, every segment start 128-aligned; null = dense
+  const int* counts;    // [groups] rows really present in each segment (null: offsets[g+1] - offsets[g]); rows
+                        // past the count are neither multiplied as whole tiles nor stored
   int groups;
   int M;                // rows of A (dense) / capacity of A (grouped)
   int N;                // rows of B per group (GEMM N)
@@ -78,6 +80,7 @@ struct SharedStorage {
   uint32_t tmem_base;
   int abort_flag;
   int offs[kMaxGroups + 1];
+  int cnt[kMaxGroups];
 };
 
 struct Tile {
@@ -91,10 +94,11 @@ struct Tile {
 // Grouped: groups in order, inside a group nt-major with mt fastest.
 struct TileWalker {
   const int* offs;
+  const int* cnt;
   int groups, n_tiles, M, m_rotate;
   int g, before;  // grouped walk state: current group and number of tiles in earlier groups
-  __device__ TileWalker(const int* offs_, int groups_, int n_tiles_, int M_, int m_rotate_ = 0)
-      : offs(offs_), groups(groups_), n_tiles(n_tiles_), M(M_), m_rotate(m_rotate_), g(0), before(0) {}
+  __device__ TileWalker(const int* offs_, const int* cnt_, int groups_, int n_tiles_, int M_, int m_rotate_ = 0)
+      : offs(offs_), cnt(cnt_), groups(groups_), n_tiles(n_tiles_), M(M_), m_rotate(m_rotate_), g(0), before(0) {}
   __device__ bool get(int tile, Tile& t) {
     if (offs == nullptr) {
       const int m_tiles = (M + BM - 1) / BM;
@@ -106,7 +110,7 @@ struct TileWalker {
       return true;
     }
     while (g < groups) {
-      const int rows = offs[g + 1] - offs[g];
+      const int rows = cnt[g];
       const int m_tiles = (rows + BM - 1) / BM;
       const int here = m_tiles * n_tiles;
       if (tile < before + here) {
@@ -114,7 +118,7 @@ struct TileWalker {
         t.g = g;
         t.nt = local / m_tiles;
         t.m0 = offs[g] + (local % m_tiles) * BM;
-        t.m_end = offs[g + 1];
+        t.m_end = offs[g] + rows;
         return true;
       }
       before += here;
@@ -159,6 +163,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
   if (p.offsets != nullptr) {
     for (int i = threadIdx.x; i <= p.groups; i += kThreads) ss.offs[i] = p.offsets[i];
+    for (int i = threadIdx.x; i < p.groups; i += kThreads) {
+      const int padded = p.offsets[i + 1] - p.offsets[i];
+      ss.cnt[i] = p.counts != nullptr ? min(max(p.counts[i], 0), padded) : padded;
+    }
   }
   if (warp == 1) {
     tmem_alloc(&ss.tmem_base, kTmemCols);
@@ -175,7 +183,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
+      TileWalker walk(offs, ss.cnt, p.groups, n_tiles, p.M, p.m_rotate);
       Tile t;
       uint32_t it = 0;
       uint32_t ready_mask = 0;
@@ -231,7 +239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc(BM, BN, KIND == KIND_FP8 ? 0 : 1, KIND == KIND_FP8 ? 0 : 1);
-      TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
+      TileWalker walk(offs, ss.cnt, p.groups, n_tiles, p.M, p.m_rotate);
       Tile t;
       uint32_t it = 0;   // smem stage counter
       uint32_t acc = 0;  // accumulator hand-off counter
@@ -271,7 +279,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int quad = warp & 3;        // TMEM lane quadrant this warp may access
     const int half = ew >> 2;         // which 64 columns of the tile
     const int row_in_tile = quad * 32 + lane;
-    TileWalker walk(offs, p.groups, n_tiles, p.M, p.m_rotate);
+    TileWalker walk(offs, ss.cnt, p.groups, n_tiles, p.M, p.m_rotate);
     Tile t;
     uint32_t acc = 0;
     bool ok = true;
@@ -525,6 +533,7 @@ struct BgGemmHooks {
 };
 static thread_local BgGemmHooks g_hooks;
 static thread_local bool g_hooks_set = false;
+static thread_local const int* g_counts = nullptr;
 
 void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch, const uint32_t* epoch_base, int m_rotate,
                        void* const* peer_out,
@@ -542,6 +551,10 @@ void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch
   g_hooks_set = true;
 }
 
+// Real row counts of the next grouped bg_gemm on this thread: counts[g] rows of segment g are present, the
+// rest of the (128-aligned) segment is padding that is neither computed as whole tiles nor stored.
+void bg_gemm_set_counts(const int* counts) { g_counts = counts; }
+
 // Dense or grouped GEMM.  kind: 0 = e4m3 block scaled, 1 = bf16.  epi: 0 = store, 1 = silu-mul
 // (weight rows interleaved in 32-row gate/up blocks; output has N/2 columns).
 // offsets == nullptr -> dense [M, K] x [N, K]^T.  Otherwise A holds `groups` row segments
@@ -556,6 +569,8 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
   if (K % bk != 0 || groups > kMaxGroups || (epi == EPI_SILU_MUL && (N % 256) != 0)) return -1;
   if (offsets == nullptr) groups = 1;
   GemmParams p;
+  p.counts = (offsets != nullptr) ? g_counts : nullptr;
+  g_counts = nullptr;
   p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
   p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
   p.a_ready = nullptr; p.a_ready_rows = 1; p.epoch = 0; p.epoch_base = nullptr; p.m_rotate = 0; p.row_map = nullptr; p.rs_rows_per_rank = 1;

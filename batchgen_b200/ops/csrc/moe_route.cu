@@ -154,14 +154,16 @@ __global__ void moe_scatter_kernel(const int* __restrict__ topk_idx, int n_pairs
 }
 
 // One block per grouped row: gather hidden[src_row[r]] (bf16) and quantise to e4m3 with 1x128
-// scales.  Padding rows (src < 0) become zeros with scale 0 so they produce exact zeros.
+// scales.  Padding rows (src < 0) become zeros with scale 0 so they produce exact zeros, or are left
+// untouched when `zero_padding` is 0 (the grouped GEMM is then given the real row counts).
 __global__ void __launch_bounds__(256)
 moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const int* __restrict__ src_row,
                         const int* __restrict__ total_rows, uint8_t* __restrict__ q, float* __restrict__ s,
-                        int s_stride, int K, int pow2) {
+                        int s_stride, int K, int pow2, int zero_padding) {
   const int r = blockIdx.x;
   if (r >= *total_rows) return;
   const int src = src_row[r];
+  if (src < 0 && !zero_padding) return;
   for (int v = threadIdx.x; v < K / 8; v += blockDim.x) {
     float f[8];
     if (src >= 0) {
@@ -276,12 +278,12 @@ int bg_moe_permute(const int* topk_idx, int T, int K, int lo, int hi, int align,
 }
 
 int bg_moe_gather_quant(const void* hidden, int ldh, const int* src_row, const int* total_rows, void* q, float* s,
-                        int s_stride, int cap, int K, int pow2, cudaStream_t stream) {
+                        int s_stride, int cap, int K, int pow2, int zero_padding, cudaStream_t stream) {
   using namespace bg;
   if (cap <= 0) return 0;
   if (K % 128 != 0) return -1;
   moe_gather_quant_kernel<<<cap, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, src_row,
-                                                   total_rows, reinterpret_cast<uint8_t*>(q), s, s_stride, K, pow2);
+                                                   total_rows, reinterpret_cast<uint8_t*>(q), s, s_stride, K, pow2, zero_padding);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

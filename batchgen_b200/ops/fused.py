@@ -24,8 +24,11 @@ def _scale_buffer(T: int, KB: int, device) -> torch.Tensor:
 
 
 def act_quant(x: torch.Tensor, pow2_scale: bool = False, silu_mul: bool = False,
-              valid_rows: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """1x128 e4m3 quantisation of x [T, K] (or of silu(x[:, :K]) * x[:, K:] when ``silu_mul``)."""
+              valid_rows: Optional[torch.Tensor] = None,
+              row_src: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """1x128 e4m3 quantisation of x [T, K] (or of silu(x[:, :K]) * x[:, K:] when ``silu_mul``).
+    ``valid_rows`` (device int) bounds the rows processed; ``row_src`` (int32 [T]) marks padding rows of
+    expert segments with a negative value: they are skipped (their outputs stay undefined)."""
     if not x.is_cuda:
         y = ref.silu_mul(x) if silu_mul else x
         return ref.act_quant(y, 128, pow2_scale)
@@ -37,7 +40,7 @@ def act_quant(x: torch.Tensor, pow2_scale: bool = False, silu_mul: bool = False,
     rc = _ext.lib().bg_act_quant(ctypes.c_int(1 if silu_mul else 0), _ext.ptr(x), _ext.ptr(q), _ext.ptr(s),
                                  ctypes.c_int(s.stride(1)), ctypes.c_int(T), ctypes.c_int(K),
                                  ctypes.c_int(x.stride(0)), ctypes.c_int(int(pow2_scale)), _ext.ptr(valid_rows),
-                                 _ext.stream())
+                                 _ext.ptr(row_src), _ext.stream())
     _ext.check(rc, "bg_act_quant")
     return q, s
 

@@ -75,9 +75,11 @@ def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
 
 def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
                      offsets: torch.Tensor, out: Optional[torch.Tensor] = None,
-                     silu_mul: bool = False) -> torch.Tensor:
+                     silu_mul: bool = False, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ragged grouped GEMM.  xq: [R, K] rows grouped by expert, segment e = offsets[e]:offsets[e+1]
-    (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K]."""
+    (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K].  ``counts`` (int32 [E],
+    device) gives the rows really present in each segment: padding rows are then neither stored nor, as
+    whole tiles, computed (their output rows stay undefined)."""
     E, N, K = wq.shape
     R = xq.shape[0]
     if not xq.is_cuda:
@@ -93,6 +95,9 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
         return out
     s, stride = _scales_kb_major(xs)
     assert offsets.dtype == torch.int32 and offsets.is_cuda
+    if counts is not None:
+        assert counts.dtype == torch.int32 and counts.is_cuda and counts.numel() >= E
+        _ext.lib().bg_gemm_set_counts(_ext.ptr(counts))
     _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq.view(E * N, K), ws, out,
             offsets, E, R, N, K)
     return out

@@ -112,11 +112,15 @@ def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.
                                    ctypes.c_int(hi), ctypes.c_int(ROW_ALIGN), _ext.ptr(offsets), _ext.ptr(cursor),
                                    _ext.ptr(pos), _ext.ptr(src), ctypes.c_int(cap), _ext.ptr(num_valid), _ext.stream())
     _ext.check(rc, "bg_moe_permute", kernels=2)
+    offsets.real_counts = cursor          # after the scatter pass: rows really present in each segment
     return src, pos, offsets
 
 
-def gather_quant(hidden: torch.Tensor, src_row: torch.Tensor, offsets: torch.Tensor, pow2_scale: bool = False):
-    """Gather hidden rows into expert-grouped order and quantise -> (q [cap, K] e4m3, s [cap, K/128])."""
+def gather_quant(hidden: torch.Tensor, src_row: torch.Tensor, offsets: torch.Tensor, pow2_scale: bool = False,
+                 zero_padding: bool = True):
+    """Gather hidden rows into expert-grouped order and quantise -> (q [cap, K] e4m3, s [cap, K/128]).
+    Padding rows of a segment become zeros, or stay undefined with ``zero_padding=False`` (for a grouped
+    GEMM that is given the real row counts)."""
     K = hidden.shape[1]
     if not hidden.is_cuda:
         rows = hidden[src_row.clamp_min(0).long()].float()
@@ -128,7 +132,7 @@ def gather_quant(hidden: torch.Tensor, src_row: torch.Tensor, offsets: torch.Ten
     rc = _ext.lib().bg_moe_gather_quant(_ext.ptr(hidden), ctypes.c_int(hidden.stride(0)), _ext.ptr(src_row),
                                         _ext.ptr(offsets[-1:]), _ext.ptr(q), _ext.ptr(s), ctypes.c_int(s.stride(1)),
                                         ctypes.c_int(cap), ctypes.c_int(K), ctypes.c_int(int(pow2_scale)),
-                                        _ext.stream())
+                                        ctypes.c_int(int(zero_padding)), _ext.stream())
     _ext.check(rc, "bg_moe_gather_quant")
     return q, s
 
@@ -159,9 +163,10 @@ def _activation(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
 
 
 def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None,
-                    timer=None):
+                    timer=None, counts: Optional[torch.Tensor] = None, row_src: Optional[torch.Tensor] = None):
     """Run gate/up -> activation -> down for rows already grouped by expert.  fp8 path takes
-    (xq, xs); the unquantised path takes ``x_dense``.  Returns y [rows, Hout]."""
+    (xq, xs); the unquantised path takes ``x_dense``.  Returns y [rows, Hout].  With ``counts`` (real rows
+    per segment) and ``row_src`` (negative on padding rows) the padding rows are skipped end to end."""
     if timer is None:
         from ..utils.timing import null_timer
         timer = null_timer()
@@ -169,11 +174,11 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         if xq.is_cuda:
             assert ew.interleaved, "call ExpertWeights.to_device_layout() after loading"
             with timer.timed("moe.s1_gemm"):
-                act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True)
+                act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True, counts=counts)
             with timer.timed("moe.act_quant"):
-                aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:])
+                aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:], row_src=row_src)
             with timer.timed("moe.s3_gemm"):
-                return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
+                return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets, counts=counts)
         gu = ref.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets)
         act = _activation(gu, ew.activation)
         aq, as_ = ref.act_quant(act)
@@ -213,9 +218,11 @@ def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.
     with timer.timed("moe.permute"):
         src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid)
     if ew.quant == "fp8_block":
+        counts = getattr(offsets, "real_counts", None)
         with timer.timed("moe.gather_quant"):
-            xq, xs = gather_quant(hidden, src, offsets)
-        y = grouped_experts(xq, xs, offsets, ew, timer=timer)
+            xq, xs = gather_quant(hidden, src, offsets, zero_padding=counts is None)
+        y = grouped_experts(xq, xs, offsets, ew, timer=timer, counts=counts,
+                            row_src=src if counts is not None else None)
     else:
         rows = hidden[src.clamp_min(0).long()]
         rows = torch.where((src >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))

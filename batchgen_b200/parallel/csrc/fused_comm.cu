@@ -211,6 +211,7 @@ ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers
 // Step 2 (one block): wait for every rank's counts, then derive
 //   row_base[e]   first row, in the receive buffer of e's owner, for this rank's tokens of expert e
 //   offsets[El+1] segment offsets (128-aligned) of this rank's own receive buffer
+//   offsets[El+1 .. 2El+1)  real row count of each local expert's segment
 //   cursor[e] = 0
 __global__ void __launch_bounds__(1024)
 ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, Epoch epoch_e, int E, int world,
@@ -248,7 +249,10 @@ ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_r
     for (int j = 0; j < El; ++j) {
       const int e = d * El + j;
       seg[e] = run;
-      if (d == my_rank) offsets[j] = run;
+      if (d == my_rank) {
+        offsets[j] = run;
+        offsets[El + 1 + j] = tot[e];      // rows really present in the segment (the rest is alignment padding)
+      }
       run += ((tot[e] + align - 1) / align) * align;
     }
     if (d == my_rank) {

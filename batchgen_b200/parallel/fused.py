@@ -93,7 +93,10 @@ class FusedComm(NcclComm):
         self.counters = torch.zeros(8, dtype=torch.int32, device=dev)
         self.row_base = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self.cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
-        self.offsets = torch.zeros(num_experts // W + 1, dtype=torch.int32, device=dev)
+        El = num_experts // W
+        self.offsets_buf = torch.zeros(2 * El + 1, dtype=torch.int32, device=dev)   # [El + 1 offsets | El real counts]
+        self.offsets = self.offsets_buf[: El + 1]
+        self.recv_counts = self.offsets_buf[El + 1:]
         self.total_rows = torch.zeros(1, dtype=torch.int32, device=dev)
         self.sent_row = torch.zeros(Tl * top_k, dtype=torch.int32, device=dev)
         self.ident_pos = torch.arange(Tl * top_k, dtype=torch.int32, device=dev)
@@ -243,7 +246,8 @@ class FusedComm(NcclComm):
         xs = self.recv_s.t()[: self.recv_cap]
         with timer.timed("moe.s1_gemm"):
             self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
-            act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True)
+            act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
+                                            counts=self.recv_counts)
         with timer.timed("moe.act_quant"):
             aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
@@ -253,7 +257,7 @@ class FusedComm(NcclComm):
                             done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
             out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
             gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets,
-                                      out=_StrideCarrier(out_stub, self.recv_cap))
+                                      out=_StrideCarrier(out_stub, self.recv_cap), counts=self.recv_counts)
         self.nvlink_bytes += Tl * K * H * 2 * (W - 1) // W
         with timer.timed("moe.return_wait_combine"):
             rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),

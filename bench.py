@@ -60,6 +60,8 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the decode step eagerly instead of as a CUDA graph")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     ap.add_argument("--profile-ops", default="", help="write a per-operator CUDA-event breakdown to this file")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -250,7 +252,11 @@ def main() -> int:
         decode_step_device()
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     l0 = _ext.LAUNCHES["count"]
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     ms = timed(decode_step_device, args.steps)
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     launches = _ext.LAUNCHES["count"] - l0
     clocks = sampler.stop() if sampler else {}
     _ext.check_status()
