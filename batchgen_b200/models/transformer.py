@@ -265,8 +265,13 @@ class Transformer:
         k = ref.apply_rope(k, cos, sin, cfg.rope_interleaved)
         kvc = cache.latent(l)                           # [P, page, 2 * Hkv_total * D]; this rank's slice is cached
         ref.kv_cache_write(kvc, torch.cat([k.reshape(T, -1), v.reshape(T, -1)], -1), meta.slot_mapping)
-        out = torch.zeros(T, Hq, D, dtype=x.dtype, device=x.device)
         window = cfg.sliding_window if (cfg.sliding_window and l % 2 == 0) else 0
+        if meta.mode == "decode" and x.is_cuda:
+            # paged flash-decoding kernel: lengths stay on the device (graph capturable)
+            o = attn_ops.gqa_decode(q.contiguous(), kvc, meta.block_table, meta.seqlens, Hkv, cfg.softmax_scale,
+                                    window=window, sinks=lw.sinks)
+            return linear(o.reshape(T, -1), lw.wo)
+        out = torch.zeros(T, Hq, D, dtype=x.dtype, device=x.device)
         if meta.mode == "decode":
             spans = [(b, b + 1, b, int(meta.seqlens[b]) - 1) for b in range(T)]
         else:

@@ -71,3 +71,49 @@ def mla_out_absorb(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:
         _head_gemm(o_lat.view(T, H * L), L, L, w_uv, out, out.stride(0), V)
         return out
     return torch.bmm(o_lat.transpose(0, 1), w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
+
+
+_GQA_SCRATCH = {}
+
+
+def gqa_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, seqlens: torch.Tensor, num_kv_heads: int,
+               scale: float, window: int = 0, sinks: Optional[torch.Tensor] = None, num_splits: int = 0) -> torch.Tensor:
+    """Paged GQA decode.  q [B, Hq, D]; cache [P, page, 2 * Hkv * D] (K heads then V heads per token);
+    seqlens [B] int32 = tokens visible to each query (its own included) -> [B, Hq, D].  ``window`` > 0 limits
+    every query to its last ``window`` positions; ``sinks`` [Hq] joins the softmax denominator."""
+    B, Hq, D = q.shape
+    page = cache.shape[1]
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128)):
+        out = torch.zeros_like(q)
+        for b in range(B):
+            L = int(seqlens[b])
+            kv = ref.gather_paged(cache, block_table[b], L)
+            ks = kv[:, : num_kv_heads * D].reshape(L, num_kv_heads, D)
+            vs = kv[:, num_kv_heads * D:].reshape(L, num_kv_heads, D)
+            out[b:b + 1] = ref.gqa_attention(q[b:b + 1], ks, vs, scale, q_start=L - 1, window=window, sinks=sinks)
+        return out
+    q = q.contiguous()
+    if num_splits <= 0:
+        ctas = B * num_kv_heads
+        sms = _ext.num_sms(q.device)
+        max_tiles = max(1, (block_table.shape[1] * page) // 64)
+        if window > 0:
+            max_tiles = min(max_tiles, window // 64 + 2)
+        num_splits = max(1, min(16, -(-2 * sms // ctas), max_tiles))
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if num_splits > 1:
+        key = (str(q.device), B * Hq * num_splits, D)
+        buf = _GQA_SCRATCH.get(key)
+        if buf is None:
+            buf = (torch.empty(B * Hq * num_splits * D, dtype=torch.float32, device=q.device),
+                   torch.empty(B * Hq * num_splits * 2, dtype=torch.float32, device=q.device))
+            _GQA_SCRATCH[key] = buf
+        part_o, part_ml = buf
+    rc = _ext.lib().bg_gqa_decode(_ext.ptr(q), _ext.ptr(cache), _ext.ptr(block_table), ctypes.c_int(block_table.stride(0)),
+                                  _ext.ptr(seqlens), _ext.ptr(sinks.float().contiguous() if sinks is not None else None),
+                                  _ext.ptr(out), _ext.ptr(part_o), _ext.ptr(part_ml), ctypes.c_int(B), ctypes.c_int(Hq),
+                                  ctypes.c_int(num_kv_heads), ctypes.c_int(D), ctypes.c_int(page), ctypes.c_int(window),
+                                  ctypes.c_float(scale), ctypes.c_int(num_splits), _ext.stream())
+    _ext.check(rc, "bg_gqa_decode", kernels=2 if num_splits > 1 else 1)
+    return out
