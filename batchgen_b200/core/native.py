@@ -307,3 +307,147 @@ def cpu_gqa_decode(q: torch.Tensor, k_pages: Sequence[Sequence[int]], v_pages: S
     if rc != 0:
         raise ValueError("bad GQA geometry")
     return out
+
+
+class ParameterStore:
+    """Node-shared weight region: the server creates it and loads converted checkpoint shards into it with
+    parallel readers; workers attach by descriptor and read tensors as views (optionally pinned for DMA).
+
+    Reference parity: core/Parameter_Server/Parameter_Server.cpp (allocate + read), core/Weights_Storage/
+    Weights_Storage.h:70-178 (worker-side attach, cudaHostRegister, per-module tensor map)."""
+
+    def __init__(self, nbytes: int = 0, fd: Optional[int] = None, huge_pages: bool = True, read_only: bool = False):
+        L = lib()
+        L.bgc_pstore_create.restype = ctypes.c_void_p
+        L.bgc_pstore_attach.restype = ctypes.c_void_p
+        L.bgc_pstore_base.restype = ctypes.c_void_p
+        L.bgc_pstore_bytes.restype = ctypes.c_ulonglong
+        if fd is None:
+            out = ctypes.c_int(-1)
+            self._h = L.bgc_pstore_create(ctypes.c_ulonglong(nbytes), ctypes.c_int(int(huge_pages)), ctypes.byref(out))
+            self.fd = out.value
+        else:
+            self._h = L.bgc_pstore_attach(ctypes.c_int(fd), ctypes.c_int(int(read_only)))
+            self.fd = fd
+        if not self._h:
+            raise MemoryError("parameter store: could not create or attach the shared region")
+        self.nbytes = int(L.bgc_pstore_bytes(ctypes.c_void_p(self._h)))
+        self.base = int(L.bgc_pstore_base(ctypes.c_void_p(self._h)))
+        self.index: Dict[str, Tuple[int, torch.dtype, Tuple[int, ...]]] = {}
+        self._pinned = False
+
+    def load_converted(self, ckpt_dir: str, threads: int = 8) -> int:
+        """Read every ``*.bin`` shard of a converted checkpoint (see ``ckpt.converter``) back to back into the
+        region and index its tensors.  Returns the bytes loaded."""
+        import glob
+        import json
+        import os
+        metas = sorted(glob.glob(os.path.join(ckpt_dir, "*.json")))
+        paths, offs, sizes = [], [], []
+        cur = 0
+        for m in metas:
+            with open(m) as f:
+                meta = json.load(f)
+            n = int(meta["total_byte_size"])
+            paths.append(os.path.join(ckpt_dir, meta["file_name"]).encode())
+            offs.append(cur)
+            sizes.append(n)
+            for name, t in meta["state_dict"].items():
+                self.index[name] = (cur + int(t["offset"]), getattr(torch, t["dtype"].replace("torch.", "")), tuple(t["shape"]))
+            cur += (n + 255) // 256 * 256
+        if cur > self.nbytes:
+            raise MemoryError(f"checkpoint needs {cur} bytes, the store holds {self.nbytes}")
+        arr = (ctypes.c_char_p * len(paths))(*paths)
+        o = (ctypes.c_ulonglong * len(paths))(*offs)
+        z = (ctypes.c_ulonglong * len(paths))(*sizes)
+        rc = lib().bgc_pstore_load_files(ctypes.c_void_p(self._h), arr, o, z, ctypes.c_int(len(paths)), ctypes.c_int(threads))
+        if rc != 0:
+            raise OSError(f"parameter store: reading {paths[-rc - 1].decode()} failed")
+        return sum(sizes)
+
+    @staticmethod
+    def bytes_needed(ckpt_dir: str) -> int:
+        import glob
+        import json
+        import os
+        total = 0
+        for m in sorted(glob.glob(os.path.join(ckpt_dir, "*.json"))):
+            with open(m) as f:
+                total += (int(json.load(f)["total_byte_size"]) + 255) // 256 * 256
+        return total
+
+    def export_index(self) -> Dict[str, Tuple[int, str, Tuple[int, ...]]]:
+        return {k: (o, str(d), s) for k, (o, d, s) in self.index.items()}
+
+    def import_index(self, idx) -> None:
+        self.index = {k: (o, getattr(torch, d.replace("torch.", "")), tuple(s)) for k, (o, d, s) in idx.items()}
+
+    def tensor(self, name: str) -> torch.Tensor:
+        off, dtype, shape = self.index[name]
+        n = 1
+        for v in shape:
+            n *= v
+        buf = (ctypes.c_char * (n * torch.empty(0, dtype=dtype).element_size())).from_address(self.base + off)
+        return torch.frombuffer(buf, dtype=dtype, count=n).view(*shape)
+
+    def loader(self):
+        """``WeightSource`` loader: name, shape -> tensor view or None."""
+        def load(name, shape):
+            return self.tensor(name) if name in self.index else None
+        return load
+
+    def pin(self) -> bool:
+        if not torch.cuda.is_available() or self._pinned:
+            return self._pinned
+        self._pinned = lib().bgc_pin_host(ctypes.c_void_p(self.base), ctypes.c_ulonglong(self.nbytes)) == 0
+        return self._pinned
+
+    def close(self) -> None:
+        if self._h:
+            if self._pinned:
+                lib().bgc_unpin_host(ctypes.c_void_p(self.base))
+            lib().bgc_pstore_destroy(ctypes.c_void_p(self._h))
+            self._h = None
+
+
+class ReplicaControlBlock:
+    """Shared-memory barrier words of a weight replica group (owner publishes a frame -> readers pull ->
+    readers acknowledge -> owner reuses the slot), with abort flags and bounded waits."""
+    OK, TIMEOUT, ABORTED = 0, 1, 2
+
+    def __init__(self, store: ParameterStore, offset: int, members: int, init: bool):
+        L = lib()
+        L.bgc_rcb_bytes.restype = ctypes.c_ulonglong
+        L.bgc_rcb_slot_frame.restype = ctypes.c_ulonglong
+        self.nbytes = int(L.bgc_rcb_bytes())
+        if offset % 64 or offset + self.nbytes > store.nbytes:
+            raise ValueError("control block must be 64-byte aligned inside the shared region")
+        self._mem = ctypes.c_void_p(store.base + offset)
+        self._store = store
+        if init and L.bgc_rcb_init(self._mem, ctypes.c_int(members)) != 0:
+            raise ValueError("replica control block: bad member count")
+
+    @staticmethod
+    def size() -> int:
+        L = lib()
+        L.bgc_rcb_bytes.restype = ctypes.c_ulonglong
+        return int(L.bgc_rcb_bytes())
+
+    def publish(self, member: int, mtype: int, slot: int, frame: int) -> None:
+        if lib().bgc_rcb_publish(self._mem, member, mtype, slot, ctypes.c_ulonglong(frame)) != 0:
+            raise ValueError("publish: bad arguments or uninitialised block")
+
+    def wait_published(self, owner: int, mtype: int, frame: int, timeout_ms: int = 300_000) -> int:
+        return lib().bgc_rcb_wait_published(self._mem, owner, mtype, ctypes.c_ulonglong(frame), timeout_ms)
+
+    def ack_pulled(self, member: int, mtype: int, frame: int) -> None:
+        lib().bgc_rcb_ack_pulled(self._mem, member, mtype, ctypes.c_ulonglong(frame))
+
+    def wait_all_pulled(self, owner: int, mtype: int, frame: int, timeout_ms: int = 300_000) -> int:
+        return lib().bgc_rcb_wait_all_pulled(self._mem, owner, mtype, ctypes.c_ulonglong(frame), timeout_ms)
+
+    def slot_frame(self, member: int, slot: int) -> int:
+        return int(lib().bgc_rcb_slot_frame(self._mem, member, slot))
+
+    def abort(self, member: int) -> None:
+        lib().bgc_rcb_abort(self._mem, member)

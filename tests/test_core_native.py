@@ -164,3 +164,65 @@ def test_cpu_gqa_decode_matches_reference():
             v = vs[b].reshape(-1, Hkv, D)[:L].float()
             want = ref.gqa_attention(q[b:b + 1], k, v, D ** -0.5, q_start=L - 1, window=window)[0]
             assert torch.allclose(out[b], want, atol=2e-4, rtol=1e-3), (b, window)
+
+
+def test_parameter_store_loads_converted_checkpoint_and_shares_it(tmp_path):
+    import multiprocessing as mp
+
+    import torch
+
+    from batchgen_b200.ckpt import converter
+    from batchgen_b200.core.native import ParameterStore
+    g = torch.Generator().manual_seed(0)
+    shards = {"a": {"w1": torch.randn(33, 7, generator=g), "w2": torch.arange(10, dtype=torch.int32)},
+              "b": {"w3": torch.randn(5, 5, generator=g).to(torch.bfloat16)}}
+    out = tmp_path / "conv"
+    for name, tensors in shards.items():
+        converter.convert_shard(str(tmp_path / f"{name}.pt"), str(out), tensors=tensors)
+    store = ParameterStore(ParameterStore.bytes_needed(str(out)) + 4096)
+    assert store.load_converted(str(out), threads=3) > 0
+    for tensors in shards.values():
+        for k, v in tensors.items():
+            assert torch.equal(store.tensor(k), v)
+    idx = store.export_index()
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+
+    def child():
+        w = ParameterStore(fd=store.fd, read_only=True)
+        w.import_index(idx)
+        q.put(float(w.tensor("w1").sum()))
+        w.close()
+
+    p = ctx.Process(target=child)
+    p.start()
+    assert abs(q.get(timeout=20) - float(shards["a"]["w1"].sum())) < 1e-4
+    p.join(20)
+    store.close()
+
+
+def test_replica_control_block_barriers_and_abort():
+    import threading
+
+    from batchgen_b200.core.native import ParameterStore, ReplicaControlBlock
+    store = ParameterStore(ReplicaControlBlock.size() + 4096)
+    owner = ReplicaControlBlock(store, 0, members=3, init=True)
+    readers = [ReplicaControlBlock(store, 0, members=3, init=False) for _ in range(2)]
+    assert readers[0].wait_published(0, 1, frame=1, timeout_ms=30) == ReplicaControlBlock.TIMEOUT
+    got = []
+
+    def reader(i):
+        rc = readers[i - 1].wait_published(0, 1, frame=1, timeout_ms=5000)
+        got.append((i, rc, readers[i - 1].slot_frame(0, 4)))
+        readers[i - 1].ack_pulled(i, 1, 1)
+
+    ts = [threading.Thread(target=reader, args=(i,)) for i in (1, 2)]
+    [t.start() for t in ts]
+    owner.publish(0, 1, slot=4, frame=1)
+    assert owner.wait_all_pulled(0, 1, frame=1, timeout_ms=5000) == ReplicaControlBlock.OK
+    [t.join() for t in ts]
+    assert sorted(got) == [(1, 0, 1), (2, 0, 1)]
+    assert owner.wait_all_pulled(0, 1, frame=2, timeout_ms=30) == ReplicaControlBlock.TIMEOUT
+    readers[1].abort(2)                                           # a member leaves: waits end at once, by name
+    assert owner.wait_all_pulled(0, 1, frame=2, timeout_ms=5000) == ReplicaControlBlock.ABORTED
+    store.close()
