@@ -126,3 +126,92 @@ def test_runtime_locks_and_reclaim(tmp_path):
     assert not (shm / "bg_run-abc123_kv").exists() and (shm / "other").exists()
     with pytest.raises(rl.RuntimeLockError):
         rl.hold_run_lock(tmp_path / "nowhere")
+
+
+def test_process_utils_and_hugepage_plan():
+    import multiprocessing as mp
+    import os
+    import signal
+
+    from batchgen_b200.server import process_utils as pu
+    assert pu.hugepage_plan(3 << 30, free_1g=4).kind == "1g"
+    assert pu.hugepage_plan(3 << 30, free_1g=2, free_2m=2000).kind == "2m"
+    assert pu.hugepage_plan(3 << 30).kind == "base" and pu.hugepage_plan(100 << 20, free_1g=8, free_2m=100).kind == "2m"
+    assert set(pu.read_hugepage_pools()) == {"free_2m", "free_1g"}
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+
+    def middle():
+        def grandchild():
+            pu.die_with_parent(signal.SIGKILL)
+            q.put(os.getpid())
+            import time
+            time.sleep(60)
+        p = ctx.Process(target=grandchild)
+        p.start()
+        q.put(("ready", None))
+        import time
+        time.sleep(60)
+
+    m = ctx.Process(target=middle)
+    m.start()
+    got = [q.get(timeout=20), q.get(timeout=20)]
+    gpid = next(g for g in got if isinstance(g, int))
+    m.kill()                                                      # the server dies hard ...
+    m.join(10)
+    import time
+    for _ in range(100):                                          # ... and its worker follows
+        try:
+            os.kill(gpid, 0)
+            time.sleep(0.05)
+        except ProcessLookupError:
+            break
+    else:
+        os.kill(gpid, signal.SIGKILL)
+        raise AssertionError("grandchild survived its parent")
+
+
+def test_launch_readiness_gates(tmp_path):
+    import socket
+
+    from batchgen_b200.server import launch_readiness as lr
+    rep = lr.check_node(None, str(tmp_path / "run"), str(tmp_path / "store"), "127.0.0.1", [], gpus=2, gpu_count_fn=lambda: 1)
+    assert not rep.ok and [f.name for f in rep.failures()] == ["gpus"]
+    assert not lr.gate_model_dir(str(tmp_path)).ok
+    (tmp_path / "m.bin").write_bytes(b"x")
+    (tmp_path / "m.json").write_text("{}")
+    assert lr.gate_model_dir(str(tmp_path)).ok
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        s.listen(1)
+        port = s.getsockname()[1]
+        assert not lr.gate_port_free("127.0.0.1", port).ok
+    t = [0.0]
+    res = lr.gate_path_appears(str(tmp_path / "never"), 1.0, clock=lambda: t[0], sleep=lambda d: t.__setitem__(0, t[0] + d))
+    assert not res.ok and "did not appear" in res.detail
+    assert lr.gate_free_space("space", str(tmp_path), 1).ok and not lr.gate_free_space("space", str(tmp_path), 1 << 60).ok
+    assert '"ok": false' in rep.to_json()
+
+
+def test_weight_store_staging_is_idempotent_and_detects_damage(tmp_path):
+    from batchgen_b200.server import weight_store_staging as ws
+    src = tmp_path / "src"
+    src.mkdir()
+    for i in range(4):
+        (src / f"shard{i}.bin").write_bytes(bytes([i]) * (1000 + i))
+        (src / f"shard{i}.json").write_text(f'{{"i": {i}}}')
+    dst = tmp_path / "tmpfs"
+    a = ws.stage_store(str(src), str(dst))
+    assert not a.reused and a.copied_bytes > 4000 and ws.verify_store(str(dst), check_digests=True) is None
+    b = ws.stage_store(str(src), str(dst))
+    assert b.reused and b.copied_bytes == 0 and b.listing_digest == a.listing_digest
+    (dst / "shard2.bin").write_bytes(b"short")
+    assert "shard2.bin" in ws.verify_store(str(dst))
+    c = ws.stage_store(str(src), str(dst))
+    assert not c.reused and c.copied_bytes == 1002 and ws.verify_store(str(dst), True) is None
+    part = ws.stage_store(str(src), str(tmp_path / "node1"), partition=(1, 2))
+    assert sorted(part.files) == ["shard1.bin", "shard1.json", "shard3.bin", "shard3.json"]
+    (src / "orphan.bin").write_bytes(b"x")
+    import pytest as _pt
+    with _pt.raises(FileNotFoundError):
+        ws.stage_store(str(src), str(dst))
