@@ -124,6 +124,7 @@ class LayerWeights:
     w_uk: torch.Tensor = None        # [Hh, nope, kv_lora] (a view of w_uk_t)
     w_uk_t: torch.Tensor = None      # [Hh, kv_lora, nope] contiguous
     w_uv: torch.Tensor = None        # [Hh, v, kv_lora]
+    w_kvb: torch.Tensor = None       # [Hh * (nope + v), kv_lora] (CUDA, expanded prefill only)
     wo: Linear = None                # [H, Hh * v]
     # GQA
     wqkv: Linear = None              # [(Hq + 2 Hkv) * D, H]
@@ -196,6 +197,10 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
             lw.w_uk_t = kvb[:, : cfg.qk_nope_head_dim].transpose(1, 2).contiguous().to(dtype)
             lw.w_uk = lw.w_uk_t.transpose(1, 2)
             lw.w_uv = kvb[:, cfg.qk_nope_head_dim:].contiguous().to(dtype)
+            if str(dev).startswith("cuda") and cfg.qk_nope_head_dim == 128 and cfg.v_head_dim == 128 \
+                    and cfg.qk_rope_head_dim == 64 and not cfg.has_dsa:
+                # whole kv_b ([heads * (nope + v), kv_lora]) for the expanded prefill attention
+                lw.w_kvb = kvb.reshape(-1, cfg.kv_lora_rank).contiguous().to(dtype)
             wo = src.get(f"{p}.self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
             wo = wo.view(H, cfg.num_heads, cfg.v_head_dim)[:, h0:h1].reshape(H, -1)
             lw.wo = make_linear(wo, quant, dtype)

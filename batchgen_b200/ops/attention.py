@@ -117,3 +117,43 @@ def gqa_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
                                   ctypes.c_float(scale), ctypes.c_int(num_splits), _ext.stream())
     _ext.check(rc, "bg_gqa_decode", kernels=2 if num_splits > 1 else 1)
     return out
+
+
+def mha_prefill_work(cu_seqlens: Sequence[int], ctx_lens: Sequence[int], k_starts: Sequence[int]) -> torch.Tensor:
+    """Work list of the expanded-prefill kernel: one row (q_row0, n_q, k_row0, kv0) per 128-query tile; query i
+    of a tile sees the first kv0 + i keys of its sequence, whose key rows start at ``k_starts[seq]``.  Longest
+    key ranges first."""
+    rows = []
+    for i in range(len(cu_seqlens) - 1):
+        a, b = int(cu_seqlens[i]), int(cu_seqlens[i + 1])
+        for q0 in range(a, b, 128):
+            rows.append((q0, min(128, b - q0), int(k_starts[i]), int(ctx_lens[i]) + (q0 - a) + 1))
+    rows.sort(key=lambda r: -(r[3] + r[1]))
+    return torch.tensor(rows, dtype=torch.int32).view(-1, 4)
+
+
+def mha_prefill(q: torch.Tensor, kv: torch.Tensor, kpe: torch.Tensor, work: torch.Tensor, scale: float) -> torch.Tensor:
+    """Causal varlen attention in the expanded MLA form.  q [Tq, H, 192] (nope | roped pe); kv [Tk, H, 256]
+    (key nope | value, the kv_b projection of the latent rows); kpe [Tk, >= 64] (roped shared key part in the
+    first 64 columns, may be a strided view); ``work`` from ``mha_prefill_work`` -> [Tq, H, 128]."""
+    Tq, H, _ = q.shape
+    Tk = kv.shape[0]
+    if not (q.is_cuda and q.dtype == torch.bfloat16):
+        out = torch.zeros(Tq, H, 128, dtype=q.dtype)
+        kf = torch.cat([kv[..., :128].float(), kpe[:, None, :64].float().expand(Tk, H, 64)], -1)
+        vf = kv[..., 128:].float()
+        for q0, nq, k0, kv0 in work.tolist():
+            for i in range(nq):
+                n = kv0 + i
+                s = torch.einsum("hd,khd->hk", q[q0 + i].float(), kf[k0:k0 + n]) * scale
+                out[q0 + i] = torch.einsum("hk,khd->hd", torch.softmax(s, -1), vf[k0:k0 + n]).to(q.dtype)
+        return out
+    assert q.is_contiguous() and kv.is_contiguous() and kpe.stride(1) == 1
+    out = torch.empty(Tq, H, 128, dtype=torch.bfloat16, device=q.device)
+    work = work.to(q.device)
+    rc = _ext.lib().bg_mha_prefill(_ext.ptr(q), _ext.ptr(kv), _ext.ptr(kpe), ctypes.c_longlong(kpe.stride(0)), _ext.ptr(out),
+                                   _ext.ptr(work), ctypes.c_int(work.shape[0]), ctypes.c_int(Tq), ctypes.c_int(Tk),
+                                   ctypes.c_int(H), ctypes.c_float(scale), _ext.ptr(_ext.status_word(q.device)),
+                                   _ext.stream())
+    _ext.check(rc, "bg_mha_prefill")
+    return out

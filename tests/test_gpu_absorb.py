@@ -58,3 +58,58 @@ def test_grouped_gemm_with_real_counts():
             assert _rel(out[a:a + n], want[a:a + n]) < 1e-2
         pad_end = offsets[e + 1].item()
         assert (out[a + n:pad_end] == sentinel).all(), "padding rows must not be stored"
+
+
+@pytest.mark.parametrize("H", [4, 16])
+def test_expanded_mla_prefill_attention(H):
+    """Varlen causal attention over up-projected keys / values, with cached context on one sequence."""
+    from batchgen_b200.ops import _ext, attention
+    g = torch.Generator().manual_seed(H)
+    lens, ctx = [300, 70, 129], [0, 200, 64]                 # new tokens and cached context per sequence
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    k_starts, tk = [], 0
+    for n, c in zip(lens, ctx):
+        k_starts.append(tk)
+        tk += n + c
+    Tq = cu[-1]
+    q = (torch.randn(Tq, H, 192, generator=g) * 0.5).to(torch.bfloat16)
+    kv = (torch.randn(tk, H, 256, generator=g) * 0.5).to(torch.bfloat16)
+    lat = (torch.randn(tk, 576, generator=g) * 0.5).to(torch.bfloat16)
+    kpe = lat[:, 512:]                                        # strided view, as the model passes it
+    work = attention.mha_prefill_work(cu, ctx, k_starts)
+    scale = 192 ** -0.5
+    got = attention.mha_prefill(q.cuda(), kv.cuda(), lat.cuda()[:, 512:], work, scale).cpu().float()
+    _ext.check_status()
+    want = attention.mha_prefill(q.float(), kv.float(), kpe.float(), work, scale)
+    assert _rel(got, want) < 1.5e-2
+
+
+def test_model_prefill_uses_expanded_attention_and_matches_cpu():
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.models.transformer import AttnMeta
+    from batchgen_b200.runtime.kv_cache import PagedKVCache, build_block_table, slots_for_range
+    cfg = get_model_config("tiny-deepseek-v3", hidden_size=1024, q_lora_rank=512, kv_lora_rank=512,
+                           qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_heads=16,
+                           intermediate_size=2048, moe_intermediate_size=512, n_routed_experts=16,
+                           num_experts_per_tok=4, n_group=4, topk_group=2, vocab_size=4096, quant="fp8_block")
+    lens = [330, 200]
+    ids = torch.randint(2, cfg.vocab_size, (sum(lens),), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+
+    def run(device, dtype_name, dtype):
+        model = build_model(cfg, device, dtype_name, seed=0)
+        kv = PagedKVCache(cfg, 16, 64, device, dtype)
+        pages = [kv.alloc.alloc((n + 63) // 64) for n in lens]
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(device)
+        slots = torch.tensor(sum((slots_for_range(p, 0, n, 64) for p, n in zip(pages, lens)), []), device=device)
+        meta = AttnMeta(mode="prefill", positions=pos, slot_mapping=slots, block_table=build_block_table(pages, device),
+                        cu_seqlens=[0, lens[0], sum(lens)], ctx_lens=[0, 0])
+        return model, model.forward(ids.to(device), meta, kv).float().cpu()
+
+    _, cpu = run("cpu", "fp32", torch.float32)
+    model, gpu = run("cuda", "bf16", torch.bfloat16)
+    assert model.w.layers[0].w_kvb is not None
+    rel = ((gpu - cpu).norm() / cpu.norm()).item()
+    assert rel < 0.08, rel
