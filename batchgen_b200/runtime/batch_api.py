@@ -122,6 +122,8 @@ def prompt_ids(req: BatchRequest, tokenizer) -> List[int]:
         except TypeError:
             return list(tokenizer.apply_chat_template(req.body["messages"], add_generation_prompt=True))
     p = req.body["prompt"]
+    if isinstance(p, list) and p and all(isinstance(t, int) for t in p):
+        return list(p)                      # pre-tokenised prompt (array of token ids), as the completions API allows
     return list(tokenizer.encode(p))
 
 

@@ -104,3 +104,27 @@ def test_eventlog_schema_and_flight_recorder(tmp_path):
     c.bump("decode_steps")
     c.bump("decode_steps", 2)
     assert c.c["decode_steps"] == 3 and not c.maybe_flush() and c.maybe_flush(force=True)
+
+
+def test_workload_profiles_and_driver_roundtrip(tmp_path):
+    """Synthetic workload files of the benchmark configurations run through the offline batch API."""
+    import json
+    import subprocess
+    import sys
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).resolve().parent.parent))
+    from benchmarks import workloads as wl
+    p = wl.scaled(wl.PROFILES["long-grouped"], 1 / 2048)
+    lines = list(wl.batch_lines(p, 1000, seed=1))
+    assert len(lines) == p.requests and p.groups >= 1
+    a, b = json.loads(lines[0])["body"]["prompt"], json.loads(lines[1])["body"]["prompt"]
+    assert a[: len(a) - p.suffix_tokens] == b[: len(b) - p.suffix_tokens]        # members of a group share the prefix
+    assert wl.summary(wl.PROFILES["mixed-1k"])["decode_tokens_total"] == 512 * 1024
+    path = tmp_path / "tiny.jsonl"
+    path.write_text("\n".join(wl.batch_lines(wl.PROFILES["tiny"], 1024)) + "\n")
+    root = str(__import__("pathlib").Path(__file__).resolve().parent.parent)
+    out = subprocess.run([sys.executable, "benchmarks/batch_driver.py", str(path), "--model", "tiny-deepseek-v3"],
+                         cwd=root, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["prompt_tokens"] == 8 * 32 and res["decode_tokens"] == 8 * 16 and res["bct_s"] > 0
+    assert res["stats"]["completed"] == 8
