@@ -88,6 +88,7 @@ class Transformer:
         self.dtype = weights.embed.dtype
         self.rope = RopeTables(cfg, max_positions, self.device)
         self.timer = null_timer()     # utils.timing.TimingStats when profiling
+        self.streamer = None          # models.streaming.StreamedExperts when the routed experts live in host memory
         self.expanded_prefill_min_tokens = 256   # below this the absorbed kernel is as fast and saves the kv_b GEMM
 
     # ------------------------------------------------------------------ helpers
@@ -322,12 +323,15 @@ class Transformer:
         h = x
         if cfg.moe_latent_size:
             h = linear(x, lw.latent_down)
+        ew = lw.experts if self.streamer is None else self.streamer.get(l)     # streamed: blocks until the slot landed
         with tm.timed("moe.routed_experts", l):
             if self.comm is not None and self.layout.ep_size > 1:
-                routed = self.comm.moe(h, idx, w, lw.experts, cfg.n_routed_experts, num_valid=meta.num_valid)
+                routed = self.comm.moe(h, idx, w, ew, cfg.n_routed_experts, num_valid=meta.num_valid)
             else:
-                routed = moe_ops.experts_forward(h, idx, w, lw.experts, 0, cfg.n_routed_experts,
+                routed = moe_ops.experts_forward(h, idx, w, ew, 0, cfg.n_routed_experts,
                                                  num_valid=meta.num_valid, timer=tm)
+        if self.streamer is not None:
+            self.streamer.release(l)               # the slot returns once the kernels queued above have run
         if cfg.moe_latent_size:
             routed = linear(fused.rmsnorm(routed, lw.latent_norm, cfg.rms_eps)[0], lw.latent_up)
         return routed if shared is None else routed + shared
@@ -370,6 +374,8 @@ class Transformer:
             logits = (x @ self.w.lm_head.t()).float()
         if tp:
             logits = self.comm.tp_gather_vocab(logits)
+        if self.streamer is not None:
+            self.streamer.end_step()
         return logits
 
     # ------------------------------------------------------------------ sequence-parallel forward

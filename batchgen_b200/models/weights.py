@@ -156,7 +156,7 @@ class ModelWeights:
 
 
 def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, dtype: torch.dtype,
-                  alias_experts_every: int = 0) -> ModelWeights:
+                  alias_experts_every: int = 0, experts_on_host: bool = False) -> ModelWeights:
     """Create this rank's weights.  ``alias_experts_every`` > 0 makes MoE layers share physical
     expert storage in a cycle of that many distinct sets (benchmark-only: lets a model whose
     expert bytes exceed HBM run with identical FLOPs and HBM traffic per layer)."""
@@ -280,6 +280,12 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                         w13_s=torch.stack(s13) if s13 else None, w2_s=torch.stack(s2) if s2 else None,
                         quant=equant, activation=cfg.activation).to_device_layout()
                     expert_sets[key] = lw.experts
+            if experts_on_host and lw.experts.w13.is_cuda:
+                # streamed models never hold all layers' experts on the GPU: park each set on the host at once
+                e = lw.experts
+                for f in ("w13", "w2", "w13_s", "w2_s"):
+                    if getattr(e, f) is not None:
+                        setattr(e, f, getattr(e, f).cpu())
             if cfg.n_shared_experts:
                 lw.w13, lw.w2 = mlp_pair(f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H,
                                          shard=not layout.sequence_parallel)

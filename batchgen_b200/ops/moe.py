@@ -43,9 +43,10 @@ class ExpertWeights:
     def num_experts(self) -> int:
         return self.w13.shape[0]
 
-    def to_device_layout(self) -> "ExpertWeights":
-        """Reorder w13 rows for the fused SiLU epilogue (GPU, fp8 only)."""
-        if self.quant not in ("fp8_block", "mxfp4") or self.interleaved or not self.w13.is_cuda:
+    def to_device_layout(self, force: bool = False) -> "ExpertWeights":
+        """Reorder w13 rows for the fused SiLU epilogue (quantised experts; on CUDA tensors, or on host tensors
+        that will be streamed to the GPU when ``force``)."""
+        if self.quant not in ("fp8_block", "mxfp4") or self.interleaved or not (self.w13.is_cuda or force):
             return self
         perm = gemm.interleave_gate_up_rows(self.w13.shape[1], self.w13.device)
         if self.quant == "mxfp4":

@@ -62,3 +62,41 @@ def test_kv_mover_host_to_device_and_back(use_kernel):
     assert mover.bytes_moved == 6 * nbytes
     mover.close()
     kv.close()
+
+
+def test_streamed_fp8_experts_match_resident_on_gpu():
+    """FP8 experts parked in pinned host memory and streamed through the CUDA weight ring: same logits as the
+    resident model, every MoE layer copied once per pass, slots released on the consumer stream."""
+    import torch
+
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.models.transformer import AttnMeta
+    from batchgen_b200.ops import _ext
+    from batchgen_b200.runtime.kv_cache import PagedKVCache, build_block_table, slots_for_range
+    cfg = get_model_config("tiny-deepseek-v3", hidden_size=1024, q_lora_rank=512, kv_lora_rank=512,
+                           qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_heads=16,
+                           intermediate_size=2048, moe_intermediate_size=512, n_routed_experts=16,
+                           num_experts_per_tok=4, n_group=4, topk_group=2, vocab_size=4096, quant="fp8_block",
+                           num_layers=5, first_k_dense=1)
+    n = 100
+    ids = torch.randint(2, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).cuda()
+
+    def run(model):
+        kv = PagedKVCache(cfg, 8, 64, "cuda", torch.bfloat16)
+        pages = kv.alloc.alloc(2)
+        meta = AttnMeta(mode="prefill", positions=torch.arange(n, dtype=torch.int32, device="cuda"),
+                        slot_mapping=torch.tensor(slots_for_range(pages, 0, n, 64), device="cuda"),
+                        block_table=build_block_table([pages], "cuda"), cu_seqlens=[0, n], ctx_lens=[0])
+        out = model.forward(ids, meta, kv)
+        torch.cuda.synchronize()
+        return out
+
+    resident = run(build_model(cfg, "cuda", "bf16", seed=0))
+    streamed = build_model(cfg, "cuda", "bf16", seed=0, stream_experts=True, ring_slots=2)
+    a, b = run(streamed), run(streamed)
+    _ext.check_status()
+    assert torch.equal(a, resident) and torch.equal(b, resident)
+    st = streamed.streamer.stats()
+    assert st["modules_copied"] == 2 * 4 and st["bytes_copied"] == 2 * streamed.streamer.bytes_per_pass
+    streamed.streamer.close()
