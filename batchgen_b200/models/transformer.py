@@ -49,6 +49,7 @@ class AttnMeta:
     logit_rows: Optional[torch.Tensor] = None   # rows of T whose logits are wanted (prefill: last tokens)
     num_valid: Optional[torch.Tensor] = None    # decode under CUDA graphs: device count of real rows
     dsa_selection: dict = field(default_factory=dict)  # layer -> (sel_idx, sel_len) reused by shared layers
+    _own_slots: Optional[torch.Tensor] = None   # slot mapping masked to this rank's rows (request-parallel decode)
 
 
 class RopeTables:
@@ -88,6 +89,9 @@ class Transformer:
         self.dtype = weights.embed.dtype
         self.rope = RopeTables(cfg, max_positions, self.device)
         self.timer = null_timer()     # utils.timing.TimingStats when profiling
+        # decode attention core split by request inside the TP group (static row ownership: row i belongs to rank
+        # i // (T / world) for as long as it decodes); off by default because the engine may re-order rows
+        self.attn_request_parallel = False
         self.streamer = None          # models.streaming.StreamedExperts when the routed experts live in host memory
         self.expanded_prefill_min_tokens = 256   # below this the absorbed kernel is as fast and saves the kv_b GEMM
 
@@ -149,7 +153,10 @@ class Transformer:
             with tm.timed("attn.dsa_indexer", l):
                 sel = self._dsa_select(l, lw, x, qn, meta, cache)
         with tm.timed("attn.core_" + meta.mode, l):
-            o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
+            if self._request_parallel(meta, T):
+                o_lat = self._mla_core_request_parallel(l, q_abs, q_pe, meta, cache)
+            else:
+                o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
         # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
         with tm.timed("attn.out_absorb", l):
             return attn_ops.mla_out_absorb(o_lat, lw.w_uv)
@@ -158,12 +165,42 @@ class Transformer:
         cfg = self.cfg
         T = q_a.shape[0]
         Hh = lw.w_uk.shape[0]
-        fused.mla_kv_write(kv_a, lw.kv_norm, meta.positions, self.rope.cos, self.rope.sin, meta.slot_mapping,
+        slots = meta.slot_mapping
+        if self._request_parallel(meta, T):
+            # request-parallel attention core: a row's latent KV lives only on the rank that owns the row
+            if meta._own_slots is None:
+                W, r = self.layout.tp_size, self.layout.tp_rank
+                own = torch.zeros(T, dtype=torch.bool, device=slots.device)
+                own[r * (T // W):(r + 1) * (T // W)] = True
+                meta._own_slots = torch.where(own, slots, torch.full_like(slots, -1))
+            slots = meta._own_slots
+        fused.mla_kv_write(kv_a, lw.kv_norm, meta.positions, self.rope.cos, self.rope.sin, slots,
                            cache.latent(l), cfg.kv_lora_rank, cfg.rms_eps, cfg.rope_interleaved)
         qn, qnq, qns = fused.rmsnorm(q_a, lw.q_norm, cfg.rms_eps, quant=lw.wq_b.is_fp8)
         q = linear(qn, lw.wq_b, qnq, qns).view(T, Hh, cfg.qk_head_dim)
         fused.rope_q_(q, meta.positions, self.rope.cos, self.rope.sin, cfg.qk_rope_head_dim, cfg.rope_interleaved)
         self._q, self._qn = q, qn
+
+    def _request_parallel(self, meta: AttnMeta, T: int) -> bool:
+        return (self.attn_request_parallel and meta.mode == "decode" and self.comm is not None
+                and self.layout.tp_size > 1 and T % self.layout.tp_size == 0 and not self.cfg.has_dsa)
+
+    def _mla_core_request_parallel(self, l, q_abs, q_pe, meta: AttnMeta, cache):
+        """Decode attention with the projections head-sharded (TP) but the core split by request: an
+        all-to-all turns [all rows, my heads] queries into [my rows, all heads], each rank attends over the
+        latent KV of its own rows only (the KV is not replicated: 1/world of the bytes per rank instead of
+        all of them), and a second all-to-all returns [all rows, my heads] outputs for the out-absorb and
+        o_proj.  Row i belongs to rank i // (T / world)."""
+        W, r = self.layout.tp_size, self.layout.tp_rank
+        T, Hh, L = q_abs.shape
+        Tl = T // W
+        q = torch.cat([q_abs, q_pe], -1).view(W, Tl, Hh, -1)
+        q = self.comm.all_to_all(q).permute(1, 0, 2, 3).reshape(Tl, W * Hh, -1)
+        rows = slice(r * Tl, (r + 1) * Tl)
+        o = attn_ops.mla_decode(q[..., :L].contiguous(), q[..., L:].contiguous(), cache.latent(l),
+                                meta.block_table[rows], meta.seqlens[rows], self.cfg.softmax_scale, self.cfg.kv_lora_rank)
+        o = o.view(Tl, W, Hh, L).permute(1, 0, 2, 3)
+        return self.comm.all_to_all(o).reshape(T, Hh, L)
 
     def _mla_core(self, l, lw, q_abs, q_pe, sel, meta, cache):
         cfg = self.cfg

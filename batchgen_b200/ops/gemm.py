@@ -8,6 +8,7 @@ tensor is transposed on the fly.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -42,8 +43,44 @@ def _scales_kb_major(xs: torch.Tensor):
     return t, t.stride(0)
 
 
-def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K):
+_WIDE = os.environ.get("BG_GEMM_WIDE", "auto")       # "0": always 128x128 tiles, "1": 128x256 whenever allowed
+
+
+_hooks_pending = False     # set by the fused-communication layer right before a GEMM that consumes collective hooks
+
+
+def hooks_pending() -> None:
+    global _hooks_pending
+    _hooks_pending = True
+
+
+def _use_wide(kind, D, M, N, wide) -> bool:
+    """128 x 256 tiles pay off when there are plenty of tiles to fill the SMs; GEMMs that consume collective
+    hooks (rows stored to peers, flag waits) and bf16 operands stay on the 128 x 128 kernel."""
+    global _hooks_pending
+    if _hooks_pending:
+        _hooks_pending = False
+        return False
+    if kind != KIND_FP8 or wide is False or _WIDE == "0" or not isinstance(D, torch.Tensor):
+        return False
+    if wide is True or _WIDE == "1":
+        return True
+    tiles = -(-M // 128) * -(-N // 128)
+    return tiles >= 2 * _ext.num_sms(D.device)
+
+
+def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None):
     L = _ext.lib()
+    if _use_wide(kind, D, M, N, wide):
+        rc = L.bg_gemm_fp8_n256(ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride), _ext.ptr(B),
+                                _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets), _ext.ptr(counts),
+                                ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                                ctypes.c_int(_ext.num_sms(A.device)), ctypes.c_void_p(0), ctypes.c_uint32(0),
+                                ctypes.c_void_p(0), ctypes.c_int(1), _ext.ptr(_ext.status_word(A.device)), _ext.stream())
+        _ext.check(rc, "bg_gemm_fp8_n256")
+        return
+    if counts is not None:
+        L.bg_gemm_set_counts(_ext.ptr(counts))
     rc = L.bg_gemm(ctypes.c_int(kind), ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride),
                    _ext.ptr(B), _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets),
                    ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
@@ -52,7 +89,7 @@ def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K):
 
 
 def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
-             out: Optional[torch.Tensor] = None, silu_mul: bool = False) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, silu_mul: bool = False, wide: Optional[bool] = None) -> torch.Tensor:
     """[T, K] e4m3 x [N, K] e4m3 -> [T, N] (bf16 on GPU).  With ``silu_mul`` the weight must be in
     the interleaved gate/up layout and the result has N/2 columns."""
     T, K = xq.shape
@@ -69,13 +106,14 @@ def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     if T == 0:
         return out
     s, stride = _scales_kb_major(xs)
-    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq, ws, out, None, 1, T, N, K)
+    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq, ws, out, None, 1, T, N, K, wide=wide)
     return out
 
 
 def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
                      offsets: torch.Tensor, out: Optional[torch.Tensor] = None,
-                     silu_mul: bool = False, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     silu_mul: bool = False, counts: Optional[torch.Tensor] = None,
+                     wide: Optional[bool] = None) -> torch.Tensor:
     """Ragged grouped GEMM.  xq: [R, K] rows grouped by expert, segment e = offsets[e]:offsets[e+1]
     (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K].  ``counts`` (int32 [E],
     device) gives the rows really present in each segment: padding rows are then neither stored nor, as
@@ -97,9 +135,8 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
     assert offsets.dtype == torch.int32 and offsets.is_cuda
     if counts is not None:
         assert counts.dtype == torch.int32 and counts.is_cuda and counts.numel() >= E
-        _ext.lib().bg_gemm_set_counts(_ext.ptr(counts))
     _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq.view(E * N, K), ws, out,
-            offsets, E, R, N, K)
+            offsets, E, R, N, K, wide=wide, counts=counts)
     return out
 
 

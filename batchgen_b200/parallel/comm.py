@@ -48,6 +48,16 @@ class NcclComm:
         dist.all_gather(parts, logits.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)
 
+    def all_to_all(self, x: torch.Tensor) -> torch.Tensor:
+        """x [world, ...]: slice d goes to rank d; returns [world, ...] with slice s received from rank s."""
+        if self.world == 1:
+            return x
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=self.group)
+        self.bytes_sent += x.numel() * x.element_size() * (self.world - 1) // self.world
+        return out
+
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return x

@@ -176,6 +176,7 @@ class FusedComm(NcclComm):
 
     def _set_hooks(self, a_ready=None, a_ready_rows=0, epoch=0, m_rotate=0, peer_out=None, row_map=None,
                    rs_rows=0, done_index=0, done_counter=None, peer_flags=None):
+        gemm_ops.hooks_pending()                 # the next GEMM consumes these hooks on the 128 x 128 kernel
         _ext.lib().bg_gemm_set_hooks(
             a_ready if a_ready is not None else ctypes.c_void_p(0), ctypes.c_int(a_ready_rows), ctypes.c_uint32(epoch),
             self._base(), ctypes.c_int(m_rotate), peer_out if peer_out is not None else ctypes.c_void_p(0),

@@ -57,6 +57,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=384, help="decode rows of the whole job")
     ap.add_argument("--prefill-tokens", type=int, default=8192)
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--attn-core", default="auto", choices=["auto", "heads", "requests"],
+                    help="decode attention core inside the TP group: split by heads (latent KV replicated) or by "
+                         "request (all-to-all of queries/outputs, KV of a row on one rank); auto = requests for N > 1")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the decode step eagerly instead of as a CUDA graph")
@@ -124,6 +127,8 @@ def main() -> int:
     t0 = time.time()
     model = build_model(cfg, device=dev, dtype="bf16", seed=0, layout=layout, comm=comm,
                         max_positions=8192, alias_experts_every=alias, gen_device=dev)
+    req_core = world > 1 and args.attn_core in ("auto", "requests") and B % world == 0 and not cfg.has_dsa
+    model.attn_request_parallel = req_core
     torch.cuda.synchronize()
     build_s = time.time() - t0
 
@@ -248,7 +253,8 @@ def main() -> int:
     if cfg.is_mla:
         # longest sequences first in the attention work lists (static device buffers: graphs see the new order)
         from batchgen_b200.ops import mla_kernel
-        mla_kernel.reorder_decode_work(dev, [int(c) for c in ctx])
+        own = ctx[rank * (B // world):(rank + 1) * (B // world)] if req_core else ctx
+        mla_kernel.reorder_decode_work(dev, [int(c) for c in own])
         decode_step_device()
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     l0 = _ext.LAUNCHES["count"]
@@ -352,6 +358,8 @@ def main() -> int:
             "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": B,
                        "seq_len": int(sum(ctx) / len(ctx)), "prompt_lens": "U[512,4096]", "decoded_so_far": 512,
                        "parallelism": f"tp{world}+ep{world}",
+                       "attn_core": ("head-sharded projections (TP), decode core split by request with an all-to-all "
+                                     "inside the TP group" if req_core else "split by heads"),
                        "comm": ("fused-nvlink-kernels" if fused else "nccl") if world > 1 else "none",
                        "distinct_expert_sets": sets, "moe_layers": n_moe, "cuda_graph": runner is not None,
                        "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",

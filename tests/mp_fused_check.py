@@ -75,12 +75,41 @@ def main():
     def rel(a, b):
         return float((a.float() - b.float()).norm() / b.float().norm())
 
+    # ---- one decode step after the prefill, with the attention core split by request inside the TP group
+    def decode_after_prefill(model, sp: bool, request_parallel: bool):
+        kv = PagedKVCache(cfg, 16 + sum((n + 63) // 64 + 1 for n in lens), 64, dev, torch.bfloat16)
+        pages = [kv.alloc.alloc((n + 1 + 63) // 64) for n in lens]
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
+        slots = torch.tensor(sum((slots_for_range(p, 0, n, 64) for p, n in zip(pages, lens)), []), device=dev)
+        bt = build_block_table(pages, dev)
+        pre = AttnMeta(mode="prefill", positions=pos, slot_mapping=slots, block_table=bt, cu_seqlens=[0, lens[0], T],
+                       ctx_lens=[0, 0])
+        model.attn_request_parallel = False
+        (model.forward_sp if sp else model.forward)(ids, pre, kv)
+        nxt = torch.tensor([7, 11], dtype=torch.int32, device=dev)
+        dslots = torch.tensor([slots_for_range(p, n, n + 1, 64)[0] for p, n in zip(pages, lens)], device=dev)
+        dec = AttnMeta(mode="decode", positions=torch.tensor(lens, dtype=torch.int32, device=dev), slot_mapping=dslots,
+                       block_table=bt, seqlens=torch.tensor([n + 1 for n in lens], dtype=torch.int32, device=dev))
+        model.attn_request_parallel = request_parallel
+        out = (model.forward_sp if sp else model.forward)(nxt, dec, kv)
+        model.attn_request_parallel = False
+        return out
+
+    dec_rel = None
+    if world == 2 and len(lens) == 2:
+        d_full = decode_after_prefill(full, False, False)
+        d_nccl = decode_after_prefill(nccl_model, False, True)
+        d_sp = decode_after_prefill(sp_model, True, True)                  # own row only
+        torch.cuda.synchronize()
+        _ext.check_status()
+        dec_rel = max(rel(d_nccl, d_full), rel(d_sp, d_full[rank:rank + 1]))
+
     res = {"rel_fused_vs_full": rel(got, want_loc), "rel_nccl_vs_full": rel(got_nccl, want_loc),
            "repeatable": bool(torch.equal(outs[0], outs[-1])),
            "argmax_agree": float((got.argmax(-1) == want_loc.argmax(-1)).float().mean()),
-           "nvlink_bytes": comm.nvlink_bytes}
+           "nvlink_bytes": comm.nvlink_bytes, "decode_request_parallel_rel": dec_rel}
     t = torch.tensor([res["rel_fused_vs_full"], res["rel_nccl_vs_full"], float(res["repeatable"]),
-                      res["argmax_agree"]], device=dev)
+                      res["argmax_agree"], dec_rel if dec_rel is not None else 0.0], device=dev)
     tmax = t.clone()
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     tmin = t.clone()
@@ -88,7 +117,8 @@ def main():
     if rank == 0:
         print(json.dumps({"world": world, "rel_fused_vs_full_max": float(tmax[0]), "rel_nccl_vs_full_max": float(tmax[1]),
                           "repeatable_all": bool(tmin[2] > 0.5), "argmax_agree_min": float(tmin[3]),
-                          "nvlink_bytes": res["nvlink_bytes"]}))
+                          "nvlink_bytes": res["nvlink_bytes"],
+                          "decode_request_parallel_rel_max": float(tmax[4]) if dec_rel is not None else None}))
     dist.destroy_process_group()
 
 

@@ -113,3 +113,54 @@ def test_model_prefill_uses_expanded_attention_and_matches_cpu():
     assert model.w.layers[0].w_kvb is not None
     rel = ((gpu - cpu).norm() / cpu.norm()).item()
     assert rel < 0.08, rel
+
+
+@pytest.mark.parametrize("T,N,K,silu", [(300, 512, 256, False), (128, 256, 128, False), (515, 768, 1024, True), (1, 2112, 7168, False)])
+def test_wide_tile_fp8_gemm_matches_reference(T, N, K, silu):
+    """128 x 256-tile kernel: same contract as the 128 x 128 one."""
+    from batchgen_b200.ops import _ext, gemm, ref
+    FP8 = torch.float8_e4m3fn
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(T, K, generator=g)
+    xq, xs = ref.act_quant(x)
+    wq = (torch.randn(N, K, generator=g) * 0.1).to(FP8)
+    ws = torch.rand((N + 127) // 128, K // 128, generator=g) + 0.5
+    want = ref.fp8_gemm(xq, xs, wq, ws)
+    wq_dev = wq.cuda()
+    if silu:
+        perm = gemm.interleave_gate_up_rows(N)
+        wq_dev = wq.view(torch.uint8)[perm].contiguous().view(FP8).cuda()
+        want = ref.silu_mul(want)
+    xs_dev = xs.cuda().t().contiguous().t()
+    got = gemm.fp8_gemm(xq.cuda(), xs_dev, wq_dev, ws.cuda(), silu_mul=silu, wide=True).cpu().float()
+    narrow = gemm.fp8_gemm(xq.cuda(), xs_dev, wq_dev, ws.cuda(), silu_mul=silu, wide=False).cpu().float()
+    _ext.check_status()
+    assert _rel(got, want) < 1e-2
+    assert torch.equal(got, narrow)            # same accumulation order: bit-identical to the narrow kernel
+
+
+def test_wide_tile_grouped_gemm_with_counts():
+    from batchgen_b200.ops import _ext, gemm, ref
+    FP8 = torch.float8_e4m3fn
+    g = torch.Generator().manual_seed(11)
+    E, N, K = 3, 512, 256
+    rows = [130, 0, 7]
+    starts, cur = [], 0
+    for r in rows:
+        starts.append(cur)
+        cur += (r + 127) // 128 * 128
+    offsets = torch.tensor(starts + [cur], dtype=torch.int32)
+    xq, xs = ref.act_quant(torch.randn(cur, K, generator=g))
+    wq = (torch.randn(E, N, K, generator=g) * 0.1).to(FP8)
+    ws = torch.rand(E, N // 128, K // 128, generator=g) + 0.5
+    out = torch.full((cur, N), 768.0, dtype=torch.bfloat16, device="cuda")
+    gemm.grouped_fp8_gemm(xq.cuda(), xs.cuda().t().contiguous().t(), wq.cuda(), ws.cuda(), offsets.cuda(), out=out,
+                          counts=torch.tensor(rows, dtype=torch.int32).cuda(), wide=True)
+    _ext.check_status()
+    want = ref.grouped_fp8_gemm(xq, xs, wq, ws, offsets)
+    out = out.cpu().float()
+    for e in range(E):
+        a, n = starts[e], rows[e]
+        if n:
+            assert _rel(out[a:a + n], want[a:a + n]) < 1e-2
+        assert (out[a + n:offsets[e + 1].item()] == 768.0).all()
