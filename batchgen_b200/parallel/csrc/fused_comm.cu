@@ -335,6 +335,31 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, i
   }
 }
 
+// All-to-all of equal slices over peer memory: slice d of `src` ([world, slice]) is stored into rank d's
+// receive buffer at slot my_rank; when the last CTA is done every rank's flag (index + my_rank) is raised.
+// grid = (blocks per slice, world); blockIdx.y walks the destinations in ring order starting with this rank.
+__global__ void __launch_bounds__(256)
+a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t slice_vec, int my_rank, int world, Peers flags,
+                int ready_index, Epoch epoch_e, unsigned int* counter) {
+  const uint32_t epoch = epoch_e.get();
+  const int d = (my_rank + blockIdx.y) % world;
+  const uint4* s = src + (size_t)d * slice_vec;
+  uint4* o = reinterpret_cast<uint4*>(dst.p[d]) + (size_t)my_rank * slice_vec;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < slice_vec; i += (size_t)gridDim.x * blockDim.x) o[i] = s[i];
+  // last-CTA-out over the whole 2-D grid
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x * gridDim.y - 1) {
+      *counter = 0u;
+      __threadfence_system();
+      signal_all(flags, ready_index + my_rank, world, epoch);
+    }
+  }
+}
+
 __global__ void bump_epoch_kernel(uint32_t* base, uint32_t n) {
   if (threadIdx.x == 0) *base += n;
 }
@@ -416,6 +441,22 @@ int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T,
                                                  recv_s_stride, to_peers(recv_info, world), recv_cap, sent_row, my_rank,
                                                  world, to_peers(flags, world), ready_index, Epoch{epoch, epoch_base}, counter,
                                                  status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// src: [world, slice_bytes] (slice_bytes a multiple of 16); dst[r]: rank r's receive buffer [world, slice_bytes].
+int bg_a2a_push(const void* src, void* const* dst, unsigned long long slice_bytes, int my_rank, int world,
+                void* const* flags, int ready_index, uint32_t epoch, const uint32_t* epoch_base, unsigned int* counter,
+                cudaStream_t stream) {
+  if (slice_bytes == 0) return 0;
+  if (slice_bytes % 16 != 0 || world < 1 || world > 8) return -1;
+  const size_t vec = slice_bytes / 16;
+  int bx = (int)((vec + 255) / 256);
+  if (bx > 64) bx = 64;
+  dim3 grid(bx, world);
+  bg::comm::a2a_push_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), to_peers(dst, world), vec, my_rank,
+                                                      world, to_peers(flags, world), ready_index,
+                                                      bg::comm::Epoch{epoch, epoch_base}, counter);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

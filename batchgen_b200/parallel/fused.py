@@ -35,7 +35,7 @@ from .comm import NcclComm
 from .symm import MAX_WORLD, SymmetricHeap
 
 FP8 = torch.float8_e4m3fn
-AG_READY, RS_READY, CNT_READY, DISP_READY, RET_READY = 0, 8, 16, 24, 32
+AG_READY, RS_READY, CNT_READY, DISP_READY, RET_READY, A2A_READY = 0, 8, 16, 24, 32, 40
 ALIGN = 128
 
 
@@ -55,8 +55,10 @@ class FusedComm(NcclComm):
         self._started = False
 
     # ------------------------------------------------------------------ setup
-    def configure(self, hidden: int, expert_hidden: int, num_experts: int, top_k: int, max_tokens: int) -> None:
-        """Size and carve the symmetric heap for steps of at most ``max_tokens`` tokens (whole job)."""
+    def configure(self, hidden: int, expert_hidden: int, num_experts: int, top_k: int, max_tokens: int,
+                  a2a_bytes: int = 0) -> None:
+        """Size and carve the symmetric heap for steps of at most ``max_tokens`` tokens (whole job).
+        ``a2a_bytes``: capacity of each of the two all-to-all receive buffers (request-parallel attention)."""
         W = self.world
         T = _pad(max_tokens, W * 8)
         self.T_max, self.H, self.He, self.E, self.K = T, hidden, expert_hidden, num_experts, top_k
@@ -71,6 +73,7 @@ class FusedComm(NcclComm):
             "recv_q": cap * expert_hidden, "recv_s": (expert_hidden // 128) * _pad(cap, 4) * 4,
             "recv_info": cap * 8,
             "ret": Tl * top_k * expert_hidden * 2,
+            "a2a0": _pad(a2a_bytes, 1024), "a2a1": _pad(a2a_bytes, 1024),
         }
         total = sum(_pad(v, 1024) for v in sizes.values()) + 64 * 1024
         self.heap = SymmetricHeap(total, self.device, self.group)
@@ -100,7 +103,11 @@ class FusedComm(NcclComm):
         self.total_rows = torch.zeros(1, dtype=torch.int32, device=dev)
         self.sent_row = torch.zeros(Tl * top_k, dtype=torch.int32, device=dev)
         self.ident_pos = torch.arange(Tl * top_k, dtype=torch.int32, device=dev)
-        self.last = {AG_READY: 0, RS_READY: 0, CNT_READY: 0, DISP_READY: 0, RET_READY: 0}
+        self.a2a_bytes = _pad(a2a_bytes, 1024)
+        self.a2a_bufs = [h.view("a2a0", torch.uint8, (self.a2a_bytes,)), h.view("a2a1", torch.uint8, (self.a2a_bytes,))] \
+            if a2a_bytes else []
+        self._a2a_turn = 0
+        self.last = {AG_READY: 0, RS_READY: 0, CNT_READY: 0, DISP_READY: 0, RET_READY: 0, A2A_READY: 0}
         # Epochs are (offset within the step) + (device-resident base).  The base is bumped by a kernel at
         # the end of every step, so a captured CUDA graph advances its epochs on every replay.
         self.epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -206,6 +213,32 @@ class FusedComm(NcclComm):
         out = self.rs_buf.view(-1)[: T * N].view(T, N)      # only its row stride is used by the scatter epilogue
         gemm_ops.fp8_gemm(xq, xs, lin.w, lin.s, out=out)
         self.nvlink_bytes += (self.world - 1) * Tl * N * 2
+
+    # ------------------------------------------------------------------ all-to-all over peer memory
+    def all_to_all(self, x: torch.Tensor) -> torch.Tensor:
+        """x [world, ...]: slice d is stored into rank d's receive buffer by a push kernel (plain peer stores +
+        arrival flags), then a one-warp kernel waits for every rank's flag.  Two receive buffers alternate, so a
+        result stays valid until the call after next.  Falls back to NCCL for messages beyond the buffers."""
+        W = self.world
+        x = x.contiguous()
+        nbytes = x.numel() * x.element_size()
+        slice_bytes = nbytes // W
+        if W == 1 or not self.a2a_bufs or nbytes > self.a2a_bytes or slice_bytes % 16:
+            return super().all_to_all(x)
+        name = "a2a0" if self._a2a_turn == 0 else "a2a1"
+        buf = self.a2a_bufs[self._a2a_turn]
+        self._a2a_turn ^= 1
+        epoch = self._next(A2A_READY)
+        st = _ext.stream()
+        rc = _ext.lib().bg_a2a_push(_ext.ptr(x), self.heap.peer_ptrs(name), ctypes.c_ulonglong(slice_bytes),
+                                    ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(A2A_READY),
+                                    ctypes.c_uint32(epoch), self._base(), _ext.ptr(self.counters[4:5]), st)
+        _ext.check(rc, "bg_a2a_push")
+        rc = _ext.lib().bg_wait_flags(self._flag_ptr(A2A_READY), ctypes.c_int(W), ctypes.c_uint32(epoch), self._base(),
+                                      self._status(), st)
+        _ext.check(rc, "bg_wait_flags")
+        self.nvlink_bytes += slice_bytes * (W - 1)
+        return buf[:nbytes].view(x.dtype).view(x.shape)
 
     # ------------------------------------------------------------------ expert parallel
     def moe_sp(self, h_local: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,

@@ -113,7 +113,8 @@ def main() -> int:
     layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=fused)
     if fused:
         comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
-                       max_tokens=max(B, args.prefill_tokens))
+                       max_tokens=max(B, args.prefill_tokens),
+                       a2a_bytes=B * (cfg.num_heads // world) * cfg.kv_cache_dim * 2 if cfg.is_mla else 0)
     n_moe = cfg.num_layers - cfg.first_k_dense
     expert_bytes_layer = (cfg.n_routed_experts // world) * 3 * cfg.moe_intermediate_size * cfg.hidden_size
     kv_bytes = total_pages * page * cfg.kv_cache_dim * 2 * cfg.num_layers

@@ -61,7 +61,8 @@ def main():
     got_nccl = nccl_model.forward(ids, meta, kv)[rank * Tl:(rank + 1) * Tl]
     # ---- fused sequence-parallel path
     comm = FusedComm(dev)
-    comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok, max_tokens=T)
+    comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok, max_tokens=T,
+                   a2a_bytes=T * 16 * cfg.kv_cache_dim * 2)
     layout_sp = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=True)
     sp_model = build_model(cfg, dev, "bf16", seed=0, layout=layout_sp, comm=comm)
     outs = []
