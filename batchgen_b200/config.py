@@ -68,7 +68,7 @@ class ModelConfig:
     index_topk: int = 0
     indexer_full_layers: Tuple[int, ...] = ()   # layers that own an indexer; others reuse
     # ---- quantisation of linear / expert weights
-    quant: str = "none"                    # none | fp8_block | mxfp4
+    quant: str = "none"                    # none | fp8_block | mxfp4 | int4
     quant_block: int = 128
     # ---- misc
     eos_token_id: int = 1

@@ -250,8 +250,11 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                 e0, e1 = layout.expert_range(E)
                 w13s, w2s, s13, s2 = [], [], [], []
                 equant = "fp8_block" if quant == "fp8_block" else "none"
-                if cfg.quant == "mxfp4" and eh % 64 == 0 and I % 64 == 0:
-                    from ..ops import mxfp4
+                if cfg.quant in ("mxfp4", "int4") and eh % 64 == 0 and I % 64 == 0:
+                    if cfg.quant == "mxfp4":
+                        from ..ops import mxfp4
+                    else:
+                        from ..ops import int4 as mxfp4     # same interface: quantize(w) -> (packed, scales)
                     for e in range(e0, e1):
                         ep = f"{p}.mlp.experts.{e}"
                         g = src.get(f"{ep}.gate_proj.weight", (I, eh))
@@ -261,7 +264,7 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                         q2, sc2 = mxfp4.quantize(d)
                         w13s.append(q13); s13.append(sc13); w2s.append(q2); s2.append(sc2)
                     lw.experts = ExpertWeights(w13=torch.stack(w13s), w2=torch.stack(w2s), w13_s=torch.stack(s13),
-                                               w2_s=torch.stack(s2), quant="mxfp4",
+                                               w2_s=torch.stack(s2), quant=cfg.quant,
                                                activation=cfg.activation).to_device_layout()
                     expert_sets[key] = lw.experts
                 for e in (range(e0, e1) if key not in expert_sets else ()):

@@ -39,6 +39,8 @@ constexpr int kQBytes = BN * BK / 2;      // 4 KB packed
 constexpr int kStageBytes = kABytes + kWBytes + kQBytes;
 constexpr int EPI_STORE = 0;
 constexpr int EPI_SILU_MUL = 1;
+constexpr int QMODE_MXFP4 = 0;            // e2m1 values, one e8m0 scale per 32
+constexpr int QMODE_INT4 = 1;             // offset-binary int4 (value = q - 8), one bf16 scale per 32
 
 struct Params {
   const uint8_t* ws;     // [groups * N, K / 32] e8m0
@@ -93,7 +95,7 @@ __device__ __forceinline__ float e8m0_to_float(uint32_t e) {
   return e == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(e << 23);
 }
 
-template <int EPI>
+template <int EPI, int QMODE>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ, Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -193,15 +195,21 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     Tile t;
     uint32_t it = 0;
     bool ok = true;
-    const int sk = p.K / 32;                 // scale bytes per weight row
+    constexpr int kScaleBytes = QMODE == QMODE_INT4 ? 2 : 1;     // bf16 group scale or e8m0 block scale
+    const int sk = (p.K / 32) * kScaleBytes;                     // scale bytes per weight row
     for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
       const int nrow = t.nt * BN + r;
       const bool row_ok = nrow < p.N;
       const uint8_t* srow = p.ws + (size_t)(t.g * p.N + (row_ok ? nrow : 0)) * sk;
-      uint32_t sc_next = *reinterpret_cast<const uint16_t*>(srow);
+      // the two scales of a 64-wide K stage: 2 bytes (e8m0) or 4 bytes (bf16)
+      auto load_scales = [&](int kb) -> uint32_t {
+        return QMODE == QMODE_INT4 ? *reinterpret_cast<const uint32_t*>(srow + 4 * kb)
+                                   : static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(srow + 2 * kb));
+      };
+      uint32_t sc_next = load_scales(0);
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const uint32_t sc = sc_next;
-        if (kb + 1 < KB) sc_next = *reinterpret_cast<const uint16_t*>(srow + 2 * (kb + 1));
+        if (kb + 1 < KB) sc_next = load_scales(kb + 1);
         const int s = it % kStages;
         if (!mbar_wait(&ss.full[s], (it / kStages) & 1, abort_flag, kTimeoutEpilogue)) { ok = false; break; }
         const uint4* q = reinterpret_cast<const uint4*>(q_tiles + s * kQBytes + r * (BK / 2));
@@ -209,17 +217,24 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
         for (int h = 0; h < 2; ++h) {        // 32 weights per scale
           const uint4 v = q[h];
-          const float f = row_ok ? e8m0_to_float((sc >> (8 * h)) & 0xFFu) : 0.f;
+          float f;
+          if (QMODE == QMODE_INT4) f = row_ok ? __uint_as_float(((sc >> (16 * h)) & 0xFFFFu) << 16) : 0.f;   // bf16 -> fp32
+          else f = row_ok ? e8m0_to_float((sc >> (8 * h)) & 0xFFu) : 0.f;
           const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {      // 8 weights -> one 16-byte chunk
             __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-              const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(
-                  static_cast<__nv_fp4x2_storage_t>((words[c] >> (8 * b)) & 0xFFu), __NV_E2M1);
-              const float2 ff = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-              o[b] = __floats2bfloat162_rn(ff.x * f, ff.y * f);
+              const uint32_t byte = (words[c] >> (8 * b)) & 0xFFu;
+              if (QMODE == QMODE_INT4) {     // offset-binary nibbles: value = q - 8
+                o[b] = __floats2bfloat162_rn((static_cast<float>(byte & 0xFu) - 8.f) * f,
+                                             (static_cast<float>(byte >> 4) - 8.f) * f);
+              } else {
+                const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+                const float2 ff = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+                o[b] = __floats2bfloat162_rn(ff.x * f, ff.y * f);
+              }
             }
             const int chunk = h * 4 + c;
             *reinterpret_cast<uint4*>(wrow + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
@@ -336,7 +351,7 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
-template <int EPI>
+template <int EPI, int QMODE>
 static int launch(const void* A, const void* Wq, const Params& p, int b_rows, int num_sms, cudaStream_t stream) {
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return -10;
@@ -362,7 +377,7 @@ static int launch(const void* A, const void* Wq, const Params& p, int b_rows, in
       return -12;
   }
   static bool attr_set = false;
-  auto kern = mxfp4_gemm_kernel<EPI>;
+  auto kern = mxfp4_gemm_kernel<EPI, QMODE>;
   const size_t smem = kStages * kStageBytes + sizeof(Shared) + 1024;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -13;
@@ -395,8 +410,24 @@ int bg_mxfp4_gemm(int epi, const void* A, const void* Wq, const void* Ws, void* 
   Params p;
   p.ws = reinterpret_cast<const uint8_t*>(Ws); p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
   p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
-  if (epi == EPI_SILU_MUL) return launch<EPI_SILU_MUL>(A, Wq, p, groups * N, num_sms, stream);
-  return launch<EPI_STORE>(A, Wq, p, groups * N, num_sms, stream);
+  if (epi == EPI_SILU_MUL) return launch<EPI_SILU_MUL, QMODE_MXFP4>(A, Wq, p, groups * N, num_sms, stream);
+  return launch<EPI_STORE, QMODE_MXFP4>(A, Wq, p, groups * N, num_sms, stream);
+}
+
+// INT4 W4A16 (group size 32): Wq packs two offset-binary nibbles per byte (low nibble = even k, value = q - 8),
+// Ws: [groups * N, K / 32] bf16 scales.  Everything else as bg_mxfp4_gemm.
+// Replaces (by behaviour): the Marlin / INT4 WGMMA grouped kernels of the Kimi-K2.5 family (W4A16, gs = 32).
+int bg_int4_gemm(int epi, const void* A, const void* Wq, const void* Ws, void* D, int ldd, const int* offsets,
+                 int groups, int M, int N, int K, int num_sms, int* status, cudaStream_t stream) {
+  using namespace bg::mx;
+  if (M <= 0 || N <= 0) return 0;
+  if (K % BK != 0 || groups > kMaxGroups || (epi == EPI_SILU_MUL && (N % 128) != 0) || (ldd % 8) != 0) return -1;
+  if (offsets == nullptr) groups = 1;
+  Params p;
+  p.ws = reinterpret_cast<const uint8_t*>(Ws); p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.offsets = offsets; p.groups = groups; p.M = M; p.N = N; p.K = K; p.status = status;
+  if (epi == EPI_SILU_MUL) return launch<EPI_SILU_MUL, QMODE_INT4>(A, Wq, p, groups * N, num_sms, stream);
+  return launch<EPI_STORE, QMODE_INT4>(A, Wq, p, groups * N, num_sms, stream);
 }
 
 // out[i] = e2m1(wq[i]) * 2^(ws[i / 32] - 127), n elements (multiple of 32).

@@ -36,6 +36,7 @@ constexpr int KIND_FP8 = 0;
 constexpr int KIND_BF16 = 1;
 constexpr int EPI_STORE = 0;
 constexpr int EPI_SILU_MUL = 1;  // B rows interleaved (32 gate, 32 up): out = silu(gate) * up
+constexpr int EPI_STORE_F32 = 2;  // fp32 output (router logits): D is float*, ldd in floats
 
 struct GemmParams {
   const float* sA;      // [KB, sa_stride] (transposed: scale of row m, block kb at sA[kb*sa_stride+m])
@@ -389,6 +390,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (col0 + j + q < n_out) dst[j + q] = __float2bfloat16(silu(r[j + q]) * r[32 + j + q]);
             }
           }
+        } else if (EPI == EPI_STORE_F32) {
+          const int col0 = t.nt * BN + half * 64;
+          float* dst = reinterpret_cast<float*>(p.D) + out_row * p.ldd + col0;
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            if (col0 + j + 4 <= p.N) {
+              *reinterpret_cast<float4*>(dst + j) = make_float4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+              for (int q = 0; q < 4; ++q)
+                if (col0 + j + q < p.N) dst[j + q] = r[j + q];
+            }
+          }
         } else if (p.peer_out[0] == nullptr) {
           const int col0 = t.nt * BN + half * 64;
           __nv_bfloat16* dst = out_base + out_row * p.ldd + col0;
@@ -406,7 +419,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
-      if (EPI != EPI_SILU_MUL && p.peer_out[0] != nullptr) {
+      if (EPI == EPI_STORE && p.peer_out[0] != nullptr) {
         // Rows bound for peer memory leave as whole 128-byte runs: the warp's 32 x 64 block goes through
         // shared memory 16 rows at a time, then 8 lanes write one row's 128 bytes together (a row per
         // thread would cross NVLink as 16-byte fragments).  Chunks are XOR-swizzled against bank conflicts.
@@ -586,12 +599,14 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
     g_hooks_set = false;
   }
   // rows bound for peer memory are written in 16-byte pieces: whole pieces and aligned rows only
-  if (p.peer_out[0] != nullptr && (epi == EPI_SILU_MUL || (N % 8) != 0 || (ldd % 8) != 0)) return -1;
+  if (p.peer_out[0] != nullptr && (epi != EPI_STORE || (N % 8) != 0 || (ldd % 8) != 0)) return -1;
+  if (epi == EPI_STORE_F32 && (kind != KIND_BF16 || (ldd % 4) != 0)) return -1;
   const int b_rows = groups * N;
   if (kind == KIND_FP8 && epi == EPI_STORE) return launch_gemm<KIND_FP8, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
   if (kind == KIND_FP8 && epi == EPI_SILU_MUL) return launch_gemm<KIND_FP8, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);
   if (kind == KIND_BF16 && epi == EPI_STORE) return launch_gemm<KIND_BF16, EPI_STORE>(A, B, p, M, b_rows, num_sms, stream);
   if (kind == KIND_BF16 && epi == EPI_SILU_MUL) return launch_gemm<KIND_BF16, EPI_SILU_MUL>(A, B, p, M, b_rows, num_sms, stream);
+  if (kind == KIND_BF16 && epi == EPI_STORE_F32) return launch_gemm<KIND_BF16, EPI_STORE_F32>(A, B, p, M, b_rows, num_sms, stream);
   return -2;
 }
 

@@ -16,7 +16,7 @@ import torch
 from . import _ext, ref
 
 KIND_FP8, KIND_BF16 = 0, 1
-EPI_STORE, EPI_SILU_MUL = 0, 1
+EPI_STORE, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2
 
 
 def interleave_gate_up_rows(n_rows: int, device=None) -> torch.Tensor:
@@ -140,15 +140,17 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
     return out
 
 
-def bf16_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """[T, K] bf16 x [N, K] bf16 -> [T, N] bf16 (fp32 accumulate in TMEM)."""
+def bf16_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, fp32_out: bool = False) -> torch.Tensor:
+    """[T, K] bf16 x [N, K] bf16 -> [T, N] bf16, or fp32 with ``fp32_out`` (fp32 accumulate in TMEM; one
+    accumulation order whatever the batch size: every output element sums its K products in the same order)."""
     if not x.is_cuda:
-        return (x.float() @ w.float().t()).to(x.dtype)
+        y = x.float() @ w.float().t()
+        return y if fp32_out else y.to(x.dtype)
     T, K = x.shape
     N = w.shape[0]
     if out is None:
-        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(T, N, dtype=torch.float32 if fp32_out else torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    _launch(KIND_BF16, EPI_STORE, x, None, 0, w, None, out, None, 1, T, N, K)
+    _launch(KIND_BF16, EPI_STORE_F32 if fp32_out else EPI_STORE, x, None, 0, w, None, out, None, 1, T, N, K)
     return out

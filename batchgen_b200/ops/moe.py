@@ -30,6 +30,7 @@ class ExpertWeights:
                           on CUDA, w13 rows are stored in the gate/up tile-interleaved order.
     quant == "mxfp4":     w13/w2 packed e2m1 (uint8, two values per byte) with e8m0 scales per 32
                           (w13 [E, 2I, Kh/2], w13_s [E, 2I, Kh/32]); same interleave rule on CUDA.
+    quant == "int4":      w13/w2 packed offset-binary int4 with bf16 scales per 32 (same shapes).
     """
     w13: torch.Tensor
     w2: torch.Tensor
@@ -46,10 +47,10 @@ class ExpertWeights:
     def to_device_layout(self, force: bool = False) -> "ExpertWeights":
         """Reorder w13 rows for the fused SiLU epilogue (quantised experts; on CUDA tensors, or on host tensors
         that will be streamed to the GPU when ``force``)."""
-        if self.quant not in ("fp8_block", "mxfp4") or self.interleaved or not (self.w13.is_cuda or force):
+        if self.quant not in ("fp8_block", "mxfp4", "int4") or self.interleaved or not (self.w13.is_cuda or force):
             return self
         perm = gemm.interleave_gate_up_rows(self.w13.shape[1], self.w13.device)
-        if self.quant == "mxfp4":
+        if self.quant in ("mxfp4", "int4"):
             if self.activation != "silu":
                 return self                      # other activations run unfused: natural row order
             self.w13 = self.w13[:, perm].contiguous()
@@ -60,10 +61,20 @@ class ExpertWeights:
         return self
 
 
+_ROUTER_LP = {}
+
+
 def router_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """fp32 router logits [T, E] = hidden @ weight^T (weight [E, H])."""
+    """fp32 router logits [T, E] = hidden @ weight^T (weight [E, H]).  On the GPU: the bf16 tcgen05 GEMM with
+    an fp32 epilogue (the bf16 copy of the router weight is made once per weight tensor)."""
     if hidden.is_cuda and hidden.dtype == torch.bfloat16:
-        return torch.mm(hidden, weight.to(torch.bfloat16).t(), out_dtype=torch.float32)
+        key = (weight.data_ptr(), tuple(weight.shape))
+        w = _ROUTER_LP.get(key)
+        if w is None:
+            w = _ROUTER_LP[key] = weight.to(torch.bfloat16).contiguous()
+        if hidden.shape[1] % 64 == 0 and hidden.stride(1) == 1 and hidden.stride(0) == hidden.shape[1]:
+            return gemm.bf16_gemm(hidden, w, fp32_out=True)
+        return torch.mm(hidden, w.t(), out_dtype=torch.float32)
     return hidden.float() @ weight.float().t()
 
 
@@ -184,8 +195,14 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         act = _activation(gu, ew.activation)
         aq, as_ = ref.act_quant(act)
         return ref.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
-    if ew.quant == "mxfp4":
-        from . import mxfp4
+    if ew.quant in ("mxfp4", "int4"):
+        if ew.quant == "mxfp4":
+            from . import mxfp4
+        else:                                  # INT4 W4A16, group 32: same kernel, other expansion
+            from . import int4 as _i4
+
+            class mxfp4:                       # noqa: N801 - same call shape as the mxfp4 module
+                grouped_mxfp4_gemm = staticmethod(_i4.grouped_int4_gemm)
         x = x_dense
         if x.is_cuda and ew.interleaved:
             with timer.timed("moe.s1_gemm"):

@@ -62,7 +62,7 @@ class DeploymentPlan:
 
 
 def _quant_bytes(cfg: ModelConfig) -> float:
-    return {"fp8_block": 1.0 + 4.0 / (128 * 128), "mxfp4": 0.5 + 1.0 / 32, "none": 2.0}[cfg.quant]
+    return {"fp8_block": 1.0 + 4.0 / (128 * 128), "mxfp4": 0.5 + 1.0 / 32, "int4": 0.5 + 2.0 / 32, "none": 2.0}[cfg.quant]
 
 
 def weight_bytes_per_rank(cfg: ModelConfig, tp: int, ep: int, sequence_parallel: bool = True,

@@ -164,3 +164,17 @@ def test_wide_tile_grouped_gemm_with_counts():
         if n:
             assert _rel(out[a:a + n], want[a:a + n]) < 1e-2
         assert (out[a + n:offsets[e + 1].item()] == 768.0).all()
+
+
+def test_router_logits_fp32_epilogue():
+    from batchgen_b200.ops import _ext, moe
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(300, 1024, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(256, 1024, generator=g) * 0.05).cuda()
+    got = moe.router_logits(x, w)
+    _ext.check_status()
+    assert got.dtype == torch.float32 and got.shape == (300, 256)
+    want = x.float() @ w.to(torch.bfloat16).float().t()
+    assert _rel(got, want) < 1e-4
+    # batch invariance: a row's logits do not depend on which other rows are in the batch
+    assert torch.equal(moe.router_logits(x[:7].contiguous(), w), got[:7])

@@ -64,3 +64,35 @@ def test_grouped_gemm(silu):
         if silu:
             ref_e = torch.nn.functional.silu(ref_e[:, : N // 2]) * ref_e[:, N // 2:]
         assert _rel(y[starts[e]:ends[e]], ref_e) < 8e-3, e
+
+
+@pytest.mark.parametrize("silu", [False, True])
+def test_int4_grouped_gemm(silu):
+    from batchgen_b200.ops import _ext, int4
+    from batchgen_b200.ops.gemm import interleave_gate_up_rows
+    g = torch.Generator().manual_seed(8)
+    E, N, K = 3, 256, 256
+    rows = [130, 0, 5]
+    starts, cur = [], 0
+    for r in rows:
+        starts.append(cur)
+        cur += (r + 127) // 128 * 128
+    offsets = torch.tensor(starts + [cur], dtype=torch.int32)
+    x = torch.randn(cur, K, generator=g).to(torch.bfloat16)
+    q, s = int4.quantize(torch.randn(E, N, K, generator=g) * 0.05)
+    wd = int4.dequantize(q, s)
+    qd, sd = q.cuda(), s.cuda()
+    if silu:
+        perm = interleave_gate_up_rows(N).cuda()
+        qd, sd = qd[:, perm].contiguous(), sd[:, perm].contiguous()
+    y = int4.grouped_int4_gemm(x.cuda(), qd, sd, offsets.cuda(), silu_mul=silu).cpu()
+    _ext.check_status()
+    for e in range(E):
+        a, n = starts[e], rows[e]
+        if not n:
+            continue
+        want = x[a:a + n].float() @ wd[e].t()
+        if silu:
+            want = torch.nn.functional.silu(want[:, : N // 2]) * want[:, N // 2:]
+        assert _rel(y[a:a + n], want) < 8e-3, e
+    assert _rel(int4.int4_gemm(x[:40].cuda(), q[0].cuda(), s[0].cuda()).cpu(), x[:40].float() @ wd[0].t()) < 8e-3
