@@ -67,6 +67,12 @@ class ModelConfig:
     index_head_dim: int = 0
     index_topk: int = 0
     indexer_full_layers: Tuple[int, ...] = ()   # layers that own an indexer; others reuse
+    # ---- KDA linear-attention layers (Kimi-Linear / Kimi-K3): those layers keep a recurrent state per
+    # sequence instead of paged KV; the other layers are MLA
+    kda_layers: Tuple[int, ...] = ()
+    kda_num_heads: int = 0
+    kda_head_dim: int = 128
+    kda_gate_rank: int = 0                 # width of the low-rank decay-gate projection (0 = head dim)
     # ---- quantisation of linear / expert weights
     quant: str = "none"                    # none | fp8_block | mxfp4 | int4
     quant_block: int = 128
@@ -108,6 +114,22 @@ class ModelConfig:
             scale = scale * m * m
         return scale
 
+    @property
+    def has_kda(self) -> bool:
+        return len(self.kda_layers) > 0
+
+    def layer_is_kda(self, layer: int) -> bool:
+        return layer in self.kda_layers
+
+    @property
+    def kda_rank(self) -> int:
+        return self.kda_gate_rank or self.kda_head_dim
+
+    def kda_state_bytes_per_seq(self, tp_size: int = 1) -> int:
+        """Recurrent state (fp32 [H, D, D]) plus convolution windows (fp32 [3 H D, 3]) of all KDA layers."""
+        h, d = self.kda_num_heads // tp_size, self.kda_head_dim
+        return len(self.kda_layers) * 4 * (h * d * d + 9 * h * d)
+
     def is_moe_layer(self, layer: int) -> bool:
         return self.n_routed_experts > 0 and layer >= self.first_k_dense
 
@@ -117,7 +139,7 @@ class ModelConfig:
         return (not self.indexer_full_layers) or layer in self.indexer_full_layers
 
     def kv_bytes_per_token(self, kv_dtype_bytes: int = 2) -> int:
-        b = self.num_layers * self.kv_cache_dim * kv_dtype_bytes
+        b = (self.num_layers - len(self.kda_layers)) * self.kv_cache_dim * kv_dtype_bytes
         if self.has_dsa:
             n_idx = len(self.indexer_full_layers) or self.num_layers
             b += n_idx * (self.index_head_dim + 4)  # e4m3 keys + fp32 scale per token
@@ -127,7 +149,10 @@ class ModelConfig:
         h = self.hidden_size
         n = 2 * self.vocab_size * h
         for l in range(self.num_layers):
-            if self.is_mla:
+            if self.layer_is_kda(l):
+                hd = self.kda_num_heads * self.kda_head_dim
+                n += h * (4 * hd + self.kda_num_heads + self.kda_rank) + self.kda_rank * hd + hd * h
+            elif self.is_mla:
                 n += h * self.q_lora_rank + self.q_lora_rank * self.num_heads * self.qk_head_dim
                 n += h * self.kv_cache_dim
                 n += self.kv_lora_rank * self.num_heads * (self.qk_nope_head_dim + self.v_head_dim)
@@ -150,6 +175,8 @@ class ModelConfig:
     def from_dict(cls, d: Dict) -> "ModelConfig":
         names = {f.name for f in dataclasses.fields(cls)}
         kw = {k: v for k, v in d.items() if k in names}
+        if "kda_layers" in kw:
+            kw["kda_layers"] = tuple(kw["kda_layers"])
         if "indexer_full_layers" in kw:
             kw["indexer_full_layers"] = tuple(kw["indexer_full_layers"])
         return cls(**kw)
@@ -172,6 +199,13 @@ def tiny_kimi_k3() -> ModelConfig:
     return ModelConfig(name="tiny-kimi-k3", family="kimi_k3", num_layers=2, first_k_dense=0,
                        n_routed_experts=16, num_experts_per_tok=4, moe_latent_size=128,
                        moe_intermediate_size=64, quant="none")
+
+
+def tiny_kimi_linear() -> ModelConfig:
+    """Three KDA layers to one MLA layer, as in Kimi-Linear; LatentMoE off."""
+    return ModelConfig(name="tiny-kimi-linear", family="kimi_k3", num_layers=4, first_k_dense=1,
+                       n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                       kda_layers=(0, 1, 2), kda_num_heads=2, kda_head_dim=64, kda_gate_rank=32)
 
 
 def tiny_gpt_oss() -> ModelConfig:
@@ -215,6 +249,24 @@ def kimi_k3() -> ModelConfig:
         v_head_dim=128, quant="mxfp4", quant_block=32)
 
 
+def kimi_k3_kda() -> ModelConfig:
+    """Kimi-K3 with its linear-attention layers: of the 93 layers every fourth (24 in all) is NoPE-MLA,
+    the other 69 are KDA (64 heads of 128)."""
+    import dataclasses
+    mla = set(range(3, 93, 4)) | {92}
+    return dataclasses.replace(kimi_k3(), name="kimi-k3-kda", kda_layers=tuple(l for l in range(93) if l not in mla),
+                               kda_num_heads=64, kda_head_dim=128)
+
+
+def kimi_linear_48b() -> ModelConfig:
+    return ModelConfig(
+        name="kimi-linear-48b", family="kimi_k3", vocab_size=163840, hidden_size=2304, num_layers=27,
+        first_k_dense=1, intermediate_size=9216, moe_intermediate_size=1024, n_routed_experts=256,
+        n_shared_experts=1, num_experts_per_tok=8, routed_scaling_factor=2.446, num_heads=32,
+        q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+        kda_layers=tuple(l for l in range(27) if l % 4 != 3), kda_num_heads=32, kda_head_dim=128)
+
+
 def kimi_k25() -> ModelConfig:
     return ModelConfig(
         name="kimi-k2.5", family="kimi_k25", vocab_size=163840, hidden_size=7168, num_layers=61,
@@ -246,6 +298,9 @@ _PRESETS = {
     "tiny-deepseek-v3": tiny_deepseek_v3,
     "tiny-glm5": tiny_glm5,
     "tiny-kimi-k3": tiny_kimi_k3,
+    "tiny-kimi-linear": tiny_kimi_linear,
+    "kimi-k3-kda": kimi_k3_kda,
+    "kimi-linear-48b": kimi_linear_48b,
     "tiny-gpt-oss": tiny_gpt_oss,
     "deepseek-v3-671b": deepseek_v3_671b,
     "deepseek-r1": deepseek_v3_671b,
@@ -261,6 +316,8 @@ _PRESETS = {
 _PATTERNS = [
     (r"deepseek[-_/]?(ai/)?.*(v3|r1)", "deepseek-v3-671b"),
     (r"glm[-_]?5", "glm-5.3-fp8"),
+    (r"kimi[-_]?linear", "kimi-linear-48b"),
+    (r"kimi[-_]?k3[-_]?kda", "kimi-k3-kda"),
     (r"kimi[-_]?k3", "kimi-k3"),
     (r"kimi[-_]?k2", "kimi-k2.5"),
     (r"gpt[-_]?oss", "gpt-oss-120b"),
@@ -306,6 +363,7 @@ class EngineConfig:
     decision_frequency_pages: int = 2
     max_prefill_tokens: int = 131072            # packed micro-batch token cap
     max_decode_batch: int = 512                 # rows per rank in decode
+    max_state_slots: int = 0                    # sequences holding recurrent (KDA) state at once; 0 = max_decode_batch
     max_model_len: int = -1
     enable_cuda_graph: bool = True
     cuda_graph_max_bucket_size: int = 128

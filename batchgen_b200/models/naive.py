@@ -54,6 +54,11 @@ class NaiveModel:
         for l in range(cfg.num_layers):
             p = f"model.layers.{l}"
             x = self._rms(h, f"{p}.input_layernorm.weight", H)
+            if cfg.layer_is_kda(l):
+                h = h + self._kda(x, p)
+                x = self._rms(h, f"{p}.post_attention_layernorm.weight", H)
+                h = h + (self._moe(x, p) if cfg.is_moe_layer(l) else self._mlp(x, f"{p}.mlp", cfg.intermediate_size, H))
+                continue
             # ---- MLA, expanded form
             q_a = x @ self._g(f"{p}.self_attn.q_a_proj.weight", (cfg.q_lora_rank, H)).t()
             q_a = self._rms(q_a, f"{p}.self_attn.q_a_layernorm.weight", cfg.q_lora_rank)
@@ -86,6 +91,38 @@ class NaiveModel:
         h = self._rms(h, "model.norm.weight", H)
         head = "model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"
         return h @ self._g(head, (cfg.vocab_size, H)).t()
+
+    def _kda(self, x, p):
+        """Gated delta-rule linear attention over the whole sequence, one token at a time."""
+        cfg = self.cfg
+        Hk, D, r, H, L = cfg.kda_num_heads, cfg.kda_head_dim, cfg.kda_rank, cfg.hidden_size, x.shape[0]
+        a = f"{p}.self_attn"
+
+        def conv(name):
+            raw = x @ self._g(f"{a}.{name}_proj.weight", (Hk * D, H)).t()
+            w = self._g(f"{a}.{name}_conv1d.weight", (Hk * D, 4), "bias")
+            padded = torch.cat([torch.zeros(3, Hk * D), raw], 0)
+            y = sum(padded[i:i + L] * w[:, i] for i in range(4))
+            return F.silu(y).view(L, Hk, D)
+
+        q, k, v = conv("q"), conv("k"), conv("v")
+        q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+        k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        f = (x @ self._g(f"{a}.f_a_proj.weight", (r, H)).t()) @ self._g(f"{a}.f_b_proj.weight", (Hk * D, r)).t()
+        A = self._g(f"{a}.A_log", (Hk,), "bias").exp()
+        decay = torch.exp(-A.view(1, Hk, 1) * F.softplus(f.view(L, Hk, D) + self._g(f"{a}.dt_bias", (Hk * D,), "bias").view(1, Hk, D)))
+        beta = torch.sigmoid(x @ self._g(f"{a}.b_proj.weight", (Hk, H)).t())
+        z = (x @ self._g(f"{a}.g_proj.weight", (Hk * D, H)).t()).view(L, Hk, D)
+        S = torch.zeros(Hk, D, D)
+        o = torch.zeros(L, Hk, D)
+        for t in range(L):
+            S = S * decay[t].unsqueeze(-1)
+            pred = (S * k[t].unsqueeze(-1)).sum(1)
+            S = S + k[t].unsqueeze(-1) * (beta[t].unsqueeze(-1) * (v[t] - pred)).unsqueeze(1)
+            o[t] = (S * q[t].unsqueeze(-1)).sum(1)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * self._g(f"{a}.o_norm.weight", (D,), "norm")
+        o = (o * torch.sigmoid(z)).reshape(L, Hk * D)
+        return o @ self._g(f"{a}.o_proj.weight", (H, Hk * D)).t()
 
     def _moe(self, x, p):
         cfg = self.cfg

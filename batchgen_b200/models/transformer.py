@@ -32,6 +32,7 @@ import torch
 from ..config import ModelConfig
 from ..ops import attention as attn_ops
 from ..ops import fused, gemm, ref
+from ..ops import kda as kda_ops
 from ..ops import moe as moe_ops
 from ..utils.timing import null_timer
 from .weights import LayerWeights, Linear, ModelWeights, ParallelLayout
@@ -49,6 +50,8 @@ class AttnMeta:
     logit_rows: Optional[torch.Tensor] = None   # rows of T whose logits are wanted (prefill: last tokens)
     num_valid: Optional[torch.Tensor] = None    # decode under CUDA graphs: device count of real rows
     dsa_selection: dict = field(default_factory=dict)  # layer -> (sel_idx, sel_len) reused by shared layers
+    state_slots: Optional[torch.Tensor] = None  # KDA layers: [nseq] int32 state slot of each sequence (< 0 = skip)
+    state_has_initial: Optional[torch.Tensor] = None  # prefill: [nseq] int32, 0 = start from a zero state
     _own_slots: Optional[torch.Tensor] = None   # slot mapping masked to this rank's rows (request-parallel decode)
 
 
@@ -180,6 +183,28 @@ class Transformer:
         q = linear(qn, lw.wq_b, qnq, qns).view(T, Hh, cfg.qk_head_dim)
         fused.rope_q_(q, meta.positions, self.rope.cos, self.rope.sin, cfg.qk_rope_head_dim, cfg.rope_interleaved)
         self._q, self._qn = q, qn
+
+    def _kda(self, l: int, lw: LayerWeights, x, meta: AttnMeta, cache) -> torch.Tensor:
+        """KDA layer: one stacked projection (q | k | v | output gate | low-rank decay gate | beta), the decay
+        gate's second factor, the fused conv + delta-rule + gated-norm kernel over the sequence's state slot,
+        then o_proj.  Heads are sharded over the TP group; the state of a sequence lives in ``cache.state``."""
+        cfg, kw, tm = self.cfg, lw.kda, self.timer
+        Hh, D, r = kw.heads, cfg.kda_head_dim, cfg.kda_rank
+        HD = Hh * D
+        with tm.timed("kda.proj", l):
+            proj = linear(x, kw.w_in)
+            f = linear(proj[:, 4 * HD: 4 * HD + r].contiguous(), kw.f_b)
+        conv, rec = cache.state.layer(l)
+        if meta.state_slots is None:
+            raise RuntimeError("a model with KDA layers needs AttnMeta.state_slots")
+        with tm.timed("kda.core_" + meta.mode, l):
+            o = kda_ops.kda_forward(proj[:, : 3 * HD], f, proj[:, 4 * HD + r: 4 * HD + r + Hh], proj[:, 3 * HD: 4 * HD],
+                                    kda_ops.KDAParams(kw.conv_w, None, kw.A_log, kw.dt_bias, kw.o_norm), conv, rec,
+                                    meta.state_slots, meta.cu_seqlens if meta.mode == "prefill" else None,
+                                    meta.state_has_initial if meta.mode == "prefill" else None, Hh, D, D ** -0.5,
+                                    cfg.rms_eps)
+        with tm.timed("attn.o_proj", l):
+            return linear(o, lw.wo)
 
     def _request_parallel(self, meta: AttnMeta, T: int) -> bool:
         return (self.attn_request_parallel and meta.mode == "decode" and self.comm is not None
@@ -381,7 +406,7 @@ class Transformer:
         residual = None
         tp = self.comm is not None and self.layout.tp_size > 1
         for l, lw in enumerate(self.w.layers):
-            fp8_in = (lw.wqkv_a or lw.wqkv).is_fp8
+            fp8_in = lw.kda is None and (lw.wqkv_a or lw.wqkv).is_fp8
             tm = self.timer
             with tm.timed("norm", l):
                 if residual is None:
@@ -389,7 +414,10 @@ class Transformer:
                     x, xq, xs = self._norm(h, lw.input_norm, None, fp8_in)
                 else:
                     x, xq, xs = self._norm(h, lw.input_norm, residual, fp8_in)
-            a = self._mla(l, lw, x, xq, xs, meta, cache) if cfg.is_mla else self._gqa(l, lw, x, xq, xs, meta, cache)
+            if lw.kda is not None:
+                a = self._kda(l, lw, x, meta, cache)
+            else:
+                a = self._mla(l, lw, x, xq, xs, meta, cache) if cfg.is_mla else self._gqa(l, lw, x, xq, xs, meta, cache)
             if tp:
                 with tm.timed("comm.tp_reduce", l):
                     a = self.comm.tp_reduce(a)

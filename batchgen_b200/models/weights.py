@@ -113,8 +113,22 @@ def dequant_linear(lin: Linear) -> torch.Tensor:
 
 
 @dataclass
+class KDAWeights:
+    """One KDA layer (this rank's heads).  ``w_in`` stacks every projection that reads the layer input, in the
+    column order q | k | v | z (output gate) | f_a (low-rank decay gate) | beta, so one GEMM feeds them all."""
+    w_in: Linear = None              # [4 Hh D + r + pad(Hh), H]
+    f_b: Linear = None               # [Hh D, r]
+    conv_w: torch.Tensor = None      # [3 Hh D, 4] fp32
+    A_log: torch.Tensor = None       # [Hh] fp32
+    dt_bias: torch.Tensor = None     # [Hh D] fp32
+    o_norm: torch.Tensor = None      # [D] fp32
+    heads: int = 0
+
+
+@dataclass
 class LayerWeights:
     input_norm: torch.Tensor = None
+    kda: KDAWeights = None
     post_norm: torch.Tensor = None
     # MLA
     wqkv_a: Linear = None            # [q_lora + kv_lora + rope, H]
@@ -180,7 +194,30 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
         lw.input_norm = src.get(f"{p}.input_layernorm.weight", (H,), "norm").to(dtype)
         lw.post_norm = src.get(f"{p}.post_attention_layernorm.weight", (H,), "norm").to(dtype)
         h0, h1 = layout.head_range(cfg.num_heads)
-        if cfg.is_mla:
+        if cfg.layer_is_kda(l):
+            Hk, D, r = cfg.kda_num_heads, cfg.kda_head_dim, cfg.kda_rank
+            a0, a1 = layout.head_range(Hk)
+            Hh = a1 - a0
+            rows = lambda name, n_per: src.get(f"{p}.self_attn.{name}.weight", (Hk * n_per, H)).view(Hk, n_per, H)[a0:a1].reshape(-1, H)
+            parts = [rows("q_proj", D), rows("k_proj", D), rows("v_proj", D), rows("g_proj", D),
+                     src.get(f"{p}.self_attn.f_a_proj.weight", (r, H)), rows("b_proj", 1)]
+            pad = (-Hh) % 8                                  # keep the stacked width a multiple of 8 columns
+            if pad:
+                parts.append(torch.zeros(pad, H, dtype=torch.float32, device=parts[0].device))
+            kw = KDAWeights(heads=Hh)
+            kw.w_in = make_linear(torch.cat(parts, 0), "none", dtype)
+            fb = src.get(f"{p}.self_attn.f_b_proj.weight", (Hk * D, r)).view(Hk, D, r)[a0:a1].reshape(-1, r)
+            kw.f_b = make_linear(fb, "none", dtype)
+            conv = [src.get(f"{p}.self_attn.{n}_conv1d.weight", (Hk * D, 4), "bias").view(Hk, D, 4)[a0:a1].reshape(-1, 4)
+                    for n in ("q", "k", "v")]
+            kw.conv_w = torch.cat(conv, 0).float().contiguous()
+            kw.A_log = src.get(f"{p}.self_attn.A_log", (Hk,), "bias")[a0:a1].float().contiguous()
+            kw.dt_bias = src.get(f"{p}.self_attn.dt_bias", (Hk * D,), "bias").view(Hk, D)[a0:a1].reshape(-1).float().contiguous()
+            kw.o_norm = src.get(f"{p}.self_attn.o_norm.weight", (D,), "norm").float().contiguous()
+            wo = src.get(f"{p}.self_attn.o_proj.weight", (H, Hk * D)).view(H, Hk, D)[:, a0:a1].reshape(H, -1)
+            lw.wo = make_linear(wo, quant, dtype)
+            lw.kda = kw
+        elif cfg.is_mla:
             qa = src.get(f"{p}.self_attn.q_a_proj.weight", (cfg.q_lora_rank, H))
             kva = src.get(f"{p}.self_attn.kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_head_dim, H))
             lw.wqkv_a = make_linear(torch.cat([qa, kva], 0), quant, dtype)

@@ -67,7 +67,15 @@ class Engine:
         n_pages = num_gpu_pages or ecfg.num_gpu_pages
         if not n_pages:
             raise ValueError("num_gpu_pages must be given (see planner.size_kv_pool for automatic sizing)")
-        self.kv = PagedKVCache(self.cfg, n_pages, ecfg.page_size, self.device, kv_dtype)
+        state_slots, state_heads = 0, None
+        if self.cfg.has_kda:
+            # every live sequence holds one recurrent-state slot from its prefill until it completes or is evicted
+            state_slots = ecfg.max_state_slots or ecfg.max_decode_batch
+            state_heads = next(lw.kda.heads for lw in model.w.layers if lw.kda is not None)
+            if ecfg.enable_prefix_cache:
+                raise ValueError("prefix reuse needs per-page state snapshots, which KDA layers do not keep")
+        self.kv = PagedKVCache(self.cfg, n_pages, ecfg.page_size, self.device, kv_dtype, state_slots=state_slots,
+                               state_heads=state_heads)
         self.host_kv = (PagedKVCache(self.cfg, num_host_pages, ecfg.page_size, "cpu", kv_dtype, pinned=True)
                         if num_host_pages else None)
         self.prefix = PrefixCache(self.kv.alloc, ecfg.page_size) if ecfg.enable_prefix_cache else None
@@ -114,8 +122,14 @@ class Engine:
             return 0
         return self.prefix.evict(want)
 
+    def _release_state(self, s: Sequence) -> None:
+        if s.state_slot >= 0:
+            self.kv.state.release(s.state_slot)
+            s.state_slot = -1
+
     def _complete(self, s: Sequence, reason: str) -> None:
         s.finish_reason = reason
+        self._release_state(s)
         if s.gpu_pages:
             self.kv.alloc.free(s.gpu_pages)
             s.gpu_pages = []
@@ -138,10 +152,13 @@ class Engine:
                                          reclaimable_pages=reclaimable)
         live = len(self._by_status(S.PREFILLED, S.IN_DECODE, S.ON_HOLD))
         self.guard.observe(len(sel.admitted), live, (len(cands), self._free_pages()))
-        if not sel.admitted:
+        admitted = list(sel.admitted)
+        if self.kv.state is not None:                 # sequence-slot cap of the recurrent-state pool
+            admitted = admitted[: self.kv.state.num_free]
+        if not admitted:
             return 0
         t0 = time.perf_counter()
-        wave = [self.seqs[i] for i in sel.admitted]
+        wave = [self.seqs[i] for i in admitted]
         new_lens: List[int] = []
         for s in wave:
             s.transition(S.IN_PREFILL)
@@ -156,6 +173,8 @@ class Engine:
             if need > self._free_pages():
                 self._reclaim(need - self._free_pages())
             s.gpu_pages = list(cached_pages) + self.kv.alloc.alloc(need)
+            if self.kv.state is not None and s.state_slot < 0:
+                s.state_slot = self.kv.state.acquire()
             s.cached_prefix_tokens = n_cached
             s.num_cached_tokens = n_cached
             new_lens.append(n_total - n_cached)
@@ -198,6 +217,10 @@ class Engine:
             slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
             block_table=build_block_table([s.gpu_pages for s in group], dev),
             cu_seqlens=cu, ctx_lens=ctx_lens,
+            state_slots=(torch.tensor([s.state_slot for s in group], dtype=torch.int32, device=dev)
+                         if self.kv.state is not None else None),
+            state_has_initial=(torch.tensor([int(c > 0) for c in ctx_lens], dtype=torch.int32, device=dev)
+                               if self.kv.state is not None else None),
             logit_rows=torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev))
         logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
         toks = self._sample(logits, group).tolist()
@@ -268,6 +291,7 @@ class Engine:
             self.kv.alloc.free(s.gpu_pages)
         if s.host_pages and self.host_kv is not None:
             self.host_kv.alloc.free(s.host_pages)
+        self._release_state(s)
         s.evict()
         s.output_ids = list(s.output_ids)     # decoded tokens are kept and replayed through prefill
         self.stats.evictions += 1
@@ -287,7 +311,9 @@ class Engine:
                 positions=torch.tensor(pos, dtype=torch.int32, device=dev),
                 slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
                 block_table=build_block_table([s.gpu_pages for s in rows], dev),
-                seqlens=torch.tensor(lens, dtype=torch.int32, device=dev))
+                seqlens=torch.tensor(lens, dtype=torch.int32, device=dev),
+                state_slots=(torch.tensor([s.state_slot for s in rows], dtype=torch.int32, device=dev)
+                             if self.kv.state is not None else None))
             logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
         toks = self._sample(logits, rows).tolist()
         for s, t in zip(rows, toks):

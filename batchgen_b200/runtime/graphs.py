@@ -87,7 +87,10 @@ class DecodeGraphRunner:
         self.lens = torch.zeros(B, dtype=torch.int32, device=d)
         self.bt = torch.zeros(B, max_pages_per_seq, dtype=torch.int32, device=d)
         self.num_valid = torch.zeros(1, dtype=torch.int32, device=d)
+        # KDA state slot of each row (-1 = padding row: the kernel skips it, so warm-up and capture touch no state)
+        self.state_slots = torch.full((B,), -1, dtype=torch.int32, device=d) if model.cfg.has_kda else None
         pin = torch.cuda.is_available()
+        self.h_state = torch.full((B,), -1, dtype=torch.int32, pin_memory=pin)
         self.h_ids = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
         self.h_pos = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
         self.h_slots = torch.full((B,), -1, dtype=torch.int64, pin_memory=pin)
@@ -112,7 +115,8 @@ class DecodeGraphRunner:
     # ------------------------------------------------------------------ capture
     def _meta(self, b: int) -> AttnMeta:
         return AttnMeta(mode="decode", positions=self.pos[:b], slot_mapping=self.slots[:b], block_table=self.bt[:b],
-                        seqlens=self.lens[:b], num_valid=self.num_valid)
+                        seqlens=self.lens[:b], num_valid=self.num_valid,
+                        state_slots=None if self.state_slots is None else self.state_slots[:b])
 
     def _forward(self, b: int) -> torch.Tensor:
         if self.sp:
@@ -126,8 +130,14 @@ class DecodeGraphRunner:
         side = torch.cuda.Stream(self.dev)
         side.wait_stream(torch.cuda.current_stream(self.dev))
         with torch.cuda.stream(side):
+            staged = None
+            if self.state_slots is not None:         # recurrent state is not idempotent: warm up on no slot at all
+                staged = self.state_slots.clone()
+                self.state_slots.fill_(-1)
             for _ in range(2):                       # warm-up: caches, attributes, work lists
                 self._forward(bucket)
+            if staged is not None:
+                self.state_slots.copy_(staged)
         torch.cuda.current_stream(self.dev).wait_stream(side)
         torch.cuda.synchronize(self.dev)
         g = torch.cuda.CUDAGraph()
@@ -150,10 +160,16 @@ class DecodeGraphRunner:
             self.capture(b)
 
     # ------------------------------------------------------------------ replay
-    def stage(self, ids: Optional[Seq[int]], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]]) -> int:
+    def stage(self, ids: Optional[Seq[int]], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]],
+              state_slots: Optional[Seq[int]] = None) -> int:
         """Fill the pinned staging buffers and enqueue the host->device copies.  Returns the bucket."""
         n = len(pos)
         b = self.bucketing.bucket_for(n)
+        if self.state_slots is not None:
+            self.h_state[:b] = -1
+            if state_slots is not None:
+                self.h_state[:n] = torch.as_tensor(state_slots, dtype=torch.int32)
+            self.state_slots[:b].copy_(self.h_state[:b], non_blocking=True)
         if ids is not None:
             self.h_ids[:n] = torch.as_tensor(ids, dtype=torch.int32)
         self.h_pos[:n] = torch.as_tensor(pos, dtype=torch.int32)
@@ -224,7 +240,8 @@ class DecodeGraphRunner:
 
     def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
         """Engine hook (``Engine.graph_runner``): logits of the live rows."""
-        b = self.stage(ids, pos, slots, lens, [s.gpu_pages for s in rows])
+        b = self.stage(ids, pos, slots, lens, [s.gpu_pages for s in rows],
+                       [s.state_slot for s in rows] if self.state_slots is not None else None)
         key = tuple(id(s) for s in rows)
         if key != self._row_key and self.model.cfg.is_mla and torch.device(self.dev).type == "cuda":
             # batch membership changed: put the longest sequences first in the attention work lists

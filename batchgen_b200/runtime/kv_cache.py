@@ -70,12 +70,16 @@ class PagedKVCache:
     """One tier (device or pinned host) of paged KV."""
 
     def __init__(self, cfg: ModelConfig, num_pages: int, page_size: int, device, dtype: torch.dtype,
-                 pinned: bool = False, row_dim: Optional[int] = None):
+                 pinned: bool = False, row_dim: Optional[int] = None, state_slots: int = 0,
+                 state_heads: Optional[int] = None):
         self.cfg, self.num_pages, self.page_size = cfg, num_pages, page_size
         self.device = torch.device(device)
         self.row_dim = row_dim or cfg.kv_cache_dim
         pin = pinned and self.device.type == "cpu" and torch.cuda.is_available()
-        self.kv = torch.zeros(cfg.num_layers, num_pages, page_size, self.row_dim, dtype=dtype, device=self.device,
+        # KDA layers keep no paged KV: layer l's rows live at index kv_index[l] of the pool
+        kv_layers = [l for l in range(cfg.num_layers) if not cfg.layer_is_kda(l)]
+        self.kv_index = {l: i for i, l in enumerate(kv_layers)}
+        self.kv = torch.zeros(len(kv_layers), num_pages, page_size, self.row_dim, dtype=dtype, device=self.device,
                               pin_memory=pin)
         self.idx_layers: Dict[int, int] = {}
         self.idx_k = self.idx_s = None
@@ -87,10 +91,12 @@ class PagedKVCache:
             self.idx_s = torch.zeros(len(layers), num_pages, page_size, dtype=torch.float32, device=self.device,
                                      pin_memory=pin)
         self.alloc = PageAllocator(num_pages)
+        # recurrent state of the KDA layers (device tier only)
+        self.state = StateSlotPool(cfg, state_slots, self.device, state_heads) if (cfg.has_kda and state_slots) else None
 
     # ---- views used by the model
     def latent(self, layer: int) -> torch.Tensor:
-        return self.kv[layer]
+        return self.kv[self.kv_index[layer]]
 
     def index_keys(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
         i = self.idx_layers[layer]
@@ -104,7 +110,7 @@ class PagedKVCache:
         self.idx_s[i].view(-1)[slots] = ks[valid]
 
     def bytes_per_page(self) -> int:
-        b = self.kv[0, 0].numel() * self.kv.element_size() * self.cfg.num_layers
+        b = self.kv[0, 0].numel() * self.kv.element_size() * self.kv.shape[0]
         if self.idx_k is not None:
             b += len(self.idx_layers) * (self.idx_k[0, 0].numel() + 4 * self.page_size)
         return b
@@ -130,6 +136,40 @@ class PagedKVCache:
                 if self.idx_k is not None:
                     self.idx_k[:, d].copy_(other.idx_k[:, s], non_blocking=True)
                     self.idx_s[:, d].copy_(other.idx_s[:, s], non_blocking=True)
+
+
+class StateSlotPool:
+    """Per-sequence recurrent state of the KDA layers: ``rec[i]`` [slots, H, D, D] fp32 and ``conv[i]``
+    [slots, 3 H D, 3] fp32 for the i-th KDA layer, plus a free list of slots.  A sequence holds one slot from
+    its first prefill chunk until it completes or is evicted (its state cannot be rebuilt from paged KV).
+
+    Reference parity: the KDA / compressed state GPU managers and their sequence-slot caps
+    (batchgen/kv_cache/kda_state_gpu_manager.py, batchgen/prefill.py:374-387)."""
+
+    def __init__(self, cfg: ModelConfig, num_slots: int, device, heads: Optional[int] = None):
+        self.layers = {l: i for i, l in enumerate(cfg.kda_layers)}
+        H, D = heads or cfg.kda_num_heads, cfg.kda_head_dim
+        self.num_slots = num_slots
+        self.rec = torch.zeros(len(self.layers), num_slots, H, D, D, dtype=torch.float32, device=device)
+        self.conv = torch.zeros(len(self.layers), num_slots, 3 * H * D, 3, dtype=torch.float32, device=device)
+        self._free = list(range(num_slots - 1, -1, -1))
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def acquire(self) -> int:
+        if not self._free:
+            raise OutOfPages("no free state slot")
+        return self._free.pop()
+
+    def release(self, slot: int) -> None:
+        assert 0 <= slot < self.num_slots and slot not in self._free
+        self._free.append(slot)
+
+    def layer(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        i = self.layers[layer]
+        return self.conv[i], self.rec[i]
 
 
 class _NullCtx:

@@ -98,6 +98,7 @@ class Sequence:
     # KV bookkeeping
     gpu_pages: List[int] = field(default_factory=list)      # physical GPU pages in order
     host_pages: List[int] = field(default_factory=list)     # physical host pages in order
+    state_slot: int = -1                                    # recurrent-state slot (models with KDA layers)
     num_cached_tokens: int = 0                              # tokens whose KV exists (either tier)
     cached_prefix_tokens: int = 0                           # tokens served by the prefix cache
     had_initial_gpu_reservation: bool = False

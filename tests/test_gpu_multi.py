@@ -33,3 +33,14 @@ def test_fused_sequence_parallel_forward_matches():
     assert res["argmax_agree_min"] > 0.8, res
     if res.get("decode_request_parallel_rel_max") is not None:      # decode with the request-parallel attention core
         assert res["decode_request_parallel_rel_max"] < 0.08, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_rank_leaves_between_steps_and_survivors_carry_on():
+    """A rank exits with nothing in flight; the other learns of it from the control store before its next
+    launch, skips the collective, sees a bounded device wait expire with a status, and keeps computing."""
+    res = _run("mp_rank_exit.py", 2, timeout=240)
+    assert res["steps_done"] == 3 and res["lost"] and res["lost"][0] == 1, res
+    assert "down" in res["lost"][1], res
+    assert res["ok_math"] and res["still_ok"] and res["wait_status"] == 1, res
+    assert 0.15 < res["waited_s"] < 5.0, res

@@ -1,0 +1,79 @@
+"""KDA (gated delta-rule linear attention): op-level reference properties and the engine on a model with
+KDA layers against the naive oracle (CPU, fp32)."""
+import torch
+
+from batchgen_b200.config import EngineConfig, get_model_config
+from batchgen_b200.models import build_model
+from batchgen_b200.models.naive import NaiveModel
+from batchgen_b200.models.weights import WeightSource
+from batchgen_b200.ops import kda
+from batchgen_b200.runtime.engine import Engine
+from batchgen_b200.runtime.sequence import SamplingParams
+
+
+def _inputs(T, H, D, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    HD = H * D
+    qkv = torch.randn(T, 3 * HD, generator=g)
+    f = torch.randn(T, HD, generator=g)
+    beta = torch.randn(T, H, generator=g)
+    z = torch.randn(T, HD, generator=g)
+    p = kda.KDAParams(conv_w=torch.randn(3 * HD, 4, generator=g) * 0.5, conv_b=None,
+                      A_log=torch.randn(H, generator=g) * 0.3, dt_bias=torch.randn(HD, generator=g) * 0.3,
+                      norm_w=1.0 + 0.1 * torch.randn(D, generator=g))
+    return qkv, f, beta, z, p
+
+
+def test_chunked_prefill_and_decode_continue_the_same_state():
+    H, D, T = 2, 16, 11
+    qkv, f, beta, z, p = _inputs(T, H, D)
+    conv = torch.zeros(3, 3 * H * D, 3)
+    rec = torch.zeros(3, H, D, D)
+    whole = kda.kda_forward(qkv, f, beta, z, p, conv, rec, [1], [0, T], [0], H, D, D ** -0.5, 1e-6)
+    # the same tokens as a 6-token chunk, a 4-token continuation and one decode step, in another slot
+    a = kda.kda_forward(qkv[:6], f[:6], beta[:6], z[:6], p, conv, rec, [2], [0, 6], [0], H, D, D ** -0.5, 1e-6)
+    b = kda.kda_forward(qkv[6:10], f[6:10], beta[6:10], z[6:10], p, conv, rec, [2], [0, 4], [1], H, D, D ** -0.5, 1e-6)
+    c = kda.kda_forward(qkv[10:], f[10:], beta[10:], z[10:], p, conv, rec, [2], None, None, H, D, D ** -0.5, 1e-6)
+    assert torch.allclose(torch.cat([a, b, c]), whole, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(rec[1], rec[2], atol=1e-6) and torch.allclose(conv[1], conv[2])
+    assert rec[0].abs().max() == 0                       # untouched slot
+
+
+def test_packed_sequences_are_independent_and_negative_slots_are_skipped():
+    H, D = 2, 16
+    qkv, f, beta, z, p = _inputs(9, H, D, seed=1)
+    conv = torch.zeros(4, 3 * H * D, 3)
+    rec = torch.zeros(4, H, D, D)
+    out = kda.kda_forward(qkv, f, beta, z, p, conv, rec, [0, -1, 3], [0, 4, 6, 9], [0, 0, 0], H, D, 0.25, 1e-6)
+    conv2, rec2 = torch.zeros_like(conv), torch.zeros_like(rec)
+    solo = kda.kda_forward(qkv[6:], f[6:], beta[6:], z[6:], p, conv2, rec2, [1], [0, 3], [0], H, D, 0.25, 1e-6)
+    assert torch.allclose(out[6:], solo, atol=1e-6)
+    assert out[4:6].abs().max() == 0 and rec[1].abs().max() == 0
+    assert torch.allclose(rec[3], rec2[1])
+
+
+def test_decay_bounds_and_delta_rule_fixed_point():
+    H, D = 1, 8
+    g = kda.kda_gate(torch.randn(5, H * D), torch.zeros(H), torch.zeros(H * D), H, D)
+    assert (g <= 0).all()
+    # with no decay and beta = 1, writing (k, v) then reading with q = k returns v exactly (k has unit norm)
+    k = torch.randn(1, H, D)
+    v = torch.randn(1, H, D)
+    S = torch.zeros(H, D, D)
+    o = kda.kda_recurrent_ref(k.clone(), k.clone(), v, torch.zeros(1, H, D), torch.ones(1, H), S, 1.0)
+    assert torch.allclose(o, v, atol=1e-4)
+
+
+def test_engine_with_kda_layers_matches_naive_oracle():
+    cfg = get_model_config("tiny-kimi-linear")
+    model = build_model(cfg, device="cpu", dtype=torch.float32, seed=11)
+    ecfg = EngineConfig(page_size=16, max_decode_batch=4, max_state_slots=2, enable_cuda_graph=False)
+    eng = Engine(model, ecfg, num_gpu_pages=64)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 17, 5)]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True))
+    oracle = NaiveModel(cfg, WeightSource(seed=11))
+    for pr, o in zip(prompts, outs):
+        assert o == oracle.generate(pr, 4)
+    assert eng.kv.state.num_free == 2                    # three sequences shared two slots and returned them
+    assert eng.kv.kv.shape[0] == 1                       # only the MLA layer owns paged KV
