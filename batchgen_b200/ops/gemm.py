@@ -69,14 +69,21 @@ def _use_wide(kind, D, M, N, wide) -> bool:
     return tiles >= 2 * _ext.num_sms(D.device)
 
 
-def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None):
+def wide_enabled() -> bool:
+    return _WIDE != "0"
+
+
+def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None, a_ready=None):
+    """``a_ready`` = (flag pointer, epoch, epoch-base pointer, world): the rows of A are pushed by peers and the
+    128 x 256 kernel's producer waits for every rank's arrival flag (only that kernel takes it this way)."""
     L = _ext.lib()
-    if _use_wide(kind, D, M, N, wide):
+    if a_ready is not None or _use_wide(kind, D, M, N, wide):
+        flag, epoch, base, world = a_ready if a_ready is not None else (ctypes.c_void_p(0), 0, ctypes.c_void_p(0), 1)
         rc = L.bg_gemm_fp8_n256(ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride), _ext.ptr(B),
                                 _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets), _ext.ptr(counts),
                                 ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
-                                ctypes.c_int(_ext.num_sms(A.device)), ctypes.c_void_p(0), ctypes.c_uint32(0),
-                                ctypes.c_void_p(0), ctypes.c_int(1), _ext.ptr(_ext.status_word(A.device)), _ext.stream())
+                                ctypes.c_int(_ext.num_sms(A.device)), flag, ctypes.c_uint32(epoch),
+                                base, ctypes.c_int(world), _ext.ptr(_ext.status_word(A.device)), _ext.stream())
         _ext.check(rc, "bg_gemm_fp8_n256")
         return
     if counts is not None:
@@ -113,7 +120,7 @@ def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
 def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
                      offsets: torch.Tensor, out: Optional[torch.Tensor] = None,
                      silu_mul: bool = False, counts: Optional[torch.Tensor] = None,
-                     wide: Optional[bool] = None) -> torch.Tensor:
+                     wide: Optional[bool] = None, a_ready=None) -> torch.Tensor:
     """Ragged grouped GEMM.  xq: [R, K] rows grouped by expert, segment e = offsets[e]:offsets[e+1]
     (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K].  ``counts`` (int32 [E],
     device) gives the rows really present in each segment: padding rows are then neither stored nor, as
@@ -136,7 +143,7 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
     if counts is not None:
         assert counts.dtype == torch.int32 and counts.is_cuda and counts.numel() >= E
     _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq.view(E * N, K), ws, out,
-            offsets, E, R, N, K, wide=wide, counts=counts)
+            offsets, E, R, N, K, wide=wide, counts=counts, a_ready=a_ready)
     return out
 
 

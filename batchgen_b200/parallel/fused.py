@@ -279,9 +279,16 @@ class FusedComm(NcclComm):
         # ---- experts on the receive buffer: the gate/up GEMM waits for every source rank's rows
         xs = self.recv_s.t()[: self.recv_cap]
         with timer.timed("moe.s1_gemm"):
-            self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
-            act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
-                                            counts=self.recv_counts)
+            if gemm_ops.wide_enabled() and Tl * K >= 4096:
+                # prefill-sized steps: 128 x 256 tiles (less operand traffic per FLOP); its producer waits for
+                # the arrival flags itself
+                act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
+                                                counts=self.recv_counts,
+                                                a_ready=(self._flag_ptr(DISP_READY), e_disp, self._base(), W))
+            else:
+                self._set_hooks(a_ready=self._flag_ptr(DISP_READY), a_ready_rows=0, epoch=e_disp)
+                act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
+                                                counts=self.recv_counts)
         with timer.timed("moe.act_quant"):
             aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
