@@ -3,7 +3,7 @@
 
     python benchmarks/kernel_bench.py <case> [--iters N] [size flags]
 
-Cases: gemm_fp8, gemm_bf16, grouped_fp8, mla_decode, mla_prefill, norm_quant.  Each case uses inputs
+Cases: gemm_fp8, gemm_bf16, grouped_fp8, mla_decode, mla_prefill, mha_prefill, kda_decode, kda_prefill, norm_quant.  Each case uses inputs
 larger than the 126 MB L2, warms up, times with CUDA events on the launching stream and prints one JSON
 line: time, achieved TFLOP/s or GB/s, and the fraction "of measured" peak (MEASURED_PEAKS.json at the
 repository root when present, else the fallback figures 6.65 TB/s / 1.59 PFLOP/s, "of fallback").
@@ -113,6 +113,36 @@ def main():
             fl = 2.0 * B * (L * (L + 1) / 2) * H * (576 + 512)
         out.update(shape=[B, H, L], ms=ms, kv_gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm,
                    tflops=fl / ms / 1e9, frac_of_bf16_gemm_peak=fl / ms / 1e9 / tf, peak_note=tag)
+    elif a.case == "mha_prefill":
+        from batchgen_b200.ops import attention as attn_ops
+        B, H, L = a.batch, a.heads, a.ctx
+        T = B * L
+        q = torch.randn(T, H, 192, device=dev).to(torch.bfloat16)
+        kv = torch.randn(T, H, 256, device=dev).to(torch.bfloat16)
+        kpe = torch.randn(T, 64, device=dev).to(torch.bfloat16)
+        cu = [i * L for i in range(B + 1)]
+        work = attn_ops.mha_prefill_work(cu, [0] * B, cu[:-1]).to(dev)
+        ms = timeit(lambda: attn_ops.mha_prefill(q, kv, kpe, work, 0.07), a.iters)
+        fl = 2.0 * B * (L * (L + 1) / 2) * H * (192 + 128)
+        out.update(shape=[B, H, L], ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_gemm_peak=fl / ms / 1e9 / tf, peak_note=tag)
+    elif a.case in ("kda_decode", "kda_prefill"):
+        from batchgen_b200.ops import kda
+        B, H, D = a.batch, a.heads, 128
+        L = 1 if a.case == "kda_decode" else a.ctx
+        T, HD = B * L, H * D
+        wide = torch.randn(T, 4 * HD + 8, device=dev).to(torch.bfloat16)
+        f = torch.randn(T, HD, device=dev).to(torch.bfloat16)
+        p = kda.KDAParams(torch.randn(3 * HD, 4, device=dev) * 0.5, None, torch.zeros(H, device=dev),
+                          torch.zeros(HD, device=dev), torch.ones(D, device=dev))
+        conv = torch.zeros(B, 3 * HD, 3, device=dev)
+        rec = torch.zeros(B, H, D, D, device=dev)
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        cu = None if L == 1 else torch.arange(B + 1, dtype=torch.int32, device=dev) * L
+        ms = timeit(lambda: kda.kda_forward(wide[:, : 3 * HD], f, wide[:, 4 * HD: 4 * HD + H], wide[:, 3 * HD: 4 * HD], p,
+                                            conv, rec, slots, cu, None, H, D, D ** -0.5, 1e-6), a.iters)
+        byts = 2 * B * H * D * D * 4 + T * HD * 2 * 6
+        out.update(shape=[B, H, L], ms=ms, gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm,
+                   us_per_token=ms * 1e3 / L, peak_note=tag)
     elif a.case == "norm_quant":
         T, H = a.m, 7168
         x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)

@@ -1,4 +1,5 @@
 """Sampling residency, lifespan rings, restart coordinator, runtime locks."""
+import os
 import threading
 import time
 
@@ -215,3 +216,64 @@ def test_weight_store_staging_is_idempotent_and_detects_damage(tmp_path):
     import pytest as _pt
     with _pt.raises(FileNotFoundError):
         ws.stage_store(str(src), str(dst))
+
+
+# ---------------------------------------------------------------------------------------------- lane leases
+def test_lane_lease_handover_and_conflicts(tmp_path, monkeypatch):
+    from batchgen_b200.server import runtime_lease as rl
+    root = tmp_path / "lanes"
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    want = rl.expected_for_server(["GPU-aaa", "GPU-bbb"], 8000, 29500, tmp_path / "store")
+    res = rl.LaneReservation.reserve("prod-a", want, lock_root=root)
+    # a second launcher cannot take an overlapping lane
+    other = rl.expected_for_server(["GPU-bbb"], 8001, 29501, tmp_path / "store2")
+    with pytest.raises(rl.LaneLeaseError, match="held by another run"):
+        rl.LaneReservation.reserve("prod-b", other, lock_root=root)
+    # the server adopts exactly what it is about to use
+    with pytest.raises(rl.LaneLeaseError, match="another instance"):
+        rl.LaneLease.adopt(res.manifest_fd, "prod-x", want, lock_root=root)
+    with pytest.raises(rl.LaneLeaseError, match="does not cover"):
+        rl.LaneLease.adopt(res.manifest_fd, "prod-a", want | {"port:9"}, lock_root=root)
+    lease = rl.LaneLease.adopt(res.manifest_fd, "prod-a", want, lock_root=root)
+    assert lease.held == len(want) == 5
+    lease.release()                                      # closes the shared descriptions: the lane is free again
+    res2 = rl.LaneReservation.reserve("prod-b", other, lock_root=root)
+    res2.release()
+
+
+def test_lane_lease_rejects_foreign_descriptors_and_unsafe_root(tmp_path):
+    import json
+    from batchgen_b200.server import runtime_lease as rl
+    root = tmp_path / "lanes"
+    want = rl.resource_names(["GPU-x"], [1234], [])
+    res = rl.LaneReservation.reserve("inst", want, lock_root=root)
+    # a manifest that points a resource at some other file
+    stray = os.open(tmp_path / "stray", os.O_RDWR | os.O_CREAT, 0o600)
+    fake = dict(res.fds)
+    fake["port:1234"] = stray
+    mfd = os.open(tmp_path / "m.json", os.O_RDWR | os.O_CREAT, 0o600)
+    os.pwrite(mfd, json.dumps({"version": 1, "instance_id": "inst", "resources": fake}).encode(), 0)
+    with pytest.raises(rl.LaneLeaseError, match="not its lock file"):
+        rl.LaneLease.adopt(mfd, "inst", want, lock_root=root)
+    os.chmod(root, 0o755)
+    with pytest.raises(rl.LaneLeaseError, match="mode 0700"):
+        rl.LaneLease.adopt(res.manifest_fd, "inst", want, lock_root=root)
+    os.chmod(root, 0o700)
+    res.release()
+    os.close(stray)
+    os.close(mfd)
+
+
+def test_run_identity_names():
+    from batchgen_b200.server import runtime_lease as rl
+    a = rl.RunIdentity.create("prod-a")
+    b = rl.RunIdentity.create("prod-a")
+    assert a.run_id != b.run_id and a.shm_name("host_kv").startswith(f"bgb200_prod-a_{a.run_id}.")
+    assert a.runtime_dir != b.runtime_dir
+    for bad in ("", "Prod", "-x", "a" * 49):
+        with pytest.raises(ValueError):
+            rl.RunIdentity.create(bad)
+    with pytest.raises(ValueError):
+        rl.RunIdentity.create("ok", run_id="xyz")
+    with pytest.raises(ValueError):
+        rl.RunIdentity.create("ok", mode="both")
