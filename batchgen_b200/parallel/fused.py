@@ -24,6 +24,7 @@ Every wait is bounded; an expired wait raises the status word that ``ops._ext.ch
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -36,6 +37,8 @@ from .symm import MAX_WORLD, SymmetricHeap
 
 FP8 = torch.float8_e4m3fn
 AG_READY, RS_READY, CNT_READY, DISP_READY, RET_READY, A2A_READY = 0, 8, 16, 24, 32, 40
+# rows this rank sends per step from which the gate/up grouped GEMM of the expert-parallel path runs on 128 x 256 tiles
+WIDE_S1_MIN_ROWS = int(os.environ.get("BG_WIDE_S1_MIN_ROWS", "0"))
 ALIGN = 128
 
 
@@ -278,8 +281,13 @@ class FusedComm(NcclComm):
         self.nvlink_bytes += Tl * K * (H + 4 * (H // 128)) * (W - 1) // W
         # ---- experts on the receive buffer: the gate/up GEMM waits for every source rank's rows
         xs = self.recv_s.t()[: self.recv_cap]
+        if timer.enabled:
+            # profiling only: take the wait for the peers' rows out of the GEMM's interval
+            with timer.timed("moe.dispatch_wait"):
+                _ext.check(L.bg_wait_flags(self._flag_ptr(DISP_READY), ctypes.c_int(W), ctypes.c_uint32(e_disp),
+                                           self._base(), self._status(), st), "bg_wait_flags")
         with timer.timed("moe.s1_gemm"):
-            if gemm_ops.wide_enabled() and Tl * K >= 4096:
+            if gemm_ops.wide_enabled() and Tl * K >= WIDE_S1_MIN_ROWS:
                 # prefill-sized steps: 128 x 256 tiles (less operand traffic per FLOP); its producer waits for
                 # the arrival flags itself
                 act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
