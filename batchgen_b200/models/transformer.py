@@ -149,15 +149,21 @@ class Transformer:
             return o.reshape(T, -1)
         q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
         # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
+        rp = self._request_parallel(meta, T)
         with tm.timed("attn.q_absorb", l):
-            q_abs = attn_ops.mla_q_absorb(q, lw.w_uk_t, cfg.qk_nope_head_dim)
+            if rp:      # both query parts in one [T, Hh, kv_lora + rope] buffer: the exchange moves it as it is
+                qbuf = torch.empty(T, q.shape[1], cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=q.dtype, device=q.device)
+                q_abs = attn_ops.mla_q_absorb(q, lw.w_uk_t, cfg.qk_nope_head_dim, out=qbuf[..., : cfg.kv_lora_rank])
+                qbuf[..., cfg.kv_lora_rank:] = q_pe
+            else:
+                q_abs = attn_ops.mla_q_absorb(q, lw.w_uk_t, cfg.qk_nope_head_dim)
         sel = None
         if cfg.has_dsa:
             with tm.timed("attn.dsa_indexer", l):
                 sel = self._dsa_select(l, lw, x, qn, meta, cache)
         with tm.timed("attn.core_" + meta.mode, l):
-            if self._request_parallel(meta, T):
-                o_lat = self._mla_core_request_parallel(l, q_abs, q_pe, meta, cache)
+            if rp:
+                o_lat = self._mla_core_request_parallel(l, qbuf, meta, cache)
             else:
                 o_lat = self._mla_core(l, lw, q_abs, q_pe, sel, meta, cache)
         # out-absorb W_UV: [T, Hh, kv_lora] x [Hh, v, kv_lora]^T -> [T, Hh * v]
@@ -210,22 +216,21 @@ class Transformer:
         return (self.attn_request_parallel and meta.mode == "decode" and self.comm is not None
                 and self.layout.tp_size > 1 and T % self.layout.tp_size == 0 and not self.cfg.has_dsa)
 
-    def _mla_core_request_parallel(self, l, q_abs, q_pe, meta: AttnMeta, cache):
+    def _mla_core_request_parallel(self, l, qbuf, meta: AttnMeta, cache):
         """Decode attention with the projections head-sharded (TP) but the core split by request: an
         all-to-all turns [all rows, my heads] queries into [my rows, all heads], each rank attends over the
         latent KV of its own rows only (the KV is not replicated: 1/world of the bytes per rank instead of
         all of them), and a second all-to-all returns [all rows, my heads] outputs for the out-absorb and
         o_proj.  Row i belongs to rank i // (T / world)."""
         W, r = self.layout.tp_size, self.layout.tp_rank
-        T, Hh, L = q_abs.shape
+        T, Hh, D = qbuf.shape                          # [all rows, my heads, kv_lora + rope]
+        L = self.cfg.kv_lora_rank
         Tl = T // W
-        q = torch.cat([q_abs, q_pe], -1).view(W, Tl, Hh, -1)
-        q = self.comm.all_to_all(q).permute(1, 0, 2, 3).reshape(Tl, W * Hh, -1)
+        q = self.comm.a2a_rows_to_ranks(qbuf.view(T, Hh * D)).view(Tl, W * Hh, D)
         rows = slice(r * Tl, (r + 1) * Tl)
-        o = attn_ops.mla_decode(q[..., :L].contiguous(), q[..., L:].contiguous(), cache.latent(l),
-                                meta.block_table[rows], meta.seqlens[rows], self.cfg.softmax_scale, self.cfg.kv_lora_rank)
-        o = o.view(Tl, W, Hh, L).permute(1, 0, 2, 3)
-        return self.comm.all_to_all(o).reshape(T, Hh, L)
+        o = attn_ops.mla_decode(q[..., :L], q[..., L:], cache.latent(l), meta.block_table[rows], meta.seqlens[rows],
+                                self.cfg.softmax_scale, self.cfg.kv_lora_rank)
+        return self.comm.a2a_ranks_to_rows(o.view(Tl, W, Hh * L)).view(T, Hh, L)
 
     def _mla_core(self, l, lw, q_abs, q_pe, sel, meta, cache):
         cfg = self.cfg

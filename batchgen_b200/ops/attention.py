@@ -51,15 +51,21 @@ def _head_gemm(a: torch.Tensor, a_head: int, K: int, w: torch.Tensor, out: torch
     _ext.check(rc, "bg_head_gemm")
 
 
-def mla_q_absorb(q: torch.Tensor, w_uk_t: torch.Tensor, nope: int) -> torch.Tensor:
-    """q [T, H, nope + rope] (the q projection, in place) x W_UK^T [H, kv_lora, nope] -> q_abs [T, H, kv_lora]."""
+def mla_q_absorb(q: torch.Tensor, w_uk_t: torch.Tensor, nope: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, H, nope + rope] (the q projection, in place) x W_UK^T [H, kv_lora, nope] -> q_abs [T, H, kv_lora].
+    ``out`` may be a [T, H, kv_lora] view of a wider buffer (unit inner stride)."""
     T, H, D = q.shape
     if (q.is_cuda and q.dtype == torch.bfloat16) and q.stride(2) == 1 and q.stride(1) == D and nope % 64 == 0 and D % 8 == 0:
-        out = torch.empty(T, H, w_uk_t.shape[1], dtype=q.dtype, device=q.device)
+        if out is None:
+            out = torch.empty(T, H, w_uk_t.shape[1], dtype=q.dtype, device=q.device)
         _head_gemm(q.view(T, H * D) if q.is_contiguous() else q.as_strided((T, H * D), (q.stride(0), 1)), D, nope,
                    w_uk_t, out, out.stride(0), out.stride(1))
         return out
-    return torch.bmm(q[..., :nope].transpose(0, 1), w_uk_t.transpose(1, 2)).transpose(0, 1)
+    res = torch.bmm(q[..., :nope].transpose(0, 1), w_uk_t.transpose(1, 2)).transpose(0, 1)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def mla_out_absorb(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:

@@ -106,7 +106,7 @@ int bg_mla_decode_split_noalloc(const void* q_abs, const void* q_pe, long long q
   int rc = (ncol == 16) ? launch<16>(tkv, tq, tqpe, p, (int)n_work, stream) : launch<32>(tkv, tq, tqpe, p, (int)n_work, stream);
   if (rc == -12) return BG_NOALLOC_E_SETUP;
   if (rc != 0) return rc;
-  mla_merge_kernel<<<B * groups, 128, 0, stream>>>(p.part_o, p.part_ml, &s->items[0][0], p.out, ncol, H, hpg);
+  mla_merge_kernel<<<dim3(B * groups, ncol), 128, 0, stream>>>(p.part_o, p.part_ml, &s->items[0][0], p.out, ncol, H, hpg);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -502,35 +502,39 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
   if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
 }
 
-// Merge split-KV partials: one block per (row, head); slot of split s = first_slot[item] + s.
+// Merge split-KV partials: one block per (work item, column); slot of split s = first_slot[item] + s.  A block's
+// loads do not depend on one another (no early exit between them), so the splits' rows stream in together.
 static __global__ void __launch_bounds__(128)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
                  __nv_bfloat16* __restrict__ out, int ncol, int H, int hpg) {
   // items[i] = {q_row, n_q, head_group, first_slot, n_splits}
   const int* it = items + blockIdx.x * 5;
   const int q_row = it[0], n_q = it[1], hg = it[2], first = it[3], ns = it[4];
-  for (int j = 0; j < ncol; ++j) {
-    const int qi = j / hpg, hl = j % hpg;
-    if (qi >= n_q) continue;
-    float m = -INFINITY;
-    for (int s = 0; s < ns; ++s) m = fmaxf(m, part_ml[((size_t)(first + s) * ncol + j) * 2]);
-    float l = 0.f;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < ns; ++s) {
-      const float ms = part_ml[((size_t)(first + s) * ncol + j) * 2];
-      const float ls = part_ml[((size_t)(first + s) * ncol + j) * 2 + 1];
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - m);
-      l += ls * f;
-      const float* po = part_o + ((size_t)(first + s) * ncol + j) * kLatent;
+  const int j = blockIdx.y;
+  const int qi = j / hpg, hl = j % hpg;
+  if (qi >= n_q) return;
+  const float* ml = part_ml + ((size_t)first * ncol + j) * 2;
+  const size_t ml_step = (size_t)ncol * 2, o_step = (size_t)ncol * kLatent;
+  float m = -INFINITY;
+  for (int s = 0; s < ns; ++s) m = fmaxf(m, ml[s * ml_step]);
+  float l = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* po = part_o + ((size_t)first * ncol + j) * kLatent + threadIdx.x;
+#pragma unroll 4
+  for (int s = 0; s < ns; ++s) {
+    const float ms = ml[s * ml_step], ls = ml[s * ml_step + 1];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    l = fmaf(ls, f, l);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) acc[q] += po[threadIdx.x + 128 * q] * f;
+    for (int q = 0; q < 4; ++q) {
+      const float v = po[s * o_step + 128 * q];
+      acc[q] = (f == 0.f) ? acc[q] : fmaf(v, f, acc[q]);        // an empty split's partial row is undefined
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat16* o = out + ((size_t)(q_row + qi) * H + hg * hpg + hl) * kLatent;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) o[threadIdx.x + 128 * q] = __float2bfloat16(acc[q] * inv);
   }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  __nv_bfloat16* o = out + ((size_t)(q_row + qi) * H + hg * hpg + hl) * kLatent;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) o[threadIdx.x + 128 * q] = __float2bfloat16(acc[q] * inv);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -53,10 +53,12 @@ def _qpe_view(q_pe: torch.Tensor):
 
 def _launch(q_abs, q_pe, cache, work, n_work, block_table, seqlens, out, part_o, part_ml, H, hpg, ncol, scale):
     q_pe, qpe_stride = _qpe_view(q_pe)
+    q_abs, qabs_stride = _qpe_view(q_abs)          # same rule: unit inner stride, dense over heads, 16-byte steps
     R = q_abs.shape[0]
     P, S, D = cache.shape
-    rc = _ext.lib().bg_mla_attention(
-        _ext.ptr(q_abs), _ext.ptr(q_pe), ctypes.c_longlong(qpe_stride), ctypes.c_longlong(R * H), _ext.ptr(cache),
+    rc = _ext.lib().bg_mla_attention_strided(
+        _ext.ptr(q_abs), ctypes.c_longlong(qabs_stride), _ext.ptr(q_pe), ctypes.c_longlong(qpe_stride),
+        ctypes.c_longlong(R * H), _ext.ptr(cache),
         ctypes.c_longlong(P * S), _ext.ptr(work), ctypes.c_int(n_work), _ext.ptr(block_table),
         ctypes.c_int(block_table.stride(0)), _ext.ptr(seqlens), _ext.ptr(out), _ext.ptr(part_o), _ext.ptr(part_ml),
         ctypes.c_int(H), ctypes.c_int(hpg), ctypes.c_int(ncol), ctypes.c_float(scale),
@@ -104,7 +106,7 @@ def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_
     """q_abs [B, H, 512], q_pe [B, H, 64] -> [B, H, 512]."""
     B, H, _ = q_abs.shape
     dev = q_abs.device
-    q_abs = q_abs.contiguous()
+    # q_abs may be a strided view (see _launch); only a non-unit inner stride forces a copy there
     hpg, ncol = _geometry(H, prefill=False)
     groups = H // hpg
     if num_splits <= 0:
@@ -139,7 +141,7 @@ def mla_prefill_tc(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], c
     """Varlen causal MLA: query j of sequence i attends to cache positions 0 .. ctx_i + j."""
     T, H, _ = q_abs.shape
     dev = q_abs.device
-    q_abs = q_abs.contiguous()
+    # (strided q_abs views are accepted, see _launch)
     hpg, ncol = _geometry(H, prefill=True)
     groups, qt = H // hpg, ncol // hpg
     rows = []

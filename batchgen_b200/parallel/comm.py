@@ -58,6 +58,18 @@ class NcclComm:
         self.bytes_sent += x.numel() * x.element_size() * (self.world - 1) // self.world
         return out
 
+    def a2a_rows_to_ranks(self, x: torch.Tensor) -> torch.Tensor:
+        """x [world * n, c] (block d of n rows is bound for rank d) -> [n, world, c]: for each of this rank's n rows,
+        the c-wide piece every rank holds of it."""
+        W = self.world
+        n = x.shape[0] // W
+        return self.all_to_all(x.view(W, n, -1)).transpose(0, 1).contiguous()
+
+    def a2a_ranks_to_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """The inverse exchange: x [n, world, c] (piece d of every row returns to rank d) -> [world * n, c]."""
+        n, W, c = x.shape
+        return self.all_to_all(x.transpose(0, 1).contiguous()).view(W * n, c)
+
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return x

@@ -335,17 +335,25 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, i
   }
 }
 
-// All-to-all of equal slices over peer memory: slice d of `src` ([world, slice]) is stored into rank d's
-// receive buffer at slot my_rank; when the last CTA is done every rank's flag (index + my_rank) is raised.
-// grid = (blocks per slice, world); blockIdx.y walks the destinations in ring order starting with this rank.
+// All-to-all of equal slices over peer memory.  A slice is `n_chunks` chunks of `chunk_vec` 16-byte vectors; chunk b
+// bound for rank d is read at src + d * src_d + b * src_b and stored into rank d's receive buffer at
+// my_rank * dst_r + b * dst_b (all in vectors), so either side of the exchange can be laid out [rank, chunk] or
+// [chunk, rank] and no transposing copy is needed around it.  When the last CTA is done every rank's flag
+// (index + my_rank) is raised.  grid = (blocks per slice, world); blockIdx.y walks the destinations in ring order
+// starting with this rank.
 __global__ void __launch_bounds__(256)
-a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t slice_vec, int my_rank, int world, Peers flags,
-                int ready_index, Epoch epoch_e, unsigned int* counter) {
+a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_t chunk_vec, size_t src_d, size_t src_b,
+                size_t dst_r, size_t dst_b, int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e,
+                unsigned int* counter) {
   const uint32_t epoch = epoch_e.get();
   const int d = (my_rank + blockIdx.y) % world;
-  const uint4* s = src + (size_t)d * slice_vec;
-  uint4* o = reinterpret_cast<uint4*>(dst.p[d]) + (size_t)my_rank * slice_vec;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < slice_vec; i += (size_t)gridDim.x * blockDim.x) o[i] = s[i];
+  const uint4* s = src + (size_t)d * src_d;
+  uint4* o = reinterpret_cast<uint4*>(dst.p[d]) + (size_t)my_rank * dst_r;
+  const size_t total = n_chunks * chunk_vec;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = i / chunk_vec, within = i - b * chunk_vec;
+    o[b * dst_b + within] = s[b * src_b + within];
+  }
   // last-CTA-out over the whole 2-D grid
   __threadfence_system();
   __syncthreads();
@@ -444,20 +452,30 @@ int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T,
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// Chunked form (see a2a_push_kernel): sizes and strides in bytes, multiples of 16.
+int bg_a2a_push_chunks(const void* src, void* const* dst, unsigned long long n_chunks, unsigned long long chunk_bytes,
+                       unsigned long long src_d, unsigned long long src_b, unsigned long long dst_r,
+                       unsigned long long dst_b, int my_rank, int world, void* const* flags, int ready_index,
+                       uint32_t epoch, const uint32_t* epoch_base, unsigned int* counter, cudaStream_t stream) {
+  if (n_chunks == 0 || chunk_bytes == 0) return 0;
+  if ((chunk_bytes | src_d | src_b | dst_r | dst_b) % 16 != 0 || world < 1 || world > 8) return -1;
+  const size_t vec = n_chunks * (chunk_bytes / 16);
+  int bx = (int)((vec + 255) / 256);
+  if (bx > 64) bx = 64;
+  dim3 grid(bx, world);
+  bg::comm::a2a_push_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), to_peers(dst, world), n_chunks,
+                                                      chunk_bytes / 16, src_d / 16, src_b / 16, dst_r / 16, dst_b / 16,
+                                                      my_rank, world, to_peers(flags, world), ready_index,
+                                                      bg::comm::Epoch{epoch, epoch_base}, counter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 // src: [world, slice_bytes] (slice_bytes a multiple of 16); dst[r]: rank r's receive buffer [world, slice_bytes].
 int bg_a2a_push(const void* src, void* const* dst, unsigned long long slice_bytes, int my_rank, int world,
                 void* const* flags, int ready_index, uint32_t epoch, const uint32_t* epoch_base, unsigned int* counter,
                 cudaStream_t stream) {
-  if (slice_bytes == 0) return 0;
-  if (slice_bytes % 16 != 0 || world < 1 || world > 8) return -1;
-  const size_t vec = slice_bytes / 16;
-  int bx = (int)((vec + 255) / 256);
-  if (bx > 64) bx = 64;
-  dim3 grid(bx, world);
-  bg::comm::a2a_push_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), to_peers(dst, world), vec, my_rank,
-                                                      world, to_peers(flags, world), ready_index,
-                                                      bg::comm::Epoch{epoch, epoch_base}, counter);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return bg_a2a_push_chunks(src, dst, 1, slice_bytes, slice_bytes, 0, slice_bytes, 0, my_rank, world, flags, ready_index,
+                            epoch, epoch_base, counter, stream);
 }
 
 int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int* status,

@@ -228,20 +228,53 @@ class FusedComm(NcclComm):
         slice_bytes = nbytes // W
         if W == 1 or not self.a2a_bufs or nbytes > self.a2a_bytes or slice_bytes % 16:
             return super().all_to_all(x)
+        buf = self._a2a_exchange(x, 1, slice_bytes, slice_bytes, 0, slice_bytes, 0)
+        return buf[:nbytes].view(x.dtype).view(x.shape)
+
+    def _a2a_exchange(self, x, n_chunks, chunk_bytes, src_d, src_b, dst_r, dst_b) -> torch.Tensor:
+        """One chunked push (see ``a2a_push_kernel``) plus the wait for every rank's arrival flag; returns the
+        receive buffer (bytes)."""
+        W = self.world
         name = "a2a0" if self._a2a_turn == 0 else "a2a1"
         buf = self.a2a_bufs[self._a2a_turn]
         self._a2a_turn ^= 1
         epoch = self._next(A2A_READY)
         st = _ext.stream()
-        rc = _ext.lib().bg_a2a_push(_ext.ptr(x), self.heap.peer_ptrs(name), ctypes.c_ulonglong(slice_bytes),
-                                    ctypes.c_int(self.rank), ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(A2A_READY),
-                                    ctypes.c_uint32(epoch), self._base(), _ext.ptr(self.counters[4:5]), st)
-        _ext.check(rc, "bg_a2a_push")
+        ull = ctypes.c_ulonglong
+        rc = _ext.lib().bg_a2a_push_chunks(_ext.ptr(x), self.heap.peer_ptrs(name), ull(n_chunks), ull(chunk_bytes),
+                                           ull(src_d), ull(src_b), ull(dst_r), ull(dst_b), ctypes.c_int(self.rank),
+                                           ctypes.c_int(W), self.flag_ptrs, ctypes.c_int(A2A_READY),
+                                           ctypes.c_uint32(epoch), self._base(), _ext.ptr(self.counters[4:5]), st)
+        _ext.check(rc, "bg_a2a_push_chunks")
         rc = _ext.lib().bg_wait_flags(self._flag_ptr(A2A_READY), ctypes.c_int(W), ctypes.c_uint32(epoch), self._base(),
                                       self._status(), st)
         _ext.check(rc, "bg_wait_flags")
-        self.nvlink_bytes += slice_bytes * (W - 1)
-        return buf[:nbytes].view(x.dtype).view(x.shape)
+        self.nvlink_bytes += n_chunks * chunk_bytes * (W - 1)
+        return buf
+
+    def _a2a_fits(self, x: torch.Tensor, chunk_bytes: int) -> bool:
+        return (self.world > 1 and bool(self.a2a_bufs) and x.is_contiguous()
+                and x.numel() * x.element_size() <= self.a2a_bytes and chunk_bytes % 16 == 0)
+
+    def a2a_rows_to_ranks(self, x: torch.Tensor) -> torch.Tensor:
+        """[world * n, c] -> [n, world, c]; the push kernel stores each row's piece at its final place, so no
+        transposing copy follows."""
+        W = self.world
+        n, c = x.shape[0] // W, x.shape[1]
+        cb = c * x.element_size()
+        if not self._a2a_fits(x, cb):
+            return super().a2a_rows_to_ranks(x)
+        buf = self._a2a_exchange(x, n, cb, n * cb, cb, cb, W * cb)
+        return buf[: x.numel() * x.element_size()].view(x.dtype).view(n, W, c)
+
+    def a2a_ranks_to_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """[n, world, c] -> [world * n, c], reading each destination's pieces in place."""
+        n, W, c = x.shape
+        cb = c * x.element_size()
+        if not self._a2a_fits(x, cb):
+            return super().a2a_ranks_to_rows(x)
+        buf = self._a2a_exchange(x, n, cb, cb, W * cb, n * cb, cb)
+        return buf[: x.numel() * x.element_size()].view(x.dtype).view(W * n, c)
 
     # ------------------------------------------------------------------ expert parallel
     def moe_sp(self, h_local: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,

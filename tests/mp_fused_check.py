@@ -63,6 +63,13 @@ def main():
     comm = FusedComm(dev)
     comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok, max_tokens=T,
                    a2a_bytes=T * 16 * cfg.kv_cache_dim * 2)
+    # ---- chunked exchanges over peer memory against the NCCL form of the same exchange (3 rows per rank)
+    xa = (torch.randn(world * 3, 192, device=dev) + rank).to(torch.bfloat16)
+    got_a = comm.a2a_rows_to_ranks(xa).clone()
+    want_a = NcclComm.a2a_rows_to_ranks(comm, xa)
+    got_b = comm.a2a_ranks_to_rows(got_a).clone()
+    want_b = NcclComm.a2a_ranks_to_rows(comm, want_a)
+    a2a_ok = bool(torch.equal(got_a, want_a) and torch.equal(got_b, want_b) and got_a.shape == (3, world, 192))
     layout_sp = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=True)
     sp_model = build_model(cfg, dev, "bf16", seed=0, layout=layout_sp, comm=comm)
     outs = []
@@ -106,7 +113,7 @@ def main():
         dec_rel = max(rel(d_nccl, d_full), rel(d_sp, d_full[rank:rank + 1]))
 
     res = {"rel_fused_vs_full": rel(got, want_loc), "rel_nccl_vs_full": rel(got_nccl, want_loc),
-           "repeatable": bool(torch.equal(outs[0], outs[-1])),
+           "repeatable": bool(torch.equal(outs[0], outs[-1]) and a2a_ok),
            "argmax_agree": float((got.argmax(-1) == want_loc.argmax(-1)).float().mean()),
            "nvlink_bytes": comm.nvlink_bytes, "decode_request_parallel_rel": dec_rel}
     t = torch.tensor([res["rel_fused_vs_full"], res["rel_nccl_vs_full"], float(res["repeatable"]),
