@@ -51,7 +51,7 @@ __device__ __forceinline__ float sigmoid(float x) { return 1.f / (1.f + __expf(-
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
 template <int D>
-__global__ void __launch_bounds__(2 * D) kda_seq_kernel(const Params p) {
+__global__ void __launch_bounds__(2 * D, 2) kda_seq_kernel(const Params p) {
   constexpr int R = D / 2;                 // state rows per thread: two threads share a value column
   constexpr int kWarpsHalf = D / 32;
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
