@@ -455,6 +455,9 @@ class Transformer:
         the step (T divisible by the world size); returns fp32 logits of this rank's own rows
         [T / world, vocab] (rows rank*Tl .. (rank+1)*Tl)."""
         cfg, comm, tm = self.cfg, self.comm, self.timer
+        if cfg.has_kda or not cfg.is_mla:
+            raise NotImplementedError("the fused sequence-parallel path covers MLA layers; models with KDA or GQA "
+                                      "layers run tensor-parallel through forward() and the collective baseline")
         W, r = comm.world, comm.rank
         T = ids.shape[0]
         assert T % W == 0, "pad the step to a multiple of the world size"

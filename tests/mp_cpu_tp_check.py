@@ -60,7 +60,33 @@ def main():
     ok_layout = all(bool(torch.equal(y[:, s], torch.arange(world * 2 * 3, dtype=torch.float32).view(world, 2, 3)[rank] + 100 * s))
                     for s in range(world))
     z = comm.a2a_ranks_to_rows(y)
-    err = torch.tensor([float((got_p - want_p).abs().max()), float((got_d_heads - want_d).abs().max()),
+    # a model with KDA layers: heads of the linear-attention layers are sharded like the MLA heads, the recurrent
+    # state of a rank covers its own heads only
+    kcfg = get_model_config("tiny-kimi-linear")
+    klens = [6, 9]
+    kids = torch.randint(2, kcfg.vocab_size, (sum(klens),), generator=g, dtype=torch.int32)
+
+    def run_kda(model, heads):
+        kv = PagedKVCache(kcfg, 16, ps, "cpu", torch.float32, state_slots=4, state_heads=heads)
+        pages = [kv.alloc.alloc(1) for _ in klens]
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in klens])
+        slots = torch.tensor(sum((slots_for_range(p, 0, n, ps) for p, n in zip(pages, klens)), []))
+        bt = build_block_table(pages, "cpu")
+        st = torch.tensor([2, 0], dtype=torch.int32)
+        pre = AttnMeta(mode="prefill", positions=pos, slot_mapping=slots, block_table=bt, cu_seqlens=[0, 6, 15],
+                       ctx_lens=[0, 0], state_slots=st, state_has_initial=torch.zeros(2, dtype=torch.int32))
+        a = model.forward(kids, pre, kv)
+        dslots = torch.tensor([slots_for_range(p, n, n + 1, ps)[0] for p, n in zip(pages, klens)])
+        dec = AttnMeta(mode="decode", positions=torch.tensor(klens, dtype=torch.int32), slot_mapping=dslots,
+                       block_table=bt, seqlens=torch.tensor([n + 1 for n in klens], dtype=torch.int32), state_slots=st)
+        return a, model.forward(torch.tensor([5, 6], dtype=torch.int32), dec, kv)
+
+    kfull = build_model(kcfg, "cpu", torch.float32, seed=1)
+    ktp = build_model(kcfg, "cpu", torch.float32, seed=1, layout=layout, comm=comm)
+    kp, kd = run_kda(kfull, kcfg.kda_num_heads)
+    tp_p, tp_d = run_kda(ktp, kcfg.kda_num_heads // world)
+    kda_err = max(float((tp_p - kp).abs().max()), float((tp_d - kd).abs().max()))
+    err = torch.tensor([max(float((got_p - want_p).abs().max()), kda_err), float((got_d_heads - want_d).abs().max()),
                         float((got_d_req - want_d).abs().max()), 0.0 if (ok_layout and torch.equal(z, x)) else 1.0])
     dist.all_reduce(err, op=dist.ReduceOp.MAX)
     if rank == 0:
