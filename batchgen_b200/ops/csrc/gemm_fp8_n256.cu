@@ -43,6 +43,16 @@ struct Params {
   uint32_t epoch;
   const uint32_t* epoch_base;
   int world;
+  // row return (EPI_STORE only): row r of D is stored at row row_map[r].y of rank row_map[r].x's buffer instead
+  // (x < 0: dropped).  Each thread writes its 128-byte run with 16-byte stores, which suits decode-sized steps
+  // (a few MB per launch); the 128 x 128 kernel stages rows through shared memory for the large ones.  When the
+  // last CTA is done, flag done_index + my_rank of every rank is set to done_epoch (+ *epoch_base).
+  void* peer_out[8];
+  const int2* row_map;
+  uint32_t* peer_flags[8];
+  int done_index, my_rank;
+  uint32_t done_epoch;
+  unsigned int* done_counter;
 };
 
 struct Shared {
@@ -282,6 +292,11 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         } else {
           const int col0 = gslice * 64;
           __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+          if (p.row_map != nullptr) {
+            const int2 rm = p.row_map[row];
+            if (rm.x < 0 || rm.x >= p.world) continue;
+            dst = reinterpret_cast<__nv_bfloat16*>(p.peer_out[rm.x]) + (size_t)rm.y * p.ldd + col0;
+          }
 #pragma unroll
           for (int j = 0; j < 64; j += 8) {
             if (col0 + j + 8 <= p.N) {
@@ -298,11 +313,23 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       }
     }
   }
+  if (p.done_counter != nullptr) __threadfence_system();   // this thread's peer stores, before the CTA reports
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
+  if (threadIdx.x == 0 && p.done_counter != nullptr) {
+    // the last CTA to get here tells every rank that this rank's rows have all been stored
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(p.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_counter = 0u;
+      __threadfence_system();
+      const uint32_t e = p.done_epoch + (p.epoch_base != nullptr ? *p.epoch_base : 0u);
+      for (int r = 0; r < p.world; ++r) st_relaxed_sys(p.peer_flags[r] + p.done_index + p.my_rank, e);
+    }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -359,20 +386,53 @@ extern "C" {
 
 // Same arguments as bg_gemm for kind 0 (e4m3 block scaled); a_ready / epoch / epoch_base / world describe an A
 // operand pushed by peers (null: local), counts the real rows of each grouped segment (null: padded).
+static int gemm_fp8_n256_impl(int epi, const void* A, const float* sA, int sa_stride, const void* B, const float* sB,
+                              void* D, int ldd, const int* offsets, const int* counts, int groups, int M, int N, int K,
+                              int num_sms, bg::g256::Params p, cudaStream_t stream) {
+  using namespace bg::g256;
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 128 != 0 || groups > kMaxGroups || (epi == EPI_SILU_MUL && (N % 256) != 0) || (ldd % 8) != 0) return -1;
+  if (p.row_map != nullptr && (epi != EPI_STORE || (N % 8) != 0)) return -1;
+  if (offsets == nullptr) groups = 1;
+  p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.offsets = offsets; p.counts = offsets != nullptr ? counts : nullptr; p.groups = groups; p.M = M; p.N = N; p.K = K;
+  if (epi == EPI_SILU_MUL) return launch<EPI_SILU_MUL>(A, B, p, groups * N, num_sms, stream);
+  return launch<EPI_STORE>(A, B, p, groups * N, num_sms, stream);
+}
+
+static bg::g256::Params plain_params(const uint32_t* a_ready, uint32_t epoch, const uint32_t* epoch_base, int world,
+                                     int* status) {
+  bg::g256::Params p;
+  p.status = status; p.a_ready = a_ready; p.epoch = epoch; p.epoch_base = epoch_base; p.world = world;
+  p.row_map = nullptr; p.done_counter = nullptr; p.done_index = 0; p.my_rank = 0; p.done_epoch = 0;
+  for (int i = 0; i < 8; ++i) { p.peer_out[i] = nullptr; p.peer_flags[i] = nullptr; }
+  return p;
+}
+
 int bg_gemm_fp8_n256(int epi, const void* A, const float* sA, int sa_stride, const void* B, const float* sB, void* D,
                      int ldd, const int* offsets, const int* counts, int groups, int M, int N, int K, int num_sms,
                      const uint32_t* a_ready, uint32_t epoch, const uint32_t* epoch_base, int world, int* status,
                      cudaStream_t stream) {
-  using namespace bg::g256;
-  if (M <= 0 || N <= 0) return 0;
-  if (K % 128 != 0 || groups > kMaxGroups || (epi == EPI_SILU_MUL && (N % 256) != 0) || (ldd % 8) != 0) return -1;
-  if (offsets == nullptr) groups = 1;
-  Params p;
-  p.sA = sA; p.sa_stride = sa_stride; p.sB = sB; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
-  p.offsets = offsets; p.counts = offsets != nullptr ? counts : nullptr; p.groups = groups; p.M = M; p.N = N; p.K = K;
-  p.status = status; p.a_ready = a_ready; p.epoch = epoch; p.epoch_base = epoch_base; p.world = world;
-  if (epi == EPI_SILU_MUL) return launch<EPI_SILU_MUL>(A, B, p, groups * N, num_sms, stream);
-  return launch<EPI_STORE>(A, B, p, groups * N, num_sms, stream);
+  return gemm_fp8_n256_impl(epi, A, sA, sa_stride, B, sB, D, ldd, offsets, counts, groups, M, N, K, num_sms,
+                            plain_params(a_ready, epoch, epoch_base, world, status), stream);
+}
+
+// Grouped GEMM whose output rows return to other ranks: row r goes to peer_out[row_map[r].x] at row row_map[r].y
+// (row stride ldd elements); afterwards every rank's flag done_index + my_rank is raised to done_epoch.
+int bg_gemm_fp8_n256_return(const void* A, const float* sA, int sa_stride, const void* B, const float* sB, int ldd,
+                            const int* offsets, const int* counts, int groups, int M, int N, int K, int num_sms,
+                            void* const* peer_out, const void* row_map, uint32_t* const* peer_flags, int done_index,
+                            uint32_t done_epoch, const uint32_t* epoch_base, unsigned int* done_counter, int my_rank,
+                            int world, int* status, cudaStream_t stream) {
+  if (world < 1 || world > 8 || peer_out == nullptr || row_map == nullptr || peer_flags == nullptr ||
+      done_counter == nullptr || offsets == nullptr)
+    return -1;
+  bg::g256::Params p = plain_params(nullptr, 0, epoch_base, world, status);
+  for (int i = 0; i < world; ++i) { p.peer_out[i] = peer_out[i]; p.peer_flags[i] = peer_flags[i]; }
+  p.row_map = reinterpret_cast<const int2*>(row_map);
+  p.done_index = done_index; p.done_epoch = done_epoch; p.done_counter = done_counter; p.my_rank = my_rank;
+  return gemm_fp8_n256_impl(bg::g256::EPI_STORE, A, sA, sa_stride, B, sB, peer_out[my_rank], ldd, offsets, counts, groups,
+                            M, N, K, num_sms, p, stream);
 }
 
 }  // extern "C"

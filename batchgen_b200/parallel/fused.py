@@ -39,6 +39,9 @@ FP8 = torch.float8_e4m3fn
 AG_READY, RS_READY, CNT_READY, DISP_READY, RET_READY, A2A_READY = 0, 8, 16, 24, 32, 40
 # rows this rank sends per step from which the gate/up grouped GEMM of the expert-parallel path runs on 128 x 256 tiles
 WIDE_S1_MIN_ROWS = int(os.environ.get("BG_WIDE_S1_MIN_ROWS", "0"))
+# rows this rank sends per step up to which the down-projection returns rows from the 128 x 256 kernel (per-thread
+# 16-byte peer stores); larger steps keep the 128 x 128 kernel whose epilogue stages 128-byte runs through shared memory
+WIDE_S3_MAX_ROWS = int(os.environ.get("BG_WIDE_S3_MAX_ROWS", "4096"))
 ALIGN = 128
 
 
@@ -335,11 +338,24 @@ class FusedComm(NcclComm):
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
         with timer.timed("moe.s3_gemm_return"):
             e_ret = self._next(RET_READY)
-            self._set_hooks(peer_out=self.heap.peer_ptrs("ret"), row_map=self.recv_info, epoch=e_ret,
-                            done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
-            out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
-            gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets,
-                                      out=_StrideCarrier(out_stub, self.recv_cap), counts=self.recv_counts)
+            El, Hout, I = ew.w2.shape
+            if gemm_ops.wide_enabled() and Tl * K <= WIDE_S3_MAX_ROWS and Hout % 8 == 0 and I % 128 == 0:
+                # decode-sized steps: 128 x 256 tiles stream the weights faster; rows leave with plain 16-byte stores
+                sc, sc_stride = gemm_ops._scales_kb_major(as_)
+                rc = L.bg_gemm_fp8_n256_return(
+                    _ext.ptr(aq), _ext.ptr(sc), ctypes.c_int(sc_stride), _ext.ptr(ew.w2), _ext.ptr(ew.w2_s),
+                    ctypes.c_int(Hout), _ext.ptr(self.offsets), _ext.ptr(self.recv_counts), ctypes.c_int(El),
+                    ctypes.c_int(self.recv_cap), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
+                    self.heap.peer_ptrs("ret"), _ext.ptr(self.recv_info), self.flag_ptrs, ctypes.c_int(RET_READY),
+                    ctypes.c_uint32(e_ret), self._base(), _ext.ptr(self.counters[3:4]), ctypes.c_int(self.rank),
+                    ctypes.c_int(W), self._status(), st)
+                _ext.check(rc, "bg_gemm_fp8_n256_return")
+            else:
+                self._set_hooks(peer_out=self.heap.peer_ptrs("ret"), row_map=self.recv_info, epoch=e_ret,
+                                done_index=RET_READY, done_counter=self.counters[3:4], peer_flags=self.flag_ptrs)
+                out_stub = self.rs_buf.view(-1)[: ew.w2.shape[1]].view(1, -1)   # row stride carrier only
+                gemm_ops.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, self.offsets,
+                                          out=_StrideCarrier(out_stub, self.recv_cap), counts=self.recv_counts)
         self.nvlink_bytes += Tl * K * H * 2 * (W - 1) // W
         with timer.timed("moe.return_wait_combine"):
             rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),
