@@ -364,6 +364,7 @@ class EngineConfig:
     max_prefill_tokens: int = 131072            # packed micro-batch token cap
     max_decode_batch: int = 512                 # rows per rank in decode
     max_state_slots: int = 0                    # sequences holding recurrent (KDA) state at once; 0 = max_decode_batch
+    max_host_state_items: int = 0               # parked recurrent states in host memory; 0 = 4 x the device slots
     max_model_len: int = -1
     enable_cuda_graph: bool = True
     cuda_graph_max_bucket_size: int = 128

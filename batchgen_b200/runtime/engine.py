@@ -25,7 +25,7 @@ from ..config import EngineConfig, ModelConfig
 from ..models.transformer import AttnMeta, Transformer
 from ..ops import sampling as sampling_ops
 from . import scheduler as sched
-from .kv_cache import PagedKVCache, build_block_table, slots_for_range
+from .kv_cache import HostStateStore, PagedKVCache, build_block_table, slots_for_range
 from .prefix_cache import PrefixCache
 from .sequence import (PageBufferConfig, SamplingParams, Sequence, SequenceStatus, gpu_pages_first_load,
                        pages_for)
@@ -78,6 +78,9 @@ class Engine:
                                state_heads=state_heads)
         self.host_kv = (PagedKVCache(self.cfg, num_host_pages, ecfg.page_size, "cpu", kv_dtype, pinned=True)
                         if num_host_pages else None)
+        self.host_state = None
+        if self.kv.state is not None and self.host_kv is not None:
+            self.host_state = HostStateStore(self.kv.state, ecfg.max_host_state_items or 4 * state_slots)
         self.prefix = PrefixCache(self.kv.alloc, ecfg.page_size) if ecfg.enable_prefix_cache else None
         self.kv_token_budget = (ecfg.max_model_len if ecfg.max_model_len > 0 else n_pages * ecfg.page_size)
         self.seqs: Dict[int, Sequence] = {}
@@ -126,6 +129,9 @@ class Engine:
         if s.state_slot >= 0:
             self.kv.state.release(s.state_slot)
             s.state_slot = -1
+        if s.state_item >= 0:
+            self.host_state.release(s.state_item)
+            s.state_item = -1
 
     def _complete(self, s: Sequence, reason: str) -> None:
         s.finish_reason = reason
@@ -246,6 +252,8 @@ class Engine:
     def _enter_decode(self, s: Sequence) -> bool:
         """Make sure the row's KV and growth buffer are on the GPU; returns False if it does not fit."""
         want = gpu_pages_first_load(s.context_len, self.buf, self.kv_token_budget)
+        if s.state_item >= 0 and self.kv.state.num_free == 0:
+            return False                              # no slot for the parked state yet
         if s.host_pages and not s.gpu_pages:          # parked in the host tier: load back
             need = max(want, len(s.host_pages))
             if need > self._free_pages():
@@ -254,6 +262,11 @@ class Engine:
                 return False
             s.gpu_pages = self.kv.alloc.alloc(need)
             self.kv.copy_pages_from(self.host_kv, s.host_pages, s.gpu_pages[: len(s.host_pages)], self.copy_stream)
+            if s.state_item >= 0:
+                s.state_slot = self.kv.state.acquire()
+                self.host_state.load(self.kv.state, s.state_item, s.state_slot, self.copy_stream)
+                self.host_state.release(s.state_item)
+                s.state_item = -1
             if self.copy_stream is not None:
                 torch.cuda.current_stream().wait_stream(self.copy_stream)
             self.host_kv.alloc.free(s.host_pages)
@@ -276,8 +289,15 @@ class Engine:
         if self.host_kv is not None and self.host_kv.alloc.num_free >= used:
             s.host_pages = self.host_kv.alloc.alloc(used)
             self.host_kv.copy_pages_from(self.kv, s.gpu_pages[:used], s.host_pages, self.copy_stream)
+            if self.host_state is not None and s.state_slot >= 0 and self.host_state.num_free:
+                if self.copy_stream is not None:
+                    self.copy_stream.wait_stream(torch.cuda.current_stream())
+                s.state_item = self.host_state.offload(self.kv.state, s.state_slot, self.copy_stream)
             if self.copy_stream is not None:
                 self.copy_stream.synchronize()
+            if s.state_item >= 0:                      # the slot goes to whoever is scheduled next
+                self.kv.state.release(s.state_slot)
+                s.state_slot = -1
             self.kv.alloc.free(s.gpu_pages)
             s.gpu_pages = []
             self.stats.offloaded_pages += used

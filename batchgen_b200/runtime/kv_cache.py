@@ -172,6 +172,51 @@ class StateSlotPool:
         return self.conv[i], self.rec[i]
 
 
+class HostStateStore:
+    """Host-memory store of recurrent (KDA) state items: a sequence that leaves the decode batch parks its state
+    here (pinned memory, copies on the engine's copy stream) and gives its device slot to another sequence; the
+    state returns to any free slot when the sequence is scheduled again.
+
+    Reference parity: the compressed-state host manager with asynchronous offload / load of state items
+    (core/KV_Storage/compressed_state_host_manager.h)."""
+
+    def __init__(self, pool: StateSlotPool, num_items: int, pinned: bool = True):
+        pin = pinned and torch.cuda.is_available()
+        self.rec = torch.zeros(pool.rec.shape[0], num_items, *pool.rec.shape[2:], dtype=pool.rec.dtype, pin_memory=pin)
+        self.conv = torch.zeros(pool.conv.shape[0], num_items, *pool.conv.shape[2:], dtype=pool.conv.dtype, pin_memory=pin)
+        self.num_items = num_items
+        self._free = list(range(num_items - 1, -1, -1))
+        self.offloads = self.loads = 0
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def offload(self, pool: StateSlotPool, slot: int, stream=None) -> int:
+        """Copy the state of ``slot`` (all KDA layers) to a free item; returns the item.  The caller releases the
+        slot once the copy stream has been synchronised or ordered before the slot's next writer."""
+        if not self._free:
+            raise OutOfPages("no free host state item")
+        item = self._free.pop()
+        ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
+        with ctx:
+            self.rec[:, item].copy_(pool.rec[:, slot], non_blocking=True)
+            self.conv[:, item].copy_(pool.conv[:, slot], non_blocking=True)
+        self.offloads += 1
+        return item
+
+    def load(self, pool: StateSlotPool, item: int, slot: int, stream=None) -> None:
+        ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
+        with ctx:
+            pool.rec[:, slot].copy_(self.rec[:, item], non_blocking=True)
+            pool.conv[:, slot].copy_(self.conv[:, item], non_blocking=True)
+        self.loads += 1
+
+    def release(self, item: int) -> None:
+        assert 0 <= item < self.num_items and item not in self._free
+        self._free.append(item)
+
+
 class _NullCtx:
     def __enter__(self):
         return self

@@ -99,6 +99,7 @@ class Sequence:
     gpu_pages: List[int] = field(default_factory=list)      # physical GPU pages in order
     host_pages: List[int] = field(default_factory=list)     # physical host pages in order
     state_slot: int = -1                                    # recurrent-state slot (models with KDA layers)
+    state_item: int = -1                                    # host item holding the state while the row is on hold
     num_cached_tokens: int = 0                              # tokens whose KV exists (either tier)
     cached_prefix_tokens: int = 0                           # tokens served by the prefix cache
     had_initial_gpu_reservation: bool = False

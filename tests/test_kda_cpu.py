@@ -77,3 +77,22 @@ def test_engine_with_kda_layers_matches_naive_oracle():
         assert o == oracle.generate(pr, 4)
     assert eng.kv.state.num_free == 2                    # three sequences shared two slots and returned them
     assert eng.kv.kv.shape[0] == 1                       # only the MLA layer owns paged KV
+
+
+def test_parked_sequences_move_their_state_to_host_and_back():
+    """Few GPU pages and a host tier: rows are put on hold and resumed; the recurrent state of a held row travels
+    to the host store and returns to whatever slot is free, and the tokens equal an unconstrained run."""
+    cfg = get_model_config("tiny-kimi-linear")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(2, cfg.vocab_size, (32,), generator=g).tolist() for _ in range(5)]
+    params = SamplingParams(max_new_tokens=40, temperature=0.0, ignore_eos=True)
+    big = Engine(build_model(cfg, device="cpu", dtype=torch.float32, seed=0),
+                 EngineConfig(page_size=16, max_decode_batch=8, enable_cuda_graph=False), num_gpu_pages=256)
+    want = big.generate(prompts, params)
+    ecfg = EngineConfig(page_size=16, initial_gpu_page_buffer=2, extension_gpu_page_buffer=1, decision_frequency_pages=1,
+                        max_decode_batch=8, max_state_slots=5, enable_cuda_graph=False)
+    eng = Engine(build_model(cfg, device="cpu", dtype=torch.float32, seed=0), ecfg, num_gpu_pages=18, num_host_pages=64)
+    assert eng.host_state is not None
+    assert eng.generate(prompts, params) == want
+    assert eng.stats.holds > 0 and eng.host_state.offloads > 0 and eng.host_state.loads == eng.host_state.offloads
+    assert eng.kv.state.num_free == 5 and eng.host_state.num_free == eng.host_state.num_items
