@@ -289,16 +289,16 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
                 equant = "fp8_block" if quant == "fp8_block" else "none"
                 if cfg.quant in ("mxfp4", "int4") and eh % 64 == 0 and I % 64 == 0:
                     if cfg.quant == "mxfp4":
-                        from ..ops import mxfp4
+                        from ..ops.mxfp4 import quantize as quantize_w4
                     else:
-                        from ..ops import int4 as mxfp4     # same interface: quantize(w) -> (packed, scales)
+                        from ..ops.int4 import quantize as quantize_w4
                     for e in range(e0, e1):
                         ep = f"{p}.mlp.experts.{e}"
                         g = src.get(f"{ep}.gate_proj.weight", (I, eh))
                         u = src.get(f"{ep}.up_proj.weight", (I, eh))
                         d = src.get(f"{ep}.down_proj.weight", (eh, I))
-                        q13, sc13 = mxfp4.quantize(torch.cat([g, u], 0))
-                        q2, sc2 = mxfp4.quantize(d)
+                        q13, sc13 = quantize_w4(torch.cat([g, u], 0))
+                        q2, sc2 = quantize_w4(d)
                         w13s.append(q13); s13.append(sc13); w2s.append(q2); s2.append(sc2)
                     lw.experts = ExpertWeights(w13=torch.stack(w13s), w2=torch.stack(w2s), w13_s=torch.stack(s13),
                                                w2_s=torch.stack(s2), quant=cfg.quant,

@@ -196,23 +196,21 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         aq, as_ = ref.act_quant(act)
         return ref.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
     if ew.quant in ("mxfp4", "int4"):
+        # W4A16, groups of 32: one tcgen05 kernel, two expansions (e2m1 x e8m0 scale, or offset-binary int4 x bf16 scale)
         if ew.quant == "mxfp4":
-            from . import mxfp4
-        else:                                  # INT4 W4A16, group 32: same kernel, other expansion
-            from . import int4 as _i4
-
-            class mxfp4:                       # noqa: N801 - same call shape as the mxfp4 module
-                grouped_mxfp4_gemm = staticmethod(_i4.grouped_int4_gemm)
+            from .mxfp4 import grouped_mxfp4_gemm as grouped_w4
+        else:
+            from .int4 import grouped_int4_gemm as grouped_w4
         x = x_dense
         if x.is_cuda and ew.interleaved:
             with timer.timed("moe.s1_gemm"):
-                act = mxfp4.grouped_mxfp4_gemm(x, ew.w13, ew.w13_s, offsets, silu_mul=True)
+                act = grouped_w4(x, ew.w13, ew.w13_s, offsets, silu_mul=True)
         else:
             with timer.timed("moe.s1_gemm"):
-                gu = mxfp4.grouped_mxfp4_gemm(x, ew.w13, ew.w13_s, offsets)
+                gu = grouped_w4(x, ew.w13, ew.w13_s, offsets)
             act = _activation(gu, ew.activation).to(x.dtype)
         with timer.timed("moe.s3_gemm"):
-            return mxfp4.grouped_mxfp4_gemm(act, ew.w2, ew.w2_s, offsets)
+            return grouped_w4(act, ew.w2, ew.w2_s, offsets)
     # unquantised experts (CPU fp32 oracle path and bf16 debugging)
     x = x_dense
     out = torch.zeros(x.shape[0], ew.w2.shape[1], dtype=x.dtype, device=x.device)
