@@ -37,7 +37,7 @@ def die_with_parent() -> None:
 
 def setup_nccl_env() -> None:
     """NCCL settings for a single NVSwitch node.  NVLS stays at NCCL's default here (the reference turns it
-    off because multicast registration made graph capture slow, server_worker_main_loop.py:553-571)."""
+    off because registering buffers with the switch made graph capture slow, server_worker_main_loop.py:553-571)."""
     os.environ.setdefault("TORCH_NCCL_ENABLE_MONITORING", "0")
     os.environ.setdefault("NCCL_SOCKET_IFNAME", "lo")
     if os.environ.get("BATCHGEN_DETERMINISTIC") == "1":
