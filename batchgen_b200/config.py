@@ -375,6 +375,7 @@ class EngineConfig:
     world_size: int = 1
     attn_tp_size: int = 1                       # TP degree of attention (1 = DP attention)
     ep_size: int = 1                            # expert parallel degree
+    decode_attn_split: str = "heads"            # heads | requests: how a TP group divides the decode attention core
     moe_comm: str = "fused"                     # fused | nccl  (nccl = all_gather/reduce_scatter baseline)
     tp_comm: str = "fused"                      # fused | nccl
     expert_offload_ratio: float = 0.0           # fraction of local experts kept in host DRAM
@@ -392,6 +393,8 @@ class EngineConfig:
             raise ValueError("ep_size must be 1 or world_size")
         if not 0.0 <= self.expert_offload_ratio <= 1.0:
             raise ValueError("expert_offload_ratio must be in [0, 1]")
+        if self.decode_attn_split not in ("heads", "requests"):
+            raise ValueError("decode_attn_split must be 'heads' or 'requests'")
         if self.kv_dtype not in ("bf16", "fp8", "fp32"):
             raise ValueError(f"unsupported kv dtype {self.kv_dtype}")
 

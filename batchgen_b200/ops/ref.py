@@ -261,6 +261,8 @@ def moe_combine(expert_out: torch.Tensor, pos: torch.Tensor, weights: torch.Tens
     T, K = pos.shape
     H = expert_out.shape[-1]
     acc = torch.zeros(T, H, dtype=torch.float32, device=expert_out.device)
+    if expert_out.shape[0] == 0:            # none of this rank's experts was chosen in this step
+        return acc.to(out_dtype or expert_out.dtype)
     for k in range(K):
         p = pos[:, k]
         valid = p >= 0

@@ -316,30 +316,60 @@ class Engine:
         s.output_ids = list(s.output_ids)     # decoded tokens are kept and replayed through prefill
         self.stats.evictions += 1
 
+    def _owner_layout(self, rows: List[Sequence]) -> List[Optional[Sequence]]:
+        """Request-split decode attention: arrange the step's rows in one block per TP rank (a row always in
+        the block of its owner, the rank whose KV copy its decode steps extend) and pad every block to the same
+        length with empty rows (``None``).  A new row goes to the rank that owns the fewest live rows; every
+        rank runs this same code on the same inputs, so all agree without talking."""
+        W = self.model.layout.tp_size
+        load = [0] * W
+        for s in self.seqs.values():
+            if s.decode_owner >= 0 and s.status in (S.PREFILLED, S.IN_DECODE, S.ON_HOLD):
+                load[s.decode_owner] += 1
+        blocks: List[List[Sequence]] = [[] for _ in range(W)]
+        for s in rows:
+            if s.decode_owner < 0:
+                s.decode_owner = min(range(W), key=lambda r: (load[r], r))
+                load[s.decode_owner] += 1
+            blocks[s.decode_owner].append(s)
+        per = max(len(b) for b in blocks)
+        if self.graph_runner is not None:                # the whole step must be one of the captured sizes
+            per = -(-self.graph_runner.bucketing.bucket_for(W * per) // W)
+        layout: List[Optional[Sequence]] = []
+        for b in blocks:
+            layout += b + [None] * (per - len(b))
+        return layout
+
     def _decode_step(self, rows: List[Sequence]) -> None:
         ps = self.buf.page_size
         dev = self.device
-        ids = [s.all_ids[s.num_cached_tokens] for s in rows]
-        pos = [s.num_cached_tokens for s in rows]
-        slots = [s.gpu_pages[p // ps] * ps + p % ps for s, p in zip(rows, pos)]
-        lens = [p + 1 for p in pos]
+        split = self.model.attn_request_parallel and self.model.layout.tp_size > 1
+        layout: List[Optional[Sequence]] = self._owner_layout(rows) if split else list(rows)
+        real = [i for i, s in enumerate(layout) if s is not None]
+        ids = [s.all_ids[s.num_cached_tokens] if s is not None else 0 for s in layout]
+        pos = [s.num_cached_tokens if s is not None else 0 for s in layout]
+        slots = [s.gpu_pages[p // ps] * ps + p % ps if s is not None else -1 for s, p in zip(layout, pos)]
+        lens = [p + 1 if s is not None else 0 for s, p in zip(layout, pos)]
         if self.graph_runner is not None:
-            logits = self.graph_runner.decode(self, rows, ids, pos, slots, lens)
+            logits = self.graph_runner.decode(self, layout, ids, pos, slots, lens)
         else:
             meta = AttnMeta(
                 mode="decode",
                 positions=torch.tensor(pos, dtype=torch.int32, device=dev),
                 slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
-                block_table=build_block_table([s.gpu_pages for s in rows], dev),
+                block_table=build_block_table([s.gpu_pages if s is not None else [] for s in layout], dev),
                 seqlens=torch.tensor(lens, dtype=torch.int32, device=dev),
-                state_slots=(torch.tensor([s.state_slot for s in rows], dtype=torch.int32, device=dev)
-                             if self.kv.state is not None else None))
+                state_slots=(torch.tensor([s.state_slot if s is not None else -1 for s in layout], dtype=torch.int32,
+                                          device=dev) if self.kv.state is not None else None))
             logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
-        toks = self._sample(logits, rows).tolist()
-        for s, t in zip(rows, toks):
+        if len(real) != len(layout):
+            logits = logits[torch.tensor(real, dtype=torch.long, device=logits.device)]
+        live = [layout[i] for i in real]
+        toks = self._sample(logits, live).tolist()
+        for s, t in zip(live, toks):
             s.num_cached_tokens += 1
             s.output_ids.append(int(t))
-        self.stats.decode_tokens += len(rows)
+        self.stats.decode_tokens += len(live)
         self.stats.decode_steps += 1
 
     def _decode_interval(self) -> int:

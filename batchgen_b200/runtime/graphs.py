@@ -239,9 +239,10 @@ class DecodeGraphRunner:
         return self._ring[handle][: self._ring_n[handle]]
 
     def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
-        """Engine hook (``Engine.graph_runner``): logits of the live rows."""
-        b = self.stage(ids, pos, slots, lens, [s.gpu_pages for s in rows],
-                       [s.state_slot for s in rows] if self.state_slots is not None else None)
+        """Engine hook (``Engine.graph_runner``): logits of the step's rows (``None`` entries are empty rows that
+        pad a rank's block in request-split decode; their logits are returned too and ignored by the engine)."""
+        b = self.stage(ids, pos, slots, lens, [s.gpu_pages if s is not None else [] for s in rows],
+                       [s.state_slot if s is not None else -1 for s in rows] if self.state_slots is not None else None)
         key = tuple(id(s) for s in rows)
         if key != self._row_key and self.model.cfg.is_mla and torch.device(self.dev).type == "cuda":
             # batch membership changed: put the longest sequences first in the attention work lists

@@ -69,6 +69,8 @@ def build_engine(args, rank: int, world: int, device: str):
         layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
     model = build_model(cfg, device=device, dtype=dtype, seed=args.seed, layout=layout, comm=comm, loader=loader,
                         max_positions=max(8192, args.max_model_len if args.max_model_len > 0 else 8192))
+    if world > 1 and ecfg.decode_attn_split == "requests" and cfg.is_mla and not cfg.has_dsa:
+        model.attn_request_parallel = True       # the engine pins every sequence to an owner rank (Engine._owner_layout)
     pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
     eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages)
     if device.startswith("cuda") and ecfg.enable_cuda_graph:

@@ -38,3 +38,9 @@ def test_parked_row_migrates_to_another_rank_and_finishes_there():
 def test_migration_carries_recurrent_state():
     res = _run_child("mp_migration_check.py", 29645, {"BG_MIG_MODEL": "tiny-kimi-linear"})
     assert res["plan"] and res["on_rank1"] and res["tokens_equal"], res
+
+
+def test_engine_decodes_with_rows_pinned_to_owner_ranks():
+    res = _run_child("mp_engine_split_check.py", 29647)
+    assert res["tokens_equal"], res
+    assert sorted(set(res["owners"])) == [0, 1], res          # both ranks own rows
