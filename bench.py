@@ -134,7 +134,7 @@ def main() -> int:
     build_s = time.time() - t0
 
     kv = PagedKVCache(cfg, total_pages + (args.prefill_tokens // page + 8), page, dev, torch.bfloat16)
-    for l in range(cfg.num_layers):
+    for l in range(kv.kv.shape[0]):                        # one slab per layer that keeps paged KV
         kv.kv[l].normal_(0.0, 0.5)
     # ---- decode step inputs (device resident for the kernel-timed number)
     gen = torch.Generator().manual_seed(7)
