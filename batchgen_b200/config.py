@@ -208,6 +208,13 @@ def tiny_kimi_linear() -> ModelConfig:
                        kda_layers=(0, 1, 2), kda_num_heads=2, kda_head_dim=64, kda_gate_rank=32)
 
 
+def tiny_kimi_k31() -> ModelConfig:
+    """KDA layers plus an MLA layer that carries a DSA indexer (the Kimi-K3.1 arrangement)."""
+    import dataclasses
+    return dataclasses.replace(tiny_kimi_linear(), name="tiny-kimi-k3.1", index_n_heads=4, index_head_dim=32,
+                               index_topk=16, indexer_full_layers=(3,))
+
+
 def tiny_gpt_oss() -> ModelConfig:
     return ModelConfig(name="tiny-gpt-oss", family="gpt_oss", num_layers=2, first_k_dense=0,
                        num_heads=8, num_kv_heads=2, head_dim=32, sliding_window=16,
@@ -258,6 +265,15 @@ def kimi_k3_kda() -> ModelConfig:
                                kda_num_heads=64, kda_head_dim=128)
 
 
+def kimi_k31() -> ModelConfig:
+    """Kimi-K3.1: K3 with KDA layers and a DSA indexer (top-2048, 32 heads of 128) on every MLA layer."""
+    import dataclasses
+    base = kimi_k3_kda()
+    mla = tuple(l for l in range(base.num_layers) if l not in base.kda_layers)
+    return dataclasses.replace(base, name="kimi-k3.1", index_n_heads=32, index_head_dim=128, index_topk=2048,
+                               indexer_full_layers=mla)
+
+
 def kimi_linear_48b() -> ModelConfig:
     return ModelConfig(
         name="kimi-linear-48b", family="kimi_k3", vocab_size=163840, hidden_size=2304, num_layers=27,
@@ -299,6 +315,8 @@ _PRESETS = {
     "tiny-glm5": tiny_glm5,
     "tiny-kimi-k3": tiny_kimi_k3,
     "tiny-kimi-linear": tiny_kimi_linear,
+    "tiny-kimi-k3.1": tiny_kimi_k31,
+    "kimi-k3.1": kimi_k31,
     "kimi-k3-kda": kimi_k3_kda,
     "kimi-linear-48b": kimi_linear_48b,
     "tiny-gpt-oss": tiny_gpt_oss,
@@ -317,6 +335,7 @@ _PATTERNS = [
     (r"deepseek[-_/]?(ai/)?.*(v3|r1)", "deepseek-v3-671b"),
     (r"glm[-_]?5", "glm-5.3-fp8"),
     (r"kimi[-_]?linear", "kimi-linear-48b"),
+    (r"kimi[-_]?k3\.1", "kimi-k3.1"),
     (r"kimi[-_]?k3[-_]?kda", "kimi-k3-kda"),
     (r"kimi[-_]?k3", "kimi-k3"),
     (r"kimi[-_]?k2", "kimi-k2.5"),

@@ -96,3 +96,16 @@ def test_parked_sequences_move_their_state_to_host_and_back():
     assert eng.generate(prompts, params) == want
     assert eng.stats.holds > 0 and eng.host_state.offloads > 0 and eng.host_state.loads == eng.host_state.offloads
     assert eng.kv.state.num_free == 5 and eng.host_state.num_free == eng.host_state.num_items
+
+
+def test_kda_layers_with_a_dsa_indexed_mla_layer_match_naive():
+    cfg = get_model_config("tiny-kimi-k3.1")
+    model = build_model(cfg, device="cpu", dtype=torch.float32, seed=5)
+    eng = Engine(model, EngineConfig(page_size=16, max_decode_batch=4, enable_cuda_graph=False), num_gpu_pages=64)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (30, 21)]   # longer than top-k 16
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True))
+    oracle = NaiveModel(cfg, WeightSource(seed=5))
+    for pr, o in zip(prompts, outs):
+        assert o == oracle.generate(pr, 4)
+    assert get_model_config("kimi-k3.1").has_dsa and len(get_model_config("kimi-k3.1").indexer_full_layers) == 24
