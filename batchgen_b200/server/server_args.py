@@ -58,6 +58,10 @@ class ServerArgs:
     enable_prefix_cache: bool = False
     # comm
     moe_comm: str = "fused"
+    decode_attn_split: str = "heads"            # heads | requests (rows pinned to owner ranks inside the TP group)
+    # recurrent state (models with KDA layers)
+    max_state_slots: int = 0
+    max_host_state_items: int = 0
     # output
     parse_thinking: bool = False
     parse_tool_call: bool = False
@@ -97,7 +101,8 @@ class ServerArgs:
             cuda_graph_num_buckets=self.cuda_graph_num_buckets, enable_prefix_cache=self.enable_prefix_cache,
             adaptive_chunk=self.adaptive_chunk, world_size=self.world_size, attn_tp_size=tp,
             ep_size=self.world_size, moe_comm=self.moe_comm, expert_offload_ratio=self.ep_offloading_ratio,
-            seed=self.seed)
+            decode_attn_split=self.decode_attn_split, max_state_slots=self.max_state_slots,
+            max_host_state_items=self.max_host_state_items, seed=self.seed)
 
 
 def build_parser() -> argparse.ArgumentParser:
