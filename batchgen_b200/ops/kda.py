@@ -63,6 +63,41 @@ def kda_recurrent_ref(q, k, v, g, beta, S, scale: float):
     return out
 
 
+def kda_chunk_ref(q, k, v, g, beta, S, scale: float, chunk: int = 64):
+    """The same recurrence in chunk form (the shape a tensor-core prefill kernel takes): inside a chunk the
+    writes u_i = beta_i (v_i - S_(i-1)'^T k_i) solve a unit lower-triangular system, after which outputs and the
+    state at the chunk end are plain matrix products.  With G the running sum of the log decay inside the chunk,
+
+        M[i, j]  = sum_c k_i[c] k_j[c] exp(G_i[c] - G_j[c])          (j < i)
+        (I + diag(beta) M) U = diag(beta) (V - (K * exp(G)) S_0)
+        O        = (Q * exp(G)) S_0 + tril(Q-to-K decayed products) U
+        S_end    = exp(G_last) * S_0 + sum_j (k_j * exp(G_last - G_j)) u_j^T
+
+    q, k, v, g [n, H, D]; beta [n, H] (after sigmoid); S [H, D, D] updated in place; returns o [n, H, D].  fp32."""
+    n, H, D = q.shape
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * scale
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    out = torch.empty_like(v)
+    for a in range(0, n, chunk):
+        b = min(n, a + chunk)
+        C = b - a
+        qc, kc, vc, bc = (t[a:b].transpose(0, 1) for t in (q, k, v, beta.unsqueeze(-1)))     # [H, C, D] / [H, C, 1]
+        G = g[a:b].transpose(0, 1).cumsum(1)                                               # [H, C, D]
+        # decayed pair products; the exponent is <= 0 wherever it is used (j <= i)
+        diff = (G.unsqueeze(2) - G.unsqueeze(1)).clamp_max(0.0).exp()                       # [H, i, j, D]
+        kk = torch.einsum("hid,hjd,hijd->hij", kc, kc, diff)
+        qk = torch.einsum("hid,hjd,hijd->hij", qc, kc, diff)
+        eye = torch.eye(C, dtype=q.dtype, device=q.device)
+        A = eye + bc * torch.tril(kk, -1)
+        rhs = bc * (vc - torch.einsum("hcd,hdv->hcv", kc * G.exp(), S))
+        U = torch.linalg.solve_triangular(A, rhs, upper=False)
+        out[a:b] = (torch.einsum("hcd,hdv->hcv", qc * G.exp(), S) + torch.tril(qk) @ U).transpose(0, 1)
+        last = G[:, -1:, :]                                                                 # [H, 1, D]
+        S.mul_(last.squeeze(1).exp().unsqueeze(-1))
+        S.add_(torch.einsum("hcd,hcv->hdv", kc * (last - G).exp(), U))
+    return out
+
+
 def _forward_ref(qkv, f, beta, z, p: KDAParams, conv_state, rec_state, slots, cu, has_initial, H, D, scale, eps):
     T = qkv.shape[0]
     HD = H * D
@@ -81,7 +116,8 @@ def _forward_ref(qkv, f, beta, z, p: KDAParams, conv_state, rec_state, slots, cu
         qh, kh, vh = (y[:, s * HD:(s + 1) * HD].view(-1, H, D) for s in range(3))
         g = kda_gate(f[a:b], p.A_log, p.dt_bias, H, D)
         S = rec_state[slot].float()
-        o = kda_recurrent_ref(qh, kh, vh, g, torch.sigmoid(beta[a:b].float()), S, scale)
+        step = kda_chunk_ref if (b - a) > 128 else kda_recurrent_ref           # long prompts: chunk form
+        o = step(qh, kh, vh, g, torch.sigmoid(beta[a:b].float()), S, scale)
         rec_state[slot].copy_(S)
         o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * p.norm_w.float()
         out[a:b] = (o * torch.sigmoid(z[a:b].float().view(-1, H, D))).reshape(-1, HD)

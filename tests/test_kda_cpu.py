@@ -109,3 +109,17 @@ def test_kda_layers_with_a_dsa_indexed_mla_layer_match_naive():
     for pr, o in zip(prompts, outs):
         assert o == oracle.generate(pr, 4)
     assert get_model_config("kimi-k3.1").has_dsa and len(get_model_config("kimi-k3.1").indexer_full_layers) == 24
+
+
+def test_chunk_form_equals_the_recurrence():
+    g0 = torch.Generator().manual_seed(4)
+    n, H, D = 150, 2, 16
+    q, k, v = (torch.randn(n, H, D, generator=g0) for _ in range(3))
+    g = -torch.rand(n, H, D, generator=g0) * 0.3
+    beta = torch.rand(n, H, generator=g0)
+    S0 = torch.randn(H, D, D, generator=g0) * 0.2
+    Sa, Sb = S0.clone(), S0.clone()
+    a = kda.kda_recurrent_ref(q, k, v, g, beta, Sa, 0.25)
+    b = kda.kda_chunk_ref(q, k, v, g, beta, Sb, 0.25, chunk=64)
+    assert torch.allclose(a, b, atol=2e-4, rtol=2e-4)
+    assert torch.allclose(Sa, Sb, atol=2e-4, rtol=2e-4)
