@@ -192,12 +192,16 @@ class HostStateStore:
     def num_free(self) -> int:
         return len(self._free)
 
+    def reserve(self) -> int:
+        """Take a free item without filling it (a migrated row's state is received straight into it)."""
+        if not self._free:
+            raise OutOfPages("no free host state item")
+        return self._free.pop()
+
     def offload(self, pool: StateSlotPool, slot: int, stream=None) -> int:
         """Copy the state of ``slot`` (all KDA layers) to a free item; returns the item.  The caller releases the
         slot once the copy stream has been synchronised or ordered before the slot's next writer."""
-        if not self._free:
-            raise OutOfPages("no free host state item")
-        item = self._free.pop()
+        item = self.reserve()
         ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
         with ctx:
             self.rec[:, item].copy_(pool.rec[:, slot], non_blocking=True)

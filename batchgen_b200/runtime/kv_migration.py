@@ -96,9 +96,9 @@ def recv_sequence(engine, src: int, group=None) -> Sequence:
     s.host_pages = pages
     if d["has_state"]:
         hs = engine.host_state
-        if hs is None or not hs.num_free:
-            raise RuntimeError("the destination has no free host state item")
-        item = hs._free.pop()
+        if hs is None:
+            raise RuntimeError("the destination keeps no host state store")
+        item = hs.reserve()
         rec, conv = torch.empty_like(hs.rec[:, item]), torch.empty_like(hs.conv[:, item])
         dist.recv(rec, src, group=group)
         dist.recv(conv, src, group=group)
