@@ -118,3 +118,34 @@ def test_weight_replica_plan():
     assert [f.frame for f in frames] == sorted(f.frame for f in frames)
     assert wr.derive_frame_plan({"attn": ["attn_2", "attn_1"]}) is None     # out of order
     assert wr.derive_frame_plan({"x": ["weird"]}) is None
+
+
+def test_owner_layout_blocks_pads_and_keeps_owners():
+    """Request-split decode: one block per rank, rows stay with their owner, new rows go to the least loaded rank,
+    and the step length is rounded to a captured graph size."""
+    import types
+
+    from batchgen_b200.runtime.engine import Engine
+    from batchgen_b200.runtime.sequence import S, Sequence
+
+    seqs = {i: Sequence(global_idx=i, prompt_ids=[1, 2, 3]) for i in range(7)}
+    for s in seqs.values():
+        s.status = S.IN_DECODE
+    eng = types.SimpleNamespace(model=types.SimpleNamespace(layout=types.SimpleNamespace(tp_size=4)), seqs=seqs,
+                                graph_runner=None)
+    layout = Engine._owner_layout(eng, list(seqs.values()))
+    assert len(layout) == 8 and [s.decode_owner for s in seqs.values()] == [0, 1, 2, 3, 0, 1, 2]
+    assert [None if s is None else s.global_idx for s in layout] == [0, 4, 1, 5, 2, 6, 3, None]
+    # rows 0 and 4 leave; a new row joins the rank that now owns the fewest; nobody else moves
+    for i in (0, 4):
+        seqs[i].status = S.COMPLETED
+    seqs[7] = Sequence(global_idx=7, prompt_ids=[1])
+    seqs[7].status = S.IN_DECODE
+    live = [s for s in seqs.values() if s.status == S.IN_DECODE]
+    before = {s.global_idx: s.decode_owner for s in live if s.decode_owner >= 0}
+    layout = Engine._owner_layout(eng, live)
+    assert seqs[7].decode_owner == 0 and all(s.decode_owner == o for s in live for g, o in before.items() if s.global_idx == g)
+    assert [None if s is None else s.global_idx for s in layout] == [7, None, 1, 5, 2, 6, 3, None]
+    # with a graph runner the whole step is one of the captured sizes (a multiple of the group size)
+    eng.graph_runner = types.SimpleNamespace(bucketing=types.SimpleNamespace(bucket_for=lambda n: 16))
+    assert len(Engine._owner_layout(eng, live)) == 16
