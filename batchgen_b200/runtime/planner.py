@@ -121,6 +121,12 @@ def plan_deployment(cfg: ModelConfig, ecfg: EngineConfig, machine: MachineProfil
                           fits, note)
 
 
+def state_pool_bytes(cfg: ModelConfig, ecfg: EngineConfig) -> int:
+    """Device bytes of the recurrent-state pool (KDA layers): one slot per sequence that may be live at once."""
+    slots = ecfg.max_state_slots or ecfg.max_decode_batch
+    return slots * cfg.kda_state_bytes_per_seq(max(ecfg.attn_tp_size, 1))
+
+
 def size_kv_pool(cfg: ModelConfig, ecfg: EngineConfig, device: str, dtype) -> Tuple[int, int]:
     """Pages for the device pool and the host tier on the live machine (model already resident)."""
     import torch
@@ -132,6 +138,8 @@ def size_kv_pool(cfg: ModelConfig, ecfg: EngineConfig, device: str, dtype) -> Tu
     if str(device).startswith("cuda"):
         free, total = torch.cuda.mem_get_info(torch.device(device))
         reserve = int(total * (1.0 - ecfg.gpu_memory_frac)) + 4 * GiB      # graphs + prefill workspace headroom
+        if cfg.has_kda:                                                    # recurrent-state slots come out of the same memory
+            reserve += state_pool_bytes(cfg, ecfg)
         pages = max(16, (free - reserve) // page_bytes)
         if ecfg.max_model_len > 0:
             pages = min(pages, ecfg.max_decode_batch * (-(-ecfg.max_model_len // ecfg.page_size) + 1))

@@ -149,3 +149,13 @@ def test_owner_layout_blocks_pads_and_keeps_owners():
     # with a graph runner the whole step is one of the captured sizes (a multiple of the group size)
     eng.graph_runner = types.SimpleNamespace(bucketing=types.SimpleNamespace(bucket_for=lambda n: 16))
     assert len(Engine._owner_layout(eng, live)) == 16
+
+
+def test_state_pool_is_budgeted():
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.runtime.planner import state_pool_bytes
+    cfg = get_model_config("kimi-k3-kda")
+    one = state_pool_bytes(cfg, EngineConfig(max_state_slots=1, attn_tp_size=8, world_size=8))
+    # 69 layers x 8 heads x (128 x 128 + 9 x 128) fp32
+    assert one == 69 * 8 * (128 * 128 + 9 * 128) * 4
+    assert state_pool_bytes(cfg, EngineConfig(max_decode_batch=64, attn_tp_size=8, world_size=8)) == 64 * one
