@@ -8,8 +8,11 @@
 //     through unified virtual addressing — pinned host pointers are valid device pointers, so one
 //     launch moves hundreds of small fragments (the per-layer rows of decode appends) either way.
 // submit() returns a task id; done()/wait() poll or block on the task's event (KVAsyncTask in the
-// reference).  Pointer tables are staged in a pinned ring owned by the mover, so submit allocates
-// nothing after construction.
+// reference).  Pointer tables are staged in a pinned ring owned by the mover and every ring entry owns its
+// dependency event, so submit allocates nothing and creates nothing after construction.  The kernel path
+// moves 16 bytes per thread and therefore needs 16-byte aligned fragments; a request with a misaligned
+// pointer takes the copy-engine path instead.  The first CUDA error of a request is returned as a negative
+// task id (-100 - cudaError) and nothing is recorded for it.
 //
 // Reference parity: core/KV_Storage/uva_copy_kernel.cu:53-73, core/HtoD_Engine/HtoD_Engine_Kernels.cu:4,
 // core/HtoD_Engine/HtoD_Engine.cu:1784-1830 (batched page copy), core/DtoH_Engine/DtoH_Engine.h:42-71,
@@ -41,13 +44,17 @@ class KVMover {
           cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) == cudaSuccess &&
           cudaHostAlloc(&tables_, sizeof(void*) * 2 * (size_t)cap_ * ring_, cudaHostAllocMapped) == cudaSuccess;
     events_.resize(ring_, nullptr);
+    deps_.resize(ring_, nullptr);
     for (int i = 0; ok_ && i < ring_; ++i)
-      ok_ = cudaEventCreateWithFlags(&events_[i], cudaEventDisableTiming) == cudaSuccess;
+      ok_ = cudaEventCreateWithFlags(&events_[i], cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&deps_[i], cudaEventDisableTiming) == cudaSuccess;
     busy_.assign(ring_, 0);
   }
   ~KVMover() {
     if (stream_) cudaStreamSynchronize(stream_);
     for (auto e : events_)
+      if (e) cudaEventDestroy(e);
+    for (auto e : deps_)
       if (e) cudaEventDestroy(e);
     if (tables_) cudaFreeHost(tables_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -66,13 +73,19 @@ class KVMover {
     }
     if (slot < 0) return -2;
     next_ = (slot + 1) % ring_;
-    cudaSetDevice(device_);
+    cudaError_t err = cudaSetDevice(device_);
+    auto note = [&err](cudaError_t e) { if (err == cudaSuccess && e != cudaSuccess) err = e; };
     if (after_stream != nullptr) {   // order the transfer after work already queued on a compute stream
-      cudaEvent_t dep;
-      cudaEventCreateWithFlags(&dep, cudaEventDisableTiming);
-      cudaEventRecord(dep, reinterpret_cast<cudaStream_t>(after_stream));
-      cudaStreamWaitEvent(stream_, dep, 0);
-      cudaEventDestroy(dep);
+      note(cudaEventRecord(deps_[slot], reinterpret_cast<cudaStream_t>(after_stream)));
+      note(cudaStreamWaitEvent(stream_, deps_[slot], 0));
+    }
+    if (use_kernel) {                // 16 bytes per thread: every fragment must start on a 16-byte boundary
+      uintptr_t any = 0;
+      for (int i = 0; i < n; ++i) any |= reinterpret_cast<uintptr_t>(src[i]) | reinterpret_cast<uintptr_t>(dst[i]);
+      if (any % 16 != 0) {
+        use_kernel = 0;
+        fallbacks_ += 1;
+      }
     }
     if (use_kernel) {
       void** ts = tables_ + (size_t)slot * 2 * cap_;
@@ -82,13 +95,18 @@ class KVMover {
         td[i] = dst[i];
       }
       void **ds = nullptr, **dd = nullptr;
-      cudaHostGetDevicePointer(reinterpret_cast<void**>(&ds), ts, 0);
-      cudaHostGetDevicePointer(reinterpret_cast<void**>(&dd), td, 0);
-      if (n > 0) page_copy_kernel<<<n, 256, 0, stream_>>>(ds, dd, bytes);
+      note(cudaHostGetDevicePointer(reinterpret_cast<void**>(&ds), ts, 0));
+      note(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dd), td, 0));
+      if (n > 0 && err == cudaSuccess) {
+        page_copy_kernel<<<n, 256, 0, stream_>>>(ds, dd, bytes);
+        note(cudaGetLastError());
+      }
     } else {
-      for (int i = 0; i < n; ++i) cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDefault, stream_);
+      for (int i = 0; i < n && err == cudaSuccess; ++i)
+        note(cudaMemcpyAsync(dst[i], src[i], bytes, cudaMemcpyDefault, stream_));
     }
-    cudaEventRecord(events_[slot], stream_);
+    if (err == cudaSuccess) note(cudaEventRecord(events_[slot], stream_));
+    if (err != cudaSuccess) return -100 - (long)err;     // nothing handed out for a request that was not queued
     busy_[slot] = 1;
     bytes_moved_ += (uint64_t)n * bytes;
     tasks_ += 1;
@@ -109,17 +127,19 @@ class KVMover {
   }
   uint64_t bytes_moved() const { return bytes_moved_; }
   uint64_t tasks() const { return tasks_; }
+  uint64_t misaligned_fallbacks() const { return fallbacks_; }
 
  private:
   int device_, cap_, ring_;
   bool ok_ = false;
   cudaStream_t stream_ = nullptr;
   void** tables_ = nullptr;
-  std::vector<cudaEvent_t> events_;
+  std::vector<cudaEvent_t> events_;   // completion of the task in each ring entry
+  std::vector<cudaEvent_t> deps_;     // dependency on a compute stream, one per ring entry
   std::vector<char> busy_;
   int next_ = 0;
   std::mutex mu_;
-  uint64_t bytes_moved_ = 0, tasks_ = 0;
+  uint64_t bytes_moved_ = 0, tasks_ = 0, fallbacks_ = 0;
 };
 
 }  // namespace bgcore
@@ -145,6 +165,7 @@ int bgc_mover_stream_wait(void* m, long task, void* stream) {
   return static_cast<bgcore::KVMover*>(m)->stream_wait(task, stream);
 }
 unsigned long long bgc_mover_bytes(void* m) { return static_cast<bgcore::KVMover*>(m)->bytes_moved(); }
+unsigned long long bgc_mover_misaligned(void* m) { return static_cast<bgcore::KVMover*>(m)->misaligned_fallbacks(); }
 int bgc_pin_host(void* p, size_t bytes) { return cudaHostRegister(p, bytes, cudaHostRegisterDefault) == cudaSuccess ? 0 : -1; }
 int bgc_unpin_host(void* p) { return cudaHostUnregister(p) == cudaSuccess ? 0 : -1; }
 

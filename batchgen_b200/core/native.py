@@ -39,6 +39,7 @@ def lib() -> ctypes.CDLL:
         L.bgc_mover_create.restype = ctypes.c_void_p
         L.bgc_mover_submit.restype = ctypes.c_long
         L.bgc_mover_bytes.restype = ctypes.c_ulonglong
+        L.bgc_mover_misaligned.restype = ctypes.c_ulonglong
         _LIB = L
     return _LIB
 
@@ -279,6 +280,11 @@ class KVMover:
     @property
     def bytes_moved(self) -> int:
         return int(self.L.bgc_mover_bytes(self.h))
+
+    @property
+    def misaligned_fallbacks(self) -> int:
+        """Kernel-path requests that went to the copy engine because a fragment was not 16-byte aligned."""
+        return int(self.L.bgc_mover_misaligned(self.h))
 
     def close(self) -> None:
         if self.h:

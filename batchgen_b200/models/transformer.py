@@ -78,6 +78,9 @@ def linear(x, lin: Linear, xq=None, xs=None, silu_mul: bool = False):
         return y
     if x.is_cuda and x.dtype == torch.bfloat16 and lin.w.shape[1] % 64 == 0:
         return gemm.bf16_gemm(x.contiguous(), lin.w)
+    if x.is_cuda:
+        from ..ops.policy import library_fallback
+        library_fallback("linear", f"x {tuple(x.shape)} {x.dtype}, K {lin.w.shape[1]}; the bf16 GEMM needs K % 64 == 0")
     return x @ lin.w.t()
 
 
@@ -109,6 +112,16 @@ class Transformer:
 
     def _norm(self, x, w, residual, quant):
         return fused.rmsnorm(x, w, self.cfg.rms_eps, residual=residual, quant=quant)
+
+    def _lm_head(self, x) -> torch.Tensor:
+        """fp32 logits = x @ lm_head^T: the bf16 tcgen05 GEMM with an fp32 epilogue on the GPU."""
+        w = self.w.lm_head
+        if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 64 == 0:
+            return gemm.bf16_gemm(x.contiguous(), w, fp32_out=True)
+        if x.is_cuda:
+            from ..ops.policy import library_fallback
+            library_fallback("lm_head", f"x {x.dtype}, weight {tuple(w.shape)} {w.dtype}")
+        return (x @ w.t()).float()
 
     # ------------------------------------------------------------------ attention
     def _mla(self, l: int, lw: LayerWeights, x, xq, xs, meta: AttnMeta, cache) -> torch.Tensor:
@@ -441,7 +454,7 @@ class Transformer:
         if meta.logit_rows is not None:
             x = x[meta.logit_rows.long()]
         with self.timer.timed("lm_head"):
-            logits = (x @ self.w.lm_head.t()).float()
+            logits = self._lm_head(x)
         if tp:
             logits = self.comm.tp_gather_vocab(logits)
         if self.streamer is not None:
@@ -514,4 +527,4 @@ class Transformer:
             rows = meta.logit_rows.long()
             x = x[rows[(rows >= r * Tl) & (rows < (r + 1) * Tl)] - r * Tl]
         with tm.timed("lm_head"):
-            return (x @ self.w.lm_head.t()).float()
+            return self._lm_head(x)

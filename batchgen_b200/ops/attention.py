@@ -61,6 +61,10 @@ def mla_q_absorb(q: torch.Tensor, w_uk_t: torch.Tensor, nope: int, out: Optional
         _head_gemm(q.view(T, H * D) if q.is_contiguous() else q.as_strided((T, H * D), (q.stride(0), 1)), D, nope,
                    w_uk_t, out, out.stride(0), out.stride(1))
         return out
+    if q.is_cuda:
+        from .policy import library_fallback
+        library_fallback("mla_q_absorb", f"q {tuple(q.shape)} {q.dtype} strides {q.stride()}, nope {nope}; the per-head "
+                                         "GEMM needs bf16, dense heads, nope % 64 == 0")
     res = torch.bmm(q[..., :nope].transpose(0, 1), w_uk_t.transpose(1, 2)).transpose(0, 1)
     if out is not None:
         out.copy_(res)
@@ -76,6 +80,10 @@ def mla_out_absorb(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:
         out = torch.empty(T, H * V, dtype=o_lat.dtype, device=o_lat.device)
         _head_gemm(o_lat.view(T, H * L), L, L, w_uv, out, out.stride(0), V)
         return out
+    if o_lat.is_cuda:
+        from .policy import library_fallback
+        library_fallback("mla_out_absorb", f"o_lat {tuple(o_lat.shape)} {o_lat.dtype}, v {V}; the per-head GEMM needs "
+                                           "bf16, contiguous, latent % 64 == 0, v % 8 == 0")
     return torch.bmm(o_lat.transpose(0, 1), w_uv.transpose(1, 2)).transpose(0, 1).reshape(T, -1)
 
 
@@ -90,6 +98,9 @@ def gqa_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, 
     B, Hq, D = q.shape
     page = cache.shape[1]
     if not (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128)):
+        if q.is_cuda:
+            from .policy import library_fallback
+            library_fallback("gqa_decode", f"q {q.dtype}, head_dim {D}; the kernel needs bf16 and head_dim 64 or 128")
         out = torch.zeros_like(q)
         for b in range(B):
             L = int(seqlens[b])

@@ -16,12 +16,16 @@
 //     problems are refused with BG_NOALLOC_E_TOO_LARGE and nothing is launched.
 //   * Cost: the array is about 16.9 MB and is held by every GPU that loads the library, until the
 //     process exits.
-//   * The first call on a device resolves the array's device address (cudaGetSymbolAddress) and sets a
-//     kernel attribute.  Make that first call before any stream capture begins on that device.
-//   * Every call shares the one array, which keeps the contents of the previous call; the kernels
-//     overwrite every word they later read, so nothing needs clearing.  Two calls whose kernels can
-//     overlap on the GPU (different streams without an ordering between them) race on it: serialise
-//     them.
+//   * The first call on a device resolves the array's device address (cudaGetSymbolAddress) and sets the
+//     shared-memory attribute of both column variants of the kernel on that device.  Make that first call
+//     before any stream capture begins on that device.
+//   * Every call shares the one array, which keeps the contents of the previous call.  Each call first
+//     resets the (max, sum) pair of every partial it owns to "empty", and the kernels overwrite every
+//     other word they later read.  Two calls whose kernels can overlap on the GPU (different streams
+//     without an ordering between them) race on it: serialise them.
+//   * Pass a non-null `status` when the result must be trusted: a CTA whose bounded wait ran out writes
+//     no partial (the merge then leaves it out) and raises *status; with a null `status` nothing tells
+//     the caller that the output misses part of the KV range.
 //   * The call itself calls no cudaMalloc / cudaFree and no allocating library routine.
 #pragma once
 #include <cuda_runtime.h>

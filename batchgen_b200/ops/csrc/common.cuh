@@ -232,6 +232,25 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t valu
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
+// ---------------------------------------------------------------- host: per-device kernel attributes
+// The dynamic shared-memory limit of a kernel is a per-device (per-context) attribute, so "already set" is
+// tracked per device: a process that drives several GPUs sets it once on each.
+constexpr int kMaxDevices = 64;
+struct DeviceOnce {
+  bool done[kMaxDevices] = {};
+};
+template <typename Kernel>
+inline bool ensure_dynamic_smem(Kernel kernel, size_t bytes, DeviceOnce& once) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (tracked && once.done[dev]) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+    return false;
+  if (tracked) once.done[dev] = true;
+  return true;
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

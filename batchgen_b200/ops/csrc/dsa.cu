@@ -367,12 +367,8 @@ int bg_indexer_scores(const void* q8, const float* gate, const void* keys, long 
   p.bt_stride = bt_stride; p.lengths = lengths; p.scores = scores; p.ld_scores = ld_scores;
   p.tiles_per_cta = tiles_per_cta; p.status = status;
   const size_t smem = kScoreStages * kTileKeys * kD + kHeads * kD + sizeof(ScoreShared) + 1024;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(indexer_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return -12;
-    attr = true;
-  }
+  static bg::DeviceOnce attr;
+  if (!bg::ensure_dynamic_smem(indexer_scores_kernel, smem, attr)) return -12;
   indexer_scores_kernel<<<dim3(chunks, B), kScoreThreads, smem, stream>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }

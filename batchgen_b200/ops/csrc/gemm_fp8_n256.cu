@@ -363,13 +363,10 @@ static int launch(const void* A, const void* B, const Params& p, int b_rows, int
   CUtensorMap ta, tb;
   if (make_map(&ta, A, (uint64_t)p.M, (uint64_t)p.K, BM) != 0) return -10;
   if (make_map(&tb, B, (uint64_t)b_rows, (uint64_t)p.K, BN) != 0) return -11;
-  static bool attr_set = false;
+  static DeviceOnce attr_set;   // one per template instantiation, tracked per device
   auto kern = gemm_fp8_n256_kernel<EPI>;
   const size_t smem = kStages * (BM + BN) * BKB + sizeof(Shared) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -12;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
   const int n_tiles = (p.N + BN - 1) / BN;
   const long long m_tiles = p.offsets != nullptr ? (long long)p.M / BM + p.groups : (p.M + BM - 1) / BM;
   long long grid = m_tiles * n_tiles;

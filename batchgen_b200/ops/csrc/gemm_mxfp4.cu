@@ -376,13 +376,10 @@ static int launch(const void* A, const void* Wq, const Params& p, int b_rows, in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return -12;
   }
-  static bool attr_set = false;
+  static DeviceOnce attr_set;
   auto kern = mxfp4_gemm_kernel<EPI, QMODE>;
   const size_t smem = kStages * kStageBytes + sizeof(Shared) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -13;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem(kern, smem, attr_set)) return -13;
   const int n_tiles = (p.N + BN - 1) / BN;
   // upper bound on the tile count (grouped: every segment start is 128-aligned, so <= M/128 + groups row tiles)
   const long long m_tiles = p.offsets != nullptr ? (long long)p.M / BM + p.groups : (p.M + BM - 1) / BM;

@@ -517,13 +517,10 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
   CUtensorMap tmA, tmB;
   if (make_map_2d(&tmA, A, a_rows, p.K, eb, BM) != 0) return -10;
   if (make_map_2d(&tmB, B, b_rows, p.K, eb, BN) != 0) return -11;
-  static bool attr_set = false;  // one flag per template instantiation; one process drives one GPU
+  static DeviceOnce attr_set;   // one per template instantiation, tracked per device
   auto kern = gemm_kernel<KIND, EPI>;
   const size_t smem = gemm_smem_bytes();
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -12;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
   int grid = num_sms;
   if (p.offsets == nullptr) {
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);

@@ -163,13 +163,10 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t ro
 
 template <int BN>
 static int launch(const CUtensorMap& a, const CUtensorMap& w, const Params& p, int H, int* status, cudaStream_t stream) {
-  static bool attr_set = false;
+  static DeviceOnce attr_set;
   auto kern = head_gemm_kernel<BN>;
   const size_t smem = kStages * (BM * 128 + BN * 128) + sizeof(Shared<BN>) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -12;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
   dim3 grid((p.T + BM - 1) / BM, H, (p.N + BN - 1) / BN);
   kern<<<grid, kThreads, smem, stream>>>(a, w, p, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;

@@ -352,13 +352,9 @@ int bg_mha_prefill(const void* q, const void* kv, const void* kpe, long long kpe
   if (make_map(&tq, q, (uint64_t)H * kDqk, (uint64_t)Tq, (uint64_t)H * kDqk, BM) != 0) return -10;
   if (make_map(&tk, kv, (uint64_t)H * kKvRow, (uint64_t)Tk, (uint64_t)H * kKvRow, BN) != 0) return -11;
   if (make_map(&tv, kpe, 64, (uint64_t)Tk, (uint64_t)kpe_stride, BN) != 0) return -12;
-  static bool attr_set = false;
+  static bg::DeviceOnce attr_set;
   const size_t smem = kQBytes + kStages * (kKBytes + kVBytes) + kPBytes + sizeof(Shared) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(mha_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return -13;
-    attr_set = true;
-  }
+  if (!bg::ensure_dynamic_smem(mha_prefill_kernel, smem, attr_set)) return -13;
   dim3 grid(n_work, H);
   mha_prefill_kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, reinterpret_cast<const Work*>(work),
                                                        reinterpret_cast<__nv_bfloat16*>(out), H,

@@ -22,10 +22,18 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoallocS
 static void* g_scratch_dev_ptr[64] = {nullptr};
 
 // Fills the work and merge lists for a decode batch: item (b, g) owns slots (b*groups + g)*splits ...
-static __global__ void noalloc_fill_lists(NoallocScratch* s, int B, int groups, int splits) {
+// It also resets the (running max, row sum) pair of every partial this call owns to (-inf, 0), the value the merge
+// skips: the array keeps the previous call's partials, and a CTA that gives up on a bounded wait writes nothing, so
+// without the reset the merge would fold stale numbers into a plausible-looking result.
+static __global__ void noalloc_fill_lists(NoallocScratch* s, int B, int groups, int splits, int ncol) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int n_work = B * groups * splits;
   if (i < n_work) {
+    float* ml = &s->part_ml[0][0][0] + (size_t)i * ncol * 2;     // pitch of this launch's column variant
+    for (int c = 0; c < ncol; ++c) {
+      ml[2 * c] = -INFINITY;
+      ml[2 * c + 1] = 0.f;
+    }
     const int item = i / splits;
     Work w;
     w.q_row = item / groups;
@@ -83,6 +91,9 @@ int bg_mla_decode_split_noalloc(const void* q_abs, const void* q_pe, long long q
   if (g_scratch_dev_ptr[dev] == nullptr) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return BG_NOALLOC_E_SETUP;
+    // both column variants get their shared-memory limit now, so that no later call on this device (which may run
+    // inside a stream capture) has an attribute to set or a module to load
+    if (!prepare_device<16>() || !prepare_device<32>()) return BG_NOALLOC_E_SETUP;
     g_scratch_dev_ptr[dev] = ptr;
   }
   NoallocScratch* s = reinterpret_cast<NoallocScratch*>(g_scratch_dev_ptr[dev]);
@@ -92,7 +103,7 @@ int bg_mla_decode_split_noalloc(const void* q_abs, const void* q_pe, long long q
   if (make_map(&tq, q_abs, (long long)B * H, kLatent, kLatent * 2, hpg) != 0) return BG_NOALLOC_E_SETUP;
   if (make_map(&tqpe, q_pe, (long long)B * H, kRope, qpe_stride * 2, hpg) != 0) return BG_NOALLOC_E_SETUP;
 
-  noalloc_fill_lists<<<((int)n_work + 127) / 128, 128, 0, stream>>>(s, B, groups, num_splits);
+  noalloc_fill_lists<<<((int)n_work + 127) / 128, 128, 0, stream>>>(s, B, groups, num_splits, ncol);
   if (cudaGetLastError() != cudaSuccess) return -2;
 
   Params p;

@@ -565,16 +565,20 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// Sets the kernel's shared-memory limit on the current device (once per device and column variant).  Callers that
+// must not run attribute calls later (a stream capture in progress) call this for every variant up front.
+template <int NCOL>
+static bool prepare_device() {
+  static DeviceOnce attr_set;
+  return ensure_dynamic_smem(mla_kernel<NCOL>, Cfg<NCOL>::kSmemTiles + sizeof(Shared) + 1024, attr_set);
+}
+
 template <int NCOL>
 static int launch(const CUtensorMap& kv, const CUtensorMap& q, const CUtensorMap& qpe, const Params& p, int n_work,
                   cudaStream_t stream) {
-  static bool attr_set = false;
   auto kern = mla_kernel<NCOL>;
   const size_t smem = Cfg<NCOL>::kSmemTiles + sizeof(Shared) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -12;
-    attr_set = true;
-  }
+  if (!prepare_device<NCOL>()) return -12;
   kern<<<n_work, kThreads, smem, stream>>>(kv, q, qpe, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }

@@ -1,10 +1,13 @@
 // Token sampling: one block per row.  Greedy rows (temperature <= 0) take an arg-max fast path.
-// Sampled rows apply temperature, then keep the intersection of top-k and the top-p nucleus and
-// draw from it with a caller-provided uniform number.  The kept set is found without sorting: a
-// token with probability p is kept iff fewer than k tokens are more probable and the mass of the
-// more probable tokens is below top_p, which is monotone in p, so the cut is a binary search over
-// probability with one pass over the row per step.  The draw walks the kept tokens in vocabulary
-// order.  Rows with a non-finite maximum bump a device counter instead of raising.
+// Sampled rows apply temperature, then top-k, then the top-p nucleus *of the distribution renormalised
+// over the top-k survivors* (the two filters are sequential, as in batchgen/sampling.py:417-461), and
+// draw from what is left with a caller-provided uniform number.  The kept set is found without
+// sorting: a token with probability p is kept iff fewer than k tokens are more probable and the mass of
+// the more probable tokens is at most top_p * Z_k (Z_k = mass of the top-k set), which is monotone in
+// p, so each cut is a binary search over probability with one pass over the row per step.  With both
+// filters active a first search finds the top-k cut and one more pass takes Z_k.  The draw walks the
+// kept tokens in vocabulary order.  Rows with a non-finite maximum bump a device counter instead of
+// raising.
 //
 // Replaces (by behaviour): the torch-op sampler batchgen/sampling.py:296-530 (per-row
 // temperature/top-p/top-k tensors, greedy split, on-device bad-row counter).
@@ -100,7 +103,29 @@ sample_kernel(const T* __restrict__ logits, long long ld, int V, const float* __
   const float inv_z = 1.0f / z;
   const int k = (top_k != nullptr && top_k[row] > 0) ? top_k[row] : V;
   const float pp = top_p != nullptr ? top_p[row] : 1.0f;
-  // ---- cut: smallest tau such that {p > tau} has count < k and mass < top_p  -> keep p >= cut
+  // ---- Z_k: mass of the top-k set (only needed when the nucleus is taken inside a real top-k cut)
+  float zk = 1.0f;
+  if (k < V && pp < 1.0f) {
+    float lo_t = 0.f, hi_t = 1.0f;  // invariant: {p > hi_t} has fewer than k members
+    for (int it = 0; it < 26; ++it) {
+      const float mid = 0.5f * (lo_t + hi_t);
+      float cnt = 0.f;
+      for (int i = lo; i < hi; ++i) {
+        const float p = __expf((ld_logit(l, i) - gmax) * inv_t) * inv_z;
+        if (p > mid) cnt += 1.f;
+      }
+      cnt = block_reduce_sum(cnt, red);
+      if (cnt < (float)k) hi_t = mid; else lo_t = mid;
+    }
+    float mass = 0.f;
+    for (int i = lo; i < hi; ++i) {
+      const float p = __expf((ld_logit(l, i) - gmax) * inv_t) * inv_z;
+      if (p > lo_t) mass += p;
+    }
+    zk = block_reduce_sum(mass, red);
+  }
+  const float mass_cap = pp * zk;
+  // ---- cut: smallest tau such that {p > tau} has count < k and mass <= top_p * Z_k  -> keep p > cut
   float cut = 0.f;
   if (k < V || pp < 1.0f) {
     float lo_t = 0.f, hi_t = 1.0f;  // invariant: tau = hi_t satisfies the constraints (p_max <= 1)
@@ -113,7 +138,7 @@ sample_kernel(const T* __restrict__ logits, long long ld, int V, const float* __
       }
       mass = block_reduce_sum(mass, red);
       cnt = block_reduce_sum(cnt, red);
-      if (cnt < (float)k && mass < pp) hi_t = mid; else lo_t = mid;
+      if (cnt < (float)k && (pp >= 1.0f || mass <= mass_cap)) hi_t = mid; else lo_t = mid;
     }
     cut = lo_t;  // tokens with p > lo_t: the first token violating the constraint sits just below
   }

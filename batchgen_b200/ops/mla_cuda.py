@@ -1,8 +1,9 @@
 """CUDA entry points of the MLA attention operators.
 
-``mla_decode`` runs the tcgen05 paged-latent kernel (``csrc/mla_decode_tcgen05.cu``) when the
-library exports it; shapes the kernel does not cover go through a batched library path
-(gather + bmm) that is also the numerics cross-check used by the GPU tests.
+``mla_decode`` / ``mla_prefill`` run the tcgen05 paged-latent kernel (``csrc/mla_tcgen05.cuh``, C entry points in
+``csrc/mla_tcgen05.cu``).  Geometries the kernel does not cover (test-sized latent widths) have a batched library
+path (gather + bmm) that is also the numerics cross-check used by the GPU tests; it runs only when
+``ops.policy`` allows it and raises otherwise.
 """
 from __future__ import annotations
 
@@ -12,6 +13,12 @@ from typing import Sequence
 import torch
 
 from . import _ext
+from .policy import library_fallback
+
+
+def _why(q_abs, q_pe, cache, kv_lora) -> str:
+    return (f"dtype {q_abs.dtype}, kv_lora {kv_lora}, rope {q_pe.shape[-1]}, page {cache.shape[1]}, "
+            f"heads {q_abs.shape[1]}; the kernel needs bf16, 512 + 64, 64-token pages, heads % 8 == 0")
 
 
 def _gather_padded(cache: torch.Tensor, block_table: torch.Tensor, max_len: int) -> torch.Tensor:
@@ -38,15 +45,13 @@ def mla_decode(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora):
     if _kernel_supports(q_abs, q_pe, cache, kv_lora):
         from .mla_kernel import mla_decode_tc
         return mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora)
+    library_fallback("mla_decode", _why(q_abs, q_pe, cache, kv_lora))
     return mla_decode_lib(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora)
 
 
 def _kernel_supports(q_abs, q_pe, cache, kv_lora) -> bool:
     """The tcgen05 kernel covers the production geometry: bf16, 512 + 64 latent row, 64-token pages,
     a multiple of 8 heads per rank.  Other (test-sized) geometries use the library path."""
-    import os
-    if os.environ.get("BG_MLA_IMPL", "") == "lib":
-        return False
     return (q_abs.dtype == torch.bfloat16 and kv_lora == 512 and q_pe.shape[-1] == 64 and cache.shape[1] == 64
             and cache.dtype == torch.bfloat16 and q_abs.shape[1] % 8 == 0 and cache.is_contiguous())
 
@@ -55,6 +60,7 @@ def mla_prefill(q_abs, q_pe, cache, block_table, cu_seqlens: Sequence[int], ctx_
     if _kernel_supports(q_abs, q_pe, cache, kv_lora):
         from .mla_kernel import mla_prefill_tc
         return mla_prefill_tc(q_abs, q_pe, cache, block_table, cu_seqlens, ctx_lens, scale, kv_lora)
+    library_fallback("mla_prefill", _why(q_abs, q_pe, cache, kv_lora))
     return mla_prefill_lib(q_abs, q_pe, cache, block_table, cu_seqlens, ctx_lens, scale, kv_lora)
 
 
@@ -93,6 +99,7 @@ def sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, 
     if _kernel_supports(q_abs, q_pe, cache, kv_lora):
         from . import dsa
         return dsa.sparse_mla_decode(q_abs.contiguous(), q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
+    library_fallback("sparse_mla_decode", _why(q_abs, q_pe, cache, kv_lora))
     return sparse_mla_decode_lib(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, kv_lora)
 
 

@@ -32,15 +32,49 @@ def _geometry(H: int, prefill: bool) -> Tuple[int, int]:
     raise ValueError(f"the MLA kernel needs a multiple of 8 heads per rank, got {H}")
 
 
+_RETIRED: list = []      # replaced scratch buffers: a captured CUDA graph may still hold their addresses
+
+
 def _scratch(device, slots: int, ncol: int):
+    """Split-KV partial buffers for ``slots`` work items.  A launch captured in a CUDA graph keeps the addresses it
+    was given, so a buffer that is outgrown is never freed: it moves to ``_RETIRED`` and the graphs that captured it
+    keep working on it.  ``reserve_decode_scratch`` sizes the buffer for every bucket up front, so that growth after
+    the first capture does not happen at all in the graph runner."""
     key = (str(device), ncol)
     cur = _SCRATCH.get(key)
     if cur is None or cur[0].shape[0] < slots:
+        if cur is not None:
+            _RETIRED.append(cur)
         n = max(slots, 256)
         cur = (torch.empty(n, ncol, 512, dtype=torch.float32, device=device),
                torch.empty(n, ncol, 2, dtype=torch.float32, device=device))
         _SCRATCH[key] = cur
     return cur
+
+
+def decode_splits(B: int, H: int, max_tiles: int, sms: int) -> int:
+    """Split count of a decode launch.  A CTA costs about 12 us before and after its tiles (query load, TMEM,
+    pipeline fill, partial store), a 64-token tile 1.7 - 2.7 us: about two rounds of CTAs over the SMs balance
+    ragged lengths (longest first, see reorder_decode_work) without paying that fixed cost too often.  Measured on
+    48 rows x 16 heads x 4096 tokens with 13 splits (four rounds): 87 us, 0.41 of copy bandwidth."""
+    hpg, _ = _geometry(H, prefill=False)
+    ctas = B * (H // hpg)
+    return max(1, min(16, int(2.0 * sms / ctas + 0.5), max(1, max_tiles) // 4))
+
+
+def decode_slots(B: int, H: int, max_tiles: int, sms: int) -> int:
+    """Work items (= scratch slots) of a decode launch of batch ``B``; not monotone in ``B``."""
+    hpg, _ = _geometry(H, prefill=False)
+    return B * (H // hpg) * decode_splits(B, H, max_tiles, sms)
+
+
+def reserve_decode_scratch(device, batch_sizes: Sequence[int], H: int, max_tiles: int, sms: int) -> int:
+    """Size the split-KV scratch once for the largest slot count over ``batch_sizes`` (the graph buckets), before the
+    first capture.  Returns that slot count."""
+    _, ncol = _geometry(H, prefill=False)
+    need = max(decode_slots(b, H, max_tiles, sms) for b in batch_sizes)
+    _scratch(device, need, ncol)
+    return need
 
 
 def _qpe_view(q_pe: torch.Tensor):
@@ -110,14 +144,7 @@ def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_
     hpg, ncol = _geometry(H, prefill=False)
     groups = H // hpg
     if num_splits <= 0:
-        # A CTA costs about 12 us before and after its tiles (query load, TMEM, pipeline fill, partial store), a
-        # 64-token tile 1.7 - 2.7 us: about two rounds of CTAs over the SMs balance ragged lengths (longest
-        # first, see reorder_decode_work) without paying that fixed cost too often.  Measured on 48 rows x 16
-        # heads x 4096 tokens with 13 splits (four rounds): 87 us, 0.41 of copy bandwidth.
-        ctas = B * groups
-        sms = _ext.num_sms(dev)
-        max_tiles = max(1, (block_table.shape[1] * cache.shape[1]) // KV_TILE)
-        num_splits = max(1, min(16, int(2.0 * sms / ctas + 0.5), max_tiles // 4))
+        num_splits = decode_splits(B, H, (block_table.shape[1] * cache.shape[1]) // KV_TILE, _ext.num_sms(dev))
     key = (str(dev), B, H, num_splits)
     cached = _DECODE_WORK.get(key)
     if cached is None:

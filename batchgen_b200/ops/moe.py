@@ -74,6 +74,9 @@ def router_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
             w = _ROUTER_LP[key] = weight.to(torch.bfloat16).contiguous()
         if hidden.shape[1] % 64 == 0 and hidden.stride(1) == 1 and hidden.stride(0) == hidden.shape[1]:
             return gemm.bf16_gemm(hidden, w, fp32_out=True)
+        from .policy import library_fallback
+        library_fallback("router_logits", f"hidden {tuple(hidden.shape)} strides {hidden.stride()}; the GEMM needs "
+                                          "contiguous rows with K % 64 == 0")
         return torch.mm(hidden, w.t(), out_dtype=torch.float32)
     return hidden.float() @ weight.float().t()
 

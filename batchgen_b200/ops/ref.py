@@ -436,8 +436,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     ranks = torch.arange(V, device=logits.device).unsqueeze(0)
     k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V)).unsqueeze(-1)
     keep = ranks < k
-    cum = torch.cumsum(sp, -1)
-    keep &= (cum - sp) < top_p.float().unsqueeze(-1)
+    # the filters are sequential (batchgen/sampling.py:417-461): the nucleus is taken on the distribution
+    # renormalised over the top-k survivors; a token stays while the mass before it is at most top_p
+    sk = torch.where(keep, sp, torch.zeros_like(sp))
+    zk = sk.sum(-1, keepdim=True)
+    cum = torch.cumsum(sk, -1)
+    tp = top_p.float().unsqueeze(-1)
+    keep &= ((cum - sk) <= tp * zk) | (tp >= 1.0)
     keep[:, 0] = True
     sp = torch.where(keep, sp, torch.zeros_like(sp))
     sp = sp / sp.sum(-1, keepdim=True)

@@ -111,6 +111,7 @@ class DecodeGraphRunner:
         self._ring_n = [0, 0]
         self._ring_next = 0
         self._row_key = None
+        self._scratch_reserved = False
 
     # ------------------------------------------------------------------ capture
     def _meta(self, b: int) -> AttnMeta:
@@ -126,6 +127,7 @@ class DecodeGraphRunner:
     def capture(self, bucket: int) -> None:
         if bucket in self.graphs:
             return
+        self.reserve_attention_scratch()
         free0 = torch.cuda.mem_get_info(self.dev)[0]
         side = torch.cuda.Stream(self.dev)
         side.wait_stream(torch.cuda.current_stream(self.dev))
@@ -155,7 +157,32 @@ class DecodeGraphRunner:
             dist.barrier()
         self.ledger.per_bucket[bucket] = max(0, free0 - torch.cuda.mem_get_info(self.dev)[0])
 
+    def reserve_attention_scratch(self) -> int:
+        """Size the split-KV scratch of the MLA decode kernel for every bucket before anything is captured: the slot
+        count (rows x head groups x splits) is not monotone in the batch size, and a captured launch keeps the
+        addresses it was given.  Returns the largest slot count (0 when the model has no such kernel)."""
+        cfg = self.model.cfg
+        if not cfg.is_mla or torch.device(self.dev).type != "cuda" or self._scratch_reserved:
+            return 0
+        from ..ops import _ext, mla_kernel
+        W = self.model.layout.tp_size
+        sms = _ext.num_sms(self.dev)
+        need = 0
+        for b in self.bucketing.buckets:
+            if self.model.attn_request_parallel and W > 1 and b % W == 0 and not cfg.has_dsa:
+                rows, heads = b // W, cfg.num_heads            # own rows, every head
+            else:
+                rows, heads = b, cfg.num_heads // W
+            tiles = [self.max_pages * self.kv.page_size // mla_kernel.KV_TILE]
+            if cfg.has_dsa:                                    # sparse decode runs the same kernel over top-k rows
+                tiles.append(-(-cfg.index_topk // mla_kernel.KV_TILE))
+            for t in tiles:
+                need = max(need, mla_kernel.reserve_decode_scratch(self.dev, [rows], heads, t, sms))
+        self._scratch_reserved = True
+        return need
+
     def capture_all(self) -> None:
+        self.reserve_attention_scratch()
         for b in sorted(self.bucketing.buckets, reverse=True):   # largest first: smaller ones reuse its pool
             self.capture(b)
 

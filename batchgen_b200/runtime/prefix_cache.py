@@ -8,8 +8,8 @@ entries (only the cache holds the page) are reclaimable in LRU order, leaves fir
 Reference parity: core/KV_Storage/host_prefix_cache_coordinator.h:13-174 (commit /
 lookup_and_attach / evict / clear over a 256-bit page hash chain, ``BuildPrefixHashChain`` :101) and
 its Python client batchgen/prefix_reuse/prefill.py:64, commit.py:10-30, eviction.py:11-25.  The
-native coordinator in ``core/csrc/prefix_cache.h`` implements the same contract for the node-shared
-host tier; this class is the in-process (per-rank GPU pool) variant and the executable spec.
+native coordinator in ``core/csrc/host_kv.cpp`` (the prefix methods of ``core.native.HostPagedKV``) implements the same contract
+for the node-shared host tier; this class is the in-process (per-rank GPU pool) variant and the executable spec.
 """
 from __future__ import annotations
 

@@ -42,7 +42,8 @@ def reference_arm(args) -> int:
     if why is None:
         why = ("reference imports but its Blackwell path needs FlashMLA/DeepGEMM/UCX libraries that are not "
                "installed and cannot be fetched offline")
-    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line for the whole job, whatever the launcher started
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
     return 0
 
 

@@ -227,6 +227,36 @@ def test_sampling_greedy_and_constraints():
     assert torch.equal(tok1, logits.argmax(-1))
 
 
+def test_sampling_topk_then_topp_matches_reference_order():
+    """Both filters active: the kernel's draw equals the sequential reference (top-k, then the nucleus of the
+    renormalised survivors) for the same uniform numbers."""
+    T, V = 96, 4096
+    g = torch.Generator(device="cpu").manual_seed(3)
+    logits = (torch.randn(T, V, generator=g) * 3.0).to(DEV)
+    temp = torch.full((T,), 0.7, device=DEV)
+    tk = torch.tensor([2, 5, 20, 50] * (T // 4), device=DEV, dtype=torch.int32)
+    tp = torch.tensor([0.5, 0.8, 0.3] * (T // 3), device=DEV)
+    u = torch.rand(T, generator=g).to(DEV)
+    tok = sampling.sample(logits, temp, tk, tp, uniform=u).long().cpu()
+    # kept set from the reference's sequential rule; the kernel's token must be inside it
+    lf = logits.float().cpu() / 0.7
+    sp, si = torch.sort(torch.softmax(lf, -1), -1, descending=True)
+    for r in range(T):
+        k = int(tk[r])
+        sk = sp[r, :k]
+        cum = torch.cumsum(sk, 0)
+        keep = (cum - sk) <= float(tp[r]) * float(sk.sum())
+        keep[0] = True
+        allowed = set(si[r, :k][keep].tolist())
+        assert int(tok[r]) in allowed, (r, int(tok[r]), sorted(allowed)[:8])
+    # the example that separates the two semantics: p = (.3, .2, .1 x 5), k = 2, top_p = .5 keeps token 0 only
+    p = torch.tensor([0.3, 0.2, 0.1, 0.1, 0.1, 0.1, 0.1], device=DEV)
+    lg = p.log().unsqueeze(0).repeat(64, 1).contiguous()
+    t2 = sampling.sample(lg, torch.ones(64, device=DEV), torch.full((64,), 2, device=DEV, dtype=torch.int32),
+                         torch.full((64,), 0.5, device=DEV), uniform=torch.linspace(0, 0.999, 64, device=DEV))
+    assert set(t2.tolist()) == {0}
+
+
 def test_sampling_distribution():
     V, N = 50, 4000
     base = torch.randn(V, device=DEV)

@@ -64,6 +64,14 @@ def test_other_families_on_gpu_match_cpu(name):
     """GQA family (sinks, alternating sliding window), latent-MoE MLA family, DSA family: prefill logits of the
     GPU model agree with the fp32 CPU run of the same weights; greedy decode through the engine completes."""
     from batchgen_b200.ops import _ext
+    from batchgen_b200.ops.policy import allow_library_fallback
+    # these presets have test-sized geometries (latent 64, head_dim 32) that no production kernel covers: the
+    # library paths are allowed explicitly here; on production geometries they raise
+    with allow_library_fallback():
+        _other_family(name, _ext)
+
+
+def _other_family(name, _ext):
     # DSA: keep every key selectable, otherwise near-tied index scores pick different keys in bf16 / fp8 than
     # in fp32 and the comparison measures the tie-breaks (each DSA kernel has its own reference test)
     cfg = get_model_config(name, index_topk=128) if name == "tiny-glm5" else get_model_config(name)

@@ -36,7 +36,7 @@ def _inputs(lens, H, seed):
                                                                                          device=DEV)
 
 
-def _call_noalloc(lib, q_abs, q_pe, cache, bt, sl, splits, scale):
+def _call_noalloc(lib, q_abs, q_pe, cache, bt, sl, splits, scale, status=None):
     B, H, _ = q_abs.shape
     out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=DEV)
     P, S, D = cache.shape
@@ -45,7 +45,8 @@ def _call_noalloc(lib, q_abs, q_pe, cache, bt, sl, splits, scale):
     rc = fn(ctypes.c_void_p(q_abs.data_ptr()), ctypes.c_void_p(q_pe.data_ptr()), ctypes.c_longlong(q_pe.stride(1)),
             ctypes.c_int(B), ctypes.c_int(H), ctypes.c_void_p(cache.data_ptr()), ctypes.c_longlong(P * S),
             ctypes.c_void_p(bt.data_ptr()), ctypes.c_int(bt.stride(0)), ctypes.c_void_p(sl.data_ptr()),
-            ctypes.c_void_p(out.data_ptr()), ctypes.c_int(splits), ctypes.c_float(scale), ctypes.c_void_p(0),
+            ctypes.c_void_p(out.data_ptr()), ctypes.c_int(splits), ctypes.c_float(scale),
+            ctypes.c_void_p(0 if status is None else status.data_ptr()),
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     return rc, out
 
@@ -55,9 +56,13 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice():
     from batchgen_b200.ops.mla_kernel import mla_decode_tc
     lib = _ext.lib()
     lib.bg_noalloc_strerror.restype = ctypes.c_char_p
-    for call, (lens, H, splits) in enumerate([([1000, 130, 64, 2500], 16, 4), ([777, 90, 1300], 32, 3)]):
+    # 16 and 32 heads fill their column variant; 8 and 24 heads run 8 heads per group on the 16-column variant with
+    # half of the columns unused
+    cases = [([1000, 130, 64, 2500], 16, 4), ([777, 90, 1300], 32, 3), ([900, 70, 2100], 8, 4), ([400, 1500], 24, 3)]
+    status = _ext.status_word(DEV)
+    for call, (lens, H, splits) in enumerate(cases):
         cache, bt, q_abs, q_pe, sl = _inputs(lens, H, seed=10 + call)
-        rc, got = _call_noalloc(lib, q_abs, q_pe, cache, bt, sl, splits, 0.07)
+        rc, got = _call_noalloc(lib, q_abs, q_pe, cache, bt, sl, splits, 0.07, status=status if call % 2 else None)
         assert rc == 0, lib.bg_noalloc_strerror(rc)
         want = mla_decode_tc(q_abs, q_pe, cache, bt, sl, 0.07, 512, num_splits=splits)
         torch.cuda.synchronize()
