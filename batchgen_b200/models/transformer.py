@@ -159,6 +159,8 @@ class Transformer:
                     meta._mha_work_key = key
                 o = attn_ops.mha_prefill(q, kvb.view(T, Hh, 256), lat[:, cfg.kv_lora_rank:], meta._mha_work,
                                          cfg.softmax_scale)
+                if meta.cu_seqlens[-1] < T:
+                    o[meta.cu_seqlens[-1]:].zero_()      # padding rows of a sequence-parallel step belong to no sequence
             return o.reshape(T, -1)
         q_nope, q_pe = q[..., : cfg.qk_nope_head_dim], q[..., cfg.qk_nope_head_dim:]
         # absorb W_UK: [T, Hh, nope] x [Hh, nope, kv_lora] -> [T, Hh, kv_lora]
@@ -260,6 +262,8 @@ class Transformer:
             else:
                 o_lat = attn_ops.mla_prefill(q_abs.contiguous(), q_pe.contiguous(), cache.latent(l), meta.block_table,
                                              meta.cu_seqlens, meta.ctx_lens, cfg.softmax_scale, cfg.kv_lora_rank)
+            if meta.cu_seqlens[-1] < q_abs.shape[0]:
+                o_lat[meta.cu_seqlens[-1]:].zero_()      # padding rows of a sequence-parallel step belong to no sequence
         return o_lat
 
     def _dsa_select(self, l, lw, x, qn, meta: AttnMeta, cache):
@@ -462,6 +466,21 @@ class Transformer:
         return logits
 
     # ------------------------------------------------------------------ sequence-parallel forward
+    @staticmethod
+    def supports_sequence_parallel(cfg: ModelConfig) -> Optional[str]:
+        """``None`` when ``forward_sp`` (fused NVLink kernels) can run ``cfg``, otherwise the reason it cannot."""
+        if not cfg.is_mla:
+            return "GQA attention runs tensor-parallel through forward() and the collective baseline"
+        if cfg.has_kda:
+            return "KDA layers run tensor-parallel through forward() and the collective baseline"
+        if cfg.quant != "fp8_block":
+            return "the fused kernels move block-scaled FP8 rows; other expert formats use the collective baseline"
+        if cfg.moe_latent_size:
+            return "latent-MoE projections are not part of the fused path"
+        if cfg.hidden_size % 128 or cfg.expert_hidden % 128:
+            return "hidden sizes must be multiples of the 128-wide quantisation block"
+        return None
+
     def forward_sp(self, ids: torch.Tensor, meta: AttnMeta, cache) -> torch.Tensor:
         """Tensor-parallel attention + expert-parallel MoE with a row-sharded residual stream and the
         collectives fused into the kernels (``parallel.fused.FusedComm``).  ``ids`` holds all T tokens of

@@ -12,6 +12,13 @@ decode tokens, watermark re-entry into prefill) is kept, see ``scheduler.py``.
 
 All ranks of a TP/EP job run this loop in lock step over identical inputs, so every decision is taken
 redundantly and identically on each rank; only model collectives cross ranks.
+
+Two model paths sit under the same loop.  With the NCCL baseline (or one GPU) every rank calls
+``Transformer.forward`` on all rows of the step and samples all of them identically.  With the fused
+NVLink kernels (``parallel.fused.FusedComm`` and a sequence-parallel weight layout) the step is padded to a
+multiple of the world size, every rank calls ``Transformer.forward_sp`` and receives the logits of its own
+block of rows only, samples those, and the sampled tokens are all-gathered (``_sample_sharded``), so that
+every rank again holds every token before the next scheduling decision.
 """
 from __future__ import annotations
 
@@ -93,6 +100,16 @@ class Engine:
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(ecfg.seed)
         self.step_hook: Optional[Callable[[str], None]] = None   # watchdog feed
+        comm = model.comm
+        # > 1: the model runs forward_sp over a row-sharded residual stream (fused NVLink kernels)
+        self.sp_world = (comm.world if (comm is not None and getattr(comm, "fused", False) and comm.world > 1
+                                        and model.layout.sequence_parallel) else 1)
+        from .sampling_residency import DecodeSamplingResidency
+        self._residency = DecodeSamplingResidency(max(ecfg.max_decode_batch, 1) + 8 * max(self.sp_world, 1),
+                                                  self.device)
+        self._samp_key: Optional[tuple] = None
+        self._samp_rows: List[Optional[Sequence]] = []
+        self._samp_epoch = 0
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None, custom_id: str = "",
@@ -217,6 +234,14 @@ class Engine:
             cu.append(cu[-1] + (b - a))
             ctx_lens.append(a)
         dev = self.device
+        T = len(ids)
+        W = self.sp_world
+        pad = (-T) % W                                # fused path: whole rows-per-rank blocks; padding rows write no KV
+        if pad:
+            ids += [0] * pad
+            pos += [0] * pad
+            slots += [-1] * pad
+        logit_rows = [c - 1 for c in cu[1:]]
         meta = AttnMeta(
             mode="prefill",
             positions=torch.tensor(pos, dtype=torch.int32, device=dev),
@@ -227,9 +252,15 @@ class Engine:
                          if self.kv.state is not None else None),
             state_has_initial=(torch.tensor([int(c > 0) for c in ctx_lens], dtype=torch.int32, device=dev)
                                if self.kv.state is not None else None),
-            logit_rows=torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev))
-        logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
-        toks = self._sample(logits, group).tolist()
+            logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),
+            num_valid=torch.tensor([T], dtype=torch.int32, device=dev) if W > 1 else None)
+        ids_t = torch.tensor(ids, dtype=torch.int32, device=dev)
+        if W > 1:
+            logits = self.model.forward_sp(ids_t, meta, self.kv)      # wanted rows that this rank owns
+            toks = self._sample_sharded(logits, group, logit_rows, T + pad)
+        else:
+            logits = self.model.forward(ids_t, meta, self.kv)
+            toks = self._sample(logits, group).tolist()
         for s, t in zip(group, toks):
             full_len = len(s.all_ids if s.reentry_decoded_baseline else s.prompt_ids)
             self.stats.prefill_tokens += full_len - s.num_cached_tokens
@@ -239,14 +270,70 @@ class Engine:
             s.reentry_decoded_baseline = 0
 
     # ------------------------------------------------------------------ sampling
-    def _sample(self, logits: torch.Tensor, rows: List[Sequence]) -> torch.Tensor:
-        if all(s.params.temperature <= 0 for s in rows):
-            return sampling_ops.greedy(logits)
+    @staticmethod
+    def _greedy_row(s: Optional[Sequence]) -> bool:
+        return s is None or s.params.temperature <= 0
+
+    def _sample(self, logits: torch.Tensor, rows: List[Optional[Sequence]], resident: bool = False,
+                uniform: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Tokens for ``logits`` rows; ``rows[i]`` owns row i (``None`` = padding row, sampled greedily and dropped
+        by the caller).  ``resident``: the per-row parameters come from the device-resident cache, which is
+        re-uploaded only when the ordered row set changes (decode steps)."""
+        if all(self._greedy_row(s) for s in rows):
+            return sampling_ops.greedy(logits, out)
         dev = logits.device
-        temp = torch.tensor([s.params.temperature for s in rows], dtype=torch.float32, device=dev)
-        tk = torch.tensor([s.params.top_k for s in rows], dtype=torch.int32, device=dev)
-        tp = torch.tensor([s.params.top_p for s in rows], dtype=torch.float32, device=dev)
-        return sampling_ops.sample(logits, temp, tk, tp, generator=self._gen)
+        if resident:
+            key = tuple(s.global_idx if s is not None else -1 for s in rows)
+            if key != self._samp_key:                  # rebind (never mutate) on change: the cache keys on identity
+                self._samp_key, self._samp_rows = key, list(rows)
+                self._samp_epoch += 1
+            prm = [dict(temperature=0.0, top_p=1.0, top_k=0) if s is None else s.params for s in self._samp_rows]
+            v = self._residency.view(self._samp_rows, prm, self._samp_epoch, 0)
+            temp, tk, tp = v.temperature, v.top_k, v.top_p
+        else:
+            temp = torch.tensor([0.0 if s is None else s.params.temperature for s in rows], dtype=torch.float32,
+                                device=dev)
+            tk = torch.tensor([0 if s is None else s.params.top_k for s in rows], dtype=torch.int32, device=dev)
+            tp = torch.tensor([1.0 if s is None else s.params.top_p for s in rows], dtype=torch.float32, device=dev)
+        return sampling_ops.sample(logits, temp, tk, tp, uniform=uniform, out=out, generator=self._gen)
+
+    def _sample_sharded(self, logits: torch.Tensor, rows: List[Optional[Sequence]], row_index: List[int],
+                        padded_rows: int, resident: bool = False) -> List[int]:
+        """Fused sequence-parallel path.  ``logits`` holds, in order, the wanted rows that this rank owns: wanted
+        row i is row ``row_index[i]`` (ascending) of the padded step and belongs to rank ``row_index[i] //
+        (padded_rows / world)``.  Every rank samples its own rows, then one all-gather gives every rank every
+        token.  Random draws use one uniform number per wanted row taken from the generator that all ranks seed
+        alike, so the result does not depend on which rank owns a row."""
+        import torch.distributed as dist
+        comm = self.model.comm
+        W, r = self.sp_world, comm.rank
+        Tl = padded_rows // W
+        owners = [j // Tl for j in row_index]
+        counts = [0] * W
+        for o in owners:
+            counts[o] += 1
+        maxc = max(counts) if counts else 0
+        dev = self.device
+        if maxc == 0:
+            return []
+        tok_local = torch.zeros(maxc, dtype=torch.int32, device=dev)
+        mine = [i for i, o in enumerate(owners) if o == r]
+        uniform = None
+        if not all(self._greedy_row(s) for s in rows):
+            u_all = torch.rand(len(rows), device=dev, generator=self._gen)      # the same numbers on every rank
+            uniform = u_all[torch.tensor(mine, dtype=torch.long, device=dev)] if mine else None
+        if mine:
+            self._sample(logits, [rows[i] for i in mine], resident=resident, uniform=uniform,
+                         out=tok_local[: len(mine)])
+        gathered = torch.empty(W * maxc, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(gathered, tok_local, group=getattr(comm, "group", None))
+        g = gathered.view(W, maxc).tolist()
+        cursor = [0] * W
+        toks = []
+        for o in owners:
+            toks.append(g[o][cursor[o]])
+            cursor[o] += 1
+        return toks
 
     # ------------------------------------------------------------------ decode
     def _enter_decode(self, s: Sequence) -> bool:
@@ -343,16 +430,21 @@ class Engine:
     def _decode_step(self, rows: List[Sequence]) -> None:
         ps = self.buf.page_size
         dev = self.device
+        W = self.sp_world
         split = self.model.attn_request_parallel and self.model.layout.tp_size > 1
         layout: List[Optional[Sequence]] = self._owner_layout(rows) if split else list(rows)
-        real = [i for i, s in enumerate(layout) if s is not None]
+        if W > 1 and self.graph_runner is None and len(layout) % W:
+            layout += [None] * ((-len(layout)) % W)      # fused path: whole rows-per-rank blocks
         ids = [s.all_ids[s.num_cached_tokens] if s is not None else 0 for s in layout]
         pos = [s.num_cached_tokens if s is not None else 0 for s in layout]
         slots = [s.gpu_pages[p // ps] * ps + p % ps if s is not None else -1 for s, p in zip(layout, pos)]
         lens = [p + 1 if s is not None else 0 for s, p in zip(layout, pos)]
         if self.graph_runner is not None:
-            logits = self.graph_runner.decode(self, layout, ids, pos, slots, lens)
+            logits, bucket = self.graph_runner.decode(self, layout, ids, pos, slots, lens)
+            if W > 1:
+                layout = layout + [None] * (bucket - len(layout))    # the captured step covers the whole bucket
         else:
+            n_real = sum(1 for s in layout if s is not None)
             meta = AttnMeta(
                 mode="decode",
                 positions=torch.tensor(pos, dtype=torch.int32, device=dev),
@@ -361,15 +453,27 @@ class Engine:
                 seqlens=torch.tensor(lens, dtype=torch.int32, device=dev),
                 state_slots=(torch.tensor([s.state_slot if s is not None else -1 for s in layout], dtype=torch.int32,
                                           device=dev) if self.kv.state is not None else None))
-            logits = self.model.forward(torch.tensor(ids, dtype=torch.int32, device=dev), meta, self.kv)
-        if len(real) != len(layout):
-            logits = logits[torch.tensor(real, dtype=torch.long, device=logits.device)]
-        live = [layout[i] for i in real]
-        toks = self._sample(logits, live).tolist()
-        for s, t in zip(live, toks):
+            ids_t = torch.tensor(ids, dtype=torch.int32, device=dev)
+            if W > 1:
+                if not split and n_real != len(layout):
+                    # padding rows sit at the end: the router skips them (request-split layouts pad inside the
+                    # blocks instead; there the empty rows are routed like any row and dropped afterwards)
+                    meta.num_valid = torch.tensor([n_real], dtype=torch.int32, device=dev)
+                logits = self.model.forward_sp(ids_t, meta, self.kv)
+            else:
+                logits = self.model.forward(ids_t, meta, self.kv)
+        if W > 1:
+            toks = self._sample_sharded(logits, layout, list(range(len(layout))), len(layout), resident=True)
+        else:
+            toks = self._sample(logits, layout, resident=True).tolist()
+        n = 0
+        for s, t in zip(layout, toks):
+            if s is None:
+                continue
             s.num_cached_tokens += 1
             s.output_ids.append(int(t))
-        self.stats.decode_tokens += len(live)
+            n += 1
+        self.stats.decode_tokens += n
         self.stats.decode_steps += 1
 
     def _decode_interval(self) -> int:

@@ -265,9 +265,11 @@ class DecodeGraphRunner:
         self._ring_ev[handle].synchronize()
         return self._ring[handle][: self._ring_n[handle]]
 
-    def decode(self, engine, rows, ids, pos, slots, lens) -> torch.Tensor:
-        """Engine hook (``Engine.graph_runner``): logits of the step's rows (``None`` entries are empty rows that
-        pad a rank's block in request-split decode; their logits are returned too and ignored by the engine)."""
+    def decode(self, engine, rows, ids, pos, slots, lens):
+        """Engine hook (``Engine.graph_runner``): (logits, bucket) of the step.  ``None`` entries of ``rows`` are empty
+        rows that pad a rank's block in request-split decode; their logits are returned too and ignored by the
+        engine.  Without sequence parallelism the logits cover ``rows``; with it they cover this rank's block of the
+        bucket (rows past ``len(rows)`` are padding)."""
         b = self.stage(ids, pos, slots, lens, [s.gpu_pages if s is not None else [] for s in rows],
                        [s.state_slot if s is not None else -1 for s in rows] if self.state_slots is not None else None)
         key = tuple(id(s) for s in rows)
@@ -276,8 +278,12 @@ class DecodeGraphRunner:
             from ..ops import mla_kernel
             self._row_key = key
             padded = list(lens) + [0] * (b - len(lens))
+            W = self.model.layout.tp_size
+            if self.model.attn_request_parallel and W > 1 and b % W == 0:
+                r = self.model.layout.tp_rank            # request-split core: this rank attends over its own block
+                padded = padded[r * (b // W):(r + 1) * (b // W)]
             mla_kernel.reorder_decode_work(self.dev, padded)
-        return self.replay(b, len(rows))
+        return self.replay(b, len(rows)), b
 
 
 def compare_eager_vs_graph(runner: DecodeGraphRunner, ids, pos, slots, lens, page_lists, atol=0.0, rtol=0.0):

@@ -57,7 +57,8 @@ class ServerArgs:
     # prefix
     enable_prefix_cache: bool = False
     # comm
-    moe_comm: str = "fused"
+    moe_comm: str = "fused"                     # fused (in-kernel NVLink exchange) | nccl (collective baseline)
+    fused_max_tokens: int = 16384               # largest step (prefill micro-batch) of the fused path; sizes its heap
     decode_attn_split: str = "heads"            # heads | requests (rows pinned to owner ranks inside the TP group)
     # recurrent state (models with KDA layers)
     max_state_slots: int = 0
@@ -150,6 +151,8 @@ def validate_server_args(a: ServerArgs) -> ServerArgs:
         raise ServerArgsError("--ep-offloading-ratio needs --enable-ep-with-offloading")
     if a.moe_comm not in ("fused", "nccl"):
         raise ServerArgsError("--moe-comm must be fused or nccl")
+    if a.fused_max_tokens < 8 * a.world_size:
+        raise ServerArgsError("--fused-max-tokens must hold at least 8 rows per rank")
     if a.cuda_graph_max_bucket_size <= 0 or a.cuda_graph_num_buckets <= 0:
         raise ServerArgsError("CUDA graph bucket settings must be positive")
     if a.log_level not in ("debug", "info", "warning", "error"):

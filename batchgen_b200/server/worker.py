@@ -63,14 +63,30 @@ def build_engine(args, rank: int, world: int, device: str):
         loader = ConvertedCheckpoint(args.converted_ckpt_dir).loader()
     comm = None
     layout = ParallelLayout()
+    fused = False
     if world > 1:
-        from ..parallel.comm import NcclComm
-        comm = NcclComm()
-        layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+        from ..models.transformer import Transformer
+        from ..parallel import make_comm
+        why_not = Transformer.supports_sequence_parallel(cfg) if device.startswith("cuda") else "no GPU"
+        fused = args.moe_comm == "fused" and why_not is None
+        if args.moe_comm == "fused" and not fused:
+            from ..utils import eventlog
+            eventlog.get_log().info("worker.comm", rank=rank, chosen="nccl", reason=why_not)
+        comm = make_comm("fused" if fused else "nccl", device if fused else None)
+        layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=fused)
     model = build_model(cfg, device=device, dtype=dtype, seed=args.seed, layout=layout, comm=comm, loader=loader,
                         max_positions=max(8192, args.max_model_len if args.max_model_len > 0 else 8192))
     if world > 1 and ecfg.decode_attn_split == "requests" and cfg.is_mla and not cfg.has_dsa:
         model.attn_request_parallel = True       # the engine pins every sequence to an owner rank (Engine._owner_layout)
+    if fused:
+        # steps of the fused path are bounded by the symmetric heap: cap the packed prefill micro-batch
+        ecfg.max_prefill_tokens = min(ecfg.max_prefill_tokens, args.fused_max_tokens)
+        step_rows = max(ecfg.max_prefill_tokens, ecfg.max_decode_batch + 8 * world)
+        a2a = 0
+        if model.attn_request_parallel:
+            a2a = (ecfg.max_decode_batch + 8 * world) * (cfg.num_heads // world) * cfg.kv_cache_dim * 2
+        comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
+                       max_tokens=step_rows, a2a_bytes=a2a)
     pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
     eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages)
     if device.startswith("cuda") and ecfg.enable_cuda_graph:
@@ -79,7 +95,7 @@ def build_engine(args, rank: int, world: int, device: str):
         eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=ecfg.max_decode_batch,
                                              max_pages_per_seq=min(max_pages, pages),
                                              num_buckets=ecfg.cuda_graph_num_buckets,
-                                             max_bucket=ecfg.cuda_graph_max_bucket_size)
+                                             max_bucket=ecfg.cuda_graph_max_bucket_size, sequence_parallel=fused)
     return cfg, eng
 
 

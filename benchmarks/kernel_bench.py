@@ -8,6 +8,14 @@ larger than the 126 MB L2, warms up, times with CUDA events on the launching str
 line: time, achieved TFLOP/s or GB/s, and the fraction "of measured" peak (MEASURED_PEAKS.json at the
 repository root when present, else the fallback figures 6.65 TB/s / 1.59 PFLOP/s, "of fallback").
 The same command lines are the ones profiled with ncu for the summaries under profiles/.
+
+``--impl`` selects what is timed on the same inputs: ``ours`` (this repository's kernel), or a library anchor —
+``flashinfer`` for ``mla_decode`` (``flashinfer.mla.trtllm_batch_decode_with_kv_cache_mla`` on the trtllm-gen
+backend, called the way the reference calls it on Blackwell, batchgen/attention/mla/trtllm_gen_mla.py:49-93) and
+``torch`` / ``vllm`` for ``gemm_fp8`` (cuBLASLt through ``torch._scaled_mm`` with 1x128 / 128x128 block scales where
+the build supports them, else row-wise scales, else a bf16 ``torch.matmul``; vLLM's CUTLASS block-scaled GEMM).  A
+library anchor is not the reference itself; it is the kernel the reference (or a stock serving stack) would call on
+this GPU.  The output names which variant really ran.
 """
 import argparse
 import json
@@ -44,6 +52,59 @@ def timeit(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
+_FI_WS = {}
+
+
+def flashinfer_mla_decode(q, cache, bt, sl, max_len, scale):
+    """The reference's Blackwell MLA decode call (dense form): absorbed query [B, 1, H, 576], latent cache
+    [P, 64, 576], one zero-initialised 128 MiB workspace per device that every call reuses."""
+    from flashinfer.mla import trtllm_batch_decode_with_kv_cache_mla
+    B, H, W = q.shape
+    ws = _FI_WS.setdefault(q.device.index, torch.zeros(128 * 1024 * 1024, dtype=torch.uint8, device=q.device))
+    q4 = q.view(B, 1, H, W)
+
+    def run():
+        return trtllm_batch_decode_with_kv_cache_mla(
+            query=q4, kv_cache=cache, workspace_buffer=ws, qk_nope_head_dim=512, kv_lora_rank=512,
+            qk_rope_head_dim=W - 512, block_tables=bt, seq_lens=sl.clamp(min=1), max_seq_len=int(max_len),
+            sparse_mla_top_k=0, bmm1_scale=float(scale), bmm2_scale=1.0, backend="trtllm-gen")
+    run()
+    return run
+
+
+def library_fp8_gemm(impl, xq, xs, wq, ws):
+    """-> (callable, name of the variant that ran).  xq [M, K] e4m3 with 1x128 scales xs [M, K/128] (a transposed view of
+    a [K/128, M] buffer), wq [N, K] e4m3 with 128x128 scales ws [N/128, K/128]."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    tried = []
+    if impl == "vllm":
+        from vllm import _custom_ops as vops
+        sa = xs.contiguous()                                   # [M, K/128]
+        sb = ws.t().contiguous()                               # [K/128, N/128]
+        fn = lambda: vops.cutlass_scaled_mm(xq, wq.t(), sa, sb, torch.bfloat16)
+        fn()
+        return fn, "vllm cutlass_scaled_mm, 1x128 / 128x128 block scales"
+    # torch._scaled_mm: block scales first (1x128 activations, 128x128 weights), then row-wise, then bf16
+    for name, sa, sb in (
+            ("torch._scaled_mm (cuBLASLt), 1x128 / 128x128 block scales", xs.t().contiguous().t(), ws.t().contiguous()),
+            ("torch._scaled_mm (cuBLASLt), 1x128 / 128x128 block scales (row-major scale_a)", xs.contiguous(),
+             ws.t().contiguous()),
+            ("torch._scaled_mm (cuBLASLt), row-wise scales (coarser than the block scales of ours)",
+             xs[:, :1].contiguous(), ws[:1, :1].expand(1, N).contiguous())):
+        try:
+            fn = lambda sa=sa, sb=sb: torch._scaled_mm(xq, wq.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+            fn()
+            torch.cuda.synchronize()
+            return fn, name
+        except Exception as e:  # noqa: BLE001
+            tried.append(f"{name}: {type(e).__name__}: {str(e)[:120]}")
+    xb, wb = xq.to(torch.bfloat16), wq.to(torch.bfloat16)
+    fn = lambda: torch.matmul(xb, wb.t())
+    fn()
+    return fn, "torch.matmul bf16 (cuBLAS); FP8 library variants failed: " + " | ".join(tried)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
@@ -56,6 +117,8 @@ def main():
     ap.add_argument("--batch", type=int, default=96)
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "flashinfer", "torch", "vllm"])
+    ap.add_argument("--check", action="store_true", help="also compare the library result with this repository's")
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, tag = peaks()
@@ -67,7 +130,16 @@ def main():
             wq = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn)
             xs = torch.rand(K // 128, M, device=dev).t()
             ws = torch.rand((N + 127) // 128, K // 128, device=dev)
-            ms = timeit(lambda: gemm.fp8_gemm(xq, xs, wq, ws), a.iters)
+            if a.impl == "ours":
+                ms = timeit(lambda: gemm.fp8_gemm(xq, xs, wq, ws), a.iters)
+            else:
+                fn, variant = library_fp8_gemm(a.impl, xq, xs, wq, ws)
+                out["impl"] = variant
+                ms = timeit(fn, a.iters)
+                if a.check:
+                    want = gemm.fp8_gemm(xq, xs, wq, ws).float()
+                    got = fn().float()
+                    out["rel_vs_ours"] = float((got - want).norm() / want.norm())
             byts = M * K + N * K + M * N * 2
         else:
             x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
@@ -99,7 +171,16 @@ def main():
             q = torch.randn(B, H, 576, device=dev).to(torch.bfloat16)
             qa, qp = q[..., :512].contiguous(), q[..., 512:].contiguous()
             sl = torch.full((B,), L, dtype=torch.int32, device=dev)
-            ms = timeit(lambda: mla_decode_tc(qa, qp, cache, bt, sl, 0.1, 512), a.iters)
+            if a.impl == "ours":
+                ms = timeit(lambda: mla_decode_tc(qa, qp, cache, bt, sl, 0.1, 512), a.iters)
+            else:
+                fn = flashinfer_mla_decode(q, cache, bt, sl, L, 0.1)
+                out["impl"] = "flashinfer.mla.trtllm_batch_decode_with_kv_cache_mla (trtllm-gen)"
+                ms = timeit(fn, a.iters)
+                if a.check:
+                    want = mla_decode_tc(qa, qp, cache, bt, sl, 0.1, 512).float()
+                    got = fn().view(B, H, 512).float()
+                    out["rel_vs_ours"] = float((got - want).norm() / want.norm())
             byts = B * L * 1152
             fl = 2.0 * B * L * H * (576 + 512)
         else:

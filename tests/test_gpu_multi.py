@@ -36,6 +36,19 @@ def test_fused_sequence_parallel_forward_matches():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_engine_generates_over_the_fused_path():
+    """``Engine.generate`` on the fused sequence-parallel path (eager and under CUDA graphs, decode attention split
+    by heads and by request) against the NCCL baseline engine and the unsharded engine."""
+    res = _run("mp_engine_fused_check.py", 2, timeout=900)
+    assert res["lengths_ok"], res
+    assert res["graph_equals_eager"] and res["split_graph_equals_split"], res
+    assert res["sampled_consistent"], res
+    assert res["first_fused_vs_full"] >= 0.75 and res["first_nccl_vs_full"] >= 0.75, res
+    assert res["first_fused_vs_nccl"] >= 0.75, res
+    assert res["tokens_split_vs_heads"] >= 0.6, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_rank_leaves_between_steps_and_survivors_carry_on():
     """A rank exits with nothing in flight; the other learns of it from the control store before its next
     launch, skips the collective, sees a bounded device wait expire with a status, and keeps computing."""
