@@ -61,17 +61,16 @@ class ExpertWeights:
         return self
 
 
-_ROUTER_LP = {}
-
-
 def router_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """fp32 router logits [T, E] = hidden @ weight^T (weight [E, H]).  On the GPU: the bf16 tcgen05 GEMM with
     an fp32 epilogue (the bf16 copy of the router weight is made once per weight tensor)."""
     if hidden.is_cuda and hidden.dtype == torch.bfloat16:
-        key = (weight.data_ptr(), tuple(weight.shape))
-        w = _ROUTER_LP.get(key)
+        # the bf16 copy rides on the weight tensor object itself (a cache keyed by address would serve a stale copy
+        # once the allocator hands the address of a freed router weight to a new model)
+        w = getattr(weight, "_bg_bf16", None)
         if w is None:
-            w = _ROUTER_LP[key] = weight.to(torch.bfloat16).contiguous()
+            w = weight if weight.dtype == torch.bfloat16 and weight.is_contiguous() else weight.to(torch.bfloat16).contiguous()
+            weight._bg_bf16 = w
         if hidden.shape[1] % 64 == 0 and hidden.stride(1) == 1 and hidden.stride(0) == hidden.shape[1]:
             return gemm.bf16_gemm(hidden, w, fp32_out=True)
         from .policy import library_fallback

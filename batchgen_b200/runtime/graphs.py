@@ -209,6 +209,9 @@ class DecodeGraphRunner:
             self.h_lens[n:b] = 0
         for i, pl in enumerate(page_lists):
             k = len(pl)
+            if k > self.max_pages:
+                raise ValueError(f"row {i} holds {k} pages but the captured block table has {self.max_pages} columns "
+                                 f"(max_pages_per_seq)")
             self.h_bt[i, :k] = torch.as_tensor(pl, dtype=torch.int32)
         self.h_nv[0] = n
         nb = True

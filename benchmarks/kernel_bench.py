@@ -80,8 +80,8 @@ def library_fp8_gemm(impl, xq, xs, wq, ws):
     tried = []
     if impl == "vllm":
         from vllm import _custom_ops as vops
-        sa = xs.contiguous()                                   # [M, K/128]
-        sb = ws.t().contiguous()                               # [K/128, N/128]
+        sa = xs                                                # [M, K/128], M-major (a view of the [K/128, M] buffer)
+        sb = ws.t()                                            # [K/128, N/128] view of the [N/128, K/128] scales
         fn = lambda: vops.cutlass_scaled_mm(xq, wq.t(), sa, sb, torch.bfloat16)
         fn()
         return fn, "vllm cutlass_scaled_mm, 1x128 / 128x128 block scales"

@@ -45,7 +45,7 @@ def main():
         cfgE = ecfg(decode_attn_split="requests" if split else "heads", seed=seed)
         eng = Engine(model, cfgE, num_gpu_pages=96)
         if graph:
-            eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=16, max_pages_per_seq=8, num_buckets=3,
+            eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=16, max_pages_per_seq=48, num_buckets=3,
                                                  max_bucket=16, sequence_parallel=eng.sp_world > 1)
         out = eng.generate(prompts, params)
         torch.cuda.synchronize()

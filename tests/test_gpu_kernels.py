@@ -78,6 +78,19 @@ def test_bf16_gemm(M, N, K):
     _close(gemm.bf16_gemm(x, w), x.float() @ w.float().t())
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 16, 1024), (150, 4096, 1024), (48, 129280, 7168)])
+def test_bf16_gemm_fp32_epilogue(M, N, K):
+    """fp32-output epilogue at the router shape and at lm_head shapes (many column tiles)."""
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    got = gemm.bf16_gemm(x, w, fp32_out=True)
+    assert got.dtype == torch.float32
+    want = x.float() @ w.float().t()
+    torch.cuda.synchronize()
+    err = (got - want).abs().max().item()
+    assert err <= 2e-3 * want.abs().max().item(), (err, want.abs().max().item())
+
+
 def test_fp8_gemm_fused_silu():
     M, I, K = 300, 256, 512
     x = torch.randn(M, K, device=DEV)

@@ -31,6 +31,9 @@ def test_fused_sequence_parallel_forward_matches():
     assert res["rel_nccl_vs_full_max"] < 0.08, res
     assert res["rel_fused_vs_full_max"] < 0.08, res
     assert res["argmax_agree_min"] > 0.8, res
+    # the two multi-GPU paths against each other, directly: same size as either against the unsharded model (each
+    # path rounds its bf16 / e4m3 intermediates independently; 0.04 on this 3-layer random model)
+    assert res["rel_fused_vs_nccl_max"] < 0.06, res
     if res.get("decode_request_parallel_rel_max") is not None:      # decode with the request-parallel attention core
         assert res["decode_request_parallel_rel_max"] < 0.08, res
 
