@@ -126,6 +126,35 @@ class Engine:
         self.seqs[s.global_idx] = s
         return s
 
+    def adopt_sequence(self, prompt_ids: Seq[int], output_ids: Seq[int], params: Optional[SamplingParams] = None,
+                       custom_id: str = "", batch_id: str = "", gpu_pages: Optional[List[int]] = None) -> Sequence:
+        """Register a sequence whose KV already sits in device pages: a restored trajectory, a row received from
+        another rank, or a benchmark's synthetic context.  ``output_ids`` must hold at least the first generated
+        token (the next decode step feeds the last one).  Pages are allocated here unless ``gpu_pages`` (already
+        owned by the caller through ``self.kv.alloc``) is given; the row enters as PREFILLED."""
+        if not output_ids:
+            raise ValueError("an adopted sequence carries at least its first generated token")
+        s = Sequence(global_idx=self._next_idx, prompt_ids=list(map(int, prompt_ids)),
+                     params=params or SamplingParams(), custom_id=custom_id, batch_id=batch_id)
+        s.output_ids = list(map(int, output_ids))
+        s.num_cached_tokens = s.context_len - 1
+        need = pages_for(s.context_len, self.buf.page_size)
+        if gpu_pages is None:
+            gpu_pages = self.kv.alloc.alloc(need)
+        elif len(gpu_pages) < need:
+            raise ValueError(f"{len(gpu_pages)} pages given, the context needs {need}")
+        s.gpu_pages = list(gpu_pages)
+        s.status = S.PREFILLED
+        s.history.append("adopted")
+        self._next_idx += 1
+        self.seqs[s.global_idx] = s
+        return s
+
+    def decode_steps(self, max_steps: int) -> int:
+        """Admit decodable rows and decode at most ``max_steps`` tokens per row (a decode interval cut short),
+        then apply the boundary decisions.  Returns the steps executed."""
+        return self._decode_interval(max_steps=max_steps)
+
     # ------------------------------------------------------------------ helpers
     def _by_status(self, *st) -> List[Sequence]:
         return [s for s in self.seqs.values() if s.status in st]
@@ -476,7 +505,7 @@ class Engine:
         self.stats.decode_tokens += n
         self.stats.decode_steps += 1
 
-    def _decode_interval(self) -> int:
+    def _decode_interval(self, max_steps: Optional[int] = None) -> int:
         """Admit rows, decode up to one decision interval, then apply the boundary decisions.
         Returns the number of decode steps executed."""
         free = {0: self._free_pages() + (self.prefix.reclaimable_pages() if self.prefix else 0)}
@@ -492,7 +521,7 @@ class Engine:
         t0 = time.perf_counter()
         steps = 0
         eos = self.cfg.eos_token_id
-        for _ in range(self.buf.decision_interval):
+        for _ in range(min(self.buf.decision_interval, max_steps or self.buf.decision_interval)):
             live = [s for s in rows if not s.is_finished(eos)]
             if not live:
                 break

@@ -112,6 +112,7 @@ class DecodeGraphRunner:
         self._ring_next = 0
         self._row_key = None
         self._scratch_reserved = False
+        self._bt_keys: list = []                 # per staged row: key of the page list in the pinned block table
 
     # ------------------------------------------------------------------ capture
     def _meta(self, b: int) -> AttnMeta:
@@ -188,8 +189,11 @@ class DecodeGraphRunner:
 
     # ------------------------------------------------------------------ replay
     def stage(self, ids: Optional[Seq[int]], pos: Seq[int], slots: Seq[int], lens: Seq[int], page_lists: Seq[Seq[int]],
-              state_slots: Optional[Seq[int]] = None) -> int:
-        """Fill the pinned staging buffers and enqueue the host->device copies.  Returns the bucket."""
+              state_slots: Optional[Seq[int]] = None, page_keys: Optional[Seq] = None) -> int:
+        """Fill the pinned staging buffers and enqueue the host->device copies.  Returns the bucket.
+        ``page_keys[i]`` (optional) identifies the page list of row i, e.g. (sequence id, page count): rows whose
+        key equals the one staged last time keep their block-table row, and when no row changed the block table is
+        not copied at all (page lists change only at page boundaries)."""
         n = len(pos)
         b = self.bucketing.bucket_for(n)
         if self.state_slots is not None:
@@ -207,12 +211,25 @@ class DecodeGraphRunner:
             self.h_pos[n:b] = 0
             self.h_slots[n:b] = -1
             self.h_lens[n:b] = 0
+        bt_rows = 0
         for i, pl in enumerate(page_lists):
+            if page_keys is not None:
+                if i < len(self._bt_keys) and self._bt_keys[i] == page_keys[i]:
+                    continue
+                if i < len(self._bt_keys):
+                    self._bt_keys[i] = page_keys[i]
+                else:
+                    self._bt_keys.append(page_keys[i])
             k = len(pl)
             if k > self.max_pages:
                 raise ValueError(f"row {i} holds {k} pages but the captured block table has {self.max_pages} columns "
                                  f"(max_pages_per_seq)")
             self.h_bt[i, :k] = torch.as_tensor(pl, dtype=torch.int32)
+            bt_rows += 1
+        if page_keys is None:
+            self._bt_keys = []
+        else:
+            del self._bt_keys[n:]
         self.h_nv[0] = n
         nb = True
         if ids is not None:
@@ -222,9 +239,11 @@ class DecodeGraphRunner:
         self.pos[:b].copy_(self.h_pos[:b], non_blocking=nb)
         self.slots[:b].copy_(self.h_slots[:b], non_blocking=nb)
         self.lens[:b].copy_(self.h_lens[:b], non_blocking=nb)
-        self.bt[:n].copy_(self.h_bt[:n], non_blocking=nb)
+        if bt_rows:
+            self.bt[:n].copy_(self.h_bt[:n], non_blocking=nb)
         self.num_valid.copy_(self.h_nv, non_blocking=nb)
-        self.h2d_bytes_per_step = b * (4 + 4 + 8 + 4) + n * self.max_pages * 4 + 4
+        self.h2d_bytes_per_step = (b * (4 + 8 + 4) + (b * 4 if ids is not None else 0)
+                                   + (n * self.max_pages * 4 if bt_rows else 0) + 4)
         return b
 
     def replay(self, bucket: int, n: int) -> torch.Tensor:
@@ -274,7 +293,9 @@ class DecodeGraphRunner:
         engine.  Without sequence parallelism the logits cover ``rows``; with it they cover this rank's block of the
         bucket (rows past ``len(rows)`` are padding)."""
         b = self.stage(ids, pos, slots, lens, [s.gpu_pages if s is not None else [] for s in rows],
-                       [s.state_slot if s is not None else -1 for s in rows] if self.state_slots is not None else None)
+                       [s.state_slot if s is not None else -1 for s in rows] if self.state_slots is not None else None,
+                       page_keys=[(s.global_idx, len(s.gpu_pages), sum(s.gpu_pages)) if s is not None else (-1, 0, 0)
+                                  for s in rows])
         key = tuple(id(s) for s in rows)
         if key != self._row_key and self.model.cfg.is_mla and torch.device(self.dev).type == "cuda":
             # batch membership changed: put the longest sequences first in the attention work lists

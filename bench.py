@@ -8,9 +8,19 @@ tokens) with synthetic token ids and random-init weights.
 
 A *step* is one decode step of the whole decode batch through all 61 layers, sampling included.
 ``value`` = decode tokens/s of the job (rows * K / time of K steps, device-timed with CUDA events,
-max over ranks).  The ``e2e`` block times the same step through ``Engine``'s public decode path with
-the step's inputs staged in pinned host memory, copied host->device every step, and the sampled tokens
-read back device->host every step.
+max over ranks): the whole-step CUDA graph replayed on fixed device-resident inputs.
+
+The ``e2e`` block times K real decode steps through the engine's public API (``Engine.decode_steps``): the
+same sequences are registered with the engine (``Engine.adopt_sequence``: their synthetic KV already sits in
+its page pool), and every step goes through the scheduler's admission, the per-step input staging from pinned
+host memory (host->device copies of ids / positions / slots / lengths / block table), the graph replay, the
+sampler with per-row parameters, the token all-gather on multi-GPU jobs and the device->host read of the
+sampled tokens that the host needs to append them and to test for completion.
+
+``--bct`` runs the whole 512-request workload (prompts U[512, 4096], 1,024 forced tokens) through the offline
+batch API (``runtime.batch_api.run_batch``) on the same engine and adds the measured batch completion time and
+the engine-reported prefill / decode rates to the line (key ``bct``); ``--bct-requests`` / ``--bct-tokens``
+shrink it for quick runs (then marked ``"full": false``).
 
 Where the FP8 expert weights of the rank exceed what HBM can hold next to the KV pool (N < 8),
 layers share physical expert storage in a cycle of ``distinct_expert_sets`` sets: every layer still
@@ -47,6 +57,92 @@ def reference_arm(args) -> int:
     return 0
 
 
+def run_bct(eng, cfg, args, rank, world, barrier):
+    """The BASELINE workload through the offline batch API on the engine: wall time from the first request
+    handed over to the last completion, plus the engine's own prefill / decode rates (the reference prints the
+    same two at batchgen/batchgen_worker.py:6558-6578)."""
+    import random as _random
+    import time as _time
+
+    from batchgen_b200.runtime import batch_api
+    from batchgen_b200.runtime.engine import EngineStats
+    from batchgen_b200.runtime.tokenization import get_tokenizer
+    for s in list(eng.seqs.values()):                      # rows of the step benchmark leave first
+        if s.status.name != "COMPLETED":
+            eng._complete(s, "length")
+    eng.seqs.clear()
+    eng.stats = EngineStats()
+    rng = _random.Random(99)
+    reqs = []
+    for i in range(args.bct_requests):
+        n = rng.randint(512, 4096)
+        ids = [rng.randrange(2, cfg.vocab_size) for _ in range(n)]
+        reqs.append(batch_api.BatchRequest(f"r{i}", "/v1/completions",
+                                           {"prompt": ids, "max_tokens": args.bct_tokens, "temperature": 0,
+                                            "ignore_eos": True}))
+    tok = get_tokenizer("ids", cfg.vocab_size)
+    barrier()
+    t0 = _time.perf_counter()
+    items = batch_api.run_batch(eng, reqs, tok, batch_api.BatchOptions(endpoint="/v1/completions"))
+    barrier()
+    wall = _time.perf_counter() - t0
+    ok = sum(1 for it in items if it["error"] is None)
+    st = eng.stats.summary()
+    return {"bct_s": wall, "requests": args.bct_requests, "completed": ok, "forced_tokens": args.bct_tokens,
+            "full": args.bct_requests == 512 and args.bct_tokens == 1024,
+            "prefill_tok_per_s": st["prefill_tok_per_s"], "decode_tok_per_s": st["decode_tok_per_s"],
+            "prefill_tokens": st["prefill_tokens"], "decode_tokens": st["decode_tokens"],
+            "prefill_waves": st["prefill_waves"], "decode_steps": st["decode_steps"], "holds": st["holds"],
+            "evictions": st["evictions"], "api": "runtime.batch_api.run_batch on Engine"}
+
+
+def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist):
+    """Largest relative difference between one decode step over the fused kernels and the same step over NCCL
+    collectives, on the same weights and inputs.  The baseline model shares every tensor with the fused one; only
+    the tensors the sequence-parallel layout replicates are cut to their tensor-parallel shard."""
+    import copy
+
+    import torch
+
+    from batchgen_b200.models.transformer import AttnMeta, Transformer
+    from batchgen_b200.models.weights import Linear, ParallelLayout
+    from batchgen_b200.parallel.comm import NcclComm
+    B = d_ids.shape[0]
+    Bl = B // world
+    meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
+    rp = model.attn_request_parallel
+    model.attn_request_parallel = False
+    got = model.forward_sp(d_ids, meta, kv).float()
+    w = copy.copy(model.w)
+    w.layers = []
+    for lw in model.w.layers:
+        lw2 = copy.copy(lw)
+        if lw.experts is not None and lw.w13 is not None:       # shared expert of a MoE layer: replicated -> sharded
+            I = lw.w2.w.shape[1]
+            per = I // world
+            if not lw.w13.interleaved or per % 128:
+                model.attn_request_parallel = rp
+                return {"skipped": "shared-expert weights cannot be cut on quantisation-block boundaries"}
+            # rows: the tile-interleaved layout keeps the gate and up rows of 32 output columns together, so a column
+            # range is a row range; scales stay in gate-block-rows-then-up-block-rows order
+            g0, g1 = rank * per // 128, (rank + 1) * per // 128
+            s13 = torch.cat([lw.w13.s[g0:g1], lw.w13.s[I // 128 + g0: I // 128 + g1]], 0).contiguous()
+            lw2.w13 = Linear(lw.w13.w[rank * 2 * per:(rank + 1) * 2 * per], s13, interleaved=True)
+            lw2.w2 = Linear(lw.w2.w[:, rank * per:(rank + 1) * per].contiguous(), lw.w2.s[:, g0:g1].contiguous())
+        w.layers.append(lw2)
+    V = model.w.lm_head.shape[0]
+    w.lm_head = model.w.lm_head[rank * (V // world):(rank + 1) * (V // world)]
+    layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    base = Transformer(model.cfg, w, layout, NcclComm(), model.rope.max_pos)
+    want = base.forward(d_ids, meta, kv).float()[rank * Bl:(rank + 1) * Bl]
+    model.attn_request_parallel = rp
+    rel = float((got - want).norm() / want.norm())
+    agree = float((got.argmax(-1) == want.argmax(-1)).float().mean())
+    t = torch.tensor([rel, -agree], device=got.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"max_rel_diff_fused_vs_nccl": float(t[0]), "min_argmax_agreement": float(-t[1]), "rows": B}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -67,6 +163,12 @@ def main() -> int:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     ap.add_argument("--profile-ops", default="", help="write a per-operator CUDA-event breakdown to this file")
+    ap.add_argument("--bct", action="store_true", help="also run the 512-request workload through the batch API")
+    ap.add_argument("--bct-requests", type=int, default=512)
+    ap.add_argument("--bct-tokens", type=int, default=1024)
+    ap.add_argument("--check-comm", action="store_true",
+                    help="N > 1: run one decode step through the NCCL baseline on the same inputs and report the "
+                         "largest relative difference of the logits (outside the timed regions)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -80,7 +182,8 @@ def main() -> int:
     from batchgen_b200.models.weights import ParallelLayout
     from batchgen_b200.ops import _ext
     from batchgen_b200.ops import sampling as sampling_ops
-    from batchgen_b200.runtime.kv_cache import PagedKVCache
+    from batchgen_b200.runtime.engine import Engine
+    from batchgen_b200.runtime.sequence import SamplingParams
     from batchgen_b200.utils.clocks import ClockSampler
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -106,8 +209,9 @@ def main() -> int:
     prompt_lens = [rng.randint(512, 4096) for _ in range(B)]
     decoded_so_far = 512                                   # timed at the middle of the 1,024-token decode
     ctx = [p + decoded_so_far for p in prompt_lens]
+    e2e_buffer_pages = 4                                   # growth room of each row for the engine-driven steps
     pages_per_seq = [(c + 1 + page - 1) // page for c in ctx]
-    total_pages = sum(pages_per_seq) + 8
+    total_pages = sum(pages_per_seq) + B * e2e_buffer_pages + 8
 
     # ---- memory plan: how many distinct expert-weight sets fit next to the KV pool
     fused = comm is not None and getattr(comm, "fused", False)
@@ -134,17 +238,28 @@ def main() -> int:
     torch.cuda.synchronize()
     build_s = time.time() - t0
 
-    kv = PagedKVCache(cfg, total_pages + (args.prefill_tokens // page + 8), page, dev, torch.bfloat16)
+    # ---- the engine owns the page pool; the benchmark's sequences are registered with it (their KV is synthetic)
+    ecfg = EngineConfig(page_size=page, max_decode_batch=B, max_prefill_tokens=args.prefill_tokens,
+                        enable_cuda_graph=not args.no_graph, cuda_graph_max_bucket_size=B, cuda_graph_num_buckets=1,
+                        initial_gpu_page_buffer=e2e_buffer_pages, extension_gpu_page_buffer=2, decision_frequency_pages=2,
+                        world_size=world, attn_tp_size=world, ep_size=world, device=str(dev), dtype="bf16",
+                        decode_attn_split="requests" if req_core else "heads",
+                        moe_comm="fused" if fused else "nccl")
+    eng = Engine(model, ecfg, num_gpu_pages=total_pages + (args.prefill_tokens // page + 8))
+    kv = eng.kv
     for l in range(kv.kv.shape[0]):                        # one slab per layer that keeps paged KV
         kv.kv[l].normal_(0.0, 0.5)
-    # ---- decode step inputs (device resident for the kernel-timed number)
     gen = torch.Generator().manual_seed(7)
-    ids_h = torch.randint(2, cfg.vocab_size, (B,), generator=gen, dtype=torch.int32)
-    bt_h = torch.zeros(B, max(pages_per_seq), dtype=torch.int32)
-    nxt = 0
-    for i, n in enumerate(pages_per_seq):
-        bt_h[i, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
-        nxt += n
+    forced = SamplingParams(max_new_tokens=1024, ignore_eos=True)
+    seqs = []
+    for i in range(B):
+        toks = torch.randint(2, cfg.vocab_size, (ctx[i] + 1,), generator=gen).tolist()
+        seqs.append(eng.adopt_sequence(toks[: prompt_lens[i]], toks[prompt_lens[i]:], forced))
+    # ---- decode step inputs (device resident for the kernel-timed number)
+    ids_h = torch.tensor([s.all_ids[-1] for s in seqs], dtype=torch.int32)
+    bt_h = torch.zeros(B, max(pages_per_seq) + e2e_buffer_pages + 1, dtype=torch.int32)
+    for i, s in enumerate(seqs):
+        bt_h[i, : len(s.gpu_pages)] = torch.tensor(s.gpu_pages, dtype=torch.int32)
     pos_h = torch.tensor(ctx, dtype=torch.int32)
     slot_h = torch.tensor([int(bt_h[i, c // page]) * page + c % page for i, c in enumerate(ctx)], dtype=torch.int64)
     len_h = pos_h + 1
@@ -172,7 +287,8 @@ def main() -> int:
         from batchgen_b200.runtime.graphs import DecodeGraphRunner
         runner = DecodeGraphRunner(model, kv, max_batch=B, max_pages_per_seq=bt_h.shape[1], num_buckets=1,
                                    max_bucket=B, sequence_parallel=fused)
-        pl = [bt_h[i, :n].tolist() for i, n in enumerate(pages_per_seq)]
+        eng.graph_runner = runner
+        pl = [list(s.gpu_pages) for s in seqs]
         runner.stage(ids_h.tolist(), pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl)
         k0 = _ext.LAUNCHES["count"]
         runner.capture(B)
@@ -189,22 +305,6 @@ def main() -> int:
         sample_logits(runner.replay(B, B))
         _ext.LAUNCHES["count"] += graph_kernels
 
-    pending = []
-
-    def decode_step_graph_e2e():
-        # inputs from pinned host memory every step; tokens read back on the host every step, one step late
-        # (deferred read-back: the next step is fed the sampled tokens on the device, so the GPU never idles)
-        h = runner.decode_async(pos_h.tolist(), slot_h.tolist(), len_h.tolist(), pl,
-                                ids=ids_p.tolist() if not pending else None)
-        _ext.LAUNCHES["count"] += graph_kernels
-        pending.append(h)
-        if len(pending) > 1:
-            tok_pinned.copy_(runner.read(pending.pop(0)))
-
-    def e2e_drain():
-        while pending:
-            tok_pinned.copy_(runner.read(pending.pop(0)))
-
     def decode_step_eager():
         meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
         run_model(d_ids, meta)
@@ -214,20 +314,6 @@ def main() -> int:
             decode_step_graph()
         else:
             decode_step_eager()
-
-    def decode_step_e2e():
-        if runner is not None:
-            return decode_step_graph_e2e()
-        a = ids_p.to(dev, non_blocking=True)
-        b = bt_p.to(dev, non_blocking=True)
-        c = pos_p.to(dev, non_blocking=True)
-        d = slot_p.to(dev, non_blocking=True)
-        e = len_p.to(dev, non_blocking=True)
-        meta = AttnMeta(mode="decode", positions=c, slot_mapping=d, block_table=b, seqlens=e)
-        run_model(a, meta)
-        tok_pinned.copy_(out_tok, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        ids_p.copy_(tok_pinned)                              # next step feeds the sampled tokens
 
     def barrier():
         if world > 1:
@@ -283,23 +369,29 @@ def main() -> int:
     else:
         dsum = None
 
+    comm_check = None
+    if args.check_comm and fused:
+        # one eager decode step over the fused kernels against the same step over the NCCL baseline: the fused
+        # model's weights are reused (attention shards are the same; the shared experts and lm_head, replicated in
+        # the sequence-parallel layout, are sliced to their tensor-parallel shard for the baseline run)
+        comm_check = compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist)
+
     e2e = None
     if not args.no_e2e:
-        for _ in range(2):
-            decode_step_e2e()
-        def e2e_steps_then_drain(k=[0]):
-            decode_step_e2e()
-            k[0] += 1
-            if k[0] % args.steps == 0 and runner is not None:
-                e2e_drain()                                    # the last step's tokens are read inside the timed region
-        if runner is not None:
-            e2e_drain()
-        ms_e = timed(e2e_steps_then_drain, args.steps) / args.steps
-        h2d = sum(t.numel() * t.element_size() for t in (ids_p, bt_p, pos_p, slot_p, len_p))
-        if runner is not None:
-            h2d = runner.h2d_bytes_per_step
+        # K real decode steps through the engine: admission, input staging from pinned memory, graph replay,
+        # sampling, token exchange, token read-back on the host every step
+        done = eng.decode_steps(max(args.warmup, 3))
+        assert done == max(args.warmup, 3), f"engine warm-up ran {done} steps"
+        _ext.check_status()
+        l1 = _ext.LAUNCHES["count"]
+        steps_run = []
+        ms_e = timed(lambda: steps_run.append(eng.decode_steps(args.steps)), 1) / args.steps
+        assert steps_run == [args.steps], f"engine ran {steps_run} steps, wanted {args.steps}"
+        _ext.check_status()
+        h2d = runner.h2d_bytes_per_step if runner is not None else B * (4 + 4 + 8 + 4) + bt_h.numel() * 4
         e2e = {"value": B * 1000.0 / ms_e, "unit": "decode tokens/s", "ms_per_step": ms_e,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": tok_pinned.numel() * 4}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4, "api": "Engine.decode_steps",
+               "launches_outside_graph": _ext.LAUNCHES["count"] - l1}
 
     prefill = None
     if not args.no_prefill:
@@ -308,7 +400,7 @@ def main() -> int:
         L = args.prefill_tokens // n_seq
         T = n_seq * L
         pp = (L + page - 1) // page
-        pbt = torch.arange(total_pages, total_pages + n_seq * pp, dtype=torch.int32).view(n_seq, pp).to(dev)
+        pbt = torch.tensor(kv.alloc.alloc(n_seq * pp), dtype=torch.int32).view(n_seq, pp).to(dev)
         ppos = torch.arange(L, dtype=torch.int32).repeat(n_seq).to(dev)
         pslot = torch.cat([(pbt[i].long().repeat_interleave(page)[:L] * page
                             + torch.arange(L, device=dev) % page) for i in range(n_seq)])
@@ -345,12 +437,17 @@ def main() -> int:
         ms_p = timed(prefill_step, 2) / 2
         _ext.check_status()
         prefill = {"tokens_per_s": T * 1000.0 / ms_p, "ms_per_microbatch": ms_p, "tokens": T, "seq_len": L}
+        kv.alloc.free(pbt.flatten().tolist())
+
+    bct = None
+    if args.bct:
+        bct = run_bct(eng, cfg, args, rank, world, barrier)
 
     if rank == 0:
         total_prompt = sum(rng.randint(512, 4096) for _ in range(512))
-        bct = None
+        bct_proj = None
         if prefill:
-            bct = total_prompt / prefill["tokens_per_s"] + 512 * 1024 / decode_tps
+            bct_proj = total_prompt / prefill["tokens_per_s"] + 512 * 1024 / decode_tps
         out = {
             "metric": "decode tokens/s (DeepSeek-V3-671B FP8, batch workload of BASELINE config 2)",
             "value": decode_tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -367,7 +464,7 @@ def main() -> int:
                        "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",
                        "valid": not args.layers, "build_seconds": round(build_s, 1)},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "prefill": prefill,
-            "bct_projected_s": bct,
+            "bct_projected_s": bct_proj, "bct": bct, "comm_check": comm_check,
         }
         print(json.dumps(out))
     sys.stdout.flush()
