@@ -8,6 +8,7 @@ Prefill work lists are built per micro-batch from the host-side ``cu_seqlens``.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Sequence, Tuple
 
 import torch
@@ -136,10 +137,53 @@ def reorder_decode_work(device, lengths: Sequence[int]) -> int:
     return n
 
 
+_PERSIST: Dict[str, Tuple[torch.Tensor, ...]] = {}
+MAX_PERSIST_PAIRS = 2048
+PERSIST = os.environ.get("BG_MLA_PERSIST", "1") != "0"
+
+
+def _persist_scratch(dev):
+    """Fixed-size scratch of the persistent decode kernel (partials of cut pairs, per-pair arrival counters, every
+    CTA's copy of the tile prefix sums).  Sized by the SM count alone, allocated once per device and never replaced,
+    so launches captured in CUDA graphs keep valid addresses."""
+    key = str(dev)
+    cur = _PERSIST.get(key)
+    if cur is None:
+        ctas = _ext.num_sms(dev)
+        cur = (torch.empty(2 * ctas * 64 * 512, dtype=torch.float32, device=dev),
+               torch.empty(2 * ctas * 64 * 2, dtype=torch.float32, device=dev),
+               torch.zeros(MAX_PERSIST_PAIRS, dtype=torch.int32, device=dev),
+               torch.empty(ctas * (MAX_PERSIST_PAIRS + 1), dtype=torch.int32, device=dev))
+        _PERSIST[key] = cur
+    return cur
+
+
+def mla_decode_persist(q_abs, q_pe, cache, block_table, seqlens, scale):
+    """Persistent decode kernel (``csrc/mla_decode_persist.cu``): heads % 64 == 0, one query per sequence.  The KV
+    tiles of the whole batch are cut into equal shares per SM on the device, from the device-side lengths."""
+    B, H, _ = q_abs.shape
+    dev = q_abs.device
+    q_pe, qpe_stride = _qpe_view(q_pe)
+    q_abs, qabs_stride = _qpe_view(q_abs)
+    P, S, D = cache.shape
+    part_o, part_ml, counters, prefix = _persist_scratch(dev)
+    out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=dev)
+    rc = _ext.lib().bg_mla_decode_persist(
+        _ext.ptr(q_abs), ctypes.c_longlong(qabs_stride), _ext.ptr(q_pe), ctypes.c_longlong(qpe_stride), ctypes.c_int(B),
+        ctypes.c_int(H), _ext.ptr(cache), ctypes.c_longlong(P * S), _ext.ptr(block_table),
+        ctypes.c_int(block_table.stride(0)), _ext.ptr(seqlens), _ext.ptr(out), _ext.ptr(part_o), _ext.ptr(part_ml),
+        _ext.ptr(counters), _ext.ptr(prefix), ctypes.c_int(_ext.num_sms(dev)), ctypes.c_float(scale),
+        _ext.ptr(_ext.status_word(dev)), _ext.stream())
+    _ext.check(rc, "bg_mla_decode_persist")
+    return out
+
+
 def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_splits: int = 0):
     """q_abs [B, H, 512], q_pe [B, H, 64] -> [B, H, 512]."""
     B, H, _ = q_abs.shape
     dev = q_abs.device
+    if PERSIST and num_splits <= 0 and H % 64 == 0 and B * (H // 64) <= MAX_PERSIST_PAIRS:
+        return mla_decode_persist(q_abs, q_pe, cache, block_table, seqlens, scale)
     # q_abs may be a strided view (see _launch); only a non-unit inner stride forces a copy there
     hpg, ncol = _geometry(H, prefill=False)
     groups = H // hpg

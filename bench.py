@@ -99,7 +99,10 @@ def run_bct(eng, cfg, args, rank, world, barrier):
 def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist):
     """Largest relative difference between one decode step over the fused kernels and the same step over NCCL
     collectives, on the same weights and inputs.  The baseline model shares every tensor with the fused one; only
-    the tensors the sequence-parallel layout replicates are cut to their tensor-parallel shard."""
+    the tensors the sequence-parallel layout replicates are cut to their tensor-parallel shard.  Both runs use the
+    first dense layers plus two MoE layers at full width: through all 61 randomly initialised layers the top-8
+    routing of near-uniform router scores flips on rounding noise and the two paths decorrelate (0.8 relative
+    difference measured), which says nothing about the kernels."""
     import copy
 
     import torch
@@ -112,10 +115,16 @@ def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world,
     meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
     rp = model.attn_request_parallel
     model.attn_request_parallel = False
-    got = model.forward_sp(d_ids, meta, kv).float()
+    n_layers = min(len(model.w.layers), model.cfg.first_k_dense + 2)
+    all_layers = model.w.layers
+    model.w.layers = all_layers[:n_layers]
+    try:
+        got = model.forward_sp(d_ids, meta, kv).float()
+    finally:
+        model.w.layers = all_layers
     w = copy.copy(model.w)
     w.layers = []
-    for lw in model.w.layers:
+    for lw in all_layers[:n_layers]:
         lw2 = copy.copy(lw)
         if lw.experts is not None and lw.w13 is not None:       # shared expert of a MoE layer: replicated -> sharded
             I = lw.w2.w.shape[1]
@@ -140,7 +149,8 @@ def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world,
     agree = float((got.argmax(-1) == want.argmax(-1)).float().mean())
     t = torch.tensor([rel, -agree], device=got.device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return {"max_rel_diff_fused_vs_nccl": float(t[0]), "min_argmax_agreement": float(-t[1]), "rows": B}
+    return {"max_rel_diff_fused_vs_nccl": float(t[0]), "min_argmax_agreement": float(-t[1]), "rows": B,
+            "layers_compared": n_layers}
 
 
 def main() -> int:

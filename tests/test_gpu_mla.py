@@ -103,3 +103,44 @@ def test_library_path_agrees():
     a = mla_cuda.mla_decode_lib(q[..., :512].contiguous(), q[..., 512:].contiguous(), cache, bt, sl, 0.1, 512)
     b = mla_decode_tc(q[..., :512].contiguous(), q[..., 512:].contiguous(), cache, bt, sl, 0.1, 512)
     _check(b, a)
+
+
+# ---------------------------------------------------------------- persistent decode kernel (heads % 64 == 0)
+@pytest.mark.parametrize("H", [64, 128])
+@pytest.mark.parametrize("lens", [[1], [64, 65, 127, 128, 129], [700, 3, 2049, 300], [0, 300, 0, 1]])
+def test_persistent_decode_matches_reference(H, lens):
+    from batchgen_b200.ops.mla_kernel import mla_decode_persist
+    B = len(lens)
+    cache, bt = _setup(B, H, lens, seed=5)
+    q = torch.randn(B, H, 576, device=DEV).to(torch.bfloat16)
+    q_abs, q_pe = q[..., :512], q[..., 512:]                      # strided views of one [B, H, 576] buffer
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    for _ in range(2):                                            # twice: the pair counters must be back at zero
+        got = mla_decode_persist(q_abs, q_pe, cache, bt, sl, 0.1)
+        torch.cuda.synchronize()
+    want = ref.mla_decode(q_abs.float().cpu(), q_pe.float().cpu(), cache.float().cpu(), bt.cpu(), sl.cpu(), 0.1, 512)
+    live = [i for i, n in enumerate(lens) if n > 0]
+    _check(got.cpu()[live], want[live])
+    dead = [i for i, n in enumerate(lens) if n == 0]
+    if dead:
+        assert float(got[dead].float().abs().max()) == 0.0       # rows without tokens come out as zeros
+
+
+@pytest.mark.parametrize("B,H,max_len,seed", [(200, 128, 3000, 7), (1, 128, 20000, 8), (48, 128, 2816, 9),
+                                               (300, 64, 700, 10)])
+def test_persistent_decode_cuts_and_merges(B, H, max_len, seed):
+    """Ragged batches whose tile sequence is cut across CTAs inside pairs (partials + merge by the last arriver), one
+    very long sequence cut across every CTA, and many short pairs per CTA; against the per-CTA kernel."""
+    from batchgen_b200.ops.mla_kernel import mla_decode_persist
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(max(1, max_len // 8), max_len + 1, (B,), generator=g).tolist() if B > 1 else [max_len]
+    cache, bt = _setup(B, H, lens, seed=seed)
+    q = (torch.randn(B, H, 576, device=DEV) * 1.5).to(torch.bfloat16)
+    q_abs, q_pe = q[..., :512].contiguous(), q[..., 512:].contiguous()
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = mla_decode_persist(q_abs, q_pe, cache, bt, sl, 0.12)
+    got2 = mla_decode_persist(q_abs, q_pe, cache, bt, sl, 0.12)
+    want = mla_decode_tc(q_abs, q_pe, cache, bt, sl, 0.12, 512, num_splits=1)
+    torch.cuda.synchronize()
+    _check(got, want)
+    assert torch.equal(got, got2)
