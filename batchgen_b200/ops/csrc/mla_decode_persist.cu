@@ -4,11 +4,13 @@
 // tiles, S of tile t+1 issued before P.V of tile t).  What this kernel changes is everything around the tiles,
 // which is where a decode step of few rows x many heads spent most of its time:
 //
-//   * Work is not one CTA per (sequence, head group, split).  The (sequence, head group) pairs are laid end to end
-//     in units of KV tiles, the total is cut into gridDim.x equal chunks, and CTA k walks chunk k: a run of
-//     *segments*, each a range of tiles of one pair.  The cut is computed in the kernel from the device-side
-//     sequence lengths (every CTA scans the same prefix sums), so a captured CUDA graph balances whatever lengths
-//     it is replayed on and no host-side work list or split count exists.
+//   * Work is not one CTA per (sequence, head group, split).  The sequences are laid end to end in units of KV
+//     tiles, the total is cut into gridDim.x / groups equal chunks, and the CTAs k * groups + g (g = head group of
+//     64 heads) all walk chunk k: a run of *segments*, each a range of tiles of one sequence.  The CTAs of one chunk
+//     sit next to each other and stream the same tiles at the same pace, so every tile comes from DRAM once and from
+//     L2 for the other head groups.  The cut is computed in the kernel from the device-side sequence lengths (every
+//     CTA scans the same prefix sums), so a captured CUDA graph balances whatever lengths it is replayed on and no
+//     host-side work list or split count exists.
 //   * TMEM, barriers and the tile ring are set up once per CTA.  Between segments only the query tile is reloaded
 //     (after the last S of the previous segment has read it), while the KV loads of the next segment are already
 //     in flight and the tensor pipe idles only for the previous segment's accumulator read-out.
@@ -30,8 +32,8 @@
 namespace bg {
 namespace mla {
 
-constexpr int kPersistThreads = 192;
-constexpr int kMaxPairsPersist = 2048;      // (sequence, head group) pairs one launch can schedule
+constexpr int kPersistThreads = 224;        // producer, S issuer, four softmax warps, P.V issuer
+constexpr int kMaxPairsPersist = 2048;      // sequences one launch can schedule
 constexpr int kPrefetchTiles = 3;           // how far ahead of the shared-memory loads the L2 prefetch runs
 constexpr int kMinChunkTiles = 4;           // a CTA's share is at least this many tiles (tiny batches use fewer CTAs)
 constexpr int kPPairs = 8;                  // ring of 16 KB slots (two 64-dim chunks of one tile)
@@ -44,9 +46,9 @@ struct PersistParams {
   int bt_stride;
   const int* seqlens;
   __nv_bfloat16* out;       // [B, H, 512]
-  float* part_o;            // [2 * gridDim.x, 64, 512]
+  float* part_o;            // [2 * gridDim.x] slots of 64 x 512 floats, see the epilogue for the order inside a slot
   float* part_ml;           // [2 * gridDim.x, 64, 2]
-  unsigned int* counters;   // [pairs], zero between launches (the merging CTA resets its counter)
+  unsigned int* counters;   // [B * groups], zero between launches (the merging CTA resets its counter)
   int* prefix;              // [gridDim.x, kMaxPairsPersist + 1]: every CTA's own copy of the tile prefix sums
   int B;
   int H;
@@ -63,6 +65,7 @@ struct PersistShared {
   uint64_t rope_full[kPRope];
   uint64_t rope_empty[kPRope];
   uint64_t s_full[2];
+  uint64_t s_free[2];
   uint64_t p_full;
   uint64_t o_done;
   uint64_t o_free;
@@ -76,7 +79,22 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c
                : "memory");
 }
 
-// One segment: tiles [t0, t1) of pair `pair`.
+// 16 TMEM lanes x 32 columns for each half of the warp: thread i < 16 receives columns [c, c + 32) of lane (base + i),
+// thread i + 16 receives columns [c + 32, c + 64) of the same lane.  One score row is thus split between two threads.
+__device__ __forceinline__ void tmem_ld_16x32bx2_x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x32bx2.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32], 32;"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// One segment: tiles [t0, t1) of sequence `seq` (the CTA's head group is fixed); pair = seq * groups + group.
 struct Seg {
   int pair, seq, group;
   int t0, t1;
@@ -88,10 +106,10 @@ struct Seg {
 // Walks the segments of chunk [cb, ce) of the global tile sequence.  Every role of the CTA builds the same walk.
 struct SegWalk {
   const int* prefix;
-  int P, groups, cb, ce, p, cta;
+  int P, groups, group, cb, ce, p, cta;
   bool first;
   __device__ SegWalk(const int* prefix_, int P_, int groups_, int cb_, int ce_, int cta_)
-      : prefix(prefix_), P(P_), groups(groups_), cb(cb_), ce(ce_), cta(cta_), first(true) {
+      : prefix(prefix_), P(P_), groups(groups_), group(cta_ % groups_), cb(cb_), ce(ce_), cta(cta_), first(true) {
     // first pair with prefix[p + 1] > cb
     int lo = 0, hi = P;
     while (lo < hi) {
@@ -104,9 +122,9 @@ struct SegWalk {
     while (p < P && prefix[p + 1] <= max(prefix[p], cb)) ++p;   // empty pairs and pairs that end before the chunk
     if (p >= P || prefix[p] >= ce) return false;
     const int a = prefix[p], b = prefix[p + 1];
-    s.pair = p;
-    s.seq = p / groups;
-    s.group = p - s.seq * groups;
+    s.seq = p;
+    s.group = group;
+    s.pair = p * groups + group;
     s.tiles_pair = b - a;
     s.t0 = max(a, cb) - a;
     s.t1 = min(b, ce) - a;
@@ -152,7 +170,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ss.abort_flag;
-  const int P = p.B * p.groups;
+  const int P = p.B;                     // the tile sequence runs over sequences; the head group is the CTA's own
 
   if (threadIdx.x == 0) {
     mbar_init(&ss.q_full, 1);
@@ -161,6 +179,8 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
     for (int i = 0; i < kPRope; ++i) { mbar_init(&ss.rope_full[i], 1); mbar_init(&ss.rope_empty[i], 1); }
     mbar_init(&ss.s_full[0], 1);
     mbar_init(&ss.s_full[1], 1);
+    mbar_init(&ss.s_free[0], NS);
+    mbar_init(&ss.s_free[1], NS);
     mbar_init(&ss.p_full, NS);
     mbar_init(&ss.o_done, 1);
     mbar_init(&ss.o_free, NS);
@@ -177,7 +197,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   // written and read by this CTA only.
   int* prefix = p.prefix + (size_t)blockIdx.x * (kMaxPairsPersist + 1);
   for (int i = threadIdx.x; i < P; i += kPersistThreads) {
-    const int len = p.seqlens[i / p.groups];
+    const int len = p.seqlens[i];
     prefix[i + 1] = (max(len, 0) + kTile - 1) / kTile;
   }
   if (threadIdx.x == 0) prefix[0] = 0;
@@ -205,8 +225,11 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   const uint32_t tmem_base = ss.tmem_base;
   const int total = prefix[P];
   const int n_cta = gridDim.x;
-  const int chunk = max((total + n_cta - 1) / n_cta, kMinChunkTiles);
-  const int cb = min(total, (int)blockIdx.x * chunk), ce = min(total, cb + chunk);
+  const int n_chunks = max(n_cta / p.groups, 1);
+  const int chunk = max((total + n_chunks - 1) / n_chunks, kMinChunkTiles);
+  const int my_chunk = blockIdx.x / p.groups;
+  const int cb = (my_chunk < n_chunks) ? min(total, my_chunk * chunk) : total;
+  const int ce = min(total, cb + chunk);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -214,18 +237,29 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
       tma_prefetch_desc(&tm_kv);
       TileCursor cur(prefix, P, p.groups, cb, ce, blockIdx.x);
       TileCursor pre(prefix, P, p.groups, cb, ce, blockIdx.x);
-      auto prefetch_tile = [&](const TileCursor& c) {
-        const int row0 = p.block_table[(size_t)c.s.seq * p.bt_stride + c.t] * kPage;
+      // The page of a tile is looked up once, kPrefetchTiles tiles before the tile is loaded: the lookup (a dependent
+      // global load) feeds the L2 prefetch at once and waits in a small register queue for the shared-memory load.
+      int rq[kPrefetchTiles];
+      auto page_row = [&](const TileCursor& c) {
+        return p.block_table[(size_t)c.s.seq * p.bt_stride + c.t] * kPage;
+      };
+      auto prefetch_rows = [&](int row0) {
 #pragma unroll
         for (int ch = 0; ch < 9; ++ch) tma_prefetch_l2_2d(&tm_kv, ch * 64, row0);
       };
-      for (int i = 0; i < kPrefetchTiles && pre.valid; ++i) {
-        prefetch_tile(pre);
-        pre.advance();
+#pragma unroll
+      for (int i = 0; i < kPrefetchTiles; ++i) {
+        rq[i] = 0;
+        if (pre.valid) {
+          rq[i] = page_row(pre);
+          prefetch_rows(rq[i]);
+          pre.advance();
+        }
       }
       bool ok = true;
       uint32_t pit = 0, rit = 0, seg_no = 0;
       int loaded_pair = -1;
+      BG_TR(0, 0, 7);
       auto load_q = [&](const Seg& s) -> bool {
         if (seg_no > 0 && !mbar_wait(&ss.q_empty, (seg_no - 1) & 1, abort_flag, kTimeoutProducer)) return false;
         mbar_expect_tx(&ss.q_full, kPQBytes);
@@ -243,10 +277,15 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
           if (!load_q(cur.s)) { ok = false; break; }
           loaded_pair = cur.s.pair;
         }
-        const int row0 = p.block_table[(size_t)cur.s.seq * p.bt_stride + cur.t] * kPage;
+        const int row0 = rq[0];
+#pragma unroll
+        for (int i = 0; i + 1 < kPrefetchTiles; ++i) rq[i] = rq[i + 1];
+        const bool more = pre.valid;
+        if (more) rq[kPrefetchTiles - 1] = page_row(pre);      // issued now, first used after this tile's loads
         for (int m = 0; m < 4 && ok; ++m, ++pit) {
           const int slot = pit % kPPairs;
           if (!mbar_wait(&ss.pair_empty[slot], ((pit / kPPairs) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
+          if (m == 0) BG_TR(0, rit, 0);
           mbar_expect_tx(&ss.pair_full[slot], kPairBytes);
           uint8_t* dst = pair_buf + slot * kPairBytes;
           tma_load_2d(dst, &tm_kv, &ss.pair_full[slot], (2 * m) * 64, row0);
@@ -257,13 +296,14 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
         if (!mbar_wait(&ss.rope_empty[rslot], ((rit / kPRope) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
         mbar_expect_tx(&ss.rope_full[rslot], kChunkBytes);
         tma_load_2d(rope_buf + rslot * kChunkBytes, &tm_kv, &ss.rope_full[rslot], 8 * 64, row0);
+        BG_TR(0, rit, 1);
         ++rit;
         if (seg_start && cur.s.pair != loaded_pair) {
           if (!load_q(cur.s)) { ok = false; break; }
           loaded_pair = cur.s.pair;
         }
-        if (pre.valid) {
-          prefetch_tile(pre);
+        if (more) {
+          prefetch_rows(rq[kPrefetchTiles - 1]);
           pre.advance();
         }
         cur.advance();
@@ -280,61 +320,73 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ S issuer: S(g) = Q . KV(g)^T, as far ahead as the
+    // two score buffers and the tile ring allow (the P.V MMAs are issued by their own warp, so a wait for the
+    // softmax never holds back the next tile's scores)
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kMRows, kTile, 0, 0);
+      SegWalk walk(prefix, P, p.groups, cb, ce, blockIdx.x);
+      Seg s;
+      bool ok = true;
+      uint32_t g = 0;         // tiles issued so far, over all segments
+      uint32_t seg_no = 0;
+      while (ok && walk.next(s)) {
+        const int n_tiles = s.t1 - s.t0;
+        if (!mbar_wait(&ss.q_full, seg_no & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        for (int t = 0; ok && t < n_tiles; ++t, ++g) {
+          BG_TR(1, g, 0);
+          if (g >= 2 && !mbar_wait(&ss.s_free[g & 1], ((g >> 1) - 1) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tm_s = tmem_base + (g & 1) * kTile;
+          for (int m = 0; m < 4 && ok; ++m) {
+            const uint32_t pit = g * 4 + m;
+            const int slot = pit % kPPairs;
+            if (!mbar_wait(&ss.pair_full[slot], (pit / kPPairs) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+            tc_fence_after();
+            for (int cc = 0; cc < 2; ++cc) {
+              const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + (2 * m + cc) * 64 * 128));
+              const uint64_t bdesc = make_smem_desc_sw128(smem_u32(pair_buf + slot * kPairBytes + cc * kChunkBytes));
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, (m | cc | k) ? 1u : 0u);
+            }
+          }
+          if (!ok) break;
+          const int rslot = g % kPRope;
+          if (!mbar_wait(&ss.rope_full[rslot], (g / kPRope) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          BG_TR(1, g, 1);
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + 8 * 64 * 128));
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(rope_buf + rslot * kChunkBytes));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, 1u);
+          tc_commit(&ss.rope_empty[rslot]);
+          tc_commit(&ss.s_full[g & 1]);
+          if (t + 1 == n_tiles) tc_commit(&ss.q_empty);      // the query buffer may be refilled for the next segment
+          BG_TR(1, g, 2);
+        }
+        ++seg_no;
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ P.V issuer: O += P(g) . KV(g)[:, 0:512]
+    if (elect_one()) {
       constexpr uint32_t idesc_pv = make_idesc_bf16(kMRows, 128, 0, 1);
       const uint32_t tm_o = tmem_base + 2 * kTile;
       SegWalk walk(prefix, P, p.groups, cb, ce, blockIdx.x);
       Seg s;
       bool ok = true;
-      uint32_t gt = 0;        // tiles issued so far (S side), over all segments
-      uint32_t seg_no = 0;
-      // S(tile g) = Q . KV^T over 9 chunks into S buffer g & 1; `last` releases the query buffer afterwards
-      auto issue_s = [&](uint32_t g, bool last) -> bool {
-        const uint32_t tm_s = tmem_base + (g & 1) * kTile;
-        for (int m = 0; m < 4; ++m) {
-          const uint32_t pit = g * 4 + m;
-          const int slot = pit % kPPairs;
-          if (!mbar_wait(&ss.pair_full[slot], (pit / kPPairs) & 1, abort_flag, kTimeoutMma)) return false;
-          tc_fence_after();
-          for (int cc = 0; cc < 2; ++cc) {
-            const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + (2 * m + cc) * 64 * 128));
-            const uint64_t bdesc = make_smem_desc_sw128(smem_u32(pair_buf + slot * kPairBytes + cc * kChunkBytes));
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, (m | cc | k) ? 1u : 0u);
-          }
-        }
-        const int rslot = g % kPRope;
-        if (!mbar_wait(&ss.rope_full[rslot], (g / kPRope) & 1, abort_flag, kTimeoutMma)) return false;
-        tc_fence_after();
-        const uint64_t adesc = make_smem_desc_sw128(smem_u32(q_buf + 8 * 64 * 128));
-        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(rope_buf + rslot * kChunkBytes));
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, 1u);
-        tc_commit(&ss.rope_empty[rslot]);
-        tc_commit(&ss.s_full[g & 1]);
-        if (last) tc_commit(&ss.q_empty);
-        return true;
-      };
+      uint32_t g = 0, seg_no = 0;
       while (ok && walk.next(s)) {
         const int n_tiles = s.t1 - s.t0;
-        if (!mbar_wait(&ss.q_full, seg_no & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t g0 = gt;
-        if (!issue_s(g0, n_tiles == 1)) { ok = false; break; }
-        for (int t = 0; ok && t < n_tiles; ++t) {
-          const uint32_t g = g0 + t;
-          bool next_issued = true;
-          if (t + 1 < n_tiles) {
-            next_issued = mbar_test(&ss.rope_full[(g + 1) % kPRope], ((g + 1) / kPRope) & 1);
-            if (next_issued && !issue_s(g + 1, t + 2 == n_tiles)) { ok = false; break; }
-          }
+        for (int t = 0; ok && t < n_tiles; ++t, ++g) {
           if (t == 0 && seg_no > 0) {       // the previous segment's accumulator must have been read out
             if (!mbar_wait(&ss.o_free, (seg_no - 1) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
           }
+          BG_TR(1, g, 3);
           if (!mbar_wait(&ss.p_full, g & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          BG_TR(1, g, 4);
           tc_fence_after();
           const uint64_t pdesc = make_smem_desc_sw128(smem_u32(p_buf));
           for (int m = 0; m < 4; ++m) {
@@ -349,9 +401,8 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
             tc_commit(&ss.pair_empty[slot]);
           }
           tc_commit(&ss.o_done);
-          if (!next_issued && !issue_s(g + 1, t + 2 == n_tiles)) { ok = false; break; }
+          BG_TR(1, g, 5);
         }
-        gt = g0 + n_tiles;
         ++seg_no;
       }
     }
@@ -362,7 +413,6 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
     const int col = quad * 16 + (lane & 15);
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tm_o = tmem_base + 2 * kTile + lane_addr;
-    const int src_lane = lane & 15;
     const int stid = threadIdx.x - 64;                 // 0 .. 127
     uint8_t* prow = p_buf + (col >> 3) * 1024 + (col & 7) * 128;
     SegWalk walk(prefix, P, p.groups, cb, ce, blockIdx.x);
@@ -375,31 +425,36 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
       float m_run = -INFINITY, l_run = 0.f;
       for (int t = 0; ok && t < n_tiles; ++t) {
         const uint32_t g = gt + t;
+        if (threadIdx.x == 64) BG_TR(2, g, 0);
         if (softmax_vote_any<NS>(!mbar_wait(&ss.s_full[g & 1], (g >> 1) & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
+        if (threadIdx.x == 64) BG_TR(2, g, 1);
         tc_fence_after();
-        const int tok0 = (s.t0 + t) * kTile;
-        uint32_t sv[64];
-        tmem_ld<32>(tmem_base + lane_addr + (g & 1) * kTile, sv);
-        tmem_ld<32>(tmem_base + lane_addr + (g & 1) * kTile + 32, sv + 32);
+        // lanes 0..15 take tokens 0..31 of the tile for their column, lanes 16..31 tokens 32..63 of the same column
+        const int tok0 = (s.t0 + t) * kTile + (lo ? 0 : 32);
+        uint32_t sv[32];
+        tmem_ld_16x32bx2_x32(tmem_base + lane_addr + (g & 1) * kTile, sv);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&ss.s_free[g & 1]);                  // the scores are in registers: the buffer may take S(g + 2)
         float mt = -INFINITY;
-        const int n_ok = lo ? min(max(lim - tok0, 0), kTile) : 0;
+        const int n_ok = min(max(lim - tok0, 0), 32);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
+        for (int j = 0; j < 32; ++j) {
           const float v = (j < n_ok) ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
           sv[j] = __float_as_uint(v);
           mt = fmaxf(mt, v);
         }
+        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
         const bool grow = mt > m_run + 8.f;
         const float m_new = grow ? mt : m_run;
         const float alpha = (grow && m_run != -INFINITY) ? ex2_approx(m_run - m_new) : 1.f;
         // probabilities first (registers only); the wait for the previous P.V comes after
-        uint32_t pk[32];
+        uint32_t pk[16];
         float lsum = 0.f;
-        if (lo) {
+        {
           const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
 #pragma unroll
-          for (int q = 0; q < 32; ++q) {
+          for (int q = 0; q < 16; ++q) {
             const float p0 = ex2_approx(__uint_as_float(sv[2 * q]) + neg_m);
             const float p1 = ex2_approx(__uint_as_float(sv[2 * q + 1]) + neg_m);
             const __nv_bfloat162 o = __floats2bfloat162_rn(p0, p1);
@@ -407,44 +462,52 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
             pk[q] = *reinterpret_cast<const uint32_t*>(&o);
           }
         }
+        if (threadIdx.x == 64) BG_TR(2, g, 2);
         // the previous tile's second GEMM reads P and accumulates into O: both are touched below
         if (t > 0 && softmax_vote_any<NS>(!mbar_wait(&ss.o_done, (g - 1) & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
         tc_fence_after();
-        const float alpha_row = __shfl_sync(0xffffffffu, alpha, src_lane);
-        if (t > 0 && __any_sync(0xffffffffu, alpha_row != 1.f)) {
+        if (threadIdx.x == 64) BG_TR(2, g, 3);
+        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
           for (int c = 0; c < 8; ++c) {
             uint32_t ov[32];
             tmem_ld<32>(tm_o + c * 32, ov);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha_row);
+            for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
             tmem_st<32>(tm_o + c * 32, ov);
           }
           tmem_st_wait();
         }
-        if (lo) {
+        {
+          const int c0 = lo ? 0 : 4;               // 16-byte pieces of the 128-byte P row this lane writes
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(prow + ((c ^ (col & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-          l_run = l_run * alpha + lsum;
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(prow + (((c0 + c) ^ (col & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          l_run = l_run * alpha + lsum;            // per-lane share of the row sum; the two halves are added at the end
           m_run = m_new;
         }
         fence_async_smem();
         tc_fence_before();
         mbar_arrive(&ss.p_full);
+        if (threadIdx.x == 64) BG_TR(2, g, 4);
       }
       if (!ok) break;
+      if (threadIdx.x == 64) BG_TR(2, gt + n_tiles - 1, 5);
       // ---- read the accumulator out
       const uint32_t g_last = gt + n_tiles - 1;
       if (softmax_vote_any<NS>(!mbar_wait(&ss.o_done, g_last & 1, abort_flag, kTimeoutEpilogue))) { ok = false; break; }
       tc_fence_after();
-      const float l_row = __shfl_sync(0xffffffffu, l_run, src_lane);
-      const float m_row = __shfl_sync(0xffffffffu, m_run, src_lane);
+      const float l_row = l_run + __shfl_xor_sync(0xffffffffu, l_run, 16);
+      const float m_row = m_run;
       const int dim0 = lo ? 0 : 256;
       const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
       __nv_bfloat16* orow = p.out + ((size_t)s.seq * p.H + s.group * 64 + col) * kLatent + dim0;
-      float* prow_o = p.part_o + ((size_t)s.slot * 64 + col) * kLatent + dim0;
+      // A partial slot is not row-major: the piece (chunk c, 16-byte group q) of all 128 (column, half) rows is one
+      // contiguous 2 KB run, so a warp's store (and the merging warp's load) covers 512 contiguous bytes instead of 32
+      // rows 2 KB apart.
+      const int rr = quad * 32 + lane;
+      uint4* pslot = reinterpret_cast<uint4*>(p.part_o) + (size_t)s.slot * (64 * kLatent / 4);
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t ov[32];
@@ -465,8 +528,8 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            __stcg(reinterpret_cast<uint4*>(prow_o + c * 32 + j), make_uint4(ov[j], ov[j + 1], ov[j + 2], ov[j + 3]));
+          for (int q = 0; q < 8; ++q)
+            __stcg(pslot + (c * 8 + q) * 128 + rr, make_uint4(ov[4 * q], ov[4 * q + 1], ov[4 * q + 2], ov[4 * q + 3]));
         }
       }
       if (!s.whole) {
@@ -477,8 +540,8 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
         // ---- the CTA that arrives last at the pair's counter merges the pair
         __threadfence();
         softmax_bar<NS>();
-        const int a_t = prefix[s.pair], b_t = prefix[s.pair + 1];
-        const int ka = a_t / chunk, kb = (b_t - 1) / chunk;
+        const int a_t = prefix[s.seq], b_t = prefix[s.seq + 1];
+        const int ka = a_t / chunk, kb = (b_t - 1) / chunk;          // chunks that hold tiles of this sequence
         const int n_seg = kb - ka + 1;
         if (stid == 0) {
           const unsigned int prev = atomicAdd(p.counters + s.pair, 1u);
@@ -488,56 +551,71 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
         softmax_bar<NS>();
         if (ss.merge_flag) {
           __threadfence();
-          // warp q merges columns 16q .. 16q + 15; a lane owns dims {4 * lane + 128 * i + 0..3}
-          for (int cc = 0; cc < 16; ++cc) {
-            const int c2 = quad * 16 + cc;
-            float mx = -INFINITY;
-            for (int k = ka; k <= kb; ++k) {
-              const int sl = 2 * k + ((k == ka && a_t > ka * chunk) ? 1 : 0);
-              mx = fmaxf(mx, __ldcg(p.part_ml + ((size_t)sl * 64 + c2) * 2));
-            }
-            float acc[16];
+          // slot of chunk k's piece of this sequence: the CTA (k, group) wrote it as its first segment unless the
+          // sequence starts inside chunk ka
+          auto slot_of = [&](int k) { return 2 * (k * p.groups + s.group) + ((k == ka && a_t > ka * chunk) ? 1 : 0); };
+          // every thread merges the (column, half) row it owns in the epilogue layout: weights of the pieces first,
+          // then the 256 dims in eight chunks of 32; the loads of two pieces are issued together
+          float mx = -INFINITY;
+#pragma unroll 4
+          for (int k = ka; k <= kb; ++k) mx = fmaxf(mx, __ldcg(p.part_ml + ((size_t)slot_of(k) * 64 + col) * 2));
+          float l = 0.f;
+#pragma unroll 4
+          for (int k = ka; k <= kb; ++k) {
+            const float ms = __ldcg(p.part_ml + ((size_t)slot_of(k) * 64 + col) * 2);
+            const float ls = __ldcg(p.part_ml + ((size_t)slot_of(k) * 64 + col) * 2 + 1);
+            l = fmaf(ls, (ms == -INFINITY) ? 0.f : exp2f(ms - mx), l);
+          }
+          const float invl = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            float acc[32];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-            float l = 0.f;
-            for (int k = ka; k <= kb; ++k) {
-              const int sl = 2 * k + ((k == ka && a_t > ka * chunk) ? 1 : 0);
-              const float ms = __ldcg(p.part_ml + ((size_t)sl * 64 + c2) * 2);
-              const float ls = __ldcg(p.part_ml + ((size_t)sl * 64 + c2) * 2 + 1);
-              const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
-              l = fmaf(ls, f, l);
-              if (f != 0.f) {
-                const float4* src = reinterpret_cast<const float4*>(p.part_o + ((size_t)sl * 64 + c2) * kLatent);
+            for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+            for (int k0 = ka; k0 <= kb; k0 += 2) {
+              uint4 v[2][8];
+              float f[2];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float4 v = __ldcg(src + lane + 32 * i);
-                  acc[4 * i + 0] = fmaf(v.x, f, acc[4 * i + 0]);
-                  acc[4 * i + 1] = fmaf(v.y, f, acc[4 * i + 1]);
-                  acc[4 * i + 2] = fmaf(v.z, f, acc[4 * i + 2]);
-                  acc[4 * i + 3] = fmaf(v.w, f, acc[4 * i + 3]);
+              for (int u = 0; u < 2; ++u) {
+                const int k = min(k0 + u, kb);
+                const int sl = slot_of(k);
+                const float ms = __ldcg(p.part_ml + ((size_t)sl * 64 + col) * 2);
+                f[u] = (k0 + u > kb || ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+                const uint4* src = reinterpret_cast<const uint4*>(p.part_o) + (size_t)sl * (64 * kLatent / 4) + c * 8 * 128 + rr;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[u][q] = __ldcg(src + q * 128);
+              }
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                if (f[u] == 0.f) continue;            // an empty piece's partial is undefined
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  acc[4 * q + 0] = fmaf(__uint_as_float(v[u][q].x), f[u], acc[4 * q + 0]);
+                  acc[4 * q + 1] = fmaf(__uint_as_float(v[u][q].y), f[u], acc[4 * q + 1]);
+                  acc[4 * q + 2] = fmaf(__uint_as_float(v[u][q].z), f[u], acc[4 * q + 2]);
+                  acc[4 * q + 3] = fmaf(__uint_as_float(v[u][q].w), f[u], acc[4 * q + 3]);
                 }
               }
             }
-            const float invl = l > 0.f ? 1.0f / l : 0.f;
-            __nv_bfloat16* o = p.out + ((size_t)s.seq * p.H + s.group * 64 + c2) * kLatent;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              __align__(8) __nv_bfloat162 w2[2];
-              w2[0] = __floats2bfloat162_rn(acc[4 * i] * invl, acc[4 * i + 1] * invl);
-              w2[1] = __floats2bfloat162_rn(acc[4 * i + 2] * invl, acc[4 * i + 3] * invl);
-              *reinterpret_cast<uint2*>(o + 4 * lane + 128 * i) = *reinterpret_cast<const uint2*>(w2);
+            for (int j = 0; j < 32; j += 8) {
+              __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(acc[j + 2 * q] * invl, acc[j + 2 * q + 1] * invl);
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = *reinterpret_cast<const uint4*>(o);
             }
           }
         }
         softmax_bar<NS>();        // merge_flag is rewritten by the next cut segment
       }
+      if (threadIdx.x == 64) BG_TR(2, gt + n_tiles - 1, 6);
       gt += n_tiles;
       ++seg_no;
     }
     // ---- sequences without any token (padding rows of a graph bucket): their output rows are zeros
-    for (int pr = blockIdx.x; pr < P; pr += n_cta) {
-      if (prefix[pr + 1] != prefix[pr]) continue;
+    for (int pr = blockIdx.x; pr < P * p.groups; pr += n_cta) {
       const int seq = pr / p.groups, grp = pr - seq * p.groups;
+      if (prefix[seq + 1] != prefix[seq]) continue;
       uint4* o = reinterpret_cast<uint4*>(p.out + ((size_t)seq * p.H + grp * 64) * kLatent);
       for (int i = stid; i < 64 * kLatent / 8; i += NS) o[i] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -576,7 +654,7 @@ int bg_mla_decode_persist(const void* q_abs, long long qabs_stride, const void* 
       ctas <= 0)
     return -1;
   const int groups = H / 64;
-  if ((long long)B * groups > kMaxPairsPersist) return -3;
+  if (B > kMaxPairsPersist || groups > ctas) return -3;
   CUtensorMap tkv, tq, tqpe;
   if (make_map(&tkv, cache, cache_rows, kRow, kRow * 2, kPage) != 0) return -10;
   if (make_map(&tq, q_abs, (long long)B * H, kLatent, qabs_stride * 2, 64) != 0) return -11;

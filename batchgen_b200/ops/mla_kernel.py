@@ -152,7 +152,7 @@ def _persist_scratch(dev):
         ctas = _ext.num_sms(dev)
         cur = (torch.empty(2 * ctas * 64 * 512, dtype=torch.float32, device=dev),
                torch.empty(2 * ctas * 64 * 2, dtype=torch.float32, device=dev),
-               torch.zeros(MAX_PERSIST_PAIRS, dtype=torch.int32, device=dev),
+               torch.zeros(MAX_PERSIST_PAIRS * 16, dtype=torch.int32, device=dev),      # one counter per (sequence, group)
                torch.empty(ctas * (MAX_PERSIST_PAIRS + 1), dtype=torch.int32, device=dev))
         _PERSIST[key] = cur
     return cur
@@ -182,7 +182,7 @@ def mla_decode_tc(q_abs, q_pe, cache, block_table, seqlens, scale, kv_lora, num_
     """q_abs [B, H, 512], q_pe [B, H, 64] -> [B, H, 512]."""
     B, H, _ = q_abs.shape
     dev = q_abs.device
-    if PERSIST and num_splits <= 0 and H % 64 == 0 and B * (H // 64) <= MAX_PERSIST_PAIRS:
+    if PERSIST and num_splits <= 0 and H % 64 == 0 and B <= MAX_PERSIST_PAIRS and H // 64 <= 16:
         return mla_decode_persist(q_abs, q_pe, cache, block_table, seqlens, scale)
     # q_abs may be a strided view (see _launch); only a non-unit inner stride forces a copy there
     hpg, ncol = _geometry(H, prefill=False)

@@ -32,12 +32,25 @@ from ..config import EngineConfig, ModelConfig
 from ..models.transformer import AttnMeta, Transformer
 from ..ops import sampling as sampling_ops
 from . import scheduler as sched
+from . import wave_plan
 from .kv_cache import HostStateStore, PagedKVCache, build_block_table, slots_for_range
 from .prefix_cache import PrefixCache
 from .sequence import (PageBufferConfig, SamplingParams, Sequence, SequenceStatus, gpu_pages_first_load,
                        pages_for)
 
 S = SequenceStatus
+
+
+@dataclass
+class _PrefillRow:
+    """One packed row of a prefill micro-batch: ``tokens`` continue a context of ``start`` tokens whose KV sits in
+    the first pages of ``pages`` (``pages`` covers positions 0 .. start + len(tokens)).  ``seq`` receives the token
+    sampled from the row's last position; rows without a sequence (a shared prefix computed once for several
+    prompts) produce no logits."""
+    tokens: List[int]
+    start: int
+    pages: List[int]
+    seq: Optional[Sequence] = None
 
 
 @dataclass
@@ -53,6 +66,8 @@ class EngineStats:
     evictions: int = 0
     loads: int = 0
     offloaded_pages: int = 0
+    shared_prefix_tokens: int = 0      # prompt tokens not computed because another prompt of the wave shares them
+    trajectory_commits: int = 0        # completed rows whose prompt + output pages were left in the prefix cache
 
     def summary(self) -> Dict[str, float]:
         return dict(
@@ -182,6 +197,14 @@ class Engine:
     def _complete(self, s: Sequence, reason: str) -> None:
         s.finish_reason = reason
         self._release_state(s)
+        split = self.model.attn_request_parallel and self.model.layout.tp_size > 1    # decoded KV lives on the owner only
+        if self.prefix is not None and s.gpu_pages and s.num_cached_tokens >= self.buf.page_size \
+                and not str(reason).startswith("error") and not split:
+            # trajectory commit: the full pages of prompt + generated tokens stay in the prefix cache, so a later turn
+            # whose prompt extends this one (an agent session) restores them instead of recomputing
+            # (batchgen/prefix_reuse/trajectory_commit.py: a finished turn commits its KV up to a page boundary)
+            if self.prefix.commit(s.all_ids[: s.num_cached_tokens], s.gpu_pages):
+                self.stats.trajectory_commits += 1
         if s.gpu_pages:
             self.kv.alloc.free(s.gpu_pages)
             s.gpu_pages = []
@@ -211,33 +234,28 @@ class Engine:
             return 0
         t0 = time.perf_counter()
         wave = [self.seqs[i] for i in admitted]
-        new_lens: List[int] = []
         for s in wave:
             s.transition(S.IN_PREFILL)
-            ids = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
-            n_total = len(ids)
-            cached_pages: List[int] = []
-            if self.prefix is not None:
-                cached_pages, _ = self.prefix.lookup(ids)
-                self.prefix.attach(cached_pages)
-            n_cached = len(cached_pages) * self.buf.page_size
-            need = pages_for(n_total + 1, self.buf.page_size) - len(cached_pages)
-            if need > self._free_pages():
-                self._reclaim(need - self._free_pages())
-            s.gpu_pages = list(cached_pages) + self.kv.alloc.alloc(need)
-            if self.kv.state is not None and s.state_slot < 0:
-                s.state_slot = self.kv.state.acquire()
-            s.cached_prefix_tokens = n_cached
-            s.num_cached_tokens = n_cached
-            new_lens.append(n_total - n_cached)
-        # pack into token-capped micro-batches and run them
-        for mb in sched.prepack_ffd(new_lens, self.ecfg.max_prefill_tokens):
-            group = [wave[i] for i in mb.seq_indices]
-            self._run_prefill_microbatch(group)
+        if self.prefix is not None:
+            self._prefill_wave_shared(wave)
+        else:
+            new_lens: List[int] = []
+            for s in wave:
+                n_total = len(self._prefill_ids(s))
+                need = pages_for(n_total + 1, self.buf.page_size)
+                s.gpu_pages = self._alloc_pages(need)
+                if self.kv.state is not None and s.state_slot < 0:
+                    s.state_slot = self.kv.state.acquire()
+                s.cached_prefix_tokens = 0
+                s.num_cached_tokens = 0
+                new_lens.append(n_total)
+            # pack into token-capped micro-batches and run them
+            for mb in sched.prepack_ffd(new_lens, self.ecfg.max_prefill_tokens):
+                self._run_prefill_microbatch([wave[i] for i in mb.seq_indices])
         for s in wave:
             if self.prefix is not None:
-                ids = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
-                self.prefix.commit(ids, s.gpu_pages)
+                self.prefix.commit(self._prefill_ids(s), s.gpu_pages)
+            s.reentry_decoded_baseline = 0
             s.transition(S.PREFILLED)
             fin = s.is_finished(self.cfg.eos_token_id)
             if fin:
@@ -247,19 +265,93 @@ class Engine:
         self.stats.prefill_waves += 1
         return len(wave)
 
+    @staticmethod
+    def _prefill_ids(s: Sequence) -> List[int]:
+        """Tokens a prefill recomputes: the prompt, plus the tokens decoded before an eviction."""
+        return s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
+
+    def _alloc_pages(self, n: int) -> List[int]:
+        if n > self._free_pages():
+            self._reclaim(n - self._free_pages())
+        return self.kv.alloc.alloc(n)
+
+    def _prefill_wave_shared(self, wave: List[Sequence]) -> None:
+        """Prefill a wave so that every prefix shared inside it is computed once (in-wave prefix pool), on top of
+        the page-level prefix cache that carries prefixes across waves.
+
+        ``wave_plan.plan_wave_prefix_sharing`` cuts the prompts into page-sized blocks, finds the segments that two
+        or more prompts pass through and orders the work so that a segment is resident before anything reads it.
+        A segment is computed from one member's tokens into pages of its own; every member then holds a reference
+        to those pages at the head of its block table and computes only its private tail.  A prompt whose longest
+        cached prefix (from an earlier wave or turn) is at least as long as its in-wave chain uses the cached pages
+        instead (the planner's *materialized* prefix).  Reference parity: batchgen/prefix_reuse/wave_runtime.py:30-427
+        (pool wave: allocate, attach members, commit), executor.py:1-10 (chunk -> prepacked forward with pooled
+        ancestors as computed prefix)."""
+        ps = self.buf.page_size
+        ids_of = [self._prefill_ids(s) for s in wave]
+        cached: Dict[int, List[int]] = {}
+        hits = []
+        for i, ids in enumerate(ids_of):
+            pages, _ = self.prefix.lookup(ids)
+            if pages:
+                cached[i] = pages
+                hits.append(wave_plan.MaterializedPrefix(i, len(pages) * ps))
+        plan = wave_plan.plan_wave_prefix_sharing(ids_of, ps, threshold=2, chunk_tokens=self.ecfg.max_prefill_tokens,
+                                                  materialized=hits)
+        seg_pages: Dict[int, List[int]] = {}
+        for chunk in plan.chunks:
+            rows: List[_PrefillRow] = []
+            for idx in chunk:
+                it = plan.items[idx]
+                chain: List[int] = []
+                for sid in it.prefix_segments:
+                    chain += seg_pages[sid]
+                if it.kind == "materialize":
+                    seg = plan.segments[it.ref]
+                    pages = cached[seg.members[0]][: seg.tokens // ps]
+                    self.prefix.attach(pages)                     # the pool's own reference, dropped below
+                    seg_pages[it.ref] = pages
+                elif it.kind == "segment":
+                    seg = plan.segments[it.ref]
+                    own = self._alloc_pages(seg.tokens // ps)
+                    seg_pages[it.ref] = own
+                    rows.append(_PrefillRow(ids_of[seg.members[0]][it.token_start:it.token_end], it.token_start,
+                                            chain + own))
+                    self.stats.shared_prefix_tokens += (len(seg.members) - 1) * seg.tokens
+                else:
+                    s = wave[it.ref]
+                    n_total = len(ids_of[it.ref])
+                    own = self._alloc_pages(pages_for(n_total + 1, ps) - it.token_start // ps)
+                    self.kv.alloc.share(chain)                    # this member's references to the shared pages
+                    s.gpu_pages = chain + own
+                    s.cached_prefix_tokens = it.token_start
+                    s.num_cached_tokens = it.token_start
+                    rows.append(_PrefillRow(ids_of[it.ref][it.token_start:], it.token_start, s.gpu_pages, s))
+            if rows:
+                self._run_prefill_rows(rows)
+        for pages in seg_pages.values():
+            self.kv.alloc.free(pages)
+
     def _run_prefill_microbatch(self, group: List[Sequence]) -> None:
+        rows = []
+        for s in group:
+            full = self._prefill_ids(s)
+            rows.append(_PrefillRow(full[s.num_cached_tokens:], s.num_cached_tokens, s.gpu_pages, s))
+        self._run_prefill_rows(rows)
+
+    def _run_prefill_rows(self, rows: List[_PrefillRow]) -> None:
+        """One packed prefill forward over ``rows``; rows that belong to a sequence get their first token sampled."""
         ps = self.buf.page_size
         ids: List[int] = []
         pos: List[int] = []
         slots: List[int] = []
         cu = [0]
         ctx_lens: List[int] = []
-        for s in group:
-            full = s.all_ids if s.reentry_decoded_baseline else s.prompt_ids
-            a, b = s.num_cached_tokens, len(full)
-            ids += full[a:b]
+        for r in rows:
+            a, b = r.start, r.start + len(r.tokens)
+            ids += r.tokens
             pos += list(range(a, b))
-            slots += slots_for_range(s.gpu_pages, a, b, ps)
+            slots += slots_for_range(r.pages, a, b, ps)
             cu.append(cu[-1] + (b - a))
             ctx_lens.append(a)
         dev = self.device
@@ -270,33 +362,33 @@ class Engine:
             ids += [0] * pad
             pos += [0] * pad
             slots += [-1] * pad
-        logit_rows = [c - 1 for c in cu[1:]]
+        group = [r.seq for r in rows if r.seq is not None]
+        logit_rows = [cu[i + 1] - 1 for i, r in enumerate(rows) if r.seq is not None]
+        has_state = self.kv.state is not None
         meta = AttnMeta(
             mode="prefill",
             positions=torch.tensor(pos, dtype=torch.int32, device=dev),
             slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
-            block_table=build_block_table([s.gpu_pages for s in group], dev),
+            block_table=build_block_table([r.pages for r in rows], dev),
             cu_seqlens=cu, ctx_lens=ctx_lens,
-            state_slots=(torch.tensor([s.state_slot for s in group], dtype=torch.int32, device=dev)
-                         if self.kv.state is not None else None),
+            state_slots=(torch.tensor([r.seq.state_slot if r.seq is not None else -1 for r in rows], dtype=torch.int32,
+                                      device=dev) if has_state else None),
             state_has_initial=(torch.tensor([int(c > 0) for c in ctx_lens], dtype=torch.int32, device=dev)
-                               if self.kv.state is not None else None),
+                               if has_state else None),
             logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),
             num_valid=torch.tensor([T], dtype=torch.int32, device=dev) if W > 1 else None)
         ids_t = torch.tensor(ids, dtype=torch.int32, device=dev)
+        self.stats.prefill_tokens += T
         if W > 1:
             logits = self.model.forward_sp(ids_t, meta, self.kv)      # wanted rows that this rank owns
-            toks = self._sample_sharded(logits, group, logit_rows, T + pad)
+            toks = self._sample_sharded(logits, group, logit_rows, T + pad) if group else []
         else:
             logits = self.model.forward(ids_t, meta, self.kv)
-            toks = self._sample(logits, group).tolist()
+            toks = self._sample(logits, group).tolist() if group else []
         for s, t in zip(group, toks):
-            full_len = len(s.all_ids if s.reentry_decoded_baseline else s.prompt_ids)
-            self.stats.prefill_tokens += full_len - s.num_cached_tokens
             self.stats.prefill_cached_tokens += s.cached_prefix_tokens
-            s.num_cached_tokens = full_len
+            s.num_cached_tokens = len(self._prefill_ids(s))
             s.output_ids.append(int(t))
-            s.reentry_decoded_baseline = 0
 
     # ------------------------------------------------------------------ sampling
     @staticmethod

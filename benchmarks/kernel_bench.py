@@ -39,15 +39,50 @@ def peaks():
     return 6650.0, 1590.0, "of fallback"
 
 
+_CLOCK = {}
+
+
+def sm_clock_mhz():
+    """Current SM clock of device 0 (read through NVML; reading changes nothing), or None."""
+    try:
+        import pynvml
+        if "h" not in _CLOCK:
+            pynvml.nvmlInit()
+            _CLOCK["h"] = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        return int(pynvml.nvmlDeviceGetClockInfo(_CLOCK["h"], pynvml.NVML_CLOCK_SM))
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def spin_up(seconds=0.4):
+    """Keep the GPU busy for a while before a short kernel is timed: an idle B200 sits at a few hundred MHz and takes
+    tens of milliseconds to raise its clocks, so a microsecond-scale kernel timed cold runs at a fraction of the
+    clock it sees inside a real step."""
+    a = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    e = torch.cuda.Event(enable_timing=True)
+    s0 = torch.cuda.Event(enable_timing=True)
+    s0.record()
+    while True:
+        for _ in range(20):
+            a @ a
+        e.record()
+        e.synchronize()
+        if s0.elapsed_time(e) >= seconds * 1e3:
+            break
+
+
 def timeit(fn, iters, warmup=3):
     for _ in range(warmup):
         fn()
+    spin_up()
+    fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
         fn()
     e1.record()
+    _CLOCK["mhz"] = sm_clock_mhz()          # sampled while the timed launches are still running or just done
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
 
@@ -235,6 +270,7 @@ def main():
     else:
         raise SystemExit(f"unknown case {a.case}")
     _ext.check_status()
+    out["sm_mhz_at_timing"] = _CLOCK.get("mhz")
     print(json.dumps(out))
 
 
