@@ -44,6 +44,16 @@ def _scales_kb_major(xs: torch.Tensor):
 
 
 _WIDE = os.environ.get("BG_GEMM_WIDE", "auto")       # "0": always 128x128 tiles, "1": 128x256 whenever allowed
+_SWAPAB = os.environ.get("BG_GEMM_SWAPAB", "auto")   # "0": never, "1": whenever allowed; auto: few rows per weight matrix
+SWAPAB_MAX_ROWS = 32                                 # rows per weight matrix (on average) up to which weights go on the M side
+
+
+def use_swapab(rows_per_matrix: float, N: int, K: int) -> bool:
+    """The swapped-operand kernel (weights on the MMA M side, 32-token tiles) is the weight-streaming kernel of
+    decode-sized steps: it wins while a weight matrix sees about one token tile."""
+    if _SWAPAB == "0" or N % 128 or K % 128 or K // 128 > 160:
+        return False
+    return _SWAPAB == "1" or rows_per_matrix <= SWAPAB_MAX_ROWS
 
 
 _hooks_pending = False     # set by the fused-communication layer right before a GEMM that consumes collective hooks
@@ -73,10 +83,23 @@ def wide_enabled() -> bool:
     return _WIDE != "0"
 
 
-def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None, a_ready=None):
+def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None, a_ready=None,
+            swapab=False):
     """``a_ready`` = (flag pointer, epoch, epoch-base pointer, world): the rows of A are pushed by peers and the
-    128 x 256 kernel's producer waits for every rank's arrival flag (only that kernel takes it this way)."""
+    128 x 256 kernel's producer waits for every rank's arrival flag (only that kernel and the swapped-operand kernel
+    take it this way)."""
     L = _ext.lib()
+    if swapab and kind == KIND_FP8 and epi != EPI_STORE_F32:
+        global _hooks_pending
+        assert not _hooks_pending, "collective hooks belong to the 128 x 128 kernel"
+        flag, epoch, base, world = a_ready if a_ready is not None else (ctypes.c_void_p(0), 0, ctypes.c_void_p(0), 1)
+        rc = L.bg_gemm_fp8_swapab(ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride), _ext.ptr(B),
+                                  _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets), _ext.ptr(counts),
+                                  ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                                  ctypes.c_int(_ext.num_sms(A.device)), flag, ctypes.c_uint32(epoch),
+                                  base, ctypes.c_int(world), _ext.ptr(_ext.status_word(A.device)), _ext.stream())
+        _ext.check(rc, "bg_gemm_fp8_swapab")
+        return
     if a_ready is not None or _use_wide(kind, D, M, N, wide):
         flag, epoch, base, world = a_ready if a_ready is not None else (ctypes.c_void_p(0), 0, ctypes.c_void_p(0), 1)
         rc = L.bg_gemm_fp8_n256(ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride), _ext.ptr(B),
@@ -96,7 +119,8 @@ def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wid
 
 
 def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
-             out: Optional[torch.Tensor] = None, silu_mul: bool = False, wide: Optional[bool] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, silu_mul: bool = False, wide: Optional[bool] = None,
+             swapab: Optional[bool] = None) -> torch.Tensor:
     """[T, K] e4m3 x [N, K] e4m3 -> [T, N] (bf16 on GPU).  With ``silu_mul`` the weight must be in
     the interleaved gate/up layout and the result has N/2 columns."""
     T, K = xq.shape
@@ -113,18 +137,22 @@ def fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     if T == 0:
         return out
     s, stride = _scales_kb_major(xs)
-    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq, ws, out, None, 1, T, N, K, wide=wide)
+    if swapab is None:
+        swapab = (not _hooks_pending) and wide is None and use_swapab(T / 2, N, K)     # up to two 32-token tiles
+    _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq, ws, out, None, 1, T, N, K, wide=wide,
+            swapab=swapab)
     return out
 
 
 def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
                      offsets: torch.Tensor, out: Optional[torch.Tensor] = None,
                      silu_mul: bool = False, counts: Optional[torch.Tensor] = None,
-                     wide: Optional[bool] = None, a_ready=None) -> torch.Tensor:
+                     wide: Optional[bool] = None, a_ready=None, rows_hint: Optional[int] = None) -> torch.Tensor:
     """Ragged grouped GEMM.  xq: [R, K] rows grouped by expert, segment e = offsets[e]:offsets[e+1]
     (int32 on device, every start a multiple of 128 on the GPU path); wq: [E, N, K].  ``counts`` (int32 [E],
     device) gives the rows really present in each segment: padding rows are then neither stored nor, as
-    whole tiles, computed (their output rows stay undefined)."""
+    whole tiles, computed (their output rows stay undefined).  ``rows_hint``: rows the caller expects to be really
+    present in total (the padded row count R says little); few rows per expert select the swapped-operand kernel."""
     E, N, K = wq.shape
     R = xq.shape[0]
     if not xq.is_cuda:
@@ -142,8 +170,9 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
     assert offsets.dtype == torch.int32 and offsets.is_cuda
     if counts is not None:
         assert counts.dtype == torch.int32 and counts.is_cuda and counts.numel() >= E
+    swapab = (not _hooks_pending) and wide is None and rows_hint is not None and use_swapab(rows_hint / max(E, 1), N, K)
     _launch(KIND_FP8, EPI_SILU_MUL if silu_mul else EPI_STORE, xq, s, stride, wq.view(E * N, K), ws, out,
-            offsets, E, R, N, K, wide=wide, counts=counts, a_ready=a_ready)
+            offsets, E, R, N, K, wide=wide, counts=counts, a_ready=a_ready, swapab=swapab)
     return out
 
 

@@ -177,7 +177,8 @@ def _activation(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
 
 
 def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None,
-                    timer=None, counts: Optional[torch.Tensor] = None, row_src: Optional[torch.Tensor] = None):
+                    timer=None, counts: Optional[torch.Tensor] = None, row_src: Optional[torch.Tensor] = None,
+                    rows_hint: Optional[int] = None):
     """Run gate/up -> activation -> down for rows already grouped by expert.  fp8 path takes
     (xq, xs); the unquantised path takes ``x_dense``.  Returns y [rows, Hout].  With ``counts`` (real rows
     per segment) and ``row_src`` (negative on padding rows) the padding rows are skipped end to end."""
@@ -188,11 +189,12 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         if xq.is_cuda:
             assert ew.interleaved, "call ExpertWeights.to_device_layout() after loading"
             with timer.timed("moe.s1_gemm"):
-                act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True, counts=counts)
+                act = gemm.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets, silu_mul=True, counts=counts,
+                                            rows_hint=rows_hint)
             with timer.timed("moe.act_quant"):
                 aq, as_ = fused.act_quant(act, valid_rows=offsets[-1:], row_src=row_src)
             with timer.timed("moe.s3_gemm"):
-                return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets, counts=counts)
+                return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets, counts=counts, rows_hint=rows_hint)
         gu = ref.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets)
         act = _activation(gu, ew.activation)
         aq, as_ = ref.act_quant(act)
@@ -240,7 +242,8 @@ def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.
         with timer.timed("moe.gather_quant"):
             xq, xs = gather_quant(hidden, src, offsets, zero_padding=counts is None)
         y = grouped_experts(xq, xs, offsets, ew, timer=timer, counts=counts,
-                            row_src=src if counts is not None else None)
+                            row_src=src if counts is not None else None,
+                            rows_hint=(hidden.shape[0] * topk_idx.shape[1] if counts is not None else None))
     else:
         rows = hidden[src.clamp_min(0).long()]
         rows = torch.where((src >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))

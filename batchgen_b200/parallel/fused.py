@@ -322,8 +322,15 @@ class FusedComm(NcclComm):
             with timer.timed("moe.dispatch_wait"):
                 _ext.check(L.bg_wait_flags(self._flag_ptr(DISP_READY), ctypes.c_int(W), ctypes.c_uint32(e_disp),
                                            self._base(), self._status(), st), "bg_wait_flags")
+        # decode-sized steps (about one 32-token tile per expert): weights on the MMA's M side
+        small = gemm_ops.use_swapab(Tl * K / max(E // W, 1), ew.w13.shape[1], ew.w13.shape[2]) and \
+            ew.w2.shape[1] % 128 == 0 and ew.w2.shape[2] % 128 == 0
         with timer.timed("moe.s1_gemm"):
-            if gemm_ops.wide_enabled() and Tl * K >= WIDE_S1_MIN_ROWS:
+            if small:
+                act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
+                                                counts=self.recv_counts, rows_hint=Tl * K,
+                                                a_ready=(self._flag_ptr(DISP_READY), e_disp, self._base(), W))
+            elif gemm_ops.wide_enabled() and Tl * K >= WIDE_S1_MIN_ROWS:
                 # prefill-sized steps: 128 x 256 tiles (less operand traffic per FLOP); its producer waits for
                 # the arrival flags itself
                 act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
@@ -339,7 +346,17 @@ class FusedComm(NcclComm):
         with timer.timed("moe.s3_gemm_return"):
             e_ret = self._next(RET_READY)
             El, Hout, I = ew.w2.shape
-            if gemm_ops.wide_enabled() and Tl * K <= WIDE_S3_MAX_ROWS and Hout % 8 == 0 and I % 128 == 0:
+            if small:
+                sc, sc_stride = gemm_ops._scales_kb_major(as_)
+                rc = L.bg_gemm_fp8_swapab_return(
+                    _ext.ptr(aq), _ext.ptr(sc), ctypes.c_int(sc_stride), _ext.ptr(ew.w2), _ext.ptr(ew.w2_s),
+                    ctypes.c_int(Hout), _ext.ptr(self.offsets), _ext.ptr(self.recv_counts), ctypes.c_int(El),
+                    ctypes.c_int(self.recv_cap), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
+                    self.heap.peer_ptrs("ret"), _ext.ptr(self.recv_info), self.flag_ptrs, ctypes.c_int(RET_READY),
+                    ctypes.c_uint32(e_ret), self._base(), _ext.ptr(self.counters[3:4]), ctypes.c_int(self.rank),
+                    ctypes.c_int(W), self._status(), st)
+                _ext.check(rc, "bg_gemm_fp8_swapab_return")
+            elif gemm_ops.wide_enabled() and Tl * K <= WIDE_S3_MAX_ROWS and Hout % 8 == 0 and I % 128 == 0:
                 # decode-sized steps: 128 x 256 tiles stream the weights faster; rows leave with plain 16-byte stores
                 sc, sc_stride = gemm_ops._scales_kb_major(as_)
                 rc = L.bg_gemm_fp8_n256_return(

@@ -96,7 +96,7 @@ def run_bct(eng, cfg, args, rank, world, barrier):
             "evictions": st["evictions"], "api": "runtime.batch_api.run_batch on Engine"}
 
 
-def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist):
+def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist, n_layers=None):
     """Largest relative difference between one decode step over the fused kernels and the same step over NCCL
     collectives, on the same weights and inputs.  The baseline model shares every tensor with the fused one; only
     the tensors the sequence-parallel layout replicates are cut to their tensor-parallel shard.  Both runs use the
@@ -115,7 +115,7 @@ def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world,
     meta = AttnMeta(mode="decode", positions=d_pos, slot_mapping=d_slot, block_table=d_bt, seqlens=d_len)
     rp = model.attn_request_parallel
     model.attn_request_parallel = False
-    n_layers = min(len(model.w.layers), model.cfg.first_k_dense + 2)
+    n_layers = min(len(model.w.layers), n_layers or (model.cfg.first_k_dense + 2))
     all_layers = model.w.layers
     model.w.layers = all_layers[:n_layers]
     try:
@@ -161,6 +161,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="deepseek-v3-671b")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="debug only: fewer routed experts, e.g. 64 on 2 GPUs gives each rank the 32 experts it holds on "
+                         "8 (result marked invalid)")
     ap.add_argument("--batch", type=int, default=384, help="decode rows of the whole job")
     ap.add_argument("--prefill-tokens", type=int, default=8192)
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
@@ -213,6 +216,10 @@ def main() -> int:
     cfg = get_model_config(args.model)
     if args.layers:
         cfg.num_layers = args.layers
+    if args.experts:
+        cfg.n_routed_experts = args.experts
+        cfg.n_group = min(cfg.n_group, max(1, args.experts // 8))
+        cfg.topk_group = min(cfg.topk_group, cfg.n_group)
     page = 64
     rng = random.Random(1234)
     B = args.batch
@@ -376,6 +383,11 @@ def main() -> int:
         torch.cuda.synchronize()
         dsum = model.timer.summary()
         model.timer = TimingStats()
+        if rank == 0:
+            with open(args.profile_ops, "w") as f:
+                f.write("== decode step: ms per step by operator (CUDA events, eager) ==\n")
+                for op, d in dsum.items():
+                    f.write(f"{op:32s} {d['ms_per_step']:10.3f} ms  {d['share'] * 100:5.1f}%  calls {d['calls']}\n")
     else:
         dsum = None
 
@@ -384,7 +396,9 @@ def main() -> int:
         # one eager decode step over the fused kernels against the same step over the NCCL baseline: the fused
         # model's weights are reused (attention shards are the same; the shared experts and lm_head, replicated in
         # the sequence-parallel layout, are sliced to their tensor-parallel shard for the baseline run)
-        comm_check = compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist)
+        # dense layers only (no routing: pure rounding noise of the two data paths), then with one and two MoE layers
+        comm_check = {f"layers_{n}": compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist, n)
+                      for n in (cfg.first_k_dense, cfg.first_k_dense + 1, cfg.first_k_dense + 2)}
 
     e2e = None
     if not args.no_e2e:
@@ -439,11 +453,10 @@ def main() -> int:
             from batchgen_b200.utils.timing import null_timer
             model.timer = null_timer()
         if args.profile_ops and rank == 0:
-            with open(args.profile_ops, "w") as f:
-                for title, sm in (("decode step", dsum), ("prefill micro-batch", psum)):
-                    f.write(f"== {title}: ms per step by operator (CUDA events, eager) ==\n")
-                    for op, d in sm.items():
-                        f.write(f"{op:32s} {d['ms_per_step']:10.3f} ms  {d['share'] * 100:5.1f}%  calls {d['calls']}\n")
+            with open(args.profile_ops, "a") as f:
+                f.write("== prefill micro-batch: ms per step by operator (CUDA events, eager) ==\n")
+                for op, d in psum.items():
+                    f.write(f"{op:32s} {d['ms_per_step']:10.3f} ms  {d['share'] * 100:5.1f}%  calls {d['calls']}\n")
         ms_p = timed(prefill_step, 2) / 2
         _ext.check_status()
         prefill = {"tokens_per_s": T * 1000.0 / ms_p, "ms_per_microbatch": ms_p, "tokens": T, "seq_len": L}
@@ -472,7 +485,7 @@ def main() -> int:
                        "comm": ("fused-nvlink-kernels" if fused else "nccl") if world > 1 else "none",
                        "distinct_expert_sets": sets, "moe_layers": n_moe, "cuda_graph": runner is not None,
                        "l2_note": "inputs (weights + KV, tens of GB per step) exceed the 126 MB L2",
-                       "valid": not args.layers, "build_seconds": round(build_s, 1)},
+                       "valid": not (args.layers or args.experts), "build_seconds": round(build_s, 1)},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "prefill": prefill,
             "bct_projected_s": bct_proj, "bct": bct, "comm_check": comm_check,
         }

@@ -192,8 +192,9 @@ def main():
         xs = torch.rand(K // 128, E * pad, device=dev).t()
         wq = torch.randn(E, N, K, device=dev).to(torch.float8_e4m3fn)
         ws = torch.rand(E, N // 128, K // 128, device=dev)
-        ms = timeit(lambda: gemm.grouped_fp8_gemm(xq, xs, wq, ws, offs), a.iters)
-        byts = E * N * K + E * pad * K + E * pad * N * 2
+        cnt = torch.full((E,), R, dtype=torch.int32, device=dev)          # real rows per expert; the rest is padding
+        ms = timeit(lambda: gemm.grouped_fp8_gemm(xq, xs, wq, ws, offs, counts=cnt, rows_hint=E * R), a.iters)
+        byts = E * N * K + E * R * K + E * R * N * 2
         out.update(shape=[E, R, N, K], ms=ms, gbs=byts / ms / 1e6, frac_of_hbm=byts / ms / 1e6 / hbm,
                    tflops=2.0 * E * pad * N * K / ms / 1e9, peak_note=tag)
     elif a.case in ("mla_decode", "mla_prefill"):
