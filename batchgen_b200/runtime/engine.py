@@ -548,18 +548,27 @@ class Engine:
             layout += b + [None] * (per - len(b))
         return layout
 
-    def _decode_step(self, rows: List[Sequence]) -> None:
+    def _step_layout(self, rows: List[Sequence]):
+        """(layout, positions, KV slots, lengths) of one decode step over ``rows``; ``None`` layout entries are
+        padding rows."""
         ps = self.buf.page_size
-        dev = self.device
         W = self.sp_world
         split = self.model.attn_request_parallel and self.model.layout.tp_size > 1
         layout: List[Optional[Sequence]] = self._owner_layout(rows) if split else list(rows)
         if W > 1 and self.graph_runner is None and len(layout) % W:
             layout += [None] * ((-len(layout)) % W)      # fused path: whole rows-per-rank blocks
-        ids = [s.all_ids[s.num_cached_tokens] if s is not None else 0 for s in layout]
         pos = [s.num_cached_tokens if s is not None else 0 for s in layout]
         slots = [s.gpu_pages[p // ps] * ps + p % ps if s is not None else -1 for s, p in zip(layout, pos)]
         lens = [p + 1 if s is not None else 0 for s, p in zip(layout, pos)]
+        return layout, pos, slots, lens
+
+    def _decode_step(self, rows: List[Sequence]) -> None:
+        """One synchronous decode step (the path without captured graphs)."""
+        dev = self.device
+        W = self.sp_world
+        split = self.model.attn_request_parallel and self.model.layout.tp_size > 1
+        layout, pos, slots, lens = self._step_layout(rows)
+        ids = [s.all_ids[s.num_cached_tokens] if s is not None else 0 for s in layout]
         if self.graph_runner is not None:
             logits, bucket = self.graph_runner.decode(self, layout, ids, pos, slots, lens)
             if W > 1:
@@ -597,6 +606,58 @@ class Engine:
         self.stats.decode_tokens += n
         self.stats.decode_steps += 1
 
+    # -------- deferred read-back: the host sees a step's tokens while the next step already runs
+    def _launch_decode(self, rows: List[Sequence], feed_key) -> dict:
+        """Enqueue one captured decode step and the device-side sampling without waiting for the result.  When the
+        step's layout equals ``feed_key`` (the layout of the step launched just before), its input tokens are the
+        ones that step sampled, taken on the device; otherwise they come from the host.  The reference keeps the same
+        one-step lag (batchgen/worker/deferred_readback.py:57)."""
+        runner = self.graph_runner
+        W = self.sp_world
+        layout, pos, slots, lens = self._step_layout(rows)
+        key = tuple(s.global_idx if s is not None else -1 for s in layout)
+        ids = None if key == feed_key else [s.all_ids[s.num_cached_tokens] if s is not None else 0 for s in layout]
+        logits, bucket = runner.decode(self, layout, ids, pos, slots, lens)
+        n = len(layout)
+        if W > 1:
+            import torch.distributed as dist
+            comm = self.model.comm
+            full = layout + [None] * (bucket - n)
+            Tl = bucket // W
+            mine = full[comm.rank * Tl:(comm.rank + 1) * Tl]
+            uniform = None
+            if not all(self._greedy_row(s) for s in full):
+                u_all = torch.rand(bucket, device=self.device, generator=self._gen)   # the same numbers on every rank
+                uniform = u_all[comm.rank * Tl:(comm.rank + 1) * Tl]
+            tl = runner._tok_local[:Tl]
+            self._sample(logits[:Tl], mine, resident=True, uniform=uniform, out=tl)
+            dist.all_gather_into_tensor(runner.tokens[:bucket], tl, group=getattr(comm, "group", None))
+        else:
+            self._sample(logits, layout, resident=True, out=runner.tokens[:n])
+        handle = runner.start_readback(n)
+        for s in layout:
+            if s is not None:
+                s.num_cached_tokens += 1
+                s.inflight_tokens += 1
+        self.stats.decode_steps += 1
+        return dict(layout=layout, key=key, handle=handle, rows=[s.global_idx for s in rows])
+
+    def _retire_decode(self, pending: dict) -> None:
+        """Bring a launched step's tokens to the host and append them to their rows.  A row that had already ended
+        when the step was launched (its end-of-sequence token became visible one step late) drops the extra token."""
+        toks = self.graph_runner.read(pending["handle"]).tolist()
+        eos = self.cfg.eos_token_id
+        n = 0
+        for s, t in zip(pending["layout"], toks):
+            if s is None:
+                continue
+            s.inflight_tokens -= 1
+            if s.inflight_tokens == 0 and s.is_finished(eos):
+                continue
+            s.output_ids.append(int(t))
+            n += 1
+        self.stats.decode_tokens += n
+
     def _decode_interval(self, max_steps: Optional[int] = None) -> int:
         """Admit rows, decode up to one decision interval, then apply the boundary decisions.
         Returns the number of decode steps executed."""
@@ -613,17 +674,40 @@ class Engine:
         t0 = time.perf_counter()
         steps = 0
         eos = self.cfg.eos_token_id
-        for _ in range(min(self.buf.decision_interval, max_steps or self.buf.decision_interval)):
-            live = [s for s in rows if not s.is_finished(eos)]
+        limit = min(self.buf.decision_interval, max_steps or self.buf.decision_interval)
+        deferred = self.graph_runner is not None and self.ecfg.deferred_readback
+        pending: Optional[dict] = None
+
+        def launchable(s: Sequence) -> bool:
+            return (not s.is_finished(eos)
+                    and s.num_decoded + s.inflight_tokens < s.params.max_new_tokens)
+
+        for _ in range(limit):
+            live = [s for s in rows if launchable(s)]
             if not live:
                 break
             # a row about to cross into a page it does not own ends the interval early
             if any(pages_for(s.num_cached_tokens + 1, self.buf.page_size) > len(s.gpu_pages) for s in live):
                 break
-            self._decode_step(live)
+            if not deferred:
+                self._decode_step(live)
+            else:
+                if pending is not None and pending["rows"] != [s.global_idx for s in live]:
+                    # the batch changes: its input tokens come from the host, so the step in flight lands first
+                    self._retire_decode(pending)
+                    pending = None
+                    live = [s for s in live if launchable(s)]
+                    if not live:
+                        break
+                nxt = self._launch_decode(live, pending["key"] if pending is not None else None)
+                if pending is not None:
+                    self._retire_decode(pending)
+                pending = nxt
             steps += 1
             if self.step_hook is not None:
                 self.step_hook("decode")
+        if pending is not None:
+            self._retire_decode(pending)
         self._sync()
         self.stats.decode_seconds += time.perf_counter() - t0
         self._apply_boundary()
@@ -720,7 +804,9 @@ class Engine:
                 raise RuntimeError("engine did not converge")
         return sorted(self.seqs.values(), key=lambda s: s.global_idx)
 
-    def generate(self, prompts: Seq[Seq[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
-        seqs = [self.add_request(p, params) for p in prompts]
+    def generate(self, prompts: Seq[Seq[int]], params=None) -> List[List[int]]:
+        """Token ids generated for every prompt; ``params`` is one ``SamplingParams`` for all or one per prompt."""
+        per = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        seqs = [self.add_request(p, q) for p, q in zip(prompts, per)]
         self.run_to_completion()
         return [s.output_ids for s in seqs]

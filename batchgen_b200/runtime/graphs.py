@@ -109,6 +109,7 @@ class DecodeGraphRunner:
         self._ring = [torch.zeros(B, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._ring_ev = [torch.cuda.Event() if pin else None for _ in range(2)]
         self._ring_n = [0, 0]
+        self._stage_ev = torch.cuda.Event() if pin else None
         self._ring_next = 0
         self._row_key = None
         self._scratch_reserved = False
@@ -196,6 +197,8 @@ class DecodeGraphRunner:
         not copied at all (page lists change only at page boundaries)."""
         n = len(pos)
         b = self.bucketing.bucket_for(n)
+        if self._stage_ev is not None:
+            self._stage_ev.synchronize()            # the copies of the step staged before have left the pinned buffers
         if self.state_slots is not None:
             self.h_state[:b] = -1
             if state_slots is not None:
@@ -242,6 +245,8 @@ class DecodeGraphRunner:
         if bt_rows:
             self.bt[:n].copy_(self.h_bt[:n], non_blocking=nb)
         self.num_valid.copy_(self.h_nv, non_blocking=nb)
+        if self._stage_ev is not None:
+            self._stage_ev.record()
         self.h2d_bytes_per_step = (b * (4 + 8 + 4) + (b * 4 if ids is not None else 0)
                                    + (n * self.max_pages * 4 if bt_rows else 0) + 4)
         return b
@@ -275,16 +280,22 @@ class DecodeGraphRunner:
             dist.all_gather_into_tensor(self.tokens[:b], tl)
         else:
             (sampler or sampling_ops.greedy)(logits, self.tokens[:n])
+        return self.start_readback(n)
+
+    def start_readback(self, n: int) -> int:
+        """Start the device -> host copy of the first ``n`` sampled tokens into the next pinned ring slot."""
         slot = self._ring_next
         self._ring_next ^= 1
         self._ring[slot][:n].copy_(self.tokens[:n], non_blocking=True)
-        self._ring_ev[slot].record()
+        if self._ring_ev[slot] is not None:
+            self._ring_ev[slot].record()
         self._ring_n[slot] = n
         return slot
 
     def read(self, handle: int) -> torch.Tensor:
         """Tokens of the step that returned ``handle`` (blocks until its copy has landed)."""
-        self._ring_ev[handle].synchronize()
+        if self._ring_ev[handle] is not None:
+            self._ring_ev[handle].synchronize()
         return self._ring[handle][: self._ring_n[handle]]
 
     def decode(self, engine, rows, ids, pos, slots, lens):

@@ -54,10 +54,16 @@ def sm_clock_mhz():
         return None
 
 
-def spin_up(seconds=0.4):
+SPIN_SECONDS = 0.4
+
+
+def spin_up(seconds=None):
     """Keep the GPU busy for a while before a short kernel is timed: an idle B200 sits at a few hundred MHz and takes
     tens of milliseconds to raise its clocks, so a microsecond-scale kernel timed cold runs at a fraction of the
     clock it sees inside a real step."""
+    seconds = SPIN_SECONDS if seconds is None else seconds
+    if seconds <= 0:
+        return
     a = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
     e = torch.cuda.Event(enable_timing=True)
     s0 = torch.cuda.Event(enable_timing=True)
@@ -152,9 +158,12 @@ def main():
     ap.add_argument("--batch", type=int, default=96)
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--spin", type=float, default=0.4, help="seconds of GEMM load before timing (0 under a profiler)")
     ap.add_argument("--impl", default="ours", choices=["ours", "flashinfer", "torch", "vllm"])
     ap.add_argument("--check", action="store_true", help="also compare the library result with this repository's")
     a = ap.parse_args()
+    global SPIN_SECONDS
+    SPIN_SECONDS = a.spin
     dev = "cuda"
     hbm, tf, tag = peaks()
     out = {"case": a.case}

@@ -44,6 +44,30 @@ def test_graph_decode_equals_eager_and_engine_tokens_match():
     assert eng.graph_runner.ledger.total >= 0
 
 
+def test_deferred_readback_gives_the_same_tokens_and_stops():
+    """Rows of different lengths, one of them ended by its end-of-sequence token: the engine that reads a step's
+    tokens one step late returns exactly what the synchronous engine returns."""
+    cfg = _cfg()
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 90, 65, 120)]
+    free = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    probe = Engine(build_model(cfg, "cuda", "bf16", seed=0), EngineConfig(page_size=64), num_gpu_pages=256)
+    first = probe.generate(prompts, free)
+    cfg.eos_token_id = first[1][4]               # row 1 stops after its fifth token
+    plist = [SamplingParams(max_new_tokens=n) for n in (12, 12, 7, 3)]
+    outs = []
+    for deferred in (False, True):
+        model = build_model(cfg, "cuda", "bf16", seed=0)
+        eng = Engine(model, EngineConfig(page_size=64, deferred_readback=deferred), num_gpu_pages=256)
+        eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=8, max_pages_per_seq=64, num_buckets=3)
+        outs.append(eng.generate(prompts, plist))
+        torch.cuda.synchronize()
+        assert all(s.inflight_tokens == 0 for s in eng.seqs.values())
+    assert outs[0] == outs[1]
+    assert outs[1][1][-1] == cfg.eos_token_id and len(outs[1][1]) <= 5
+    assert [len(o) for o in outs[1]][2:] == [7, 3]
+
+
 def test_buckets():
     b = generate_buckets(128, 16)
     assert b[-1] == 128 and b[0] >= 1 and b == sorted(set(b))
