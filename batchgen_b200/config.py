@@ -400,6 +400,7 @@ class EngineConfig:
     expert_offload_ratio: float = 0.0           # fraction of local experts kept in host DRAM
     weight_ring_slots: int = 4
     seed: int = 0
+    host_kv_backend: str = "native"       # "native": node-shared region + asynchronous movers (GPU); "torch": pinned tensor
     deferred_readback: bool = True      # with captured decode graphs: read a step's tokens while the next one runs
     device: str = "cpu"
     dtype: str = "fp32"                         # fp32 (CPU oracle) | bf16 (GPU)

@@ -61,7 +61,8 @@ class KVMover {
   }
   bool ok() const { return ok_; }
 
-  // Returns a task id >= 0, -1 if the request is too large, -2 if every ring entry is still in flight.
+  // Returns a task id >= 0, -1 if the request is too large.  With every ring entry still in flight the call waits
+  // for the oldest transfer (counted in ring_waits) and reuses its entry; -2 if that wait fails.
   long submit(const void* const* src, void* const* dst, int n, size_t bytes, int use_kernel, void* after_stream) {
     if (!ok_ || n > cap_) return -1;
     std::lock_guard<std::mutex> lk(mu_);
@@ -71,7 +72,12 @@ class KVMover {
       if (busy_[c] && cudaEventQuery(events_[c]) != cudaErrorNotReady) busy_[c] = 0;
       if (!busy_[c]) { slot = c; break; }
     }
-    if (slot < 0) return -2;
+    if (slot < 0) {                  // every entry in flight: the oldest one (transfers run in order) is reused
+      slot = next_;
+      if (cudaEventSynchronize(events_[slot]) != cudaSuccess) return -2;
+      busy_[slot] = 0;
+      ring_waits_ += 1;
+    }
     next_ = (slot + 1) % ring_;
     cudaError_t err = cudaSetDevice(device_);
     auto note = [&err](cudaError_t e) { if (err == cudaSuccess && e != cudaSuccess) err = e; };
@@ -139,7 +145,7 @@ class KVMover {
   std::vector<char> busy_;
   int next_ = 0;
   std::mutex mu_;
-  uint64_t bytes_moved_ = 0, tasks_ = 0, fallbacks_ = 0;
+  uint64_t bytes_moved_ = 0, tasks_ = 0, fallbacks_ = 0, ring_waits_ = 0;
 };
 
 }  // namespace bgcore

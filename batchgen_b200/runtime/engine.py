@@ -68,6 +68,9 @@ class EngineStats:
     offloaded_pages: int = 0
     shared_prefix_tokens: int = 0      # prompt tokens not computed because another prompt of the wave shares them
     trajectory_commits: int = 0        # completed rows whose prompt + output pages were left in the prefix cache
+    growth_evictions: int = 0          # parked rows evicted to make host-tier room for a row that had to be parked
+    transfer_waits: int = 0            # times the host blocked on a page transfer (pool exhausted with copies in flight)
+    prefix_promoted_pages: int = 0     # prefix pages brought back from the host tier's coordinator
 
     def summary(self) -> Dict[str, float]:
         return dict(
@@ -79,7 +82,7 @@ class EngineStats:
 class Engine:
     def __init__(self, model: Transformer, ecfg: EngineConfig, num_gpu_pages: Optional[int] = None,
                  num_host_pages: int = 0, on_complete: Optional[Callable[[Sequence], None]] = None,
-                 graph_runner=None):
+                 graph_runner=None, host_kv_fd: Optional[int] = None):
         ecfg.validate()
         self.model, self.cfg, self.ecfg = model, model.cfg, ecfg
         self.device = model.device
@@ -98,8 +101,23 @@ class Engine:
                 raise ValueError("prefix reuse needs per-page state snapshots, which KDA layers do not keep")
         self.kv = PagedKVCache(self.cfg, n_pages, ecfg.page_size, self.device, kv_dtype, state_slots=state_slots,
                                state_heads=state_heads)
-        self.host_kv = (PagedKVCache(self.cfg, num_host_pages, ecfg.page_size, "cpu", kv_dtype, pinned=True)
-                        if num_host_pages else None)
+        # host tier: on a GPU the native region + asynchronous movers (a region created by the server is attached
+        # through ``host_kv_fd``); the pinned torch tensor is the CPU / fallback form of the same tier
+        self.host_tier = None
+        if (num_host_pages or host_kv_fd is not None) and self.device.type == "cuda" \
+                and ecfg.host_kv_backend == "native" and not self.cfg.has_kda:
+            from .host_tier import NativeHostTier
+            self.host_tier = NativeHostTier(self.kv, num_host_pages, fd=host_kv_fd)
+            self.host_kv = self.host_tier                  # same allocator face (``.alloc``)
+        else:
+            self.host_kv = (PagedKVCache(self.cfg, num_host_pages, ecfg.page_size, "cpu", kv_dtype, pinned=True)
+                            if num_host_pages else None)
+        from .continuous_batching import AdaptiveChunkSizer
+        # host-KV reservation chunk follows the decode lengths actually seen (EMA), from the configured start value
+        self.chunk_sizer = AdaptiveChunkSizer(initial_chunk=ecfg.host_kv_chunk_size,
+                                              min_chunk=min(1024, ecfg.host_kv_chunk_size))
+        self._deferred_gpu: List[tuple] = []               # (transfer tasks, device pages freed when they are done)
+        self._deferred_host: List[tuple] = []              # (transfer tasks, host pages released when they are done)
         self.host_state = None
         if self.kv.state is not None and self.host_kv is not None:
             self.host_state = HostStateStore(self.kv.state, ecfg.max_host_state_items or 4 * state_slots)
@@ -155,7 +173,7 @@ class Engine:
         s.num_cached_tokens = s.context_len - 1
         need = pages_for(s.context_len, self.buf.page_size)
         if gpu_pages is None:
-            gpu_pages = self.kv.alloc.alloc(need)
+            gpu_pages = self._take_pages(need)
         elif len(gpu_pages) < need:
             raise ValueError(f"{len(gpu_pages)} pages given, the context needs {need}")
         s.gpu_pages = list(gpu_pages)
@@ -175,16 +193,58 @@ class Engine:
         return [s for s in self.seqs.values() if s.status in st]
 
     def _free_pages(self) -> int:
-        return self.kv.alloc.num_free
+        """Device pages available to the scheduler: free ones plus those whose offload is still in flight (they are
+        free by the time anything is written to them, see ``_take_pages``).  Counting them makes the schedule
+        independent of transfer timing."""
+        if self._deferred_gpu or self._deferred_host:
+            self._drain_deferred()
+        return self.kv.alloc.num_free + sum(len(p) for _, p in self._deferred_gpu)
+
+    def _take_pages(self, n: int) -> List[int]:
+        """Allocate device pages; blocks on transfers in flight only when the free list alone cannot serve."""
+        if self._deferred_gpu and self.kv.alloc.num_free < n:
+            self._drain_deferred()
+            if self.kv.alloc.num_free < n:
+                self._drain_deferred(block=True)
+        return self.kv.alloc.alloc(n)
+
+    def _drain_deferred(self, block: bool = False) -> None:
+        """Pages that a transfer in flight still reads go back to their allocator once the transfer is done."""
+        if self.host_tier is None:
+            return
+        for queue, alloc in ((self._deferred_gpu, self.kv.alloc), (self._deferred_host, self.host_tier.alloc)):
+            keep = []
+            for tasks, pages in queue:
+                if block:
+                    self.host_tier.wait(tasks)
+                    self.stats.transfer_waits += 1
+                if block or self.host_tier.done(tasks):
+                    alloc.free(pages)
+                else:
+                    keep.append((tasks, pages))
+            queue[:] = keep
 
     def _sync(self) -> None:
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
 
     def _reclaim(self, want: int) -> int:
-        if self.prefix is None or want <= 0:
+        if want <= 0:
             return 0
-        return self.prefix.evict(want)
+        if self.prefix is None:
+            return 0
+        # demoted pages count as free at once (``_free_pages``); ``_take_pages`` waits for their copies if it must
+        return self.prefix.evict(want, on_evict=self._demote_prefix_page if self.host_tier else None)
+
+    def _demote_prefix_page(self, key: bytes, page: int) -> bool:
+        """A prefix page leaves the device cache: keep it in the host tier's coordinator.  Returns True when the
+        page's release was taken over (it is freed when the copy is done)."""
+        stream = torch.cuda.current_stream().cuda_stream
+        tasks = self.host_tier.demote(key, page, after_stream=stream)
+        if tasks is None:
+            return False
+        self._deferred_gpu.append((tasks, [page]))
+        return True
 
     def _release_state(self, s: Sequence) -> None:
         if s.state_slot >= 0:
@@ -196,6 +256,8 @@ class Engine:
 
     def _complete(self, s: Sequence, reason: str) -> None:
         s.finish_reason = reason
+        if not str(reason).startswith("error"):
+            self.chunk_sizer.report_completion(s.num_decoded)
         self._release_state(s)
         split = self.model.attn_request_parallel and self.model.layout.tp_size > 1    # decoded KV lives on the owner only
         if self.prefix is not None and s.gpu_pages and s.num_cached_tokens >= self.buf.page_size \
@@ -265,6 +327,38 @@ class Engine:
         self.stats.prefill_waves += 1
         return len(wave)
 
+    def _promote_from_host(self, ids: Seq[int], pages: List[int]) -> List[int]:
+        """Second level of the prefix cache: pages that continue the device hit ``pages`` and were demoted to the
+        host tier come back into device pages (asynchronous load, ordered before the prefill on the device) and
+        re-enter the device cache.  Returns the extended page list."""
+        from .prefix_cache import build_prefix_hash_chain
+        ps = self.buf.page_size
+        keys = build_prefix_hash_chain(ids[: max(len(ids) - 1, 0)], ps)
+        rest = keys[len(pages):]
+        if not rest:
+            return pages
+        host_pages = self.host_tier.lookup(rest)
+        if not host_pages:
+            return pages
+        n = len(host_pages)
+        if n > self._free_pages():
+            self._reclaim(n - self._free_pages())
+        n = min(n, self._free_pages())
+        if n == 0:
+            self.host_tier.alloc.free(host_pages)
+            return pages
+        new = self._take_pages(n)
+        cur = torch.cuda.current_stream().cuda_stream
+        tasks = self.host_tier.load(host_pages[:n], new, after_stream=cur)
+        self.host_tier.stream_wait(tasks, cur)
+        self._deferred_host.append((tasks, host_pages))           # the caller's references from the lookup
+        out = pages + new
+        self.prefix.commit(ids[: len(out) * ps], out)               # the device cache takes its own reference
+        self.kv.alloc.free(new)
+        self.host_tier.promoted_pages += n
+        self.stats.prefix_promoted_pages += n
+        return out
+
     @staticmethod
     def _prefill_ids(s: Sequence) -> List[int]:
         """Tokens a prefill recomputes: the prompt, plus the tokens decoded before an eviction."""
@@ -273,7 +367,7 @@ class Engine:
     def _alloc_pages(self, n: int) -> List[int]:
         if n > self._free_pages():
             self._reclaim(n - self._free_pages())
-        return self.kv.alloc.alloc(n)
+        return self._take_pages(n)
 
     def _prefill_wave_shared(self, wave: List[Sequence]) -> None:
         """Prefill a wave so that every prefix shared inside it is computed once (in-wave prefix pool), on top of
@@ -293,6 +387,8 @@ class Engine:
         hits = []
         for i, ids in enumerate(ids_of):
             pages, _ = self.prefix.lookup(ids)
+            if self.host_tier is not None:
+                pages = self._promote_from_host(ids, pages)
             if pages:
                 cached[i] = pages
                 hits.append(wave_plan.MaterializedPrefix(i, len(pages) * ps))
@@ -468,25 +564,36 @@ class Engine:
                 self._reclaim(need - self._free_pages())
             if need > self._free_pages():
                 return False
-            s.gpu_pages = self.kv.alloc.alloc(need)
-            self.kv.copy_pages_from(self.host_kv, s.host_pages, s.gpu_pages[: len(s.host_pages)], self.copy_stream)
+            s.gpu_pages = self._take_pages(need)
+            if self.host_tier is not None:
+                # asynchronous load: the compute stream waits on the device, the host goes on; the host pages are
+                # released when the copy is done
+                cur = torch.cuda.current_stream().cuda_stream   # after the kernels that may still read these pages
+                tasks = self.host_tier.load(s.host_pages, s.gpu_pages[: len(s.host_pages)], after_stream=cur)
+                self.host_tier.stream_wait(tasks, cur)
+                self._deferred_host.append((tasks, s.host_pages))
+                s.host_pages = []
+                self.stats.loads += 1
+            else:
+                self.kv.copy_pages_from(self.host_kv, s.host_pages, s.gpu_pages[: len(s.host_pages)], self.copy_stream)
             if s.state_item >= 0:
                 s.state_slot = self.kv.state.acquire()
                 self.host_state.load(self.kv.state, s.state_item, s.state_slot, self.copy_stream)
                 self.host_state.release(s.state_item)
                 s.state_item = -1
-            if self.copy_stream is not None:
-                torch.cuda.current_stream().wait_stream(self.copy_stream)
-            self.host_kv.alloc.free(s.host_pages)
-            s.host_pages = []
-            self.stats.loads += 1
+            if s.host_pages:
+                if self.copy_stream is not None:
+                    torch.cuda.current_stream().wait_stream(self.copy_stream)
+                self.host_kv.alloc.free(s.host_pages)
+                s.host_pages = []
+                self.stats.loads += 1
         extra = want - len(s.gpu_pages)
         if extra > 0:
             if extra > self._free_pages():
                 self._reclaim(extra - self._free_pages())
             if extra > self._free_pages():
                 return False
-            s.gpu_pages += self.kv.alloc.alloc(extra)
+            s.gpu_pages += self._take_pages(extra)
         s.had_initial_gpu_reservation = True
         s.transition(S.IN_DECODE)
         return True
@@ -494,7 +601,22 @@ class Engine:
     def _hold(self, s: Sequence) -> None:
         """Take a row out of the decode batch; move its KV to the host tier when there is one."""
         used = pages_for(s.num_cached_tokens, self.buf.page_size)
-        if self.host_kv is not None and self.host_kv.alloc.num_free >= used:
+        if self.host_tier is not None and self._deferred_host and self.host_tier.alloc.num_free < used:
+            self._drain_deferred(block=True)           # host pages of finished loads
+        if self.host_kv is not None and self.host_kv.alloc.num_free < used:
+            self._make_host_room(s, used)
+        if self.host_tier is not None and self.host_tier.alloc.num_free >= used:
+            # asynchronous offload after the kernels that wrote the KV; the device pages return to the pool when
+            # the copy is done (no host synchronisation here)
+            s.host_pages = self.host_tier.alloc.alloc(used)
+            tasks = self.host_tier.offload(s.gpu_pages[:used], s.host_pages,
+                                           after_stream=torch.cuda.current_stream().cuda_stream)
+            self._deferred_gpu.append((tasks, s.gpu_pages))
+            s.gpu_pages = []
+            self.stats.offloaded_pages += used
+            s.transition(S.ON_HOLD)
+            self.stats.holds += 1
+        elif self.host_tier is None and self.host_kv is not None and self.host_kv.alloc.num_free >= used:
             s.host_pages = self.host_kv.alloc.alloc(used)
             self.host_kv.copy_pages_from(self.kv, s.gpu_pages[:used], s.host_pages, self.copy_stream)
             if self.host_state is not None and s.state_slot >= 0 and self.host_state.num_free:
@@ -513,6 +635,29 @@ class Engine:
             self.stats.holds += 1
         else:
             self._evict(s)
+
+    def _make_host_room(self, s: Sequence, need: int) -> None:
+        """The host tier cannot take ``need`` more pages for row ``s``: parked rows give theirs up, cheapest to
+        recompute first (they fall back to EVICTED and are re-prefilled later), only as many as the debt requires
+        (batchgen/continuous_batching.py:578-700: eviction is strictly growth driven)."""
+        from .continuous_batching import EvictionStrategy, plan_host_kv_growth_evictions
+        held = [q for q in self.seqs.values() if q.status == S.ON_HOLD and q.host_pages and q is not s]
+        if not held:
+            return
+        total = self.host_kv.num_pages
+        plan = plan_host_kv_growth_evictions(
+            active_uuids=[str(q.global_idx) for q in held] + [str(s.global_idx)], completed_uuids=[],
+            host_growth_uuids=[str(s.global_idx)], host_growth_pages=[need],
+            eviction_candidates=[(str(q.global_idx), dict(host_owned_pages=len(q.host_pages),
+                                                          decoded_length=q.num_decoded, global_idx=q.global_idx))
+                                 for q in held],
+            free_pages=self.host_kv.alloc.num_free, total_pages=total, completed_pages=0,
+            strategy=EvictionStrategy.SHORTEST_FIRST)
+        if not plan.growth_feasible_after_eviction:
+            return                                     # evicting everybody would still not fit: ``s`` is evicted instead
+        for uid in plan.evicted_uuids:
+            self._evict(self.seqs[int(uid)])
+            self.stats.growth_evictions += 1
 
     def _evict(self, s: Sequence) -> None:
         if s.gpu_pages:
@@ -717,7 +862,7 @@ class Engine:
         free_host = self.host_kv.alloc.num_free if self.host_kv is not None else 0
         d = sched.compute_boundary_decisions(
             list(self.seqs.values()), self.cfg.eos_token_id, {0: self._free_pages()}, free_host, self.buf,
-            self.kv_token_budget, self.ecfg.max_decode_batch, self.ecfg.host_kv_chunk_size, host_tier=False,
+            self.kv_token_budget, self.ecfg.max_decode_batch, self.chunk_sizer.get_chunk_size(), host_tier=False,
             reclaimable_host_pages=0)
         if d.scheduler_error:
             raise RuntimeError(d.scheduler_error)
@@ -735,7 +880,7 @@ class Engine:
             if extra > self._free_pages():
                 self._hold(s)
                 continue
-            s.gpu_pages += self.kv.alloc.alloc(extra)
+            s.gpu_pages += self._take_pages(extra)
         for gi in d.load:
             s = self.seqs[gi]
             if s.status in (S.PREFILLED, S.ON_HOLD):

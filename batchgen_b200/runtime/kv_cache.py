@@ -66,6 +66,17 @@ class PageAllocator:
         return self._ref[page]
 
 
+def host_page_bytes(cfg: ModelConfig, page_size: int, kv_elem_bytes: int = 2) -> int:
+    """Bytes of one page over all layers (latent KV, then DSA index keys and their scales): the page size of the
+    node-shared host region, which the server computes without building a model."""
+    kv_layers = sum(1 for l in range(cfg.num_layers) if not cfg.layer_is_kda(l))
+    b = kv_layers * page_size * cfg.kv_cache_dim * kv_elem_bytes
+    if cfg.has_dsa:
+        n = len(list(cfg.indexer_full_layers) or range(cfg.num_layers))
+        b += n * page_size * (cfg.index_head_dim + 4)
+    return b
+
+
 class PagedKVCache:
     """One tier (device or pinned host) of paged KV."""
 

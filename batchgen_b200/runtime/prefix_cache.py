@@ -94,8 +94,10 @@ class PrefixCache:
     def reclaimable_pages(self) -> int:
         return sum(1 for e in self._entries.values() if self.alloc.refcount(e.page) == 1)
 
-    def evict(self, want_pages: int) -> int:
-        """Free up to ``want_pages`` pages held only by the cache, LRU leaves first."""
+    def evict(self, want_pages: int, on_evict=None) -> int:
+        """Free up to ``want_pages`` pages held only by the cache, LRU leaves first.  ``on_evict(key, page)`` sees
+        every page before it goes; when it returns True it has taken over the page's release (a copy that still
+        reads the page is in flight) and the page counts as freed."""
         freed = 0
         progress = True
         while freed < want_pages and progress:
@@ -103,7 +105,8 @@ class PrefixCache:
             for k in list(self._entries.keys()):
                 e = self._entries[k]
                 if e.children == 0 and self.alloc.refcount(e.page) == 1:
-                    self.alloc.free([e.page])
+                    if on_evict is None or not on_evict(k, e.page):
+                        self.alloc.free([e.page])
                     if e.parent is not None and e.parent in self._entries:
                         self._entries[e.parent].children -= 1
                     del self._entries[k]

@@ -42,6 +42,7 @@ class ServerArgs:
     extension_gpu_page_buffer: int = 4
     decision_frequency_pages: int = 2
     host_kv_watermark: int = 70
+    host_kv_region: str = ""                   # set by the server: path of the node-shared host KV region's descriptor
     host_kv_chunk_size: int = 8192
     adaptive_chunk: bool = False
     max_decode_batch: int = 512

@@ -88,7 +88,10 @@ def build_engine(args, rank: int, world: int, device: str):
         comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
                        max_tokens=step_rows, a2a_bytes=a2a)
     pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
-    eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages)
+    host_fd = None
+    if getattr(args, "host_kv_region", "") and device.startswith("cuda"):
+        host_fd = os.open(args.host_kv_region, os.O_RDWR)      # the server's region: same pages for every worker
+    eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages, host_kv_fd=host_fd)
     if device.startswith("cuda") and ecfg.enable_cuda_graph:
         from ..runtime.graphs import DecodeGraphRunner
         max_pages = -(-eng.kv_token_budget // ecfg.page_size)

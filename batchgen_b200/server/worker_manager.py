@@ -15,6 +15,7 @@ the TCPStore control plane reduces to in-process state), batchgen/server/watchdo
 from __future__ import annotations
 
 import multiprocessing as mp
+import os
 import threading
 import time
 from typing import Callable, Dict, List, Optional
@@ -72,6 +73,7 @@ class WorkerManager:
         self._monitor_stop = threading.Event()
         self._hooks: Dict[str, Callable] = {}
         self._target = worker_target
+        self.host_region = None                           # node-shared host KV region (core.native.HostPagedKV)
         self._lock = threading.RLock()
         self.watchdog: Optional[Watchdog] = None
         self.phase = "idle"
@@ -100,6 +102,7 @@ class WorkerManager:
             self.last_error = None
             W = self.args.world_size
             self.procs = []
+            self._create_host_region()
             for r in range(W):
                 p = self.ctx.Process(target=target, name=f"bg-worker-{r}",
                                      args=(r, W, self.args, self.request_queue, self.response_queue, self._ready,
@@ -127,6 +130,36 @@ class WorkerManager:
             self.watchdog = Watchdog(lambda: self.feed.value, self.args.watchdog_timeout, self._on_stall,
                                      armed=lambda: self.state == "ready" and bool(self._hooks.get("has_work", lambda: False)()))
             self.watchdog.start()
+
+    def _create_host_region(self) -> None:
+        """The node's host KV region belongs to the server: every worker of the cohort attaches to the same pages
+        and the same prefix coordinator.  Created with the cohort for GPU deployments with a host tier
+        (--host-kv-cache-size > 0) and dropped with it: pages that a dead worker's parked rows still reference
+        cannot be told from live ones, so a restart starts from an empty region."""
+        a = self.args
+        if self.host_region is not None or a.host_kv_cache_size <= 0 or a.device == "cpu":
+            return
+        try:
+            import torch
+            if a.device == "auto" and not torch.cuda.is_available():
+                return
+            from ..config import get_model_config
+            from ..core import native
+            from ..runtime.kv_cache import host_page_bytes
+            cfg = get_model_config(a.model) if isinstance(a.model, str) else a.model
+            page_bytes = host_page_bytes(cfg, a.page_size)
+            pages = int(a.host_kv_cache_size * (1 << 30)) // page_bytes
+            if pages <= 0:
+                return
+            self.host_region = native.HostPagedKV(pages, page_bytes, 2 * pages)
+            a.host_kv_region = f"/proc/{os.getpid()}/fd/{self.host_region.fd}"
+            from ..utils import eventlog
+            eventlog.get_log().info("server.host_kv_region", pages=pages, page_bytes=page_bytes, path=a.host_kv_region)
+        except Exception as exc:                          # noqa: BLE001 - workers fall back to private regions
+            self.host_region = None
+            a.host_kv_region = ""
+            from ..utils import eventlog
+            eventlog.get_log().warning("server.host_kv_region_failed", error=str(exc))
 
     def _on_stall(self, elapsed: float) -> None:
         self.last_error = f"watchdog: no engine step for {elapsed:.1f} s while work was pending"
@@ -176,6 +209,10 @@ class WorkerManager:
             p.join(timeout=timeout)
         self._kill_all()
         self.procs = []
+        if self.host_region is not None:
+            self.host_region.close()
+            self.host_region = None
+            self.args.host_kv_region = ""
         self.state = "stopped"
 
     def restart_workers(self, reason: str = "requested") -> int:

@@ -464,7 +464,13 @@ def main() -> int:
 
     bct = None
     if args.bct:
-        bct = run_bct(eng, cfg, args, rank, world, barrier)
+        if rank == 0:                                   # the step numbers survive a failure of the long workload
+            print(json.dumps({"partial": True, "ms_per_step": ms_step, "value": decode_tps, "e2e": e2e,
+                              "prefill": prefill, "comm_check": comm_check}), file=sys.stderr, flush=True)
+        try:
+            bct = run_bct(eng, cfg, args, rank, world, barrier)
+        except Exception as exc:                        # noqa: BLE001 - reported in the result line
+            bct = {"error": f"{type(exc).__name__}: {exc}"[:400]}
 
     if rank == 0:
         total_prompt = sum(rng.randint(512, 4096) for _ in range(512))

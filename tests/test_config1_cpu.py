@@ -98,6 +98,21 @@ def test_host_tier_hold_and_reload_same_tokens():
     assert eng.generate(prompts, params) == big
 
 
+def test_full_host_tier_evicts_parked_rows_by_growth_debt():
+    """The host tier is too small for every parked row: parked rows with the least decoded give their pages up
+    (and are re-prefilled later) only when another row must be parked; the tokens do not change."""
+    cfg = get_model_config("tiny-deepseek-v3")
+    prompts = _prompts(cfg, 8, 32, seed=9)
+    params = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    big = _engine(cfg, pages=256).generate(prompts, params)
+    ecfg = EngineConfig(page_size=16, initial_gpu_page_buffer=2, extension_gpu_page_buffer=1,
+                        decision_frequency_pages=1)
+    eng = Engine(build_model(cfg, seed=0), ecfg, num_gpu_pages=14, num_host_pages=6)
+    assert eng.generate(prompts, params) == big
+    assert eng.stats.growth_evictions > 0 and eng.stats.evictions >= eng.stats.growth_evictions
+    assert eng.chunk_sizer.completed_count == 8 and eng.chunk_sizer.ema_decode_length == 40.0
+
+
 def test_other_families_run_and_match_naive():
     for name in ("tiny-glm5", "tiny-kimi-k3"):
         cfg = get_model_config(name)
