@@ -354,6 +354,8 @@ class ParameterStore:
         for m in metas:
             with open(m) as f:
                 meta = json.load(f)
+            if "total_byte_size" not in meta:           # not a shard description (e.g. a staging manifest)
+                continue
             n = int(meta["total_byte_size"])
             paths.append(os.path.join(ckpt_dir, meta["file_name"]).encode())
             offs.append(cur)
@@ -379,7 +381,7 @@ class ParameterStore:
         total = 0
         for m in sorted(glob.glob(os.path.join(ckpt_dir, "*.json"))):
             with open(m) as f:
-                total += (int(json.load(f)["total_byte_size"]) + 255) // 256 * 256
+                total += (int(json.load(f).get("total_byte_size", 0)) + 255) // 256 * 256
         return total
 
     def export_index(self) -> Dict[str, Tuple[int, str, Tuple[int, ...]]]:

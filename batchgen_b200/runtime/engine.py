@@ -68,6 +68,7 @@ class EngineStats:
     offloaded_pages: int = 0
     shared_prefix_tokens: int = 0      # prompt tokens not computed because another prompt of the wave shares them
     trajectory_commits: int = 0        # completed rows whose prompt + output pages were left in the prefix cache
+    prefill_chunks: int = 0            # forwards that computed a piece of a prompt longer than max_prefill_tokens
     growth_evictions: int = 0          # parked rows evicted to make host-tier room for a row that had to be parked
     transfer_waits: int = 0            # times the host blocked on a page transfer (pool exhausted with copies in flight)
     prefix_promoted_pages: int = 0     # prefix pages brought back from the host tier's coordinator
@@ -436,7 +437,35 @@ class Engine:
         self._run_prefill_rows(rows)
 
     def _run_prefill_rows(self, rows: List[_PrefillRow]) -> None:
-        """One packed prefill forward over ``rows``; rows that belong to a sequence get their first token sampled."""
+        """Prefill ``rows``; rows that belong to a sequence get their first token sampled.  A row longer than
+        ``max_prefill_tokens`` is computed in pieces over consecutive forwards (chunked prefill: every piece attends
+        over the KV its predecessors wrote; only the last piece produces a token), so activation memory is bounded
+        by the cap whatever the prompt length (batchgen/prefill.py: chunked long-context prefill)."""
+        cap = max(int(self.ecfg.max_prefill_tokens), 1)
+        if not any(len(r.tokens) > cap for r in rows):
+            return self._run_prefill_forward(rows)
+        pending = [(r, 0) for r in rows]
+        while pending:
+            batch: List[_PrefillRow] = []
+            later = []
+            used = 0
+            for r, off in pending:
+                room = cap - used
+                if room <= 0:
+                    later.append((r, off))
+                    continue
+                n = min(len(r.tokens) - off, room)
+                last = off + n == len(r.tokens)
+                batch.append(_PrefillRow(r.tokens[off:off + n], r.start + off, r.pages, r.seq if last else None))
+                used += n
+                if not last:
+                    later.append((r, off + n))
+            self._run_prefill_forward(batch)
+            self.stats.prefill_chunks += 1
+            pending = later
+
+    def _run_prefill_forward(self, rows: List[_PrefillRow]) -> None:
+        """One packed prefill forward over ``rows``."""
         ps = self.buf.page_size
         ids: List[int] = []
         pos: List[int] = []

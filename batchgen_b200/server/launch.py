@@ -24,6 +24,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         log.error("preflight.failed", reason=str(e))
         log.close()
         return 3
+    from . import run_guard
+    from .runtime_lease import LaneLeaseError
+    from .runtime_locks import RuntimeLockError
+    try:
+        guard = run_guard.acquire(args)
+    except (RuntimeLockError, LaneLeaseError, ValueError) as e:
+        log.error("run_guard.failed", reason=str(e))
+        log.close()
+        return 4
+    log.info("run_guard", instance=guard.identity.instance_id, run_id=guard.identity.run_id,
+             runtime_dir=str(guard.run_dir), reclaimed=guard.reclaimed, lease=guard.lease.held if guard.lease else 0)
     from .http_server import launch_server
     log.info("server.config", **{k: v for k, v in vars(args).items()})
     try:
@@ -31,6 +42,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     except KeyboardInterrupt:
         pass
     finally:
+        guard.close()
         log.close()
     return 0
 

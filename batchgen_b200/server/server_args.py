@@ -79,6 +79,18 @@ class ServerArgs:
     log_dir: str = ""
     log_level: str = "info"
     # http
+    weight_store_stage_dir: str = ""            # copy the converted checkpoint here first (local NVMe) and verify it
+    shared_weight_store: bool = True            # load the converted checkpoint once into a node-shared region
+    param_store_path: str = ""                  # set by the server: descriptor path of the shared weight region
+    query_book_mb: int = 64                     # node-shared token book (prompts + generated tokens), MiB
+    instance_id: str = ""                       # stable name of this deployment (default: port<port>)
+    run_mode: str = "exclusive"                 # "shared": several servers on the machine, a lane lease is mandatory
+    runtime_root: str = ""                      # directory of the host / instance / run locks
+    lane_manifest_fd: int = -1                  # inherited descriptor of the launcher's lane manifest
+    lane_gpus: str = ""                         # leased GPU UUIDs (default: CUDA_VISIBLE_DEVICES)
+    lane_lock_root: str = ""
+    runtime_dir: str = ""                       # set by the server: this run's directory (workers take its run lock)
+    run_id: str = ""                            # set by the server
     host: str = "127.0.0.1"
     port: int = 8000
     # capacity

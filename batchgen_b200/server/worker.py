@@ -44,6 +44,9 @@ def setup_nccl_env() -> None:
         os.environ.setdefault("NCCL_ALGO", "allreduce:tree")
 
 
+_STORES: list = []
+
+
 def build_engine(args, rank: int, world: int, device: str):
     import torch
 
@@ -58,7 +61,14 @@ def build_engine(args, rank: int, world: int, device: str):
     ecfg.device = device
     dtype = "bf16" if device.startswith("cuda") else "fp32"
     loader = None
-    if args.converted_ckpt_dir:
+    if getattr(args, "param_store_path", "") and getattr(args, "param_store_index", None):
+        # the server read the checkpoint once into a node-shared region: attach and serve tensors as views
+        from ..core import native
+        store = native.ParameterStore(fd=os.open(args.param_store_path, os.O_RDONLY), read_only=True)
+        store.import_index(args.param_store_index)
+        loader = store.loader()
+        _STORES.append(store)                         # the mapping must outlive the tensors built from it
+    elif args.converted_ckpt_dir:
         from ..ckpt.converter import ConvertedCheckpoint
         loader = ConvertedCheckpoint(args.converted_ckpt_dir).loader()
     comm = None
@@ -106,6 +116,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                 feed_counter=None) -> None:
     """Entry point of a worker process (also callable in-process for tests)."""
     die_with_parent()
+    from . import run_guard
+    run_lock = run_guard.join_run(args)               # noqa: F841 - held (shared) until the process exits
     from ..utils import eventlog
     log = eventlog.configure_process(f"worker{rank}", args.log_dir or None, args.log_level,
                                      flight_recorder=bool(args.log_dir))
@@ -141,14 +153,39 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
 
         by_idx: Dict[int, Dict[str, Any]] = {}
         cancelled = set()
+        # the token book: prompts live once per node in a shared int32 table; rank 0 binds a slot and writes the
+        # prompt, the step broadcast then carries (offset, length) instead of the tokens, and completions are read
+        # back from the book (batchgen/query_book.py, batchgen/batchgen_worker.py: node-shared token memfd)
+        from ..runtime.query_book import NodeSharedTokens, QueryBook
+        qb_tokens = max(int(getattr(args, "query_book_mb", 64)), 1) * (1 << 20) // 4
+        qb_rows = max(qb_tokens // 4096, 4)
+        handle = [None]
+        shared = None
+        if rank == 0:
+            shared = NodeSharedTokens.create(qb_rows, 4096)
+            handle[0] = shared.handle()
+        if world > 1:
+            dist.broadcast_object_list(handle, src=0)
+            if rank != 0:
+                shared = NodeSharedTokens.attach(tuple(handle[0]))
+        book = QueryBook(qb_rows * 4096 * 4, page_tokens=4096, storage=shared.tensor)   # rank 0 allocates and writes
+        flat = shared.tensor.view(-1)
 
         def on_complete(seq) -> None:
             meta = by_idx.pop(seq.global_idx, None)
             if meta is None:
                 return
             reason = "cancelled" if meta["batch_id"] in cancelled else seq.finish_reason
+            out_ids = list(seq.output_ids)
+            if rank == 0 and meta.get("qb_slot") is not None:
+                qs = meta["qb_slot"]
+                room = book.metadata(qs).remaining
+                book.append_tokens([qs] * min(len(out_ids), room), out_ids[:room])
+                if room >= len(out_ids):
+                    out_ids = book.generated_tokens(qs).tolist()       # the book is the record of the trajectory
+                book.release(qs)
             up({"type": "completion", "slot": meta["slot"], "batch_id": meta["batch_id"],
-                "request_id": meta["request_id"], "output_ids": list(seq.output_ids),
+                "request_id": meta["request_id"], "output_ids": out_ids,
                 "prompt_tokens": len(seq.prompt_ids), "cached_tokens": seq.cached_prefix_tokens,
                 "finish_reason": reason})
 
@@ -171,6 +208,19 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                     pass
                 if shutdown_flag.is_set():
                     msgs.append({"type": "shutdown"})
+                for m in msgs:                          # prompts move into the book; the broadcast carries references
+                    if m.get("type") != "admit":
+                        continue
+                    for e in m["entries"]:
+                        ids = e.get("prompt_ids")
+                        want = len(ids or ()) + int(e["sampling"].get("max_new_tokens", 0)) + 1
+                        uid = f'{e["batch_id"]}/{e["request_id"]}/{e["slot"]}'
+                        if not ids or book.has_sequence(uid) or not book.can_reserve(want):
+                            continue                     # no room (or a bad request): the tokens travel inline
+                        qs = book.bind(uid, want)
+                        book.write_prompt(qs, torch.tensor(ids, dtype=torch.int32))
+                        e["qb"] = (qs, book._base(qs), len(ids))
+                        e["prompt_ids"] = None
             if world > 1:
                 box = [msgs]
                 dist.broadcast_object_list(box, src=0)
@@ -188,10 +238,16 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                     for e in m["entries"]:
                         try:
                             sp = SamplingParams(**e["sampling"])
-                            s = eng.add_request(e["prompt_ids"], sp, custom_id=e["request_id"], batch_id=e["batch_id"])
+                            ids, qs = e["prompt_ids"], None
+                            if e.get("qb") is not None:
+                                qs, base, n = e["qb"]
+                                ids = flat[base:base + n].tolist()
+                            s = eng.add_request(ids, sp, custom_id=e["request_id"], batch_id=e["batch_id"])
                             by_idx[s.global_idx] = {"slot": e["slot"], "batch_id": e["batch_id"],
-                                                    "request_id": e["request_id"]}
+                                                    "request_id": e["request_id"], "qb_slot": qs}
                         except Exception as ex:  # noqa: BLE001  (bad request: report, keep serving)
+                            if rank == 0 and e.get("qb") is not None:
+                                book.release(e["qb"][0])
                             up({"type": "completion", "slot": e["slot"], "batch_id": e["batch_id"],
                                 "request_id": e["request_id"], "output_ids": [], "prompt_tokens": 0,
                                 "cached_tokens": 0, "finish_reason": f"error: {ex}"})
@@ -210,7 +266,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             if rank == 0 and time.monotonic() - last_beat > 5.0:
                 last_beat = time.monotonic()
                 up({"type": "heartbeat", "ts": time.time(), "live": len(eng.seqs), "free_pages": eng.kv.alloc.num_free,
-                    "stats": eng.stats.summary()})
+                    "stats": eng.stats.summary(), "query_book": {"active": book.active_count,
+                                                                  "free_pages": book.free_page_count}})
         log.info("worker.shutdown", rank=rank)
     except Exception as ex:  # noqa: BLE001
         log.error("worker.fatal", rank=rank, error=str(ex), trace=traceback.format_exc()[-1500:])

@@ -74,6 +74,8 @@ class WorkerManager:
         self._hooks: Dict[str, Callable] = {}
         self._target = worker_target
         self.host_region = None                           # node-shared host KV region (core.native.HostPagedKV)
+        self.weight_store = None                          # node-shared weights (core.native.ParameterStore)
+        self.weight_index: Optional[Dict] = None
         self._lock = threading.RLock()
         self.watchdog: Optional[Watchdog] = None
         self.phase = "idle"
@@ -103,7 +105,9 @@ class WorkerManager:
             W = self.args.world_size
             self.procs = []
             self._create_host_region()
+            self._load_weight_store()
             for r in range(W):
+                self.args.param_store_index = self.weight_index      # travels with the pickled arguments
                 p = self.ctx.Process(target=target, name=f"bg-worker-{r}",
                                      args=(r, W, self.args, self.request_queue, self.response_queue, self._ready,
                                            self._shutdown, self.feed), daemon=True)
@@ -160,6 +164,36 @@ class WorkerManager:
             a.host_kv_region = ""
             from ..utils import eventlog
             eventlog.get_log().warning("server.host_kv_region_failed", error=str(exc))
+
+    def _load_weight_store(self) -> None:
+        """Checkpoint weights are read once per node, not once per worker: the server stages the converted
+        checkpoint (optional copy to a local directory with a verified manifest), reads its shards with parallel
+        readers into one shared region and hands workers the region's descriptor and tensor index; a worker's
+        loader then returns views of that memory.  The region survives worker restarts.
+        (batchgen/server/worker_manager.py: the server owns the weight memfd; server/weight_store_staging.py.)"""
+        a = self.args
+        if not a.converted_ckpt_dir or not a.shared_weight_store or self.weight_store is not None:
+            return
+        from ..core import native
+        from ..utils import eventlog
+        from . import weight_store_staging as staging
+        log = eventlog.get_log()
+        src = a.converted_ckpt_dir
+        if a.weight_store_stage_dir:
+            staged = staging.stage_store(src, a.weight_store_stage_dir)
+            problem = staging.verify_store(staged.root)
+            if problem is not None:
+                raise WorkerStartError(f"staged weight store is not usable: {problem}")
+            log.info("server.weight_store_staged", root=staged.root, reused=staged.reused, copied_bytes=staged.copied_bytes)
+            src = staged.root
+        t0 = time.monotonic()
+        store = native.ParameterStore(nbytes=native.ParameterStore.bytes_needed(src), huge_pages=True)
+        loaded = store.load_converted(src, threads=8)
+        self.weight_store = store
+        a.param_store_path = f"/proc/{os.getpid()}/fd/{store.fd}"
+        self.weight_index = store.export_index()
+        log.info("server.weight_store_loaded", bytes=loaded, tensors=len(self.weight_index),
+                 seconds=round(time.monotonic() - t0, 2), path=a.param_store_path)
 
     def _on_stall(self, elapsed: float) -> None:
         self.last_error = f"watchdog: no engine step for {elapsed:.1f} s while work was pending"

@@ -22,6 +22,12 @@ batch API (``runtime.batch_api.run_batch``) on the same engine and adds the meas
 the engine-reported prefill / decode rates to the line (key ``bct``); ``--bct-requests`` / ``--bct-tokens``
 shrink it for quick runs (then marked ``"full": false``).
 
+``--workload distinct64k | grouped64k`` (with ``--model glm-5.3-fp8``) runs the long-context workloads of the
+sparse-attention (DSA) model through the same batch API instead of the decode-step benchmark: ``--requests`` prompts
+of ``--ctx-tokens`` distinct tokens each, or ``--requests / 8`` shared prefixes with eight 64-token suffixes each,
+``--bct-tokens`` forced decode tokens; the line reports the measured completion time and the engine's prefill and
+decode rates.
+
 Where the FP8 expert weights of the rank exceed what HBM can hold next to the KV pool (N < 8),
 layers share physical expert storage in a cycle of ``distinct_expert_sets`` sets: every layer still
 streams its full expert bytes from HBM (a set is far larger than L2) and executes every FLOP.
@@ -94,6 +100,118 @@ def run_bct(eng, cfg, args, rank, world, barrier):
             "prefill_tokens": st["prefill_tokens"], "decode_tokens": st["decode_tokens"],
             "prefill_waves": st["prefill_waves"], "decode_steps": st["decode_steps"], "holds": st["holds"],
             "evictions": st["evictions"], "api": "runtime.batch_api.run_batch on Engine"}
+
+
+def run_longctx(args) -> int:
+    """Long-context workloads (BASELINE configs 3 and 4) through Engine + batch API: chunked prefill of
+    ``--ctx-tokens``-token prompts (8,192-token pieces; the DSA indexer scores every earlier key for each query and
+    the attention reads the 2,048 selected rows), in-wave prefix sharing for the grouped form, then sparse decode."""
+    import torch
+    import torch.distributed as dist
+
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.models.weights import ParallelLayout
+    from batchgen_b200.ops import _ext
+    from batchgen_b200.runtime import batch_api
+    from batchgen_b200.runtime.engine import Engine
+    from batchgen_b200.runtime.kv_cache import host_page_bytes
+    from batchgen_b200.runtime.tokenization import get_tokenizer
+    from batchgen_b200.utils.clocks import ClockSampler
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        from batchgen_b200.parallel import make_comm
+        comm = make_comm("nccl", None)                  # DSA layers run the tensor-parallel layout over NCCL
+    _ext.lib()
+    cfg = get_model_config(args.model)
+    if args.layers:
+        cfg.num_layers = args.layers
+        cfg.indexer_full_layers = tuple(l for l in cfg.indexer_full_layers if l < args.layers)
+    page, L, N, R = 64, args.ctx_tokens, args.bct_tokens, args.requests
+    grouped = args.workload == "grouped64k"
+    groups = max(1, R // 8) if grouped else R
+    rng = random.Random(4321)
+    if grouped:
+        prefixes = [[rng.randrange(2, cfg.vocab_size) for _ in range(L - 64)] for _ in range(groups)]
+        prompts = [prefixes[i // 8] + [rng.randrange(2, cfg.vocab_size) for _ in range(64)] for i in range(groups * 8)]
+    else:
+        prompts = [[rng.randrange(2, cfg.vocab_size) for _ in range(L)] for _ in range(R)]
+    R = len(prompts)
+    per_req = (L + N) // page + 3
+    total_pages = (groups * (L // page) + R * (N // page + 4) + 16) if grouped else (R * per_req + 16)
+    layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+    n_moe = cfg.num_layers - cfg.first_k_dense
+    expert_bytes_layer = (cfg.n_routed_experts // world) * 3 * cfg.moe_intermediate_size * cfg.hidden_size
+    kv_bytes = total_pages * host_page_bytes(cfg, page)
+    free_b, _ = torch.cuda.mem_get_info(dev)
+    other = 30e9 / world + 16e9                               # attention / dense / shared / embeddings + workspace
+    budget = free_b * 0.94 - kv_bytes - other
+    if budget < expert_bytes_layer:
+        raise SystemExit(f"{R} requests of {L} tokens need {kv_bytes / 1e9:.0f} GB of KV: too many for this GPU")
+    sets = int(max(1, min(n_moe, budget // expert_bytes_layer)))
+    alias = 0 if sets >= n_moe else sets
+    t0 = time.time()
+    model = build_model(cfg, device=dev, dtype="bf16", seed=0, layout=layout, comm=comm,
+                        max_positions=L + N + 2 * page, alias_experts_every=alias, gen_device=dev)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+    ecfg = EngineConfig(page_size=page, max_decode_batch=max(R, 8), max_prefill_tokens=args.prefill_tokens,
+                        enable_cuda_graph=False, enable_prefix_cache=True, initial_gpu_page_buffer=N // page + 2,
+                        extension_gpu_page_buffer=2, decision_frequency_pages=2, world_size=world,
+                        attn_tp_size=world, ep_size=world, device=str(dev), dtype="bf16", moe_comm="nccl")
+    eng = Engine(model, ecfg, num_gpu_pages=total_pages)
+    reqs = [batch_api.BatchRequest(f"r{i}", "/v1/completions",
+                                   {"prompt": p, "max_tokens": N, "temperature": 0, "ignore_eos": True})
+            for i, p in enumerate(prompts)]
+    tok = get_tokenizer("ids", cfg.vocab_size)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    l0 = _ext.LAUNCHES["count"]
+    barrier()
+    t0 = time.perf_counter()
+    items = batch_api.run_batch(eng, reqs, tok, batch_api.BatchOptions(endpoint="/v1/completions"))
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop() if sampler is not None else None
+    _ext.check_status()
+    st = eng.stats.summary()
+    if rank == 0:
+        ok = sum(1 for it in items if it["error"] is None)
+        full = (args.model == "glm-5.3-fp8" and L == 65536 and N == 4096 and not args.layers
+                and R == (512 if grouped else 312))
+        print(json.dumps({
+            "metric": f"batch completion time ({cfg.name}, {args.workload})", "value": wall, "unit": "s",
+            "n_gpus": world, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "impl": "ours",
+            "dtype": "fp8(e4m3 block-scaled weights+activations, e4m3 index keys)/bf16", "data": "synthetic",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "workload": args.workload, "requests": R,
+                       "completed": ok, "ctx_tokens": L, "forced_tokens": N, "prefix_groups": groups if grouped else 0,
+                       "parallelism": f"tp{world}+ep{world}", "comm": "nccl" if world > 1 else "none",
+                       "prefill_piece_tokens": args.prefill_tokens, "index_topk": cfg.index_topk,
+                       "distinct_expert_sets": sets, "full_size_workload": full, "valid": not args.layers,
+                       "api": "runtime.batch_api.run_batch on Engine", "build_seconds": round(build_s, 1)},
+            "prefill_tok_per_s": st["prefill_tok_per_s"], "decode_tok_per_s": st["decode_tok_per_s"],
+            "prefill_tokens": st["prefill_tokens"], "shared_prefix_tokens": st["shared_prefix_tokens"],
+            "prefill_chunks": st["prefill_chunks"], "prefill_seconds": st["prefill_seconds"],
+            "decode_tokens": st["decode_tokens"], "decode_seconds": st["decode_seconds"],
+            "decode_steps": st["decode_steps"], "clocks": clocks, "gpu_launches": _ext.LAUNCHES["count"] - l0}))
+    sys.stdout.flush()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
 
 
 def compare_with_nccl(model, kv, d_ids, d_pos, d_slot, d_bt, d_len, rank, world, dist, n_layers=None):
@@ -179,12 +297,19 @@ def main() -> int:
     ap.add_argument("--bct", action="store_true", help="also run the 512-request workload through the batch API")
     ap.add_argument("--bct-requests", type=int, default=512)
     ap.add_argument("--bct-tokens", type=int, default=1024)
+    ap.add_argument("--workload", default="decode", choices=["decode", "distinct64k", "grouped64k"],
+                    help="decode: the headline decode-step benchmark; the others: long-context DSA workloads "
+                         "(use with --model glm-5.3-fp8)")
+    ap.add_argument("--requests", type=int, default=2, help="requests of a long-context workload")
+    ap.add_argument("--ctx-tokens", type=int, default=65536, help="prompt tokens of a long-context request")
     ap.add_argument("--check-comm", action="store_true",
                     help="N > 1: run one decode step through the NCCL baseline on the same inputs and report the "
                          "largest relative difference of the logits (outside the timed regions)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload != "decode":
+        return run_longctx(args)
 
     import torch
     import torch.distributed as dist

@@ -113,6 +113,23 @@ def test_full_host_tier_evicts_parked_rows_by_growth_debt():
     assert eng.chunk_sizer.completed_count == 8 and eng.chunk_sizer.ema_decode_length == 40.0
 
 
+def test_chunked_prefill_of_long_prompts_matches_one_shot():
+    """Prompts longer than max_prefill_tokens are computed in pieces; tokens equal the one-shot prefill, for the
+    dense-attention model and for the DSA model (its indexer scores the keys written by earlier pieces)."""
+    for name in ("tiny-deepseek-v3", "tiny-glm5"):
+        cfg = get_model_config(name)
+        prompts = _prompts(cfg, 3, 90, seed=21) + _prompts(cfg, 1, 17, seed=22)
+        params = SamplingParams(max_new_tokens=5, ignore_eos=True)
+        outs = []
+        for cap in (8192, 32):
+            for prefix in (False, True):
+                ecfg = EngineConfig(page_size=16, max_prefill_tokens=cap, enable_prefix_cache=prefix)
+                eng = Engine(build_model(cfg, seed=0), ecfg, num_gpu_pages=64)
+                outs.append(eng.generate(prompts, params))
+                assert (eng.stats.prefill_chunks > 0) == (cap == 32), (name, cap, prefix)
+        assert all(o == outs[0] for o in outs[1:]), name
+
+
 def test_other_families_run_and_match_naive():
     for name in ("tiny-glm5", "tiny-kimi-k3"):
         cfg = get_model_config(name)

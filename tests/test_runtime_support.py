@@ -277,3 +277,38 @@ def test_run_identity_names():
         rl.RunIdentity.create("ok", run_id="xyz")
     with pytest.raises(ValueError):
         rl.RunIdentity.create("ok", mode="both")
+
+
+# ---------------------------------------------------------------------------------------------- run guard
+def test_run_guard_locks_instance_adopts_lease_and_reclaims(tmp_path, monkeypatch):
+    """The launcher path: one server per instance id, the lane lease checked against the server's own arguments,
+    workers join the run, and the next start reclaims a run that nobody holds any more."""
+    from batchgen_b200.server import run_guard, runtime_lease as rl, runtime_locks as locks
+    from batchgen_b200.server.server_args import ServerArgs
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    root, lanes = tmp_path / "rt", tmp_path / "lanes"
+    args = ServerArgs(instance_id="prod-a", runtime_root=str(root), port=8123, dist_init_addr="127.0.0.1:29611",
+                      storage_path=str(tmp_path / "store"), lane_gpus="GPU-aaa,GPU-bbb", lane_lock_root=str(lanes))
+    want = rl.expected_for_server(["GPU-aaa", "GPU-bbb"], 8123, 29611, tmp_path / "store")
+    res = rl.LaneReservation.reserve("prod-a", want, lock_root=lanes)
+    args.lane_manifest_fd = res.manifest_fd
+    guard = run_guard.acquire(args)
+    assert guard.lease is not None and guard.lease.held == 5
+    assert args.runtime_dir == str(guard.run_dir) and args.run_id == guard.identity.run_id
+    worker_lock = run_guard.join_run(args)                    # what every worker process does
+    assert worker_lock is not None and not locks.run_is_dead(guard.run_dir)
+    # a second server of the same instance is refused while the first one lives
+    again = ServerArgs(instance_id="prod-a", runtime_root=str(root), port=8124)
+    with pytest.raises(locks.RuntimeLockError):
+        run_guard.acquire(again)
+    # shared mode without a lease is refused
+    shared = ServerArgs(instance_id="prod-b", runtime_root=str(root), port=8125, run_mode="shared")
+    with pytest.raises(rl.LaneLeaseError):
+        run_guard.acquire(shared)
+    dead_run = guard.run_dir.name
+    worker_lock.close()
+    guard.close()
+    nxt = run_guard.acquire(ServerArgs(instance_id="prod-a", runtime_root=str(root), port=8123))
+    assert dead_run in nxt.reclaimed and nxt.lease is None
+    assert run_guard.join_run(ServerArgs()) is None           # unguarded server (in-process tests)
+    nxt.close()

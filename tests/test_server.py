@@ -198,3 +198,51 @@ def test_server_args_validation(tmp_path):
                 dict(ep_offloading_ratio=0.5), dict(extension_gpu_page_buffer=1, decision_frequency_pages=2)):
         with pytest.raises(ServerArgsError):
             validate_server_args(ServerArgs(**bad))
+
+
+def test_server_loads_checkpoint_once_into_the_shared_store(tmp_path):
+    """With a converted checkpoint the server stages it, reads it once into a node-shared region and the worker
+    builds its model from views of that region: same completions as a worker that reads the files itself."""
+    from batchgen_b200.ckpt.converter import convert_dir, save_model_checkpoint
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.models.weights import WeightSource
+    cfg = get_model_config("tiny-deepseek-v3")
+    save_model_checkpoint(cfg, WeightSource(seed=5), str(tmp_path / "hf"), shard_layers=2)
+    convert_dir(str(tmp_path / "hf"), str(tmp_path / "conv"), workers=2)
+    texts = []
+    for shared in (True, False):
+        kw = dict(converted_ckpt_dir=str(tmp_path / "conv"), shared_weight_store=shared)
+        if shared:
+            kw["weight_store_stage_dir"] = str(tmp_path / "stage")
+        app = create_app(_args(tmp_path / f"s{int(shared)}", **kw))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            wm = app.state.worker
+            assert (wm.weight_store is not None) == shared
+            if shared:
+                assert len(wm.weight_index) > 50 and os.path.exists(tmp_path / "stage" / "MANIFEST.json")
+            f = _upload(c, _lines(3, max_tokens=6))
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"])
+            assert b["status"] == "completed", b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
+    assert texts[0] == texts[1]
+
+
+def test_two_rank_cpu_cohort_reads_prompts_from_the_shared_token_book(tmp_path):
+    """Two gloo ranks: rank 0 writes prompts into the node-shared token book, the follower reads them from there
+    (the step broadcast carries offsets only); completions equal those of the one-rank server."""
+    texts = []
+    for world in (1, 2):
+        app = create_app(_args(tmp_path / f"w{world}", world_size=world,
+                               dist_init_addr=f"127.0.0.1:{29640 + world}", enable_prefix_cache=False))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            f = _upload(c, _lines(4, max_tokens=5))
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"])
+            assert b["status"] == "completed" and b["request_counts"]["completed"] == 4, b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
+    assert texts[0] == texts[1]
