@@ -277,16 +277,23 @@ class Transformer:
         T = x.shape[0]
         Hi, Di = cfg.index_n_heads, cfg.index_head_dim
         rd = cfg.qk_rope_head_dim
-        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
         gpu = x.is_cuda and x.dtype == torch.bfloat16
         if gpu:
             from ..ops import dsa as dsa_ops
             gpu = dsa_ops.supported(Hi, Di, cache.page_size)
         q = linear(qn, lw.idx_wq).view(T, Hi, Di)
-        q = torch.cat([ref.apply_rope(q[..., :rd], cos, sin, cfg.rope_interleaved), q[..., rd:]], dim=-1)
-        gates = (x.float() @ lw.idx_head_w.float().t()) * (Hi ** -0.5) * (Di ** -0.5)
+        gate_mul = (Hi ** -0.5) * (Di ** -0.5)
         if gpu:
-            # fused LayerNorm + RoPE + e4m3 + paged store, FP8 scores on tcgen05, radix-select top-k
+            # head gates on the bf16 tensor-core GEMM (fp32 epilogue); RoPE + e4m3 + gate scaling in one kernel;
+            # LayerNorm + RoPE + e4m3 + paged store of the index keys in one kernel; FP8 scores on tcgen05;
+            # radix-select top-k.  Row lengths and the row -> sequence map are device tensors built once per step.
+            hw = getattr(lw.idx_head_w, "_bg_bf16", None)
+            if hw is None:
+                hw = lw.idx_head_w.to(torch.bfloat16).contiguous()
+                lw.idx_head_w._bg_bf16 = hw
+            gates = gemm.bf16_gemm(x, hw, fp32_out=True)
+            q8, g = dsa_ops.index_q_prepare(q, meta.positions, self.rope.cos, self.rope.sin, rd, cfg.rope_interleaved,
+                                            gates, gate_mul)
             ck, cs = cache.index_keys(l)
             dsa_ops.index_k_write(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b, meta.positions, self.rope.cos,
                                   self.rope.sin, rd, cfg.rope_interleaved, meta.slot_mapping, ck, cs)
@@ -294,18 +301,15 @@ class Transformer:
                 lengths, bt = meta.seqlens, meta.block_table
                 max_len = bt.shape[1] * cache.page_size
             else:
-                row_seq = torch.zeros(T, dtype=torch.long, device=x.device)
-                lens = torch.zeros(T, dtype=torch.int32, device=x.device)
-                for i in range(len(meta.cu_seqlens) - 1):
-                    a, b = meta.cu_seqlens[i], meta.cu_seqlens[i + 1]
-                    row_seq[a:b] = i
-                    lens[a:b] = torch.arange(b - a, device=x.device, dtype=torch.int32) + meta.ctx_lens[i] + 1
-                lengths, bt = lens, meta.block_table[row_seq].contiguous()
+                lengths, bt = self._prefill_row_tables(meta, T)
                 max_len = max(meta.ctx_lens[i] + meta.cu_seqlens[i + 1] - meta.cu_seqlens[i]
                               for i in range(len(meta.cu_seqlens) - 1))
-            out = dsa_ops.indexer_select(q.contiguous(), gates, ck, cs, bt, lengths, cfg.index_topk, max_len)
+            out = dsa_ops.indexer_select(q8, g, ck, cs, bt, lengths, cfg.index_topk, max_len, prepared=True)
             meta.dsa_selection[l] = out
             return out
+        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
+        q = torch.cat([ref.apply_rope(q[..., :rd], cos, sin, cfg.rope_interleaved), q[..., rd:]], dim=-1)
+        gates = (x.float() @ lw.idx_head_w.float().t()) * gate_mul
         k = ref.layernorm(linear(x, lw.idx_wk), lw.idx_k_norm_w, lw.idx_k_norm_b)
         k = torch.cat([ref.apply_rope(k[:, :rd], cos, sin, cfg.rope_interleaved), k[:, rd:]], dim=-1)
         kq, ks = ref.index_k_quant(k)
@@ -341,13 +345,26 @@ class Transformer:
         meta.dsa_selection[l] = out
         return out
 
+    def _prefill_row_tables(self, meta: AttnMeta, T: int):
+        """Per query row of a prefill step: (number of keys it may see, block-table row of its sequence).  Built
+        once per step on the device (a row at position p sees p + 1 keys) and kept on ``meta`` for all layers."""
+        if getattr(meta, "_row_tables", None) is None:
+            dev = meta.positions.device
+            counts = torch.tensor([meta.cu_seqlens[i + 1] - meta.cu_seqlens[i] for i in range(len(meta.cu_seqlens) - 1)],
+                                  device=dev)
+            row_seq = torch.repeat_interleave(torch.arange(counts.numel(), device=dev), counts)
+            if row_seq.numel() < T:                      # padding rows of a sequence-parallel step: no keys
+                row_seq = torch.cat([row_seq, row_seq.new_zeros(T - row_seq.numel())])
+            lens = (meta.positions + 1).to(torch.int32)
+            if meta.cu_seqlens[-1] < T:
+                lens[meta.cu_seqlens[-1]:] = 0
+            meta._row_tables = (lens.contiguous(), meta.block_table[row_seq].contiguous())
+        return meta._row_tables
+
     def _sparse_prefill(self, q_abs, q_pe, latent, meta: AttnMeta, sel):
         """Sparse MLA for prefill rows: every query row is a one-token 'decode' over its own selection."""
         T = q_abs.shape[0]
-        row_seq = torch.zeros(T, dtype=torch.long, device=q_abs.device)
-        for i in range(len(meta.cu_seqlens) - 1):
-            row_seq[meta.cu_seqlens[i]: meta.cu_seqlens[i + 1]] = i
-        bt = meta.block_table[row_seq]
+        _, bt = self._prefill_row_tables(meta, T)
         return attn_ops.sparse_mla_decode(q_abs, q_pe, latent, bt, sel[0], sel[1], self.cfg.softmax_scale,
                                           self.cfg.kv_lora_rank)
 

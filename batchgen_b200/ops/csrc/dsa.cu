@@ -321,6 +321,68 @@ static EncodeTiledFn get_encode() {
 }
 
 }  // namespace dsa
+
+namespace dsa {
+
+// Indexer queries: RoPE on the leading `rope` dims of every head, per-head e4m3 quantisation, and the per-head
+// scale folded into the head gate (gate_out = gate_in * gate_mul * scale).  q [T, 32, 128] bf16 with row stride
+// ldq; one warp per (token, head), lane l owns dims 4l..4l+3.
+__global__ void __launch_bounds__(256)
+index_q_prepare_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const int* __restrict__ positions,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rope, int interleaved,
+                       const float* __restrict__ gate_in, float gate_mul, uint8_t* __restrict__ q8,
+                       float* __restrict__ gate_out, int heads) {
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int pos = positions[t];
+  const int half = rope / 2;
+  for (int h = threadIdx.x >> 5; h < heads; h += blockDim.x >> 5) {
+    const __nv_bfloat16* src = q + (size_t)t * ldq + (size_t)h * kD + lane * 4;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = __bfloat162float(src[i]);
+    if (interleaved) {
+      if (lane * 4 < rope) {
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int i = (lane * 4) / 2 + p;
+          const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+          const float a = x[2 * p], b = x[2 * p + 1];
+          x[2 * p] = a * c - b * s;
+          x[2 * p + 1] = b * c + a * s;
+        }
+      }
+    } else {
+      const int lanes_half = half / 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d = lane * 4 + i;
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], lanes_half);
+        if (d < rope) {
+          const int j = d % half;
+          const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+          x[i] = (d < half) ? x[i] * c - other * s : x[i] * c + other * s;
+        }
+      }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[i] = __bfloat162float(__float2bfloat16(x[i]));      // the unfused path rounds the rotated query to bf16
+      amax = fmaxf(amax, fabsf(x[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = fmaxf(amax, 1e-4f) / 448.0f;
+    const float inv = 1.0f / sc;
+    __nv_fp8x4_e4m3 packed(make_float4(x[0] * inv, x[1] * inv, x[2] * inv, x[3] * inv));
+    *reinterpret_cast<__nv_fp8x4_e4m3*>(q8 + ((size_t)t * heads + h) * kD + lane * 4) = packed;
+    if (lane == 0) gate_out[(size_t)t * heads + h] = gate_in[(size_t)t * heads + h] * gate_mul * sc;
+  }
+}
+
+}  // namespace dsa
+
 }  // namespace bg
 
 extern "C" {
@@ -335,6 +397,19 @@ int bg_index_k_write(const void* k, int ldk, const void* ln_w, const void* ln_b,
       reinterpret_cast<const __nv_bfloat16*>(k), ldk, reinterpret_cast<const __nv_bfloat16*>(ln_w),
       reinterpret_cast<const __nv_bfloat16*>(ln_b), positions, cos_t, sin_t, rope, interleaved, slots,
       reinterpret_cast<uint8_t*>(cache_k), cache_s, T, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// q [T, heads(32), 128] bf16 (row stride ldq elements) -> q8 [T, heads, 128] e4m3 and gate_out [T, heads] fp32.
+int bg_index_q_prepare(const void* q, long long ldq, const int* positions, const float* cos_t, const float* sin_t,
+                       int rope, int interleaved, const float* gate_in, float gate_mul, void* q8, float* gate_out,
+                       int T, int heads, cudaStream_t stream) {
+  using namespace bg::dsa;
+  if (T <= 0) return 0;
+  if (rope % 8 != 0 || rope > kD || heads <= 0) return -1;
+  index_q_prepare_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q), ldq, positions, cos_t, sin_t,
+                                                rope, interleaved, gate_in, gate_mul,
+                                                reinterpret_cast<uint8_t*>(q8), gate_out, heads);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -40,6 +40,23 @@ def quantize_index_q(q: torch.Tensor, gates: torch.Tensor) -> Tuple[torch.Tensor
     return q8.contiguous(), (gates.float() * s).contiguous()
 
 
+def index_q_prepare(q: torch.Tensor, positions: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
+                    rope: int, interleaved: bool, gates: torch.Tensor, gate_mul: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [T, 32, 128] bf16 (the index-query projection) -> (RoPE on the leading ``rope`` dims, e4m3 per head,
+    ``gates * gate_mul`` with the per-head scale folded in): one kernel for rotate + quantise + gate scaling."""
+    T, H, D = q.shape
+    assert q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D and gates.dtype == torch.float32
+    assert gates.is_contiguous() and positions.dtype == torch.int32
+    q8 = torch.empty(T, H, D, dtype=FP8, device=q.device)
+    g = torch.empty(T, H, dtype=torch.float32, device=q.device)
+    rc = _ext.lib().bg_index_q_prepare(_ext.ptr(q), ctypes.c_longlong(q.stride(0)), _ext.ptr(positions),
+                                       _ext.ptr(cos_table), _ext.ptr(sin_table), ctypes.c_int(rope),
+                                       ctypes.c_int(int(interleaved)), _ext.ptr(gates), ctypes.c_float(gate_mul),
+                                       _ext.ptr(q8), _ext.ptr(g), ctypes.c_int(T), ctypes.c_int(H), _ext.stream())
+    _ext.check(rc, "bg_index_q_prepare")
+    return q8, g
+
+
 def indexer_scores(q8, gates, cache_k, cache_s, block_table, lengths, max_len: int) -> torch.Tensor:
     """-> fp32 scores [B, max_len] (entries past a row's length are undefined)."""
     B = q8.shape[0]
@@ -67,8 +84,9 @@ def topk_select(scores: torch.Tensor, lengths: torch.Tensor, k: int) -> Tuple[to
     return idx, n
 
 
-def indexer_select(q, gates, cache_k, cache_s, block_table, lengths, topk: int, max_len: int):
-    q8, g = quantize_index_q(q, gates)
+def indexer_select(q, gates, cache_k, cache_s, block_table, lengths, topk: int, max_len: int, prepared: bool = False):
+    """``prepared``: ``q`` / ``gates`` already come from ``index_q_prepare`` (e4m3 queries, scaled gates)."""
+    q8, g = (q, gates) if prepared else quantize_index_q(q, gates)
     scores = indexer_scores(q8, g, cache_k, cache_s, block_table, lengths, max_len)
     return topk_select(scores, lengths, topk)
 

@@ -46,6 +46,27 @@ def test_index_k_write(interleaved):
     assert (cs.view(-1)[untouched] == 0).all()
 
 
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_index_q_prepare_matches_rotate_then_quantise(interleaved):
+    T, H, D, rope = 300, 32, 128, 64
+    q = torch.randn(T, H, D, device=DEV).to(torch.bfloat16)
+    gates = torch.randn(T, H, device=DEV)
+    pos = torch.randint(0, 4000, (T,), device=DEV, dtype=torch.int32)
+    inv = ref.rope_inv_freq(rope, 10000.0)
+    ang = torch.arange(4096, dtype=torch.float32).unsqueeze(-1) * inv
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    q8, g = dsa.index_q_prepare(q, pos, cos, sin, rope, interleaved, gates, 0.125)
+    c, s_ = cos[pos.long()].unsqueeze(1), sin[pos.long()].unsqueeze(1)
+    qr = torch.cat([ref.apply_rope(q[..., :rope].float(), c, s_, interleaved), q[..., rope:].float()], -1)
+    qr = qr.to(torch.bfloat16)
+    want8, wantg = dsa.quantize_index_q(qr, gates * 0.125)
+    deq_got = q8.float() * (g / (gates * 0.125)).unsqueeze(-1)
+    deq_want = want8.float() * (wantg / (gates * 0.125)).unsqueeze(-1)
+    assert torch.allclose(g, wantg, rtol=1e-5, atol=1e-8)
+    assert (deq_got - deq_want).abs().max() <= 0.07 * qr.float().abs().max()      # one e4m3 step at the top binade
+    assert (deq_got - qr.float()).norm() / qr.float().norm() < 0.04
+
+
 def _keys(lens, seed=0):
     g = torch.Generator(device=DEV).manual_seed(seed)
     S = 64
