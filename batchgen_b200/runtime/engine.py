@@ -117,6 +117,8 @@ class Engine:
         # host-KV reservation chunk follows the decode lengths actually seen (EMA), from the configured start value
         self.chunk_sizer = AdaptiveChunkSizer(initial_chunk=ecfg.host_kv_chunk_size,
                                               min_chunk=min(1024, ecfg.host_kv_chunk_size))
+        from ..utils.step_ring import StepRing
+        self.step_ring = StepRing(256)                     # the most recent forwards, for heartbeats and fatal messages
         self._deferred_gpu: List[tuple] = []               # (transfer tasks, device pages freed when they are done)
         self._deferred_host: List[tuple] = []              # (transfer tasks, host pages released when they are done)
         self.host_state = None
@@ -504,6 +506,7 @@ class Engine:
             num_valid=torch.tensor([T], dtype=torch.int32, device=dev) if W > 1 else None)
         ids_t = torch.tensor(ids, dtype=torch.int32, device=dev)
         self.stats.prefill_tokens += T
+        self.step_ring.record("prefill", len(rows), T)
         if W > 1:
             logits = self.model.forward_sp(ids_t, meta, self.kv)      # wanted rows that this rank owns
             toks = self._sample_sharded(logits, group, logit_rows, T + pad) if group else []
@@ -878,6 +881,7 @@ class Engine:
                     self._retire_decode(pending)
                 pending = nxt
             steps += 1
+            self.step_ring.record("decode", len(live), len(live))
             if self.step_hook is not None:
                 self.step_hook("decode")
         if pending is not None:

@@ -21,6 +21,7 @@ import ctypes
 import os
 import queue as queue_mod
 import signal
+import sys
 import time
 import traceback
 from typing import Any, Dict, List, Optional
@@ -47,7 +48,7 @@ def setup_nccl_env() -> None:
 _STORES: list = []
 
 
-def build_engine(args, rank: int, world: int, device: str):
+def build_engine(args, rank: int, world: int, device: str, phases=None):
     import torch
 
     from ..config import get_model_config
@@ -97,12 +98,16 @@ def build_engine(args, rank: int, world: int, device: str):
             a2a = (ecfg.max_decode_batch + 8 * world) * (cfg.num_heads // world) * cfg.kv_cache_dim * 2
         comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
                        max_tokens=step_rows, a2a_bytes=a2a)
+    if phases is not None:
+        phases.enter(rank, "kv-pool")
     pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
     host_fd = None
     if getattr(args, "host_kv_region", "") and device.startswith("cuda"):
         host_fd = os.open(args.host_kv_region, os.O_RDWR)      # the server's region: same pages for every worker
     eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages, host_kv_fd=host_fd)
     if device.startswith("cuda") and ecfg.enable_cuda_graph:
+        if phases is not None:
+            phases.enter(rank, "graph-capture")
         from ..runtime.graphs import DecodeGraphRunner
         max_pages = -(-eng.kv_token_budget // ecfg.page_size)
         eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=ecfg.max_decode_batch,
@@ -128,11 +133,20 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
         if rank == 0:
             response_queue.put(msg)
 
+    from .startup_phases import record_of
+    phases = record_of(args)
+    import faulthandler
+    try:                                                  # SIGUSR1 -> stack dump of every thread (watchdog asks for it)
+        stack_file = open(os.path.join(args.log_dir, f"worker{rank}.stacks"), "a") if args.log_dir else sys.stderr
+        faulthandler.register(signal.SIGUSR1, file=stack_file, all_threads=True)
+    except (OSError, ValueError, AttributeError):
+        pass
     try:
         use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
         device = f"cuda:{rank}" if use_cuda else "cpu"
         if use_cuda:
             torch.cuda.set_device(rank)
+        phases.enter(rank, "communicator-init")
         if world > 1:
             setup_nccl_env()
             dist.init_process_group("nccl" if use_cuda else "gloo", init_method=f"tcp://{args.dist_init_addr}",
@@ -140,7 +154,9 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             t = torch.ones(1, device=device)
             dist.all_reduce(t)                        # warm-up: the first collective builds the communicators
         from ..runtime.sequence import SamplingParams
-        cfg, eng = build_engine(args, rank, world, device)
+        phases.enter(rank, "model-build")
+        cfg, eng = build_engine(args, rank, world, device, phases=phases)
+        phases.enter(rank, "prewarm")
         log.info("worker.ready", rank=rank, device=device, gpu_pages=eng.kv.num_pages,
                  host_pages=eng.host_kv.num_pages if eng.host_kv else 0)
         up({"type": "deployment_capacity", "gpu_pages": eng.kv.num_pages, "page_size": eng.buf.page_size,
@@ -148,6 +164,7 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             "model": cfg.name, "vocab_size": cfg.vocab_size})
         if world > 1:
             dist.barrier()
+        phases.enter(rank, "serving")
         if rank == 0:
             ready_event.set()
 
@@ -266,12 +283,14 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             if rank == 0 and time.monotonic() - last_beat > 5.0:
                 last_beat = time.monotonic()
                 up({"type": "heartbeat", "ts": time.time(), "live": len(eng.seqs), "free_pages": eng.kv.alloc.num_free,
-                    "stats": eng.stats.summary(), "query_book": {"active": book.active_count,
+                    "stats": eng.stats.summary(), "steps": eng.step_ring.summary(), "query_book": {"active": book.active_count,
                                                                   "free_pages": book.free_page_count}})
         log.info("worker.shutdown", rank=rank)
     except Exception as ex:  # noqa: BLE001
         log.error("worker.fatal", rank=rank, error=str(ex), trace=traceback.format_exc()[-1500:])
-        response_queue.put({"type": "worker_fatal", "rank": rank, "error": f"{type(ex).__name__}: {ex}"})
+        recent = eng.step_ring.tail(8) if "eng" in locals() else []
+        response_queue.put({"type": "worker_fatal", "rank": rank, "error": f"{type(ex).__name__}: {ex}",
+                            "recent_steps": recent})
         raise
     finally:
         try:

@@ -76,6 +76,9 @@ class WorkerManager:
         self.host_region = None                           # node-shared host KV region (core.native.HostPagedKV)
         self.weight_store = None                          # node-shared weights (core.native.ParameterStore)
         self.weight_index: Optional[Dict] = None
+        self.startup = None                               # server.startup_phases.StartupRecord of the current cohort
+        self.startup_budgets: Optional[Dict[str, float]] = None      # None: the module's defaults
+        self.kernel_log_path = "/dev/kmsg"
         self._lock = threading.RLock()
         self.watchdog: Optional[Watchdog] = None
         self.phase = "idle"
@@ -104,20 +107,37 @@ class WorkerManager:
             self.last_error = None
             W = self.args.world_size
             self.procs = []
+            from . import startup_phases
+            self.startup = startup_phases.StartupRecord(W + 1, self.ctx)    # slot W: the server's own phases
+            self.args.startup_record = self.startup
             self._create_host_region()
-            self._load_weight_store()
+            with self.startup.phase(W, "store-staging"):
+                self._load_weight_store()
+            self.startup.enter(W, "serving")
             for r in range(W):
                 self.args.param_store_index = self.weight_index      # travels with the pickled arguments
                 p = self.ctx.Process(target=target, name=f"bg-worker-{r}",
                                      args=(r, W, self.args, self.request_queue, self.response_queue, self._ready,
                                            self._shutdown, self.feed), daemon=True)
                 p.start()
+                self.startup.enter(r, "spawned")
                 self.procs.append(p)
         deadline = time.monotonic() + (timeout or self.args.startup_timeout)
         while not self._ready.wait(0.1):
             dead = [p for p in self.procs if not p.is_alive()]
             if dead:
-                self.last_error = f"worker {dead[0].name} exited with code {dead[0].exitcode} during start-up"
+                self.last_error = (f"worker {dead[0].name} exited with code {dead[0].exitcode} during start-up"
+                                   f"{self._oom_note(dead)} (phases: {self.startup.snapshot()})")
+                self._kill_all()
+                self.state = "failed"
+                raise WorkerStartError(self.last_error)
+            stalled = self.startup.stalled(self.startup_budgets)
+            if stalled:
+                slot, phase, sec, limit = stalled[0]
+                who = f"rank {slot}" if slot < self.args.world_size else "the server"
+                self.last_error = (f"start-up stalled: {who} has been in phase '{phase}' for {sec:.0f} s "
+                                   f"(budget {limit:.0f} s)")
+                self._dump_stacks()
                 self._kill_all()
                 self.state = "failed"
                 raise WorkerStartError(self.last_error)
@@ -195,8 +215,29 @@ class WorkerManager:
         log.info("server.weight_store_loaded", bytes=loaded, tensors=len(self.weight_index),
                  seconds=round(time.monotonic() - t0, 2), path=a.param_store_path)
 
+    def _oom_note(self, procs) -> str:
+        """', killed by the kernel OOM killer' when the kernel log says so for one of ``procs``."""
+        if not any(p.exitcode in (-9, 137) for p in procs):
+            return ""
+        from . import oom_attribution
+        rec = oom_attribution.attribute([p.pid for p in procs if p.pid], self.kernel_log_path)
+        return f": {rec.describe()}" if rec is not None else ""
+
+    def _dump_stacks(self) -> None:
+        """Ask every live worker for a Python stack dump (they register SIGUSR1 with ``faulthandler``; the dump goes
+        to the worker's log directory or stderr) before the cohort is killed."""
+        import signal
+        for p in self.procs:
+            if p.is_alive() and p.pid:
+                try:
+                    os.kill(p.pid, signal.SIGUSR1)
+                except OSError:
+                    pass
+        time.sleep(0.3)
+
     def _on_stall(self, elapsed: float) -> None:
         self.last_error = f"watchdog: no engine step for {elapsed:.1f} s while work was pending"
+        self._dump_stacks()
         self._fail_cohort(self.last_error)
 
     def _monitor_loop(self) -> None:
@@ -205,7 +246,7 @@ class WorkerManager:
                 continue
             dead = [p for p in self.procs if not p.is_alive()]
             if dead:
-                self._fail_cohort(f"worker {dead[0].name} exited with code {dead[0].exitcode}")
+                self._fail_cohort(f"worker {dead[0].name} exited with code {dead[0].exitcode}{self._oom_note(dead)}")
                 return
 
     def _fail_cohort(self, reason: str) -> None:

@@ -312,3 +312,67 @@ def test_run_guard_locks_instance_adopts_lease_and_reclaims(tmp_path, monkeypatc
     assert dead_run in nxt.reclaimed and nxt.lease is None
     assert run_guard.join_run(ServerArgs()) is None           # unguarded server (in-process tests)
     nxt.close()
+
+
+# ---------------------------------------------------------------------------------------------- start-up phases, OOM, step ring
+def test_startup_record_names_the_stalled_phase():
+    from batchgen_b200.server import startup_phases as sp
+    rec = sp.StartupRecord(3)
+    assert rec.read(0) is None and rec.stalled() == []
+    rec.enter(0, "communicator-init")
+    rec.enter(1, "model-build")
+    t = rec.read(1)[1]
+    assert rec.read(0)[0] == "communicator-init" and rec.snapshot()[1][0] == "model-build"
+    # rank 1 has sat in model-build past its budget; rank 0 moved on in time, slot 2 never started
+    rec.enter(0, "serving")
+    got = rec.stalled({"model-build": 5.0, "communicator-init": 5.0}, now=t + 9.0)
+    assert [(s, p) for s, p, _, _ in got] == [(1, "model-build")] and 8.9 < got[0][2] < 9.5 and got[0][3] == 5.0
+    assert rec.stalled({"model-build": 50.0}, now=t + 9.0) == []
+    with rec.phase(2, "kv-pool"):
+        assert rec.read(2)[0] == "kv-pool"
+    null = sp.record_of(object())
+    null.enter(0, "model-build")                           # a worker without a manager reports to nobody
+
+
+def test_worker_manager_fails_a_start_that_sits_in_one_phase(tmp_path):
+    """A worker that never leaves communicator-init: the manager names rank and phase instead of waiting for the
+    total start-up timeout."""
+    from batchgen_b200.server.server_args import ServerArgs
+    from batchgen_b200.server.worker_manager import WorkerManager, WorkerStartError
+    args = ServerArgs(model="tiny-deepseek-v3", device="cpu", startup_timeout=60.0, storage_path=str(tmp_path))
+    wm = WorkerManager(args, worker_target=_stuck_worker)
+    wm.startup_budgets = {"communicator-init": 1.0}
+    t0 = time.monotonic()
+    with pytest.raises(WorkerStartError, match="rank 0 has been in phase 'communicator-init'"):
+        wm.start()
+    assert time.monotonic() - t0 < 30 and wm.state == "failed"
+
+
+def _stuck_worker(rank, world, args, rq, wq, ready, shutdown, feed):
+    from batchgen_b200.server.startup_phases import record_of
+    record_of(args).enter(rank, "communicator-init")
+    time.sleep(120)
+
+
+def test_oom_attribution_reads_the_kernel_log(tmp_path):
+    from batchgen_b200.server import oom_attribution as oa
+    log = tmp_path / "kmsg"
+    log.write_text(
+        "6,1200,5000,-;usb 1-1: new device\\n"
+        "3,1201,6000,-;Out of memory: Killed process 4242 (bg-worker-1) total-vm:9000000kB, anon-rss:73400320kB, file-rss:0kB\\n"
+        "6,1202,7000,-;oom-kill:constraint=CONSTRAINT_NONE,nodemask=(null),task=python,pid=777,uid=0\\n")
+    rec = oa.attribute([1, 4242], str(log))
+    assert rec is not None and rec.pid == 4242 and rec.comm == "bg-worker-1" and rec.anon_rss_kb == 73400320
+    assert "OOM killer" in rec.describe() and "70.0 GiB" in rec.describe()
+    assert oa.attribute([777], str(log)).comm == "python"
+    assert oa.attribute([5], str(log)) is None and oa.attribute([5], str(tmp_path / "missing")) is None
+
+
+def test_step_ring_keeps_the_latest_events():
+    from batchgen_b200.utils.step_ring import StepRing
+    r = StepRing(4)
+    for i in range(6):
+        r.record("decode" if i % 2 else "prefill", rows=i, tokens=10 * i, seconds=0.001 * (i + 1))
+    assert len(r) == 4 and [e["rows"] for e in r.tail(10)] == [2, 3, 4, 5]
+    s = r.summary()
+    assert s["decode"]["events"] == 2 and s["decode"]["tokens"] == 80 and abs(s["decode"]["max_ms"] - 6.0) < 1e-6
