@@ -251,6 +251,38 @@ inline bool ensure_dynamic_smem(Kernel kernel, size_t bytes, DeviceOnce& once) {
   return true;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel starts with pdl_prologue(): it lets the next kernel of the stream begin launching (its blocks take
+// free SMs and run their own prologue) and then waits until the kernels it depends on have completed and their
+// writes are visible.  Without the launch attribute both instructions do nothing.  launch_pdl() sets the attribute,
+// so the gap between two kernels of a captured step shrinks from a full launch to the dependency hand-over.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("BG_PDL");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
                float* __restrict__ out_s, int s_stride, int H, int ldx, int ldo, float eps, int pow2) {
+  bg::pdl_prologue();
   extern __shared__ float row[];  // H floats
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -118,6 +119,7 @@ __global__ void __launch_bounds__(256)
 act_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int s_stride,
                  int T, int K, int ldx, int pow2, const int* __restrict__ valid_rows,
                  const int* __restrict__ row_src) {
+  bg::pdl_prologue();
   const int t = blockIdx.x;
   if (valid_rows != nullptr && t >= *valid_rows) return;
   if (row_src != nullptr && row_src[t] < 0) return;      // padding row of an expert segment: nothing reads it
@@ -167,6 +169,7 @@ mla_kv_write_kernel(const __nv_bfloat16* __restrict__ kv_a, int ld, const __nv_b
                     const int* __restrict__ positions, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, const long long* __restrict__ slots,
                     __nv_bfloat16* __restrict__ cache, int kv_lora, int rope, float eps, int interleaved) {
+  bg::pdl_prologue();
   __shared__ float red[32];
   const int t = blockIdx.x;
   const long long slot = slots[t];
@@ -201,6 +204,7 @@ mla_kv_write_kernel(const __nv_bfloat16* __restrict__ kv_a, int ld, const __nv_b
 __global__ void rope_q_kernel(__nv_bfloat16* __restrict__ q, int H, int D, int rope, const int* __restrict__ positions,
                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int interleaved,
                               long long ld_t) {
+  bg::pdl_prologue();
   const int t = blockIdx.x;
   const int half = rope / 2;
   const int pos = positions[t];
@@ -234,7 +238,7 @@ int bg_rmsnorm(const void* x, void* residual, const void* w, void* out, void* ou
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
   auto Q = reinterpret_cast<uint8_t*>(out_q);
 #define BG_LAUNCH(ADD, QNT)                                                                                      \
-  rmsnorm_kernel<ADD, QNT><<<T, kNormThreads, smem, stream>>>(X, R, W, O, Q, out_s, s_stride, H, ldx, ldo, eps, pow2)
+  bg::launch_pdl(rmsnorm_kernel<ADD, QNT>, dim3(T), dim3(kNormThreads), smem, stream, X, R, W, O, Q, out_s, s_stride, H, ldx, ldo, eps, pow2)
   if (residual != nullptr && out_q != nullptr) BG_LAUNCH(true, true);
   else if (residual != nullptr) BG_LAUNCH(true, false);
   else if (out_q != nullptr) BG_LAUNCH(false, true);
@@ -253,8 +257,8 @@ int bg_act_quant(int mode, const void* x, void* q, float* s, int s_stride, int T
   const int threads = K / 8 >= 256 ? 256 : ((K / 8 + 31) / 32) * 32;
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
   auto Q = reinterpret_cast<uint8_t*>(q);
-  if (mode == 0) act_quant_kernel<0><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
-  else act_quant_kernel<1><<<T, threads, 0, stream>>>(X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
+  if (mode == 0) bg::launch_pdl(act_quant_kernel<0>, dim3(T), dim3(threads), 0, stream, X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
+  else bg::launch_pdl(act_quant_kernel<1>, dim3(T), dim3(threads), 0, stream, X, Q, s, s_stride, T, K, ldx, pow2, valid_rows, row_src);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -263,7 +267,7 @@ int bg_mla_kv_write(const void* kv_a, int ld, const void* w, const int* position
                     int interleaved, cudaStream_t stream) {
   using namespace bg;
   if (T <= 0) return 0;
-  mla_kv_write_kernel<<<T, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(kv_a), ld,
+  bg::launch_pdl(mla_kv_write_kernel, dim3(T), dim3(128), 0, stream, reinterpret_cast<const __nv_bfloat16*>(kv_a), ld,
                                              reinterpret_cast<const __nv_bfloat16*>(w), positions, cos_t, sin_t, slots,
                                              reinterpret_cast<__nv_bfloat16*>(cache), kv_lora, rope, eps, interleaved);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -273,7 +277,7 @@ int bg_rope_q(void* q, int T, int H, int D, int rope, const int* positions, cons
               int interleaved, long long ld_t, cudaStream_t stream) {
   using namespace bg;
   if (T <= 0) return 0;
-  rope_q_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(q), H, D, rope, positions, cos_t, sin_t,
+  bg::launch_pdl(rope_q_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<__nv_bfloat16*>(q), H, D, rope, positions, cos_t, sin_t,
                                        interleaved, ld_t);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -109,6 +109,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  bg::pdl_prologue();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = smem;
@@ -219,9 +220,9 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     bool ok = true;
     const bool remote_a = (p.a_ready != nullptr);
     for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
-      float r[64];
+      float2 r2[32];                                // 64 fp32 accumulators as pairs: promotion uses packed FMAs
 #pragma unroll
-      for (int j = 0; j < 64; ++j) r[j] = 0.f;
+      for (int j = 0; j < 32; ++j) r2[j] = make_float2(0.f, 0.f);
       const int row = t.m0 + row_in_tile;
       const bool row_ok = row < t.m_end;
       const float* sa_ptr = p.sA + row;
@@ -260,14 +261,20 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + slice * 64;
         const float s_lo = sa * sbl, s_hi = sa * sbh;
+        const float2 s_lo2 = make_float2(s_lo, s_lo), s_hi2 = make_float2(s_hi, s_hi);
+        // two 16-column chunks in flight: chunk c + 1 is read from TMEM while chunk c is promoted, and the promotion
+        // is 8 packed FMAs (fma.rn.f32x2) per chunk instead of 16 scalar ones
+        uint32_t v[2][16];
+        tmem_ld16(taddr, v[0]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[16];
-          tmem_ld16(taddr + c * 16, v);
           tmem_ld_wait();
-          const float sc = c < 2 ? s_lo : s_hi;
+          if (c + 1 < 4) tmem_ld16(taddr + (c + 1) * 16, v[(c + 1) & 1]);
+          const float2 sc = c < 2 ? s_lo2 : s_hi2;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) r[c * 16 + j] = fmaf(__uint_as_float(v[j]), sc, r[c * 16 + j]);
+          for (int j = 0; j < 8; ++j)
+            r2[c * 8 + j] = __ffma2_rn(make_float2(__uint_as_float(v[c & 1][2 * j]), __uint_as_float(v[c & 1][2 * j + 1])),
+                                       sc, r2[c * 8 + j]);
         }
         tc_fence_before();
         __syncwarp();
@@ -285,7 +292,8 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q)
-                o[q] = __floats2bfloat162_rn(silu(r[j + 2 * q]) * r[32 + j + 2 * q], silu(r[j + 2 * q + 1]) * r[32 + j + 2 * q + 1]);
+                o[q] = __floats2bfloat162_rn(silu(r2[j / 2 + q].x) * r2[16 + j / 2 + q].x,
+                                             silu(r2[j / 2 + q].y) * r2[16 + j / 2 + q].y);
               *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(o);
             }
           }
@@ -302,11 +310,11 @@ gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (col0 + j + 8 <= p.N) {
               __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(r[j + 2 * q], r[j + 2 * q + 1]);
+              for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(r2[j / 2 + q].x, r2[j / 2 + q].y);
               *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(o);
             } else {
               for (int q = 0; q < 8; ++q)
-                if (col0 + j + q < p.N) dst[j + q] = __float2bfloat16(r[j + q]);
+                if (col0 + j + q < p.N) dst[j + q] = __float2bfloat16((q & 1) ? r2[(j + q) / 2].y : r2[(j + q) / 2].x);
             }
           }
         }
@@ -372,7 +380,7 @@ static int launch(const void* A, const void* B, const Params& p, int b_rows, int
   long long grid = m_tiles * n_tiles;
   if (grid > num_sms) grid = num_sms;
   if (grid < 1) grid = 1;
-  kern<<<(int)grid, kThreads, smem, stream>>>(ta, tb, p);
+  bg::launch_pdl(kern, dim3((int)grid), dim3(kThreads), smem, stream, ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 

@@ -107,6 +107,7 @@ struct Walker {
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, Params p) {
+  bg::pdl_prologue();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_tiles = smem;                                   // kStages x 16 KB
@@ -394,7 +395,7 @@ static int launch(const void* X, const void* W, const Params& p, int w_rows, int
   auto kern = gemm_fp8_swapab_kernel<EPI>;
   const size_t smem = kStages * (BW + BT) * BKB + sizeof(Shared) + 1024;
   if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
-  kern<<<num_sms, kThreads, smem, stream>>>(tw, tx, p);
+  bg::launch_pdl(kern, dim3(num_sms), dim3(kThreads), smem, stream, tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 

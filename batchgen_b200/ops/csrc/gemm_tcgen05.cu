@@ -132,6 +132,7 @@ struct TileWalker {
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  bg::pdl_prologue();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: operand stages first (1024-byte aligned), bookkeeping after
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -342,10 +343,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) mbar_arrive(&ss.tmem_empty[buf]);
         const float s_lo = sa * sbl, s_hi = sa * sbh;
+        const float2 s_lo2 = make_float2(s_lo, s_lo), s_hi2 = make_float2(s_hi, s_hi);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          r[j] = fmaf(__uint_as_float(v0[j]), s_lo, r[j]);
-          r[32 + j] = fmaf(__uint_as_float(v1[j]), s_hi, r[32 + j]);
+        for (int j = 0; j < 32; j += 2) {              // packed FMAs (fma.rn.f32x2): half the issue slots
+          const float2 a = __ffma2_rn(make_float2(__uint_as_float(v0[j]), __uint_as_float(v0[j + 1])), s_lo2,
+                                      make_float2(r[j], r[j + 1]));
+          const float2 b = __ffma2_rn(make_float2(__uint_as_float(v1[j]), __uint_as_float(v1[j + 1])), s_hi2,
+                                      make_float2(r[32 + j], r[33 + j]));
+          r[j] = a.x;
+          r[j + 1] = a.y;
+          r[32 + j] = b.x;
+          r[33 + j] = b.y;
         }
       }
       if (!ok) break;
@@ -527,7 +535,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
     if (tiles < grid) grid = tiles;
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, kThreads, smem, stream>>>(tmA, tmB, p);
+  bg::launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 

@@ -40,6 +40,7 @@ template <int BN> struct Shared {
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 head_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, Params p, int* status) {
+  bg::pdl_prologue();
   constexpr int kABytes = BM * 128, kWBytes = BN * 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -168,7 +169,7 @@ static int launch(const CUtensorMap& a, const CUtensorMap& w, const Params& p, i
   const size_t smem = kStages * (BM * 128 + BN * 128) + sizeof(Shared<BN>) + 1024;
   if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
   dim3 grid((p.T + BM - 1) / BM, H, (p.N + BN - 1) / BN);
-  kern<<<grid, kThreads, smem, stream>>>(a, w, p, status);
+  bg::launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, a, w, p, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 

@@ -159,6 +159,7 @@ struct TileCursor {
 __global__ void __launch_bounds__(kPersistThreads, 1)
 mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                           const __grid_constant__ CUtensorMap tm_qpe, PersistParams p) {
+  bg::pdl_prologue();
   constexpr int NS = 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -666,7 +667,7 @@ int bg_mla_decode_persist(const void* q_abs, long long qabs_stride, const void* 
   static bg::DeviceOnce attr_set;
   const size_t smem = kPSmemTiles + sizeof(PersistShared) + 1024;
   if (!bg::ensure_dynamic_smem(mla_decode_persist_kernel, smem, attr_set)) return -13;
-  mla_decode_persist_kernel<<<ctas, kPersistThreads, smem, stream>>>(tkv, tq, tqpe, p);
+  bg::launch_pdl(mla_decode_persist_kernel, dim3(ctas), dim3(kPersistThreads), smem, stream, tkv, tq, tqpe, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -14;
 }
 

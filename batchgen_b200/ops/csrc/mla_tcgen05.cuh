@@ -205,6 +205,7 @@ template <int NCOL>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
            const __grid_constant__ CUtensorMap tm_qpe, Params p) {
+  bg::pdl_prologue();
   using C = Cfg<NCOL>;
   constexpr int NS = 128;                                       // softmax threads
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -507,6 +508,7 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
 static __global__ void __launch_bounds__(128)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
                  __nv_bfloat16* __restrict__ out, int ncol, int H, int hpg) {
+  bg::pdl_prologue();
   // items[i] = {q_row, n_q, head_group, first_slot, n_splits}
   const int* it = items + blockIdx.x * 5;
   const int q_row = it[0], n_q = it[1], hg = it[2], first = it[3], ns = it[4];
@@ -579,7 +581,7 @@ static int launch(const CUtensorMap& kv, const CUtensorMap& q, const CUtensorMap
   auto kern = mla_kernel<NCOL>;
   const size_t smem = Cfg<NCOL>::kSmemTiles + sizeof(Shared) + 1024;
   if (!prepare_device<NCOL>()) return -12;
-  kern<<<n_work, kThreads, smem, stream>>>(kv, q, qpe, p);
+  bg::launch_pdl(kern, dim3(n_work), dim3(kThreads), smem, stream, kv, q, qpe, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 

@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
                    float* __restrict__ w_out, int T, int E, int K, int n_group, int topk_group, int norm, float scale,
                    int softmax_mode, const int* __restrict__ num_valid) {
+  bg::pdl_prologue();
   __shared__ float choice_s[4][kMaxExperts];
   __shared__ float score_s[4][kMaxExperts];
   __shared__ float group_s[4][32];
@@ -116,6 +117,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 __global__ void __launch_bounds__(1024)
 moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int lo, int hi, int align, int* __restrict__ offsets,
                  int* __restrict__ cursor, const int* __restrict__ num_valid, int K) {
+  bg::pdl_prologue();
   __shared__ int cnt[kMaxExperts];
   const int El = hi - lo;
   for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
@@ -140,6 +142,7 @@ moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int lo, int hi, 
 __global__ void moe_scatter_kernel(const int* __restrict__ topk_idx, int n_pairs, int K, int lo, int hi,
                                    const int* __restrict__ offsets, int* __restrict__ cursor, int* __restrict__ pos,
                                    int* __restrict__ src_row, const int* __restrict__ num_valid) {
+  bg::pdl_prologue();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int limit = (num_valid != nullptr) ? *num_valid * K : n_pairs;
@@ -160,6 +163,7 @@ __global__ void __launch_bounds__(256)
 moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const int* __restrict__ src_row,
                         const int* __restrict__ total_rows, uint8_t* __restrict__ q, float* __restrict__ s,
                         int s_stride, int K, int pow2, int zero_padding) {
+  bg::pdl_prologue();
   const int r = blockIdx.x;
   if (r >= *total_rows) return;
   const int src = src_row[r];
@@ -200,6 +204,7 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __restrict__ pos,
                    const float* __restrict__ w, const __nv_bfloat16* __restrict__ extra, int lde,
                    __nv_bfloat16* __restrict__ out, int ldo, int K, int H, int out_fp32) {
+  bg::pdl_prologue();
   const int t = blockIdx.x;
   __shared__ int p_s[kMaxTopK];
   __shared__ float w_s[kMaxTopK];
@@ -258,7 +263,7 @@ int bg_router_topk(const float* logits, const float* bias, int* idx, float* w, i
   using namespace bg;
   if (T <= 0) return 0;
   if (E > kMaxExperts || K > kMaxTopK || n_group > 32 || (n_group > 1 && E % n_group != 0)) return -1;
-  router_topk_kernel<<<(T + 3) / 4, 128, 0, stream>>>(logits, bias, idx, w, T, E, K, n_group, topk_group, norm, scale,
+  bg::launch_pdl(router_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, bias, idx, w, T, E, K, n_group, topk_group, norm, scale,
                                                       softmax_mode, num_valid);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -270,9 +275,9 @@ int bg_moe_permute(const int* topk_idx, int T, int K, int lo, int hi, int align,
   if (hi - lo > kMaxExperts) return -1;
   if (cudaMemsetAsync(src_row, 0xFF, (size_t)cap * sizeof(int), stream) != cudaSuccess) return -3;
   const int n_pairs = T * K;
-  moe_count_kernel<<<1, 1024, 0, stream>>>(topk_idx, n_pairs, lo, hi, align, offsets, cursor, num_valid, K);
+  bg::launch_pdl(moe_count_kernel, dim3(1), dim3(1024), 0, stream, topk_idx, n_pairs, lo, hi, align, offsets, cursor, num_valid, K);
   if (n_pairs > 0)
-    moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(topk_idx, n_pairs, K, lo, hi, offsets, cursor, pos,
+    bg::launch_pdl(moe_scatter_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0, stream, topk_idx, n_pairs, K, lo, hi, offsets, cursor, pos,
                                                                  src_row, num_valid);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -282,7 +287,7 @@ int bg_moe_gather_quant(const void* hidden, int ldh, const int* src_row, const i
   using namespace bg;
   if (cap <= 0) return 0;
   if (K % 128 != 0) return -1;
-  moe_gather_quant_kernel<<<cap, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, src_row,
+  bg::launch_pdl(moe_gather_quant_kernel, dim3(cap), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, src_row,
                                                    total_rows, reinterpret_cast<uint8_t*>(q), s, s_stride, K, pow2, zero_padding);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -292,7 +297,7 @@ int bg_moe_combine(const void* y, int ldy, const int* pos, const float* w, const
   using namespace bg;
   if (T <= 0) return 0;
   if (K > kMaxTopK || H % 8 != 0) return -1;
-  moe_combine_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(y), ldy, pos, w,
+  bg::launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(y), ldy, pos, w,
                                             reinterpret_cast<const __nv_bfloat16*>(extra), lde,
                                             reinterpret_cast<__nv_bfloat16*>(out), ldo, K, H, out_fp32);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(kSampThreads)
 sample_kernel(const T* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ out, int* __restrict__ bad_rows) {
+  bg::pdl_prologue();
   __shared__ float red[33];
   __shared__ float redv[32];
   __shared__ int redi[32];
@@ -190,10 +191,10 @@ int bg_sample(int dtype, const void* logits, long long ld, int T, int V, const f
   if (T <= 0) return 0;
   if (temperature != nullptr && uniform == nullptr) return -1;
   if (dtype == 0)
-    sample_kernel<float><<<T, kSampThreads, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, V, temperature,
+    bg::launch_pdl(sample_kernel<float>, dim3(T), dim3(kSampThreads), 0, stream, reinterpret_cast<const float*>(logits), ld, V, temperature,
                                                           top_k, top_p, uniform, out, bad_rows);
   else
-    sample_kernel<__nv_bfloat16><<<T, kSampThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld,
+    bg::launch_pdl(sample_kernel<__nv_bfloat16>, dim3(T), dim3(kSampThreads), 0, stream, reinterpret_cast<const __nv_bfloat16*>(logits), ld,
                                                                   V, temperature, top_k, top_p, uniform, out, bad_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -76,6 +76,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
                           Peers ag_s, int ag_s_stride, int push, int rows, int H, float eps, int my_rank, int world,
                           Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter, int* status,
                           int has_residual) {
+  bg::pdl_prologue();
   const uint32_t wait_epoch = wait_epoch_e.get();
   const uint32_t epoch = epoch_e.get();
   extern __shared__ float rowbuf[];
@@ -186,6 +187,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
 __global__ void __launch_bounds__(1024)
 ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers cnt, int my_rank, int world, Peers flags,
                      int ready_index, Epoch epoch_e, int2* __restrict__ row_info, int row_cap) {
+  bg::pdl_prologue();
   const uint32_t epoch = epoch_e.get();
   __shared__ int c[kMaxExperts];
   for (int e = threadIdx.x; e < E; e += blockDim.x) c[e] = 0;
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(1024)
 ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, Epoch epoch_e, int E, int world,
                  int my_rank, int align, int* __restrict__ row_base, int* __restrict__ offsets,
                  int* __restrict__ cursor, int* __restrict__ total_rows, int* status) {
+  bg::pdl_prologue();
   __shared__ int tot[kMaxExperts];
   __shared__ int mine[kMaxExperts];
   __shared__ int seg[kMaxExperts];
@@ -273,6 +276,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
                         Peers recv_s, int recv_s_stride, Peers recv_info, int recv_cap, int* __restrict__ sent_row,
                         int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter,
                         int* status) {
+  bg::pdl_prologue();
   const uint32_t epoch = epoch_e.get();
   __shared__ int dest_rank[16], dest_row[16];
   const int t = blockIdx.x;
@@ -328,6 +332,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
 }
 
 __global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, int* status, uint64_t budget_ns) {
+  bg::pdl_prologue();
   const uint32_t epoch = epoch_e.get();
   if (threadIdx.x < n) {
     if (!wait_flag_ge(flags + threadIdx.x, epoch, status, budget_ns) && status != nullptr)
@@ -345,6 +350,7 @@ __global__ void __launch_bounds__(256)
 a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_t chunk_vec, size_t src_d, size_t src_b,
                 size_t dst_r, size_t dst_b, int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e,
                 unsigned int* counter) {
+  bg::pdl_prologue();
   const uint32_t epoch = epoch_e.get();
   const int d = (my_rank + blockIdx.y) % world;
   const uint4* s = src + (size_t)d * src_d;
@@ -369,10 +375,12 @@ a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_
 }
 
 __global__ void bump_epoch_kernel(uint32_t* base, uint32_t n) {
+  bg::pdl_prologue();
   if (threadIdx.x == 0) *base += n;
 }
 
 __global__ void signal_kernel(Peers flags, int index, int world, Epoch epoch_e) {
+  bg::pdl_prologue();
   const uint32_t epoch = epoch_e.get();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -402,7 +410,7 @@ int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_r
   using namespace bg::comm;
   if (rows <= 0) return 0;
   if (H % 128 != 0 || world > kMaxWorld) return -1;
-  sp_norm_quant_push_kernel<<<rows, 256, (size_t)H * sizeof(float), stream>>>(
+  bg::launch_pdl(sp_norm_quant_push_kernel, dim3(rows), dim3(256), (size_t)H * sizeof(float), stream, 
       reinterpret_cast<const __nv_bfloat16*>(partials), n_src, src_ready, Epoch{wait_epoch, epoch_base},
       reinterpret_cast<__nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<uint8_t*>(loc_q), loc_s, loc_s_stride, to_peers(ag_q, world),
@@ -416,7 +424,7 @@ int bg_ep_count_push(const int* topk_idx, int n_pairs, int E, void* const* cnt, 
                      int row_cap, cudaStream_t stream) {
   using namespace bg::comm;
   if (E > kMaxExperts || world > kMaxWorld) return -1;
-  ep_count_push_kernel<<<1, 1024, 0, stream>>>(topk_idx, n_pairs, E, to_peers(cnt, world), my_rank, world,
+  bg::launch_pdl(ep_count_push_kernel, dim3(1), dim3(1024), 0, stream, topk_idx, n_pairs, E, to_peers(cnt, world), my_rank, world,
                                                to_peers(flags, world), ready_index, Epoch{epoch, epoch_base},
                                                reinterpret_cast<int2*>(row_info), row_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -427,7 +435,7 @@ int bg_ep_layout(const int* cnt, const uint32_t* cnt_ready, uint32_t epoch, cons
                  int* row_base, int* offsets, int* cursor, int* total_rows, int* status, cudaStream_t stream) {
   using namespace bg::comm;
   if (E > kMaxExperts || E % world != 0) return -1;
-  ep_layout_kernel<<<1, 1024, 0, stream>>>(cnt, cnt_ready, Epoch{epoch, epoch_base}, E, world, my_rank, align, row_base,
+  bg::launch_pdl(ep_layout_kernel, dim3(1), dim3(1024), 0, stream, cnt, cnt_ready, Epoch{epoch, epoch_base}, E, world, my_rank, align, row_base,
                                            offsets, cursor,
                                            total_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -441,10 +449,10 @@ int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T,
   using namespace bg::comm;
   if (K > 16 || H % 128 != 0) return -1;
   if (T <= 0) {  // nothing to send, but peers still wait for this rank's flag
-    signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), ready_index + my_rank, world, Epoch{epoch, epoch_base});
+    bg::launch_pdl(signal_kernel, dim3(1), dim3(32), 0, stream, to_peers(flags, world), ready_index + my_rank, world, Epoch{epoch, epoch_base});
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
-  ep_dispatch_send_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, topk_idx, K, E, H,
+  bg::launch_pdl(ep_dispatch_send_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(hidden), ldh, topk_idx, K, E, H,
                                                  row_base, cursor, to_peers(recv_q, world), to_peers(recv_s, world),
                                                  recv_s_stride, to_peers(recv_info, world), recv_cap, sent_row, my_rank,
                                                  world, to_peers(flags, world), ready_index, Epoch{epoch, epoch_base}, counter,
@@ -463,7 +471,7 @@ int bg_a2a_push_chunks(const void* src, void* const* dst, unsigned long long n_c
   int bx = (int)((vec + 255) / 256);
   if (bx > 64) bx = 64;
   dim3 grid(bx, world);
-  bg::comm::a2a_push_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), to_peers(dst, world), n_chunks,
+  bg::launch_pdl(bg::comm::a2a_push_kernel, dim3(grid), dim3(256), 0, stream, reinterpret_cast<const uint4*>(src), to_peers(dst, world), n_chunks,
                                                       chunk_bytes / 16, src_d / 16, src_b / 16, dst_r / 16, dst_b / 16,
                                                       my_rank, world, to_peers(flags, world), ready_index,
                                                       bg::comm::Epoch{epoch, epoch_base}, counter);
@@ -480,7 +488,7 @@ int bg_a2a_push(const void* src, void* const* dst, unsigned long long slice_byte
 
 int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int* status,
                   cudaStream_t stream) {
-  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
+  bg::launch_pdl(bg::comm::wait_flags_kernel, dim3(1), dim3(32), 0, stream, flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
                                                     bg::kFlagBudgetNs);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -490,18 +498,18 @@ int bg_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* 
 int bg_wait_flags_budget(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, int budget_ms,
                          int* status, cudaStream_t stream) {
   if (n < 0 || n > 32 || budget_ms < 0) return -1;
-  bg::comm::wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
+  bg::launch_pdl(bg::comm::wait_flags_kernel, dim3(1), dim3(32), 0, stream, flags, n, bg::comm::Epoch{epoch, epoch_base}, status,
                                                     (uint64_t)budget_ms * 1000000ull);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int bg_signal(void* const* flags, int index, int world, uint32_t epoch, const uint32_t* epoch_base, cudaStream_t stream) {
-  bg::comm::signal_kernel<<<1, 32, 0, stream>>>(to_peers(flags, world), index, world, bg::comm::Epoch{epoch, epoch_base});
+  bg::launch_pdl(bg::comm::signal_kernel, dim3(1), dim3(32), 0, stream, to_peers(flags, world), index, world, bg::comm::Epoch{epoch, epoch_base});
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int bg_bump_epoch(uint32_t* base, uint32_t n, cudaStream_t stream) {
-  bg::comm::bump_epoch_kernel<<<1, 32, 0, stream>>>(base, n);
+  bg::launch_pdl(bg::comm::bump_epoch_kernel, dim3(1), dim3(32), 0, stream, base, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
