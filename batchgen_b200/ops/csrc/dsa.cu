@@ -291,13 +291,23 @@ topk_select_kernel(const float* __restrict__ scores, long long ld, const int* __
   if (threadIdx.x == 0) out_len[b] = k;
 }
 
-// One block per (sequence, selected row): copy a latent row into the dense buffer.
+// One block per (sequence, selected row): copy a latent row into the dense buffer.  Rows between the selection's
+// length and the end of its last 64-row tile are zero-filled (the attention kernel multiplies them by a zero
+// probability, so they must be finite); rows past that tile are never read and stay untouched, so the caller does
+// not have to clear the buffer.
 __global__ void __launch_bounds__(64)
 gather_rows_kernel(const uint4* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ sel_idx, int ld_sel, const int* __restrict__ sel_len, uint4* __restrict__ out,
                    int row_vec, int page, int max_sel) {
   const int b = blockIdx.y, j = blockIdx.x;
-  if (j >= sel_len[b]) return;
+  const int n = sel_len[b];
+  if (j >= n) {
+    if (j < (n + page - 1) / page * page) {
+      uint4* z = out + ((size_t)b * max_sel + j) * row_vec;
+      for (int i = threadIdx.x; i < row_vec; i += blockDim.x) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return;
+  }
   const int pos = sel_idx[(size_t)b * ld_sel + j];
   const size_t slot = (size_t)block_table[(size_t)b * bt_stride + pos / page] * page + pos % page;
   const uint4* src = cache + slot * row_vec;

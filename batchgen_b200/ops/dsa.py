@@ -101,7 +101,7 @@ def sparse_mla_decode(q_abs, q_pe, cache, block_table, sel_idx, sel_len, scale, 
         return torch.cat(outs, 0)
     P, S, D = cache.shape
     K = (sel_idx.shape[1] + S - 1) // S * S
-    dense = torch.zeros(B, K, D, dtype=cache.dtype, device=cache.device)
+    dense = torch.empty(B, K, D, dtype=cache.dtype, device=cache.device)     # the gather zero-fills what is read
     rc = _ext.lib().bg_gather_rows(_ext.ptr(cache), _ext.ptr(block_table), ctypes.c_int(block_table.stride(0)),
                                    _ext.ptr(sel_idx), ctypes.c_int(sel_idx.stride(0)), _ext.ptr(sel_len),
                                    _ext.ptr(dense), ctypes.c_int(D * cache.element_size()), ctypes.c_int(S),

@@ -287,9 +287,27 @@ class Engine:
         if not cands:
             return 0
         reclaimable = self.prefix.reclaimable_pages() if self.prefix else 0
+        segs, ledger = None, None
+        if self.prefix is not None:
+            # marginal page charges: a page-sized prefix block is paid for by the first prompt that needs it; prompts
+            # that share it (in this wave, or through the prefix cache) pay for their private tail only
+            segs, ledger, held = {}, sched.SharedPrefixLedger(), set()
+            for s in cands:
+                keys = self._prefix_keys(s)
+                segs[s.global_idx] = [(k, 1) for k in keys]
+                for k in keys:
+                    page = self.prefix.page_of(k)
+                    if page is None:
+                        break
+                    if page not in held:
+                        held.add(page)
+                        ledger.charge(0, [(k, 1)])
+                        if self.kv.alloc.refcount(page) == 1:
+                            reclaimable -= 1               # a hit stays where it is: not part of the budget
         sel = sched.select_prefill_batch(cands, self._free_pages(), self.buf,
                                          reserve_decode_tokens=self.buf.page_size,
-                                         reclaimable_pages=reclaimable)
+                                         prefix_segments=segs, ledger=ledger,
+                                         reclaimable_pages=max(reclaimable, 0))
         live = len(self._by_status(S.PREFILLED, S.IN_DECODE, S.ON_HOLD))
         self.guard.observe(len(sel.admitted), live, (len(cands), self._free_pages()))
         admitted = list(sel.admitted)
@@ -361,6 +379,17 @@ class Engine:
         self.host_tier.promoted_pages += n
         self.stats.prefix_promoted_pages += n
         return out
+
+    def _prefix_keys(self, s: Sequence) -> List[bytes]:
+        """Chain keys of the full pages of the tokens a prefill of ``s`` would compute (all but the last token, which
+        is always computed); cached on the sequence until its token count changes."""
+        from .prefix_cache import build_prefix_hash_chain
+        ids = self._prefill_ids(s)
+        cached = getattr(s, "_prefix_key_cache", None)
+        if cached is None or cached[0] != len(ids):
+            cached = (len(ids), build_prefix_hash_chain(ids[: max(len(ids) - 1, 0)], self.buf.page_size))
+            s._prefix_key_cache = cached
+        return cached[1]
 
     @staticmethod
     def _prefill_ids(s: Sequence) -> List[int]:

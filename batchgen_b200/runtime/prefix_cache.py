@@ -69,6 +69,11 @@ class PrefixCache:
             self.misses += 1
         return pages, hit
 
+    def page_of(self, key: bytes) -> Optional[int]:
+        """The cached page of a chain key, without touching the LRU order or the hit counters."""
+        e = self._entries.get(key)
+        return None if e is None else e.page
+
     def attach(self, pages: Seq[int]) -> None:
         """A sequence starts using cached pages: take a reference for it."""
         self.alloc.share(pages)

@@ -169,6 +169,19 @@ def run_longctx(args) -> int:
                         extension_gpu_page_buffer=2, decision_frequency_pages=2, world_size=world,
                         attn_tp_size=world, ep_size=world, device=str(dev), dtype="bf16", moe_comm="nccl")
     eng = Engine(model, ecfg, num_gpu_pages=total_pages)
+    graph_note = "eager"
+    if not args.no_graph and world == 1:
+        # the decode step (indexer, top-k, gather, sparse attention, experts) as one CUDA graph per batch bucket
+        from batchgen_b200.runtime.graphs import DecodeGraphRunner
+        try:
+            eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=max(R, 8), max_pages_per_seq=per_req,
+                                                 num_buckets=2, max_bucket=max(R, 8))
+            eng.graph_runner.capture_all()
+            graph_note = "cuda graph"
+        except Exception as exc:                           # noqa: BLE001 - reported in the line, eager decode instead
+            eng.graph_runner = None
+            graph_note = f"eager (capture failed: {type(exc).__name__}: {str(exc)[:120]})"
+            torch.cuda.synchronize()
     reqs = [batch_api.BatchRequest(f"r{i}", "/v1/completions",
                                    {"prompt": p, "max_tokens": N, "temperature": 0, "ignore_eos": True})
             for i, p in enumerate(prompts)]
@@ -200,7 +213,7 @@ def run_longctx(args) -> int:
             "config": {"model": cfg.name, "layers": cfg.num_layers, "workload": args.workload, "requests": R,
                        "completed": ok, "ctx_tokens": L, "forced_tokens": N, "prefix_groups": groups if grouped else 0,
                        "parallelism": f"tp{world}+ep{world}", "comm": "nccl" if world > 1 else "none",
-                       "prefill_piece_tokens": args.prefill_tokens, "index_topk": cfg.index_topk,
+                       "prefill_piece_tokens": args.prefill_tokens, "index_topk": cfg.index_topk, "decode": graph_note,
                        "distinct_expert_sets": sets, "full_size_workload": full, "valid": not args.layers,
                        "api": "runtime.batch_api.run_batch on Engine", "build_seconds": round(build_s, 1)},
             "prefill_tok_per_s": st["prefill_tok_per_s"], "decode_tok_per_s": st["decode_tok_per_s"],
