@@ -256,10 +256,38 @@ inline bool ensure_dynamic_smem(Kernel kernel, size_t bytes, DeviceOnce& once) {
 // free SMs and run their own prologue) and then waits until the kernels it depends on have completed and their
 // writes are visible.  Without the launch attribute both instructions do nothing.  launch_pdl() sets the attribute,
 // so the gap between two kernels of a captured step shrinks from a full launch to the dependency hand-over.
-__device__ __forceinline__ void pdl_prologue() {
+//
+// Kernel trace: when a trace buffer is installed (bg_trace_set_<file>, one per translation unit), thread 0 of block
+// 0 of every kernel appends (global timer, id) on entry; consecutive entries give each kernel's period inside a
+// captured step (duration + the gap to the next kernel), which events around a graph replay cannot show.
+#ifndef BG_FILE_TAG
+#define BG_FILE_TAG 0
+#endif
+struct TraceBuf {
+  unsigned int n, cap;
+  unsigned long long rec[2];      // cap pairs of (time in ns, id) follow
+};
+static __device__ TraceBuf* g_trace = nullptr;
+__device__ __forceinline__ void pdl_prologue(unsigned int id = 0) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    TraceBuf* tb = g_trace;
+    if (tb != nullptr) {
+      const unsigned int i = atomicAdd(&tb->n, 1u);
+      if (i < tb->cap) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        tb->rec[2 * i] = t;
+        tb->rec[2 * i + 1] = id;
+      }
+    }
+  }
 }
+#define BG_TRACE_SETTER(name)                                                                       \
+  extern "C" int bg_trace_set_##name(void* p) {                                                     \
+    return cudaMemcpyToSymbol(bg::g_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;                  \
+  }
 inline bool pdl_enabled() {
   static const bool on = [] {
     const char* e = getenv("BG_PDL");

@@ -12,6 +12,7 @@
 // Replaces (by behaviour): batchgen_kernels/src/attention/csrc/rmsnorm.cu:88-254,
 // add_rmsnorm_fp8_quant.cu:243, batchgen_kernels/src/moe/fp8_blockwise/fp8_blockwise_ops.cu:39-445,
 // batchgen_kernels/src/attention/fused_kv_norm_rope_cache.cu:14, batchgen_kernels/triton/fp8_quantize.py.
+#define BG_FILE_TAG 1      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -42,7 +43,7 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
                float* __restrict__ out_s, int s_stride, int H, int ldx, int ldo, float eps, int pow2) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   extern __shared__ float row[];  // H floats
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(256)
 act_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int s_stride,
                  int T, int K, int ldx, int pow2, const int* __restrict__ valid_rows,
                  const int* __restrict__ row_src) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const int t = blockIdx.x;
   if (valid_rows != nullptr && t >= *valid_rows) return;
   if (row_src != nullptr && row_src[t] < 0) return;      // padding row of an expert segment: nothing reads it
@@ -169,7 +170,7 @@ mla_kv_write_kernel(const __nv_bfloat16* __restrict__ kv_a, int ld, const __nv_b
                     const int* __restrict__ positions, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, const long long* __restrict__ slots,
                     __nv_bfloat16* __restrict__ cache, int kv_lora, int rope, float eps, int interleaved) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   __shared__ float red[32];
   const int t = blockIdx.x;
   const long long slot = slots[t];
@@ -204,7 +205,7 @@ mla_kv_write_kernel(const __nv_bfloat16* __restrict__ kv_a, int ld, const __nv_b
 __global__ void rope_q_kernel(__nv_bfloat16* __restrict__ q, int H, int D, int rope, const int* __restrict__ positions,
                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int interleaved,
                               long long ld_t) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const int t = blockIdx.x;
   const int half = rope / 2;
   const int pos = positions[t];
@@ -283,3 +284,5 @@ int bg_rope_q(void* q, int T, int H, int D, int rope, const int* positions, cons
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(elementwise)

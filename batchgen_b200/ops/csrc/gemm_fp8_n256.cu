@@ -13,6 +13,7 @@
 //
 // Roles (576 threads, one CTA per SM, persistent): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
 // warps 2..17 epilogue.
+#define BG_FILE_TAG 3      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -109,7 +110,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_n256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = smem;
@@ -441,3 +442,5 @@ int bg_gemm_fp8_n256_return(const void* A, const float* sA, int sa_stride, const
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(gemm_fp8_n256)

@@ -24,6 +24,7 @@
 // Replaces (by behaviour): the reference's swap-AB grouped kernels for decode (batchgen_kernels/src/moe/mxfp4/
 // marlin_grouped_mxfp4_v3.cuh:163-198 idea applied to block-scaled FP8) and DeepGEMM's masked m-grouped FP8 GEMM
 // (batchgen/models/glm/glm5/moe_deepgemm_masked.py).
+#define BG_FILE_TAG 4      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -107,7 +108,7 @@ struct Walker {
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, Params p) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_tiles = smem;                                   // kStages x 16 KB
@@ -456,3 +457,5 @@ int bg_gemm_fp8_swapab_return(const void* X, const float* sA, int sa_stride, con
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(gemm_fp8_swapab)

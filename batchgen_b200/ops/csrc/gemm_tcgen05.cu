@@ -18,6 +18,7 @@
 // batchgen/gemm/w8a8_deepgemm.py:126 and batchgen/moe/grouped_fp8_deepgemm_moe.py:45-232, the
 // CuTe sm90 blockwise grouped GEMM batchgen_kernels/src/moe/fp8_blockwise/fp8_blockwise_gemm_kernel.cuh:363
 // and its fused gate+up+SiLU stage batchgen_kernels/src/moe/fp8_blockwise/fp8_blockwise_s1_kernel.cuh:131.
+#define BG_FILE_TAG 5      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -132,7 +133,7 @@ struct TileWalker {
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: operand stages first (1024-byte aligned), bookkeeping after
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -616,3 +617,5 @@ int bg_gemm(int kind, int epi, const void* A, const float* sA, int sa_stride, co
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(gemm_tcgen05)

@@ -13,6 +13,7 @@
 // Replaces (by behaviour): batchgen_kernels/src/attention/fused_q_absorb.cu:13, the Triton
 // fused_q_absorb.py and dsa/bf16_absorb.py, and the torch.bmm out-absorb of
 // batchgen/models/deepseek/deepseekv3/modeling_deepseek_v3.py (W_UV application after FlashMLA).
+#define BG_FILE_TAG 6      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -40,7 +41,7 @@ template <int BN> struct Shared {
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 head_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, Params p, int* status) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   constexpr int kABytes = BM * 128, kWBytes = BN * 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -197,3 +198,5 @@ int bg_head_gemm(const void* A, long long a_row, int a_head, long long a_cols, c
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(head_gemm)

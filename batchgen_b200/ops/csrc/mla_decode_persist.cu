@@ -27,6 +27,7 @@
 //
 // Replaces (by behaviour): flashinfer's trtllm-gen MLA decode as called by
 // batchgen/attention/mla/trtllm_gen_mla.py:49-93; contract batchgen/attention/mla/paged_decode.py:1-31.
+#define BG_FILE_TAG 7      // kernel-trace ids of this file are (tag << 16) | line
 #include "mla_tcgen05.cuh"
 
 namespace bg {
@@ -159,7 +160,7 @@ struct TileCursor {
 __global__ void __launch_bounds__(kPersistThreads, 1)
 mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                           const __grid_constant__ CUtensorMap tm_qpe, PersistParams p) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   constexpr int NS = 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -672,3 +673,5 @@ int bg_mla_decode_persist(const void* q_abs, long long qabs_stride, const void* 
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(mla_decode_persist)

@@ -1,4 +1,5 @@
 // C entry points of the tcgen05 paged-MLA kernels (kernel bodies: mla_tcgen05.cuh).
+#define BG_FILE_TAG 8      // kernel-trace ids of this file are (tag << 16) | line
 #include "mla_tcgen05.cuh"
 
 extern "C" {
@@ -52,3 +53,5 @@ int bg_mla_merge(const float* part_o, const float* part_ml, const int* items, in
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(mla_tcgen05)

@@ -205,7 +205,7 @@ template <int NCOL>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
            const __grid_constant__ CUtensorMap tm_qpe, Params p) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   using C = Cfg<NCOL>;
   constexpr int NS = 128;                                       // softmax threads
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -508,7 +508,7 @@ mla_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CU
 static __global__ void __launch_bounds__(128)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
                  __nv_bfloat16* __restrict__ out, int ncol, int H, int hpg) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   // items[i] = {q_row, n_q, head_group, first_slot, n_splits}
   const int* it = items + blockIdx.x * 5;
   const int q_row = it[0], n_q = it[1], hg = it[2], first = it[3], ns = it[4];

@@ -10,6 +10,7 @@
 // dispatch_scatter_3d.cu:152-345, routing/reduce_weighted_scatter.cu:27 and
 // dispatch_scatter_3d.cu:366-661 (ordered reduce: the k order here is fixed, so results are
 // bit-reproducible run to run).
+#define BG_FILE_TAG 2      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -22,7 +23,7 @@ __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
                    float* __restrict__ w_out, int T, int E, int K, int n_group, int topk_group, int norm, float scale,
                    int softmax_mode, const int* __restrict__ num_valid) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   __shared__ float choice_s[4][kMaxExperts];
   __shared__ float score_s[4][kMaxExperts];
   __shared__ float group_s[4][32];
@@ -117,7 +118,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 __global__ void __launch_bounds__(1024)
 moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int lo, int hi, int align, int* __restrict__ offsets,
                  int* __restrict__ cursor, const int* __restrict__ num_valid, int K) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   __shared__ int cnt[kMaxExperts];
   const int El = hi - lo;
   for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
@@ -142,7 +143,7 @@ moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int lo, int hi, 
 __global__ void moe_scatter_kernel(const int* __restrict__ topk_idx, int n_pairs, int K, int lo, int hi,
                                    const int* __restrict__ offsets, int* __restrict__ cursor, int* __restrict__ pos,
                                    int* __restrict__ src_row, const int* __restrict__ num_valid) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int limit = (num_valid != nullptr) ? *num_valid * K : n_pairs;
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(256)
 moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const int* __restrict__ src_row,
                         const int* __restrict__ total_rows, uint8_t* __restrict__ q, float* __restrict__ s,
                         int s_stride, int K, int pow2, int zero_padding) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const int r = blockIdx.x;
   if (r >= *total_rows) return;
   const int src = src_row[r];
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __restrict__ pos,
                    const float* __restrict__ w, const __nv_bfloat16* __restrict__ extra, int lde,
                    __nv_bfloat16* __restrict__ out, int ldo, int K, int H, int out_fp32) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const int t = blockIdx.x;
   __shared__ int p_s[kMaxTopK];
   __shared__ float w_s[kMaxTopK];
@@ -304,3 +305,5 @@ int bg_moe_combine(const void* y, int ldy, const int* pos, const float* w, const
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(moe_route)

@@ -11,6 +11,7 @@
 //
 // Replaces (by behaviour): the torch-op sampler batchgen/sampling.py:296-530 (per-row
 // temperature/top-p/top-k tensors, greedy split, on-device bad-row counter).
+#define BG_FILE_TAG 9      // kernel-trace ids of this file are (tag << 16) | line
 #include "common.cuh"
 
 namespace bg {
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(kSampThreads)
 sample_kernel(const T* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ out, int* __restrict__ bad_rows) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   __shared__ float red[33];
   __shared__ float redv[32];
   __shared__ int redi[32];
@@ -200,3 +201,5 @@ int bg_sample(int dtype, const void* logits, long long ld, int T, int V, const f
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(sampling)

@@ -21,6 +21,7 @@
 // batchgen/models/deepseek/deepseekv3/modeling_deepseek_v3.py:3137,3173,
 // batchgen/moe/fused_moe_mxfp4_resident.py:1020-1095) and the DeepEP low-latency dispatch/combine
 // wrapper batchgen/moe/deepep_ll.py:240-400.
+#define BG_FILE_TAG 10      // kernel-trace ids of this file are (tag << 16) | line
 #include "../../ops/csrc/common.cuh"
 
 namespace bg {
@@ -76,7 +77,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
                           Peers ag_s, int ag_s_stride, int push, int rows, int H, float eps, int my_rank, int world,
                           Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter, int* status,
                           int has_residual) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t wait_epoch = wait_epoch_e.get();
   const uint32_t epoch = epoch_e.get();
   extern __shared__ float rowbuf[];
@@ -187,7 +188,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
 __global__ void __launch_bounds__(1024)
 ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers cnt, int my_rank, int world, Peers flags,
                      int ready_index, Epoch epoch_e, int2* __restrict__ row_info, int row_cap) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   __shared__ int c[kMaxExperts];
   for (int e = threadIdx.x; e < E; e += blockDim.x) c[e] = 0;
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(1024)
 ep_layout_kernel(const int* __restrict__ cnt, const uint32_t* __restrict__ cnt_ready, Epoch epoch_e, int E, int world,
                  int my_rank, int align, int* __restrict__ row_base, int* __restrict__ offsets,
                  int* __restrict__ cursor, int* __restrict__ total_rows, int* status) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   __shared__ int tot[kMaxExperts];
   __shared__ int mine[kMaxExperts];
   __shared__ int seg[kMaxExperts];
@@ -276,7 +277,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
                         Peers recv_s, int recv_s_stride, Peers recv_info, int recv_cap, int* __restrict__ sent_row,
                         int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter,
                         int* status) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   __shared__ int dest_rank[16], dest_row[16];
   const int t = blockIdx.x;
@@ -332,7 +333,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
 }
 
 __global__ void wait_flags_kernel(const uint32_t* flags, int n, Epoch epoch_e, int* status, uint64_t budget_ns) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   if (threadIdx.x < n) {
     if (!wait_flag_ge(flags + threadIdx.x, epoch, status, budget_ns) && status != nullptr)
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(256)
 a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_t chunk_vec, size_t src_d, size_t src_b,
                 size_t dst_r, size_t dst_b, int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e,
                 unsigned int* counter) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   const int d = (my_rank + blockIdx.y) % world;
   const uint4* s = src + (size_t)d * src_d;
@@ -375,12 +376,12 @@ a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_
 }
 
 __global__ void bump_epoch_kernel(uint32_t* base, uint32_t n) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   if (threadIdx.x == 0) *base += n;
 }
 
 __global__ void signal_kernel(Peers flags, int index, int world, Epoch epoch_e) {
-  bg::pdl_prologue();
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -514,3 +515,5 @@ int bg_bump_epoch(uint32_t* base, uint32_t n, cudaStream_t stream) {
 }
 
 }  // extern "C"
+
+BG_TRACE_SETTER(fused_comm)

@@ -341,7 +341,10 @@ class FusedComm(NcclComm):
                 act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
                                                 counts=self.recv_counts)
         with timer.timed("moe.act_quant"):
-            aq, as_ = fused_ops.act_quant(act, valid_rows=self.total_rows)
+            # one block per row: launch over the rows this step can have received (every rank's rows x top-k plus
+            # one alignment gap per local expert), not over the whole receive capacity sized for prefill steps
+            bound = min(self.recv_cap, _pad(W * Tl * K, ALIGN) + (E // W) * ALIGN)
+            aq, as_ = fused_ops.act_quant(act[:bound], valid_rows=self.total_rows)
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
         with timer.timed("moe.s3_gemm_return"):
             e_ret = self._next(RET_READY)
@@ -351,7 +354,7 @@ class FusedComm(NcclComm):
                 rc = L.bg_gemm_fp8_swapab_return(
                     _ext.ptr(aq), _ext.ptr(sc), ctypes.c_int(sc_stride), _ext.ptr(ew.w2), _ext.ptr(ew.w2_s),
                     ctypes.c_int(Hout), _ext.ptr(self.offsets), _ext.ptr(self.recv_counts), ctypes.c_int(El),
-                    ctypes.c_int(self.recv_cap), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
+                    ctypes.c_int(aq.shape[0]), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
                     self.heap.peer_ptrs("ret"), _ext.ptr(self.recv_info), self.flag_ptrs, ctypes.c_int(RET_READY),
                     ctypes.c_uint32(e_ret), self._base(), _ext.ptr(self.counters[3:4]), ctypes.c_int(self.rank),
                     ctypes.c_int(W), self._status(), st)
@@ -362,7 +365,7 @@ class FusedComm(NcclComm):
                 rc = L.bg_gemm_fp8_n256_return(
                     _ext.ptr(aq), _ext.ptr(sc), ctypes.c_int(sc_stride), _ext.ptr(ew.w2), _ext.ptr(ew.w2_s),
                     ctypes.c_int(Hout), _ext.ptr(self.offsets), _ext.ptr(self.recv_counts), ctypes.c_int(El),
-                    ctypes.c_int(self.recv_cap), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
+                    ctypes.c_int(aq.shape[0]), ctypes.c_int(Hout), ctypes.c_int(I), ctypes.c_int(_ext.num_sms(self.device)),
                     self.heap.peer_ptrs("ret"), _ext.ptr(self.recv_info), self.flag_ptrs, ctypes.c_int(RET_READY),
                     ctypes.c_uint32(e_ret), self._base(), _ext.ptr(self.counters[3:4]), ctypes.c_int(self.rank),
                     ctypes.c_int(W), self._status(), st)

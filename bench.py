@@ -315,6 +315,9 @@ def main() -> int:
                          "(use with --model glm-5.3-fp8)")
     ap.add_argument("--requests", type=int, default=2, help="requests of a long-context workload")
     ap.add_argument("--ctx-tokens", type=int, default=65536, help="prompt tokens of a long-context request")
+    ap.add_argument("--trace-kernels", default="",
+                    help="write the in-step kernel timeline of one captured decode step (start stamps of this "
+                         "repository's kernels: period = duration + gap to the next kernel) to this file")
     ap.add_argument("--check-comm", action="store_true",
                     help="N > 1: run one decode step through the NCCL baseline on the same inputs and report the "
                          "largest relative difference of the logits (outside the timed regions)")
@@ -600,6 +603,25 @@ def main() -> int:
         prefill = {"tokens_per_s": T * 1000.0 / ms_p, "ms_per_microbatch": ms_p, "tokens": T, "seq_len": L}
         kv.alloc.free(pbt.flatten().tolist())
 
+    if args.trace_kernels:
+        from batchgen_b200.utils import kernel_trace
+        tbuf = kernel_trace.enable(dev)
+        barrier()
+        decode_step_device()
+        barrier()
+        kernel_trace.disable(dev)
+        if rank == 0:
+            recs = kernel_trace.read(tbuf)
+            rows = kernel_trace.summarize(recs)
+            with open(args.trace_kernels, "w") as f:
+                span = (recs[-1][0] - recs[0][0]) / 1e3 if recs else 0.0
+                f.write(f"== one captured decode step: {len(recs)} stamped kernels over {span:.1f} us ==\n")
+                for r in rows:
+                    f.write(f"{r['kernel']:36s} {r['launches']:6d} launches {r['us']:10.1f} us {r['share'] * 100:5.1f}%"
+                            f"  {r['us'] / max(r['launches'], 1):8.2f} us each\n")
+                f.write("== first layers in order (us since the first stamp, kernel) ==\n")
+                for t, tag, line in recs[:140]:
+                    f.write(f"{(t - recs[0][0]) / 1e3:10.2f}  {kernel_trace.kernel_name(tag, line)}\n")
     bct = None
     if args.bct:
         if rank == 0:                                   # the step numbers survive a failure of the long workload
