@@ -72,6 +72,13 @@ struct GemmParams {
   uint32_t* peer_flags[8];
   int done_flag_index;
   unsigned int* done_counter;
+  // split K (dense GEMMs with too few output tiles to fill the SMs): work item = (tile, split); every split
+  // accumulates its range of K blocks, parks the fp32 partial tile in `splitk_ws` and bumps the tile's counter; the
+  // split that arrives last sums all partials in split order (one summation order whoever is last), runs the
+  // epilogue and clears the counter.
+  int splits;
+  float* splitk_ws;       // [tiles * splits][64][kEpiWarps * 32]
+  int* splitk_cnt;        // [tiles], zero between launches
 };
 
 struct SharedStorage {
@@ -81,6 +88,7 @@ struct SharedStorage {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int split_last;
   int offs[kMaxGroups + 1];
   int cnt[kMaxGroups];
 };
@@ -148,6 +156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int kElemBytes = (KIND == KIND_FP8) ? 1 : 2;
   constexpr int BK = BK_BYTES / kElemBytes;  // elements of K per stage
   const int KB = p.K / BK;
+  const int S = p.splits > 1 ? p.splits : 1;     // K splits per output tile
   const int n_tiles = (p.N + BN - 1) / BN;
   const int nblk = (p.N + 127) / 128;
   volatile int* abort_flag = &ss.abort_flag;
@@ -191,7 +200,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t it = 0;
       uint32_t ready_mask = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && walk.get(item / S, t); item += gridDim.x) {
+        const int sp = item % S;
+        const int kb0 = sp * KB / S, kb1 = (sp + 1) * KB / S;
         const int brow = t.g * p.N + t.nt * BN;
         if (p.a_ready != nullptr) {
           // rows of this tile were pushed by other ranks: wait (bounded) for their arrival flags
@@ -211,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!ok) break;
           fence_proxy_async_global();
         }
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&ss.empty[s], ph ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
@@ -247,11 +258,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t it = 0;   // smem stage counter
       uint32_t acc = 0;  // accumulator hand-off counter
       bool ok = true;
-      for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+      for (int item = blockIdx.x; ok && walk.get(item / S, t); item += gridDim.x) {
+        const int sp = item % S;
+        const int kb0 = sp * KB / S, kb1 = (sp + 1) * KB / S;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          const bool new_acc = (KIND == KIND_FP8) || kb == 0;
+          const bool new_acc = (KIND == KIND_FP8) || kb == kb0;
           const int buf = acc & 1;
           if (new_acc) {
             if (!mbar_wait(&ss.tmem_empty[buf], ((acc >> 1) & 1) ^ 1, abort_flag, kTimeoutMma)) { ok = false; break; }
@@ -268,7 +281,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             else mma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
           }
           tc_commit(&ss.empty[s]);
-          const bool last_of_acc = (KIND == KIND_FP8) || kb == KB - 1;
+          const bool last_of_acc = (KIND == KIND_FP8) || kb == kb1 - 1;
           if (last_of_acc) {
             tc_commit(&ss.tmem_full[buf]);
             ++acc;
@@ -286,8 +299,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     Tile t;
     uint32_t acc = 0;
     bool ok = true;
-    const int groups_of_k = (KIND == KIND_FP8) ? KB : 1;
-    for (int tile = blockIdx.x; ok && walk.get(tile, t); tile += gridDim.x) {
+    for (int item = blockIdx.x; ok && walk.get(item / S, t); item += gridDim.x) {
+      const int tile = item / S, sp = item % S;
+      const int kb0 = sp * KB / S, kb1 = (sp + 1) * KB / S;
+      const int groups_of_k = (KIND == KIND_FP8) ? (kb1 - kb0) : 1;
       float r[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) r[j] = 0.f;
@@ -311,6 +326,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool remote_a = (p.a_ready != nullptr);
       float sa_next = 1.f, sbl_next = 1.f, sbh_next = 1.f;
       if (KIND == KIND_FP8) {
+        sa_ptr += (size_t)kb0 * p.sa_stride;         // this split's first K block
+        sb_lo += kb0;
+        sb_hi += kb0;
         if (!remote_a) sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
         sbl_next = __ldg(sb_lo);
         sbh_next = __ldg(sb_hi);
@@ -358,6 +376,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
       if (!ok) break;
+      if (S > 1) {
+        const int et = ew * 32 + lane;                              // 0 .. 255 over the epilogue warps
+        constexpr int kEpiThreads = kEpiWarps * 32;
+        float* mine = p.splitk_ws + ((size_t)tile * S + sp) * 64 * kEpiThreads + et;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) __stcg(mine + j * kEpiThreads, r[j]);
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (et == 0) {
+          const int prev = atomicAdd(p.splitk_cnt + tile, 1);
+          ss.split_last = (prev == S - 1) ? 1 : 0;
+          if (prev == S - 1) p.splitk_cnt[tile] = 0;               // ready for the next launch / graph replay
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (ss.split_last == 0) continue;                          // another split finishes this tile
+        __threadfence();
+        const float* all = p.splitk_ws + (size_t)tile * S * 64 * kEpiThreads + et;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) r[j] = 0.f;
+        for (int q = 0; q < S; ++q) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) r[j] += __ldcg(all + ((size_t)q * 64 + j) * kEpiThreads);
+        }
+      }
       __nv_bfloat16* out_base = p.D;
       size_t out_row = (size_t)row;
       bool store_ok = row_ok;
@@ -519,6 +561,22 @@ static size_t gemm_smem_bytes() {
   return kStages * (BM + BN) * BK_BYTES + ((sizeof(SharedStorage) + 15) & ~size_t(15)) + kEpiWarps * kEpiStageBytes + 1024;
 }
 
+// Split-K scratch of the calling thread's current device, installed from the host side (bg_gemm_set_splitk_ws)
+// before the first launch: allocating here would not be legal while a stream is being captured.
+struct SplitKWorkspace {
+  float* ws = nullptr;
+  int* cnt = nullptr;
+  size_t max_items = 0;     // (tile, split) partials that fit
+  int max_tiles = 0;        // counters
+};
+static SplitKWorkspace g_splitk[kMaxDevices];
+static SplitKWorkspace& splitk_workspace() {
+  static SplitKWorkspace none;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return none;
+  return g_splitk[dev];
+}
+
 template <int KIND, int EPI>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_rows, int b_rows, int num_sms,
                        cudaStream_t stream) {
@@ -531,12 +589,31 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
   const size_t smem = gemm_smem_bytes();
   if (!ensure_dynamic_smem(kern, smem, attr_set)) return -12;
   int grid = num_sms;
+  GemmParams q = p;
+  q.splits = 1;
+  q.splitk_ws = nullptr;
+  q.splitk_cnt = nullptr;
   if (p.offsets == nullptr) {
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-    if (tiles < grid) grid = tiles;
+    const int KB = p.K / (BK_BYTES / eb);
+    SplitKWorkspace& ws = splitk_workspace();
+    int S = 1;
+    if (ws.ws != nullptr && tiles * 2 <= num_sms && tiles <= ws.max_tiles) {
+      S = num_sms / tiles;
+      if (S > KB / 4) S = KB / 4;                  // at least four K blocks per split
+      if (S > 16) S = 16;
+      if ((size_t)tiles * S > ws.max_items) S = (int)(ws.max_items / tiles);
+      if (S < 2) S = 1;
+    }
+    if (S > 1) {
+      q.splits = S;
+      q.splitk_ws = ws.ws;
+      q.splitk_cnt = ws.cnt;
+    }
+    if (tiles * S < grid) grid = tiles * S;
   }
   if (grid < 1) grid = 1;
-  bg::launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, tmA, tmB, p);
+  bg::launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, tmA, tmB, q);
   return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 
@@ -568,6 +645,18 @@ void bg_gemm_set_hooks(const uint32_t* a_ready, int a_ready_rows, uint32_t epoch
   g_hooks.my_rank = my_rank; g_hooks.world = world; g_hooks.done_flag_index = done_flag_index;
   g_hooks.done_counter = done_counter;
   g_hooks_set = true;
+}
+
+// Scratch for split-K launches on the current device: `ws` holds `max_items` partial tiles of 128 x 128 fp32,
+// `counters` holds `max_tiles` zeroed ints.  Null `ws` switches split K off.
+int bg_gemm_set_splitk_ws(float* ws, long long max_items, int* counters, int max_tiles) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= bg::kMaxDevices) return -1;
+  bg::g_splitk[dev].ws = ws;
+  bg::g_splitk[dev].cnt = counters;
+  bg::g_splitk[dev].max_items = ws != nullptr ? (size_t)max_items : 0;
+  bg::g_splitk[dev].max_tiles = max_tiles;
+  return 0;
 }
 
 // Real row counts of the next grouped bg_gemm on this thread: counts[g] rows of segment g are present, the

@@ -83,6 +83,29 @@ def wide_enabled() -> bool:
     return _WIDE != "0"
 
 
+_SPLITK = os.environ.get("BG_GEMM_SPLITK", "1")
+_splitk_ws: dict = {}
+
+
+def _ensure_splitk_workspace(device) -> None:
+    """Dense GEMMs whose output has too few 128 x 128 tiles to fill the SMs (decode-sized projections, router
+    logits) split K over several CTAs; their partial tiles and per-tile counters live in one scratch per device,
+    handed to the launcher once (it may not allocate: the launch can be part of a stream capture)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key in _splitk_ws or _SPLITK == "0":
+        return
+    sms = _ext.num_sms(device)
+    ws = torch.empty(sms * 128 * 128, dtype=torch.float32, device=device)
+    cnt = torch.zeros(4096, dtype=torch.int32, device=device)
+    _splitk_ws[key] = (ws, cnt)
+    L = _ext.lib()
+    L.bg_gemm_set_splitk_ws.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
+    with torch.cuda.device(device):
+        rc = L.bg_gemm_set_splitk_ws(ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(sms),
+                                     ctypes.c_void_p(cnt.data_ptr()), ctypes.c_int(cnt.numel()))
+    _ext.check(rc, "bg_gemm_set_splitk_ws")
+
+
 def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wide=None, counts=None, a_ready=None,
             swapab=False):
     """``a_ready`` = (flag pointer, epoch, epoch-base pointer, world): the rows of A are pushed by peers and the
@@ -111,6 +134,7 @@ def _launch(kind, epi, A, sA, sa_stride, B, sB, D, offsets, groups, M, N, K, wid
         return
     if counts is not None:
         L.bg_gemm_set_counts(_ext.ptr(counts))
+    _ensure_splitk_workspace(A.device)
     rc = L.bg_gemm(ctypes.c_int(kind), ctypes.c_int(epi), _ext.ptr(A), _ext.ptr(sA), ctypes.c_int(sa_stride),
                    _ext.ptr(B), _ext.ptr(sB), _ext.ptr(D), ctypes.c_int(D.stride(0)), _ext.ptr(offsets),
                    ctypes.c_int(groups), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),

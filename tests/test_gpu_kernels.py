@@ -91,6 +91,33 @@ def test_bf16_gemm_fp32_epilogue(M, N, K):
     assert err <= 2e-3 * want.abs().max().item(), (err, want.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,K", [(96, 2112, 7168), (384, 2112, 7168), (48, 7168, 2048), (96, 1536, 1536)])
+def test_fp8_gemm_split_k_shapes(M, N, K):
+    """Decode-sized projections: few output tiles, K split over several CTAs with an in-kernel reduction.  Two
+    launches in a row (the per-tile counters must be back at zero) and bit-identical results (fixed summation order)."""
+    x = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV) * 0.05
+    xq, xs = ref.act_quant(x)
+    wq, ws = ref.weight_quant_block(w)
+    want = ref.fp8_gemm(xq, xs, wq, ws)
+    a = gemm.fp8_gemm(xq, xs, wq, ws, swapab=False)
+    b = gemm.fp8_gemm(xq, xs, wq, ws, swapab=False)
+    _close(a, want)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M", [48, 384])
+def test_router_gemm_split_k_fp32(M):
+    x = torch.randn(M, 7168, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(256, 7168, device=DEV) * 0.05).to(torch.bfloat16)
+    want = x.float() @ w.float().t()
+    a = gemm.bf16_gemm(x, w, fp32_out=True)
+    b = gemm.bf16_gemm(x, w, fp32_out=True)
+    torch.cuda.synchronize()
+    assert (a - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+    assert torch.equal(a, b)
+
+
 def test_fp8_gemm_fused_silu():
     M, I, K = 300, 256, 512
     x = torch.randn(M, K, device=DEV)
