@@ -200,7 +200,9 @@ moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ hidden, int ldh, const
   }
 }
 
-// One block per token: out[t] = (extra[t] if given) + sum_k w[t,k] * y[pos[t,k]], k ascending.
+// out[t] = (extra[t] if given) + sum_k w[t,k] * y[pos[t,k]], k ascending.  Grid (token, 2,048-column chunk): a
+// thread owns 8 columns and has the top-k rows' loads in flight together, so a 48-token decode step still fills
+// the SMs instead of walking each row serially in 48 blocks.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __restrict__ pos,
                    const float* __restrict__ w, const __nv_bfloat16* __restrict__ extra, int lde,
@@ -214,21 +216,31 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __re
     w_s[threadIdx.x] = w[(size_t)t * K + threadIdx.x];
   }
   __syncthreads();
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  const int v = blockIdx.y * blockDim.x + threadIdx.x;
+  if (v < H / 8) {
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int k = 0; k < K; ++k) {
-      const int p = p_s[k];
-      if (p < 0) continue;
-      const float wk = w_s[k];
-      uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)p * ldy + v * 8);
-      const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int k0 = 0; k0 < K; k0 += 8) {
+      uint4 raw[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 a = __bfloat1622float2(yp[i]);
-        acc[2 * i] = fmaf(wk, a.x, acc[2 * i]);
-        acc[2 * i + 1] = fmaf(wk, a.y, acc[2 * i + 1]);
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + j;
+        const int p = k < K ? p_s[k] : -1;
+        raw[j] = p >= 0 ? *reinterpret_cast<const uint4*>(y + (size_t)p * ldy + v * 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + j;
+        if (k >= K || p_s[k] < 0) continue;
+        const float wk = w_s[k];
+        const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 a = __bfloat1622float2(yp[i]);
+          acc[2 * i] = fmaf(wk, a.x, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(wk, a.y, acc[2 * i + 1]);
+        }
       }
     }
     if (extra != nullptr) {
@@ -298,7 +310,7 @@ int bg_moe_combine(const void* y, int ldy, const int* pos, const float* w, const
   using namespace bg;
   if (T <= 0) return 0;
   if (K > kMaxTopK || H % 8 != 0) return -1;
-  bg::launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(y), ldy, pos, w,
+  bg::launch_pdl(moe_combine_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, stream, reinterpret_cast<const __nv_bfloat16*>(y), ldy, pos, w,
                                             reinterpret_cast<const __nv_bfloat16*>(extra), lde,
                                             reinterpret_cast<__nv_bfloat16*>(out), ldo, K, H, out_fp32);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -201,8 +201,9 @@ def grouped_fp8_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: t
 
 
 def bf16_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, fp32_out: bool = False) -> torch.Tensor:
-    """[T, K] bf16 x [N, K] bf16 -> [T, N] bf16, or fp32 with ``fp32_out`` (fp32 accumulate in TMEM; one
-    accumulation order whatever the batch size: every output element sums its K products in the same order)."""
+    """[T, K] bf16 x [N, K] bf16 -> [T, N] bf16, or fp32 with ``fp32_out`` (fp32 accumulate in TMEM).  For a given
+    shape the summation order is fixed (repeatable bit for bit); shapes with few output tiles split K over CTAs, so
+    the order can differ between batch sizes."""
     if not x.is_cuda:
         y = x.float() @ w.float().t()
         return y if fp32_out else y.to(x.dtype)

@@ -104,9 +104,12 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, 
     return idx, w
 
 
-def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.Tensor] = None):
+def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.Tensor] = None,
+            align: int = ROW_ALIGN):
     """Group (token, k) pairs by local expert.  -> (src_row [cap] int32, pos [T, k] int32,
-    offsets [El+1] int32).  Rows past offsets[El] are unused capacity."""
+    offsets [El+1] int32).  Rows past offsets[El] are unused capacity.  ``align``: segment starts are multiples of
+    it (128 = the row tile of the wide GEMM kernels; 32 = the token tile of the swapped-operand kernel, which keeps
+    the padded capacity, and with it the per-row kernels' grids, small at decode sizes)."""
     T, K = topk_idx.shape
     El = hi - lo
     if not topk_idx.is_cuda:
@@ -116,14 +119,14 @@ def permute(topk_idx: torch.Tensor, lo: int, hi: int, num_valid: Optional[torch.
             idx[int(num_valid):] = -1
         src, pos, off = ref.moe_permute(idx, hi, lo, hi, align=1)
         return src.to(torch.int32), pos.to(torch.int32), off.to(torch.int32)
-    cap = (T * K + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN + El * ROW_ALIGN
+    cap = (T * K + align - 1) // align * align + El * align
     dev = topk_idx.device
     offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
     cursor = torch.empty(El, dtype=torch.int32, device=dev)
     pos = torch.empty(T, K, dtype=torch.int32, device=dev)
     src = torch.empty(cap, dtype=torch.int32, device=dev)
     rc = _ext.lib().bg_moe_permute(_ext.ptr(topk_idx), ctypes.c_int(T), ctypes.c_int(K), ctypes.c_int(lo),
-                                   ctypes.c_int(hi), ctypes.c_int(ROW_ALIGN), _ext.ptr(offsets), _ext.ptr(cursor),
+                                   ctypes.c_int(hi), ctypes.c_int(align), _ext.ptr(offsets), _ext.ptr(cursor),
                                    _ext.ptr(pos), _ext.ptr(src), ctypes.c_int(cap), _ext.ptr(num_valid), _ext.stream())
     _ext.check(rc, "bg_moe_permute", kernels=2)
     offsets.real_counts = cursor          # after the scatter pass: rows really present in each segment
@@ -235,8 +238,15 @@ def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.
     if timer is None:
         from ..utils.timing import null_timer
         timer = null_timer()
+    align = ROW_ALIGN
+    if ew.quant == "fp8_block" and hidden.is_cuda and ew.interleaved:
+        # decode-sized steps run on the swapped-operand kernel (32-token tiles): 32-row segment alignment keeps the
+        # padded capacity close to the real row count
+        pairs = topk_idx.shape[0] * topk_idx.shape[1]
+        if gemm.use_swapab(pairs / max(expert_hi - expert_lo, 1), ew.w13.shape[1], ew.w13.shape[2]):
+            align = 32
     with timer.timed("moe.permute"):
-        src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid)
+        src, pos, offsets = permute(topk_idx, expert_lo, expert_hi, num_valid, align=align)
     if ew.quant == "fp8_block":
         counts = getattr(offsets, "real_counts", None)
         with timer.timed("moe.gather_quant"):

@@ -290,6 +290,11 @@ class FusedComm(NcclComm):
         Tl, H = h_local.shape
         L = _ext.lib()
         st = _ext.stream()
+        # decode-sized steps (about one 32-token tile per expert): weights on the MMA's M side, segments aligned to
+        # the 32-token tile so that the padded row count stays close to the real one
+        small = gemm_ops.use_swapab(Tl * K / max(E // W, 1), ew.w13.shape[1], ew.w13.shape[2]) and \
+            ew.w2.shape[1] % 128 == 0 and ew.w2.shape[2] % 128 == 0
+        align = 32 if small else ALIGN
         with timer.timed("moe.ep_count_layout"):
             e_cnt = self._next(CNT_READY)
             rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E),
@@ -298,7 +303,7 @@ class FusedComm(NcclComm):
                                     _ext.ptr(self.recv_info), ctypes.c_int(self.recv_cap), st)
             _ext.check(rc, "bg_ep_count_push")
             rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
-                                ctypes.c_int(E), ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(ALIGN),
+                                ctypes.c_int(E), ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(align),
                                 _ext.ptr(self.row_base), _ext.ptr(self.offsets), _ext.ptr(self.cursor),
                                 _ext.ptr(self.total_rows), self._status(), st)
             _ext.check(rc, "bg_ep_layout")
@@ -322,9 +327,6 @@ class FusedComm(NcclComm):
             with timer.timed("moe.dispatch_wait"):
                 _ext.check(L.bg_wait_flags(self._flag_ptr(DISP_READY), ctypes.c_int(W), ctypes.c_uint32(e_disp),
                                            self._base(), self._status(), st), "bg_wait_flags")
-        # decode-sized steps (about one 32-token tile per expert): weights on the MMA's M side
-        small = gemm_ops.use_swapab(Tl * K / max(E // W, 1), ew.w13.shape[1], ew.w13.shape[2]) and \
-            ew.w2.shape[1] % 128 == 0 and ew.w2.shape[2] % 128 == 0
         with timer.timed("moe.s1_gemm"):
             if small:
                 act = gemm_ops.grouped_fp8_gemm(self.recv_q, xs, ew.w13, ew.w13_s, self.offsets, silu_mul=True,
@@ -343,7 +345,7 @@ class FusedComm(NcclComm):
         with timer.timed("moe.act_quant"):
             # one block per row: launch over the rows this step can have received (every rank's rows x top-k plus
             # one alignment gap per local expert), not over the whole receive capacity sized for prefill steps
-            bound = min(self.recv_cap, _pad(W * Tl * K, ALIGN) + (E // W) * ALIGN)
+            bound = min(self.recv_cap, _pad(W * Tl * K, align) + (E // W) * align)
             aq, as_ = fused_ops.act_quant(act[:bound], valid_rows=self.total_rows)
         # ---- down projection; the epilogue returns each row to its token's owner (combine)
         with timer.timed("moe.s3_gemm_return"):
