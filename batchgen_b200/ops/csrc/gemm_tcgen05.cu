@@ -597,13 +597,21 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int KB = p.K / (BK_BYTES / eb);
     SplitKWorkspace& ws = splitk_workspace();
+    // Pick the split count that minimises (waves of work items) / S plus a per-split reduction cost.  Few tiles
+    // (less than half a wave): up to 16 splits.  One to two waves (e.g. 168 tiles on 148 SMs: the second wave
+    // is 14 % full): up to 4, the partial tiles' traffic grows with tiles x S.
     int S = 1;
-    if (ws.ws != nullptr && tiles * 2 <= num_sms && tiles <= ws.max_tiles) {
-      S = num_sms / tiles;
-      if (S > KB / 4) S = KB / 4;                  // at least four K blocks per split
-      if (S > 16) S = 16;
-      if ((size_t)tiles * S > ws.max_items) S = (int)(ws.max_items / tiles);
-      if (S < 2) S = 1;
+    if (ws.ws != nullptr && tiles < 2 * num_sms && tiles <= ws.max_tiles) {
+      const int s_max = tiles * 2 <= num_sms ? 16 : 4;
+      float best = (float)((tiles + num_sms - 1) / num_sms) + 0.02f;
+      for (int c = 2; c <= s_max; ++c) {
+        if (KB / c < 4 || (size_t)tiles * c > ws.max_items) break;
+        const float cost = (float)((tiles * c + num_sms - 1) / num_sms) / (float)c + 0.02f * (float)c;
+        if (cost < 0.97f * best) {
+          best = cost;
+          S = c;
+        }
+      }
     }
     if (S > 1) {
       q.splits = S;

@@ -95,13 +95,13 @@ def _ensure_splitk_workspace(device) -> None:
     if key in _splitk_ws or _SPLITK == "0":
         return
     sms = _ext.num_sms(device)
-    ws = torch.empty(sms * 128 * 128, dtype=torch.float32, device=device)
+    ws = torch.empty(4 * sms * 128 * 128, dtype=torch.float32, device=device)      # 4 x SMs partial tiles (38 MB)
     cnt = torch.zeros(4096, dtype=torch.int32, device=device)
     _splitk_ws[key] = (ws, cnt)
     L = _ext.lib()
     L.bg_gemm_set_splitk_ws.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
     with torch.cuda.device(device):
-        rc = L.bg_gemm_set_splitk_ws(ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(sms),
+        rc = L.bg_gemm_set_splitk_ws(ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(4 * sms),
                                      ctypes.c_void_p(cnt.data_ptr()), ctypes.c_int(cnt.numel()))
     _ext.check(rc, "bg_gemm_set_splitk_ws")
 
