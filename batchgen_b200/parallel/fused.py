@@ -81,8 +81,10 @@ class FusedComm(NcclComm):
             "ret": Tl * top_k * expert_hidden * 2,
             "a2a0": _pad(a2a_bytes, 1024), "a2a1": _pad(a2a_bytes, 1024),
         }
-        total = sum(_pad(v, 1024) for v in sizes.values()) + 64 * 1024
-        self.heap = SymmetricHeap(total, self.device, self.group)
+        import os
+        guard = 4096 if os.environ.get("BG_COMM_GUARD", "0") == "1" else 0    # debug: poisoned band after every region
+        total = sum(_pad(v, 1024) + guard + 1024 for v in sizes.values()) + 64 * 1024
+        self.heap = SymmetricHeap(total, self.device, self.group, guard_bytes=guard)
         for k, v in sizes.items():
             self.heap.alloc(k, v)
         h = self.heap

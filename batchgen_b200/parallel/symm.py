@@ -23,8 +23,13 @@ MAX_WORLD = 8
 
 
 class SymmetricHeap:
-    def __init__(self, nbytes: int, device, group=None):
+    GUARD_BYTE = 0xA5
+
+    def __init__(self, nbytes: int, device, group=None, guard_bytes: int = 0):
+        """``guard_bytes`` > 0 (debug: ``BG_COMM_GUARD=1`` in ``FusedComm``) puts a poisoned band after every region;
+        ``check_guards`` then names the regions past whose end somebody - this rank or a peer - has written."""
         import torch.distributed._symmetric_memory as symm_mem
+        self.guard_bytes = int(guard_bytes)
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -51,7 +56,25 @@ class SymmetricHeap:
             raise MemoryError(f"symmetric heap exhausted: {name} needs {nbytes} B at {off} of {self.nbytes}")
         self._off = off + nbytes
         self.regions[name] = (off, nbytes)
+        if self.guard_bytes:
+            g0 = self._off
+            if g0 + self.guard_bytes > self.nbytes:
+                raise MemoryError(f"symmetric heap exhausted by the guard band of {name}")
+            self.local[g0: g0 + self.guard_bytes].fill_(self.GUARD_BYTE)
+            self._off = g0 + self.guard_bytes
         return off
+
+    def check_guards(self) -> List[str]:
+        """Regions whose guard band no longer holds the poison pattern (call after a synchronisation)."""
+        bad = []
+        if not self.guard_bytes:
+            return bad
+        torch.cuda.synchronize()
+        for name, (off, nbytes) in self.regions.items():
+            band = self.local[off + nbytes: off + nbytes + self.guard_bytes]
+            if not bool((band == self.GUARD_BYTE).all()):
+                bad.append(name)
+        return bad
 
     def view(self, name: str, dtype: torch.dtype, shape) -> torch.Tensor:
         off, nbytes = self.regions[name]

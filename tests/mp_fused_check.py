@@ -117,8 +117,12 @@ def main():
            "repeatable": bool(torch.equal(outs[0], outs[-1]) and a2a_ok),
            "argmax_agree": float((got.argmax(-1) == want_loc.argmax(-1)).float().mean()),
            "nvlink_bytes": comm.nvlink_bytes, "decode_request_parallel_rel": dec_rel}
+    torch.cuda.synchronize()
+    dist.barrier()
+    overrun = comm.heap.check_guards()        # poisoned bands after every region of the symmetric heap (BG_COMM_GUARD=1)
     t = torch.tensor([res["rel_fused_vs_full"], res["rel_nccl_vs_full"], float(res["repeatable"]),
-                      res["argmax_agree"], dec_rel if dec_rel is not None else 0.0, res["rel_fused_vs_nccl"]], device=dev)
+                      res["argmax_agree"], dec_rel if dec_rel is not None else 0.0, res["rel_fused_vs_nccl"],
+                      float(len(overrun))], device=dev)
     tmax = t.clone()
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     tmin = t.clone()
@@ -126,7 +130,8 @@ def main():
     if rank == 0:
         print(json.dumps({"world": world, "rel_fused_vs_full_max": float(tmax[0]), "rel_nccl_vs_full_max": float(tmax[1]),
                           "repeatable_all": bool(tmin[2] > 0.5), "argmax_agree_min": float(tmin[3]),
-                          "rel_fused_vs_nccl_max": float(tmax[5]),
+                          "rel_fused_vs_nccl_max": float(tmax[5]), "guard_bands_on": comm.heap.guard_bytes > 0,
+                          "guard_overruns_max": int(tmax[6]),
                           "nvlink_bytes": res["nvlink_bytes"],
                           "decode_request_parallel_rel_max": float(tmax[4]) if dec_rel is not None else None}))
     dist.destroy_process_group()

@@ -11,8 +11,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(script, nproc, timeout=600):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+def _run(script, nproc, timeout=600, **extra_env):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, script)]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env)
@@ -26,8 +26,9 @@ def _run(script, nproc, timeout=600):
 def test_fused_sequence_parallel_forward_matches():
     n = 2 if torch.cuda.device_count() < 4 else min(8, torch.cuda.device_count())
     n = 1 << (n.bit_length() - 1)
-    res = _run("mp_fused_check.py", n)
+    res = _run("mp_fused_check.py", n, BG_COMM_GUARD="1")
     assert res["repeatable_all"]
+    assert res["guard_bands_on"] and res["guard_overruns_max"] == 0, res     # nobody wrote past a heap region
     assert res["rel_nccl_vs_full_max"] < 0.08, res
     assert res["rel_fused_vs_full_max"] < 0.08, res
     assert res["argmax_agree_min"] > 0.8, res
