@@ -23,6 +23,7 @@ every rank again holds every token before the next scheduling decision.
 from __future__ import annotations
 
 import time
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence as Seq
 
@@ -32,6 +33,7 @@ from ..config import EngineConfig, ModelConfig
 from ..models.transformer import AttnMeta, Transformer
 from ..ops import sampling as sampling_ops
 from . import scheduler as sched
+from . import trajectory as trajectory_mod
 from . import wave_plan
 from .kv_cache import HostStateStore, PagedKVCache, build_block_table, slots_for_range
 from .prefix_cache import PrefixCache
@@ -71,6 +73,8 @@ class EngineStats:
     prefill_chunks: int = 0            # forwards that computed a piece of a prompt longer than max_prefill_tokens
     growth_evictions: int = 0          # parked rows evicted to make host-tier room for a row that had to be parked
     transfer_waits: int = 0            # times the host blocked on a page transfer (pool exhausted with copies in flight)
+    trajectory_frontiers: int = 0      # finished turns of sessions whose pages were pinned as the session's frontier
+    trajectory_restores: int = 0       # turns that extended their session's frontier
     prefix_promoted_pages: int = 0     # prefix pages brought back from the host tier's coordinator
 
     def summary(self) -> Dict[str, float]:
@@ -125,6 +129,15 @@ class Engine:
         if self.kv.state is not None and self.host_kv is not None:
             self.host_state = HostStateStore(self.kv.state, ecfg.max_host_state_items or 4 * state_slots)
         self.prefix = PrefixCache(self.kv.alloc, ecfg.page_size) if ecfg.enable_prefix_cache else None
+        # session frontiers: the pages of a session's last finished turn hold an extra reference, so cache pressure
+        # from other requests cannot evict a live conversation's context (released by end_session, by a diverging
+        # prompt, or oldest first when the pool runs short)
+        self.trajectories = None
+        self._session_lru: "OrderedDict[str, None]" = OrderedDict()
+        if self.prefix is not None:
+            self.trajectories = trajectory_mod.TrajectoryFrontierRegistry(
+                ecfg.page_size, self.kv.bytes_per_page(),
+                release_fn=lambda rec: self.kv.alloc.free(list(rec.page_ids)))
         self.kv_token_budget = (ecfg.max_model_len if ecfg.max_model_len > 0 else n_pages * ecfg.page_size)
         self.seqs: Dict[int, Sequence] = {}
         self._next_idx = 0
@@ -149,7 +162,8 @@ class Engine:
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt_ids: Seq[int], params: Optional[SamplingParams] = None, custom_id: str = "",
-                    batch_id: str = "", prefill_order: Optional[int] = None) -> Sequence:
+                    batch_id: str = "", prefill_order: Optional[int] = None,
+                    session_id: Optional[str] = None) -> Sequence:
         if len(prompt_ids) == 0:
             raise ValueError("empty prompt")
         params = params or SamplingParams()
@@ -160,7 +174,25 @@ class Engine:
                      custom_id=custom_id, batch_id=batch_id, prefill_order=prefill_order)
         self._next_idx += 1
         self.seqs[s.global_idx] = s
+        if session_id and self.trajectories is not None:
+            s.session_id = session_id
+            # the session's committed frontier: a hit means the turn extends it (its pages come back through the
+            # prefix cache, pinned until now by the frontier); a prompt that diverges makes the frontier useless
+            res = self.trajectories.resolve(session_id, s.prompt_ids)
+            if res.hit:
+                self.stats.trajectory_restores += 1
+                res.record.release()                    # the sequence takes its own page references at prefill
+            elif res.reason == trajectory_mod.DECLINE_PROMPT_DIVERGES:
+                self.end_session(session_id)
         return s
+
+    def end_session(self, session_id: str) -> bool:
+        """Drop the session's frontier (its pages go back to being ordinary prefix-cache entries)."""
+        if self.trajectories is None or self.trajectories.get(session_id) is None:
+            return False
+        self.trajectories.evict(session_id)
+        self._session_lru.pop(session_id, None)
+        return True
 
     def adopt_sequence(self, prompt_ids: Seq[int], output_ids: Seq[int], params: Optional[SamplingParams] = None,
                        custom_id: str = "", batch_id: str = "", gpu_pages: Optional[List[int]] = None) -> Sequence:
@@ -237,7 +269,15 @@ class Engine:
         if self.prefix is None:
             return 0
         # demoted pages count as free at once (``_free_pages``); ``_take_pages`` waits for their copies if it must
-        return self.prefix.evict(want, on_evict=self._demote_prefix_page if self.host_tier else None)
+        on_evict = self._demote_prefix_page if self.host_tier else None
+        got = self.prefix.evict(want, on_evict=on_evict)
+        if got < want and self.trajectories is not None and len(self.trajectories):
+            # still short: the oldest idle sessions give up their pins, then the cache can let those pages go
+            if self.trajectories.evict_for_pages(want - got, list(self._session_lru)):
+                for sid in [k for k in self._session_lru if self.trajectories.get(k) is None]:
+                    self._session_lru.pop(sid, None)
+                got += self.prefix.evict(want - got, on_evict=on_evict)
+        return got
 
     def _demote_prefix_page(self, key: bytes, page: int) -> bool:
         """A prefix page leaves the device cache: keep it in the host tier's coordinator.  Returns True when the
@@ -270,6 +310,14 @@ class Engine:
             # (batchgen/prefix_reuse/trajectory_commit.py: a finished turn commits its KV up to a page boundary)
             if self.prefix.commit(s.all_ids[: s.num_cached_tokens], s.gpu_pages):
                 self.stats.trajectory_commits += 1
+            sid = getattr(s, "session_id", None)
+            full = s.num_cached_tokens // self.buf.page_size
+            if sid and self.trajectories is not None and full >= 1:
+                self.kv.alloc.share(s.gpu_pages[:full])                     # the frontier's own references
+                self.trajectories.advance(sid, s.all_ids[: s.num_cached_tokens], s.gpu_pages[:full])
+                self._session_lru.pop(sid, None)
+                self._session_lru[sid] = None
+                self.stats.trajectory_frontiers += 1
         if s.gpu_pages:
             self.kv.alloc.free(s.gpu_pages)
             s.gpu_pages = []

@@ -100,6 +100,7 @@ class Sequence:
     host_pages: List[int] = field(default_factory=list)     # physical host pages in order
     state_slot: int = -1                                    # recurrent-state slot (models with KDA layers)
     state_item: int = -1                                    # host item holding the state while the row is on hold
+    session_id: Optional[str] = None                        # agent session this request is a turn of
     inflight_tokens: int = 0                                # decode steps launched whose token is not on the host yet
     decode_owner: int = -1                                  # TP rank whose KV copy is kept current (request-split decode)
     num_cached_tokens: int = 0                              # tokens whose KV exists (either tier)

@@ -155,7 +155,7 @@ class BatchScheduler:
             if not picked:
                 continue
             entries = [{"slot": s, "batch_id": r.batch_id, "request_id": r.request_id, "prompt_ids": r.prompt_ids,
-                        "sampling": r.sampling} for s, r in picked]
+                        "sampling": r.sampling, "session_id": r.meta.get("session_id")} for s, r in picked]
             self.worker.request_queue.put({"type": "admit", "entries": entries})
 
     # ------------------------------------------------------------------ completions
@@ -260,13 +260,20 @@ class BatchScheduler:
                 w.put({"type": "completion", "finish_reason": f"error: {reason}", "output_ids": [], "prompt_tokens": 0})
 
     # ------------------------------------------------------------------ synchronous single request (sessions)
-    def submit_turn(self, prompt_ids: List[int], sampling: Dict[str, Any], timeout: float = 600.0) -> Dict[str, Any]:
+    def end_session(self, session_id: str) -> None:
+        """Tell the workers that a session is over: its pinned frontier pages become ordinary cache entries."""
+        if self.worker.state == "ready":
+            self.worker.request_queue.put({"type": "end_session", "session_id": session_id})
+
+    def submit_turn(self, prompt_ids: List[int], sampling: Dict[str, Any], timeout: float = 600.0,
+                    session_id: Optional[str] = None) -> Dict[str, Any]:
         bid = "turn-" + uuid.uuid4().hex[:16]
         q: "queue_mod.Queue" = queue_mod.Queue()
         self._turn_waiters[bid] = q
         self.pool.register_batch(bid, 1)
         try:
-            self.intake.submit_batch([IntakeRequest(bid, "turn", list(prompt_ids), dict(sampling), NORMAL)])
+            self.intake.submit_batch([IntakeRequest(bid, "turn", list(prompt_ids), dict(sampling), NORMAL,
+                                                    meta={"session_id": session_id})])
             return q.get(timeout=timeout)
         finally:
             self._turn_waiters.pop(bid, None)

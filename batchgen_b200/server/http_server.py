@@ -206,11 +206,15 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
 
     @app.post("/v1/sessions/{sid}/close")
     def close_session(sid: str) -> SessionObject:
-        return sessions.end(sid, "closed")
+        out = sessions.end(sid, "closed")
+        scheduler.end_session(sid)
+        return out
 
     @app.post("/v1/sessions/{sid}/abort")
     def abort_session(sid: str) -> SessionObject:
-        return sessions.end(sid, "aborted")
+        out = sessions.end(sid, "aborted")
+        scheduler.end_session(sid)
+        return out
 
     @app.post("/v1/turns")
     def turn(req: TurnRequest) -> TurnResponse:
@@ -228,7 +232,7 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
         sampling = dict(temperature=req.temperature or 0.0, top_p=req.top_p or 1.0, top_k=req.top_k or 0,
                         max_new_tokens=req.max_completion_tokens or req.max_tokens or 256, ignore_eos=req.ignore_eos,
                         seed=None)
-        m = scheduler.submit_turn(prompt, sampling)
+        m = scheduler.submit_turn(prompt, sampling, session_id=s.id)
         fr = m.get("finish_reason") or ""
         if fr.startswith("error"):
             raise HTTPException(500, fr)

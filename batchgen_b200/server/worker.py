@@ -246,6 +246,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                 kind = m.get("type")
                 if kind == "shutdown":
                     running = False
+                elif kind == "end_session":
+                    eng.end_session(m["session_id"])
                 elif kind == "cancel":
                     cancelled.add(m["batch_id"])
                     for s in list(eng.seqs.values()):
@@ -259,7 +261,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                             if e.get("qb") is not None:
                                 qs, base, n = e["qb"]
                                 ids = flat[base:base + n].tolist()
-                            s = eng.add_request(ids, sp, custom_id=e["request_id"], batch_id=e["batch_id"])
+                            s = eng.add_request(ids, sp, custom_id=e["request_id"], batch_id=e["batch_id"],
+                                                session_id=e.get("session_id"))
                             by_idx[s.global_idx] = {"slot": e["slot"], "batch_id": e["batch_id"],
                                                     "request_id": e["request_id"], "qb_slot": qs}
                         except Exception as ex:  # noqa: BLE001  (bad request: report, keep serving)

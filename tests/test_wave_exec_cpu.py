@@ -80,3 +80,34 @@ def test_second_turn_of_a_session_restores_the_first_turns_kv():
     assert s2.cached_prefix_tokens == 64
     want = plain.generate([turn2], SamplingParams(max_new_tokens=5, ignore_eos=True))[0]
     assert s2.output_ids == want
+
+
+def test_session_frontier_survives_cache_pressure_until_the_session_ends():
+    """A session's last finished turn is pinned (an extra page reference held by its frontier): other requests that
+    churn the prefix cache cannot evict it, the next turn restores it, and ending the session releases the pin."""
+    cfg, plain = _engine(False)
+    rng = random.Random(3)
+    tok = lambda n: [rng.randrange(2, cfg.vocab_size) for _ in range(n)]
+    sp = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    _, eng = _engine(True, pages=40)
+    turn1 = tok(52)
+    s1 = eng.add_request(turn1, sp, session_id="chat-1")
+    eng.run_to_completion()
+    assert eng.stats.trajectory_frontiers == 1 and len(eng.trajectories) == 1
+    pinned = list(eng.trajectories.get("chat-1").page_ids)               # 52 + 11 cached tokens -> 3 full pages
+    assert len(pinned) == 3 and all(eng.kv.alloc.refcount(p) == 2 for p in pinned)
+    # unrelated traffic larger than the pool: the cache evicts its own entries, not the pinned pages
+    for _ in range(6):
+        eng.generate([tok(100)], SamplingParams(max_new_tokens=3, ignore_eos=True))
+    assert all(eng.kv.alloc.refcount(p) >= 2 for p in pinned)
+    turn2 = turn1 + s1.output_ids + tok(9)
+    s2 = eng.add_request(turn2, SamplingParams(max_new_tokens=4, ignore_eos=True), session_id="chat-1")
+    eng.run_to_completion()
+    assert eng.stats.trajectory_restores == 1 and s2.cached_prefix_tokens == 48
+    assert s2.output_ids == plain.generate([turn2], SamplingParams(max_new_tokens=4, ignore_eos=True))[0]
+    # the new frontier replaced the old one; a diverging prompt or end_session drops it
+    assert eng.stats.trajectory_frontiers == 2 and len(eng.trajectories) == 1
+    assert eng.end_session("chat-1") and len(eng.trajectories) == 0 and not eng.end_session("chat-1")
+    eng.prefix.clear()
+    assert eng.kv.alloc.num_used == 0
+    eng.trajectories.check_invariants()
