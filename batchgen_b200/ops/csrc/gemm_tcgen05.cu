@@ -597,18 +597,23 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int a_
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int KB = p.K / (BK_BYTES / eb);
     SplitKWorkspace& ws = splitk_workspace();
-    // Pick the split count that minimises (waves of work items) / S plus a per-split reduction cost.  Few tiles
-    // (less than half a wave): up to 16 splits.  One to two waves (e.g. 168 tiles on 148 SMs: the second wave
-    // is 14 % full): up to 4, the partial tiles' traffic grows with tiles x S.
+    // Pick the split count from a cost model in units of one K block of one tile: a work item costs its K blocks
+    // plus a fixed part (pipeline fill, accumulator hand-off, epilogue: about 10), the tile's last split pays about
+    // 3 per partial it reduces, and items run in waves over the SMs.  Measured anchors: o_proj at 384 rows (168
+    // tiles, 128 K blocks) 145 -> 121 us with a split; the shared expert's down projection (168 tiles, 16 K
+    // blocks) 25 -> 48 us when it was split, so short K stays whole.
     int S = 1;
     if (ws.ws != nullptr && tiles < 2 * num_sms && tiles <= ws.max_tiles) {
-      const int s_max = tiles * 2 <= num_sms ? 16 : 4;
-      float best = (float)((tiles + num_sms - 1) / num_sms) + 0.02f;
-      for (int c = 2; c <= s_max; ++c) {
-        if (KB / c < 4 || (size_t)tiles * c > ws.max_items) break;
-        const float cost = (float)((tiles * c + num_sms - 1) / num_sms) / (float)c + 0.02f * (float)c;
-        if (cost < 0.97f * best) {
-          best = cost;
+      auto cost = [&](int c) {
+        const int waves = (tiles * c + num_sms - 1) / num_sms;
+        return (float)waves * ((float)KB / (float)c + 10.0f) + (c > 1 ? 3.0f * (float)c : 0.0f);
+      };
+      float best = 0.9f * cost(1);                 // a split has to win by a margin
+      for (int c = 2; c <= 16; ++c) {
+        if (KB / c < 2 || (size_t)tiles * c > ws.max_items) break;
+        const float v = cost(c);
+        if (v < best) {
+          best = v;
           S = c;
         }
       }

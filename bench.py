@@ -415,7 +415,10 @@ def main() -> int:
         seqs.append(eng.adopt_sequence(toks[: prompt_lens[i]], toks[prompt_lens[i]:], forced))
     # ---- decode step inputs (device resident for the kernel-timed number)
     ids_h = torch.tensor([s.all_ids[-1] for s in seqs], dtype=torch.int32)
-    bt_h = torch.zeros(B, max(pages_per_seq) + e2e_buffer_pages + 1, dtype=torch.int32)
+    bt_cols = max(pages_per_seq) + e2e_buffer_pages + 1
+    if args.bct:                                           # the batch workload's longest row: 4,096 + forced tokens
+        bt_cols = max(bt_cols, (4096 + args.bct_tokens) // page + e2e_buffer_pages + 8)
+    bt_h = torch.zeros(B, bt_cols, dtype=torch.int32)
     for i, s in enumerate(seqs):
         bt_h[i, : len(s.gpu_pages)] = torch.tensor(s.gpu_pages, dtype=torch.int32)
     pos_h = torch.tensor(ctx, dtype=torch.int32)
