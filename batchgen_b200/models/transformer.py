@@ -99,6 +99,7 @@ class Transformer:
         # i // (T / world) for as long as it decodes); off by default because the engine may re-order rows
         self.attn_request_parallel = False
         self.streamer = None          # models.streaming.StreamedExperts when the routed experts live in host memory
+        self.overlap_shared_expert = os.environ.get("BG_OVERLAP_SHARED", "1") != "0"   # decode: shared expert on a side stream
         self.expanded_prefill_min_tokens = 256   # below this the absorbed kernel is as fast and saves the kv_b GEMM
 
     # ------------------------------------------------------------------ helpers
@@ -226,6 +227,11 @@ class Transformer:
                                     cfg.rms_eps)
         with tm.timed("attn.o_proj", l):
             return linear(o, lw.wo)
+
+    def _side_stream(self):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     def _request_parallel(self, meta: AttnMeta, T: int) -> bool:
         return (self.attn_request_parallel and meta.mode == "decode" and self.comm is not None
@@ -540,12 +546,25 @@ class Transformer:
                     idx, w = moe_ops.router_topk(logits, lw.router_bias, cfg.num_experts_per_tok, cfg.n_group,
                                                  cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor,
                                                  cfg.scoring_func, num_valid=nv_local)
-                shared = None
+                shared, join = None, None
                 if lw.w13 is not None:
-                    with tm.timed("moe.shared_expert", l):
-                        shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+                    if self.overlap_shared_expert and x.is_cuda and meta.mode == "decode" and not tm.enabled:
+                        # decode: the shared expert (weight streaming) runs on a side stream under the dispatch
+                        # chain (counts -> layout -> send: one-CTA kernels and peer handshakes that leave the GPU
+                        # idle); the combine, which adds its output, waits for it.  Safe with the split-K scratch:
+                        # at these sizes both of its GEMMs are swapped-operand launches, which do not use it.
+                        main = torch.cuda.current_stream()
+                        side = self._side_stream()
+                        side.wait_stream(main)
+                        with torch.cuda.stream(side):
+                            shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+                        shared.record_stream(main)
+                        join = lambda: main.wait_stream(side)      # noqa: E731
+                    else:
+                        with tm.timed("moe.shared_expert", l):
+                            shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
                 with tm.timed("moe.routed_experts", l):
-                    src = comm.moe_sp(x, idx, w, lw.experts, extra=shared, timer=self.timer)
+                    src = comm.moe_sp(x, idx, w, lw.experts, extra=shared, timer=self.timer, before_combine=join)
             else:
                 with tm.timed("sp.norm_push", l):
                     comm.sp_norm_push(None, residual, lw.post_norm, eps, from_rs=True, has_residual=True, push=True,

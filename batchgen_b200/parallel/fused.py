@@ -283,8 +283,9 @@ class FusedComm(NcclComm):
 
     # ------------------------------------------------------------------ expert parallel
     def moe_sp(self, h_local: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
-               extra: Optional[torch.Tensor] = None, timer=None) -> torch.Tensor:
-        """Routed-expert output for this rank's own rows (dispatch -> experts -> combine)."""
+               extra: Optional[torch.Tensor] = None, timer=None, before_combine=None) -> torch.Tensor:
+        """Routed-expert output for this rank's own rows (dispatch -> experts -> combine).  ``before_combine`` is
+        called right before the combine reads ``extra`` (the caller may have computed it on another stream)."""
         if timer is None:
             from ..utils.timing import null_timer
             timer = null_timer()
@@ -302,7 +303,8 @@ class FusedComm(NcclComm):
             rc = L.bg_ep_count_push(_ext.ptr(topk_idx), ctypes.c_int(Tl * K), ctypes.c_int(E),
                                     self.heap.peer_ptrs("cnt"), ctypes.c_int(self.rank), ctypes.c_int(W),
                                     self.flag_ptrs, ctypes.c_int(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
-                                    _ext.ptr(self.recv_info), ctypes.c_int(self.recv_cap), st)
+                                    _ext.ptr(self.recv_info),
+                                    ctypes.c_int(min(self.recv_cap, _pad(W * Tl * K, align) + (E // W) * align)), st)
             _ext.check(rc, "bg_ep_count_push")
             rc = L.bg_ep_layout(_ext.ptr(self.cnt), self._flag_ptr(CNT_READY), ctypes.c_uint32(e_cnt), self._base(),
                                 ctypes.c_int(E), ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_int(align),
@@ -385,6 +387,8 @@ class FusedComm(NcclComm):
             rc = L.bg_wait_flags(self._flag_ptr(RET_READY), ctypes.c_int(W), ctypes.c_uint32(e_ret), self._base(),
                                  self._status(), st)
             _ext.check(rc, "bg_wait_flags")
+            if before_combine is not None:
+                before_combine()
             return moe_ops.combine(self.ret[: Tl * K], self.ident_pos[: Tl * K].view(Tl, K), topk_w, extra)
 
 
