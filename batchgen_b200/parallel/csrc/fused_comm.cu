@@ -22,6 +22,8 @@
 // batchgen/moe/fused_moe_mxfp4_resident.py:1020-1095) and the DeepEP low-latency dispatch/combine
 // wrapper batchgen/moe/deepep_ll.py:240-400.
 #define BG_FILE_TAG 10      // kernel-trace ids of this file are (tag << 16) | line
+#include <cooperative_groups.h>
+
 #include "../../ops/csrc/common.cuh"
 
 namespace bg {
@@ -56,7 +58,7 @@ __device__ __forceinline__ void cta_done_signal(unsigned int* counter, const Pee
   if (threadIdx.x == 0) {
     __threadfence_system();
     const unsigned int prev = atomicAdd(counter, 1u);
-    if (prev == gridDim.x - 1) {
+    if (prev == gridDim.x * gridDim.y * gridDim.z - 1) {
       *counter = 0u;
       __threadfence_system();
       signal_all(flags, index, world, epoch);
@@ -65,7 +67,10 @@ __device__ __forceinline__ void cta_done_signal(unsigned int* counter, const Pee
 }
 
 // ---------------------------------------------------------------------------------------------
-// One block per owned row.  partials: [n_src, rows, H] bf16 in this rank's memory (n_src = world when
+// One cluster of gridDim.y blocks per owned row, each block a contiguous range of 128-column groups; the row's sum
+// of squares is combined over the cluster through distributed shared memory (a decode step has few rows: one block
+// per row left most SMs idle and made every thread walk several vectors and eight peers serially).
+// partials: [n_src, rows, H] bf16 in this rank's memory (n_src = world when
 // fed by GEMM->reduce-scatter, 1 when the input is a local tensor).  residual [rows, H] in/out.
 // Outputs: y (bf16, local, optional), local e4m3 + scales (optional), and the pushed copy into every
 // rank's gather buffer at row (my_rank * rows + r): ag_q [T, H] e4m3, ag_s [KB, ag_s_stride] fp32.
@@ -82,8 +87,15 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
   const uint32_t epoch = epoch_e.get();
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
+  __shared__ float part_ss;
   __shared__ int wait_ok;
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   const int r = blockIdx.x;
+  const int parts = gridDim.y;
+  const int groups_pp = (H / 128 + parts - 1) / parts;            // 128-column groups per block
+  const int v_lo = blockIdx.y * groups_pp * 16;
+  const int v_hi = min(H / 8, v_lo + groups_pp * 16);
   if (src_ready != nullptr) {
     if (threadIdx.x == 0) {
       int ok = 1;
@@ -95,7 +107,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
     __syncthreads();
   }
   float ss = 0.f;
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  for (int v = v_lo + threadIdx.x; v < v_hi; v += blockDim.x) {
     float f[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) f[i] = 0.f;
@@ -130,18 +142,25 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
     *reinterpret_cast<uint4*>(residual + (size_t)r * H + v * 8) = *reinterpret_cast<const uint4*>(o);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      rowbuf[v * 8 + i] = f[i];
+      rowbuf[(v - v_lo) * 8 + i] = f[i];
       ss += f[i] * f[i];
     }
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) t += red[i];
+    part_ss = t;
+  }
+  cluster.sync();                                                  // every block's partial sum is published
   float tot = 0.f;
-  for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+  for (int q = 0; q < parts; ++q) tot += *cluster.map_shared_rank(&part_ss, q);   // fixed order: reproducible
+  cluster.sync();                                                  // nobody leaves while its sum may still be read
   const float rstd = rsqrtf(tot / (float)H + eps);
   const int grow = my_rank * rows + r;
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  for (int v = v_lo + threadIdx.x; v < v_hi; v += blockDim.x) {
     uint4 wraw = *reinterpret_cast<const uint4*>(w + v * 8);
     const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wraw);
     __align__(16) __nv_bfloat162 o[4];
@@ -149,7 +168,8 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float2 ww = __bfloat1622float2(wp[i]);
-      o[i] = __floats2bfloat162_rn(rowbuf[v * 8 + 2 * i] * rstd * ww.x, rowbuf[v * 8 + 2 * i + 1] * rstd * ww.y);
+      o[i] = __floats2bfloat162_rn(rowbuf[(v - v_lo) * 8 + 2 * i] * rstd * ww.x,
+                                   rowbuf[(v - v_lo) * 8 + 2 * i + 1] * rstd * ww.y);
       float2 b = __bfloat1622float2(o[i]);
       yv[2 * i] = b.x;
       yv[2 * i + 1] = b.y;
@@ -411,7 +431,12 @@ int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_r
   using namespace bg::comm;
   if (rows <= 0) return 0;
   if (H % 128 != 0 || world > kMaxWorld) return -1;
-  bg::launch_pdl(sp_norm_quant_push_kernel, dim3(rows), dim3(256), (size_t)H * sizeof(float), stream, 
+  // few rows (decode): four blocks per row in one cluster; many rows (prefill): one block per row as before
+  const int groups = H / 128;
+  int parts = 1;
+  if (rows <= 1024) parts = groups % 4 == 0 ? 4 : (groups % 2 == 0 ? 2 : 1);
+  bg::launch_pdl_cluster(sp_norm_quant_push_kernel, dim3(rows, parts), dim3(256), dim3(1, parts, 1),
+                         (size_t)H * sizeof(float), stream, 
       reinterpret_cast<const __nv_bfloat16*>(partials), n_src, src_ready, Epoch{wait_epoch, epoch_base},
       reinterpret_cast<__nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<uint8_t*>(loc_q), loc_s, loc_s_stride, to_peers(ag_q, world),
