@@ -45,6 +45,30 @@ struct Epoch {
   __device__ __forceinline__ uint32_t get() const { return off + (base != nullptr ? *base : 0u); }
 };
 
+// One store that NVSwitch delivers to the same offset of every rank's mapping (multicast address of a symmetric
+// region; NVLS).  Bits are stored as they are.
+struct Multicast {
+  void* ag_q = nullptr;
+  void* ag_s = nullptr;
+  void* cnt = nullptr;
+};
+inline Multicast& multicast() {
+  static Multicast per_device[bg::kMaxDevices];
+  static Multicast none;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= bg::kMaxDevices) return none;
+  return per_device[dev];
+}
+
+__device__ __forceinline__ void multimem_st_b64(void* mc_addr, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y))
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_b32(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(__uint_as_float(v)) : "memory");
+}
+
 __device__ __forceinline__ void signal_all(const Peers& flags, int index, int world, uint32_t epoch) {
   // callers have fenced (system scope) after the data stores; the flag stores themselves need no fence each
   for (int r = 0; r < world; ++r) st_relaxed_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + index, epoch);
@@ -81,7 +105,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
                           uint8_t* __restrict__ loc_q, float* __restrict__ loc_s, int loc_s_stride, Peers ag_q,
                           Peers ag_s, int ag_s_stride, int push, int rows, int H, float eps, int my_rank, int world,
                           Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter, int* status,
-                          int has_residual) {
+                          int has_residual, uint8_t* __restrict__ mc_q, float* __restrict__ mc_s) {
   bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t wait_epoch = wait_epoch_e.get();
   const uint32_t epoch = epoch_e.get();
@@ -190,7 +214,11 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
       *reinterpret_cast<uint2*>(loc_q + (size_t)r * H + v * 8) = qv;
       if ((threadIdx.x & 15) == 0) loc_s[(size_t)(v / 16) * loc_s_stride + r] = sc;
     }
-    if (push) {
+    if (push && mc_q != nullptr) {
+      // NVLS: one multicast store reaches every rank's gather buffer (this rank's own copy included)
+      multimem_st_b64(mc_q + (size_t)grow * H + v * 8, qv);
+      if ((threadIdx.x & 15) == 0) multimem_st_b32(mc_s + (size_t)(v / 16) * ag_s_stride + grow, __float_as_uint(sc));
+    } else if (push) {
       for (int d = 0; d < world; ++d) {   // own copy first, then peers in ring order
         const int dst = (my_rank + d) % world;
         *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(ag_q.p[dst]) + (size_t)grow * H + v * 8) = qv;
@@ -207,7 +235,7 @@ sp_norm_quant_push_kernel(const __nv_bfloat16* __restrict__ partials, int n_src,
 // every rank's count matrix cnt[src = my_rank][E]; also clears this rank's return-address table.
 __global__ void __launch_bounds__(1024)
 ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers cnt, int my_rank, int world, Peers flags,
-                     int ready_index, Epoch epoch_e, int2* __restrict__ row_info, int row_cap) {
+                     int ready_index, Epoch epoch_e, int2* __restrict__ row_info, int row_cap, int* __restrict__ mc_cnt) {
   bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   const uint32_t epoch = epoch_e.get();
   __shared__ int c[kMaxExperts];
@@ -219,9 +247,14 @@ ep_count_push_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, Peers
     if (e >= 0 && e < E) atomicAdd(&c[e], 1);
   }
   __syncthreads();
-  for (int d = 0; d < world; ++d) {
-    int* dst = reinterpret_cast<int*>(cnt.p[(my_rank + d) % world]) + (size_t)my_rank * E;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = c[e];
+  if (mc_cnt != nullptr) {               // NVLS: one multicast store per count instead of one per rank
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+      multimem_st_b32(mc_cnt + (size_t)my_rank * E + e, (uint32_t)c[e]);
+  } else {
+    for (int d = 0; d < world; ++d) {
+      int* dst = reinterpret_cast<int*>(cnt.p[(my_rank + d) % world]) + (size_t)my_rank * E;
+      for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = c[e];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -395,6 +428,44 @@ a2a_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_chunks, size_
   }
 }
 
+// Streamed-expert fan-out: the rank that brought a weight frame onto its GPU (host -> device copy into its ring
+// slot) writes the frame into the same slot of every member of the replica group, so the frame crosses PCIe once
+// per group and NVLink once per member.  members: bit r set = rank r receives a copy.  With a multicast address
+// of the slot (NVLS) one store per 16 bytes reaches every rank; without it the kernel stores to each member in turn.
+// The last CTA raises flag (index + my_rank) on every member: the frame is complete in its slot.
+__global__ void __launch_bounds__(256)
+fanout_push_kernel(const uint4* __restrict__ src, Peers dst, size_t n_vec, unsigned int members, uint4* __restrict__ mc_dst,
+                   int my_rank, int world, Peers flags, int ready_index, Epoch epoch_e, unsigned int* counter) {
+  bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
+  const uint32_t epoch = epoch_e.get();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    if (mc_dst != nullptr) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_dst + i),
+                   "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w))
+                   : "memory");
+    } else {
+      for (int d = 1; d < world; ++d) {            // ring order, the owner's own slot already holds the frame
+        const int r = (my_rank + d) % world;
+        if (members & (1u << r)) reinterpret_cast<uint4*>(dst.p[r])[i] = v;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *counter = 0u;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        if (members & (1u << r)) st_relaxed_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + ready_index + my_rank, epoch);
+    }
+  }
+}
+
 __global__ void bump_epoch_kernel(uint32_t* base, uint32_t n) {
   bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   if (threadIdx.x == 0) *base += n;
@@ -422,6 +493,16 @@ static Peers to_peers(void* const* arr, int world) {
   return p;
 }
 
+// Multicast (NVLS) addresses of the broadcast regions of the symmetric heap on the calling thread's device; null
+// = not installed: the kernels then store to each peer in turn.
+int bg_comm_set_multicast(void* ag_q, void* ag_s, void* cnt) {
+  bg::comm::Multicast& m = bg::comm::multicast();
+  m.ag_q = ag_q;
+  m.ag_s = ag_s;
+  m.cnt = cnt;
+  return 0;
+}
+
 int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_ready, uint32_t wait_epoch,
                           const uint32_t* epoch_base,
                           void* residual, int has_residual, const void* w, void* y, void* loc_q, float* loc_s,
@@ -441,7 +522,8 @@ int bg_sp_norm_quant_push(const void* partials, int n_src, const uint32_t* src_r
       reinterpret_cast<__nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<uint8_t*>(loc_q), loc_s, loc_s_stride, to_peers(ag_q, world),
       to_peers(ag_s, world), ag_s_stride, push, rows, H, eps, my_rank, world, to_peers(flags, world), ready_index,
-      Epoch{epoch, epoch_base}, counter, status, has_residual);
+      Epoch{epoch, epoch_base}, counter, status, has_residual, reinterpret_cast<uint8_t*>(multicast().ag_q),
+      reinterpret_cast<float*>(multicast().ag_s));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -452,7 +534,8 @@ int bg_ep_count_push(const int* topk_idx, int n_pairs, int E, void* const* cnt, 
   if (E > kMaxExperts || world > kMaxWorld) return -1;
   bg::launch_pdl(ep_count_push_kernel, dim3(1), dim3(1024), 0, stream, topk_idx, n_pairs, E, to_peers(cnt, world), my_rank, world,
                                                to_peers(flags, world), ready_index, Epoch{epoch, epoch_base},
-                                               reinterpret_cast<int2*>(row_info), row_cap);
+                                               reinterpret_cast<int2*>(row_info), row_cap,
+                                               reinterpret_cast<int*>(multicast().cnt));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -483,6 +566,22 @@ int bg_ep_dispatch_send(const void* hidden, int ldh, const int* topk_idx, int T,
                                                  recv_s_stride, to_peers(recv_info, world), recv_cap, sent_row, my_rank,
                                                  world, to_peers(flags, world), ready_index, Epoch{epoch, epoch_base}, counter,
                                                  status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Fan a frame of `bytes` (multiple of 16) out from `src` (this rank's slot) to dst[r] for every rank r in `members`;
+// mc_dst: multicast address of the slot or null.
+int bg_fanout_push(const void* src, void* const* dst, unsigned long long bytes, unsigned int members, void* mc_dst,
+                   int my_rank, int world, void* const* flags, int ready_index, uint32_t epoch,
+                   const uint32_t* epoch_base, unsigned int* counter, int num_sms, cudaStream_t stream) {
+  if (bytes == 0) return 0;
+  if (bytes % 16 != 0 || world < 1 || world > 8) return -1;
+  const size_t vec = bytes / 16;
+  int bx = (int)((vec + 255) / 256);
+  if (bx > 2 * num_sms) bx = 2 * num_sms;
+  bg::launch_pdl(bg::comm::fanout_push_kernel, dim3(bx), dim3(256), 0, stream, reinterpret_cast<const uint4*>(src),
+                 to_peers(dst, world), vec, members, reinterpret_cast<uint4*>(mc_dst), my_rank, world,
+                 to_peers(flags, world), ready_index, bg::comm::Epoch{epoch, epoch_base}, counter);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -88,6 +88,17 @@ class FusedComm(NcclComm):
         for k, v in sizes.items():
             self.heap.alloc(k, v)
         h = self.heap
+        # NVLS (opt-in, BG_NVLS=1): the broadcast pushes (normalised rows + scales of the all-gather, expert counts)
+        # become one multimem store each instead of one store per peer
+        self.nvls = os.environ.get("BG_NVLS", "0") == "1" and h.mc_base != 0
+        L = _ext.lib()
+        L.bg_comm_set_multicast.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        with torch.cuda.device(self.device):
+            if self.nvls:
+                L.bg_comm_set_multicast(ctypes.c_void_p(h.mc_ptr("ag_q")), ctypes.c_void_p(h.mc_ptr("ag_s")),
+                                        ctypes.c_void_p(h.mc_ptr("cnt")))
+            else:
+                L.bg_comm_set_multicast(None, None, None)
         self.flags = h.view("flags", torch.int32, (64,))
         self.flag_ptrs = h.peer_ptrs("flags")
         self.ag_q = h.view("ag_q", torch.uint8, (T, hidden)).view(FP8)

@@ -40,6 +40,11 @@ class SymmetricHeap:
         self.local.zero_()
         self.handle = symm_mem.rendezvous(self.local, self.group)
         self.base_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        # multicast (NVLS) address of the same allocation: one store to it reaches every rank's copy; 0 = no support
+        try:
+            self.mc_base = int(self.handle.multicast_ptr or 0) if self.handle.has_multicast_support else 0
+        except (AttributeError, RuntimeError):
+            self.mc_base = 0
         assert self.base_ptrs[self.rank] == self.local.data_ptr()
         self._off = 0
         self.regions: Dict[str, Tuple[int, int]] = {}
@@ -83,6 +88,11 @@ class SymmetricHeap:
         for s in shape:
             n *= s
         return t[:n].view(*shape)
+
+    def mc_ptr(self, name: str, extra_offset: int = 0) -> int:
+        """Multicast address of a region (0 when the allocation has no multicast mapping)."""
+        off, _ = self.regions[name]
+        return self.mc_base + off + extra_offset if self.mc_base else 0
 
     def peer_ptrs(self, name: str, extra_offset: int = 0):
         """ctypes array of 8 ``void*``: the region's address on every rank (null past ``world``)."""

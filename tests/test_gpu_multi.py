@@ -61,3 +61,12 @@ def test_rank_leaves_between_steps_and_survivors_carry_on():
     assert "down" in res["lost"][1], res
     assert res["ok_math"] and res["still_ok"] and res["wait_status"] == 1, res
     assert 0.15 < res["waited_s"] < 5.0, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_streamed_expert_frames_fan_out_to_the_replica_group():
+    """F5: the owner of a frame (by the replica plan) writes it into every member's ring slot over NVLink; members
+    wait on the arrival flag; slots are reused across frames."""
+    n = 2 if torch.cuda.device_count() < 4 else 4
+    res = _run("mp_fanout_check.py", n)
+    assert res["all_equal"] and res["frames"] == 4 * n, res
