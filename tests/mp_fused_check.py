@@ -130,7 +130,7 @@ def main():
     if rank == 0:
         print(json.dumps({"world": world, "rel_fused_vs_full_max": float(tmax[0]), "rel_nccl_vs_full_max": float(tmax[1]),
                           "repeatable_all": bool(tmin[2] > 0.5), "argmax_agree_min": float(tmin[3]),
-                          "rel_fused_vs_nccl_max": float(tmax[5]), "guard_bands_on": comm.heap.guard_bytes > 0,
+                          "rel_fused_vs_nccl_max": float(tmax[5]), "guard_bands_on": comm.heap.guard_bytes > 0, "nvls": bool(comm.nvls),
                           "guard_overruns_max": int(tmax[6]),
                           "nvlink_bytes": res["nvlink_bytes"],
                           "decode_request_parallel_rel_max": float(tmax[4]) if dec_rel is not None else None}))

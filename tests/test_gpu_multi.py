@@ -70,3 +70,16 @@ def test_streamed_expert_frames_fan_out_to_the_replica_group():
     n = 2 if torch.cuda.device_count() < 4 else 4
     res = _run("mp_fanout_check.py", n)
     assert res["all_equal"] and res["frames"] == 4 * n, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_nvls_broadcast_stores_give_the_same_result():
+    """BG_NVLS=1: the all-gather push and the count push use one multimem store instead of one store per peer
+    (NCCL's own NVLS stays off in this process tree).  Skipped where the allocation has no multicast mapping."""
+    res = _run("mp_fused_check.py", 2, BG_NVLS="1", NCCL_NVLS_ENABLE="0", BG_COMM_GUARD="1")
+    if not res["nvls"]:
+        pytest.skip("the symmetric allocation has no multicast mapping on this machine")
+    assert res["repeatable_all"] and res["guard_overruns_max"] == 0, res
+    assert res["rel_fused_vs_full_max"] < 0.08 and res["rel_fused_vs_nccl_max"] < 0.06, res
+    fan = _run("mp_fanout_check.py", 2, BG_NVLS="1", NCCL_NVLS_ENABLE="0")
+    assert fan["all_equal"] and fan["nvls"], fan
