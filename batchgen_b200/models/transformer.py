@@ -384,9 +384,15 @@ class Transformer:
         q = qkv[:, : Hq * D].reshape(T, Hq, D)
         k = qkv[:, Hq * D: (Hq + Hkv) * D].reshape(T, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
-        cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
-        q = ref.apply_rope(q, cos, sin, cfg.rope_interleaved)
-        k = ref.apply_rope(k, cos, sin, cfg.rope_interleaved)
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.rope.cos.shape[1] * 2 == D:
+            # in-place RoPE kernel on the (copied, contiguous) query and key heads
+            q, k = q.contiguous(), k.contiguous()
+            fused.rope_q_(q, meta.positions, self.rope.cos, self.rope.sin, D, cfg.rope_interleaved)
+            fused.rope_q_(k, meta.positions, self.rope.cos, self.rope.sin, D, cfg.rope_interleaved)
+        else:
+            cos, sin = self.rope.cos[meta.positions.long()], self.rope.sin[meta.positions.long()]
+            q = ref.apply_rope(q, cos, sin, cfg.rope_interleaved)
+            k = ref.apply_rope(k, cos, sin, cfg.rope_interleaved)
         kvc = cache.latent(l)                           # [P, page, 2 * Hkv_total * D]; this rank's slice is cached
         ref.kv_cache_write(kvc, torch.cat([k.reshape(T, -1), v.reshape(T, -1)], -1), meta.slot_mapping)
         window = cfg.sliding_window if (cfg.sliding_window and l % 2 == 0) else 0
