@@ -80,6 +80,37 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c
                : "memory");
 }
 
+// ---- CTA pairs (thread-block cluster of two): the two head-group CTAs of a chunk walk the same KV tiles, so each
+// loads half of every tile from global memory and hands its half to the partner through distributed shared memory
+// (a plain shared -> shared::cluster bulk copy; no TMA load is multicast).  KV then crosses the L2 -> SM fabric once
+// per tile instead of twice.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void dsmem_copy(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t mbar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster),
+               "r"(src_cta), "r"(bytes), "r"(mbar_cluster)
+               : "memory");
+}
+// commit that arrives on the barrier at the same offset in every CTA of `mask`
+__device__ __forceinline__ void tc_commit_mc(uint64_t* bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+
 // 16 TMEM lanes x 32 columns for each half of the warp: thread i < 16 receives columns [c, c + 32) of lane (base + i),
 // thread i + 16 receives columns [c + 32, c + 64) of the same lane.  One score row is thus split between two threads.
 __device__ __forceinline__ void tmem_ld_16x32bx2_x32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -157,11 +188,13 @@ struct TileCursor {
   }
 };
 
-__global__ void __launch_bounds__(kPersistThreads, 1)
+template <bool PAIR>
+__global__ void __launch_bounds__(PAIR ? kPersistThreads + 32 : kPersistThreads, 1)
 mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                           const __grid_constant__ CUtensorMap tm_qpe, PersistParams p) {
   bg::pdl_prologue((BG_FILE_TAG << 16) | __LINE__);
   constexpr int NS = 128;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;      // PAIR: warp 7 forwards this CTA's half of every tile
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_buf = smem;
@@ -177,7 +210,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   if (threadIdx.x == 0) {
     mbar_init(&ss.q_full, 1);
     mbar_init(&ss.q_empty, 1);
-    for (int i = 0; i < kPPairs; ++i) { mbar_init(&ss.pair_full[i], 1); mbar_init(&ss.pair_empty[i], 1); }
+    for (int i = 0; i < kPPairs; ++i) { mbar_init(&ss.pair_full[i], 1); mbar_init(&ss.pair_empty[i], PAIR ? 2 : 1); }
     for (int i = 0; i < kPRope; ++i) { mbar_init(&ss.rope_full[i], 1); mbar_init(&ss.rope_empty[i], 1); }
     mbar_init(&ss.s_full[0], 1);
     mbar_init(&ss.s_full[1], 1);
@@ -198,7 +231,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   // sums).  The array does not fit next to the tiles in shared memory: each CTA keeps its copy in global scratch,
   // written and read by this CTA only.
   int* prefix = p.prefix + (size_t)blockIdx.x * (kMaxPairsPersist + 1);
-  for (int i = threadIdx.x; i < P; i += kPersistThreads) {
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
     const int len = p.seqlens[i];
     prefix[i + 1] = (max(len, 0) + kTile - 1) / kTile;
   }
@@ -224,6 +257,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (PAIR) cluster_sync_all();          // the partner's barriers are initialised before anything arrives on them
   const uint32_t tmem_base = ss.tmem_base;
   const int total = prefix[P];
   const int n_cta = gridDim.x;
@@ -246,8 +280,14 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
         return p.block_table[(size_t)c.s.seq * p.bt_stride + c.t] * kPage;
       };
       auto prefetch_rows = [&](int row0) {
+        if (PAIR) {                          // only what this CTA loads itself
 #pragma unroll
-        for (int ch = 0; ch < 9; ++ch) tma_prefetch_l2_2d(&tm_kv, ch * 64, row0);
+          for (int ch = 0; ch < 4; ++ch) tma_prefetch_l2_2d(&tm_kv, (4 * (int)crank + ch) * 64, row0);
+          tma_prefetch_l2_2d(&tm_kv, 8 * 64, row0);
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < 9; ++ch) tma_prefetch_l2_2d(&tm_kv, ch * 64, row0);
+        }
       };
 #pragma unroll
       for (int i = 0; i < kPrefetchTiles; ++i) {
@@ -289,9 +329,11 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
           if (!mbar_wait(&ss.pair_empty[slot], ((pit / kPPairs) & 1) ^ 1, abort_flag, kTimeoutProducer)) { ok = false; break; }
           if (m == 0) BG_TR(0, rit, 0);
           mbar_expect_tx(&ss.pair_full[slot], kPairBytes);
-          uint8_t* dst = pair_buf + slot * kPairBytes;
-          tma_load_2d(dst, &tm_kv, &ss.pair_full[slot], (2 * m) * 64, row0);
-          tma_load_2d(dst + kChunkBytes, &tm_kv, &ss.pair_full[slot], (2 * m + 1) * 64, row0);
+          if (!PAIR || (uint32_t)(m >> 1) == crank) {        // PAIR: the other two slots are filled by the partner
+            uint8_t* dst = pair_buf + slot * kPairBytes;
+            tma_load_2d(dst, &tm_kv, &ss.pair_full[slot], (2 * m) * 64, row0);
+            tma_load_2d(dst + kChunkBytes, &tm_kv, &ss.pair_full[slot], (2 * m + 1) * 64, row0);
+          }
         }
         if (!ok) break;
         const int rslot = rit % kPRope;
@@ -341,7 +383,8 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
           if (g >= 2 && !mbar_wait(&ss.s_free[g & 1], ((g >> 1) - 1) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
           tc_fence_after();
           const uint32_t tm_s = tmem_base + (g & 1) * kTile;
-          for (int m = 0; m < 4 && ok; ++m) {
+          for (int mi = 0; mi < 4 && ok; ++mi) {
+            const int m = PAIR ? (mi + 2 * (int)crank) & 3 : mi;     // PAIR: the half this CTA loaded itself comes first
             const uint32_t pit = g * 4 + m;
             const int slot = pit % kPPairs;
             if (!mbar_wait(&ss.pair_full[slot], (pit / kPPairs) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
@@ -351,7 +394,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
               const uint64_t bdesc = make_smem_desc_sw128(smem_u32(pair_buf + slot * kPairBytes + cc * kChunkBytes));
 #pragma unroll
               for (int k = 0; k < 4; ++k)
-                mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, (m | cc | k) ? 1u : 0u);
+                mma_f16(tm_s, adesc + 2 * k, bdesc + 2 * k, idesc_s, (mi | cc | k) ? 1u : 0u);
             }
           }
           if (!ok) break;
@@ -400,12 +443,29 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
               const uint64_t bdesc = make_desc_mn_sw128(b_base + j * 2048, kChunkBytes, 1024);
               mma_f16(d, pdesc + 2 * j, bdesc, idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
             }
-            tc_commit(&ss.pair_empty[slot]);
+            if (PAIR) tc_commit_mc(&ss.pair_empty[slot], 0x3);   // the slot is free once both CTAs have read it
+            else tc_commit(&ss.pair_empty[slot]);
           }
           tc_commit(&ss.o_done);
           BG_TR(1, g, 5);
         }
         ++seg_no;
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------ PAIR: hand this CTA's half of every tile to the partner
+    if (PAIR && elect_one()) {
+      const uint32_t peer = crank ^ 1u;
+      const int n_tiles = ce - cb;
+      bool ok = true;
+      for (int g = 0; ok && g < n_tiles; ++g) {
+        for (int mm = 0; mm < 2 && ok; ++mm) {
+          const uint32_t pit = (uint32_t)g * 4 + 2 * crank + mm;
+          const int slot = pit % kPPairs;
+          if (!mbar_wait(&ss.pair_full[slot], (pit / kPPairs) & 1, abort_flag, kTimeoutMma)) { ok = false; break; }
+          const uint32_t src = smem_u32(pair_buf + slot * kPairBytes);
+          dsmem_copy(map_to_cta(src, peer), src, kPairBytes, map_to_cta(smem_u32(&ss.pair_full[slot]), peer));
+        }
       }
     }
   } else {
@@ -626,6 +686,7 @@ mla_decode_persist_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gri
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (PAIR) cluster_sync_all();          // neither CTA leaves while the partner may still write into or signal it
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && ss.abort_flag != 0 && p.status != nullptr) atomicMax(p.status, ss.abort_flag);
 }
@@ -665,10 +726,47 @@ int bg_mla_decode_persist(const void* q_abs, long long qabs_stride, const void* 
   p.block_table = block_table; p.bt_stride = bt_stride; p.seqlens = seqlens;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml; p.counters = counters; p.prefix = prefix_scratch;
   p.B = B; p.H = H; p.groups = groups; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  static bg::DeviceOnce attr_set;
+  static bg::DeviceOnce attr_set, attr_set_pair;
   const size_t smem = kPSmemTiles + sizeof(PersistShared) + 1024;
-  if (!bg::ensure_dynamic_smem(mla_decode_persist_kernel, smem, attr_set)) return -13;
-  bg::launch_pdl(mla_decode_persist_kernel, dim3(ctas), dim3(kPersistThreads), smem, stream, tkv, tq, tqpe, p);
+  static const bool pair_on = [] {
+    const char* e = getenv("BG_MLA_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (pair_on && groups == 2 && ctas >= 2) {
+    // CTA pairs: both head groups of a chunk in one cluster.  The grid is cut to the number of pairs that can be
+    // resident at once (a GPC with an odd number of free SMs cannot host a last pair: a second wave of a persistent
+    // kernel would double its time).
+    auto kern = mla_decode_persist_kernel<true>;
+    if (!bg::ensure_dynamic_smem(kern, smem, attr_set_pair)) return -13;
+    static int max_pairs[bg::kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < bg::kMaxDevices && max_pairs[dev] == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(ctas & ~1);
+      cfg.blockDim = dim3(kPersistThreads + 32);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = -1;
+      max_pairs[dev] = n;
+    }
+    const int mp = (dev >= 0 && dev < bg::kMaxDevices) ? max_pairs[dev] : -1;
+    if (mp > 0) {
+      int grid = ctas & ~1;
+      if (grid > 2 * mp) grid = 2 * mp;
+      bg::launch_pdl_cluster(kern, dim3(grid), dim3(kPersistThreads + 32), dim3(2, 1, 1), smem, stream, tkv, tq, tqpe, p);
+      return cudaGetLastError() == cudaSuccess ? 0 : -14;
+    }
+  }
+  if (!bg::ensure_dynamic_smem(mla_decode_persist_kernel<false>, smem, attr_set)) return -13;
+  bg::launch_pdl(mla_decode_persist_kernel<false>, dim3(ctas), dim3(kPersistThreads), smem, stream, tkv, tq, tqpe, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -14;
 }
 
