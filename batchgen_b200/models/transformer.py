@@ -428,6 +428,23 @@ class Transformer:
                                          cfg.topk_group, cfg.norm_topk_prob, cfg.routed_scaling_factor,
                                          cfg.scoring_func, num_valid=meta.num_valid)
         shared = None
+        local = self.comm is None or self.layout.ep_size <= 1
+        if (lw.w13 is not None and local and self.streamer is None and not cfg.moe_latent_size and x.is_cuda
+                and self.overlap_shared_expert and meta.mode == "decode" and not tm.enabled
+                and lw.experts.quant == "fp8_block"):
+            # decode on one GPU: the shared expert runs on a side stream while the routed path counts, permutes and
+            # gathers its rows (small kernels that leave the GPU mostly idle); the combine adds its output, so no
+            # separate add kernel either.  The router's GEMM (a split-K launch) is already queued: the side stream's
+            # GEMMs are the only users of the split-K scratch until the join.
+            main = torch.cuda.current_stream()
+            side = self._side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
+            shared.record_stream(main)
+            return moe_ops.experts_forward(x, idx, w, lw.experts, 0, cfg.n_routed_experts, extra=shared,
+                                           num_valid=meta.num_valid, timer=tm,
+                                           before_combine=lambda: main.wait_stream(side))
         if lw.w13 is not None:
             with tm.timed("moe.shared_expert", l):
                 shared = self._mlp(x, xq, xs, lw.w13, lw.w2)

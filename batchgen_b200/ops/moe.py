@@ -233,8 +233,9 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
 def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ew: ExpertWeights,
                     expert_lo: int, expert_hi: int, extra: Optional[torch.Tensor] = None,
                     num_valid: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-                    timer=None) -> torch.Tensor:
-    """Partial MoE output of one rank: sum over the (token, k) pairs whose expert is local."""
+                    timer=None, before_combine=None) -> torch.Tensor:
+    """Partial MoE output of one rank: sum over the (token, k) pairs whose expert is local (+ ``extra``).
+    ``before_combine`` is called right before the combine reads ``extra`` (it may come from another stream)."""
     if timer is None:
         from ..utils.timing import null_timer
         timer = null_timer()
@@ -259,4 +260,6 @@ def experts_forward(hidden: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.
         rows = torch.where((src >= 0).unsqueeze(-1), rows, torch.zeros_like(rows))
         y = grouped_experts(None, None, offsets, ew, x_dense=rows)
     with timer.timed("moe.combine"):
+        if before_combine is not None:
+            before_combine()
         return combine(y, pos, topk_w, extra, out_dtype or hidden.dtype)
