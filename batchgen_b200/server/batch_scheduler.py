@@ -44,6 +44,11 @@ class BatchScheduler:
         self._lock = threading.RLock()
         self._tok_pool = concurrent.futures.ThreadPoolExecutor(max_workers=4, thread_name_prefix="tokenise")
         self.capacity: Optional[Dict[str, Any]] = None
+        dp = max(1, int(getattr(args, "dp_size", 1)))
+        self._dp_load = [0] * dp                      # running sum of prompt length^2 of the requests in flight
+        self._slot_cost: Dict[int, Any] = {}          # pool slot -> (cohort, cost) until the completion arrives
+        self._session_cohort: Dict[str, int] = {}
+        self.dp_assigned = [0] * dp                   # requests handed to each cohort so far
         self.last_heartbeat: Optional[Dict[str, Any]] = None
 
     # ------------------------------------------------------------------ lifecycle
@@ -154,9 +159,28 @@ class BatchScheduler:
             picked = self.pool.select_from_intake(self.intake)
             if not picked:
                 continue
-            entries = [{"slot": s, "batch_id": r.batch_id, "request_id": r.request_id, "prompt_ids": r.prompt_ids,
-                        "sampling": r.sampling, "session_id": r.meta.get("session_id")} for s, r in picked]
-            self.worker.request_queue.put({"type": "admit", "entries": entries})
+            dp = getattr(self.worker, "dp", 1)
+            cohorts = [0] * len(picked)
+            if dp > 1:
+                # data parallelism: longest prompts first, each to the cohort with the smallest running sum of
+                # length^2 (prefill cost); a session stays with the cohort that holds its context
+                # (batchgen/batchgen_worker.py:1987-2033)
+                from ..runtime.scheduler import assign_ranks_l2
+                lens = [len(r.prompt_ids) for _, r in picked]
+                cohorts = assign_ranks_l2(lens, dp, initial_load=self._dp_load)
+                for i, (slot, r) in enumerate(picked):
+                    sid = r.meta.get("session_id")
+                    if sid:
+                        cohorts[i] = self._session_cohort.setdefault(sid, cohorts[i])
+                    cost = len(r.prompt_ids) ** 2
+                    self._dp_load[cohorts[i]] += cost
+                    self._slot_cost[slot] = (cohorts[i], cost)
+                    self.dp_assigned[cohorts[i]] += 1
+            for c in sorted(set(cohorts)):
+                entries = [{"slot": s, "batch_id": r.batch_id, "request_id": r.request_id, "prompt_ids": r.prompt_ids,
+                            "sampling": r.sampling, "session_id": r.meta.get("session_id")}
+                           for (s, r), cc in zip(picked, cohorts) if cc == c]
+                self.worker.send({"type": "admit", "entries": entries}, cohort=c)
 
     # ------------------------------------------------------------------ completions
     def _completion_loop(self) -> None:
@@ -177,6 +201,9 @@ class BatchScheduler:
                 self.worker.last_error = m.get("error")
 
     def _on_completion(self, m: Dict[str, Any]) -> None:
+        done = self._slot_cost.pop(m.get("slot"), None)
+        if done is not None:
+            self._dp_load[done[0]] = max(0, self._dp_load[done[0]] - done[1])
         bid, rid = m["batch_id"], m["request_id"]
         waiter = self._turn_waiters.get(bid)
         if waiter is not None:
@@ -232,7 +259,7 @@ class BatchScheduler:
         if t is not None:
             t.cancelled = True
         dropped = self.intake.cancel_batch(bid)
-        self.worker.request_queue.put({"type": "cancel", "batch_id": bid})
+        self.worker.send({"type": "cancel", "batch_id": bid})
         b.status, b.cancelling_at = "cancelling", int(time.time())
         self.storage.save_batch(b)
         with self._lock:
@@ -263,7 +290,8 @@ class BatchScheduler:
     def end_session(self, session_id: str) -> None:
         """Tell the workers that a session is over: its pinned frontier pages become ordinary cache entries."""
         if self.worker.state == "ready":
-            self.worker.request_queue.put({"type": "end_session", "session_id": session_id})
+            self._session_cohort.pop(session_id, None)
+            self.worker.send({"type": "end_session", "session_id": session_id})
 
     def submit_turn(self, prompt_ids: List[int], sampling: Dict[str, Any], timeout: float = 600.0,
                     session_id: Optional[str] = None) -> Dict[str, Any]:

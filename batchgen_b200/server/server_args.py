@@ -82,6 +82,7 @@ class ServerArgs:
     weight_store_stage_dir: str = ""            # copy the converted checkpoint here first (local NVMe) and verify it
     shared_weight_store: bool = True            # load the converted checkpoint once into a node-shared region
     param_store_path: str = ""                  # set by the server: descriptor path of the shared weight region
+    dp_size: int = 1                            # data-parallel cohorts: world_size / dp_size GPUs each, requests spread by sum of L^2
     query_book_mb: int = 64                     # node-shared token book (prompts + generated tokens), MiB
     instance_id: str = ""                       # stable name of this deployment (default: port<port>)
     run_mode: str = "exclusive"                 # "shared": several servers on the machine, a lane lease is mandatory
@@ -143,6 +144,8 @@ def validate_server_args(a: ServerArgs) -> ServerArgs:
                               "restart coordinator and UCX weight store have no counterpart here)")
     if a.world_size < 1 or a.world_size > 8 or a.world_size & (a.world_size - 1):
         raise ServerArgsError("--world-size must be 1, 2, 4 or 8")
+    if a.dp_size < 1 or a.world_size % a.dp_size:
+        raise ServerArgsError("--dp-size must divide --world-size")
     if a.attn_tp_size not in (0, 1, a.world_size):
         raise ServerArgsError("--attn-tp-size must be 1 (DP attention) or the world size")
     if not 0.1 <= a.gpu_memory_frac <= 0.98:

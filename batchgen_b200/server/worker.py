@@ -48,7 +48,7 @@ def setup_nccl_env() -> None:
 _STORES: list = []
 
 
-def build_engine(args, rank: int, world: int, device: str, phases=None):
+def build_engine(args, rank: int, world: int, device: str, phases=None, phase_slot: Optional[int] = None):
     import torch
 
     from ..config import get_model_config
@@ -98,8 +98,9 @@ def build_engine(args, rank: int, world: int, device: str, phases=None):
             a2a = (ecfg.max_decode_batch + 8 * world) * (cfg.num_heads // world) * cfg.kv_cache_dim * 2
         comm.configure(cfg.hidden_size, cfg.expert_hidden, cfg.n_routed_experts, cfg.num_experts_per_tok,
                        max_tokens=step_rows, a2a_bytes=a2a)
+    phase_slot = rank if phase_slot is None else phase_slot
     if phases is not None:
-        phases.enter(rank, "kv-pool")
+        phases.enter(phase_slot, "kv-pool")
     pages, host_pages = size_kv_pool(cfg, ecfg, device, model.dtype)
     host_fd = None
     if getattr(args, "host_kv_region", "") and device.startswith("cuda"):
@@ -107,7 +108,7 @@ def build_engine(args, rank: int, world: int, device: str, phases=None):
     eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages, host_kv_fd=host_fd)
     if device.startswith("cuda") and ecfg.enable_cuda_graph:
         if phases is not None:
-            phases.enter(rank, "graph-capture")
+            phases.enter(phase_slot, "graph-capture")
         from ..runtime.graphs import DecodeGraphRunner
         max_pages = -(-eng.kv_token_budget // ecfg.page_size)
         eng.graph_runner = DecodeGraphRunner(model, eng.kv, max_batch=ecfg.max_decode_batch,
@@ -129,8 +130,13 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
     import torch
     import torch.distributed as dist
 
+    dp_rank = int(getattr(args, "dp_rank", 0))
+    gpu = int(getattr(args, "gpu_offset", 0)) + rank          # data-parallel cohorts own consecutive GPUs
+    slot = int(getattr(args, "startup_slot_base", 0)) + rank
+
     def up(msg: Dict[str, Any]) -> None:
         if rank == 0:
+            msg["cohort"] = dp_rank
             response_queue.put(msg)
 
     from .startup_phases import record_of
@@ -143,10 +149,10 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
         pass
     try:
         use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
-        device = f"cuda:{rank}" if use_cuda else "cpu"
+        device = f"cuda:{gpu}" if use_cuda else "cpu"
         if use_cuda:
-            torch.cuda.set_device(rank)
-        phases.enter(rank, "communicator-init")
+            torch.cuda.set_device(gpu)
+        phases.enter(slot, "communicator-init")
         if world > 1:
             setup_nccl_env()
             dist.init_process_group("nccl" if use_cuda else "gloo", init_method=f"tcp://{args.dist_init_addr}",
@@ -154,9 +160,9 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             t = torch.ones(1, device=device)
             dist.all_reduce(t)                        # warm-up: the first collective builds the communicators
         from ..runtime.sequence import SamplingParams
-        phases.enter(rank, "model-build")
-        cfg, eng = build_engine(args, rank, world, device, phases=phases)
-        phases.enter(rank, "prewarm")
+        phases.enter(slot, "model-build")
+        cfg, eng = build_engine(args, rank, world, device, phases=phases, phase_slot=slot)
+        phases.enter(slot, "prewarm")
         log.info("worker.ready", rank=rank, device=device, gpu_pages=eng.kv.num_pages,
                  host_pages=eng.host_kv.num_pages if eng.host_kv else 0)
         up({"type": "deployment_capacity", "gpu_pages": eng.kv.num_pages, "page_size": eng.buf.page_size,
@@ -164,7 +170,7 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             "model": cfg.name, "vocab_size": cfg.vocab_size})
         if world > 1:
             dist.barrier()
-        phases.enter(rank, "serving")
+        phases.enter(slot, "serving")
         if rank == 0:
             ready_event.set()
 
@@ -292,7 +298,7 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
     except Exception as ex:  # noqa: BLE001
         log.error("worker.fatal", rank=rank, error=str(ex), trace=traceback.format_exc()[-1500:])
         recent = eng.step_ring.tail(8) if "eng" in locals() else []
-        response_queue.put({"type": "worker_fatal", "rank": rank, "error": f"{type(ex).__name__}: {ex}",
+        response_queue.put({"type": "worker_fatal", "rank": rank, "cohort": dp_rank, "error": f"{type(ex).__name__}: {ex}",
                             "recent_steps": recent})
         raise
     finally:

@@ -59,14 +59,19 @@ class WorkerManager:
     def __init__(self, args: ServerArgs, worker_target=None):
         self.args = args
         self.ctx = mp.get_context("spawn")
-        self.request_queue = self.ctx.Queue()
+        # data parallelism: dp_size cohorts of world_size / dp_size ranks, each with its own request queue (and its own
+        # process group, engine and KV pool); all report on one response queue
+        self.dp = max(1, int(getattr(args, "dp_size", 1)))
+        self.request_queues = [self.ctx.Queue() for _ in range(self.dp)]
+        self.request_queue = self.request_queues[0]
         self.response_queue = self.ctx.Queue()
         self.procs: List[mp.Process] = []
         self.generation = 0
         self.state = "stopped"
         self.last_error: Optional[str] = None
         self.capacity: Optional[Dict] = None
-        self._ready = self.ctx.Event()
+        self._ready_events = [self.ctx.Event() for _ in range(self.dp)]
+        self._ready = self._ready_events[0]
         self._shutdown = self.ctx.Event()
         self.feed = self.ctx.Value("q", 0)
         self._monitor: Optional[threading.Thread] = None
@@ -93,6 +98,11 @@ class WorkerManager:
         if h is not None:
             h(*a)
 
+    def send(self, msg: Dict, cohort: Optional[int] = None) -> None:
+        """A message for one cohort, or for all of them (cancel, end of a session, shutdown)."""
+        for c in (range(self.dp) if cohort is None else [cohort]):
+            self.request_queues[c].put(msg)
+
     # ------------------------------------------------------------------ start / stop
     def start(self, timeout: Optional[float] = None) -> None:
         with self._lock:
@@ -102,7 +112,8 @@ class WorkerManager:
             target = self._target or worker_main
             self.state = "starting"
             self.generation += 1
-            self._ready.clear()
+            for e in self._ready_events:
+                e.clear()
             self._shutdown.clear()
             self.last_error = None
             W = self.args.world_size
@@ -114,16 +125,26 @@ class WorkerManager:
             with self.startup.phase(W, "store-staging"):
                 self._load_weight_store()
             self.startup.enter(W, "serving")
-            for r in range(W):
-                self.args.param_store_index = self.weight_index      # travels with the pickled arguments
-                p = self.ctx.Process(target=target, name=f"bg-worker-{r}",
-                                     args=(r, W, self.args, self.request_queue, self.response_queue, self._ready,
-                                           self._shutdown, self.feed), daemon=True)
-                p.start()
-                self.startup.enter(r, "spawned")
-                self.procs.append(p)
+            Wc = W // self.dp
+            self.args.param_store_index = self.weight_index      # travels with the pickled arguments
+            for c in range(self.dp):
+                a = self.args
+                if self.dp > 1:                                   # the cohort's own view of the deployment
+                    import dataclasses
+                    host, port = str(self.args.dist_init_addr).rsplit(":", 1)
+                    a = dataclasses.replace(self.args, world_size=Wc, dist_init_addr=f"{host}:{int(port) + c}")
+                    for k in ("startup_record", "param_store_index"):
+                        setattr(a, k, getattr(self.args, k, None))
+                    a.dp_rank, a.gpu_offset, a.startup_slot_base = c, c * Wc, c * Wc
+                for r in range(Wc):
+                    p = self.ctx.Process(target=target, name=f"bg-worker-{c * Wc + r}",
+                                         args=(r, Wc, a, self.request_queues[c], self.response_queue,
+                                               self._ready_events[c], self._shutdown, self.feed), daemon=True)
+                    p.start()
+                    self.startup.enter(c * Wc + r, "spawned")
+                    self.procs.append(p)
         deadline = time.monotonic() + (timeout or self.args.startup_timeout)
-        while not self._ready.wait(0.1):
+        while not all(e.wait(0.1) for e in self._ready_events):
             dead = [p for p in self.procs if not p.is_alive()]
             if dead:
                 self.last_error = (f"worker {dead[0].name} exited with code {dead[0].exitcode} during start-up"
@@ -277,7 +298,7 @@ class WorkerManager:
                 self.watchdog = None
             self._shutdown.set()
             try:
-                self.request_queue.put({"type": "shutdown"})
+                self.send({"type": "shutdown"})
             except Exception:  # noqa: BLE001
                 pass
         for p in self.procs:
@@ -298,7 +319,8 @@ class WorkerManager:
         self._hook("fail_in_flight", f"workers restarting: {reason}")
         self.stop()
         # messages addressed to the old cohort must not reach the new one
-        self.request_queue = self.ctx.Queue()
+        self.request_queues = [self.ctx.Queue() for _ in range(self.dp)]
+        self.request_queue = self.request_queues[0]
         self.response_queue = self.ctx.Queue()
         self._hook("rebind_queues", self.request_queue, self.response_queue)
         self.phase = "P2"

@@ -246,3 +246,30 @@ def test_two_rank_cpu_cohort_reads_prompts_from_the_shared_token_book(tmp_path):
             out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
             texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
     assert texts[0] == texts[1]
+
+
+def test_data_parallel_cohorts_share_the_batch(tmp_path):
+    """--dp-size 2 on two CPU ranks: two independent engines, requests spread by the sum of squared prompt lengths,
+    a session's turns stay on one cohort, results equal those of the single-engine server."""
+    texts = []
+    for dp in (1, 2):
+        app = create_app(_args(tmp_path / f"dp{dp}", world_size=dp, dp_size=dp, dist_init_addr=f"127.0.0.1:{29660 + 4 * dp}"))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            f = _upload(c, _lines(8, max_tokens=5))
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"])
+            assert b["status"] == "completed" and b["request_counts"]["completed"] == 8, b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
+            sched = app.state.scheduler
+            if dp == 2:
+                assert sched.dp_assigned[0] > 0 and sched.dp_assigned[1] > 0 and sum(sched.dp_assigned) == 8
+                s = c.post("/v1/sessions", json={}).json()
+                for turn in range(2):
+                    t = c.post("/v1/turns", json={"session_id": s["id"], "prompt": "x" * 40, "max_tokens": 3,
+                                                  "ignore_eos": True}).json()
+                assert t["usage"]["prompt_tokens_details"]["cached_tokens"] >= 32     # same cohort: context reused
+                assert len(sched._session_cohort) == 1
+                assert all(v == 0 for v in sched._dp_load)                            # every completion came back
+    assert texts[0] == texts[1]
