@@ -223,6 +223,23 @@ def tiny_gpt_oss() -> ModelConfig:
                        rope_interleaved=False)
 
 
+def tiny_minimax() -> ModelConfig:
+    """MiniMax-shaped GQA + FP8 MoE at the smallest geometry the GPU kernels tile (head_dim 128, hidden 1024)."""
+    return ModelConfig(name="tiny-minimax", family="minimax", vocab_size=4096, hidden_size=1024, num_layers=2,
+                       first_k_dense=0, moe_intermediate_size=512, n_routed_experts=16, n_shared_experts=0,
+                       num_experts_per_tok=4, num_heads=16, num_kv_heads=4, head_dim=128, rope_interleaved=False,
+                       quant="fp8_block")
+
+
+def tiny_gpt_oss_64() -> ModelConfig:
+    """GPT-OSS-shaped GQA (head_dim 64, sinks, sliding window on alternate layers) at kernel-sized geometry."""
+    return ModelConfig(name="tiny-gpt-oss-64", family="gpt_oss", vocab_size=4096, hidden_size=1024, num_layers=2,
+                       first_k_dense=0, moe_intermediate_size=512, n_routed_experts=16, n_shared_experts=0,
+                       num_experts_per_tok=4, num_heads=16, num_kv_heads=4, head_dim=64, sliding_window=128,
+                       attention_sinks=True, scoring_func="softmax", activation="swiglu_clamped",
+                       rope_interleaved=False)
+
+
 def deepseek_v3_671b() -> ModelConfig:
     return ModelConfig(
         name="deepseek-v3-671b", family="deepseek_v3", vocab_size=129280, hidden_size=7168,
@@ -320,6 +337,8 @@ _PRESETS = {
     "kimi-k3-kda": kimi_k3_kda,
     "kimi-linear-48b": kimi_linear_48b,
     "tiny-gpt-oss": tiny_gpt_oss,
+    "tiny-gpt-oss-64": tiny_gpt_oss_64,
+    "tiny-minimax": tiny_minimax,
     "deepseek-v3-671b": deepseek_v3_671b,
     "deepseek-r1": deepseek_v3_671b,
     "glm-5.3-fp8": glm5_3,

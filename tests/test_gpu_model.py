@@ -88,3 +88,11 @@ def _other_family(name, _ext):
     torch.cuda.synchronize()
     _ext.check_status()
     assert all(len(o) == 6 for o in out) and eng.kv.alloc.num_used == 0
+
+
+@pytest.mark.parametrize("name", ["tiny-minimax", "tiny-gpt-oss-64"])
+def test_gqa_families_at_kernel_sized_geometry(name):
+    """GQA families on geometries the kernels tile (head_dim 128 / 64, hidden 1024): no library fallback is allowed
+    here, so the paged GQA decode kernel, the RoPE kernel and the FP8 expert GEMMs are what runs."""
+    from batchgen_b200.ops import _ext
+    _other_family(name, _ext)
