@@ -519,6 +519,8 @@ class Transformer:
             return "GQA attention runs tensor-parallel through forward() and the collective baseline"
         if cfg.has_kda:
             return "KDA layers run tensor-parallel through forward() and the collective baseline"
+        if cfg.has_dsa:
+            return "DSA indexer layers need the full-width hidden rows: they run through forward() and the collective baseline"
         if cfg.quant != "fp8_block":
             return "the fused kernels move block-scaled FP8 rows; other expert formats use the collective baseline"
         if cfg.moe_latent_size:

@@ -72,11 +72,64 @@ def runtime_preflight(args) -> List[str]:
         out.append(f"kernel library present, {torch.cuda.device_count()} x sm_{major}{minor}")
         if args.world_size > 1 and not torch.distributed.is_nccl_available():
             raise PreflightError("torch was built without NCCL")
+        from ..config import get_model_config
+        out += model_contract(get_model_config(args.model), args.world_size // max(getattr(args, "dp_size", 1), 1), True,
+                              getattr(args, "moe_comm", "nccl"))
     else:
+        from ..config import get_model_config
+        out += model_contract(get_model_config(args.model), args.world_size // max(getattr(args, "dp_size", 1), 1), False)
         if args.world_size > 1 and not torch.distributed.is_gloo_available():
             raise PreflightError("torch was built without gloo")
         out.append("CPU execution (fp32 reference path)")
     return out
+
+
+def model_contract(cfg, world: int, on_gpu: bool, moe_comm: str = "nccl") -> List[str]:
+    """The dependency contract of one model on this engine: which geometries the hand-written kernels tile.  On a GPU
+    a model outside the contract would raise ``KernelError`` at its first step (no silent library fallback); here it
+    is refused before the workers start, with every violated rule in the message.  Returns notes for the log."""
+    notes, bad = [], []
+    if world > 1:
+        if cfg.num_heads % world:
+            bad.append(f"{cfg.num_heads} attention heads do not divide over {world} ranks")
+        if cfg.n_routed_experts and cfg.n_routed_experts % world:
+            bad.append(f"{cfg.n_routed_experts} routed experts do not divide over {world} ranks")
+    if not on_gpu:
+        if bad:
+            raise PreflightError("model contract: " + "; ".join(bad))
+        return ["fp32 reference path: no kernel geometry rules apply"]
+    heads = cfg.num_heads // max(world, 1)
+    if cfg.hidden_size % 128:
+        bad.append(f"hidden_size {cfg.hidden_size} is not a multiple of 128 (1 x 128 FP8 activation groups)")
+    if cfg.quant in ("fp8_block", "mxfp4", "int4"):
+        for name, v in (("moe_intermediate_size", cfg.moe_intermediate_size), ("intermediate_size", cfg.intermediate_size)):
+            if v and v % 128:
+                bad.append(f"{name} {v} is not a multiple of 128")
+    elif cfg.quant not in ("none",):
+        bad.append(f"quant {cfg.quant!r} has no kernel")
+    if cfg.is_mla:
+        if cfg.kv_lora_rank != 512 or cfg.qk_rope_head_dim != 64:
+            bad.append(f"MLA kernels need kv_lora_rank 512 + rope 64 (got {cfg.kv_lora_rank} + {cfg.qk_rope_head_dim})")
+        if cfg.qk_nope_head_dim % 64:
+            bad.append(f"qk_nope_head_dim {cfg.qk_nope_head_dim} is not a multiple of 64 (absorb GEMM)")
+        if heads % 8:
+            bad.append(f"{heads} heads per rank: the MLA kernels tile multiples of 8 (64 for the persistent decode kernel)")
+        notes.append("MLA decode: persistent kernel" if heads % 64 == 0 else "MLA decode: split-KV kernel (heads per rank not a multiple of 64)")
+    else:
+        if cfg.head_dim not in (64, 128):
+            bad.append(f"GQA head_dim {cfg.head_dim}: the paged decode kernel covers 64 and 128")
+        notes.append("GQA prefill runs the reference path (no prefill kernel)")
+    if cfg.has_dsa and (cfg.index_n_heads != 32 or cfg.index_head_dim != 128):
+        bad.append(f"DSA indexer kernels need 32 heads x 128 (got {cfg.index_n_heads} x {cfg.index_head_dim})")
+    if cfg.has_kda and cfg.kda_head_dim not in (64, 128):
+        bad.append(f"KDA head_dim {cfg.kda_head_dim}: the kernel covers 64 and 128")
+    if world > 1 and moe_comm == "fused":
+        from ..models.transformer import Transformer
+        why = Transformer.supports_sequence_parallel(cfg)
+        notes.append("fused NVLink path" if why is None else f"NCCL layout instead of the fused path: {why}")
+    if bad:
+        raise PreflightError("model contract: " + "; ".join(bad))
+    return notes or ["model geometry within the kernels' contract"]
 
 
 def host_memory(args) -> List[str]:

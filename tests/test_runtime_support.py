@@ -376,3 +376,19 @@ def test_step_ring_keeps_the_latest_events():
     assert len(r) == 4 and [e["rows"] for e in r.tail(10)] == [2, 3, 4, 5]
     s = r.summary()
     assert s["decode"]["events"] == 2 and s["decode"]["tokens"] == 80 and abs(s["decode"]["max_ms"] - 6.0) < 1e-6
+
+
+def test_model_contract_names_every_violated_kernel_rule():
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.server.preflight import PreflightError, model_contract
+    notes = model_contract(get_model_config("deepseek-v3-671b"), 8, True, "fused")
+    assert any("split-KV" in n for n in notes) and any("fused NVLink path" in n for n in notes)
+    assert any("persistent" in n for n in model_contract(get_model_config("deepseek-v3-671b"), 2, True))
+    assert any("NCCL layout" in n for n in model_contract(get_model_config("glm-5.3-fp8"), 8, True, "fused"))
+    model_contract(get_model_config("tiny-minimax"), 1, True)
+    with pytest.raises(PreflightError) as e:                       # the CPU-sized test preset has no kernel geometry
+        model_contract(get_model_config("tiny-deepseek-v3"), 1, True)
+    assert "kv_lora_rank 512" in str(e.value) and "heads per rank" in str(e.value)
+    assert model_contract(get_model_config("tiny-deepseek-v3"), 1, False)      # fine on the reference path
+    with pytest.raises(PreflightError, match="do not divide"):
+        model_contract(get_model_config("minimax-m2.5"), 5, False)
