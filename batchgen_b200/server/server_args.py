@@ -60,7 +60,8 @@ class ServerArgs:
     # comm
     moe_comm: str = "fused"                     # fused (in-kernel NVLink exchange) | nccl (collective baseline)
     fused_max_tokens: int = 16384               # largest step (prefill micro-batch) of the fused path; sizes its heap
-    decode_attn_split: str = "heads"            # heads | requests (rows pinned to owner ranks inside the TP group)
+    decode_attn_split: str = "auto"             # heads | requests (rows pinned to owner ranks inside the TP group) | auto:
+                                                # requests on the fused multi-GPU path of an MLA model, heads otherwise
     # recurrent state (models with KDA layers)
     max_state_slots: int = 0
     max_host_state_items: int = 0
@@ -116,7 +117,8 @@ class ServerArgs:
             cuda_graph_num_buckets=self.cuda_graph_num_buckets, enable_prefix_cache=self.enable_prefix_cache,
             adaptive_chunk=self.adaptive_chunk, world_size=self.world_size, attn_tp_size=tp,
             ep_size=self.world_size, moe_comm=self.moe_comm, expert_offload_ratio=self.ep_offloading_ratio,
-            decode_attn_split=self.decode_attn_split, max_state_slots=self.max_state_slots,
+            decode_attn_split=("heads" if self.decode_attn_split == "auto" else self.decode_attn_split),
+            max_state_slots=self.max_state_slots,
             max_host_state_items=self.max_host_state_items, seed=self.seed)
 
 

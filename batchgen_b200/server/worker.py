@@ -85,6 +85,10 @@ def build_engine(args, rank: int, world: int, device: str, phases=None, phase_sl
             eventlog.get_log().info("worker.comm", rank=rank, chosen="nccl", reason=why_not)
         comm = make_comm("fused" if fused else "nccl", device if fused else None)
         layout = ParallelLayout(tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world, sequence_parallel=fused)
+    if getattr(args, "decode_attn_split", "heads") == "auto" and fused and cfg.is_mla and not cfg.has_dsa:
+        # the latent KV of a row is shared by all heads: on the fused path each rank attends over its own rows with
+        # every head (two chunked exchanges per layer) instead of streaming every row's KV for its own heads
+        ecfg.decode_attn_split = "requests"
     model = build_model(cfg, device=device, dtype=dtype, seed=args.seed, layout=layout, comm=comm, loader=loader,
                         max_positions=max(8192, args.max_model_len if args.max_model_len > 0 else 8192))
     if world > 1 and ecfg.decode_attn_split == "requests" and cfg.is_mla and not cfg.has_dsa:
