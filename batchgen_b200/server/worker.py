@@ -48,6 +48,24 @@ def setup_nccl_env() -> None:
 _STORES: list = []
 
 
+def _memory_profile(device: str) -> Dict[str, Any]:
+    """Device and host memory of this worker for the heartbeat: allocator counters on a GPU, resident set size."""
+    out: Dict[str, Any] = {}
+    try:
+        import resource
+        out["host_rss_mb"] = resource.getrusage(resource.RUSAGE_SELF).ru_maxrss // 1024
+    except (ImportError, OSError):
+        pass
+    if device.startswith("cuda"):
+        import torch
+        free, total = torch.cuda.mem_get_info(torch.device(device))
+        out.update(device_allocated_mb=torch.cuda.memory_allocated(device) >> 20,
+                   device_reserved_mb=torch.cuda.memory_reserved(device) >> 20,
+                   device_peak_mb=torch.cuda.max_memory_allocated(device) >> 20,
+                   device_free_mb=free >> 20, device_total_mb=total >> 20)
+    return out
+
+
 def build_engine(args, rank: int, world: int, device: str, phases=None, phase_slot: Optional[int] = None):
     import torch
 
@@ -296,7 +314,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
             if rank == 0 and time.monotonic() - last_beat > 5.0:
                 last_beat = time.monotonic()
                 up({"type": "heartbeat", "ts": time.time(), "live": len(eng.seqs), "free_pages": eng.kv.alloc.num_free,
-                    "stats": eng.stats.summary(), "steps": eng.step_ring.summary(), "query_book": {"active": book.active_count,
+                    "stats": eng.stats.summary(), "steps": eng.step_ring.summary(), "memory": _memory_profile(device),
+                    "query_book": {"active": book.active_count,
                                                                   "free_pages": book.free_page_count}})
         log.info("worker.shutdown", rank=rank)
     except Exception as ex:  # noqa: BLE001
