@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Tuple
 @dataclass
 class ModelConfig:
     name: str = "tiny-deepseek-v3"
-    family: str = "deepseek_v3"  # deepseek_v3 | glm5 | kimi_k3 | kimi_k25 | gpt_oss | minimax
+    family: str = "deepseek_v3"  # deepseek_v3 | deepseek_v2 | glm5 | kimi_k3 | kimi_k25 | gpt_oss | minimax | mixtral | qwen2_moe
     vocab_size: int = 1024
     hidden_size: int = 256
     num_layers: int = 2
@@ -36,7 +36,8 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     norm_topk_prob: bool = True
-    scoring_func: str = "sigmoid"          # sigmoid | softmax
+    scoring_func: str = "sigmoid"          # sigmoid | softmax (over the selected) | softmax_all | sqrtsoftplus
+    shared_expert_gate: bool = False       # Qwen2-MoE: the shared expert's output is scaled by sigmoid(x . w_gate)
     moe_latent_size: int = 0               # Kimi-K3 LatentMoE: experts run in this width
     activation: str = "silu"               # silu | swiglu_clamped (GPT-OSS)
     # ---- attention: MLA
@@ -51,6 +52,7 @@ class ModelConfig:
     head_dim: int = 0
     sliding_window: int = 0
     attention_sinks: bool = False
+    attention_bias: bool = False           # GQA: q/k/v projections carry a bias (Qwen2)
     # ---- rope
     rope_theta: float = 10000.0
     rope_interleaved: bool = True
@@ -240,6 +242,76 @@ def tiny_gpt_oss_64() -> ModelConfig:
                        rope_interleaved=False)
 
 
+def tiny_deepseek_v2() -> ModelConfig:
+    """DeepSeek-V2 routing at toy size: softmax over all experts, groups ranked by their best expert, weights not
+    renormalised, two shared experts."""
+    return ModelConfig(name="tiny-deepseek-v2", family="deepseek_v2", num_layers=2, first_k_dense=1,
+                       n_routed_experts=16, n_shared_experts=2, num_experts_per_tok=4, n_group=4, topk_group=2,
+                       scoring_func="softmax_all", norm_topk_prob=False, routed_scaling_factor=4.0,
+                       moe_intermediate_size=64)
+
+
+def tiny_mixtral() -> ModelConfig:
+    return ModelConfig(name="tiny-mixtral", family="mixtral", num_layers=2, first_k_dense=0, num_heads=8,
+                       num_kv_heads=2, head_dim=32, scoring_func="softmax", n_shared_experts=0, n_routed_experts=8,
+                       num_experts_per_tok=2, rope_interleaved=False, rope_theta=1e6)
+
+
+def tiny_qwen2_moe() -> ModelConfig:
+    """Qwen2-MoE at toy size: biased q/k/v, softmax over all experts without renormalisation, gated shared expert."""
+    return ModelConfig(name="tiny-qwen2-moe", family="qwen2_moe", num_layers=2, first_k_dense=0, num_heads=8,
+                       num_kv_heads=2, head_dim=32, attention_bias=True, scoring_func="softmax_all",
+                       norm_topk_prob=False, n_shared_experts=2, shared_expert_gate=True, n_routed_experts=8,
+                       num_experts_per_tok=2, moe_intermediate_size=64, rope_interleaved=False, rope_theta=1e6)
+
+
+def deepseek_v2_236b() -> ModelConfig:
+    """DeepSeek-V2 (236B): the MLA + MoE generation before V3 (reference: batchgen/models/deepseek/deepseekv2/config_v2.json)."""
+    return ModelConfig(
+        name="deepseek-v2", family="deepseek_v2", vocab_size=102400, hidden_size=5120, num_layers=60,
+        first_k_dense=1, intermediate_size=12288, moe_intermediate_size=1536, n_routed_experts=160,
+        n_shared_experts=2, num_experts_per_tok=6, n_group=8, topk_group=3, routed_scaling_factor=16.0,
+        norm_topk_prob=False, scoring_func="softmax_all", num_heads=128, q_lora_rank=1536, kv_lora_rank=512,
+        qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, rope_theta=10000.0, rope_scaling_factor=40.0,
+        rope_original_max_pos=4096, rope_mscale=0.707, rope_mscale_all_dim=0.707, eos_token_id=100001,
+        bos_token_id=100000)
+
+
+def mixtral_8x7b() -> ModelConfig:
+    """Mixtral-8x7B (reference: batchgen/models/mixtral/config.py)."""
+    return ModelConfig(
+        name="mixtral-8x7b", family="mixtral", vocab_size=32000, hidden_size=4096, num_layers=32, first_k_dense=0,
+        moe_intermediate_size=14336, n_routed_experts=8, n_shared_experts=0, num_experts_per_tok=2,
+        scoring_func="softmax", num_heads=32, num_kv_heads=8, head_dim=128, rope_theta=1e6, rope_interleaved=False,
+        max_position_embeddings=32768, rms_eps=1e-5, eos_token_id=2, bos_token_id=1)
+
+
+def mixtral_8x22b() -> ModelConfig:
+    import dataclasses
+    return dataclasses.replace(mixtral_8x7b(), name="mixtral-8x22b", hidden_size=6144, num_layers=56,
+                               moe_intermediate_size=16384, num_heads=48, max_position_embeddings=65536)
+
+
+def qwen2_57b_a14b() -> ModelConfig:
+    """Qwen2-57B-A14B, the Qwen2-MoE checkpoint family the reference's Qwen initializer serves
+    (batchgen/models/Qwen_Initializer.py)."""
+    return ModelConfig(
+        name="qwen2-57b-a14b", family="qwen2_moe", vocab_size=151936, hidden_size=3584, num_layers=28,
+        first_k_dense=0, moe_intermediate_size=2560, n_routed_experts=64, n_shared_experts=8,
+        shared_expert_gate=True, num_experts_per_tok=8, scoring_func="softmax_all", norm_topk_prob=False,
+        num_heads=28, num_kv_heads=4, head_dim=128, attention_bias=True, rope_theta=1e6, rope_interleaved=False,
+        max_position_embeddings=65536, eos_token_id=151643, bos_token_id=151643)
+
+
+def qwen15_moe_a27b() -> ModelConfig:
+    return ModelConfig(
+        name="qwen1.5-moe-a2.7b", family="qwen2_moe", vocab_size=151936, hidden_size=2048, num_layers=24,
+        first_k_dense=0, moe_intermediate_size=1408, n_routed_experts=60, n_shared_experts=4,
+        shared_expert_gate=True, num_experts_per_tok=4, scoring_func="softmax_all", norm_topk_prob=False,
+        num_heads=16, num_kv_heads=16, head_dim=128, attention_bias=True, rope_theta=1e6, rope_interleaved=False,
+        max_position_embeddings=8192, eos_token_id=151643, bos_token_id=151643)
+
+
 def deepseek_v3_671b() -> ModelConfig:
     return ModelConfig(
         name="deepseek-v3-671b", family="deepseek_v3", vocab_size=129280, hidden_size=7168,
@@ -339,6 +411,14 @@ _PRESETS = {
     "tiny-gpt-oss": tiny_gpt_oss,
     "tiny-gpt-oss-64": tiny_gpt_oss_64,
     "tiny-minimax": tiny_minimax,
+    "tiny-deepseek-v2": tiny_deepseek_v2,
+    "tiny-mixtral": tiny_mixtral,
+    "tiny-qwen2-moe": tiny_qwen2_moe,
+    "deepseek-v2": deepseek_v2_236b,
+    "mixtral-8x7b": mixtral_8x7b,
+    "mixtral-8x22b": mixtral_8x22b,
+    "qwen2-57b-a14b": qwen2_57b_a14b,
+    "qwen1.5-moe-a2.7b": qwen15_moe_a27b,
     "deepseek-v3-671b": deepseek_v3_671b,
     "deepseek-r1": deepseek_v3_671b,
     "glm-5.3-fp8": glm5_3,
@@ -352,6 +432,11 @@ _PRESETS = {
 # batchgen/config/model_registry.py:63-117).
 _PATTERNS = [
     (r"deepseek[-_/]?(ai/)?.*(v3|r1)", "deepseek-v3-671b"),
+    (r"deepseek[-_/]?(ai/)?.*v2", "deepseek-v2"),
+    (r"mixtral.*8x22b", "mixtral-8x22b"),
+    (r"mixtral", "mixtral-8x7b"),
+    (r"qwen1\.5[-_]?moe", "qwen1.5-moe-a2.7b"),
+    (r"qwen2?[-_].*(moe|a14b)", "qwen2-57b-a14b"),
     (r"glm[-_]?5", "glm-5.3-fp8"),
     (r"kimi[-_]?linear", "kimi-linear-48b"),
     (r"kimi[-_]?k3\.1", "kimi-k3.1"),

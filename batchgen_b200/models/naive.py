@@ -21,7 +21,6 @@ from .weights import WeightSource
 
 class NaiveModel:
     def __init__(self, cfg: ModelConfig, src: WeightSource):
-        assert cfg.is_mla, "the naive oracle covers the MLA families"
         self.cfg, self.src = cfg, src
 
     def _g(self, name, shape, kind="normal"):
@@ -33,7 +32,7 @@ class NaiveModel:
 
     def _rope(self, x, positions):
         cfg = self.cfg
-        inv = ref.rope_inv_freq(cfg.qk_rope_head_dim, cfg.rope_theta, cfg.rope_scaling_factor,
+        inv = ref.rope_inv_freq(cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim, cfg.rope_theta, cfg.rope_scaling_factor,
                                 cfg.rope_original_max_pos, cfg.rope_beta_fast, cfg.rope_beta_slow)
         cos, sin = ref.rope_cos_sin(positions, inv)
         return ref.apply_rope(x, cos, sin, cfg.rope_interleaved)
@@ -42,7 +41,38 @@ class NaiveModel:
         g = self._g(f"{prefix}.gate_proj.weight", (inter, hid))
         u = self._g(f"{prefix}.up_proj.weight", (inter, hid))
         d = self._g(f"{prefix}.down_proj.weight", (hid, inter))
-        return (F.silu(x @ g.t()) * (x @ u.t())) @ d.t()
+        gate, up = x @ g.t(), x @ u.t()
+        if self.cfg.activation == "swiglu_clamped":       # GPT-OSS: clamp, (up + 1) * gate * sigmoid(1.702 gate)
+            gate, up = gate.clamp(max=7.0), up.clamp(-7.0, 7.0)
+            return ((up + 1.0) * gate * torch.sigmoid(1.702 * gate)) @ d.t()
+        return (F.silu(gate) * up) @ d.t()
+
+    def _gqa(self, x, l, p, pos):
+        """Grouped-query attention over the whole sequence: every query head reads the key/value head of its group."""
+        cfg = self.cfg
+        L, H, D, Hq, Hkv = x.shape[0], cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+        a = f"{p}.self_attn"
+
+        def proj(name, heads):
+            y = x @ self._g(f"{a}.{name}_proj.weight", (heads * D, H)).t()
+            if cfg.attention_bias:
+                y = y + self._g(f"{a}.{name}_proj.bias", (heads * D,), "bias")
+            return y.view(L, heads, D)
+
+        q, k, v = self._rope(proj("q", Hq), pos), self._rope(proj("k", Hkv), pos), proj("v", Hkv)
+        out = torch.zeros(L, Hq, D)
+        window = cfg.sliding_window if (cfg.sliding_window and l % 2 == 0) else 0
+        sinks = self._g(f"{a}.sinks", (Hq,), "bias") if cfg.attention_sinks else None
+        for h in range(Hq):
+            kh, vh = k[:, h // (Hq // Hkv)], v[:, h // (Hq // Hkv)]
+            for t in range(L):
+                first = max(0, t + 1 - window) if window else 0
+                sc = (kh[first: t + 1] @ q[t, h]) * cfg.softmax_scale
+                if sinks is not None:
+                    sc = torch.cat([sc, sinks[h: h + 1]])
+                pr = torch.softmax(sc, 0)[: t + 1 - first]
+                out[t, h] = pr @ vh[first: t + 1]
+        return out.reshape(L, Hq * D) @ self._g(f"{a}.o_proj.weight", (H, Hq * D)).t()
 
     @torch.no_grad()
     def logits(self, ids: List[int]) -> torch.Tensor:
@@ -54,8 +84,8 @@ class NaiveModel:
         for l in range(cfg.num_layers):
             p = f"model.layers.{l}"
             x = self._rms(h, f"{p}.input_layernorm.weight", H)
-            if cfg.layer_is_kda(l):
-                h = h + self._kda(x, p)
+            if cfg.layer_is_kda(l) or not cfg.is_mla:
+                h = h + (self._kda(x, p) if cfg.layer_is_kda(l) else self._gqa(x, l, p, pos))
                 x = self._rms(h, f"{p}.post_attention_layernorm.weight", H)
                 h = h + (self._moe(x, p) if cfg.is_moe_layer(l) else self._mlp(x, f"{p}.mlp", cfg.intermediate_size, H))
                 continue
@@ -128,7 +158,8 @@ class NaiveModel:
         cfg = self.cfg
         E, I, eh, H = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden, cfg.hidden_size
         logits = x @ self._g(f"{p}.mlp.gate.weight", (E, H)).t()
-        bias = self._g(f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias") if cfg.scoring_func == "sigmoid" else None
+        bias = (self._g(f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias")
+                if cfg.scoring_func in ("sigmoid", "sqrtsoftplus") else None)
         idx, w = ref.router_topk(logits, bias, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group,
                                  cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.scoring_func)
         xin = x
@@ -143,7 +174,10 @@ class NaiveModel:
             out = self._rms(out, f"{p}.mlp.latent_norm.weight", eh)
             out = out @ self._g(f"{p}.mlp.latent_up_proj.weight", (H, eh)).t()
         if cfg.n_shared_experts:
-            out = out + self._mlp(x, f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+            shared = self._mlp(x, f"{p}.mlp.shared_experts", I * cfg.n_shared_experts, H)
+            if cfg.shared_expert_gate:
+                shared = shared * torch.sigmoid(x @ self._g(f"{p}.mlp.shared_expert_gate.weight", (1, H)).t())
+            out = out + shared
         return out
 
     def _dsa_mask(self, l, p, x, q_a_normed, pos):

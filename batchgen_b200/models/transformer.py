@@ -380,6 +380,8 @@ class Transformer:
         D = cfg.head_dim
         Hq = lw.wo.w.shape[1] // D
         qkv = linear(x, lw.wqkv, xq, xs)
+        if lw.bqkv is not None:
+            qkv = qkv + lw.bqkv
         Hkv = (qkv.shape[1] // D - Hq) // 2
         q = qkv[:, : Hq * D].reshape(T, Hq, D)
         k = qkv[:, Hq * D: (Hq + Hkv) * D].reshape(T, Hkv, D)
@@ -431,7 +433,7 @@ class Transformer:
         local = self.comm is None or self.layout.ep_size <= 1
         if (lw.w13 is not None and local and self.streamer is None and not cfg.moe_latent_size and x.is_cuda
                 and self.overlap_shared_expert and meta.mode == "decode" and not tm.enabled
-                and lw.experts.quant == "fp8_block"):
+                and lw.experts.quant == "fp8_block" and lw.shared_gate_w is None):
             # decode on one GPU: the shared expert runs on a side stream while the routed path counts, permutes and
             # gathers its rows (small kernels that leave the GPU mostly idle); the combine adds its output, so no
             # separate add kernel either.  The router's GEMM (a split-K launch) is already queued: the side stream's
@@ -450,6 +452,8 @@ class Transformer:
                 shared = self._mlp(x, xq, xs, lw.w13, lw.w2)
             if self.comm is not None and self.layout.tp_size > 1:
                 shared = self.comm.tp_reduce(shared)
+            if lw.shared_gate_w is not None:
+                shared = shared * torch.sigmoid(x.float() @ lw.shared_gate_w.float().t()).to(shared.dtype)
         h = x
         if cfg.moe_latent_size:
             h = linear(x, lw.latent_down)
@@ -525,6 +529,8 @@ class Transformer:
             return "the fused kernels move block-scaled FP8 rows; other expert formats use the collective baseline"
         if cfg.moe_latent_size:
             return "latent-MoE projections are not part of the fused path"
+        if cfg.shared_expert_gate:
+            return "the gated shared expert is not part of the fused path"
         if cfg.hidden_size % 128 or cfg.expert_hidden % 128:
             return "hidden sizes must be multiples of the 128-wide quantisation block"
         return None

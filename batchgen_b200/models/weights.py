@@ -142,6 +142,7 @@ class LayerWeights:
     wo: Linear = None                # [H, Hh * v]
     # GQA
     wqkv: Linear = None              # [(Hq + 2 Hkv) * D, H]
+    bqkv: torch.Tensor = None        # [(Hq + 2 Hkv) * D] projection bias (Qwen2)
     sinks: torch.Tensor = None
     # DSA indexer
     idx_wq: Linear = None            # [Hi * Di, q_lora]
@@ -155,6 +156,7 @@ class LayerWeights:
     # MoE
     router_w: torch.Tensor = None    # [E, H] fp32
     router_bias: torch.Tensor = None
+    shared_gate_w: torch.Tensor = None   # [1, H]: sigmoid gate on the shared expert's output (Qwen2-MoE)
     experts: ExpertWeights = None
     latent_down: Linear = None       # Kimi-K3 LatentMoE  [latent, H]
     latent_up: Linear = None         # [H, latent]
@@ -256,6 +258,11 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
             wk = src.get(f"{p}.self_attn.k_proj.weight", (Hkv * D, H)).view(Hkv, D, H)[k0:k1].reshape(-1, H)
             wv = src.get(f"{p}.self_attn.v_proj.weight", (Hkv * D, H)).view(Hkv, D, H)[k0:k1].reshape(-1, H)
             lw.wqkv = make_linear(torch.cat([wq, wk, wv], 0), quant, dtype)
+            if cfg.attention_bias:
+                bq = src.get(f"{p}.self_attn.q_proj.bias", (Hq * D,), "bias").view(Hq, D)[h0:h1].reshape(-1)
+                bk = src.get(f"{p}.self_attn.k_proj.bias", (Hkv * D,), "bias").view(Hkv, D)[k0:k1].reshape(-1)
+                bv = src.get(f"{p}.self_attn.v_proj.bias", (Hkv * D,), "bias").view(Hkv, D)[k0:k1].reshape(-1)
+                lw.bqkv = torch.cat([bq, bk, bv], 0).to(dtype).contiguous()
             wo = src.get(f"{p}.self_attn.o_proj.weight", (H, Hq * D)).view(H, Hq, D)[:, h0:h1].reshape(H, -1)
             lw.wo = make_linear(wo, quant, dtype)
             if cfg.attention_sinks:
@@ -274,8 +281,10 @@ def build_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource, d
         if cfg.is_moe_layer(l):
             E, I, eh = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden
             lw.router_w = src.get(f"{p}.mlp.gate.weight", (E, H)).float()
-            if cfg.scoring_func == "sigmoid":
+            if cfg.scoring_func in ("sigmoid", "sqrtsoftplus"):
                 lw.router_bias = src.get(f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias").float()
+            if cfg.shared_expert_gate:
+                lw.shared_gate_w = src.get(f"{p}.mlp.shared_expert_gate.weight", (1, H)).to(dtype)
             if cfg.moe_latent_size:
                 lw.latent_down = make_linear(src.get(f"{p}.mlp.latent_down_proj.weight", (eh, H)), "none", dtype)
                 lw.latent_up = make_linear(src.get(f"{p}.mlp.latent_up_proj.weight", (H, eh)), "none", dtype)
@@ -368,6 +377,9 @@ def checkpoint_tensor_specs(cfg: ModelConfig):
             D, Hq, Hkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
             out += [(f"{a}.q_proj.weight", (Hq * D, H), "normal", l), (f"{a}.k_proj.weight", (Hkv * D, H), "normal", l),
                     (f"{a}.v_proj.weight", (Hkv * D, H), "normal", l), (f"{a}.o_proj.weight", (H, Hq * D), "normal", l)]
+            if cfg.attention_bias:
+                out += [(f"{a}.q_proj.bias", (Hq * D,), "bias", l), (f"{a}.k_proj.bias", (Hkv * D,), "bias", l),
+                        (f"{a}.v_proj.bias", (Hkv * D,), "bias", l)]
             if cfg.attention_sinks:
                 out.append((f"{a}.sinks", (Hq,), "bias", l))
 
@@ -379,8 +391,10 @@ def checkpoint_tensor_specs(cfg: ModelConfig):
         if cfg.is_moe_layer(l):
             E, I, eh = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.expert_hidden
             out.append((f"{p}.mlp.gate.weight", (E, H), "normal", l))
-            if cfg.scoring_func == "sigmoid":
+            if cfg.scoring_func in ("sigmoid", "sqrtsoftplus"):
                 out.append((f"{p}.mlp.gate.e_score_correction_bias", (E,), "bias", l))
+            if cfg.shared_expert_gate:
+                out.append((f"{p}.mlp.shared_expert_gate.weight", (1, H), "normal", l))
             if cfg.moe_latent_size:
                 out += [(f"{p}.mlp.latent_down_proj.weight", (eh, H), "normal", l),
                         (f"{p}.mlp.latent_up_proj.weight", (H, eh), "normal", l),

@@ -40,13 +40,28 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
     return;
   }
   const float* lrow = logits + (size_t)t * E;
+  // scoring modes: 0 sigmoid, 1 softmax over the selected logits, 2 softmax over every expert, 3 sqrt(softplus)
+  float rmax = -INFINITY, rinv = 0.f;
+  if (softmax_mode == 2) {
+    for (int e = lane; e < E; e += 32) rmax = fmaxf(rmax, lrow[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    float rsum = 0.f;
+    for (int e = lane; e < E; e += 32) rsum += expf(lrow[e] - rmax);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+    rinv = 1.0f / rsum;
+  }
   for (int e = lane; e < E; e += 32) {
     const float l = lrow[e];
-    if (softmax_mode) {
+    if (softmax_mode == 1) {
       score[e] = l;
       choice[e] = l;
     } else {
-      const float s = 1.0f / (1.0f + expf(-l));
+      float s;
+      if (softmax_mode == 0) s = 1.0f / (1.0f + expf(-l));
+      else if (softmax_mode == 2) s = expf(l - rmax) * rinv;
+      else s = sqrtf(l > 20.f ? l : log1pf(expf(l)));
       score[e] = s;
       choice[e] = bias != nullptr ? s + bias[e] : s;
     }
@@ -60,7 +75,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
         const float v = choice[lane * gs + i];
         if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
       }
-      group_s[warp][lane] = m1 + m2;
+      group_s[warp][lane] = softmax_mode == 2 ? m1 : m1 + m2;   // softmax_all ranks a group by its best expert
     }
     __syncwarp();
     // keep the topk_group best groups (ties -> lower index); lane g decides for group g
@@ -97,7 +112,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
     if (bi == 0x7fffffff) bi = 0;
     if (k == 0) sel_max = best;
     float wv = score[bi];
-    if (softmax_mode) wv = expf(wv - sel_max);
+    if (softmax_mode == 1) wv = expf(wv - sel_max);
     wsum += wv;
     if (lane == k) { my_w = wv; my_i = bi; }
     __syncwarp();
@@ -106,7 +121,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
   }
   if (lane < K) {
     float wv = my_w;
-    if (softmax_mode) wv = wv / wsum;
+    if (softmax_mode == 1) wv = wv / wsum;
     else if (norm && K > 1) wv = wv / (wsum + 1e-20f);
     idx_out[(size_t)t * K + lane] = my_i;
     w_out[(size_t)t * K + lane] = wv * scale;

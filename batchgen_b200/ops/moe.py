@@ -80,6 +80,9 @@ def router_logits(hidden: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return hidden.float() @ weight.float().t()
 
 
+_SCORING_MODES = {"sigmoid": 0, "softmax": 1, "softmax_all": 2, "sqrtsoftplus": 3}
+
+
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int = 1,
                 topk_group: int = 1, norm_topk_prob: bool = True, scale: float = 1.0, scoring: str = "sigmoid",
                 num_valid: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -99,7 +102,7 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, 
     rc = _ext.lib().bg_router_topk(_ext.ptr(logits), _ext.ptr(bias), _ext.ptr(idx), _ext.ptr(w), ctypes.c_int(T),
                                    ctypes.c_int(E), ctypes.c_int(top_k), ctypes.c_int(n_group),
                                    ctypes.c_int(topk_group), ctypes.c_int(int(norm_topk_prob)), ctypes.c_float(scale),
-                                   ctypes.c_int(1 if scoring == "softmax" else 0), _ext.ptr(num_valid), _ext.stream())
+                                   ctypes.c_int(_SCORING_MODES[scoring]), _ext.ptr(num_valid), _ext.stream())
     _ext.check(rc, "bg_router_topk")
     return idx, w
 

@@ -196,20 +196,32 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, 
                 scoring: str = "sigmoid") -> Tuple[torch.Tensor, torch.Tensor]:
     """logits: [T, E] fp32 -> (idx [T, k] int32 sorted by descending choice score, w [T, k] fp32).
 
-    sigmoid scoring: choice = sigmoid(logit) + bias; group-limited selection keeps the
-    ``topk_group`` groups with the largest (sum of top-2 choice scores); weights come from the
+    sigmoid scoring (DeepSeek-V3, GLM, Kimi): choice = sigmoid(logit) + bias; group-limited selection keeps
+    the ``topk_group`` groups with the largest (sum of top-2 choice scores); weights come from the
     *unbiased* sigmoid, normalised and multiplied by ``scale``.
-    softmax scoring (GPT-OSS): top-k on logits, softmax over the selected logits."""
+    softmax scoring (GPT-OSS, Mixtral): top-k on logits, softmax over the selected logits.
+    softmax_all scoring (DeepSeek-V2, Qwen2-MoE): softmax over every expert first; group-limited selection
+    ranks groups by their best expert; the weights are the selected probabilities, renormalised only when
+    ``norm_topk_prob`` is set.
+    sqrtsoftplus scoring (DeepSeek-V4): score = sqrt(softplus(logit)), chosen with the bias added, weights
+    from the unbiased score."""
     T, E = logits.shape
     lf = logits.float()
     if scoring == "softmax":
         val, idx = torch.topk(lf, top_k, dim=-1)
         return idx.to(torch.int32), torch.softmax(val, dim=-1) * scale
-    scores = torch.sigmoid(lf)
+    if scoring == "sigmoid":
+        scores = torch.sigmoid(lf)
+    elif scoring == "softmax_all":
+        scores = torch.softmax(lf, dim=-1)
+    elif scoring == "sqrtsoftplus":
+        scores = torch.sqrt(torch.nn.functional.softplus(lf))
+    else:
+        raise ValueError(f"unknown router scoring {scoring!r}")
     choice = scores if bias is None else scores + bias.float().unsqueeze(0)
     if n_group > 1:
         g = choice.view(T, n_group, E // n_group)
-        gscore = g.topk(2, dim=-1)[0].sum(-1)
+        gscore = g.max(-1)[0] if scoring == "softmax_all" else g.topk(2, dim=-1)[0].sum(-1)
         gidx = gscore.topk(topk_group, dim=-1)[1]
         gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
         emask = gmask.unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E)

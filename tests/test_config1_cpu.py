@@ -138,3 +138,36 @@ def test_other_families_run_and_match_naive():
         outs = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
         naive = NaiveModel(cfg, WeightSource(seed=0))
         assert naive.generate(prompts[0], 6) == outs[0], name
+
+
+def test_legacy_and_gqa_families_match_naive():
+    """GQA attention (sinks, sliding window, projection bias), Mixtral / DeepSeek-V2 / Qwen2-MoE routing and the gated
+    shared expert: the engine's tokens equal the textbook model's."""
+    for name in ("tiny-gpt-oss", "tiny-mixtral", "tiny-qwen2-moe", "tiny-deepseek-v2"):
+        cfg = get_model_config(name)
+        eng = _engine(cfg)
+        prompts = _prompts(cfg, 2, 24, seed=13)
+        outs = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+        naive = NaiveModel(cfg, WeightSource(seed=0))
+        assert naive.generate(prompts[1], 6) == outs[1], name
+
+
+def test_router_scoring_modes():
+    from batchgen_b200.ops import ref
+    g = torch.Generator().manual_seed(2)
+    logits = torch.randn(5, 16, generator=g)
+    idx, w = ref.router_topk(logits, None, 4, n_group=4, topk_group=2, norm_topk_prob=False, scale=2.0,
+                             scoring="softmax_all")
+    p = torch.softmax(logits, -1)
+    for t in range(5):
+        best = p[t].view(4, 4).max(-1)[0].topk(2)[1].tolist()
+        allowed = [e for e in range(16) if e // 4 in best]
+        want = sorted(allowed, key=lambda e: -float(p[t, e]))[:4]
+        assert idx[t].tolist() == want
+        assert torch.allclose(w[t], 2.0 * p[t, idx[t].long()])
+    bias = torch.randn(16, generator=g) * 0.1
+    idx, w = ref.router_topk(logits, bias, 3, scale=1.5, scoring="sqrtsoftplus")
+    sc = torch.sqrt(torch.log1p(torch.exp(logits)))
+    assert idx.tolist() == (sc + bias).topk(3)[1].tolist()
+    sel = sc.gather(1, idx.long())
+    assert torch.allclose(w, 1.5 * sel / sel.sum(-1, keepdim=True), atol=1e-6)

@@ -251,6 +251,21 @@ def test_router_softmax_topk():
     assert torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("scoring,E,K,ng,tg,norm", [("softmax_all", 160, 6, 8, 3, False), ("softmax_all", 64, 8, 1, 1, False),
+                                                     ("sqrtsoftplus", 256, 6, 1, 1, True)])
+def test_router_softmax_all_and_sqrtsoftplus(scoring, E, K, ng, tg, norm):
+    T = 200
+    logits = torch.randn(T, E, device=DEV) * 2
+    bias = torch.randn(E, device=DEV) * 0.1 if scoring == "sqrtsoftplus" else None
+    idx, w = moe.router_topk(logits, bias, K, ng, tg, norm, 1.5, scoring)
+    ridx, rw = ref.router_topk(logits, bias, K, ng, tg, norm, 1.5, scoring)
+    a, b = torch.sort(idx, -1)[0], torch.sort(ridx, -1)[0]
+    assert (a != b).any(-1).float().mean().item() < 0.01       # fp ties only
+    same = (a == b).all(-1)
+    so, sr = torch.argsort(idx, -1), torch.argsort(ridx, -1)
+    assert torch.allclose(w.gather(1, so)[same], rw.gather(1, sr)[same], rtol=1e-4, atol=1e-7)
+
+
 def test_moe_permute_gather_combine_roundtrip():
     T, K, E, H = 333, 8, 64, 1024
     lo, hi = 16, 48
