@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Tuple
 @dataclass
 class ModelConfig:
     name: str = "tiny-deepseek-v3"
-    family: str = "deepseek_v3"  # deepseek_v3 | deepseek_v2 | glm5 | kimi_k3 | kimi_k25 | gpt_oss | minimax | mixtral | qwen2_moe
+    family: str = "deepseek_v3"  # deepseek_v3 | deepseek_v2 | deepseek_v4 | glm5 | kimi_k3 | kimi_k25 | gpt_oss | minimax | mixtral | qwen2_moe
     vocab_size: int = 1024
     hidden_size: int = 256
     num_layers: int = 2
@@ -75,6 +75,18 @@ class ModelConfig:
     kda_num_heads: int = 0
     kda_head_dim: int = 128
     kda_gate_rank: int = 0                 # width of the low-rank decay-gate projection (0 = head dim)
+    # ---- DeepSeek-V4: one latent KV head shared by all query heads (K = V), a sliding window of raw KV plus one
+    # pooled entry per ``compress_ratios[layer]`` tokens (0 = window only; 4 = overlapped windows + top-k indexer),
+    # grouped low-rank output projection, hyper-connection residual streams, hash-routed first layers
+    compress_ratios: Tuple[int, ...] = ()
+    compress_rope_theta: float = 0.0
+    o_groups: int = 0
+    o_lora_rank: int = 0
+    hc_mult: int = 0
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    num_hash_layers: int = 0
+    swiglu_limit: float = 0.0
     # ---- quantisation of linear / expert weights
     quant: str = "none"                    # none | fp8_block | mxfp4 | int4
     quant_block: int = 128
@@ -89,8 +101,27 @@ class ModelConfig:
         return self.qk_nope_head_dim + self.qk_rope_head_dim
 
     @property
+    def is_v4(self) -> bool:
+        return len(self.compress_ratios) > 0
+
+    def v4_state_floats_per_seq(self) -> int:
+        """fp32 words of per-sequence state of a DeepSeek-V4 model: per layer the window ring, the compressor's
+        pending window(s) of projections and gate scores, and the same for the indexer's compressor."""
+        n, D, Di, win = 0, self.head_dim, self.index_head_dim, self.sliding_window
+        for r in self.compress_ratios:
+            n += win * D
+            if r:
+                c = 2 if r == 4 else 1
+                n += 2 * (c * r) * (c * D)
+                if r == 4:
+                    n += 2 * (2 * r) * (2 * Di)
+        return n
+
+    @property
     def kv_cache_dim(self) -> int:
         """Width of one cached latent row (normalised c_kv followed by roped k_pe)."""
+        if self.is_v4:
+            return self.head_dim
         if self.num_kv_heads > 0:
             return 2 * self.num_kv_heads * self.head_dim
         return self.kv_lora_rank + self.qk_rope_head_dim
@@ -101,7 +132,7 @@ class ModelConfig:
 
     @property
     def has_dsa(self) -> bool:
-        return self.index_topk > 0
+        return self.index_topk > 0 and not self.is_v4
 
     @property
     def expert_hidden(self) -> int:
@@ -141,6 +172,15 @@ class ModelConfig:
         return (not self.indexer_full_layers) or layer in self.indexer_full_layers
 
     def kv_bytes_per_token(self, kv_dtype_bytes: int = 2) -> int:
+        if self.is_v4:
+            # paged part only (pooled entries and their index keys); the window and compressor state is per sequence
+            b = 0.0
+            for r in self.compress_ratios:
+                if r:
+                    b += self.head_dim * kv_dtype_bytes / r
+                    if r == 4:
+                        b += self.index_head_dim * kv_dtype_bytes / r
+            return int(math.ceil(b))
         b = (self.num_layers - len(self.kda_layers)) * self.kv_cache_dim * kv_dtype_bytes
         if self.has_dsa:
             n_idx = len(self.indexer_full_layers) or self.num_layers
@@ -150,6 +190,19 @@ class ModelConfig:
     def param_count(self) -> int:
         h = self.hidden_size
         n = 2 * self.vocab_size * h
+        if self.is_v4:
+            D, Di = self.head_dim, self.index_head_dim
+            for l, r in enumerate(self.compress_ratios):
+                n += h * self.q_lora_rank + self.q_lora_rank * self.num_heads * D + h * D
+                n += self.num_heads * D * self.o_lora_rank + self.o_groups * self.o_lora_rank * h
+                if r:
+                    c = 2 if r == 4 else 1
+                    n += 2 * h * c * D
+                    if r == 4:
+                        n += self.q_lora_rank * self.index_n_heads * Di + h * self.index_n_heads + 4 * h * Di
+                n += 3 * h * self.moe_intermediate_size * (self.n_routed_experts + self.n_shared_experts)
+                n += h * self.n_routed_experts + 2 * (2 + self.hc_mult) * self.hc_mult * self.hc_mult * h
+            return n
         for l in range(self.num_layers):
             if self.layer_is_kda(l):
                 hd = self.kda_num_heads * self.kda_head_dim
@@ -181,6 +234,8 @@ class ModelConfig:
             kw["kda_layers"] = tuple(kw["kda_layers"])
         if "indexer_full_layers" in kw:
             kw["indexer_full_layers"] = tuple(kw["indexer_full_layers"])
+        if "compress_ratios" in kw:
+            kw["compress_ratios"] = tuple(kw["compress_ratios"])
         return cls(**kw)
 
 
@@ -312,6 +367,45 @@ def qwen15_moe_a27b() -> ModelConfig:
         max_position_embeddings=8192, eos_token_id=151643, bos_token_id=151643)
 
 
+def tiny_deepseek_v4() -> ModelConfig:
+    """DeepSeek-V4 at toy size: a window-only layer, an overlapped ratio-4 layer with its indexer, and a ratio-8
+    layer; the first layer routes by token id."""
+    return ModelConfig(name="tiny-deepseek-v4", family="deepseek_v4", vocab_size=512, hidden_size=128, num_layers=3,
+                       first_k_dense=0, moe_intermediate_size=64, n_routed_experts=8, n_shared_experts=1,
+                       num_experts_per_tok=2, scoring_func="sqrtsoftplus", routed_scaling_factor=1.5,
+                       num_heads=4, head_dim=64, q_lora_rank=64, qk_rope_head_dim=16, sliding_window=8,
+                       compress_ratios=(0, 4, 8), compress_rope_theta=160000.0, rope_scaling_factor=4.0,
+                       rope_original_max_pos=64, o_groups=2, o_lora_rank=32, hc_mult=2, hc_sinkhorn_iters=4,
+                       num_hash_layers=1, swiglu_limit=10.0, index_n_heads=8, index_head_dim=32, index_topk=4)
+
+
+def _v4_ratios(head: Tuple[int, ...], n_layers: int) -> Tuple[int, ...]:
+    rest = n_layers - len(head)
+    return head + tuple(4 if i % 2 == 0 else 128 for i in range(rest))
+
+
+def deepseek_v4_flash() -> ModelConfig:
+    """DeepSeek-V4-Flash (reference: batchgen/models/deepseek/deepseekv4_flash/config.py:36-119)."""
+    return ModelConfig(
+        name="deepseek-v4-flash", family="deepseek_v4", vocab_size=129280, hidden_size=4096, num_layers=43,
+        first_k_dense=0, moe_intermediate_size=2048, n_routed_experts=256, n_shared_experts=1,
+        num_experts_per_tok=6, scoring_func="sqrtsoftplus", routed_scaling_factor=1.5, norm_topk_prob=True,
+        num_heads=64, head_dim=512, q_lora_rank=1024, qk_rope_head_dim=64, sliding_window=128,
+        compress_ratios=_v4_ratios((0, 0), 43), compress_rope_theta=160000.0, rope_theta=10000.0,
+        rope_scaling_factor=16.0, rope_original_max_pos=65536, o_groups=8, o_lora_rank=1024, hc_mult=4,
+        hc_sinkhorn_iters=20, num_hash_layers=3, swiglu_limit=10.0, index_n_heads=64, index_head_dim=128,
+        index_topk=512, max_position_embeddings=1048576, quant="mxfp4", quant_block=32, eos_token_id=1,
+        bos_token_id=0)
+
+
+def deepseek_v4_pro() -> ModelConfig:
+    import dataclasses
+    return dataclasses.replace(
+        deepseek_v4_flash(), name="deepseek-v4-pro", hidden_size=7168, num_layers=61, moe_intermediate_size=3072,
+        n_routed_experts=384, routed_scaling_factor=2.5, num_heads=128, q_lora_rank=1536, o_groups=16,
+        compress_ratios=_v4_ratios((128, 128), 61), index_topk=1024)
+
+
 def deepseek_v3_671b() -> ModelConfig:
     return ModelConfig(
         name="deepseek-v3-671b", family="deepseek_v3", vocab_size=129280, hidden_size=7168,
@@ -414,6 +508,9 @@ _PRESETS = {
     "tiny-deepseek-v2": tiny_deepseek_v2,
     "tiny-mixtral": tiny_mixtral,
     "tiny-qwen2-moe": tiny_qwen2_moe,
+    "tiny-deepseek-v4": tiny_deepseek_v4,
+    "deepseek-v4-flash": deepseek_v4_flash,
+    "deepseek-v4-pro": deepseek_v4_pro,
     "deepseek-v2": deepseek_v2_236b,
     "mixtral-8x7b": mixtral_8x7b,
     "mixtral-8x22b": mixtral_8x22b,
@@ -432,6 +529,8 @@ _PRESETS = {
 # batchgen/config/model_registry.py:63-117).
 _PATTERNS = [
     (r"deepseek[-_/]?(ai/)?.*(v3|r1)", "deepseek-v3-671b"),
+    (r"deepseek[-_/]?(ai/)?.*v4[-_]?pro", "deepseek-v4-pro"),
+    (r"deepseek[-_/]?(ai/)?.*v4", "deepseek-v4-flash"),
     (r"deepseek[-_/]?(ai/)?.*v2", "deepseek-v2"),
     (r"mixtral.*8x22b", "mixtral-8x22b"),
     (r"mixtral", "mixtral-8x7b"),

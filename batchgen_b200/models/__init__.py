@@ -1,4 +1,5 @@
-"""Model families.  ``build_model`` creates a ``Transformer`` for any registered config."""
+"""Model families.  ``build_model`` creates a ``Transformer`` (or, for DeepSeek-V4, a ``DeepSeekV4``) for any
+registered config."""
 from __future__ import annotations
 
 from typing import Optional
@@ -20,6 +21,9 @@ def build_model(cfg: ModelConfig, device="cpu", dtype="fp32", seed: int = 0, lay
     dt = _DTYPES[dtype] if isinstance(dtype, str) else dtype
     layout = layout or ParallelLayout()
     src = WeightSource(seed=seed, device=device, loader=loader, gen_device=gen_device)
+    if cfg.is_v4:
+        from .deepseek_v4 import DeepSeekV4, build_v4_weights
+        return DeepSeekV4(cfg, build_v4_weights(cfg, layout, src, dt), layout, comm, max_positions)
     w = build_weights(cfg, layout, src, dt, alias_experts_every=alias_experts_every,
                       experts_on_host=stream_experts)
     model = Transformer(cfg, w, layout, comm, max_positions)

@@ -38,7 +38,8 @@ class ExpertWeights:
     w2_s: Optional[torch.Tensor] = None
     quant: str = "none"
     interleaved: bool = False
-    activation: str = "silu"
+    activation: str = "silu"             # silu | swiglu_clamped (GPT-OSS) | silu_limit (DeepSeek-V4: clamp, then SiLU(gate) * up)
+    act_limit: float = 0.0               # clamp of silu_limit (0 = none)
 
     @property
     def num_experts(self) -> int:
@@ -50,6 +51,8 @@ class ExpertWeights:
         if self.quant not in ("fp8_block", "mxfp4", "int4") or self.interleaved or not (self.w13.is_cuda or force):
             return self
         perm = gemm.interleave_gate_up_rows(self.w13.shape[1], self.w13.device)
+        if self.activation == "silu_limit" and self.act_limit > 0:
+            return self                          # the clamp is not part of the fused epilogue: natural row order
         if self.quant in ("mxfp4", "int4"):
             if self.activation != "silu":
                 return self                      # other activations run unfused: natural row order
@@ -178,8 +181,14 @@ def combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, extra: Op
     return out
 
 
-def _activation(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
-    return ref.swiglu_clamped(gate_up) if kind == "swiglu_clamped" else ref.silu_mul(gate_up)
+def _activation(gate_up: torch.Tensor, kind: str, limit: float = 0.0) -> torch.Tensor:
+    if kind == "swiglu_clamped":
+        return ref.swiglu_clamped(gate_up)
+    if kind == "silu_limit" and limit > 0:
+        I = gate_up.shape[-1] // 2
+        g, u = gate_up[..., :I].float().clamp(max=limit), gate_up[..., I:].float().clamp(-limit, limit)
+        return (torch.nn.functional.silu(g) * u).to(gate_up.dtype)
+    return ref.silu_mul(gate_up)
 
 
 def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: Optional[torch.Tensor] = None,
@@ -202,7 +211,7 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
             with timer.timed("moe.s3_gemm"):
                 return gemm.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets, counts=counts, rows_hint=rows_hint)
         gu = ref.grouped_fp8_gemm(xq, xs, ew.w13, ew.w13_s, offsets)
-        act = _activation(gu, ew.activation)
+        act = _activation(gu, ew.activation, ew.act_limit)
         aq, as_ = ref.act_quant(act)
         return ref.grouped_fp8_gemm(aq, as_, ew.w2, ew.w2_s, offsets)
     if ew.quant in ("mxfp4", "int4"):
@@ -218,7 +227,7 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         else:
             with timer.timed("moe.s1_gemm"):
                 gu = grouped_w4(x, ew.w13, ew.w13_s, offsets)
-            act = _activation(gu, ew.activation).to(x.dtype)
+            act = _activation(gu, ew.activation, ew.act_limit).to(x.dtype)
         with timer.timed("moe.s3_gemm"):
             return grouped_w4(act, ew.w2, ew.w2_s, offsets)
     # unquantised experts (CPU fp32 oracle path and bf16 debugging)
@@ -229,7 +238,7 @@ def grouped_experts(xq, xs, offsets: torch.Tensor, ew: ExpertWeights, x_dense: O
         a, b = off[e], off[e + 1]
         if b > a:
             gu = x[a:b] @ ew.w13[e].t()
-            out[a:b] = _activation(gu, ew.activation) @ ew.w2[e].t()
+            out[a:b] = _activation(gu, ew.activation, ew.act_limit) @ ew.w2[e].t()
     return out
 
 

@@ -48,11 +48,17 @@ class _PrefillRow:
     """One packed row of a prefill micro-batch: ``tokens`` continue a context of ``start`` tokens whose KV sits in
     the first pages of ``pages`` (``pages`` covers positions 0 .. start + len(tokens)).  ``seq`` receives the token
     sampled from the row's last position; rows without a sequence (a shared prefix computed once for several
-    prompts) produce no logits."""
+    prompts) produce no logits.  ``state_slot`` names the per-sequence state (recurrent or window / compressor state)
+    the row advances: every piece of a chunked prompt carries it, although only the last piece has ``seq``."""
     tokens: List[int]
     start: int
     pages: List[int]
     seq: Optional[Sequence] = None
+    state_slot: int = -1
+
+    def __post_init__(self):
+        if self.seq is not None and self.state_slot < 0:
+            self.state_slot = self.seq.state_slot
 
 
 @dataclass
@@ -104,13 +110,19 @@ class Engine:
             state_heads = next(lw.kda.heads for lw in model.w.layers if lw.kda is not None)
             if ecfg.enable_prefix_cache:
                 raise ValueError("prefix reuse needs per-page state snapshots, which KDA layers do not keep")
+        elif self.cfg.is_v4:
+            # every live sequence holds one slot of window rings and compressor windows
+            state_slots = ecfg.max_state_slots or ecfg.max_decode_batch
+            if ecfg.enable_prefix_cache:
+                raise ValueError("prefix reuse needs per-page snapshots of the window and compressor state, which "
+                                 "DeepSeek-V4 layers do not keep")
         self.kv = PagedKVCache(self.cfg, n_pages, ecfg.page_size, self.device, kv_dtype, state_slots=state_slots,
                                state_heads=state_heads)
         # host tier: on a GPU the native region + asynchronous movers (a region created by the server is attached
         # through ``host_kv_fd``); the pinned torch tensor is the CPU / fallback form of the same tier
         self.host_tier = None
         if (num_host_pages or host_kv_fd is not None) and self.device.type == "cuda" \
-                and ecfg.host_kv_backend == "native" and not self.cfg.has_kda:
+                and ecfg.host_kv_backend == "native" and not self.cfg.has_kda and not self.cfg.is_v4:
             from .host_tier import NativeHostTier
             self.host_tier = NativeHostTier(self.kv, num_host_pages, fd=host_kv_fd)
             self.host_kv = self.host_tier                  # same allocator face (``.alloc``)
@@ -535,7 +547,8 @@ class Engine:
                     continue
                 n = min(len(r.tokens) - off, room)
                 last = off + n == len(r.tokens)
-                batch.append(_PrefillRow(r.tokens[off:off + n], r.start + off, r.pages, r.seq if last else None))
+                batch.append(_PrefillRow(r.tokens[off:off + n], r.start + off, r.pages, r.seq if last else None,
+                                         state_slot=r.state_slot))
                 used += n
                 if not last:
                     later.append((r, off + n))
@@ -575,8 +588,8 @@ class Engine:
             slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
             block_table=build_block_table([r.pages for r in rows], dev),
             cu_seqlens=cu, ctx_lens=ctx_lens,
-            state_slots=(torch.tensor([r.seq.state_slot if r.seq is not None else -1 for r in rows], dtype=torch.int32,
-                                      device=dev) if has_state else None),
+            state_slots=(torch.tensor([r.state_slot for r in rows], dtype=torch.int32, device=dev)
+                         if has_state else None),
             state_has_initial=(torch.tensor([int(c > 0) for c in ctx_lens], dtype=torch.int32, device=dev)
                                if has_state else None),
             logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),

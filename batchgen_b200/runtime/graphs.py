@@ -70,6 +70,9 @@ class CaptureLedger:
 class DecodeGraphRunner:
     def __init__(self, model: Transformer, kv: PagedKVCache, max_batch: int, max_pages_per_seq: int,
                  num_buckets: int = 16, max_bucket: Optional[int] = None, sequence_parallel: bool = False):
+        if model.cfg.is_v4:
+            raise NotImplementedError("DeepSeek-V4 decode reads sequence lengths on the host (window and compressor "
+                                      "bookkeeping): it runs eagerly, without captured graphs")
         self.model, self.kv = model, kv
         self.dev = model.device
         self.sp = sequence_parallel

@@ -69,12 +69,26 @@ class PageAllocator:
 def host_page_bytes(cfg: ModelConfig, page_size: int, kv_elem_bytes: int = 2) -> int:
     """Bytes of one page over all layers (latent KV, then DSA index keys and their scales): the page size of the
     node-shared host region, which the server computes without building a model."""
+    if cfg.is_v4:
+        return sum(v4_entries_per_page(r, page_size) * (cfg.head_dim + (cfg.index_head_dim if r == 4 else 0))
+                   for r in cfg.compress_ratios if r) * kv_elem_bytes
     kv_layers = sum(1 for l in range(cfg.num_layers) if not cfg.layer_is_kda(l))
     b = kv_layers * page_size * cfg.kv_cache_dim * kv_elem_bytes
     if cfg.has_dsa:
         n = len(list(cfg.indexer_full_layers) or range(cfg.num_layers))
         b += n * page_size * (cfg.index_head_dim + 4)
     return b
+
+
+def v4_entries_per_page(ratio: int, page_size: int) -> int:
+    """Pooled entries a page of ``page_size`` tokens holds at compression ``ratio``.  Entry c (tokens c*ratio ..)
+    lives in the page of its first token, at slot ((c * ratio) % page_size) // ratio; when the ratio exceeds the
+    page only every (ratio / page_size)-th page of a sequence carries an entry."""
+    if ratio <= page_size:
+        assert page_size % ratio == 0, (ratio, page_size)
+        return page_size // ratio
+    assert ratio % page_size == 0, (ratio, page_size)
+    return 1
 
 
 class PagedKVCache:
@@ -88,7 +102,7 @@ class PagedKVCache:
         self.row_dim = row_dim or cfg.kv_cache_dim
         pin = pinned and self.device.type == "cpu" and torch.cuda.is_available()
         # KDA layers keep no paged KV: layer l's rows live at index kv_index[l] of the pool
-        kv_layers = [l for l in range(cfg.num_layers) if not cfg.layer_is_kda(l)]
+        kv_layers = [] if cfg.is_v4 else [l for l in range(cfg.num_layers) if not cfg.layer_is_kda(l)]
         self.kv_index = {l: i for i, l in enumerate(kv_layers)}
         self.kv = torch.zeros(len(kv_layers), num_pages, page_size, self.row_dim, dtype=dtype, device=self.device,
                               pin_memory=pin)
@@ -101,9 +115,25 @@ class PagedKVCache:
                                      device=self.device, pin_memory=pin)
             self.idx_s = torch.zeros(len(layers), num_pages, page_size, dtype=torch.float32, device=self.device,
                                      pin_memory=pin)
+        # DeepSeek-V4: pooled KV entries (and the indexer's pooled keys on ratio-4 layers) are the only paged rows;
+        # layer l's pool is [pages, entries per page, width]
+        self.v4_comp: Dict[int, torch.Tensor] = {}
+        self.v4_idx: Dict[int, torch.Tensor] = {}
+        for l, r in enumerate(cfg.compress_ratios):
+            if r:
+                epp = v4_entries_per_page(r, page_size)
+                self.v4_comp[l] = torch.zeros(num_pages, epp, cfg.head_dim, dtype=dtype, device=self.device, pin_memory=pin)
+                if r == 4:
+                    self.v4_idx[l] = torch.zeros(num_pages, epp, cfg.index_head_dim, dtype=dtype, device=self.device,
+                                                 pin_memory=pin)
         self.alloc = PageAllocator(num_pages)
-        # recurrent state of the KDA layers (device tier only)
-        self.state = StateSlotPool(cfg, state_slots, self.device, state_heads) if (cfg.has_kda and state_slots) else None
+        # per-sequence state (device tier only): recurrent state of the KDA layers, or the window rings and
+        # compressor windows of a DeepSeek-V4 model
+        self.state = None
+        if cfg.has_kda and state_slots:
+            self.state = StateSlotPool(cfg, state_slots, self.device, state_heads)
+        elif cfg.is_v4 and state_slots:
+            self.state = V4StatePool(cfg, state_slots, self.device)
 
     # ---- views used by the model
     def latent(self, layer: int) -> torch.Tensor:
@@ -120,7 +150,12 @@ class PagedKVCache:
         self.idx_k[i].view(-1, self.cfg.index_head_dim).view(torch.uint8)[slots] = kq[valid].view(torch.uint8)
         self.idx_s[i].view(-1)[slots] = ks[valid]
 
+    def _v4_pools(self) -> List[torch.Tensor]:
+        return list(self.v4_comp.values()) + list(self.v4_idx.values())
+
     def bytes_per_page(self) -> int:
+        if self.cfg.is_v4:
+            return sum(t[0].numel() * t.element_size() for t in self._v4_pools())
         b = self.kv[0, 0].numel() * self.kv.element_size() * self.kv.shape[0]
         if self.idx_k is not None:
             b += len(self.idx_layers) * (self.idx_k[0, 0].numel() + 4 * self.page_size)
@@ -136,6 +171,14 @@ class PagedKVCache:
         dst = torch.as_tensor(list(dst_pages), dtype=torch.long)
         ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
         with ctx:
+            if self.cfg.is_v4:
+                for mine, theirs in zip(self._v4_pools(), other._v4_pools()):
+                    if self.device.type == other.device.type == "cpu":
+                        mine[dst] = theirs[src]
+                    else:
+                        for s_, d_ in zip(src.tolist(), dst.tolist()):
+                            mine[d_].copy_(theirs[s_], non_blocking=True)
+                return
             if self.device.type == other.device.type == "cpu":
                 self.kv[:, dst] = other.kv[:, src]
                 if self.idx_k is not None:
@@ -181,6 +224,55 @@ class StateSlotPool:
     def layer(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
         i = self.layers[layer]
         return self.conv[i], self.rec[i]
+
+
+class V4StatePool:
+    """Per-sequence state of a DeepSeek-V4 model, one fp32 row per slot: for every layer the sliding-window ring of
+    raw KV rows ([window, D], row = position % window), and on compressed layers the compressor's pending windows
+    (projections and gate scores of the tokens not pooled yet; with overlapped windows also the previous window),
+    twice on ratio-4 layers (attention entries and index keys).  ``rec`` / ``conv`` follow ``StateSlotPool`` so the
+    host store parks a row the same way (``conv`` is an empty placeholder).
+
+    Reference parity: the compressed-ratio GPU KV variant and its per-sequence compressor state
+    (batchgen/kv_cache/gpu_paged_kv_manager.py, SWA / compressed-ratio variants)."""
+
+    def __init__(self, cfg: ModelConfig, num_slots: int, device):
+        self.cfg, self.num_slots = cfg, num_slots
+        D, Di, win = cfg.head_dim, cfg.index_head_dim, cfg.sliding_window
+        self.offsets: Dict[Tuple[int, str], Tuple[int, Tuple[int, ...]]] = {}
+        n = 0
+        for l, r in enumerate(cfg.compress_ratios):
+            parts = [("ring", (win, D))]
+            if r:
+                c = 2 if r == 4 else 1
+                parts += [("kv", (c * r, c * D)), ("score", (c * r, c * D))]
+                if r == 4:
+                    parts += [("idx_kv", (2 * r, 2 * Di)), ("idx_score", (2 * r, 2 * Di))]
+            for name, shape in parts:
+                self.offsets[(l, name)] = (n, shape)
+                n += shape[0] * shape[1]
+        assert n == cfg.v4_state_floats_per_seq()
+        self.rec = torch.zeros(1, num_slots, n, dtype=torch.float32, device=device)
+        self.conv = torch.zeros(1, num_slots, 1, dtype=torch.float32, device=device)
+        self._free = list(range(num_slots - 1, -1, -1))
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def acquire(self) -> int:
+        if not self._free:
+            raise OutOfPages("no free state slot")
+        return self._free.pop()
+
+    def release(self, slot: int) -> None:
+        assert 0 <= slot < self.num_slots and slot not in self._free
+        self._free.append(slot)
+
+    def view(self, slot: int, layer: int, name: str) -> torch.Tensor:
+        """A writable view of one part of ``slot``'s state."""
+        off, shape = self.offsets[(layer, name)]
+        return self.rec[0, slot, off: off + shape[0] * shape[1]].view(shape)
 
 
 class HostStateStore:

@@ -122,8 +122,11 @@ def plan_deployment(cfg: ModelConfig, ecfg: EngineConfig, machine: MachineProfil
 
 
 def state_pool_bytes(cfg: ModelConfig, ecfg: EngineConfig) -> int:
-    """Device bytes of the recurrent-state pool (KDA layers): one slot per sequence that may be live at once."""
+    """Device bytes of the per-sequence state pool (recurrent state of KDA layers, or the window rings and compressor
+    windows of DeepSeek-V4): one slot per sequence that may be live at once."""
     slots = ecfg.max_state_slots or ecfg.max_decode_batch
+    if cfg.is_v4:
+        return slots * 4 * cfg.v4_state_floats_per_seq()
     return slots * cfg.kda_state_bytes_per_seq(max(ecfg.attn_tp_size, 1))
 
 
@@ -138,7 +141,7 @@ def size_kv_pool(cfg: ModelConfig, ecfg: EngineConfig, device: str, dtype) -> Tu
     if str(device).startswith("cuda"):
         free, total = torch.cuda.mem_get_info(torch.device(device))
         reserve = int(total * (1.0 - ecfg.gpu_memory_frac)) + 4 * GiB      # graphs + prefill workspace headroom
-        if cfg.has_kda:                                                    # recurrent-state slots come out of the same memory
+        if cfg.has_kda or cfg.is_v4:                                       # per-sequence state slots come out of the same memory
             reserve += state_pool_bytes(cfg, ecfg)
         pages = max(16, (free - reserve) // page_bytes)
         if ecfg.max_model_len > 0:

@@ -107,7 +107,18 @@ def model_contract(cfg, world: int, on_gpu: bool, moe_comm: str = "nccl") -> Lis
                 bad.append(f"{name} {v} is not a multiple of 128")
     elif cfg.quant not in ("none",):
         bad.append(f"quant {cfg.quant!r} has no kernel")
-    if cfg.is_mla:
+    if cfg.is_v4:
+        k_o = cfg.num_heads * cfg.head_dim // max(cfg.o_groups, 1)
+        for name, v in (("q_lora_rank", cfg.q_lora_rank), ("head_dim", cfg.head_dim),
+                        ("heads * head_dim / o_groups", k_o), ("o_groups * o_lora_rank", cfg.o_groups * cfg.o_lora_rank)):
+            if v % 64:
+                bad.append(f"{name} {v} is not a multiple of 64 (K of the projection GEMMs)")
+        if world > 1:
+            notes.append("DeepSeek-V4: attention replicated per engine, experts expert-parallel; use --dp-size for "
+                         "data-parallel cohorts")
+        notes.append("DeepSeek-V4 attention core and compressor run as torch ops (no captured graphs); projections, "
+                     "router and experts run on the kernels")
+    elif cfg.is_mla:
         if cfg.kv_lora_rank != 512 or cfg.qk_rope_head_dim != 64:
             bad.append(f"MLA kernels need kv_lora_rank 512 + rope 64 (got {cfg.kv_lora_rank} + {cfg.qk_rope_head_dim})")
         if cfg.qk_nope_head_dim % 64:
@@ -125,7 +136,8 @@ def model_contract(cfg, world: int, on_gpu: bool, moe_comm: str = "nccl") -> Lis
         bad.append(f"KDA head_dim {cfg.kda_head_dim}: the kernel covers 64 and 128")
     if world > 1 and moe_comm == "fused":
         from ..models.transformer import Transformer
-        why = Transformer.supports_sequence_parallel(cfg)
+        why = ("DeepSeek-V4 attention is replicated inside an engine" if cfg.is_v4
+               else Transformer.supports_sequence_parallel(cfg))
         notes.append("fused NVLink path" if why is None else f"NCCL layout instead of the fused path: {why}")
     if bad:
         raise PreflightError("model contract: " + "; ".join(bad))

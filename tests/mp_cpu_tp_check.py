@@ -86,6 +86,25 @@ def main():
     kp, kd = run_kda(kfull, kcfg.kda_num_heads)
     tp_p, tp_d = run_kda(ktp, kcfg.kda_num_heads // world)
     kda_err = max(float((tp_p - kp).abs().max()), float((tp_d - kd).abs().max()))
+    # DeepSeek-V4: attention replicated on every rank, routed experts expert-parallel
+    vcfg = get_model_config("tiny-deepseek-v4")
+    vids = torch.randint(2, vcfg.vocab_size, (21,), generator=g, dtype=torch.int32)
+
+    def run_v4(model):
+        kv = PagedKVCache(vcfg, 8, ps, "cpu", torch.float32, state_slots=2)
+        pages, slot = kv.alloc.alloc(2), kv.state.acquire()
+        pre = AttnMeta(mode="prefill", positions=torch.arange(21, dtype=torch.int32),
+                       slot_mapping=torch.tensor(slots_for_range(pages, 0, 21, ps)), block_table=build_block_table([pages], "cpu"),
+                       cu_seqlens=[0, 21], ctx_lens=[0], state_slots=torch.tensor([slot], dtype=torch.int32))
+        a = model.forward(vids, pre, kv)
+        dec = AttnMeta(mode="decode", positions=torch.tensor([21], dtype=torch.int32),
+                       slot_mapping=torch.tensor(slots_for_range(pages, 21, 22, ps)), block_table=build_block_table([pages], "cpu"),
+                       seqlens=torch.tensor([22], dtype=torch.int32), state_slots=torch.tensor([slot], dtype=torch.int32))
+        return torch.cat([a, model.forward(torch.tensor([9], dtype=torch.int32), dec, kv)])
+
+    v_want = run_v4(build_model(vcfg, "cpu", torch.float32, seed=2))
+    v_got = run_v4(build_model(vcfg, "cpu", torch.float32, seed=2, layout=layout, comm=comm))
+    kda_err = max(kda_err, float((v_got - v_want).abs().max()))
     err = torch.tensor([max(float((got_p - want_p).abs().max()), kda_err), float((got_d_heads - want_d).abs().max()),
                         float((got_d_req - want_d).abs().max()), 0.0 if (ok_layout and torch.equal(z, x)) else 1.0])
     dist.all_reduce(err, op=dist.ReduceOp.MAX)

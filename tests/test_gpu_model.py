@@ -96,3 +96,61 @@ def test_gqa_families_at_kernel_sized_geometry(name):
     here, so the paged GQA decode kernel, the RoPE kernel and the FP8 expert GEMMs are what runs."""
     from batchgen_b200.ops import _ext
     _other_family(name, _ext)
+
+
+def _v4_cfg(quant="mxfp4"):
+    return get_model_config("tiny-deepseek-v4", vocab_size=4096, hidden_size=1024, head_dim=128, num_heads=8,
+                            q_lora_rank=512, qk_rope_head_dim=64, sliding_window=64, compress_ratios=(0, 4, 128),
+                            num_layers=3, o_groups=2, o_lora_rank=256, index_n_heads=8, index_head_dim=128,
+                            index_topk=256, moe_intermediate_size=512, n_routed_experts=8, num_experts_per_tok=8,
+                            rope_original_max_pos=4096, quant=quant, quant_block=32)
+
+
+@pytest.mark.parametrize("quant,tol", [("none", 0.05), ("mxfp4", 0.25)])
+def test_deepseek_v4_on_gpu_matches_cpu(quant, tol):
+    """DeepSeek-V4 at kernel-sized geometry: prefill logits agree with the bf16 CPU run of the same weights, chunked
+    prefill agrees with one pass, and greedy decode through the engine completes.  No library fallback is allowed.
+    ``mxfp4`` runs FP8 projections and MXFP4 experts with the clamped activation; there a flipped e4m3 / e2m1 rounding
+    moves the logits by several percent, so the bound is loose and the unquantised run carries the tight one."""
+    from batchgen_b200.ops import _ext
+    cfg = _v4_cfg(quant)
+    ids = torch.randint(2, cfg.vocab_size, (300,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    def run(device, dtype, cuts):
+        model = build_model(cfg, device, "fp32" if dtype == torch.float32 else "bf16", seed=0)
+        kv = PagedKVCache(cfg, 8, 64, device, dtype, state_slots=2)
+        pages, slot, out, start = kv.alloc.alloc(5), kv.state.acquire(), [], 0
+        for end in cuts:
+            n = end - start
+            meta = AttnMeta(mode="prefill", positions=torch.arange(start, end, dtype=torch.int32, device=device),
+                            slot_mapping=torch.tensor(slots_for_range(pages, start, end, 64), device=device),
+                            block_table=build_block_table([pages], device), cu_seqlens=[0, n], ctx_lens=[start],
+                            state_slots=torch.tensor([slot], dtype=torch.int32, device=device))
+            out.append(model.forward(torch.tensor(ids[start:end], dtype=torch.int32, device=device), meta, kv).float().cpu())
+            start = end
+        return torch.cat(out)
+
+    # every expert is selected (top-8 of 8) and the index top-k keeps every entry: with random weights a flipped
+    # expert or entry choice changes the logits far more than rounding does, and each selection kernel has its own
+    # test; the comparison runs against the CPU model in the same precision
+    cpu = run("cpu", torch.bfloat16, [300])
+    gpu = run("cuda", torch.bfloat16, [300])
+    rel = ((gpu - cpu).norm() / cpu.norm()).item()
+    assert rel < tol, rel
+    parts = run("cuda", torch.bfloat16, [130, 131, 300])
+    assert ((parts - gpu).norm() / gpu.norm()).item() < tol
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (140, 9, 70)]
+    eng = Engine(build_model(cfg, "cuda", "bf16", seed=0), EngineConfig(page_size=64), num_gpu_pages=64)
+    out = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    torch.cuda.synchronize()
+    _ext.check_status()
+    assert all(len(o) == 6 for o in out) and eng.kv.alloc.num_used == 0
+
+
+@pytest.mark.parametrize("name", ["tiny-mixtral", "tiny-qwen2-moe", "tiny-deepseek-v2"])
+def test_legacy_families_on_gpu_match_cpu(name):
+    from batchgen_b200.ops import _ext
+    from batchgen_b200.ops.policy import allow_library_fallback
+    with allow_library_fallback():          # test-sized geometries (head_dim 32, latent 64)
+        _other_family(name, _ext)

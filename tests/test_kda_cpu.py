@@ -123,3 +123,18 @@ def test_chunk_form_equals_the_recurrence():
     b = kda.kda_chunk_ref(q, k, v, g, beta, Sb, 0.25, chunk=64)
     assert torch.allclose(a, b, atol=2e-4, rtol=2e-4)
     assert torch.allclose(Sa, Sb, atol=2e-4, rtol=2e-4)
+
+
+def test_chunked_prefill_advances_the_recurrent_state_in_every_piece():
+    """A prompt cut into pieces by ``max_prefill_tokens``: every piece (not only the last, which samples) updates the
+    sequence's state slot, so the tokens equal the one-pass run."""
+    cfg = get_model_config("tiny-kimi-linear")
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(2, cfg.vocab_size, (40,), generator=g).tolist() for _ in range(3)]
+    params = SamplingParams(max_new_tokens=8, temperature=0.0, ignore_eos=True)
+    mk = lambda **kw: Engine(build_model(cfg, device="cpu", dtype=torch.float32, seed=0),
+                             EngineConfig(page_size=16, max_decode_batch=8, enable_cuda_graph=False, **kw), num_gpu_pages=64)
+    want = mk().generate(prompts, params)
+    eng = mk(max_prefill_tokens=24)
+    assert eng.generate(prompts, params) == want
+    assert eng.stats.prefill_chunks > 0
