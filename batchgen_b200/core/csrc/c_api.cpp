@@ -4,6 +4,7 @@
 #include <vector>
 
 #include "host_kv.h"
+#include "host_kv_views.h"
 #include "weight_ring.h"
 
 using namespace bgcore;
@@ -95,5 +96,67 @@ void bgc_prefix_stats(void* h, unsigned long long* out) {
   static_cast<HostPagedKV*>(h)->prefix_stats(s);
   for (int i = 0; i < 4; ++i) out[i] = s[i];
 }
+
+
+// ------------------------------------------------------------------ sliding-window / compressed-ratio host views
+void* bgc_swa_create(void* hostkv, int page_tokens, int row_bytes, int layers, unsigned long long window_tokens) {
+  auto* v = new SlidingWindowView(static_cast<HostPagedKV*>(hostkv), page_tokens, row_bytes, layers, window_tokens);
+  if (!v->valid()) {
+    delete v;
+    return nullptr;
+  }
+  return v;
+}
+void bgc_swa_destroy(void* v) { delete static_cast<SlidingWindowView*>(v); }
+long bgc_swa_advance(void* v, long long seq, unsigned long long raw_end) {
+  return static_cast<SlidingWindowView*>(v)->advance(seq, raw_end);
+}
+long bgc_swa_append_position(void* v, long long seq, unsigned long long raw_pos) {
+  return static_cast<SlidingWindowView*>(v)->append_position(seq, raw_pos);
+}
+long bgc_swa_write_rows(void* v, long long seq, int layer, unsigned long long raw_start, const void* rows,
+                        unsigned long long n) {
+  return static_cast<SlidingWindowView*>(v)->write_rows(seq, layer, raw_start, rows, n);
+}
+long bgc_swa_read_window(void* v, long long seq, int layer, void* out, unsigned long long cap,
+                         unsigned long long* first_raw) {
+  size_t first = 0;
+  const long n = static_cast<SlidingWindowView*>(v)->read_window(seq, layer, out, cap, &first);
+  if (first_raw != nullptr) *first_raw = first;
+  return n;
+}
+void bgc_swa_release(void* v, long long seq) { static_cast<SlidingWindowView*>(v)->release(seq); }
+unsigned long long bgc_swa_active_pages(void* v, long long seq) {
+  return static_cast<SlidingWindowView*>(v)->active_pages(seq);
+}
+unsigned long long bgc_swa_window_start(void* v, long long seq) {
+  return static_cast<SlidingWindowView*>(v)->window_start_token(seq);
+}
+
+void* bgc_cratio_create(void* hostkv, int page_tokens, int row_bytes, int layers, unsigned long long ratio) {
+  auto* v = new CompressedRatioView(static_cast<HostPagedKV*>(hostkv), page_tokens, row_bytes, layers, ratio);
+  if (!v->valid()) {
+    delete v;
+    return nullptr;
+  }
+  return v;
+}
+void bgc_cratio_destroy(void* v) { delete static_cast<CompressedRatioView*>(v); }
+long bgc_cratio_offload(void* v, long long seq, int layer, unsigned long long raw_len, const void* rows) {
+  return static_cast<CompressedRatioView*>(v)->offload(seq, layer, raw_len, rows);
+}
+long bgc_cratio_append(void* v, long long seq, int layer, unsigned long long raw_pos, const void* row) {
+  return static_cast<CompressedRatioView*>(v)->append(seq, layer, raw_pos, row);
+}
+long bgc_cratio_read(void* v, long long seq, int layer, void* out, unsigned long long cap) {
+  return static_cast<CompressedRatioView*>(v)->read(seq, layer, out, cap);
+}
+unsigned long long bgc_cratio_stored(void* v, long long seq) {
+  return static_cast<CompressedRatioView*>(v)->stored_tokens(seq);
+}
+unsigned long long bgc_cratio_pages(void* v, long long seq) {
+  return static_cast<CompressedRatioView*>(v)->pages().num_pages(seq);
+}
+void bgc_cratio_release(void* v, long long seq) { static_cast<CompressedRatioView*>(v)->release(seq); }
 
 }  // extern "C"

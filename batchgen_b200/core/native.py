@@ -37,6 +37,13 @@ def lib() -> ctypes.CDLL:
         L.bgc_hostkv_num_pages.restype = ctypes.c_ulonglong
         L.bgc_hostkv_bytes.restype = ctypes.c_ulonglong
         L.bgc_mover_create.restype = ctypes.c_void_p
+        for f in ("bgc_swa_create", "bgc_cratio_create"):
+            getattr(L, f).restype = ctypes.c_void_p
+        for f in ("bgc_swa_advance", "bgc_swa_append_position", "bgc_swa_write_rows", "bgc_swa_read_window",
+                  "bgc_cratio_offload", "bgc_cratio_append", "bgc_cratio_read"):
+            getattr(L, f).restype = ctypes.c_long
+        for f in ("bgc_swa_active_pages", "bgc_swa_window_start", "bgc_cratio_stored", "bgc_cratio_pages"):
+            getattr(L, f).restype = ctypes.c_ulonglong
         L.bgc_mover_submit.restype = ctypes.c_long
         L.bgc_mover_bytes.restype = ctypes.c_ulonglong
         L.bgc_mover_misaligned.restype = ctypes.c_ulonglong
@@ -245,6 +252,135 @@ class HostPagedKV:
                 self.L.bgc_unpin_host(ctypes.c_void_p(self.L.bgc_hostkv_base(self.h)))
                 self._pinned = False
             self.L.bgc_hostkv_destroy(self.h)
+            self.h = None
+
+
+class _RowView:
+    """Shared plumbing of the per-sequence row views: rows are fixed-size token records of one layer."""
+
+    def __init__(self, kv: HostPagedKV, row_shape: Sequence[int], dtype: torch.dtype):
+        self.kv, self.L = kv, kv.L
+        self.row_shape, self.dtype = tuple(row_shape), dtype
+        n = 1
+        for d in self.row_shape:
+            n *= d
+        self.row_bytes = n * torch.empty(0, dtype=dtype).element_size()
+
+    def _rows_ptr(self, rows: torch.Tensor):
+        assert rows.dtype == self.dtype and rows.is_contiguous() and not rows.is_cuda
+        assert tuple(rows.shape[1:]) == self.row_shape, (rows.shape, self.row_shape)
+        return ctypes.c_void_p(rows.data_ptr())
+
+    def _out(self, n: int) -> torch.Tensor:
+        return torch.empty((n,) + self.row_shape, dtype=self.dtype)
+
+    @staticmethod
+    def _check(rc: int, what: str) -> int:
+        if rc == -2:
+            raise MemoryError(f"{what}: the host KV region has no free page")
+        if rc == -3:
+            raise RuntimeError(f"{what}: a stored position has no page")
+        return rc
+
+
+class SlidingWindowHostView(_RowView):
+    """Host KV of sliding-window layers: a sequence holds only the pages that overlap its last ``window`` tokens
+    (at most window / page + 1); older pages return to the region as the sequence grows.
+
+    Reference parity: core/KV_Storage/swa_host_paged_kv_worker_view.h."""
+
+    def __init__(self, kv: HostPagedKV, page_tokens: int, layers: int, row_shape: Sequence[int], dtype: torch.dtype,
+                 window_tokens: int):
+        super().__init__(kv, row_shape, dtype)
+        self.h = ctypes.c_void_p(self.L.bgc_swa_create(kv.h, page_tokens, self.row_bytes, layers,
+                                                       ctypes.c_ulonglong(window_tokens)))
+        if not self.h:
+            raise ValueError("window must be a positive multiple of the page size and a page must hold "
+                             "layers x page_tokens rows")
+        self.window = window_tokens
+
+    def write(self, seq: int, layer: int, raw_start: int, rows: torch.Tensor) -> int:
+        """Store rows of raw positions raw_start ..; rows that already fell out of the window are skipped.  Raises
+        ``IndexError`` for a range older than the kept window."""
+        rc = self.L.bgc_swa_write_rows(self.h, ctypes.c_longlong(seq), layer, ctypes.c_ulonglong(raw_start),
+                                       self._rows_ptr(rows), ctypes.c_ulonglong(rows.shape[0]))
+        if rc == -1:
+            raise IndexError("rows older than the sliding window cannot be written")
+        return self._check(rc, "SlidingWindowHostView.write")
+
+    def append_position(self, seq: int, raw_pos: int) -> int:
+        rc = self.L.bgc_swa_append_position(self.h, ctypes.c_longlong(seq), ctypes.c_ulonglong(raw_pos))
+        if rc == -1:
+            raise IndexError("position older than the sliding window")
+        return self._check(rc, "SlidingWindowHostView.append_position")
+
+    def read(self, seq: int, layer: int) -> Tuple[torch.Tensor, int]:
+        """-> (rows of the window, oldest first; raw position of the first row)."""
+        out = self._out(self.window)
+        first = ctypes.c_ulonglong(0)
+        n = self._check(self.L.bgc_swa_read_window(self.h, ctypes.c_longlong(seq), layer, ctypes.c_void_p(out.data_ptr()),
+                                                   ctypes.c_ulonglong(self.window), ctypes.byref(first)), "read")
+        return out[:n], int(first.value)
+
+    def active_pages(self, seq: int) -> int:
+        return int(self.L.bgc_swa_active_pages(self.h, ctypes.c_longlong(seq)))
+
+    def window_start(self, seq: int) -> int:
+        return int(self.L.bgc_swa_window_start(self.h, ctypes.c_longlong(seq)))
+
+    def release(self, seq: int) -> None:
+        self.L.bgc_swa_release(self.h, ctypes.c_longlong(seq))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_swa_destroy(self.h)
+            self.h = None
+
+
+class CompressedRatioHostView(_RowView):
+    """Host KV of compressed layers: one stored row per ``ratio`` raw tokens; a decode step stores a row only when
+    its position closes a group of ``ratio``.
+
+    Reference parity: core/KV_Storage/compressed_ratio_host_paged_kv_worker_view.h."""
+
+    def __init__(self, kv: HostPagedKV, page_tokens: int, layers: int, row_shape: Sequence[int], dtype: torch.dtype,
+                 ratio: int):
+        super().__init__(kv, row_shape, dtype)
+        self.h = ctypes.c_void_p(self.L.bgc_cratio_create(kv.h, page_tokens, self.row_bytes, layers, ctypes.c_ulonglong(ratio)))
+        if not self.h:
+            raise ValueError("ratio must be positive and a page must hold layers x page_tokens rows")
+        self.ratio = ratio
+
+    def offload(self, seq: int, layer: int, raw_len: int, rows: torch.Tensor) -> int:
+        """Store the ``raw_len // ratio`` pooled rows of a prefilled sequence."""
+        assert rows.shape[0] >= raw_len // self.ratio
+        return self._check(self.L.bgc_cratio_offload(self.h, ctypes.c_longlong(seq), layer, ctypes.c_ulonglong(raw_len),
+                                                     self._rows_ptr(rows)), "CompressedRatioHostView.offload")
+
+    def append(self, seq: int, layer: int, raw_pos: int, row: torch.Tensor) -> int:
+        """Decode step at ``raw_pos``: -> the storage position written, or -1 when the position closes no group."""
+        return self._check(self.L.bgc_cratio_append(self.h, ctypes.c_longlong(seq), layer, ctypes.c_ulonglong(raw_pos),
+                                                    self._rows_ptr(row.reshape((1,) + self.row_shape))), "append")
+
+    def read(self, seq: int, layer: int) -> torch.Tensor:
+        n = self.stored(seq)
+        out = self._out(n)
+        got = self._check(self.L.bgc_cratio_read(self.h, ctypes.c_longlong(seq), layer, ctypes.c_void_p(out.data_ptr()),
+                                                 ctypes.c_ulonglong(n)), "read")
+        return out[:got]
+
+    def stored(self, seq: int) -> int:
+        return int(self.L.bgc_cratio_stored(self.h, ctypes.c_longlong(seq)))
+
+    def pages(self, seq: int) -> int:
+        return int(self.L.bgc_cratio_pages(self.h, ctypes.c_longlong(seq)))
+
+    def release(self, seq: int) -> None:
+        self.L.bgc_cratio_release(self.h, ctypes.c_longlong(seq))
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_cratio_destroy(self.h)
             self.h = None
 
 

@@ -255,3 +255,63 @@ def test_streamed_experts_match_resident_model_on_cpu():
     st = streamed_model.streamer.stats()
     assert st["modules_copied"] == 2 * 3 and st["bytes_copied"] == 2 * streamed_model.streamer.bytes_per_pass
     streamed_model.streamer.close()
+
+
+def test_sliding_window_host_view_keeps_only_the_window_pages():
+    from batchgen_b200.core.native import SlidingWindowHostView
+    page_tokens, layers, D, window = 4, 2, 8, 8
+    kv = native.HostPagedKV(num_pages=6, page_bytes=layers * page_tokens * D * 4, prefix_slots=0)
+    view = SlidingWindowHostView(kv, page_tokens, layers, (D,), torch.float32, window)
+    rows = torch.arange(40 * D, dtype=torch.float32).view(40, D)
+    # a 10-token prefill: positions 0 .. 9, window 8 -> first needed token 2 -> page 0 is still kept
+    assert view.write(7, 0, 0, rows[:10].contiguous()) == 10
+    assert view.write(7, 1, 0, (rows[:10] + 1000).contiguous()) == 10
+    assert view.active_pages(7) == 3 and view.window_start(7) == 0
+    got, first = view.read(7, 0)
+    assert first == 2 and torch.equal(got, rows[2:10])
+    # decode appends: the window start moves page by page and old pages return to the region
+    for pos in range(10, 30):
+        sp = view.append_position(7, pos)
+        assert sp == pos - view.window_start(7)
+        view.write(7, 0, pos, rows[pos: pos + 1].contiguous())
+        view.write(7, 1, pos, (rows[pos: pos + 1] + 1000).contiguous())
+        assert view.active_pages(7) <= window // page_tokens + 1
+    assert view.window_start(7) == 20 and kv.num_free == 6 - view.active_pages(7)
+    got, first = view.read(7, 1)
+    assert first == 22 and torch.equal(got, rows[22:30] + 1000)
+    with pytest.raises(IndexError):
+        view.write(7, 0, 3, rows[3:5].contiguous())           # older than the kept window
+    # a second sequence, then the region runs out
+    assert view.write(8, 0, 0, rows[:12].contiguous()) == 8      # positions 0 .. 3 are outside the window already
+    assert view.active_pages(8) == 2 and view.window_start(8) == 4
+    with pytest.raises(MemoryError):
+        view.write(9, 0, 0, rows[:8].contiguous())
+    view.release(7); view.release(8); view.release(9)
+    assert kv.num_free == 6 and kv.audit() == 0
+    with pytest.raises(ValueError):
+        SlidingWindowHostView(kv, page_tokens, layers, (D,), torch.float32, 6)     # not a multiple of the page
+    view.close(); kv.close()
+
+
+def test_compressed_ratio_host_view_stores_one_row_per_group():
+    from batchgen_b200.core.native import CompressedRatioHostView
+    page_tokens, layers, D, ratio = 4, 1, 6, 4
+    kv = native.HostPagedKV(num_pages=4, page_bytes=layers * page_tokens * D * 2, prefix_slots=0)
+    view = CompressedRatioHostView(kv, page_tokens, layers, (D,), torch.bfloat16, ratio)
+    pooled = torch.randn(16, D).to(torch.bfloat16)
+    # prefill of 14 raw tokens -> 3 stored rows in one page
+    assert view.offload(3, 0, 14, pooled[:3].contiguous()) == 3
+    assert view.stored(3) == 3 and view.pages(3) == 1
+    # decode: positions 14, 15 -> the row of group 3 is stored at position 15 only
+    assert view.append(3, 0, 14, pooled[3]) == -1 and view.stored(3) == 3
+    assert view.append(3, 0, 15, pooled[3]) == 3 and view.stored(3) == 4
+    for pos in range(16, 24):
+        sp = view.append(3, 0, pos, pooled[pos // ratio])
+        assert sp == (pos // ratio if (pos + 1) % ratio == 0 else -1)
+    assert view.stored(3) == 6 and view.pages(3) == 2
+    assert torch.equal(view.read(3, 0), pooled[:6])
+    # a sequence shorter than one group holds a page (capacity for its first row) and no rows
+    assert view.offload(4, 0, 3, pooled[:1].contiguous()) == 0 and view.stored(4) == 0 and view.pages(4) == 1
+    view.release(3); view.release(4)
+    assert kv.num_free == 4 and kv.audit() == 0
+    view.close(); kv.close()
