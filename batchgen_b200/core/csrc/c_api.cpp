@@ -5,6 +5,7 @@
 
 #include "host_kv.h"
 #include "host_kv_views.h"
+#include "weight_daemon.h"
 #include "weight_ring.h"
 
 using namespace bgcore;
@@ -158,5 +159,83 @@ unsigned long long bgc_cratio_pages(void* v, long long seq) {
   return static_cast<CompressedRatioView*>(v)->pages().num_pages(seq);
 }
 void bgc_cratio_release(void* v, long long seq) { static_cast<CompressedRatioView*>(v)->release(seq); }
+
+
+// ------------------------------------------------------------------ node weight daemon
+// peers: "node=host:port,node=host:port"
+void* bgc_wd_create(int node, const char* socket_path, int listen_port, const char* peers, int staging_slots,
+                    unsigned long long slot_bytes, int prefetch_depth, int acquire_wait_ms) {
+  DaemonConfig c;
+  c.node = node;
+  c.socket_path = socket_path ? socket_path : "";
+  c.listen_port = listen_port;
+  c.staging_slots = staging_slots;
+  c.slot_bytes = slot_bytes;
+  c.prefetch_depth = prefetch_depth;
+  c.acquire_wait_ms = acquire_wait_ms;
+  std::string p = peers ? peers : "";
+  size_t pos = 0;
+  while (pos < p.size()) {
+    size_t end = p.find(',', pos);
+    if (end == std::string::npos) end = p.size();
+    const std::string item = p.substr(pos, end - pos);
+    const size_t eq = item.find('=');
+    if (eq != std::string::npos) c.peers[std::atoi(item.substr(0, eq).c_str())] = item.substr(eq + 1);
+    pos = end + 1;
+  }
+  return new WeightDaemon(c);
+}
+void bgc_wd_destroy(void* d) { delete static_cast<WeightDaemon*>(d); }
+void bgc_wd_set_store(void* d, const void* base, unsigned long long bytes) {
+  static_cast<WeightDaemon*>(d)->set_local_store(base, bytes);
+}
+int bgc_wd_add_module(void* d, const char* key, int owner, unsigned long long offset, unsigned long long bytes) {
+  return static_cast<WeightDaemon*>(d)->add_module(key, owner, offset, bytes) ? 0 : -1;
+}
+// keys: newline-separated
+void bgc_wd_set_schedule(void* d, const char* keys) {
+  std::vector<std::string> v;
+  std::string s = keys ? keys : "";
+  size_t pos = 0;
+  while (pos < s.size()) {
+    size_t end = s.find('\n', pos);
+    if (end == std::string::npos) end = s.size();
+    if (end > pos) v.push_back(s.substr(pos, end - pos));
+    pos = end + 1;
+  }
+  static_cast<WeightDaemon*>(d)->set_schedule(v);
+}
+int bgc_wd_start(void* d) { return static_cast<WeightDaemon*>(d)->start() ? 0 : -1; }
+void bgc_wd_stop(void* d) { static_cast<WeightDaemon*>(d)->stop(); }
+int bgc_wd_staging_fd(void* d) { return static_cast<WeightDaemon*>(d)->staging_fd(); }
+unsigned long long bgc_wd_staging_bytes(void* d) { return static_cast<WeightDaemon*>(d)->staging_bytes(); }
+unsigned long long bgc_wd_epoch(void* d) { return static_cast<WeightDaemon*>(d)->epoch(); }
+unsigned long long bgc_wd_begin_swap(void* d) { return static_cast<WeightDaemon*>(d)->begin_swap(); }
+static int copy_out(const std::string& s, char* out, int cap) {
+  const int n = (int)std::min<size_t>(s.size(), cap > 0 ? cap - 1 : 0);
+  if (cap > 0) {
+    std::memcpy(out, s.data(), n);
+    out[n] = 0;
+  }
+  return (int)s.size();
+}
+int bgc_wd_finish_swap(void* d, char* out, int cap) { return copy_out(static_cast<WeightDaemon*>(d)->finish_swap(), out, cap); }
+int bgc_wd_status(void* d, char* out, int cap) { return copy_out(static_cast<WeightDaemon*>(d)->status(), out, cap); }
+
+void* bgc_wdc_create() { return new DaemonClient(); }
+void bgc_wdc_destroy(void* c) { delete static_cast<DaemonClient*>(c); }
+int bgc_wdc_connect(void* c, const char* path) { return static_cast<DaemonClient*>(c)->connect_to(path) ? 0 : -1; }
+int bgc_wdc_hello(void* c, unsigned worker, unsigned long long epoch) { return static_cast<DaemonClient*>(c)->hello(worker, epoch); }
+int bgc_wdc_acquire(void* c, const char* key, int timeout_ms, int* slot, unsigned long long* offset,
+                    unsigned long long* bytes) {
+  uint64_t off = 0, by = 0;
+  const int rc = static_cast<DaemonClient*>(c)->acquire(key, timeout_ms, slot, &off, &by);
+  *offset = off;
+  *bytes = by;
+  return rc;
+}
+int bgc_wdc_release(void* c, const char* key) { return static_cast<DaemonClient*>(c)->release(key); }
+void bgc_wdc_close(void* c) { static_cast<DaemonClient*>(c)->close_conn(); }
+int bgc_wdc_error(void* c, char* out, int cap) { return copy_out(static_cast<DaemonClient*>(c)->last_error(), out, cap); }
 
 }  // extern "C"

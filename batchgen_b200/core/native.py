@@ -37,7 +37,9 @@ def lib() -> ctypes.CDLL:
         L.bgc_hostkv_num_pages.restype = ctypes.c_ulonglong
         L.bgc_hostkv_bytes.restype = ctypes.c_ulonglong
         L.bgc_mover_create.restype = ctypes.c_void_p
-        for f in ("bgc_swa_create", "bgc_cratio_create"):
+        for f in ("bgc_wd_staging_bytes", "bgc_wd_epoch", "bgc_wd_begin_swap"):
+            getattr(L, f).restype = ctypes.c_ulonglong
+        for f in ("bgc_swa_create", "bgc_cratio_create", "bgc_wd_create", "bgc_wdc_create"):
             getattr(L, f).restype = ctypes.c_void_p
         for f in ("bgc_swa_advance", "bgc_swa_append_position", "bgc_swa_write_rows", "bgc_swa_read_window",
                   "bgc_cratio_offload", "bgc_cratio_append", "bgc_cratio_read"):
@@ -595,3 +597,118 @@ class ReplicaControlBlock:
 
     def abort(self, member: int) -> None:
         lib().bgc_rcb_abort(self._mem, member)
+
+
+class WeightDaemon:
+    """Node daemon of a distributed host weight store: serves this node's share of the modules to the other nodes,
+    keeps remote modules that the schedule needs next in a staging region, and leases them to the node's workers over
+    a unix socket (``WeightDaemonClient``).
+
+    Reference parity: core/Weights_Storage/distributed_weight_daemon.{h,cpp} (UCX RMA there; a TCP stream here)."""
+
+    def __init__(self, node: int, socket_path: str, listen_port: int = 0, peers: Optional[Dict[int, str]] = None,
+                 staging_slots: int = 4, slot_bytes: int = 0, prefetch_depth: int = 2, acquire_wait_ms: int = 50):
+        self.L = lib()
+        peer_s = ",".join(f"{n}={a}" for n, a in (peers or {}).items())
+        self.h = ctypes.c_void_p(self.L.bgc_wd_create(node, socket_path.encode(), listen_port, peer_s.encode(), staging_slots,
+                                                      ctypes.c_ulonglong(slot_bytes), prefetch_depth, acquire_wait_ms))
+        self.node, self.socket_path, self.slot_bytes = node, socket_path, slot_bytes
+        self._store = None
+        self._staging = None
+
+    def set_local_store(self, store: torch.Tensor) -> None:
+        """``store``: a contiguous uint8 host tensor holding this node's modules back to back (kept alive here)."""
+        assert store.dtype == torch.uint8 and store.is_contiguous() and not store.is_cuda
+        self._store = store
+        self.L.bgc_wd_set_store(self.h, ctypes.c_void_p(store.data_ptr()), ctypes.c_ulonglong(store.numel()))
+
+    def add_module(self, key: str, owner: int, offset: int, nbytes: int) -> None:
+        if self.L.bgc_wd_add_module(self.h, key.encode(), owner, ctypes.c_ulonglong(offset), ctypes.c_ulonglong(nbytes)) != 0:
+            raise ValueError(f"module {key!r}: outside the local store, larger than a staging slot, or a bad key")
+
+    def set_schedule(self, keys: Sequence[str]) -> None:
+        self.L.bgc_wd_set_schedule(self.h, "\n".join(keys).encode())
+
+    def start(self) -> None:
+        if self.L.bgc_wd_start(self.h) != 0:
+            raise RuntimeError("the weight daemon could not open its sockets or staging region")
+
+    def staging(self) -> torch.Tensor:
+        """The staging region as a uint8 tensor (a second mapping of the daemon's memfd, as a worker would make)."""
+        if self._staging is None:
+            import mmap
+            n = int(self.L.bgc_wd_staging_bytes(self.h))
+            self._mm = mmap.mmap(self.L.bgc_wd_staging_fd(self.h), n, mmap.MAP_SHARED, mmap.PROT_READ | mmap.PROT_WRITE)
+            self._staging = torch.frombuffer(self._mm, dtype=torch.uint8)
+        return self._staging
+
+    @property
+    def epoch(self) -> int:
+        return int(self.L.bgc_wd_epoch(self.h))
+
+    def begin_swap(self) -> int:
+        return int(self.L.bgc_wd_begin_swap(self.h))
+
+    def _json(self, fn) -> Dict:
+        import json
+        buf = ctypes.create_string_buffer(4096)
+        fn(self.h, buf, 4096)
+        return json.loads(buf.value.decode())
+
+    def finish_swap(self) -> Dict:
+        return self._json(self.L.bgc_wd_finish_swap)
+
+    def status(self) -> Dict:
+        return self._json(self.L.bgc_wd_status)
+
+    def stop(self) -> None:
+        if self.h:
+            self._staging = None
+            if getattr(self, "_mm", None) is not None:
+                try:
+                    self._mm.close()
+                except BufferError:
+                    pass
+                self._mm = None
+            self.L.bgc_wd_stop(self.h)
+            self.L.bgc_wd_destroy(self.h)
+            self.h = None
+
+
+class WeightDaemonClient:
+    """Worker side: ``acquire`` returns ("local", offset, bytes) for a module of this node's store or
+    ("staging", offset, bytes) with a lease on a staging slot; ``release`` gives the lease back."""
+
+    def __init__(self, socket_path: str, worker: int, epoch: int):
+        self.L = lib()
+        self.h = ctypes.c_void_p(self.L.bgc_wdc_create())
+        if self.L.bgc_wdc_connect(self.h, socket_path.encode()) != 0:
+            raise ConnectionError(f"no weight daemon at {socket_path}")
+        rc = self.L.bgc_wdc_hello(self.h, worker, ctypes.c_ulonglong(epoch))
+        if rc != 0:
+            raise PermissionError(f"weight daemon refused the hello: {self._error()}")
+
+    def _error(self) -> str:
+        buf = ctypes.create_string_buffer(256)
+        self.L.bgc_wdc_error(self.h, buf, 256)
+        return buf.value.decode()
+
+    def acquire(self, key: str, timeout_ms: int = 300_000) -> Tuple[str, int, int]:
+        slot, off, nb = ctypes.c_int(-1), ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+        rc = self.L.bgc_wdc_acquire(self.h, key.encode(), timeout_ms, ctypes.byref(slot), ctypes.byref(off), ctypes.byref(nb))
+        if rc == 1:
+            raise TimeoutError(f"module {key!r} was not ready within {timeout_ms} ms")
+        if rc != 0:
+            raise RuntimeError(f"acquire({key!r}) failed: {self._error()}")
+        return ("local" if slot.value < 0 else "staging"), int(off.value), int(nb.value)
+
+    def release(self, key: str) -> None:
+        rc = self.L.bgc_wdc_release(self.h, key.encode())
+        if rc not in (0, -6):
+            raise RuntimeError(f"release({key!r}) failed: {self._error()}")
+
+    def close(self) -> None:
+        if self.h:
+            self.L.bgc_wdc_close(self.h)
+            self.L.bgc_wdc_destroy(self.h)
+            self.h = None

@@ -315,3 +315,117 @@ def test_compressed_ratio_host_view_stores_one_row_per_group():
     view.release(3); view.release(4)
     assert kv.num_free == 4 and kv.audit() == 0
     view.close(); kv.close()
+
+
+def _two_daemons(tmp_path, slots=3, depth=2, n_mod=8, mod_bytes=4096):
+    """Two nodes on this host: even modules live on node 0, odd ones on node 1; the schedule visits them in order."""
+    import socket
+    ports = []
+    for _ in range(2):
+        s = socket.socket(); s.bind(("127.0.0.1", 0)); ports.append(s.getsockname()[1]); s.close()
+    keys = [f"layer{i}.experts" for i in range(n_mod)]
+    g = torch.Generator().manual_seed(0)
+    data = {k: torch.randint(0, 256, (mod_bytes,), generator=g, dtype=torch.uint8) for k in keys}
+    daemons = []
+    for node in range(2):
+        d = native.WeightDaemon(node, str(tmp_path / f"wd{node}.sock"), listen_port=ports[node],
+                                peers={1 - node: f"127.0.0.1:{ports[1 - node]}"}, staging_slots=slots,
+                                slot_bytes=mod_bytes, prefetch_depth=depth, acquire_wait_ms=50)
+        mine = [k for i, k in enumerate(keys) if i % 2 == node]
+        d.set_local_store(torch.cat([data[k] for k in mine]))
+        for i, k in enumerate(keys):
+            d.add_module(k, i % 2, (i // 2) * mod_bytes, mod_bytes)
+        d.set_schedule(keys)
+        daemons.append(d)
+    for d in daemons:
+        d.start()
+    return daemons, keys, data
+
+
+def test_weight_daemon_serves_local_and_remote_modules_with_prefetch(tmp_path):
+    daemons, keys, data = _two_daemons(tmp_path)
+    try:
+        d0 = daemons[0]
+        c = native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch)
+        staging = d0.staging()
+        for sweep in range(2):                                   # the schedule is cyclic
+            for i, k in enumerate(keys):
+                where, off, nb = c.acquire(k, timeout_ms=20_000)
+                assert nb == 4096 and where == ("local" if i % 2 == 0 else "staging")
+                src = d0._store if where == "local" else staging
+                assert torch.equal(src[off: off + nb], data[k]), k
+                c.release(k)
+        st = d0.status()
+        assert st["acquires"] == 16 and st["local"] == 8 and st["fetches"] >= 4
+        assert st["ready_hits"] >= 4                              # prefetch ran ahead of the worker
+        assert st["transport_failed"] is False and st["fetch_ms"]["count"] == st["fetches"]
+        assert daemons[1].status()["bytes_served"] == st["bytes_fetched"]
+        c.close()
+    finally:
+        for d in daemons:
+            d.stop()
+
+
+def test_weight_daemon_leases_retry_and_cohort_swap(tmp_path):
+    daemons, keys, data = _two_daemons(tmp_path, slots=2, depth=1)
+    try:
+        d0 = daemons[0]
+        with pytest.raises(PermissionError):
+            native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch + 1)      # wrong cohort epoch
+        a = native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch)
+        b = native.WeightDaemonClient(d0.socket_path, worker=1, epoch=d0.epoch)
+        assert a.acquire(keys[1], 20_000)[0] == "staging"
+        assert b.acquire(keys[3], 20_000)[0] == "staging"
+        # both slots are leased: a third remote module cannot become ready
+        with pytest.raises(TimeoutError):
+            a.acquire(keys[5], timeout_ms=300)
+        assert d0.status()["retries"] >= 1
+        b.close()                                                  # a closed connection gives its lease back
+        assert a.acquire(keys[5], 20_000)[0] == "staging"
+        with pytest.raises(RuntimeError):
+            a.acquire("no.such.module", 1000)
+        # cohort swap: the open cohort is cut off, everything is released, the next epoch is admitted
+        a2 = native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch)
+        assert a2.acquire(keys[1], 20_000)[0] == "staging"         # shares the ready slot
+        old = d0.begin_swap()
+        with pytest.raises(PermissionError):
+            native.WeightDaemonClient(d0.socket_path, worker=2, epoch=old)
+        with pytest.raises(RuntimeError):
+            a2.acquire(keys[3], 1000)
+        report = d0.finish_swap()
+        assert report["ok"] and report["epoch"] == old + 1 and report["leases_released"] >= 1
+        assert d0.status()["slots"]["leased"] == 0 and d0.status()["cursor"] == 0
+        c = native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch)
+        where, off, nb = c.acquire(keys[1], 20_000)
+        assert where == "staging" and torch.equal(d0.staging()[off: off + nb], data[keys[1]])
+        c.close(); a2.close()
+    finally:
+        for d in daemons:
+            d.stop()
+
+
+def test_weight_daemon_latches_a_transport_failure(tmp_path):
+    daemons, keys, data = _two_daemons(tmp_path)
+    try:
+        d0, d1 = daemons
+        c = native.WeightDaemonClient(d0.socket_path, worker=0, epoch=d0.epoch)
+        assert c.acquire(keys[1], 20_000)[0] == "staging"
+        c.release(keys[1])
+        d1.stop()                                                  # the owning node goes away
+        with pytest.raises((RuntimeError, TimeoutError)):
+            for k in keys[1::2] * 3:
+                c.acquire(k, 3000)
+                c.release(k)
+        for _ in range(100):
+            if d0.status()["transport_failed"]:
+                break
+            time.sleep(0.1)
+        st = d0.status()
+        assert st["transport_failed"] and "failed" in st["cohort_fault"]
+        c2 = native.WeightDaemonClient(d0.socket_path, worker=1, epoch=d0.epoch)
+        assert c2.acquire(keys[0], 1000)[0] == "local"             # local modules are still served
+        with pytest.raises(RuntimeError):
+            c2.acquire(keys[7], 1000)
+    finally:
+        for d in daemons:
+            d.stop()
