@@ -13,6 +13,9 @@ How the state is kept here:
 The compressor is written over absolute positions, so one routine serves a whole prompt, a prefill chunk that
 continues a sequence, and a decode step (a chunk of one token): pending rows of the open window come from the
 sequence's state, complete windows are pooled and written to their pages, the rest goes back to the state.
+Decode steps take a second route that handles every row of the batch in the same tensor operations and reads nothing
+back to the host (``_attention_decode``): lengths, ring rows, window closings and entry slots are all computed from
+the position tensor.
 
 Pooling of window j (ratio r, width d): softmax over the r tokens of (w_gate x_t + ape[t mod r]), per dimension,
 weights the rows w_kv x_t.  With overlapped windows (ratio 4) the projections are 2d wide: a window pools its own
@@ -245,6 +248,7 @@ class DeepSeekV4:
         self.timer = null_timer()
         self.attn_request_parallel = False
         self.streamer = None
+        self.batched_decode = True     # decode steps run all rows at once without host reads (False: row by row)
         rd = cfg.qk_rope_head_dim
         pos = torch.arange(max_positions, dtype=torch.float32)
         # compressed layers rotate with their own base and YaRN; window-only layers with the plain base
@@ -316,6 +320,91 @@ class DeepSeekV4:
             pool.view(-1, pool.shape[-1])[self._entry_slots(block_row, first, m, cw.ratio, epp, page_size)] = rows.to(pool.dtype)
         return (ctx + n) // cw.ratio
 
+    # ------------------------------------------------------------------ decode: all rows at once, no host reads
+    def _compress_step(self, cw: CompressorWeights, x, pos, slots, valid, P_kv, P_sc, pool, block_table, page_size: int):
+        """One decode token per row: park its projections in the open window, pool the rows whose window closes and
+        store their entry.  ``P_kv`` / ``P_sc`` are the state parts of every slot ([slots + 1, c r, c d]).  Rows whose
+        window stays open write a scratch value into the entry that is still in progress (nobody reads it before the
+        closing step overwrites it), and rows without a sequence use the scratch slot and the scratch page, so the
+        routine needs no row selection on the host and never writes one place from two rows."""
+        r, d = cw.ratio, cw.width
+        off = r if cw.overlap else 0
+        xf = x.float()
+        k0 = (pos % r).long()
+        row = off + k0
+        P_kv[slots, row] = xf @ cw.wkv.t()
+        P_sc[slots, row] = xf @ cw.wgate.t() + cw.ape[k0]
+        S_kv, S_sc = P_kv[slots], P_sc[slots]                                   # [B, c r, c d]
+        if cw.overlap:
+            rows = torch.cat([S_kv[:, :r, :d], S_kv[:, r:, d:]], 1)
+            gate = torch.cat([S_sc[:, :r, :d], S_sc[:, r:, d:]], 1)
+        else:
+            rows, gate = S_kv, S_sc
+        pooled = torch.nan_to_num((rows * torch.softmax(gate, dim=1)).sum(1))    # open windows may pool stale scores
+        c = (pos // r).long()
+        ent = self._rotate(self._rms(pooled.to(pool.dtype), cw.norm), c * r, True)
+        epp = pool.shape[1]
+        tok = c * r
+        page = block_table[torch.arange(len(c), device=x.device), (tok // page_size)].long()
+        page = torch.where(valid, page, torch.full_like(page, pool.shape[0] - 1))
+        pool.view(-1, pool.shape[-1])[page * epp + (tok % page_size) // r] = ent.to(pool.dtype)
+        if cw.overlap:
+            cm = (((pos + 1) % r) == 0).view(-1, 1, 1)
+            P_kv[slots, :r] = torch.where(cm, S_kv[:, r:], S_kv[:, :r])
+            P_sc[slots, :r] = torch.where(cm, S_sc[:, r:], S_sc[:, :r])
+        return (pos + 1) // r
+
+    def _attention_decode(self, l: int, lw: V4LayerWeights, x, meta: AttnMeta, cache, q, kv, qi, wi) -> torch.Tensor:
+        cfg = self.cfg
+        B, D, Hh, win = x.shape[0], cfg.head_dim, cfg.num_heads, cfg.sliding_window
+        ratio = cfg.compress_ratios[l]
+        ps = cache.page_size
+        dev = x.device
+        pos = meta.positions.long()
+        valid = meta.state_slots >= 0
+        rec = cache.state.rec[0]
+        slots = torch.where(valid, meta.state_slots, torch.full_like(meta.state_slots, rec.shape[0] - 1)).long()
+
+        def part(name):
+            off, shape = cache.state.offsets[(l, name)]
+            return rec[:, off: off + shape[0] * shape[1]].view(rec.shape[0], *shape)
+
+        R = part("ring")
+        j = (pos % win)
+        R[slots, j] = kv.float()
+        ring = R[slots]                                                          # [B, win, D]
+        jj = torch.arange(win, device=dev)
+        held = pos[:, None] - ((pos[:, None] - jj[None, :]) % win)               # position each ring row holds
+        keys, mask = ring, held >= 0
+        if ratio:
+            bt = meta.block_table
+            pool = cache.v4_comp[l]
+            E = self._compress_step(lw.comp, x, pos, slots, valid, part("kv"), part("score"), pool, bt, ps)
+            Emax = max(1, bt.shape[1] * ps // ratio)
+            c = torch.arange(Emax, device=dev)
+            tok = c * ratio
+            col = (tok // ps).clamp_max(bt.shape[1] - 1)
+            flat = bt[:, col].long() * pool.shape[1] + ((tok % ps) // ratio)[None, :]
+            ent = pool.view(-1, D)[flat].float()                                 # [B, Emax, D]
+            visible = c[None, :] < E[:, None]
+            if lw.idx_comp is not None:
+                ipool = cache.v4_idx[l]
+                self._compress_step(lw.idx_comp, x, pos, slots, valid, part("idx_kv"), part("idx_score"), ipool, bt, ps)
+                if Emax > cfg.index_topk:
+                    ik = ipool.view(-1, ipool.shape[-1])[flat].float()
+                    sc = (torch.relu(torch.einsum("bhd,bed->bhe", qi, ik)) * wi.unsqueeze(-1)).sum(1)
+                    sc = sc.masked_fill(~visible, float("-inf"))
+                    top = sc.topk(cfg.index_topk, dim=-1)[1]
+                    visible = visible & torch.zeros_like(visible).scatter_(1, top, True)
+            keys = torch.cat([keys, ent], 1)
+            mask = torch.cat([mask, visible], 1)
+        s = torch.einsum("bhd,bkd->bhk", q, keys) * D ** -0.5
+        s = s.masked_fill(~mask.unsqueeze(1), float("-inf"))
+        sink = lw.sink.view(1, Hh, 1).expand(B, Hh, 1)
+        p = torch.softmax(torch.cat([s, sink], -1), -1)[..., :-1]
+        out = torch.einsum("bhk,bkd->bhd", p, keys)
+        return torch.where(valid.view(-1, 1, 1), out, torch.zeros_like(out))
+
     # ------------------------------------------------------------------ attention
     def _attention(self, l: int, lw: V4LayerWeights, x, meta: AttnMeta, cache) -> torch.Tensor:
         cfg = self.cfg
@@ -333,6 +422,10 @@ class DeepSeekV4:
             Hi, Di = cfg.index_n_heads, cfg.index_head_dim
             qi = self._rotate(linear(qr, lw.idx_wq).view(T, Hi, Di).float(), meta.positions, True)
             wi = (x.float() @ lw.idx_wproj.float().t()) * (Di ** -0.5 * Hi ** -0.5)                 # [T, Hi]
+        if meta.mode == "decode" and self.batched_decode:
+            out = self._attention_decode(l, lw, x, meta, cache, q, kv, qi if lw.idx_wq is not None else None,
+                                         wi if lw.idx_wq is not None else None)
+            return self._project_out(lw, out, meta, compressed)
         out = torch.zeros(T, Hh, D, dtype=torch.float32, device=x.device)
         slots = meta.state_slots.tolist()
         ps = cache.page_size
@@ -381,7 +474,13 @@ class DeepSeekV4:
             sink = lw.sink.view(Hh, 1, 1).expand(Hh, n, 1)
             p = torch.softmax(torch.cat([s, sink], -1), -1)[..., :-1]
             out[a:b] = torch.einsum("hnk,kd->nhd", p, keys)
-        o = self._rotate(out, meta.positions, compressed, inverse=True).to(x.dtype)
+        return self._project_out(lw, out, meta, compressed)
+
+    def _project_out(self, lw: V4LayerWeights, out, meta: AttnMeta, compressed: bool) -> torch.Tensor:
+        """Rotate the rope dims of the attention output back, then the grouped low-rank output projection."""
+        cfg = self.cfg
+        T, Hh, D = out.shape
+        o = self._rotate(out, meta.positions, compressed, inverse=True).to(self.dtype)
         G = cfg.o_groups
         og = o.reshape(T, G, Hh // G * D)
         low = torch.cat([linear(og[:, g].contiguous(), lw.wo_a[g]) for g in range(G)], -1)

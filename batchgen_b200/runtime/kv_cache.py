@@ -122,9 +122,10 @@ class PagedKVCache:
         for l, r in enumerate(cfg.compress_ratios):
             if r:
                 epp = v4_entries_per_page(r, page_size)
-                self.v4_comp[l] = torch.zeros(num_pages, epp, cfg.head_dim, dtype=dtype, device=self.device, pin_memory=pin)
+                # one page more than the allocator hands out: rows without a sequence (padding) write there
+                self.v4_comp[l] = torch.zeros(num_pages + 1, epp, cfg.head_dim, dtype=dtype, device=self.device, pin_memory=pin)
                 if r == 4:
-                    self.v4_idx[l] = torch.zeros(num_pages, epp, cfg.index_head_dim, dtype=dtype, device=self.device,
+                    self.v4_idx[l] = torch.zeros(num_pages + 1, epp, cfg.index_head_dim, dtype=dtype, device=self.device,
                                                  pin_memory=pin)
         self.alloc = PageAllocator(num_pages)
         # per-sequence state (device tier only): recurrent state of the KDA layers, or the window rings and
@@ -252,8 +253,9 @@ class V4StatePool:
                 self.offsets[(l, name)] = (n, shape)
                 n += shape[0] * shape[1]
         assert n == cfg.v4_state_floats_per_seq()
-        self.rec = torch.zeros(1, num_slots, n, dtype=torch.float32, device=device)
-        self.conv = torch.zeros(1, num_slots, 1, dtype=torch.float32, device=device)
+        # row ``num_slots`` is scratch: decode rows without a sequence park their writes there
+        self.rec = torch.zeros(1, num_slots + 1, n, dtype=torch.float32, device=device)
+        self.conv = torch.zeros(1, num_slots + 1, 1, dtype=torch.float32, device=device)
         self._free = list(range(num_slots - 1, -1, -1))
 
     @property

@@ -146,3 +146,43 @@ def test_full_size_presets_describe_the_published_models():
     assert len(pro.compress_ratios) == pro.num_layers == 61 and pro.compress_ratios[:3] == (128, 128, 4)
     assert 2.7e11 < flash.param_count() < 3.0e11 and 1.5e12 < pro.param_count() < 1.7e12
     assert flash.kv_bytes_per_token() < 8000                 # pooled entries only: a tenth of a DeepSeek-V3 row
+
+
+def test_batched_decode_equals_row_by_row_decode():
+    """The decode step that handles all rows at once (no host reads: open windows write a scratch entry, closing
+    windows overwrite it) gives the tokens of the row-by-row routine that the prefill chunks use."""
+    cfg = get_model_config("tiny-deepseek-v4")
+    prompts = [_ids(cfg, n, seed=40 + n) for n in (5, 17, 30, 3)]
+    params = SamplingParams(max_new_tokens=20, ignore_eos=True)
+    outs = []
+    for batched in (True, False):
+        eng = _engine(cfg)
+        eng.model.batched_decode = batched
+        outs.append(eng.generate(prompts, params))
+    assert outs[0] == outs[1]
+
+
+def test_decode_rows_without_a_sequence_touch_nothing():
+    cfg = get_model_config("tiny-deepseek-v4")
+    model = build_model(cfg, seed=0)
+
+    def run(pad):
+        kv = PagedKVCache(cfg, 8, 16, "cpu", torch.float32, state_slots=3)
+        pages = [kv.alloc.alloc(2), kv.alloc.alloc(2)]
+        slots = [kv.state.acquire(), kv.state.acquire()]
+        lens = [15, 7]                                          # the first row's next token closes windows of 4 and 8
+        for i, n in enumerate(lens):
+            _forward_chunks(model, kv, _ids(cfg, n, seed=50 + i), [n], pages[i], slots[i])
+        rows = [(0, 11), (1, 13)] + ([(-1, 0)] * pad)
+        bt = build_block_table([pages[i] if i >= 0 else [0, 0] for i, _ in rows], "cpu")
+        meta = AttnMeta(mode="decode", positions=torch.tensor([lens[i] if i >= 0 else 0 for i, _ in rows], dtype=torch.int32),
+                        slot_mapping=torch.tensor([slots_for_range(pages[i], lens[i], lens[i] + 1, 16)[0] if i >= 0 else -1
+                                                   for i, _ in rows]),
+                        block_table=bt, seqlens=torch.tensor([lens[i] + 1 if i >= 0 else 1 for i, _ in rows], dtype=torch.int32),
+                        state_slots=torch.tensor([slots[i] if i >= 0 else -1 for i, _ in rows], dtype=torch.int32))
+        out = model.forward(torch.tensor([t for _, t in rows], dtype=torch.int32), meta, kv)
+        return out[:2], kv.v4_comp[1][: kv.num_pages].clone(), kv.state.rec[0, :3].clone()
+
+    a, b = run(0), run(2)
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, atol=1e-6)
