@@ -70,9 +70,6 @@ class CaptureLedger:
 class DecodeGraphRunner:
     def __init__(self, model: Transformer, kv: PagedKVCache, max_batch: int, max_pages_per_seq: int,
                  num_buckets: int = 16, max_bucket: Optional[int] = None, sequence_parallel: bool = False):
-        if model.cfg.is_v4:
-            raise NotImplementedError("DeepSeek-V4 decode reads sequence lengths on the host (window and compressor "
-                                      "bookkeeping): it runs eagerly, without captured graphs")
         self.model, self.kv = model, kv
         self.dev = model.device
         self.sp = sequence_parallel
@@ -90,8 +87,10 @@ class DecodeGraphRunner:
         self.lens = torch.zeros(B, dtype=torch.int32, device=d)
         self.bt = torch.zeros(B, max_pages_per_seq, dtype=torch.int32, device=d)
         self.num_valid = torch.zeros(1, dtype=torch.int32, device=d)
-        # KDA state slot of each row (-1 = padding row: the kernel skips it, so warm-up and capture touch no state)
-        self.state_slots = torch.full((B,), -1, dtype=torch.int32, device=d) if model.cfg.has_kda else None
+        # state slot of each row (KDA recurrent state, or DeepSeek-V4 window / compressor state); -1 = padding row: it
+        # is skipped or lands in a scratch slot, so warm-up and capture touch no sequence's state
+        self.state_slots = (torch.full((B,), -1, dtype=torch.int32, device=d)
+                            if (model.cfg.has_kda or model.cfg.is_v4) else None)
         pin = torch.cuda.is_available()
         self.h_state = torch.full((B,), -1, dtype=torch.int32, pin_memory=pin)
         self.h_ids = torch.zeros(B, dtype=torch.int32, pin_memory=pin)

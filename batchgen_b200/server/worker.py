@@ -128,7 +128,7 @@ def build_engine(args, rank: int, world: int, device: str, phases=None, phase_sl
     if getattr(args, "host_kv_region", "") and device.startswith("cuda"):
         host_fd = os.open(args.host_kv_region, os.O_RDWR)      # the server's region: same pages for every worker
     eng = Engine(model, ecfg, num_gpu_pages=pages, num_host_pages=host_pages, host_kv_fd=host_fd)
-    if device.startswith("cuda") and ecfg.enable_cuda_graph and not cfg.is_v4:      # DeepSeek-V4 decodes eagerly
+    if device.startswith("cuda") and ecfg.enable_cuda_graph:
         if phases is not None:
             phases.enter(phase_slot, "graph-capture")
         from ..runtime.graphs import DecodeGraphRunner

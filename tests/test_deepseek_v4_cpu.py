@@ -130,14 +130,10 @@ def test_parked_sequences_move_window_and_compressor_state_to_host_and_back():
     assert eng.kv.state.num_free == 5 and eng.host_state.num_free == eng.host_state.num_items
 
 
-def test_prefix_cache_and_graphs_are_refused():
+def test_prefix_cache_is_refused():
     cfg = get_model_config("tiny-deepseek-v4")
     with pytest.raises(ValueError):
         _engine(cfg, enable_prefix_cache=True)
-    from batchgen_b200.runtime.graphs import DecodeGraphRunner
-    eng = _engine(cfg)
-    with pytest.raises(NotImplementedError):
-        DecodeGraphRunner(eng.model, eng.kv, max_batch=4, max_pages_per_seq=4)
 
 
 def test_full_size_presets_describe_the_published_models():
