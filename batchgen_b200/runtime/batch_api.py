@@ -135,9 +135,15 @@ def result_item(seq: Sequence, req: BatchRequest, tokenizer, opts: BatchOptions)
              "prompt_tokens_details": {"cached_tokens": seq.cached_prefix_tokens}}
     if req.url == "/v1/chat/completions":
         reasoning, content, tool_calls = None, text, None
-        if opts.parse_thinking:
+        if hasattr(tokenizer, "parse_completion") and (opts.parse_thinking or opts.parse_tool_call):
+            # the family's own completion format (DeepSeek-V4: reasoning up to </think>, DSML tool calls)
+            parsed = tokenizer.parse_completion(text, enable_thinking=bool(req.body.get("enable_thinking", True)))
+            reasoning = (parsed["reasoning_content"] or None) if opts.parse_thinking else None
+            content = parsed["content"] if opts.parse_thinking else text
+            tool_calls = parsed["tool_calls"] if opts.parse_tool_call else None
+        elif opts.parse_thinking:
             reasoning, content = split_reasoning(text)
-        if opts.parse_tool_call:
+        if opts.parse_tool_call and not hasattr(tokenizer, "parse_completion"):
             tool_calls, content = parse_tool_calls(content)
         msg = {"role": "assistant", "content": content, "reasoning_content": reasoning,
                "tool_calls": tool_calls or None}

@@ -101,14 +101,60 @@ def render_fallback_template(messages: List[Dict], add_generation_prompt: bool =
     return "".join(parts)
 
 
-def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1):
+class DeepSeekV4Chat:
+    """A tokenizer whose chat rendering and completion parsing follow the DeepSeek-V4 format (``runtime.dsv4_encoding``:
+    the family ships no Jinja template).  ``enable_thinking`` selects thinking or chat mode, ``tools`` are attached to
+    the system message (one is created when the conversation has none)."""
+
+    def __init__(self, base):
+        self.base = base
+        self.name = f"{getattr(base, 'name', 'tokenizer')}+deepseek_v4"
+        self.vocab_size, self.bos_token_id, self.eos_token_id = base.vocab_size, base.bos_token_id, base.eos_token_id
+
+    def encode(self, text):
+        return self.base.encode(text)
+
+    def decode(self, ids, skip_special_tokens: bool = True):
+        return self.base.decode(ids, skip_special_tokens=skip_special_tokens)
+
+    def render(self, messages: List[Dict], enable_thinking: bool = True, reasoning_effort: Optional[str] = None,
+               tools: Optional[List[Dict]] = None) -> str:
+        from . import dsv4_encoding
+        msgs = [dict(m) for m in messages]
+        if tools:
+            holder = next((m for m in msgs if m.get("role") in ("system", "developer")), None)
+            if holder is None:
+                holder = {"role": "system", "content": ""}
+                msgs.insert(0, holder)
+            holder["tools"] = list(tools)
+        return dsv4_encoding.encode_messages(msgs, "thinking" if enable_thinking else "chat",
+                                             reasoning_effort=reasoning_effort)
+
+    def apply_chat_template(self, messages: List[Dict], add_generation_prompt: bool = True, enable_thinking: bool = True,
+                            reasoning_effort: Optional[str] = None, tools: Optional[List[Dict]] = None, **kw) -> List[int]:
+        self._thinking = bool(enable_thinking)
+        return self.encode(self.render(messages, enable_thinking, reasoning_effort, tools))
+
+    def parse_completion(self, text: str, enable_thinking: bool = True) -> Dict:
+        from . import dsv4_encoding
+        return dsv4_encoding.parse_completion(text, "thinking" if enable_thinking else "chat")
+
+
+def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1, chat_format: Optional[str] = None):
+    """``chat_format="deepseek_v4"`` wraps the tokenizer so that chat requests use that family's prompt format."""
     if spec in ("ids", "", None):
-        return IdTokenizer(vocab_size, bos, eos)
-    if spec == "bytes":
-        return ByteTokenizer(vocab_size, bos, eos)
-    if os.path.isdir(spec):
-        return HFTokenizer(spec)
-    raise ValueError(f"unknown tokenizer {spec!r}: use 'ids', 'bytes' or a local tokenizer directory")
+        tok = IdTokenizer(vocab_size, bos, eos)
+    elif spec == "bytes":
+        tok = ByteTokenizer(vocab_size, bos, eos)
+    elif os.path.isdir(spec):
+        tok = HFTokenizer(spec)
+    else:
+        raise ValueError(f"unknown tokenizer {spec!r}: use 'ids', 'bytes' or a local tokenizer directory")
+    if chat_format == "deepseek_v4" and not isinstance(tok, IdTokenizer):
+        return DeepSeekV4Chat(tok)
+    if chat_format not in (None, "", "deepseek_v4"):
+        raise ValueError(f"unknown chat format {chat_format!r}")
+    return tok
 
 
 _THINK = re.compile(r"<think>(.*?)</think>", re.S)

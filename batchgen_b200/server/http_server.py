@@ -81,7 +81,8 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
     cfg = get_model_config(args.model)
     storage = StorageManager(args.storage_path)
     worker = worker or WorkerManager(args)
-    tokenizer = get_tokenizer(args.tokenizer, cfg.vocab_size, cfg.bos_token_id, cfg.eos_token_id)
+    tokenizer = get_tokenizer(args.tokenizer, cfg.vocab_size, cfg.bos_token_id, cfg.eos_token_id,
+                              chat_format="deepseek_v4" if cfg.family == "deepseek_v4" else None)
     scheduler = BatchScheduler(storage, worker, args, tokenizer)
     health = ServerHealthState()
     sessions = SessionStore()
