@@ -166,7 +166,7 @@ class DecodeGraphRunner:
         count (rows x head groups x splits) is not monotone in the batch size, and a captured launch keeps the
         addresses it was given.  Returns the largest slot count (0 when the model has no such kernel)."""
         cfg = self.model.cfg
-        if not cfg.is_mla or torch.device(self.dev).type != "cuda" or self._scratch_reserved:
+        if not cfg.is_mla or cfg.is_v4 or torch.device(self.dev).type != "cuda" or self._scratch_reserved:
             return 0
         from ..ops import _ext, mla_kernel
         W = self.model.layout.tp_size

@@ -136,6 +136,9 @@ def run_longctx(args) -> int:
     if args.layers:
         cfg.num_layers = args.layers
         cfg.indexer_full_layers = tuple(l for l in cfg.indexer_full_layers if l < args.layers)
+        cfg.compress_ratios = tuple(cfg.compress_ratios[: args.layers])
+    if args.experts:
+        cfg.n_routed_experts = args.experts
     page, L, N, R = 64, args.ctx_tokens, args.bct_tokens, args.requests
     grouped = args.workload == "grouped64k"
     groups = max(1, R // 8) if grouped else R
@@ -165,7 +168,7 @@ def run_longctx(args) -> int:
     torch.cuda.synchronize()
     build_s = time.time() - t0
     ecfg = EngineConfig(page_size=page, max_decode_batch=max(R, 8), max_prefill_tokens=args.prefill_tokens,
-                        enable_cuda_graph=False, enable_prefix_cache=True, initial_gpu_page_buffer=N // page + 2,
+                        enable_cuda_graph=False, enable_prefix_cache=not cfg.is_v4, initial_gpu_page_buffer=N // page + 2,
                         extension_gpu_page_buffer=2, decision_frequency_pages=2, world_size=world,
                         attn_tp_size=world, ep_size=world, device=str(dev), dtype="bf16", moe_comm="nccl")
     eng = Engine(model, ecfg, num_gpu_pages=total_pages)
@@ -214,7 +217,8 @@ def run_longctx(args) -> int:
                        "completed": ok, "ctx_tokens": L, "forced_tokens": N, "prefix_groups": groups if grouped else 0,
                        "parallelism": f"tp{world}+ep{world}", "comm": "nccl" if world > 1 else "none",
                        "prefill_piece_tokens": args.prefill_tokens, "index_topk": cfg.index_topk, "decode": graph_note,
-                       "distinct_expert_sets": sets, "full_size_workload": full, "valid": not args.layers,
+                       "distinct_expert_sets": sets, "full_size_workload": full,
+                       "valid": not args.layers and not args.experts, "experts": cfg.n_routed_experts,
                        "api": "runtime.batch_api.run_batch on Engine", "build_seconds": round(build_s, 1)},
             "prefill_tok_per_s": st["prefill_tok_per_s"], "decode_tok_per_s": st["decode_tok_per_s"],
             "prefill_tokens": st["prefill_tokens"], "shared_prefix_tokens": st["shared_prefix_tokens"],
