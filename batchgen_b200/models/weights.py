@@ -91,7 +91,7 @@ class WeightSource:
         g = torch.Generator(device=self.gen_device)
         g.manual_seed(_seed_for(self.seed, name))
         t = torch.randn(shape, dtype=torch.float32, device=self.gen_device, generator=g).to(self.device)
-        if kind == "norm":            # norm gains around 1
+        if kind == "norm":            # norm gains close to one
             return 1.0 + 0.1 * t
         if kind == "bias":
             return 0.1 * t

@@ -7,7 +7,9 @@ import pytest
 
 from batchgen_b200.runtime import dsv4_encoding as enc
 
-GOLD = "/root/reference/batchgen/models/deepseek/deepseekv4_flash/assets/encoding/tests"
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(os.path.dirname(_REPO), "reference", "batchgen", "models", "deepseek", "deepseekv4_flash", "assets",
+                    "encoding", "tests")          # a checkout of the reference beside this repository, when there is one
 needs_gold = pytest.mark.skipif(not os.path.isdir(GOLD), reason="golden prompt files not present")
 
 
