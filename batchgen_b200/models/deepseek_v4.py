@@ -249,6 +249,8 @@ class DeepSeekV4:
         self.attn_request_parallel = False
         self.streamer = None
         self.batched_decode = True     # decode steps run all rows at once without host reads (False: row by row)
+        self.kernel_decode = True      # 512-wide heads on the GPU: the decode core runs on the absorbed-MLA kernel
+        self.kernel_math_anywhere = False   # tests: take that route on any device / geometry (reference MLA math)
         rd = cfg.qk_rope_head_dim
         pos = torch.arange(max_positions, dtype=torch.float32)
         # compressed layers rotate with their own base and YaRN; window-only layers with the plain base
@@ -398,12 +400,44 @@ class DeepSeekV4:
                     visible = visible & torch.zeros_like(visible).scatter_(1, top, True)
             keys = torch.cat([keys, ent], 1)
             mask = torch.cat([mask, visible], 1)
-        s = torch.einsum("bhd,bkd->bhk", q, keys) * D ** -0.5
-        s = s.masked_fill(~mask.unsqueeze(1), float("-inf"))
-        sink = lw.sink.view(1, Hh, 1).expand(B, Hh, 1)
-        p = torch.softmax(torch.cat([s, sink], -1), -1)[..., :-1]
-        out = torch.einsum("bhk,bkd->bhd", p, keys)
+        if self.kernel_decode and (self.kernel_math_anywhere or (x.is_cuda and D == 512 and self.dtype == torch.bfloat16
+                                                                and Hh % 8 == 0)):
+            out = self._decode_core_on_mla_kernel(q, keys, mask, lw.sink)
+        else:
+            s = torch.einsum("bhd,bkd->bhk", q, keys) * D ** -0.5
+            s = s.masked_fill(~mask.unsqueeze(1), float("-inf"))
+            sink = lw.sink.view(1, Hh, 1).expand(B, Hh, 1)
+            p = torch.softmax(torch.cat([s, sink], -1), -1)[..., :-1]
+            out = torch.einsum("bhk,bkd->bhd", p, keys)
         return torch.where(valid.view(-1, 1, 1), out, torch.zeros_like(out))
+
+    def _decode_core_on_mla_kernel(self, q, keys, mask, sink) -> torch.Tensor:
+        """The decode attention core on the absorbed-MLA decode kernel (tcgen05, 512-wide latent rows with 64 extra
+        score-only columns).  K = V = the gathered rows; the 64 extra columns, which carry the rotary part for MLA
+        models, carry flags here: column 0 is 1 on one appended row whose value part is zero and whose score is the
+        head's sink logit (the query's column 0 holds sink / scale), so the sink joins the softmax denominator only;
+        column 1 holds a large negative number on masked rows (ring rows not written yet, entries that are not visible
+        or not selected), and the query's column 1 is 1, so those rows get zero weight.  Every row of the batch then has
+        the same length and nothing is compacted."""
+        from ..ops import attention as attn_ops
+        B, Hh, D = q.shape
+        dev = q.device
+        dt = self.dtype
+        Kk = keys.shape[1]
+        page = 64
+        K = (Kk + 1 + page - 1) // page * page
+        scale = D ** -0.5
+        dense = torch.zeros(B, K, D + 64, dtype=dt, device=dev)
+        dense[:, :Kk, :D] = torch.where(mask.unsqueeze(-1), keys, torch.zeros_like(keys)).to(dt)
+        dense[:, :Kk, D + 1] = torch.where(mask, 0.0, -30000.0 / scale).to(dt)
+        dense[:, Kk, D] = 1.0
+        q_pe = torch.zeros(B, Hh, 64, dtype=dt, device=dev)
+        q_pe[:, :, 0] = (sink / scale).to(dt)
+        q_pe[:, :, 1] = 1.0
+        lens = torch.full((B,), Kk + 1, dtype=torch.int32, device=dev)
+        bt = torch.arange(B * (K // page), dtype=torch.int32, device=dev).view(B, K // page)
+        out = attn_ops.mla_decode(q.to(dt).contiguous(), q_pe, dense.view(B * (K // page), page, D + 64), bt, lens, scale, D)
+        return out.float()
 
     # ------------------------------------------------------------------ attention
     def _attention(self, l: int, lw: V4LayerWeights, x, meta: AttnMeta, cache) -> torch.Tensor:

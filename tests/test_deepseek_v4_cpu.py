@@ -182,3 +182,17 @@ def test_decode_rows_without_a_sequence_touch_nothing():
     a, b = run(0), run(2)
     for x, y in zip(a, b):
         assert torch.allclose(x, y, atol=1e-6)
+
+
+def test_decode_core_through_the_mla_decode_routine_matches_the_plain_softmax():
+    """The decode core expressed for the absorbed-MLA decode kernel (sink as an appended row scored through a flag
+    column, masked rows pushed out through a second flag column) gives the tokens of the plain masked softmax."""
+    cfg = get_model_config("tiny-deepseek-v4")
+    prompts = [_ids(cfg, n, seed=60 + n) for n in (5, 17, 30, 3)]
+    params = SamplingParams(max_new_tokens=20, ignore_eos=True)
+    outs = []
+    for route in (False, True):
+        eng = _engine(cfg)
+        eng.model.kernel_math_anywhere = route
+        outs.append(eng.generate(prompts, params))
+    assert outs[0] == outs[1]
