@@ -116,7 +116,7 @@ def model_contract(cfg, world: int, on_gpu: bool, moe_comm: str = "nccl") -> Lis
         if world > 1:
             notes.append("DeepSeek-V4: attention replicated per engine, experts expert-parallel; use --dp-size for "
                          "data-parallel cohorts")
-        notes.append("DeepSeek-V4 attention core and compressor run as torch ops (decode steps are captured like any other); projections, "
+        notes.append("DeepSeek-V4: decode attention core on the MLA decode kernel (512-wide heads), prefill core and compressor as torch ops; projections, "
                      "router and experts run on the kernels")
     elif cfg.is_mla:
         if cfg.kv_lora_rank != 512 or cfg.qk_rope_head_dim != 64:
