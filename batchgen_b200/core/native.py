@@ -712,3 +712,32 @@ class WeightDaemonClient:
             self.L.bgc_wdc_close(self.h)
             self.L.bgc_wdc_destroy(self.h)
             self.h = None
+
+
+class DistributedModuleSource:
+    """Worker-side view of a weight store that is spread over nodes: a module is read straight from this node's local
+    store when it lives here, otherwise through a lease on the node daemon's staging region (``WeightDaemonClient``).
+    ``module(key)`` returns a uint8 tensor view plus a release callable; the view is valid until released.
+
+    Reference parity: core/Weights_Storage/Weights_Storage.h:70-178 (distributed mode: node daemon socket + leases)."""
+
+    def __init__(self, local_store: torch.Tensor, staging: torch.Tensor, client: "WeightDaemonClient"):
+        assert local_store.dtype == torch.uint8 and staging.dtype == torch.uint8
+        self.local, self.staging, self.client = local_store, staging, client
+        self.local_reads = self.remote_reads = 0
+
+    def module(self, key: str, timeout_ms: int = 300_000):
+        where, off, nb = self.client.acquire(key, timeout_ms)
+        if where == "local":
+            self.local_reads += 1
+            return self.local[off: off + nb], (lambda: None)
+        self.remote_reads += 1
+        return self.staging[off: off + nb], (lambda: self.client.release(key))
+
+    def tensor(self, key: str, dtype: torch.dtype, shape: Sequence[int], timeout_ms: int = 300_000) -> torch.Tensor:
+        """A private copy of the module as a typed tensor (the lease is given back before returning)."""
+        view, release = self.module(key, timeout_ms)
+        try:
+            return view.clone().view(dtype).view(*shape)
+        finally:
+            release()

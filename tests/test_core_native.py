@@ -429,3 +429,20 @@ def test_weight_daemon_latches_a_transport_failure(tmp_path):
     finally:
         for d in daemons:
             d.stop()
+
+
+def test_distributed_module_source_reads_local_and_remote_modules(tmp_path):
+    daemons, keys, data = _two_daemons(tmp_path)
+    try:
+        d1 = daemons[1]
+        client = native.WeightDaemonClient(d1.socket_path, worker=0, epoch=d1.epoch)
+        src = native.DistributedModuleSource(d1._store, d1.staging(), client)
+        for k in keys:
+            t = src.tensor(k, torch.int16, (2048,))
+            assert torch.equal(t.view(torch.uint8), data[k]), k
+        assert src.local_reads == 4 and src.remote_reads == 4
+        assert d1.status()["slots"]["leased"] == 0               # every lease went back
+        client.close()
+    finally:
+        for d in daemons:
+            d.stop()
