@@ -196,3 +196,22 @@ def test_decode_core_through_the_mla_decode_routine_matches_the_plain_softmax():
         eng.model.kernel_math_anywhere = route
         outs.append(eng.generate(prompts, params))
     assert outs[0] == outs[1]
+
+
+def test_ratio_larger_than_the_page_places_one_entry_every_few_pages():
+    """Compression ratio 32 with 16-token pages: entry c sits in page 2c of the sequence (slot 0); whole-prompt, chunked
+    and decode paths agree with the textbook model."""
+    cfg = get_model_config("tiny-deepseek-v4", compress_ratios=(32, 4), num_layers=2, num_hash_layers=0)
+    model = build_model(cfg, seed=0)
+    ids = _ids(cfg, 100, seed=70)
+    want = NaiveV4(cfg, WeightSource(seed=0)).logits(ids)
+    kv = PagedKVCache(cfg, 16, 16, "cpu", torch.float32, state_slots=2)
+    got = _forward_chunks(model, kv, ids, [100], kv.alloc.alloc(7), kv.state.acquire())
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-3), (got - want).abs().max()
+    kv2 = PagedKVCache(cfg, 16, 16, "cpu", torch.float32, state_slots=2)
+    parts = _forward_chunks(model, kv2, ids, [31, 32, 33, 64, 95, 96, 100], list(reversed(kv2.alloc.alloc(7))), kv2.state.acquire())
+    assert torch.allclose(parts, want, atol=1e-4, rtol=1e-3), (parts - want).abs().max()
+    eng = _engine(cfg)
+    prompt = ids[:60]
+    got_tokens = eng.generate([prompt], SamplingParams(max_new_tokens=10, ignore_eos=True))[0]
+    assert got_tokens == NaiveV4(cfg, WeightSource(seed=0)).generate(prompt, 10)
