@@ -189,10 +189,14 @@ bool WeightDaemon::start() {
 }
 
 void WeightDaemon::stop() {
-  if (!started_) {
+  if (!started_) {                       // start() gave up half way: give back what it had opened
     if (listen_unix_ >= 0) ::close(listen_unix_);
     if (listen_tcp_ >= 0) ::close(listen_tcp_);
     listen_unix_ = listen_tcp_ = -1;
+    if (staging_ != nullptr) ::munmap(staging_, staging_bytes());
+    if (staging_fd_ >= 0) ::close(staging_fd_);
+    staging_ = nullptr;
+    staging_fd_ = -1;
     return;
   }
   stop_ = true;
