@@ -40,7 +40,7 @@ model definition the reference vendors beside it (assets/inference/model.py: Com
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.nn.functional as F

@@ -9,7 +9,6 @@ batchgen/models/deepseek/deepseekv4_flash/assets/inference/model.py.)
 """
 from __future__ import annotations
 
-import math
 from typing import List
 
 import torch
