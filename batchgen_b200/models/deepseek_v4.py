@@ -153,8 +153,13 @@ def build_v4_weights(cfg: ModelConfig, layout: ParallelLayout, src: WeightSource
         E, I, K = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.num_experts_per_tok
         lw.router_w = src.get(f"{f}.gate.weight", (E, H)).float()
         if l < cfg.num_hash_layers:
-            # a fixed table token id -> its K experts (distinct per token)
-            lw.tid2eid = src.get(f"{f}.gate.tid2eid", (cfg.vocab_size, E)).topk(K, dim=-1)[1]
+            # a fixed table token id -> its K experts (distinct per token): read from the checkpoint when a loader
+            # has it ([vocab, K] integers), otherwise drawn from the seeded source
+            table = src.loader(f"{f}.gate.tid2eid", (cfg.vocab_size, K)) if src.loader is not None else None
+            if table is not None:
+                lw.tid2eid = table.to(src.device, torch.int64)
+            else:
+                lw.tid2eid = src.get(f"{f}.gate.tid2eid", (cfg.vocab_size, E)).topk(K, dim=-1)[1]
         else:
             lw.router_bias = src.get(f"{f}.gate.bias", (E,), "bias").float()
         e0, e1 = layout.expert_range(E)
