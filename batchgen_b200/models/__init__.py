@@ -20,6 +20,9 @@ def build_model(cfg: ModelConfig, device="cpu", dtype="fp32", seed: int = 0, lay
     get_initializer / get_parallel_strategy_manager (batchgen/get_initializer.py:19-46)."""
     dt = _DTYPES[dtype] if isinstance(dtype, str) else dtype
     layout = layout or ParallelLayout()
+    if loader is not None:
+        from .checkpoint_names import aliased_loader
+        loader = aliased_loader(cfg, loader)            # published names of the family, when they differ
     src = WeightSource(seed=seed, device=device, loader=loader, gen_device=gen_device)
     if cfg.is_v4:
         from .deepseek_v4 import DeepSeekV4, build_v4_weights

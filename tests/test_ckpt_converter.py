@@ -57,3 +57,36 @@ def test_model_from_converted_checkpoint_generates_same_tokens(tmp_path):
     a = Engine(build_model(cfg, seed=3), ecfg, num_gpu_pages=32).generate(prompts, params)
     b = Engine(build_model(cfg, seed=999, loader=ck.loader()), ecfg, num_gpu_pages=32).generate(prompts, params)
     assert a == b
+
+
+def test_published_tensor_names_of_mixtral_and_qwen2_moe_are_found():
+    """A checkpoint that uses the families' own names (Mixtral: block_sparse_moe.experts.N.w1/w2/w3 and
+    block_sparse_moe.gate; Qwen2-MoE: mlp.shared_expert.*) loads into the same model as the builder's names."""
+    import torch
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.models.checkpoint_names import candidates
+    from batchgen_b200.models.weights import WeightSource, checkpoint_tensor_specs
+    for preset in ("tiny-mixtral", "tiny-qwen2-moe"):
+        cfg = get_model_config(preset)
+        seeded = WeightSource(seed=3)
+        published = {}
+        renamed = 0
+        for name, shape, kind, _ in checkpoint_tensor_specs(cfg):
+            alts = candidates(cfg, name)
+            renamed += bool(alts)
+            published[alts[0] if alts else name] = seeded.get(name, shape, kind)
+        assert renamed > 0
+        looked_up = []
+
+        def loader(name, shape):
+            looked_up.append(name)
+            return published.get(name)
+
+        a = build_model(cfg, seed=3)
+        b = build_model(cfg, seed=99, loader=loader)          # another seed: every tensor must come from the loader
+        for la, lb in zip(a.w.layers, b.w.layers):
+            assert torch.equal(la.experts.w13, lb.experts.w13) and torch.equal(la.router_w, lb.router_w)
+            if la.w13 is not None:
+                assert torch.equal(la.w13.w, lb.w13.w)
+        assert torch.equal(a.w.embed, b.w.embed)
