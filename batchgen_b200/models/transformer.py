@@ -519,6 +519,8 @@ class Transformer:
     @staticmethod
     def supports_sequence_parallel(cfg: ModelConfig) -> Optional[str]:
         """``None`` when ``forward_sp`` (fused NVLink kernels) can run ``cfg``, otherwise the reason it cannot."""
+        if cfg.is_v4:
+            return "DeepSeek-V4 attention is replicated inside an engine; its experts use the collective baseline"
         if not cfg.is_mla:
             return "GQA attention runs tensor-parallel through forward() and the collective baseline"
         if cfg.has_kda:
