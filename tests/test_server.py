@@ -276,16 +276,23 @@ def test_data_parallel_cohorts_share_the_batch(tmp_path):
 
 
 def test_deepseek_v4_model_serves_chat_batches_in_its_own_format(tmp_path):
-    """The server with a DeepSeek-V4 model on a CPU worker: state slots for window / compressor state, prefix cache
-    off, prompts rendered in the family's chat format (byte tokenizer), a batch completes."""
-    app = create_app(_args(tmp_path, model="tiny-deepseek-v4", enable_prefix_cache=False))
-    with TestClient(app) as c:
-        assert c.get("/health").status_code == 200, c.get("/health").text
-        f = _upload(c, _lines(5, max_tokens=6))
-        r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
-        b = _wait(c, r.json()["id"])
-        assert b["status"] == "completed" and b["request_counts"]["completed"] == 5, b
-        out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
-        usage = out[0]["response"]["body"]["usage"]
-        prompt = "<｜begin▁of▁sentence｜><｜User｜>question number 0<｜Assistant｜><think>"
-        assert usage["prompt_tokens"] == len(prompt.encode("utf-8")) and usage["completion_tokens"] == 6
+    """The server with a DeepSeek-V4 model on CPU workers: state slots for window / compressor state, prefix cache
+    off, prompts rendered in the family's chat format (byte tokenizer), a batch completes; two ranks (attention
+    replicated, experts expert-parallel over gloo) produce the tokens of one rank."""
+    texts = []
+    for world in (1, 2):
+        app = create_app(_args(tmp_path / f"w{world}", model="tiny-deepseek-v4", enable_prefix_cache=False,
+                               world_size=world, dist_init_addr=f"127.0.0.1:{29680 + world}"))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            f = _upload(c, _lines(5, max_tokens=6))
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"])
+            assert b["status"] == "completed" and b["request_counts"]["completed"] == 5, b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            out.sort(key=lambda o: o["custom_id"])
+            usage = out[0]["response"]["body"]["usage"]
+            prompt = "<｜begin▁of▁sentence｜><｜User｜>question number 0<｜Assistant｜><think>"
+            assert usage["prompt_tokens"] == len(prompt.encode("utf-8")) and usage["completion_tokens"] == 6
+            texts.append([o["response"]["body"]["choices"][0]["message"]["content"] for o in out])
+    assert texts[0] == texts[1]
