@@ -296,3 +296,35 @@ def test_deepseek_v4_model_serves_chat_batches_in_its_own_format(tmp_path):
             assert usage["prompt_tokens"] == len(prompt.encode("utf-8")) and usage["completion_tokens"] == 6
             texts.append([o["response"]["body"]["choices"][0]["message"]["content"] for o in out])
     assert texts[0] == texts[1]
+
+
+def test_oversubscribed_device_pool_with_a_host_tier_completes_with_the_same_outputs(tmp_path):
+    """Server-level oversubscription: a device pool that holds a fraction of the batch's KV plus a host tier; rows are
+    parked, resumed and (when the host tier is full too) evicted and recomputed, and every request still returns the
+    text of the unconstrained server."""
+    texts, stats = [], []
+    lines = [{"custom_id": f"r{i}", "method": "POST", "url": "/v1/chat/completions",
+              "body": {"model": "tiny", "messages": [{"role": "user", "content": f"request {i}: " + "lorem ipsum " * (2 + i % 3)}],
+                       "max_tokens": 40, "ignore_eos": True}} for i in range(10)]
+    for name, kw in (("big", dict(num_gpu_pages=512)),
+                     ("small", dict(num_gpu_pages=26, host_kv_cache_size=0.0002, max_decode_batch=8))):
+        app = create_app(_args(tmp_path / name, enable_prefix_cache=False, **kw))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            f = _upload(c, lines)
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"], timeout=240)
+            assert b["status"] == "completed" and b["request_counts"]["completed"] == 10, b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
+            done = time.time()
+            beat = None
+            while time.time() - done < 15:                   # the worker's next heartbeat carries the engine counters
+                beat = app.state.scheduler.last_heartbeat
+                if beat and beat["ts"] >= done:
+                    break
+                time.sleep(0.2)
+            stats.append(beat["stats"])
+    assert texts[0] == texts[1]
+    assert stats[0]["holds"] == 0 and stats[0]["evictions"] == 0
+    assert stats[1]["holds"] + stats[1]["evictions"] > 0, stats[1]
