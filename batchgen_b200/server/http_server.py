@@ -259,7 +259,11 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
 
     @app.get("/v1/workers/status")
     def workers_status():
-        return worker.status()
+        st = dict(worker.status())
+        beat = scheduler.last_heartbeat
+        if beat:                         # engine counters, recent steps and memory of the worker's last heartbeat
+            st["heartbeat"] = {k: beat.get(k) for k in ("ts", "live", "free_pages", "stats", "steps", "memory", "query_book")}
+        return st
 
     @app.get("/v1/pool/status")
     def pool_status() -> PoolStatus:
