@@ -198,6 +198,10 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
 
         by_idx: Dict[int, Dict[str, Any]] = {}
         cancelled = set()
+        # BATCHGEN_PROFILE_STEPS=first:last brackets those engine steps with the profiler API for an attached profiler;
+        # BATCHGEN_MEMORY_HISTORY=<dir> records allocator events and writes a snapshot when a step runs out of memory
+        from ..utils.capture_window import CaptureWindow, MemoryHistory
+        window, mem_history = CaptureWindow.from_env(), MemoryHistory.from_env()
         # the token book: prompts live once per node in a shared int32 table; rank 0 binds a slot and writes the
         # prompt, the step broadcast then carries (offset, length) instead of the tokens, and completions are read
         # back from the book (batchgen/query_book.py, batchgen/batchgen_worker.py: node-shared token memfd)
@@ -305,7 +309,16 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                 time.sleep(stuck)                      # host-side fault injection for the watchdog test
                 stuck = 0.0
             if eng.has_work():
-                eng.step()
+                window.before_step()
+                try:
+                    eng.step()
+                except Exception as ex:  # noqa: BLE001 - re-raised: only the allocator snapshot is added here
+                    if "out of memory" in str(ex).lower():
+                        snap = mem_history.dump("oom")
+                        if snap:
+                            log.error("worker.memory_snapshot", rank=rank, path=snap)
+                    raise
+                window.after_step()
                 if feed_counter is not None:
                     feed_counter.value += 1
                 # completed sequences are dropped so that the table does not grow without bound

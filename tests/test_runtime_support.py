@@ -392,3 +392,20 @@ def test_model_contract_names_every_violated_kernel_rule():
     assert model_contract(get_model_config("tiny-deepseek-v3"), 1, False)      # fine on the reference path
     with pytest.raises(PreflightError, match="do not divide"):
         model_contract(get_model_config("minimax-m2.5"), 5, False)
+
+
+def test_capture_window_brackets_the_requested_steps_once():
+    from batchgen_b200.utils.capture_window import CaptureWindow, MemoryHistory, parse_window
+    assert parse_window("3:5") == (3, 5) and parse_window("4:4") == (4, 4)
+    assert parse_window("") is None and parse_window("5:3") is None and parse_window("x:1") is None and parse_window("7") is None
+    events = []
+    w = CaptureWindow((2, 4), start=lambda: events.append(("start", w.step)), stop=lambda: events.append(("stop", w.step)))
+    for _ in range(8):
+        w.before_step()
+        w.after_step()
+    assert events == [("start", 2), ("stop", 4)] and w.done and not w.active
+    off = CaptureWindow(None, start=lambda: events.append("x"), stop=lambda: events.append("y"))
+    for _ in range(3):
+        off.before_step(); off.after_step()
+    assert len(events) == 2
+    assert MemoryHistory("").dump("t") is None              # off: nothing is written
