@@ -140,8 +140,48 @@ class DeepSeekV4Chat:
         return dsv4_encoding.parse_completion(text, "thinking" if enable_thinking else "chat")
 
 
+class HarmonyChat:
+    """A tokenizer whose chat rendering and completion parsing follow the GPT-OSS harmony format
+    (``runtime.harmony``): tools become the developer message's ``functions`` namespace, tool-call history and tool
+    results become call / result messages, completions are split by channel.  ``reasoning_effort`` is written as the
+    system message's ``Reasoning:`` line when the conversation does not set one itself."""
+
+    def __init__(self, base):
+        self.base = base
+        self.name = f"{getattr(base, 'name', 'tokenizer')}+harmony"
+        self.vocab_size, self.bos_token_id, self.eos_token_id = base.vocab_size, base.bos_token_id, base.eos_token_id
+
+    def encode(self, text):
+        return self.base.encode(text)
+
+    def decode(self, ids, skip_special_tokens: bool = True):
+        return self.base.decode(ids, skip_special_tokens=skip_special_tokens)
+
+    def render(self, messages: List[Dict], add_generation_prompt: bool = True, reasoning_effort: Optional[str] = None,
+               tools: Optional[List[Dict]] = None) -> str:
+        from . import harmony
+        msgs = [dict(m) for m in messages]
+        if reasoning_effort:
+            line = f"Reasoning: {reasoning_effort}"
+            if msgs and msgs[0].get("role") == "system":
+                if "Reasoning:" not in (msgs[0].get("content") or ""):
+                    msgs[0]["content"] = line + ("\n" + msgs[0]["content"] if msgs[0].get("content") else "")
+            else:
+                msgs.insert(0, {"role": "system", "content": line})
+        return harmony.render_harmony_prompt(msgs, tools=tools or None, add_generation_prompt=add_generation_prompt)
+
+    def apply_chat_template(self, messages: List[Dict], add_generation_prompt: bool = True,
+                            reasoning_effort: Optional[str] = None, tools: Optional[List[Dict]] = None, **kw) -> List[int]:
+        return self.encode(self.render(messages, add_generation_prompt, reasoning_effort, tools))
+
+    def parse_completion(self, text: str, enable_thinking: bool = True) -> Dict:
+        from . import harmony
+        return harmony.parse_completion(text)
+
+
 def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1, chat_format: Optional[str] = None):
-    """``chat_format="deepseek_v4"`` wraps the tokenizer so that chat requests use that family's prompt format."""
+    """``chat_format`` ("deepseek_v4" or "harmony") wraps the tokenizer so that chat requests use that family's
+    prompt format and completion parser."""
     if spec in ("ids", "", None):
         tok = IdTokenizer(vocab_size, bos, eos)
     elif spec == "bytes":
@@ -150,10 +190,10 @@ def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1, chat_f
         tok = HFTokenizer(spec)
     else:
         raise ValueError(f"unknown tokenizer {spec!r}: use 'ids', 'bytes' or a local tokenizer directory")
-    if chat_format == "deepseek_v4" and not isinstance(tok, IdTokenizer):
-        return DeepSeekV4Chat(tok)
-    if chat_format not in (None, "", "deepseek_v4"):
+    if chat_format not in (None, "", "deepseek_v4", "harmony"):
         raise ValueError(f"unknown chat format {chat_format!r}")
+    if chat_format and not isinstance(tok, IdTokenizer):          # the id tokenizer has no text to render into
+        return DeepSeekV4Chat(tok) if chat_format == "deepseek_v4" else HarmonyChat(tok)
     return tok
 
 

@@ -82,7 +82,7 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
     storage = StorageManager(args.storage_path)
     worker = worker or WorkerManager(args)
     tokenizer = get_tokenizer(args.tokenizer, cfg.vocab_size, cfg.bos_token_id, cfg.eos_token_id,
-                              chat_format="deepseek_v4" if cfg.family == "deepseek_v4" else None)
+                              chat_format={"deepseek_v4": "deepseek_v4", "gpt_oss": "harmony"}.get(cfg.family))
     scheduler = BatchScheduler(storage, worker, args, tokenizer)
     health = ServerHealthState()
     sessions = SessionStore()
