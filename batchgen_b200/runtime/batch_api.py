@@ -50,6 +50,7 @@ class BatchOptions:
     parse_tool_call: bool = False
     include_special_tokens: bool = False
     model: str = ""
+    tool_call_format: str = "json"              # json | glm | kimi | minimax | deepseek (runtime.output_parsers)
 
 
 def parse_batch_lines(lines: Iterable[str], endpoint: Optional[str] = None) -> List[BatchRequest]:
@@ -144,7 +145,8 @@ def result_item(seq: Sequence, req: BatchRequest, tokenizer, opts: BatchOptions)
         elif opts.parse_thinking:
             reasoning, content = split_reasoning(text)
         if opts.parse_tool_call and not hasattr(tokenizer, "parse_completion"):
-            tool_calls, content = parse_tool_calls(content)
+            from .output_parsers import parse_tool_calls as parse_family_calls
+            tool_calls, content = parse_family_calls(content, opts.tool_call_format or "json")
         msg = {"role": "assistant", "content": content, "reasoning_content": reasoning,
                "tool_calls": tool_calls or None}
         choice = {"index": 0, "message": msg, "logprobs": None, "finish_reason": seq.finish_reason}

@@ -82,6 +82,15 @@ class BatchScheduler:
     def enqueue(self, batch: BatchObject) -> None:
         self._prep_q.put(batch.id)
 
+    def _tool_call_format(self) -> str:
+        """The tool-call markup of the served model's family (``runtime.output_parsers``)."""
+        from ..config import get_model_config
+        from ..runtime.output_parsers import FAMILY_FORMAT
+        try:
+            return FAMILY_FORMAT.get(get_model_config(self.args.model).family, "json")
+        except KeyError:
+            return "json"
+
     def _fail_batch(self, b: BatchObject, code: str, message: str, line: Optional[int] = None) -> None:
         b.status = "failed"
         b.failed_at = int(time.time())
@@ -116,7 +125,7 @@ class BatchScheduler:
                                       temperature=b.temperature, top_p=b.top_p, top_k=b.top_k,
                                       parse_thinking=self.args.parse_thinking, parse_tool_call=self.args.parse_tool_call,
                                       include_special_tokens=self.args.detokenization_include_special_tokens,
-                                      model=self.args.model)
+                                      model=self.args.model, tool_call_format=self._tool_call_format())
         budget = (self.capacity or {}).get("kv_token_budget")
 
         def build(req):
