@@ -130,3 +130,78 @@ def execute_plan(engine, plan: Seq[Tuple[int, int, int, int]], rank: int, holder
             recv_sequence(engine, src, group)
             moved += 1
     return moved
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Hand-over between engines that share no process group (the server's data-parallel cohorts): a parked row is
+# packed into one payload (header + tensors), travels as a file or any other byte channel, and is adopted by
+# another engine under a fresh sequence number of that engine.
+def export_sequence(engine, s: Sequence) -> dict:
+    """Pack a row that is ON_HOLD in the host tier and remove it from ``engine``."""
+    if s.status != S.ON_HOLD or not s.host_pages or s.gpu_pages:
+        raise ValueError(f"seq {s.global_idx} is not parked in the host tier")
+    hk = engine.host_kv
+    if getattr(hk, "kv", None) is None or engine.cfg.is_v4:
+        raise NotImplementedError("hand-over covers the paged latent / GQA KV tiers")
+    pages = torch.as_tensor(s.host_pages, dtype=torch.long)
+    has_state = s.state_item >= 0
+    payload = {"header": json.loads(bytes(_pack_header(s, len(s.host_pages), has_state).tolist()).decode()),
+               "kv": hk.kv[:, pages].clone()}
+    payload["header"]["session_id"] = s.session_id
+    if hk.idx_k is not None:
+        payload["idx_k"] = hk.idx_k.view(torch.uint8)[:, pages].clone()
+        payload["idx_s"] = hk.idx_s[:, pages].clone()
+    if has_state:
+        hs = engine.host_state
+        payload["rec"], payload["conv"] = hs.rec[:, s.state_item].clone(), hs.conv[:, s.state_item].clone()
+        hs.release(s.state_item)
+        s.state_item = -1
+    hk.alloc.free(s.host_pages)
+    s.host_pages = []
+    del engine.seqs[s.global_idx]
+    return payload
+
+
+def import_sequence(engine, payload: dict, assigned_rank: int = 0) -> Sequence:
+    """Adopt a packed row: host pages are allocated here, the row becomes ON_HOLD under this engine's next sequence
+    number and resumes like any other parked row.  Raises ``OutOfPages`` when the host tier has no room."""
+    d = payload["header"]
+    hk = engine.host_kv
+    if hk is None:
+        raise RuntimeError("the destination keeps no host tier")
+    pages = hk.alloc.alloc(d["n_pages"])
+    idx = torch.as_tensor(pages, dtype=torch.long)
+    hk.kv[:, idx] = payload["kv"].to(hk.kv.dtype)
+    if hk.idx_k is not None and "idx_k" in payload:
+        hk.idx_k.view(torch.uint8)[:, idx] = payload["idx_k"]
+        hk.idx_s[:, idx] = payload["idx_s"]
+    s = Sequence(global_idx=engine._next_idx, prompt_ids=d["prompt_ids"], params=SamplingParams(**d["params"]),
+                 custom_id=d["custom_id"], batch_id=d["batch_id"])
+    engine._next_idx += 1
+    s.output_ids = list(d["output_ids"])
+    s.num_cached_tokens = d["num_cached_tokens"]
+    s.cached_prefix_tokens = d["cached_prefix_tokens"]
+    s.total_decoded_before_eviction = d["total_decoded_before_eviction"]
+    s.had_initial_gpu_reservation = d["had_initial_gpu_reservation"]
+    s.session_id = d.get("session_id")
+    s.host_pages = pages
+    if d["has_state"]:
+        hs = engine.host_state
+        if hs is None:
+            raise RuntimeError("the destination keeps no host state store")
+        item = hs.reserve()
+        hs.rec[:, item] = payload["rec"]
+        hs.conv[:, item] = payload["conv"]
+        s.state_item = item
+    s.status = S.ON_HOLD
+    s.history.append("adopted from another engine")
+    s.assigned_rank = assigned_rank
+    engine.seqs[s.global_idx] = s
+    return s
+
+
+def parked_rows(engine) -> List[Sequence]:
+    """Rows that can be handed over right now: on hold, KV entirely in the host tier, no step in flight; smallest first."""
+    rows = [s for s in engine.seqs.values()
+            if s.status == S.ON_HOLD and s.host_pages and not s.gpu_pages and not getattr(s, "inflight_tokens", 0)]
+    return sorted(rows, key=lambda s: (len(s.host_pages), s.global_idx))

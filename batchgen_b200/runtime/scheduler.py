@@ -352,3 +352,21 @@ def plan_kv_migration(used_pages_per_node: Seq[int], movable: Dict[int, List[Tup
         plan.append((gid, src, dst, dst * ranks_per_node + rr[dst] % ranks_per_node))
         rr[dst] += 1
     return plan
+
+
+def plan_cohort_handover(stats: Dict[int, Dict[str, int]], in_flight: Seq[int] = ()) -> Optional[Tuple[int, int, int]]:
+    """Data-parallel cohorts with separate engines: when one cohort has rows parked in its host tier (its device pool
+    is full) while another is idle, hand half of the parked rows (at least one) to the idle cohort.
+    ``stats[cohort]`` holds the last heartbeat's ``parked`` (rows that can move), ``live`` (sequences in the engine)
+    and ``host_free`` (free host pages); cohorts in ``in_flight`` already take part in a hand-over.
+    Returns (source, destination, rows) or None."""
+    busy = set(in_flight)
+    src = max((c for c in stats if c not in busy and stats[c].get("parked", 0) > 0),
+              key=lambda c: (stats[c]["parked"], -c), default=None)
+    if src is None:
+        return None
+    idle = [c for c in stats if c != src and c not in busy and stats[c].get("live", 0) == 0 and stats[c].get("host_free", 0) > 0]
+    if not idle:
+        return None
+    dst = max(idle, key=lambda c: (stats[c]["host_free"], -c))
+    return src, dst, max(1, stats[src]["parked"] // 2)

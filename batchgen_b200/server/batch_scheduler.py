@@ -16,6 +16,7 @@ mode :1380-1507, drain loop :1597-1690, completion listener :1762, output writin
 from __future__ import annotations
 
 import concurrent.futures
+import os
 import queue as queue_mod
 import threading
 import time
@@ -50,6 +51,10 @@ class BatchScheduler:
         self._session_cohort: Dict[str, int] = {}
         self.dp_assigned = [0] * dp                   # requests handed to each cohort so far
         self.last_heartbeat: Optional[Dict[str, Any]] = None
+        # hand-over of parked rows between cohorts (runtime.kv_migration.export_sequence / import_sequence)
+        self._cohort_stats: Dict[int, Dict[str, int]] = {}
+        self._handover: Dict[str, Any] = {}           # ticket -> (source, destination)
+        self.migrated_rows = 0
 
     # ------------------------------------------------------------------ lifecycle
     def start(self) -> None:
@@ -206,8 +211,54 @@ class BatchScheduler:
                 self.worker.capacity = m
             elif kind == "heartbeat":
                 self.last_heartbeat = m
+                self._cohort_stats[int(m.get("cohort", 0))] = {k: int(m.get(k, 0)) for k in ("parked", "live", "host_free")}
+                self._maybe_hand_over()
+            elif kind == "migrated_out":
+                self._on_migrated_out(m)
             elif kind == "worker_fatal":
                 self.worker.last_error = m.get("error")
+
+    # ------------------------------------------------------------------ hand-over between cohorts
+    def _handover_dir(self) -> str:
+        import tempfile
+        d = os.path.join(getattr(self.args, "runtime_dir", "") or tempfile.gettempdir(), "handover")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+    def _maybe_hand_over(self) -> None:
+        if getattr(self.worker, "dp", 1) <= 1 or not getattr(self.args, "dp_migration", True):
+            return
+        from ..runtime.scheduler import plan_cohort_handover
+        busy = [c for pair in self._handover.values() for c in pair]
+        plan = plan_cohort_handover(self._cohort_stats, busy)
+        if plan is not None:
+            self.hand_over(*plan)
+
+    def hand_over(self, src: int, dst: int, rows: int) -> str:
+        """Ask cohort ``src`` to pack up to ``rows`` parked rows; they go to ``dst`` when the reply arrives."""
+        ticket = uuid.uuid4().hex[:12]
+        self._handover[ticket] = (src, dst)
+        self._cohort_stats.get(src, {})["parked"] = 0            # until the next heartbeat says otherwise
+        self.worker.send({"type": "migrate_out", "count": rows, "dir": self._handover_dir(), "ticket": ticket, "dst": dst},
+                         cohort=src)
+        return ticket
+
+    def _on_migrated_out(self, m: Dict[str, Any]) -> None:
+        src, dst = self._handover.pop(m.get("ticket"), (int(m.get("cohort", 0)), m.get("dst")))
+        rows = m.get("rows") or []
+        if not rows or dst is None:
+            return
+        for row in rows:                                           # the rows' prefill cost now counts for the new cohort
+            slot = row["meta"]["slot"]
+            done = self._slot_cost.get(slot)
+            if done is not None:
+                self._dp_load[done[0]] = max(0, self._dp_load[done[0]] - done[1])
+                self._dp_load[dst] += done[1]
+                self._slot_cost[slot] = (dst, done[1])
+        self.migrated_rows += len(rows)
+        st = self._cohort_stats.setdefault(dst, {"parked": 0, "live": 0, "host_free": 0})
+        st["live"] = st.get("live", 0) + len(rows)
+        self.worker.send({"type": "migrate_in", "rows": rows}, cohort=dst)
 
     def _on_completion(self, m: Dict[str, Any]) -> None:
         done = self._slot_cost.pop(m.get("slot"), None)

@@ -76,6 +76,8 @@ class ServerArgs:
     decode_step_timeout: float = 120.0
     startup_timeout: float = 1800.0
     watchdog_test_stuck_time: float = 0.0       # fault injection (host side): worker sleeps this long once
+    heartbeat_interval: float = 5.0             # seconds between worker heartbeats (counters, memory, parked rows)
+    dp_migration: bool = True                   # hand parked rows of a loaded cohort to an idle one (--dp-size > 1)
     # logging
     log_dir: str = ""
     log_level: str = "info"

@@ -198,6 +198,7 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
 
         by_idx: Dict[int, Dict[str, Any]] = {}
         cancelled = set()
+        adopt: List[Dict[str, Any]] = []              # rows handed over by another cohort, waiting for host pages
         # BATCHGEN_PROFILE_STEPS=first:last brackets those engine steps with the profiler API for an attached profiler;
         # BATCHGEN_MEMORY_HISTORY=<dir> records allocator events and writes a snapshot when a step runs out of memory
         from ..utils.capture_window import CaptureWindow, MemoryHistory
@@ -280,6 +281,26 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                     running = False
                 elif kind == "end_session":
                     eng.end_session(m["session_id"])
+                elif kind == "migrate_out":
+                    # hand parked rows to another cohort: every rank of this cohort packs its copy of the same rows
+                    # (the scheduler is the same on all of them) into one file per row and rank
+                    from ..runtime import kv_migration
+                    moved = []
+                    rows = [r for r in kv_migration.parked_rows(eng) if not r.session_id and r.global_idx in by_idx]
+                    for i, s_row in enumerate(rows[: int(m.get("count", 1))]):
+                        meta = by_idx.pop(s_row.global_idx)
+                        stem = os.path.join(m["dir"], f'{m["ticket"]}_{i}')
+                        n_pages = len(s_row.host_pages)
+                        torch.save(kv_migration.export_sequence(eng, s_row), f"{stem}.r{rank}.pt")
+                        if rank == 0 and meta.get("qb_slot") is not None:
+                            book.release(meta["qb_slot"])            # the payload carries the tokens from here on
+                        moved.append({"stem": stem, "pages": n_pages,
+                                      "meta": {"slot": meta["slot"], "batch_id": meta["batch_id"],
+                                               "request_id": meta["request_id"]}})
+                    up({"type": "migrated_out", "ticket": m["ticket"], "rows": moved, "dst": m.get("dst")})
+                elif kind == "migrate_in":
+                    from ..runtime import kv_migration
+                    adopt.extend(m["rows"])
                 elif kind == "cancel":
                     cancelled.add(m["batch_id"])
                     for s in list(eng.seqs.values()):
@@ -303,6 +324,22 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                             up({"type": "completion", "slot": e["slot"], "batch_id": e["batch_id"],
                                 "request_id": e["request_id"], "output_ids": [], "prompt_tokens": 0,
                                 "cached_tokens": 0, "finish_reason": f"error: {ex}"})
+            for row in list(adopt):
+                # adopt rows another cohort handed over; a full host tier makes the row wait for the next round
+                from ..runtime import kv_migration
+                from ..runtime.kv_cache import OutOfPages
+                path = f'{row["stem"]}.r{rank}.pt'
+                try:
+                    s_new = kv_migration.import_sequence(eng, torch.load(path, weights_only=True), rank)
+                except OutOfPages:
+                    continue
+                by_idx[s_new.global_idx] = dict(row["meta"], qb_slot=None)
+                adopt.remove(row)
+                try:
+                    os.remove(path)
+                except OSError:
+                    pass
+                log.info("worker.adopted_row", rank=rank, request=row["meta"]["request_id"], pages=row["pages"])
             if not running:
                 break
             if stuck > 0 and eng.has_work():
@@ -324,9 +361,12 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                 # completed sequences are dropped so that the table does not grow without bound
                 for gi in [g for g, s in eng.seqs.items() if s.status.name == "COMPLETED"]:
                     del eng.seqs[gi]
-            if rank == 0 and time.monotonic() - last_beat > 5.0:
+            if rank == 0 and time.monotonic() - last_beat > float(getattr(args, "heartbeat_interval", 5.0)):
                 last_beat = time.monotonic()
+                from ..runtime import kv_migration
                 up({"type": "heartbeat", "ts": time.time(), "live": len(eng.seqs), "free_pages": eng.kv.alloc.num_free,
+                    "parked": len([r for r in kv_migration.parked_rows(eng) if not r.session_id]),
+                    "host_free": eng.host_kv.alloc.num_free if eng.host_kv is not None else 0,
                     "stats": eng.stats.summary(), "steps": eng.step_ring.summary(), "memory": _memory_profile(device),
                     "query_book": {"active": book.active_count,
                                                                   "free_pages": book.free_page_count}})

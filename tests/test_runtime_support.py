@@ -409,3 +409,58 @@ def test_capture_window_brackets_the_requested_steps_once():
         off.before_step(); off.after_step()
     assert len(events) == 2
     assert MemoryHistory("").dump("t") is None              # off: nothing is written
+
+
+def test_plan_cohort_handover_picks_the_loaded_and_the_idle_cohort():
+    from batchgen_b200.runtime.scheduler import plan_cohort_handover as plan
+    assert plan({}) is None
+    assert plan({0: {"parked": 0, "live": 5, "host_free": 9}, 1: {"parked": 0, "live": 0, "host_free": 9}}) is None
+    assert plan({0: {"parked": 4, "live": 9, "host_free": 1}, 1: {"parked": 0, "live": 2, "host_free": 9}}) is None   # nobody idle
+    assert plan({0: {"parked": 5, "live": 9, "host_free": 1}, 1: {"parked": 0, "live": 0, "host_free": 9}}) == (0, 1, 2)
+    assert plan({0: {"parked": 1, "live": 9, "host_free": 1}, 1: {"parked": 0, "live": 0, "host_free": 0},
+                 2: {"parked": 0, "live": 0, "host_free": 7}}) == (0, 2, 1)
+    assert plan({0: {"parked": 5, "live": 9, "host_free": 1}, 1: {"parked": 0, "live": 0, "host_free": 9}}, in_flight=[1]) is None
+
+
+def test_parked_row_moves_between_two_engines_and_keeps_its_tokens():
+    import torch
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.runtime import kv_migration as mig
+    from batchgen_b200.runtime.engine import Engine
+    from batchgen_b200.runtime.sequence import SamplingParams
+    cfg = get_model_config("tiny-deepseek-v3")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(2, cfg.vocab_size, (32,), generator=g).tolist() for _ in range(6)]
+    params = SamplingParams(max_new_tokens=48, ignore_eos=True)
+
+    def mk(pages, host):
+        ecfg = EngineConfig(page_size=16, initial_gpu_page_buffer=2, extension_gpu_page_buffer=1, decision_frequency_pages=1,
+                            max_decode_batch=8)
+        return Engine(build_model(cfg, seed=0), ecfg, num_gpu_pages=pages, num_host_pages=host)
+
+    want = mk(256, 0).generate(prompts, params)
+    a, b = mk(14, 64), mk(64, 64)
+    outs = {}
+    a.on_complete = b.on_complete = lambda s: outs.__setitem__(tuple(s.prompt_ids), list(s.output_ids))
+    for p in prompts:
+        a.add_request(p, params)
+    moved = 0
+    for _ in range(4000):
+        if a.has_work():
+            a.step()
+        if b.has_work():
+            b.step()
+        rows = mig.parked_rows(a)
+        if rows and moved < 3:
+            before = a.host_kv.alloc.num_free
+            payload = mig.export_sequence(a, rows[0])
+            assert a.host_kv.alloc.num_free == before + payload["header"]["n_pages"]
+            s = mig.import_sequence(b, payload)
+            assert s.status.name == "ON_HOLD" and s.global_idx in b.seqs
+            moved += 1
+        if not a.has_work() and not b.has_work():
+            break
+    assert moved > 0
+    assert [outs[tuple(p)] for p in prompts] == want
+    assert a.kv.alloc.num_used == 0 and b.kv.alloc.num_used == 0

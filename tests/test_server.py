@@ -328,3 +328,34 @@ def test_oversubscribed_device_pool_with_a_host_tier_completes_with_the_same_out
     assert texts[0] == texts[1]
     assert stats[0]["holds"] == 0 and stats[0]["evictions"] == 0
     assert stats[1]["holds"] + stats[1]["evictions"] > 0, stats[1]
+
+
+def test_parked_rows_of_a_loaded_cohort_move_to_an_idle_cohort(tmp_path):
+    """--dp-size 2: every request lands on cohort 0 (cohort 1 is made to look loaded), whose small device pool parks
+    rows in its host tier; the heartbeats show parked rows on one side and an idle engine on the other, the server
+    hands rows over (packed to files, adopted under new sequence numbers) and all outputs equal the one-engine run."""
+    lines = [{"custom_id": f"r{i}", "method": "POST", "url": "/v1/chat/completions",
+              "body": {"model": "tiny", "messages": [{"role": "user", "content": f"request {i}: " + "lorem ipsum " * (2 + i % 3)}],
+                       "max_tokens": 100, "ignore_eos": True}} for i in range(8)]
+    texts = []
+    for dp in (1, 2):
+        kw = dict(num_gpu_pages=512) if dp == 1 else dict(num_gpu_pages=20, host_kv_cache_size=0.0004, max_decode_batch=8,
+                                                         heartbeat_interval=0.1)
+        app = create_app(_args(tmp_path / f"dp{dp}", enable_prefix_cache=False, world_size=dp, dp_size=dp,
+                               dist_init_addr=f"127.0.0.1:{29700 + 4 * dp}", **kw))
+        with TestClient(app) as c:
+            assert c.get("/health").status_code == 200, c.get("/health").text
+            sched = app.state.scheduler
+            if dp == 2:
+                sched._dp_load[1] = 10 ** 15                      # cohort 1 looks loaded: the batch goes to cohort 0
+            f = _upload(c, lines)
+            r = c.post("/v1/batches", json={"input_file_id": f["id"], "endpoint": "/v1/chat/completions"})
+            b = _wait(c, r.json()["id"], timeout=300)
+            assert b["status"] == "completed" and b["request_counts"]["completed"] == 8, b
+            out = [json.loads(l) for l in c.get(f"/v1/files/{b['output_file_id']}/content").text.splitlines()]
+            texts.append(sorted((o["custom_id"], o["response"]["body"]["choices"][0]["message"]["content"]) for o in out))
+            if dp == 2:
+                assert sched.dp_assigned == [8, 0]
+                assert sched.migrated_rows > 0, sched._cohort_stats
+                assert not sched._handover
+    assert texts[0] == texts[1]
