@@ -338,9 +338,11 @@ class RankPacking:
 
 
 def pack_wave_ranks(prompts: Sequence[Sequence[int]], n_ranks: int, block_tokens: int, chunk_tokens: int = 131072,
-                    profile: Optional[CostProfile] = None, rounds: int = 14) -> RankPacking:
+                    profile: Optional[CostProfile] = None, rounds: int = 14,
+                    initial_load: Optional[Sequence[float]] = None) -> RankPacking:
     """Families (prompts sharing their first block) stay together; the heaviest family on the slowest rank
-    is split in two while that lowers the predicted makespan (at most ``rounds`` refinements)."""
+    is split in two while that lowers the predicted makespan (at most ``rounds`` refinements).  ``initial_load``
+    is what each rank already carries, in the unit of the score (sum of squared lengths without a profile)."""
     fam: Dict[bytes, List[int]] = {}
     for i, p in enumerate(prompts):
         key = _block_key(p[:block_tokens]) if len(p) > block_tokens else b"solo%d" % i
@@ -353,7 +355,7 @@ def pack_wave_ranks(prompts: Sequence[Sequence[int]], n_ranks: int, block_tokens
         return profile.seconds(*_unit_features(prompts, members, block_tokens, chunk_tokens))
 
     def place(us: List[List[int]]):
-        load = [0.0] * n_ranks
+        load = [float(v) for v in initial_load] if initial_load is not None else [0.0] * n_ranks
         where: List[int] = []
         order = sorted(range(len(us)), key=lambda u: -score(us[u]))
         where = [0] * len(us)

@@ -179,9 +179,7 @@ class BatchScheduler:
                 # data parallelism: longest prompts first, each to the cohort with the smallest running sum of
                 # length^2 (prefill cost); a session stays with the cohort that holds its context
                 # (batchgen/batchgen_worker.py:1987-2033)
-                from ..runtime.scheduler import assign_ranks_l2
-                lens = [len(r.prompt_ids) for _, r in picked]
-                cohorts = assign_ranks_l2(lens, dp, initial_load=self._dp_load)
+                cohorts = self._assign_cohorts([r.prompt_ids for _, r in picked], dp)
                 for i, (slot, r) in enumerate(picked):
                     sid = r.meta.get("session_id")
                     if sid:
@@ -195,6 +193,18 @@ class BatchScheduler:
                             "sampling": r.sampling, "session_id": r.meta.get("session_id")}
                            for (s, r), cc in zip(picked, cohorts) if cc == c]
                 self.worker.send({"type": "admit", "entries": entries}, cohort=c)
+
+    def _assign_cohorts(self, prompts: List[List[int]], dp: int) -> List[int]:
+        """Cohort of each request of one drain.  With prefix reuse on, prompts that share their first page travel
+        together (a cohort computes the shared prefix once; a family is split only when that lowers the predicted
+        makespan: ``wave_plan.pack_wave_ranks``); otherwise every prompt goes, longest first, to the cohort with the
+        smallest running sum of squared lengths."""
+        if getattr(self.args, "enable_prefix_cache", False) and len(prompts) > 1:
+            from ..runtime.wave_plan import pack_wave_ranks
+            return list(pack_wave_ranks(prompts, dp, int(getattr(self.args, "page_size", 64)),
+                                        initial_load=self._dp_load).rank_of)
+        from ..runtime.scheduler import assign_ranks_l2
+        return assign_ranks_l2([len(p) for p in prompts], dp, initial_load=self._dp_load)
 
     # ------------------------------------------------------------------ completions
     def _completion_loop(self) -> None:

@@ -359,3 +359,21 @@ def test_parked_rows_of_a_loaded_cohort_move_to_an_idle_cohort(tmp_path):
                 assert sched.migrated_rows > 0, sched._cohort_stats
                 assert not sched._handover
     assert texts[0] == texts[1]
+
+
+def test_cohort_assignment_keeps_prefix_families_together_when_prefix_reuse_is_on():
+    from types import SimpleNamespace
+    from batchgen_b200.server.batch_scheduler import BatchScheduler
+    sched = BatchScheduler.__new__(BatchScheduler)
+    sched._dp_load = [0, 0]
+    fam_a, fam_b = list(range(100, 180)), list(range(300, 380))
+    prompts = [fam_a + [i] * 5 for i in range(4)] + [fam_b + [i] * 9 for i in range(4)] + [[7, 8, 9]]
+    sched.args = SimpleNamespace(enable_prefix_cache=True, page_size=16)
+    got = sched._assign_cohorts(prompts, 2)
+    assert len(set(got[:4])) == 1 and len(set(got[4:8])) == 1 and got[0] != got[4]
+    sched.args = SimpleNamespace(enable_prefix_cache=False, page_size=16)
+    spread = sched._assign_cohorts(prompts, 2)
+    assert len(set(spread[:4])) == 2                       # without reuse the family is spread by cost
+    sched._dp_load = [10 ** 9, 0]
+    sched.args = SimpleNamespace(enable_prefix_cache=True, page_size=16)
+    assert set(sched._assign_cohorts(prompts, 2)) == {1}   # the loaded cohort gets nothing
