@@ -593,6 +593,10 @@ class EngineConfig:
     cuda_graph_num_buckets: int = 16
     enable_prefix_cache: bool = False
     adaptive_chunk: bool = False
+    adaptive_chunk_min: int = 1024              # bounds, smoothing and head-room of the adaptive host-KV chunk
+    adaptive_chunk_max: int = 65536
+    adaptive_chunk_ema_alpha: float = 0.1
+    adaptive_chunk_multiplier: float = 1.5
     # parallel layout
     world_size: int = 1
     attn_tp_size: int = 1                       # TP degree of attention (1 = DP attention)

@@ -132,7 +132,10 @@ class Engine:
         from .continuous_batching import AdaptiveChunkSizer
         # host-KV reservation chunk follows the decode lengths actually seen (EMA), from the configured start value
         self.chunk_sizer = AdaptiveChunkSizer(initial_chunk=ecfg.host_kv_chunk_size,
-                                              min_chunk=min(1024, ecfg.host_kv_chunk_size))
+                                              min_chunk=min(ecfg.adaptive_chunk_min, ecfg.host_kv_chunk_size),
+                                              max_chunk=max(ecfg.adaptive_chunk_max, ecfg.host_kv_chunk_size),
+                                              ema_alpha=ecfg.adaptive_chunk_ema_alpha,
+                                              multiplier=ecfg.adaptive_chunk_multiplier)
         from ..utils.step_ring import StepRing
         self.step_ring = StepRing(256)                     # the most recent forwards, for heartbeats and fatal messages
         self._deferred_gpu: List[tuple] = []               # (transfer tasks, device pages freed when they are done)

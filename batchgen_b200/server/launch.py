@@ -17,6 +17,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(f"invalid flags: {e}", file=sys.stderr)
         return 2
     log = eventlog.configure_process("server", args.log_dir or None, args.log_level, console=True)
+    from .server_args import REFERENCE_ACCEPTED
+    for flag in getattr(args, "accepted_reference_flags", []):
+        log.info("flag.accepted_without_effect", flag="--" + flag.replace("_", "-"), reason=REFERENCE_ACCEPTED[flag])
     try:
         for line in run_all_preflights(args):
             log.info("preflight", result=line)

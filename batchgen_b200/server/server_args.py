@@ -45,6 +45,10 @@ class ServerArgs:
     host_kv_region: str = ""                   # set by the server: path of the node-shared host KV region's descriptor
     host_kv_chunk_size: int = 8192
     adaptive_chunk: bool = False
+    adaptive_chunk_min: int = 1024
+    adaptive_chunk_max: int = 65536
+    adaptive_chunk_ema_alpha: float = 0.1
+    adaptive_chunk_multiplier: float = 1.5
     max_decode_batch: int = 512
     max_prefill_tokens: int = 131072
     # offload
@@ -75,6 +79,7 @@ class ServerArgs:
     watchdog_timeout: float = 600.0
     decode_step_timeout: float = 120.0
     startup_timeout: float = 1800.0
+    startup_phase_timeout_scale: float = 1.0    # stretches the per-phase stall limits of the startup watchdog
     watchdog_test_stuck_time: float = 0.0       # fault injection (host side): worker sleeps this long once
     heartbeat_interval: float = 5.0             # seconds between worker heartbeats (counters, memory, parked rows)
     dp_migration: bool = True                   # hand parked rows of a loaded cohort to an idle one (--dp-size > 1)
@@ -117,15 +122,47 @@ class ServerArgs:
             enable_cuda_graph=self.enable_cuda_graph and not self.disable_cuda_graphs,
             cuda_graph_max_bucket_size=self.cuda_graph_max_bucket_size,
             cuda_graph_num_buckets=self.cuda_graph_num_buckets, enable_prefix_cache=self.enable_prefix_cache,
-            adaptive_chunk=self.adaptive_chunk, world_size=self.world_size, attn_tp_size=tp,
+            adaptive_chunk=self.adaptive_chunk, adaptive_chunk_min=self.adaptive_chunk_min,
+            adaptive_chunk_max=self.adaptive_chunk_max, adaptive_chunk_ema_alpha=self.adaptive_chunk_ema_alpha,
+            adaptive_chunk_multiplier=self.adaptive_chunk_multiplier, world_size=self.world_size, attn_tp_size=tp,
             ep_size=self.world_size, moe_comm=self.moe_comm, expert_offload_ratio=self.ep_offloading_ratio,
             decode_attn_split=("heads" if self.decode_attn_split == "auto" else self.decode_attn_split),
             max_state_slots=self.max_state_slots,
             max_host_state_items=self.max_host_state_items, seed=self.seed)
 
 
+# Flags of the reference server that name the same setting differently here (reference flag -> field, converter).
+REFERENCE_ALIASES = {
+    "listen_ip": ("host", str), "listen_port": ("port", int), "max_pool_size": ("max_intake_capacity", int),
+    "watchdog_heartbeat_interval": ("heartbeat_interval", float), "lane_lease_manifest_fd": ("lane_manifest_fd", int),
+    "runtime_mode": ("run_mode", str), "runtime_identity": ("instance_id", str),
+    "input_ids_pool_size_gb": ("query_book_mb", lambda v: max(1, int(float(v) * 1024))),
+}
+# Flags of the reference that have no counterpart to set: accepted (a launch script written for the reference keeps
+# working) and reported once in the log with the reason.
+REFERENCE_ACCEPTED = {
+    "enable_host_kv_eviction": "eviction is always on with a host tier", "host_kv_eviction_watermark": "eviction is growth-driven",
+    "enable_prepack": "prefill micro-batches are always packed", "enable_deepep": "the fused NVLink kernels are the exchange",
+    "gpu_arch": "sm_100a only", "hf_cache_dir": "checkpoints are local directories", "pynccl_port_base": "no separate NCCL communicator",
+    "pynccl_port_span": "no separate NCCL communicator", "replicated_weights": "weights live once per node in the shared store",
+    "persistent_phase_instances": "one engine serves prefill and decode", "pre_dequantize_weights": "MXFP4 experts run on the W4A16 kernels",
+    "glm5_disable_decode_host_kv_staging": "no staging path to disable", "save_result": "results are stored as batch output files",
+    "prefix_cache_debug_stats": "prefix statistics are always in the heartbeat", "shared_prefix_admission": "shared prefixes are always charged once",
+    "enable_decode_preemption": "rows are parked at page boundaries whenever the pool runs short", "fast_init": "weights are random unless a checkpoint is given",
+    "enable_hugetlbfs": "the weight store asks for huge pages itself", "distributed_weight_config": "one node: the weight daemon is not started",
+    "restart_control_addr": "one node: the restart coordinator uses the rendezvous address",
+}
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser("batchgen_b200 server", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    compat = p.add_argument_group("flags of the reference server (aliases and accepted no-ops)")
+    for name, (field, conv) in REFERENCE_ALIASES.items():
+        compat.add_argument("--" + name.replace("_", "-"), dest=field, type=conv, default=argparse.SUPPRESS,
+                            help=f"same as --{field.replace('_', '-')}")
+    for name, why in REFERENCE_ACCEPTED.items():
+        compat.add_argument("--" + name.replace("_", "-"), dest="_accepted_" + name, nargs="?", const=True,
+                            default=argparse.SUPPRESS, help=f"accepted, no effect: {why}")
     for f in dataclasses.fields(ServerArgs):
         flag = "--" + f.name.replace("_", "-")
         if f.type in ("bool", bool):
@@ -190,5 +227,8 @@ def validate_server_args(a: ServerArgs) -> ServerArgs:
 
 
 def prepare_server_args(argv: Optional[List[str]] = None) -> ServerArgs:
-    ns = build_parser().parse_args(argv)
-    return validate_server_args(ServerArgs(**vars(ns)))
+    ns = vars(build_parser().parse_args(argv))
+    accepted = sorted(k[len("_accepted_"):] for k in ns if k.startswith("_accepted_"))
+    args = validate_server_args(ServerArgs(**{k: v for k, v in ns.items() if not k.startswith("_accepted_")}))
+    args.accepted_reference_flags = accepted             # launch.py logs them with the reason each has no effect
+    return args

@@ -152,7 +152,12 @@ class WorkerManager:
                 self._kill_all()
                 self.state = "failed"
                 raise WorkerStartError(self.last_error)
-            stalled = self.startup.stalled(self.startup_budgets)
+            budgets = self.startup_budgets
+            scale = float(getattr(self.args, "startup_phase_timeout_scale", 1.0) or 1.0)
+            if scale != 1.0:                     # slow storage or a very large checkpoint: stretch every phase's limit
+                from .startup_phases import DEFAULT_BUDGETS
+                budgets = {k: v * scale for k, v in (budgets or DEFAULT_BUDGETS).items()}
+            stalled = self.startup.stalled(budgets)
             if stalled:
                 slot, phase, sec, limit = stalled[0]
                 who = f"rank {slot}" if slot < self.args.world_size else "the server"

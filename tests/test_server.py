@@ -377,3 +377,23 @@ def test_cohort_assignment_keeps_prefix_families_together_when_prefix_reuse_is_o
     sched._dp_load = [10 ** 9, 0]
     sched.args = SimpleNamespace(enable_prefix_cache=True, page_size=16)
     assert set(sched._assign_cohorts(prompts, 2)) == {1}   # the loaded cohort gets nothing
+
+
+def test_flags_of_the_reference_server_are_understood():
+    from batchgen_b200.server.server_args import REFERENCE_ACCEPTED
+    a = prepare_server_args(["--listen-ip", "0.0.0.0", "--listen-port", "9001", "--max-pool-size", "2048",
+                             "--watchdog-heartbeat-interval", "2.5", "--runtime-mode", "exclusive",
+                             "--input-ids-pool-size-gb", "0.5", "--enable-prepack", "--fast-init", "--gpu-arch", "sm_100a",
+                             "--adaptive-chunk", "--adaptive-chunk-min", "512", "--adaptive-chunk-multiplier", "2.0",
+                             "--startup-phase-timeout-scale", "3"])
+    assert (a.host, a.port, a.max_intake_capacity, a.heartbeat_interval, a.query_book_mb) == ("0.0.0.0", 9001, 2048, 2.5, 512)
+    assert a.accepted_reference_flags == ["enable_prepack", "fast_init", "gpu_arch"]
+    assert all(k in REFERENCE_ACCEPTED for k in a.accepted_reference_flags)
+    e = a.engine_config()
+    assert e.adaptive_chunk and e.adaptive_chunk_min == 512 and e.adaptive_chunk_multiplier == 2.0
+    assert a.startup_phase_timeout_scale == 3.0
+    from batchgen_b200.models import build_model
+    from batchgen_b200.config import get_model_config
+    from batchgen_b200.runtime.engine import Engine
+    eng = Engine(build_model(get_model_config("tiny-deepseek-v3"), seed=0), e, num_gpu_pages=32)
+    assert eng.chunk_sizer.min_chunk == 512 and eng.chunk_sizer.multiplier == 2.0
