@@ -19,73 +19,73 @@ from ..config import EngineConfig, list_models
 @dataclass
 class ServerArgs:
     # model / paths
-    model: str = "tiny-deepseek-v3"
-    cache_dir: str = ""
-    converted_ckpt_dir: str = ""
-    tokenizer: str = "ids"
+    model: str = "tiny-deepseek-v3"         # preset name or a Hugging Face style id (config.get_model_config)
+    cache_dir: str = ""                     # directory for derived files (converted shards, staged stores)
+    converted_ckpt_dir: str = ""            # checkpoint in the converted format (ckpt.converter); empty = random weights
+    tokenizer: str = "ids"                  # ids | bytes | a local tokenizer directory
     # topology
-    world_size: int = 1
-    nnodes: int = 1
-    node_rank: int = 0
-    dist_init_addr: str = "127.0.0.1:29600"
+    world_size: int = 1                     # GPUs (ranks) of this server
+    nnodes: int = 1                         # nodes of the deployment (one box: 1)
+    node_rank: int = 0                      # this node's index
+    dist_init_addr: str = "127.0.0.1:29600" # host:port of the ranks' rendezvous
     attn_tp_size: int = 0                       # 0 = world_size (TP attention), 1 = data-parallel attention
     device: str = "auto"                        # auto | cuda | cpu
     # memory
     host_kv_cache_size: float = 0.0             # GB of pinned host KV (overflow tier)
-    kv_dtype: str = "bf16"
-    gpu_memory_frac: float = 0.9
-    num_gpu_pages: int = 0
-    max_model_len: int = -1
-    page_size: int = 64
+    kv_dtype: str = "bf16"                  # dtype of the paged KV (bf16)
+    gpu_memory_frac: float = 0.9            # share of device memory the engine may use (KV pool = what the weights leave of it)
+    num_gpu_pages: int = 0                  # KV pages on the device; 0 = sized from free memory
+    max_model_len: int = -1                 # longest prompt + completion admitted; -1 = what the pool holds
+    page_size: int = 64                     # tokens per KV page
     # scheduling
-    initial_gpu_page_buffer: int = 32
-    extension_gpu_page_buffer: int = 4
-    decision_frequency_pages: int = 2
-    host_kv_watermark: int = 70
+    initial_gpu_page_buffer: int = 32       # pages reserved ahead of a row when it starts decoding
+    extension_gpu_page_buffer: int = 4      # pages added at every growth decision
+    decision_frequency_pages: int = 2       # growth / hold decisions are taken every this many pages of progress
+    host_kv_watermark: int = 70             # percent of free host KV above which parked rows are brought back eagerly
     host_kv_region: str = ""                   # set by the server: path of the node-shared host KV region's descriptor
-    host_kv_chunk_size: int = 8192
-    adaptive_chunk: bool = False
-    adaptive_chunk_min: int = 1024
-    adaptive_chunk_max: int = 65536
-    adaptive_chunk_ema_alpha: float = 0.1
-    adaptive_chunk_multiplier: float = 1.5
-    max_decode_batch: int = 512
-    max_prefill_tokens: int = 131072
+    host_kv_chunk_size: int = 8192          # tokens of host KV reserved per parked row at a time
+    adaptive_chunk: bool = False            # let the chunk follow the completed decode lengths (EMA)
+    adaptive_chunk_min: int = 1024          # lower bound of the adaptive chunk, tokens
+    adaptive_chunk_max: int = 65536         # upper bound of the adaptive chunk, tokens
+    adaptive_chunk_ema_alpha: float = 0.1   # smoothing of the decode-length average
+    adaptive_chunk_multiplier: float = 1.5  # head-room over the average
+    max_decode_batch: int = 512             # decode rows per step
+    max_prefill_tokens: int = 131072        # tokens of one packed prefill micro-batch; longer prompts are prefilled in pieces
     # offload
-    enable_ep_with_offloading: bool = False
-    ep_offloading_ratio: float = 0.0
+    enable_ep_with_offloading: bool = False # keep part of the routed experts in host memory and stream them
+    ep_offloading_ratio: float = 0.0        # fraction of a rank's experts kept in host memory
     # graphs
-    enable_cuda_graph: bool = True
-    disable_cuda_graphs: bool = False
-    cuda_graph_max_bucket_size: int = 128
-    cuda_graph_num_buckets: int = 16
+    enable_cuda_graph: bool = True          # capture decode steps as CUDA graphs
+    disable_cuda_graphs: bool = False       # overrides --enable-cuda-graph
+    cuda_graph_max_bucket_size: int = 128   # largest captured batch bucket
+    cuda_graph_num_buckets: int = 16        # number of batch buckets
     # prefix
-    enable_prefix_cache: bool = False
+    enable_prefix_cache: bool = False       # page-level prefix reuse (device cache + host coordinator, in-wave sharing, session frontiers)
     # comm
     moe_comm: str = "fused"                     # fused (in-kernel NVLink exchange) | nccl (collective baseline)
     fused_max_tokens: int = 16384               # largest step (prefill micro-batch) of the fused path; sizes its heap
     decode_attn_split: str = "auto"             # heads | requests (rows pinned to owner ranks inside the TP group) | auto:
                                                 # requests on the fused multi-GPU path of an MLA model, heads otherwise
     # recurrent state (models with KDA layers)
-    max_state_slots: int = 0
-    max_host_state_items: int = 0
+    max_state_slots: int = 0                # sequences holding per-sequence state at once; 0 = max_decode_batch
+    max_host_state_items: int = 0           # parked states in host memory; 0 = 4 x the device slots
     # output
-    parse_thinking: bool = False
-    parse_tool_call: bool = False
-    detokenization_include_special_tokens: bool = False
-    storage_path: str = "./batchgen_storage"
-    incremental_output_dir: str = ""
+    parse_thinking: bool = False            # split reasoning from content in chat responses
+    parse_tool_call: bool = False           # parse the family's tool-call markup into tool_calls
+    detokenization_include_special_tokens: bool = False  # keep special tokens in the returned text
+    storage_path: str = "./batchgen_storage"   # directory of uploaded files, batches and outputs
+    incremental_output_dir: str = ""        # append each finished request's item here as it completes (crash-resilient)
     # watchdogs
-    watchdog_timeout: float = 600.0
-    decode_step_timeout: float = 120.0
-    startup_timeout: float = 1800.0
+    watchdog_timeout: float = 600.0         # seconds without engine progress before the watchdog acts; 0 = off
+    decode_step_timeout: float = 120.0      # seconds one decode step may take
+    startup_timeout: float = 1800.0         # seconds the workers get to become ready
     startup_phase_timeout_scale: float = 1.0    # stretches the per-phase stall limits of the startup watchdog
     watchdog_test_stuck_time: float = 0.0       # fault injection (host side): worker sleeps this long once
     heartbeat_interval: float = 5.0             # seconds between worker heartbeats (counters, memory, parked rows)
     dp_migration: bool = True                   # hand parked rows of a loaded cohort to an idle one (--dp-size > 1)
     # logging
-    log_dir: str = ""
-    log_level: str = "info"
+    log_dir: str = ""                       # JSONL event logs, flight recorder and stack dumps go here
+    log_level: str = "info"                 # debug | info | warning | error
     # http
     weight_store_stage_dir: str = ""            # copy the converted checkpoint here first (local NVMe) and verify it
     shared_weight_store: bool = True            # load the converted checkpoint once into a node-shared region
@@ -97,17 +97,17 @@ class ServerArgs:
     runtime_root: str = ""                      # directory of the host / instance / run locks
     lane_manifest_fd: int = -1                  # inherited descriptor of the launcher's lane manifest
     lane_gpus: str = ""                         # leased GPU UUIDs (default: CUDA_VISIBLE_DEVICES)
-    lane_lock_root: str = ""
+    lane_lock_root: str = ""                    # directory of the per-GPU / per-port lane locks
     runtime_dir: str = ""                       # set by the server: this run's directory (workers take its run lock)
     run_id: str = ""                            # set by the server
-    host: str = "127.0.0.1"
-    port: int = 8000
+    host: str = "127.0.0.1"                 # listen address
+    port: int = 8000                        # listen port
     # capacity
-    max_intake_capacity: int = 1_000_000
-    scheduling_slots: int = 4096
+    max_intake_capacity: int = 1_000_000    # requests the intake pool holds before new batches are refused
+    scheduling_slots: int = 4096            # requests in flight on the workers at once
     # cluster
-    cluster_fail_fast: bool = True
-    seed: int = 0
+    cluster_fail_fast: bool = True          # a lost rank takes the cohort down at once (no hang on the next collective)
+    seed: int = 0                           # seed of sampling and of random weights
 
     def engine_config(self) -> EngineConfig:
         tp = self.attn_tp_size or self.world_size
@@ -232,3 +232,41 @@ def prepare_server_args(argv: Optional[List[str]] = None) -> ServerArgs:
     args = validate_server_args(ServerArgs(**{k: v for k, v in ns.items() if not k.startswith("_accepted_")}))
     args.accepted_reference_flags = accepted             # launch.py logs them with the reason each has no effect
     return args
+
+
+def flags_markdown() -> str:
+    """The flag reference (``docs/server-flags.md``): one table per section of ``ServerArgs``, read from this file's
+    own field comments.  ``python -m batchgen_b200.server.server_args > docs/server-flags.md`` regenerates it."""
+    import re
+    rows, section = [], ""
+    for line in open(__file__, encoding="utf-8").read().split("@dataclass\nclass ServerArgs:")[1].split("def engine_config")[0].splitlines():
+        m = re.match(r"\s{4}# (.+)$", line)
+        if m:
+            section = m.group(1).strip()
+            continue
+        m = re.match(r"\s{4}([a-z_0-9]+):\s*([A-Za-z\[\], \.]+?)\s*=\s*(.+?)(?:\s+#\s*(.*))?$", line)
+        if m:
+            rows.append((section, m.group(1), m.group(2), m.group(3).strip(), (m.group(4) or "").strip()))
+    out = ["# Server flags", "",
+           "`python -m batchgen_b200.server.launch [flags]`.  Every field of `server/server_args.py::ServerArgs` is a flag",
+           "(`--field-name`; boolean fields that default to on also take `--no-field-name`).  This page is generated from",
+           "that dataclass: `python -m batchgen_b200.server.server_args > docs/server-flags.md`."]
+    current = None
+    for sec, name, typ, default, note in rows:
+        if sec != current:
+            out += ["", f"## {sec}", "", "| flag | type | default | meaning |", "|---|---|---|---|"]
+            current = sec
+        out.append(f"| `--{name.replace('_', '-')}` | {typ} | `{default}` | {note.replace('|', 'or')} |")
+    out += ["", "## Flags of the reference server", "",
+            "A launch script written for the reference keeps working: these names are understood as well.", "",
+            "| reference flag | here |", "|---|---|"]
+    for k, (field, _) in REFERENCE_ALIASES.items():
+        extra = " (GB are converted to MiB)" if k == "input_ids_pool_size_gb" else ""
+        out.append(f"| `--{k.replace('_', '-')}` | same as `--{field.replace('_', '-')}`{extra} |")
+    for k, why in REFERENCE_ACCEPTED.items():
+        out.append(f"| `--{k.replace('_', '-')}` | accepted, no effect: {why} |")
+    return "\n".join(out) + "\n"
+
+
+if __name__ == "__main__":
+    print(flags_markdown(), end="")
