@@ -1,8 +1,7 @@
 """Python client of the batch HTTP API.
 
     client = BatchGenHttpClient("http://127.0.0.1:8000")
-    batch = client.submit_batch("requests.jsonl", max_decoding_length=1024)     # upload + create
-    batch = client.wait_for_batch(batch["id"])
+    batch = client.submit_batch("requests.jsonl", max_decoding_length=1024)     # upload + create + wait
     text = client.download_file_content(batch["output_file_id"])
 
 Method names and behaviour follow the reference client (batchgen/batchgen_client.py; docs/client-api.md):
@@ -93,9 +92,21 @@ class BatchGenHttpClient:
                 raise TimeoutError(f"batch {batch_id} still {b['status']} after {timeout_s} s")
             time.sleep(poll_s)
 
-    def submit_batch(self, path_or_lines, endpoint: str = "/v1/chat/completions", **engine_options) -> Dict[str, Any]:
+    def submit_batch(self, path_or_lines, output_file_path: Optional[str] = None, endpoint: str = "/v1/chat/completions",
+                     poll_interval: float = 0.5, timeout: Optional[float] = None, wait: bool = True,
+                     **engine_options) -> Dict[str, Any]:
+        """Upload, create and (unless ``wait=False``) wait for the batch; with ``output_file_path`` the output JSONL is
+        saved there.  ``engine_options``: ``max_decoding_length``, ``temperature``, ``top_p``, ``top_k``, ``metadata``.
+        Use ``upload_file`` + ``create_batch`` to keep several batches in flight."""
         f = self.upload_file(path_or_lines)
-        return self.create_batch(f["id"], endpoint=endpoint, **engine_options)
+        batch = self.create_batch(f["id"], endpoint=endpoint, **engine_options)
+        if not wait:
+            return batch
+        batch = self.wait_for_batch(batch["id"], poll_s=poll_interval, timeout_s=timeout)
+        if output_file_path and batch.get("output_file_id"):
+            with open(output_file_path, "w", encoding="utf-8") as out:
+                out.write(self.download_file_content(batch["output_file_id"]))
+        return batch
 
     def download_file_content(self, file_id: str) -> str:
         return self._request("GET", f"/v1/files/{file_id}/content").text

@@ -44,8 +44,7 @@ def run_server(path: str, url: str, timeout_s: float) -> dict:
     from batchgen_b200.server.client import BatchGenHttpClient as BatchGenClient
     c = BatchGenClient(url)
     t0 = time.perf_counter()
-    batch = c.submit_batch(path, endpoint="/v1/completions")
-    batch = c.wait_for_batch(batch["id"], timeout_s=timeout_s)
+    batch = c.submit_batch(path, endpoint="/v1/completions", timeout=timeout_s)
     dt = time.perf_counter() - t0
     res = c.results(batch) if batch.get("output_file_id") else []
     return {"mode": "server", "bct_s": dt, "status": batch.get("status"), "completed": len(res),

@@ -82,6 +82,27 @@ def test_batch_round_trip_and_api_surface(server):
     assert c.post("/v1/batches", json={"input_file_id": "file-missing"}).status_code == 404
 
 
+def test_python_client_against_the_server(server, tmp_path):
+    """The client's blocking and step-by-step paths (the FastAPI test client stands in for the HTTP session)."""
+    from batchgen_b200.server.client import BatchGenHttpClient, LegacyInferenceDeprecated
+    c, app = server
+    cl = BatchGenHttpClient("", session=c)
+    assert cl.health_check() and cl.list_models()[0]["id"] == "tiny-deepseek-v3"
+    out_path = tmp_path / "out.jsonl"
+    done = cl.submit_batch(_lines(3), output_file_path=str(out_path), max_decoding_length=8)
+    assert done["status"] == "completed" and len(out_path.read_text().splitlines()) == 3
+    assert len(cl.results(done)) == 3
+    f = cl.upload_file(_lines(2))
+    b = cl.create_batch(f["id"], endpoint="/v1/chat/completions", temperature=0.0)
+    assert b["status"] in ("validating", "in_progress", "finalizing", "completed")
+    assert cl.wait_for_batch(b["id"], poll_s=0.1, timeout_s=120)["status"] == "completed"
+    pending = cl.submit_batch(_lines(1), wait=False)
+    assert cl.wait_for_batch(pending["id"], poll_s=0.1, timeout_s=120)["request_counts"]["completed"] == 1
+    assert "state" in cl.workers_status()
+    with pytest.raises(LegacyInferenceDeprecated):
+        cl.submit_inference("x")
+
+
 def test_invalid_file_and_per_request_errors(server):
     c, _ = server
     r = c.post("/v1/files", files={"file": ("bad.jsonl", b"{not json\n", "application/jsonl")}, data={"purpose": "batch"})
