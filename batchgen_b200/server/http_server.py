@@ -276,8 +276,14 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
     def health_route():
         st = "ok" if (health.startup_complete and worker.state == "ready") else (
             "failed" if worker.state == "failed" else "starting")
-        body = HealthResponse(status=st, startup_complete=health.startup_complete, workers=worker.state,
-                              detail=health.detail or worker.last_error)
+        detail = health.detail or worker.last_error
+        if st == "starting" and not detail and getattr(worker, "startup", None) is not None:
+            try:                                   # where every worker is in its start-up: "worker 0: model-build (12 s)"
+                snap = worker.startup.snapshot()
+                detail = "; ".join(f"worker {k}: {p} ({int(t)} s)" for k, (p, t) in sorted(snap.items())) or None
+            except Exception:  # noqa: BLE001 - the record may be gone while the cohort is being replaced
+                detail = None
+        body = HealthResponse(status=st, startup_complete=health.startup_complete, workers=worker.state, detail=detail)
         return JSONResponse(body.model_dump(), status_code=200 if st == "ok" else 503)
 
     @app.post("/v1/inference")
