@@ -103,6 +103,19 @@ def test_python_client_against_the_server(server, tmp_path):
         cl.submit_inference("x")
 
 
+def test_concurrent_chat_driver_walks_sessions_against_the_server(server, tmp_path):
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks"))
+    import batch_driver
+    from batchgen_b200.server.client import BatchGenHttpClient
+    c, app = server
+    path = tmp_path / "chat.jsonl"
+    path.write_text("\n".join(json.dumps(l) for l in _lines(6, max_tokens=3)) + "\n")
+    res = batch_driver.run_concurrent_chat(str(path), "", 120.0, 3, client=BatchGenHttpClient("", session=c))
+    assert res["turns"] == 6 and res["clients"] == 3 and not res["errors"], res
+    assert res["turn_latency_s"]["max"] >= res["turn_latency_s"]["p50"] > 0
+
+
 def test_invalid_file_and_per_request_errors(server):
     c, _ = server
     r = c.post("/v1/files", files={"file": ("bad.jsonl", b"{not json\n", "application/jsonl")}, data={"purpose": "batch"})
