@@ -360,7 +360,7 @@ def test_weight_daemon_serves_local_and_remote_modules_with_prefetch(tmp_path):
         assert st["ready_hits"] >= 1                              # prefetch ran ahead of the worker at least once
         assert st["transport_failed"] is False and st["fetch_ms"]["count"] == st["fetches"]
         served = daemons[1].status()["bytes_served"]             # a prefetch may be in flight between the two reads
-        assert st["bytes_fetched"] <= served <= st["bytes_fetched"] + 2 * 4096
+        assert st["bytes_fetched"] <= served <= st["bytes_fetched"] + 3 * 4096   # at most the staging slots
         c.close()
     finally:
         for d in daemons:
