@@ -156,5 +156,47 @@ def host_memory(args) -> List[str]:
     return [f"host plan fits MemTotal {total >> 30} GiB"]
 
 
+def _gpu_name() -> str:
+    """Name of GPU 0 through NVML (no CUDA context is created in the server process); "b200" when NVML is not there."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            name = pynvml.nvmlDeviceGetName(pynvml.nvmlDeviceGetHandleByIndex(0))
+        finally:
+            pynvml.nvmlShutdown()
+        return name.decode() if isinstance(name, bytes) else str(name)
+    except Exception:  # noqa: BLE001
+        return "b200"
+
+
+def deployment_plan(args) -> List[str]:
+    """The per-GPU memory plan of the model on this machine (weights, experts, workspace, what is left for KV), as
+    one log line; on a GPU a plan that leaves nothing for KV is refused unless the pool size is given explicitly."""
+    from ..config import get_model_config
+    from ..runtime import planner
+    try:
+        import torch
+        on_gpu = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
+    except Exception:  # noqa: BLE001 - no torch / no driver: plan for the CPU profile
+        on_gpu = False
+    name = _gpu_name() if on_gpu else "cpu"
+    if not on_gpu:
+        return ["deployment plan: CPU run, sized by --num-gpu-pages"]
+    cfg = get_model_config(args.model)
+    world = max(1, args.world_size // max(1, getattr(args, "dp_size", 1)))
+    machine = planner.MACHINES[planner.machine_family(name)]
+    ecfg = args.engine_config()
+    ecfg.world_size = ecfg.attn_tp_size = ecfg.ep_size = world
+    plan = planner.plan_deployment(cfg, ecfg, machine)
+    gib = lambda b: f"{b / 2 ** 30:.1f} GiB"
+    line = (f"deployment plan ({machine.name}, {world} GPUs per cohort): dense {gib(plan.weight_bytes)}, experts "
+            f"{gib(plan.expert_bytes)}, workspace + graphs {gib(plan.workspace_bytes + plan.graph_bytes)}, KV {gib(plan.kv_bytes)} "
+            f"= {plan.kv_token_capacity} tokens per GPU")
+    if not plan.fits and not args.num_gpu_pages:
+        raise PreflightError(f"{line}; {plan.note}")
+    return [line if plan.fits else f"{line}; {plan.note} (continuing: --num-gpu-pages is set)"]
+
+
 def run_all_preflights(args) -> List[str]:
-    return launch_readiness(args) + runtime_preflight(args) + host_memory(args)
+    return launch_readiness(args) + runtime_preflight(args) + host_memory(args) + deployment_plan(args)

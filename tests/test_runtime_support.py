@@ -464,3 +464,21 @@ def test_parked_row_moves_between_two_engines_and_keeps_its_tokens():
     assert moved > 0
     assert [outs[tuple(p)] for p in prompts] == want
     assert a.kv.alloc.num_used == 0 and b.kv.alloc.num_used == 0
+
+
+def test_deployment_plan_preflight_reports_and_refuses(monkeypatch):
+    import torch
+    from batchgen_b200.server import preflight
+    from batchgen_b200.server.server_args import ServerArgs
+    assert "CPU run" in preflight.deployment_plan(ServerArgs(model="tiny-deepseek-v3", device="cpu"))[0]
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(preflight, "_gpu_name", lambda: "NVIDIA B200")
+    line = preflight.deployment_plan(ServerArgs(model="deepseek-v3-671b", device="cuda", world_size=8))[0]
+    assert "b200, 8 GPUs per cohort" in line and "experts 76.1 GiB" in line
+    with pytest.raises(preflight.PreflightError) as e:
+        preflight.deployment_plan(ServerArgs(model="kimi-k3", device="cuda", world_size=8))
+    assert "ep-offloading-ratio" in str(e.value)
+    ok = preflight.deployment_plan(ServerArgs(model="kimi-k3", device="cuda", world_size=8, num_gpu_pages=1024))[0]
+    assert "continuing" in ok
+    two = preflight.deployment_plan(ServerArgs(model="gpt-oss-120b", device="cuda", world_size=8, dp_size=2))[0]
+    assert "4 GPUs per cohort" in two
