@@ -136,13 +136,18 @@ def execute_plan(engine, plan: Seq[Tuple[int, int, int, int]], rank: int, holder
 # Hand-over between engines that share no process group (the server's data-parallel cohorts): a parked row is
 # packed into one payload (header + tensors), travels as a file or any other byte channel, and is adopted by
 # another engine under a fresh sequence number of that engine.
+def can_export(engine) -> bool:
+    hk = getattr(engine, "host_kv", None)
+    return hk is not None and getattr(hk, "kv", None) is not None and not engine.cfg.is_v4
+
+
 def export_sequence(engine, s: Sequence) -> dict:
     """Pack a row that is ON_HOLD in the host tier and remove it from ``engine``."""
     if s.status != S.ON_HOLD or not s.host_pages or s.gpu_pages:
         raise ValueError(f"seq {s.global_idx} is not parked in the host tier")
     hk = engine.host_kv
-    if getattr(hk, "kv", None) is None or engine.cfg.is_v4:
-        raise NotImplementedError("hand-over covers the paged latent / GQA KV tiers")
+    if not can_export(engine):
+        raise NotImplementedError("hand-over covers the paged latent / GQA KV of the torch host tier")
     pages = torch.as_tensor(s.host_pages, dtype=torch.long)
     has_state = s.state_item >= 0
     payload = {"header": json.loads(bytes(_pack_header(s, len(s.host_pages), has_state).tolist()).decode()),
@@ -201,7 +206,11 @@ def import_sequence(engine, payload: dict, assigned_rank: int = 0) -> Sequence:
 
 
 def parked_rows(engine) -> List[Sequence]:
-    """Rows that can be handed over right now: on hold, KV entirely in the host tier, no step in flight; smallest first."""
+    """Rows that can be handed over right now: on hold, KV entirely in the host tier, no step in flight; smallest first.
+    Empty when this engine's host tier cannot be packed by ``export_sequence`` (the native region, whose rows would move
+    by page ownership instead, and the DeepSeek-V4 pools)."""
+    if not can_export(engine):
+        return []
     rows = [s for s in engine.seqs.values()
             if s.status == S.ON_HOLD and s.host_pages and not s.gpu_pages and not getattr(s, "inflight_tokens", 0)]
     return sorted(rows, key=lambda s: (len(s.host_pages), s.global_idx))

@@ -288,6 +288,8 @@ def worker_main(rank: int, world: int, args, request_queue, response_queue, read
                     moved = []
                     rows = [r for r in kv_migration.parked_rows(eng) if not r.session_id and r.global_idx in by_idx]
                     for i, s_row in enumerate(rows[: int(m.get("count", 1))]):
+                        if not kv_migration.can_export(eng):
+                            break
                         meta = by_idx.pop(s_row.global_idx)
                         stem = os.path.join(m["dir"], f'{m["ticket"]}_{i}')
                         n_pages = len(s_row.host_pages)

@@ -495,3 +495,16 @@ def test_bench_reference_arm_prints_one_json_line_and_exits_zero():
     assert r.returncode == 0, r.stderr[-500:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and ("unavailable" in line or "value" in line)
+
+
+def test_rows_of_tiers_that_cannot_be_packed_are_never_offered_for_hand_over():
+    import torch
+    from batchgen_b200.config import EngineConfig, get_model_config
+    from batchgen_b200.models import build_model
+    from batchgen_b200.runtime import kv_migration as mig
+    from batchgen_b200.runtime.engine import Engine
+    ecfg = EngineConfig(page_size=16, max_decode_batch=4, max_state_slots=4)
+    v4 = Engine(build_model(get_model_config("tiny-deepseek-v4"), seed=0), ecfg, num_gpu_pages=16, num_host_pages=16)
+    assert not mig.can_export(v4) and mig.parked_rows(v4) == []
+    plain = Engine(build_model(get_model_config("tiny-deepseek-v3"), seed=0), EngineConfig(page_size=16), num_gpu_pages=16)
+    assert not mig.can_export(plain) and mig.parked_rows(plain) == []      # no host tier at all
