@@ -101,3 +101,40 @@ def parse_tool_calls(text: str, fmt: str = "json") -> Tuple[List[Dict], str]:
             continue
         calls.append(_call(len(calls), obj.get("name", ""), obj.get("arguments", {})))
     return calls, _JSON_CALL.sub("", text).strip()
+
+
+def audit_output_file(path: str, fmt: str = "json") -> Dict[str, int]:
+    """Re-parse the raw texts of a batch output file (written without ``--parse-tool-call``) and count what the parser
+    finds: items, items with calls, calls, calls whose arguments are not valid JSON, and items that still contain an
+    opening call marker after parsing (markup the parser did not understand)."""
+    markers = {"json": "<tool_call>", "glm": "<tool_call>", "kimi": "<|tool_call_begin|>", "minimax": "<minimax:tool_call>",
+               "deepseek": "<｜tool▁call▁begin｜>"}
+    out = {"items": 0, "with_calls": 0, "calls": 0, "bad_arguments": 0, "leftover_markup": 0}
+    with open(path, encoding="utf-8") as f:
+        for line in f:
+            if not line.strip():
+                continue
+            item = json.loads(line)
+            body = ((item.get("response") or {}).get("body") or {})
+            for choice in body.get("choices", []):
+                text = (choice.get("message") or {}).get("content") or choice.get("text") or ""
+                calls, rest = parse_tool_calls(text, fmt)
+                out["items"] += 1
+                out["with_calls"] += bool(calls)
+                out["calls"] += len(calls)
+                for c in calls:
+                    try:
+                        json.loads(c["function"]["arguments"])
+                    except ValueError:
+                        out["bad_arguments"] += 1
+                out["leftover_markup"] += markers.get(fmt, "<tool_call>") in rest
+    return out
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser(description="count the tool calls a batch output file's texts parse into")
+    ap.add_argument("output_file")
+    ap.add_argument("--format", default="json", choices=["json", "glm", "kimi", "minimax", "deepseek"])
+    a = ap.parse_args()
+    print(json.dumps(audit_output_file(a.output_file, a.format)))

@@ -65,3 +65,14 @@ def test_family_table_and_batch_api_hook():
     msg = item["response"]["body"]["choices"][0]["message"]
     assert msg["reasoning_content"] == "use the tool" and msg["content"] == ""
     assert _fn(msg["tool_calls"]) == [("lookup", {"k": "v"})]
+
+
+def test_audit_of_an_output_file(tmp_path):
+    from batchgen_b200.runtime.output_parsers import audit_output_file
+    def item(text):
+        return {"custom_id": "x", "response": {"body": {"choices": [{"message": {"content": text}}]}}}
+    texts = ["plain answer", "<tool_call>f<arg_key>a</arg_key><arg_value>1</arg_value></tool_call>",
+             "<tool_call>g</tool_call><tool_call>h</tool_call>", "broken <tool_call>never closed"]
+    p = tmp_path / "out.jsonl"
+    p.write_text("\n".join(json.dumps(item(t)) for t in texts) + "\n")
+    assert audit_output_file(str(p), "glm") == {"items": 4, "with_calls": 2, "calls": 3, "bad_arguments": 0, "leftover_markup": 1}
