@@ -179,6 +179,11 @@ class HarmonyChat:
         return harmony.parse_completion(text)
 
 
+def chat_format_for(family: str) -> Optional[str]:
+    """The Python-rendered chat format of a model family (None: the tokenizer's own template)."""
+    return {"deepseek_v4": "deepseek_v4", "gpt_oss": "harmony"}.get(family)
+
+
 def get_tokenizer(spec: str, vocab_size: int, bos: int = 0, eos: int = 1, chat_format: Optional[str] = None):
     """``chat_format`` ("deepseek_v4" or "harmony") wraps the tokenizer so that chat requests use that family's
     prompt format and completion parser."""

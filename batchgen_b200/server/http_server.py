@@ -23,7 +23,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse
 
 from ..config import get_model_config
 from ..runtime import batch_api
-from ..runtime.tokenization import get_tokenizer
+from ..runtime.tokenization import chat_format_for, get_tokenizer
 from .batch_scheduler import BatchScheduler
 from .io_struct import (BatchList, BatchObject, CreateBatchRequest, CreateSessionRequest, FileDeleted, FileList,
                         HealthResponse, ModelCard, ModelList, PoolStatus, SessionObject, TurnRequest, TurnResponse)
@@ -82,7 +82,7 @@ def create_app(args: ServerArgs, worker: Optional[WorkerManager] = None, start_w
     storage = StorageManager(args.storage_path)
     worker = worker or WorkerManager(args)
     tokenizer = get_tokenizer(args.tokenizer, cfg.vocab_size, cfg.bos_token_id, cfg.eos_token_id,
-                              chat_format={"deepseek_v4": "deepseek_v4", "gpt_oss": "harmony"}.get(cfg.family))
+                              chat_format=chat_format_for(cfg.family))
     scheduler = BatchScheduler(storage, worker, args, tokenizer)
     health = ServerHealthState()
     sessions = SessionStore()
