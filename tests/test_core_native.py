@@ -447,3 +447,41 @@ def test_distributed_module_source_reads_local_and_remote_modules(tmp_path):
     finally:
         for d in daemons:
             d.stop()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_slot_kv_storage_with_heterogeneous_decode_attention(mode):
+    """Slot-based host KV: decode attention on the host kernel (mode 1), through the double-buffered device copy
+    (mode 0, on CPU tensors here) and split between both (mode 2) equals the reference attention over the same rows."""
+    from batchgen_b200.runtime.hetero_attention import HeteroAttention, SlotKVStorage
+    torch.manual_seed(1)
+    layers, Hq, Hkv, D = 2, 8, 2, 64
+    st = SlotKVStorage(layers, slots=4, max_len=48, num_kv_heads=Hkv, head_dim=D)
+    lens = [5, 40, 33]
+    slots = [st.acquire() for _ in lens]
+    kv = {}
+    for l in range(layers):
+        for s, L in zip(slots, lens):
+            k, v = torch.randn(L, Hkv, D), torch.randn(L, Hkv, D)
+            st.write(l, s, 0, k[: L - 1], v[: L - 1])           # the prompt ...
+            st.write(l, s, L - 1, k[L - 1:], v[L - 1:])         # ... and the decoded token
+            kv[(l, s)] = (k.bfloat16().float(), v.bfloat16().float())
+    assert [st.lens[s] for s in slots] == lens and st.num_free == 1
+    att = HeteroAttention(st, Hq, mode=mode, device="cpu", host_fraction=0.5, threads=4, max_batch=4)
+    for l in range(layers):
+        if mode != 1 and l + 1 < layers:
+            att.prefetch(l + 1, slots, lens)                    # the next layer streams in while this one computes
+        q = torch.randn(len(lens), Hq, D)
+        for window in (0, 16):
+            out = att.decode(l, q, slots, lens, window=window)
+            for b, (s, L) in enumerate(zip(slots, lens)):
+                k, v = kv[(l, s)]
+                want = ref.gqa_attention(q[b:b + 1], k, v, D ** -0.5, q_start=L - 1, window=window)[0]
+                assert torch.allclose(out[b], want, atol=2e-4, rtol=1e-3), (mode, l, b, window)
+    if mode == 2:
+        assert att.host_rows > 0 and att.device_rows > 0
+    with pytest.raises(ValueError):
+        st.write(0, slots[0], 47, torch.zeros(2, Hkv, D), torch.zeros(2, Hkv, D))
+    for s in slots:
+        st.release(s)
+    assert st.num_free == 4
