@@ -75,6 +75,8 @@ class BatchScheduler:
         self._quiesced.set()
 
     def resume(self) -> None:
+        self._handover.clear()              # a replaced cohort neither answers an open hand-over nor keeps its counters
+        self._cohort_stats.clear()
         self._quiesced.clear()
 
     def has_work(self) -> bool:
