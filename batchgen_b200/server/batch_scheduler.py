@@ -53,7 +53,7 @@ class BatchScheduler:
         self.last_heartbeat: Optional[Dict[str, Any]] = None
         # hand-over of parked rows between cohorts (runtime.kv_migration.export_sequence / import_sequence)
         self._cohort_stats: Dict[int, Dict[str, int]] = {}
-        self._handover: Dict[str, Any] = {}           # ticket -> (source, destination)
+        self._handover: Dict[str, Any] = {}           # ticket -> (source, destination, time asked)
         self.migrated_rows = 0
 
     # ------------------------------------------------------------------ lifecycle
@@ -241,7 +241,10 @@ class BatchScheduler:
         if getattr(self.worker, "dp", 1) <= 1 or not getattr(self.args, "dp_migration", True):
             return
         from ..runtime.scheduler import plan_cohort_handover
-        busy = [c for pair in self._handover.values() for c in pair]
+        now = time.monotonic()
+        for ticket in [t for t, v in self._handover.items() if now - v[2] > 60.0]:
+            del self._handover[ticket]                            # the source never answered: stop waiting for it
+        busy = [c for v in self._handover.values() for c in v[:2]]
         plan = plan_cohort_handover(self._cohort_stats, busy)
         if plan is not None:
             self.hand_over(*plan)
@@ -249,14 +252,14 @@ class BatchScheduler:
     def hand_over(self, src: int, dst: int, rows: int) -> str:
         """Ask cohort ``src`` to pack up to ``rows`` parked rows; they go to ``dst`` when the reply arrives."""
         ticket = uuid.uuid4().hex[:12]
-        self._handover[ticket] = (src, dst)
+        self._handover[ticket] = (src, dst, time.monotonic())
         self._cohort_stats.get(src, {})["parked"] = 0            # until the next heartbeat says otherwise
         self.worker.send({"type": "migrate_out", "count": rows, "dir": self._handover_dir(), "ticket": ticket, "dst": dst},
                          cohort=src)
         return ticket
 
     def _on_migrated_out(self, m: Dict[str, Any]) -> None:
-        src, dst = self._handover.pop(m.get("ticket"), (int(m.get("cohort", 0)), m.get("dst")))
+        src, dst = self._handover.pop(m.get("ticket"), (int(m.get("cohort", 0)), m.get("dst"), 0.0))[:2]
         rows = m.get("rows") or []
         if not rows or dst is None:
             return
